@@ -1,0 +1,230 @@
+/*
+ * shady_attn.h — C ABI of the B200 (sm_100a) attention hot path of shady-thinker.
+ *
+ * Scope: KV-cache append with Q/K RMSNorm + (m)RoPE, single-token GQA decode attention over
+ * the KV cache (split-KV + log-sum-exp merge), causal prefill attention, and the sigmoid
+ * output gate that directly follows.  These are the entry points a CUDA backend of the
+ * reference's `GpuContext` (src/gpu.rs) binds for the three private `Model` helpers
+ * `fused_split_qknorm_kvstore`, `gqa_attention` and `sigmoid_mul_gate`
+ * (src/model.rs:486-593).  Each declaration cites the reference interface it replaces.
+ *
+ * Conventions
+ *  - Every function returns an int status (SHADY_OK == 0).  Nothing aborts or throws
+ *    across this boundary; `shady_last_error` gives the message of the last failure on a
+ *    context.  (The reference panics instead: gpu.rs:43,68,271.)
+ *  - All launches are asynchronous on the context's stream and stream-ordered, which gives
+ *    the pass-to-pass ordering the reference gets from one compute pass per dispatch
+ *    (gpu.rs:223-231).  Parameters travel by value, so the reference's "flush before
+ *    overwriting the shared uniform" (model.rs:348-353) has no counterpart.
+ *  - The caller owns every buffer.  Ops allocate nothing; scratch memory is an explicit
+ *    workspace argument whose size `shady_decode_workspace_size` reports.
+ *  - A context is not thread-safe: one context per host thread per device.
+ *  - Pointers named `d_*` or documented "device" are device pointers; everything else is
+ *    host memory.
+ */
+#ifndef SHADY_ATTN_H
+#define SHADY_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ---------------------------------------------------------------- */
+#define SHADY_OK 0
+#define SHADY_ERR_BAD_ARG 1      /* null pointer, zero size, inconsistent parameters        */
+#define SHADY_ERR_UNSUPPORTED 2  /* shape/dtype outside what the kernels cover (hd > 256 …) */
+#define SHADY_ERR_CUDA 3         /* a CUDA runtime call failed; see shady_last_error        */
+#define SHADY_ERR_WORKSPACE 4    /* workspace missing or too small                          */
+#define SHADY_ERR_TIMEOUT 5      /* a bounded device-side wait gave up                      */
+
+/* ---- storage dtypes ----------------------------------------------------------------- */
+#define SHADY_F32 0
+#define SHADY_F16 1
+#define SHADY_BF16 2
+
+typedef struct shady_ctx shady_ctx;
+
+/* ===================================================================================== */
+/* Context and buffers — replaces GpuContext (src/gpu.rs:7-297)                          */
+/* ===================================================================================== */
+
+/* GpuContext::new (gpu.rs:17).  `device` is the CUDA ordinal.  `stream` may be NULL (the
+ * context creates its own non-blocking stream) or an existing cudaStream_t, which is the
+ * counterpart of GpuContext::from_device_queue (gpu.rs:24). */
+int shady_ctx_create(int device, void *stream, shady_ctx **out);
+int shady_ctx_destroy(shady_ctx *ctx);
+/* Message of the last non-zero status on this context ("" if none).  With ctx == NULL,
+ * the message of the last failed shady_ctx_create on this thread. */
+const char *shady_last_error(const shady_ctx *ctx);
+/* The cudaStream_t the context launches on. */
+void *shady_ctx_stream(const shady_ctx *ctx);
+/* Number of kernels this context has launched so far (bookkeeping for benchmarks). */
+uint64_t shady_ctx_launch_count(const shady_ctx *ctx);
+
+/* create_storage_buffer (gpu.rs:95); size is rounded up to 4 bytes as in gpu.rs:86. */
+int shady_buffer_create(shady_ctx *ctx, size_t bytes, void **d_out);
+int shady_buffer_free(shady_ctx *ctx, void *d_buf);
+/* write_buffer (gpu.rs:278): host -> device at byte offset, stream-ordered. */
+int shady_buffer_write(shady_ctx *ctx, void *d_buf, size_t offset, const void *src, size_t bytes);
+/* read_buffer (gpu.rs:252): device -> host, blocks until the data has arrived. */
+int shady_buffer_read(shady_ctx *ctx, const void *d_buf, size_t offset, void *dst, size_t bytes);
+/* copy_buffer (gpu.rs:245). */
+int shady_buffer_copy(shady_ctx *ctx, const void *d_src, void *d_dst, size_t bytes);
+/* flush (gpu.rs:237): launches are already submitted, so this only reports a pending
+ * asynchronous error. */
+int shady_flush(shady_ctx *ctx);
+/* device.poll(Maintain::Wait) (gpu.rs:116,270). */
+int shady_synchronize(shady_ctx *ctx);
+
+/* ===================================================================================== */
+/* KV cache addressing shared by the ops                                                 */
+/* ===================================================================================== */
+
+/* Each sequence's cache is rows [pos][num_kv_heads][head_dim], contiguous, K and V in
+ * separate buffers — the reference layout (gqa_attention_head.wgsl:64,
+ * fused_split_qknorm_kvstore.wgsl:220).  Sequence s lives at d_k_ptrs[s] when the pointer
+ * arrays are given, else at d_k_base + s * seq_stride elements. */
+typedef struct {
+    void *d_k_base;
+    void *d_v_base;
+    uint64_t seq_stride;     /* elements between consecutive sequences (ignored with ptr arrays) */
+    void *const *d_k_ptrs;   /* device array [num_seqs] of device pointers, or NULL */
+    void *const *d_v_ptrs;
+    uint32_t dtype;          /* SHADY_F32 / SHADY_F16 / SHADY_BF16 */
+} shady_kv_cache;
+
+/* ===================================================================================== */
+/* KV append: Q/gate split + Q/K RMSNorm(1+w) + partial (m)RoPE + cache store            */
+/* replaces Model::fused_split_qknorm_kvstore (model.rs:486-513) and                     */
+/* fused_split_qknorm_kvstore.wgsl:106-230                                               */
+/* ===================================================================================== */
+
+typedef struct {
+    /* header of the reference uniform (fused_split_qknorm_kvstore.wgsl:12-16) */
+    uint32_t num_heads;
+    uint32_t num_kv_heads;
+    uint32_t head_dim;        /* <= 256 as in the shader */
+    float eps;
+    /* constants model.rs:32-54 bakes into the shader source */
+    float rope_theta;
+    uint32_t rotary_dim;      /* PARTIAL_DIM; even, <= head_dim; 0 = no rotation */
+    uint32_t s1_limit;        /* MROPE_S1_LIMIT (reference: rotary_dim/2) */
+    uint32_t s2_limit;        /* MROPE_S2_LIMIT (reference: rotary_dim/2) */
+    uint32_t interleaved;     /* MROPE_INTERLEAVED: pairs (2i,2i+1) else (i, i+rotary_dim/2) */
+    /* batching (extension: the reference appends one token of one sequence per dispatch) */
+    uint32_t num_seqs;
+    uint32_t tokens_per_seq;  /* 1 for decode, T for prefill; token (s,j) sits at row s*T+j */
+    /* dtypes */
+    uint32_t in_dtype;        /* q_proj_full / k_proj / v_proj */
+    uint32_t q_dtype;         /* q_out */
+    uint32_t has_gate;        /* 1: q_proj_full rows are [Q|gate] (2*head_dim); 0: Q only */
+    uint32_t write_k_back;    /* 1: normed+rotated K also overwrites k_proj (wgsl:224) */
+    uint32_t _pad;
+} shady_append_params;
+
+/* d_q_proj_full [tokens][nh][(1+has_gate)*hd], d_k_proj / d_v_proj [tokens][nkv][hd] in in_dtype.
+ * d_q_out [tokens][nh][hd] in q_dtype.  d_q_gate [tokens][nh][hd] f32 (may be NULL when
+ * has_gate == 0).  d_qk_norm_bf16: bf16 weights, q [hd] then k [hd] (model.rs:157-166), or
+ * NULL to skip the RMSNorm.  d_pos_start [num_seqs] u32: token (s,j) has RoPE position and
+ * cache row pos_start[s]+j (model.rs:493-496 writes one value into all four position
+ * fields).  d_pos_h / d_pos_w: optional per-sequence start positions of the height/width
+ * mRoPE sections; NULL = same as d_pos_start. */
+int shady_kv_append_rope(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full,
+                         void *d_k_proj, const void *d_v_proj, void *d_q_out, float *d_q_gate,
+                         const shady_kv_cache *cache, const uint16_t *d_qk_norm_bf16,
+                         const uint32_t *d_pos_start, const uint32_t *d_pos_h,
+                         const uint32_t *d_pos_w);
+
+/* ===================================================================================== */
+/* Decode attention — replaces Model::gqa_attention (model.rs:516-573),                  */
+/* gqa_attention_head.wgsl:30-124 and gqa_reduce.wgsl:20-65                               */
+/* ===================================================================================== */
+
+typedef struct {
+    /* the reference's Params (gqa_attention_head.wgsl:9-18); seq_len moved to d_seq_lens */
+    uint32_t head_dim;
+    uint32_t num_kv_heads;
+    uint32_t num_q_heads;
+    uint32_t heads_per_kv;
+    uint32_t num_splits;      /* >=1: every sequence is cut into this many ceil(L/ns) ranges as in
+                                 wgsl:46-48.  0: automatic, length-balanced (needs seq_lens_host). */
+    /* batching + dtypes (extensions) */
+    uint32_t num_seqs;
+    uint32_t q_dtype;         /* SHADY_F32 or the cache dtype */
+    uint32_t out_dtype;       /* SHADY_F32 or the cache dtype */
+} shady_decode_params;
+
+/* Bytes of scratch `shady_attn_decode` needs for these parameters (upper bound over any
+ * sequence lengths; 0 when num_splits == 1). */
+int shady_decode_workspace_size(const shady_decode_params *p, size_t *bytes);
+
+/* d_q [num_seqs][nh][hd]; d_seq_lens [num_seqs] u32 = rows to attend to, *including* the
+ * token just appended (model.rs:521).  d_out [num_seqs][nh][hd].  d_lse: optional
+ * [num_seqs][nh] f32 log-sum-exp of each output row (needed to merge shards of one
+ * sequence across GPUs); NULL to skip.  d_gate: optional [num_seqs][nh][hd] f32; when given
+ * the output is multiplied by sigmoid(gate) (fuses Model::sigmoid_mul_gate, model.rs:576).
+ * seq_lens_host: the same lengths in host memory, used only to balance the split plan when
+ * num_splits == 0 (may be NULL otherwise).  A sequence of length 0 yields zeros and
+ * lse = -inf. */
+int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
+                      const shady_kv_cache *cache, const uint32_t *d_seq_lens,
+                      const uint32_t *seq_lens_host, void *d_out, float *d_lse, const float *d_gate,
+                      void *d_workspace, size_t workspace_bytes);
+
+/* Split-level output of the decode kernel without the merge: d_partials receives the
+ * reference layout [nh][num_splits][hd+2] ([hd] = lse, [hd+1] = running max) for ONE
+ * sequence (gqa_attention_head.wgsl:112-123).  Requires num_seqs == 1, num_splits >= 2. */
+int shady_attn_decode_partials(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
+                               const shady_kv_cache *cache, const uint32_t *d_seq_lens,
+                               float *d_partials);
+
+/* gqa_reduce.wgsl:20-65 with its Params {head_dim, num_splits, num_heads}.  Generalised by
+ * two strides (in floats) so that both the reference layout (split_stride = hd+2,
+ * head_stride = ns*(hd+2)) and rank-major gathered shards (split_stride = nh*(hd+2),
+ * head_stride = hd+2) merge with the same kernel.  Splits whose lse is -inf or NaN (empty
+ * ranges) get weight 0 and are not read.  d_gate as in shady_attn_decode. */
+int shady_attn_reduce(shady_ctx *ctx, uint32_t head_dim, uint32_t num_splits, uint32_t num_heads,
+                      uint64_t split_stride, uint64_t head_stride, const float *d_partials,
+                      void *d_out, uint32_t out_dtype, const float *d_gate);
+
+/* ===================================================================================== */
+/* Causal prefill attention — the batched form of the reference's token loop             */
+/* (src/inference.rs:93-95: out[t] = attend(q_t, K[0..=t], V[0..=t]))                    */
+/* ===================================================================================== */
+
+typedef struct {
+    uint32_t head_dim;        /* 128 */
+    uint32_t num_kv_heads;
+    uint32_t num_q_heads;
+    uint32_t num_seqs;        /* batch */
+    uint32_t seq_len;         /* T tokens per sequence, rows [0,T) of each cache */
+    uint32_t dtype;           /* SHADY_BF16 or SHADY_F16: Q, cache and output */
+} shady_prefill_params;
+
+/* d_q [num_seqs][T][nh][hd] (already normed/rotated by shady_kv_append_rope, which also
+ * wrote rows [0,T) of the cache); d_out same shape.  Requires cache.d_k_base addressing with
+ * seq_stride (one allocation) because the tiles are fetched through TMA tensor maps. */
+int shady_attn_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_q,
+                       const shady_kv_cache *cache, void *d_out);
+
+/* ===================================================================================== */
+/* Output gate — replaces Model::sigmoid_mul_gate (model.rs:576-593), sigmoid_mul.wgsl    */
+/* ===================================================================================== */
+/* x[i] *= 1/(1+exp(-gate[i])) in place (the reference needs a temp + copy: model.rs:584-592). */
+int shady_sigmoid_mul(shady_ctx *ctx, float *d_x, const float *d_gate, uint32_t n);
+
+/* ===================================================================================== */
+/* Synthetic data — counter-based N(0,1) fill used by the benchmark and the tests         */
+/* (no reference counterpart: the reference has no benchmark inputs).                     */
+/* ===================================================================================== */
+/* Element i of d_dst = randn(seed, tensor_id, first_idx + i) rounded to `dtype`. */
+int shady_fill_randn(shady_ctx *ctx, void *d_dst, uint64_t n, uint32_t dtype, uint64_t seed,
+                     uint64_t tensor_id, uint64_t first_idx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHADY_ATTN_H */

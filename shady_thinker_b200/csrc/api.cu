@@ -1,0 +1,212 @@
+// extern "C" surface of libshady_attn.so: context, buffers and op entry points declared in
+// include/shady_attn.h.  No torch types, no exceptions across the boundary.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace shady {
+
+static thread_local std::string g_create_error;
+
+int fail(shady_ctx *ctx, int code, const std::string &msg) {
+    if (ctx) ctx->err = msg;
+    else g_create_error = msg;
+    return code;
+}
+
+// launchers implemented in the kernel translation units
+size_t decode_workspace_bytes(const shady_ctx *ctx, const shady_decode_params *p, uint32_t kv_dtype);
+int launch_decode(shady_ctx *, const shady_decode_params *, const void *, const shady_kv_cache *, const uint32_t *,
+                  const uint32_t *, void *, float *, const float *, void *, size_t, float *);
+int launch_reduce(shady_ctx *, uint32_t, uint32_t, uint32_t, uint64_t, uint64_t, const float *, void *, uint32_t,
+                  const float *);
+int launch_sigmoid_mul(shady_ctx *, float *, const float *, uint32_t);
+int launch_append(shady_ctx *, const shady_append_params *, const void *, void *, const void *, void *, float *,
+                  const shady_kv_cache *, const uint16_t *, const uint32_t *, const uint32_t *, const uint32_t *);
+int launch_prefill(shady_ctx *, const shady_prefill_params *, const void *, const shady_kv_cache *, void *);
+
+// ---- counter-based N(0,1): the device twin of oracle_randn_at ---------------------------
+__host__ __device__ inline unsigned long long mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__global__ void fill_randn_kernel(void *dst, unsigned long long n, uint32_t dtype, unsigned long long key,
+                                  unsigned long long first_idx) {
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const unsigned long long r = mix64(key + first_idx + i);
+        const double u1 = ((double)((r >> 40) & 0xFFFFFFull) + 1.0) * (1.0 / 16777216.0);
+        const double u2 = (double)((r >> 8) & 0xFFFFFFull) * (1.0 / 16777216.0);
+        const float v = (float)(sqrt(-2.0 * log(u1)) * cos(6.283185307179586476925 * u2));
+        store_from_f32(dst, i, dtype, v);
+    }
+}
+
+}  // namespace shady
+
+using namespace shady;
+
+extern "C" {
+
+int shady_ctx_create(int device, void *stream, shady_ctx **out) {
+    if (!out) return fail(nullptr, SHADY_ERR_BAD_ARG, "ctx_create: null out pointer");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess) return fail(nullptr, SHADY_ERR_CUDA, std::string("cudaGetDeviceCount: ") + cudaGetErrorString(e));
+    if (device < 0 || device >= count) return fail(nullptr, SHADY_ERR_BAD_ARG, "ctx_create: no such CUDA device");
+    if ((e = cudaSetDevice(device)) != cudaSuccess)
+        return fail(nullptr, SHADY_ERR_CUDA, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+    cudaDeviceProp prop{};
+    if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess)
+        return fail(nullptr, SHADY_ERR_CUDA, std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e));
+    if (prop.major != 10)
+        return fail(nullptr, SHADY_ERR_UNSUPPORTED, "ctx_create: this library is built for sm_100a (B200) only");
+    shady_ctx *c = new (std::nothrow) shady_ctx();
+    if (!c) return fail(nullptr, SHADY_ERR_BAD_ARG, "ctx_create: out of host memory");
+    c->device = device;
+    c->num_sms = prop.multiProcessorCount;
+    if (stream) {
+        c->stream = reinterpret_cast<cudaStream_t>(stream);
+    } else {
+        if ((e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking)) != cudaSuccess) {
+            delete c;
+            return fail(nullptr, SHADY_ERR_CUDA, std::string("cudaStreamCreate: ") + cudaGetErrorString(e));
+        }
+        c->owns_stream = true;
+    }
+    *out = c;
+    return SHADY_OK;
+}
+
+int shady_ctx_destroy(shady_ctx *ctx) {
+    if (!ctx) return SHADY_ERR_BAD_ARG;
+    if (ctx->owns_stream) {
+        cudaSetDevice(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+        cudaStreamDestroy(ctx->stream);
+    }
+    delete ctx;
+    return SHADY_OK;
+}
+
+const char *shady_last_error(const shady_ctx *ctx) { return ctx ? ctx->err.c_str() : g_create_error.c_str(); }
+void *shady_ctx_stream(const shady_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
+uint64_t shady_ctx_launch_count(const shady_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+#define CTX_ENTER(ctx)                                   \
+    if (!(ctx)) return SHADY_ERR_BAD_ARG;                \
+    SHADY_CUDA_OK(ctx, cudaSetDevice((ctx)->device))
+
+int shady_buffer_create(shady_ctx *ctx, size_t bytes, void **d_out) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, d_out, SHADY_ERR_BAD_ARG, "buffer_create: null out pointer");
+    *d_out = nullptr;
+    const size_t aligned = (bytes + 3) & ~(size_t)3;  // gpu.rs:86
+    SHADY_CUDA_OK(ctx, cudaMalloc(d_out, aligned ? aligned : 4));
+    return SHADY_OK;
+}
+int shady_buffer_free(shady_ctx *ctx, void *d_buf) {
+    CTX_ENTER(ctx);
+    if (d_buf) SHADY_CUDA_OK(ctx, cudaFree(d_buf));
+    return SHADY_OK;
+}
+int shady_buffer_write(shady_ctx *ctx, void *d_buf, size_t offset, const void *src, size_t bytes) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, d_buf && (src || !bytes), SHADY_ERR_BAD_ARG, "buffer_write: null argument");
+    if (bytes) SHADY_CUDA_OK(ctx, cudaMemcpyAsync((char *)d_buf + offset, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return SHADY_OK;
+}
+int shady_buffer_read(shady_ctx *ctx, const void *d_buf, size_t offset, void *dst, size_t bytes) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, d_buf && (dst || !bytes), SHADY_ERR_BAD_ARG, "buffer_read: null argument");
+    if (bytes) SHADY_CUDA_OK(ctx, cudaMemcpyAsync(dst, (const char *)d_buf + offset, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    SHADY_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    return SHADY_OK;
+}
+int shady_buffer_copy(shady_ctx *ctx, const void *d_src, void *d_dst, size_t bytes) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, d_src && d_dst, SHADY_ERR_BAD_ARG, "buffer_copy: null argument");
+    if (bytes) SHADY_CUDA_OK(ctx, cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return SHADY_OK;
+}
+int shady_flush(shady_ctx *ctx) {
+    CTX_ENTER(ctx);
+    const cudaError_t e = cudaStreamQuery(ctx->stream);
+    if (e != cudaSuccess && e != cudaErrorNotReady)
+        return fail(ctx, SHADY_ERR_CUDA, std::string("flush: ") + cudaGetErrorString(e));
+    return SHADY_OK;
+}
+int shady_synchronize(shady_ctx *ctx) {
+    CTX_ENTER(ctx);
+    SHADY_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    return SHADY_OK;
+}
+
+int shady_kv_append_rope(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,
+                         const void *d_v_proj, void *d_q_out, float *d_q_gate, const shady_kv_cache *cache,
+                         const uint16_t *d_qk_norm_bf16, const uint32_t *d_pos_start, const uint32_t *d_pos_h,
+                         const uint32_t *d_pos_w) {
+    CTX_ENTER(ctx);
+    return launch_append(ctx, p, d_q_proj_full, d_k_proj, d_v_proj, d_q_out, d_q_gate, cache, d_qk_norm_bf16,
+                         d_pos_start, d_pos_h, d_pos_w);
+}
+
+int shady_decode_workspace_size(const shady_decode_params *p, size_t *bytes) {
+    if (!p || !bytes) return SHADY_ERR_BAD_ARG;
+    *bytes = decode_workspace_bytes(nullptr, p, SHADY_F16);
+    return SHADY_OK;
+}
+
+int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
+                      const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, void *d_out, float *d_lse,
+                      const float *d_gate, void *d_workspace, size_t workspace_bytes) {
+    CTX_ENTER(ctx);
+    return launch_decode(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, d_out, d_lse, d_gate, d_workspace,
+                         workspace_bytes, nullptr);
+}
+
+int shady_attn_decode_partials(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
+                               const shady_kv_cache *cache, const uint32_t *d_seq_lens, float *d_partials) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, d_partials, SHADY_ERR_BAD_ARG, "decode_partials: null output");
+    return launch_decode(ctx, p, d_q, cache, d_seq_lens, nullptr, nullptr, nullptr, nullptr, nullptr, 0, d_partials);
+}
+
+int shady_attn_reduce(shady_ctx *ctx, uint32_t head_dim, uint32_t num_splits, uint32_t num_heads, uint64_t split_stride,
+                      uint64_t head_stride, const float *d_partials, void *d_out, uint32_t out_dtype,
+                      const float *d_gate) {
+    CTX_ENTER(ctx);
+    return launch_reduce(ctx, head_dim, num_splits, num_heads, split_stride, head_stride, d_partials, d_out, out_dtype,
+                         d_gate);
+}
+
+int shady_attn_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_q, const shady_kv_cache *cache,
+                       void *d_out) {
+    CTX_ENTER(ctx);
+    return launch_prefill(ctx, p, d_q, cache, d_out);
+}
+
+int shady_sigmoid_mul(shady_ctx *ctx, float *d_x, const float *d_gate, uint32_t n) {
+    CTX_ENTER(ctx);
+    return launch_sigmoid_mul(ctx, d_x, d_gate, n);
+}
+
+int shady_fill_randn(shady_ctx *ctx, void *d_dst, uint64_t n, uint32_t dtype, uint64_t seed, uint64_t tensor_id,
+                     uint64_t first_idx) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, d_dst || !n, SHADY_ERR_BAD_ARG, "fill_randn: null destination");
+    SHADY_REQUIRE(ctx, dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "fill_randn: bad dtype");
+    if (!n) return SHADY_OK;
+    const unsigned long long key = mix64(seed ^ (tensor_id * 0xD1B54A32D192ED03ull));
+    const unsigned long long want = (n + 255) / 256;
+    const unsigned blocks = (unsigned)(want < (unsigned long long)ctx->num_sms * 16 ? want : (unsigned long long)ctx->num_sms * 16);
+    fill_randn_kernel<<<blocks, 256, 0, ctx->stream>>>(d_dst, n, dtype, key, first_idx);
+    ctx->launches++;
+    SHADY_CUDA_OK(ctx, cudaGetLastError());
+    return SHADY_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,163 @@
+// KV append: Q/gate split, Q/K RMSNorm with (1+w) bf16 weights, partial (m)RoPE, cache store.
+// Results follow fused_split_qknorm_kvstore.wgsl:106-230; the layout of the work does not:
+// one warp per (token, head) instead of a 256-thread workgroup with barrier trees, batched
+// over tokens and sequences, cache rows written in the cache's storage dtype.
+//
+// RoPE frequencies are NOT computed on the device: the host evaluates
+// 1/powf(theta, 2i/rotary_dim) once (same libm call the CPU oracle makes) and passes the
+// table by value.  At position ~1e5 a 1-ulp difference in the frequency moves the angle by
+// ~1e-2 rad, so device powf would break parity with any CPU statement of the shader.
+// cos/sin use the accurate sincosf (full-range argument reduction), never the fast
+// intrinsics: the shader takes cos/sin of up to 131071 radians in f32 (wgsl:66-68).
+#include <math.h>
+
+#include "common.cuh"
+
+namespace shady {
+
+struct AppendArgs {
+    const void *q_in;
+    void *k_io;
+    const void *v_in;
+    void *q_out;
+    float *q_gate;
+    char *k_base, *v_base;
+    unsigned long long seq_stride_bytes;
+    void *const *k_ptrs, *const *v_ptrs;
+    const uint16_t *norm_w;   // bf16 bits: q[hd] then k[hd]; NULL = no norm
+    const uint32_t *pos_start, *pos_h, *pos_w;
+    uint32_t nh, nkv, hd;
+    float eps;
+    uint32_t rd, s1, s2, interleaved;
+    uint32_t num_seqs, T;
+    uint32_t in_dtype, q_dtype, kv_dtype, has_gate, write_k_back;
+    float inv_freq[128];      // [rd/2]
+};
+
+constexpr int kAppendWarps = 4;
+
+__global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(const AppendArgs a) {
+    __shared__ float sm_vals[kAppendWarps][256];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t heads = a.nh + a.nkv;
+    const unsigned long long wid = (unsigned long long)blockIdx.x * kAppendWarps + warp;
+    const unsigned long long total = (unsigned long long)a.num_seqs * a.T * heads;
+    if (wid >= total) return;
+    const uint32_t h = (uint32_t)(wid % heads);
+    const unsigned long long tok = wid / heads;
+    const uint32_t s = (uint32_t)(tok / a.T), j = (uint32_t)(tok % a.T);
+    const uint32_t hd = a.hd;
+    float *vals = sm_vals[warp];
+    const bool is_q = h < a.nh;
+    const uint32_t kh = h - a.nh;
+
+    // ---- load the head vector (and pass the gate through) ----
+    float ssq = 0.f;
+    if (is_q) {
+        const size_t row = (tok * a.nh + h) * (size_t)(a.has_gate ? 2 * hd : hd);
+        for (uint32_t d = lane; d < hd; d += 32) {
+            const float v = load_as_f32(a.q_in, row + d, a.in_dtype);
+            vals[d] = v;
+            ssq += v * v;
+            if (a.has_gate && a.q_gate)
+                a.q_gate[(tok * a.nh + h) * (size_t)hd + d] = load_as_f32(a.q_in, row + hd + d, a.in_dtype);
+        }
+    } else {
+        const size_t row = (tok * a.nkv + kh) * (size_t)hd;
+        for (uint32_t d = lane; d < hd; d += 32) {
+            const float v = load_as_f32(a.k_io, row + d, a.in_dtype);
+            vals[d] = v;
+            ssq += v * v;
+        }
+    }
+    // ---- RMSNorm (wgsl:150-160 / :205-212) ----
+    if (a.norm_w) {
+        ssq = warp_sum(ssq);
+        const float rms = 1.0f / sqrtf(ssq / (float)hd + a.eps);
+        const uint16_t *w = a.norm_w + (is_q ? 0 : hd);
+        for (uint32_t d = lane; d < hd; d += 32) {
+            const float wf = __uint_as_float(((uint32_t)w[d]) << 16);
+            vals[d] = vals[d] * rms * (1.0f + wf);
+        }
+    }
+    __syncwarp();
+    // ---- (m)RoPE on the first rd dims (wgsl:56-104) ----
+    const uint32_t p_t = a.pos_start[s] + j;
+    const uint32_t p_h = a.pos_h ? a.pos_h[s] + j : p_t;
+    const uint32_t p_w = a.pos_w ? a.pos_w[s] + j : p_t;
+    const uint32_t half = a.rd / 2;
+    for (uint32_t i = lane; i < half; i += 32) {
+        uint32_t pos = p_t;
+        if ((i % 3u) == 1u && i < a.s1) pos = p_h;
+        else if ((i % 3u) == 2u && i < a.s2) pos = p_w;
+        const float angle = (float)pos * a.inv_freq[i];
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        const uint32_t ia = a.interleaved ? 2 * i : i;
+        const uint32_t ib = a.interleaved ? 2 * i + 1 : i + half;
+        const float x = vals[ia], y = vals[ib];
+        vals[ia] = x * cs - y * sn;
+        vals[ib] = y * cs + x * sn;
+    }
+    __syncwarp();
+    // ---- stores ----
+    if (is_q) {
+        const size_t row = (tok * a.nh + h) * (size_t)hd;
+        for (uint32_t d = lane; d < hd; d += 32) store_from_f32(a.q_out, row + d, a.q_dtype, vals[d]);
+    } else {
+        const size_t esz = a.kv_dtype == SHADY_F32 ? 4 : 2;
+        char *kc = a.k_ptrs ? reinterpret_cast<char *>(a.k_ptrs[s]) : a.k_base + a.seq_stride_bytes * s;
+        char *vc = a.v_ptrs ? reinterpret_cast<char *>(a.v_ptrs[s]) : a.v_base + a.seq_stride_bytes * s;
+        const size_t crow = ((size_t)p_t * a.nkv + kh) * hd;   // cache_position == position (model.rs:493-496)
+        const size_t row = (tok * a.nkv + kh) * (size_t)hd;
+        (void)esz;
+        for (uint32_t d = lane; d < hd; d += 32) {
+            const float kv = vals[d];
+            if (a.write_k_back) store_from_f32(a.k_io, row + d, a.in_dtype, kv);
+            store_from_f32(kc, crow + d, a.kv_dtype, kv);
+            store_from_f32(vc, crow + d, a.kv_dtype, load_as_f32(a.v_in, row + d, a.in_dtype));
+        }
+    }
+}
+
+int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,
+                  const void *d_v_proj, void *d_q_out, float *d_q_gate, const shady_kv_cache *cache,
+                  const uint16_t *d_qk_norm_bf16, const uint32_t *d_pos_start, const uint32_t *d_pos_h,
+                  const uint32_t *d_pos_w) {
+    SHADY_REQUIRE(ctx, p && d_q_proj_full && d_k_proj && d_v_proj && d_q_out && cache && d_pos_start,
+                  SHADY_ERR_BAD_ARG, "kv_append_rope: null argument");
+    SHADY_REQUIRE(ctx, p->num_heads && p->num_kv_heads && p->head_dim && p->num_seqs && p->tokens_per_seq,
+                  SHADY_ERR_BAD_ARG, "kv_append_rope: zero-sized problem");
+    SHADY_REQUIRE(ctx, p->head_dim <= 256, SHADY_ERR_UNSUPPORTED, "kv_append_rope: head_dim > 256 (the reference shader's limit)");
+    SHADY_REQUIRE(ctx, p->rotary_dim <= p->head_dim && (p->rotary_dim % 2) == 0, SHADY_ERR_BAD_ARG,
+                  "kv_append_rope: rotary_dim must be even and <= head_dim");
+    SHADY_REQUIRE(ctx, p->in_dtype <= SHADY_BF16 && p->q_dtype <= SHADY_BF16 && cache->dtype <= SHADY_BF16,
+                  SHADY_ERR_BAD_ARG, "kv_append_rope: bad dtype");
+    SHADY_REQUIRE(ctx, !p->has_gate || d_q_gate, SHADY_ERR_BAD_ARG, "kv_append_rope: has_gate needs d_q_gate");
+    SHADY_REQUIRE(ctx, (cache->d_k_ptrs && cache->d_v_ptrs) || (cache->d_k_base && cache->d_v_base),
+                  SHADY_ERR_BAD_ARG, "kv_append_rope: cache has neither base pointers nor pointer arrays");
+    AppendArgs a{};
+    a.q_in = d_q_proj_full; a.k_io = d_k_proj; a.v_in = d_v_proj; a.q_out = d_q_out; a.q_gate = d_q_gate;
+    a.k_base = (char *)cache->d_k_base; a.v_base = (char *)cache->d_v_base;
+    a.seq_stride_bytes = cache->seq_stride * dtype_size(cache->dtype);
+    a.k_ptrs = cache->d_k_ptrs; a.v_ptrs = cache->d_v_ptrs;
+    a.norm_w = d_qk_norm_bf16;
+    a.pos_start = d_pos_start; a.pos_h = d_pos_h; a.pos_w = d_pos_w;
+    a.nh = p->num_heads; a.nkv = p->num_kv_heads; a.hd = p->head_dim; a.eps = p->eps;
+    a.rd = p->rotary_dim; a.s1 = p->s1_limit; a.s2 = p->s2_limit; a.interleaved = p->interleaved;
+    a.num_seqs = p->num_seqs; a.T = p->tokens_per_seq;
+    a.in_dtype = p->in_dtype; a.q_dtype = p->q_dtype; a.kv_dtype = cache->dtype;
+    a.has_gate = p->has_gate; a.write_k_back = p->write_k_back;
+    // apply_mrope: freq = 1.0 / pow(ROPE_THETA, 2.0 * f32(freq_idx) / f32(PARTIAL_DIM))  (wgsl:57)
+    for (uint32_t i = 0; i < p->rotary_dim / 2; ++i)
+        a.inv_freq[i] = 1.0f / powf(p->rope_theta, 2.0f * (float)i / (float)p->rotary_dim);
+    const unsigned long long warps = (unsigned long long)p->num_seqs * p->tokens_per_seq * (p->num_heads + p->num_kv_heads);
+    const unsigned long long blocks = (warps + kAppendWarps - 1) / kAppendWarps;
+    SHADY_REQUIRE(ctx, blocks <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "kv_append_rope: too many tokens for one launch");
+    append_kernel<<<(unsigned)blocks, kAppendWarps * 32, 0, ctx->stream>>>(a);
+    ctx->launches++;
+    SHADY_CUDA_OK(ctx, cudaGetLastError());
+    return SHADY_OK;
+}
+
+}  // namespace shady

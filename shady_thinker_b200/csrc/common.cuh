@@ -1,0 +1,88 @@
+// Shared device/host helpers for the sm_100a attention kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/shady_attn.h"
+
+struct shady_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int num_sms = 148;
+    uint64_t launches = 0;
+    std::string err;
+};
+
+namespace shady {
+
+// ---- status plumbing ------------------------------------------------------------------
+int fail(shady_ctx *ctx, int code, const std::string &msg);
+#define SHADY_CUDA_OK(ctx, expr)                                                             \
+    do {                                                                                     \
+        cudaError_t e__ = (expr);                                                            \
+        if (e__ != cudaSuccess)                                                              \
+            return ::shady::fail(ctx, SHADY_ERR_CUDA,                                        \
+                                 std::string(#expr) + ": " + cudaGetErrorString(e__));       \
+    } while (0)
+#define SHADY_REQUIRE(ctx, cond, code, msg)                       \
+    do {                                                          \
+        if (!(cond)) return ::shady::fail(ctx, code, msg);        \
+    } while (0)
+
+inline size_t dtype_size(uint32_t dt) { return dt == SHADY_F32 ? 4 : 2; }
+
+// ---- dtype conversion -------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Load / store one element of a buffer whose dtype is only known at run time.
+__device__ __forceinline__ float load_as_f32(const void *p, size_t i, uint32_t dt) {
+    if (dt == SHADY_F32) return reinterpret_cast<const float *>(p)[i];
+    if (dt == SHADY_F16) return __half2float(reinterpret_cast<const __half *>(p)[i]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
+}
+__device__ __forceinline__ void store_from_f32(void *p, size_t i, uint32_t dt, float v) {
+    if (dt == SHADY_F32) reinterpret_cast<float *>(p)[i] = v;
+    else if (dt == SHADY_F16) reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ float sigmoidf_ref(float g) { return 1.0f / (1.0f + expf(-g)); }
+
+// Resolve the base pointer of sequence s in a KV cache (see shady_kv_cache).
+struct KvAddr {
+    const char *k_base;
+    const char *v_base;
+    unsigned long long seq_stride_bytes;
+    const void *const *k_ptrs;
+    const void *const *v_ptrs;
+};
+__device__ __forceinline__ const char *kv_seq_ptr(const char *base, const void *const *ptrs,
+                                                  unsigned long long stride_bytes, uint32_t s) {
+    return ptrs ? reinterpret_cast<const char *>(ptrs[s]) : base + stride_bytes * s;
+}
+
+}  // namespace shady

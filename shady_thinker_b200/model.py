@@ -1,0 +1,156 @@
+"""Host-side mirror of the attention part of the reference's ``Model`` (src/model.rs).
+
+Only the hot path is here: the buffers of ``InferenceState`` that the three private helpers
+touch (model.rs:57-86, 226-256), and the helpers themselves with their reference names —
+``fused_split_qknorm_kvstore`` (model.rs:486), ``gqa_attention`` (model.rs:516) and
+``sigmoid_mul_gate`` (model.rs:576) — whose bodies call the CUDA backend instead of
+``gpu.dispatch(wgsl…)``.  ``CacheSlot`` / ``alloc_cache_slot`` / ``swap_cache``
+(model.rs:93-99, 973-1029) are mirrored for the KV part.
+"""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import ops
+from ._lib import BF16, F16, F32  # noqa: F401
+from .gpu import Buffer, GpuContext
+
+#: model.rs:89 fixes this at 1 at compile time; here it is a run-time value and 0 means
+#: "pick a length-balanced split".
+NUM_ATTN_SPLITS = 0
+
+
+@dataclass
+class ModelConfig:
+    """The ``ModelConfig`` fields the hot path reads, with the reference defaults
+    (src/weights.rs:93-152)."""
+
+    num_attention_heads: int
+    num_key_value_heads: int
+    num_hidden_layers: int = 1
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e7
+    partial_rotary_factor: float = 0.25
+    mrope_interleaved: bool = True
+
+    @property
+    def rotary_dim(self) -> int:
+        # model.rs:33: (config.head_dim as f32 * config.partial_rotary_factor) as u32
+        return int(np.float32(self.head_dim) * np.float32(self.partial_rotary_factor))
+
+
+@dataclass
+class CacheSlot:
+    """model.rs:93-99 (KV part)."""
+
+    k_cache: list[Buffer]
+    v_cache: list[Buffer]
+    seq_len: int = 0
+
+
+@dataclass
+class InferenceState:
+    q_out: Buffer
+    q_proj: Buffer
+    q_gate: Buffer
+    k_out: Buffer
+    v_out: Buffer
+    attn_output: Buffer
+    attn_partials: Buffer
+    k_cache: list[Buffer]
+    v_cache: list[Buffer]
+    qknorm_params: list[Buffer | None]
+    position: Buffer
+    seq_len_dev: Buffer
+    partials_bytes: int = 0
+    extra: dict = field(default_factory=dict)
+
+
+class Model:
+    """Attention-only ``Model``: one sequence, one token per step, like the reference."""
+
+    def __init__(self, gpu: GpuContext, config: ModelConfig, max_seq_len: int, kv_dtype: int = F32,
+                 num_attn_splits: int = NUM_ATTN_SPLITS):
+        self.config = config
+        self.max_seq_len = max_seq_len
+        self.kv_dtype = kv_dtype
+        self.num_attn_splits = num_attn_splits
+        self.seq_len = 0
+        nh, nkv, hd, nl = (config.num_attention_heads, config.num_key_value_heads, config.head_dim,
+                           config.num_hidden_layers)
+        f = 4
+        esz = 4 if kv_dtype == F32 else 2
+        ws = ops.decode_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh,
+                                       num_splits=num_attn_splits, num_seqs=1)
+        mk = gpu.create_storage_buffer
+        self.state = InferenceState(
+            q_out=mk("q_out", nh * hd * 2 * f), q_proj=mk("q_proj", nh * hd * f), q_gate=mk("q_gate", nh * hd * f),
+            k_out=mk("k_out", nkv * hd * f), v_out=mk("v_out", nkv * hd * f),
+            attn_output=mk("attn_output", nh * hd * f), attn_partials=mk("attn_partials", max(ws, 4)),
+            k_cache=[mk(f"k_cache_{i}", max_seq_len * nkv * hd * esz) for i in range(nl)],
+            v_cache=[mk(f"v_cache_{i}", max_seq_len * nkv * hd * esz) for i in range(nl)],
+            qknorm_params=[None] * nl, position=mk("position", 4), seq_len_dev=mk("seq_len", 4), partials_bytes=ws)
+
+    # model.rs:337-346 — the reference packs a 5,152-byte uniform; only the bf16 weights
+    # (q then k) are data, the header fields travel by value here.
+    def init_qknorm_params(self, gpu: GpuContext, layer_idx: int, q_norm_bytes: bytes, k_norm_bytes: bytes) -> None:
+        hd = self.config.head_dim
+        if len(q_norm_bytes) != 2 * hd or len(k_norm_bytes) != 2 * hd:
+            raise ValueError("q_norm/k_norm must be head_dim bf16 values each")
+        self.state.qknorm_params[layer_idx] = gpu.upload_buffer(f"qknorm_params_{layer_idx}",
+                                                                bytes(q_norm_bytes) + bytes(k_norm_bytes))
+
+    def _cache(self, layer_idx: int) -> ops.KvCacheView:
+        return ops.KvCacheView(self.kv_dtype, self.state.k_cache[layer_idx], self.state.v_cache[layer_idx], 0)
+
+    def fused_split_qknorm_kvstore(self, gpu: GpuContext, layer_idx: int) -> None:
+        """model.rs:486-513."""
+        c, s = self.config, self.state
+        if self.seq_len >= self.max_seq_len:
+            raise IndexError("KV cache is full")
+        gpu.write_buffer(s.position, 0, struct.pack("I", self.seq_len))  # model.rs:493-496
+        ops.kv_append_rope(gpu, q_proj_full=s.q_out, k_proj=s.k_out, v_proj=s.v_out, q_out=s.q_proj, q_gate=s.q_gate,
+                           cache=self._cache(layer_idx), pos_start=s.position, num_heads=c.num_attention_heads,
+                           num_kv_heads=c.num_key_value_heads, head_dim=c.head_dim, rope_theta=c.rope_theta,
+                           rotary_dim=c.rotary_dim, interleaved=c.mrope_interleaved, eps=c.rms_norm_eps,
+                           qk_norm_bf16=s.qknorm_params[layer_idx])
+
+    def gqa_attention(self, gpu: GpuContext, layer_idx: int, fuse_gate: bool = False) -> None:
+        """model.rs:516-573.  ``fuse_gate`` folds the following ``sigmoid_mul_gate`` into the epilogue."""
+        c, s = self.config, self.state
+        seq_len = self.seq_len + 1  # include current token (model.rs:521)
+        gpu.write_buffer(s.seq_len_dev, 0, struct.pack("I", seq_len))
+        ops.attn_decode(gpu, q=s.q_proj, cache=self._cache(layer_idx), seq_lens=s.seq_len_dev, out=s.attn_output,
+                        head_dim=c.head_dim, num_kv_heads=c.num_key_value_heads, num_q_heads=c.num_attention_heads,
+                        num_seqs=1, num_splits=self.num_attn_splits, seq_lens_host=[seq_len],
+                        gate=s.q_gate if fuse_gate else None, workspace=s.attn_partials,
+                        workspace_bytes=s.partials_bytes)
+
+    def sigmoid_mul_gate(self, gpu: GpuContext) -> None:
+        """model.rs:576-593 (in place; no temp buffer + copy)."""
+        c, s = self.config, self.state
+        ops.sigmoid_mul(gpu, s.attn_output, s.q_gate, c.num_attention_heads * c.head_dim)
+
+    def attention_step(self, gpu: GpuContext, layer_idx: int) -> None:
+        """The three calls of model.rs:723-725 for one self-attention layer."""
+        self.fused_split_qknorm_kvstore(gpu, layer_idx)
+        self.gqa_attention(gpu, layer_idx)
+        self.sigmoid_mul_gate(gpu)
+
+    # -- cache slots (model.rs:973-1029, KV part) -------------------------------------------------
+    def alloc_cache_slot(self, gpu: GpuContext) -> CacheSlot:
+        c = self.config
+        esz = 4 if self.kv_dtype == F32 else 2
+        n = self.max_seq_len * c.num_key_value_heads * c.head_dim * esz
+        return CacheSlot([gpu.create_storage_buffer(f"slot_k_{i}", n) for i in range(c.num_hidden_layers)],
+                         [gpu.create_storage_buffer(f"slot_v_{i}", n) for i in range(c.num_hidden_layers)], 0)
+
+    def swap_cache(self, slot: CacheSlot) -> None:
+        s = self.state
+        s.k_cache, slot.k_cache = slot.k_cache, s.k_cache
+        s.v_cache, slot.v_cache = slot.v_cache, s.v_cache
+        self.seq_len, slot.seq_len = slot.seq_len, self.seq_len

@@ -1,0 +1,123 @@
+"""Thin functional wrappers over the C ABI ops.  Arguments are device buffers (``gpu.Buffer``,
+CUDA tensors or raw addresses); nothing here computes on the host."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from ._lib import BF16, F16, F32, AppendParams, DecodeParams, KvCache, PrefillParams
+from .gpu import GpuContext, _addr
+
+_TORCH_DTYPES = None
+
+
+def dtype_code(t) -> int:
+    """SHADY_* code of a torch dtype / numpy dtype / code."""
+    global _TORCH_DTYPES
+    if isinstance(t, int):
+        return t
+    if _TORCH_DTYPES is None:
+        import torch
+        _TORCH_DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+    if t in _TORCH_DTYPES:
+        return _TORCH_DTYPES[t]
+    return {np.dtype(np.float32): F32, np.dtype(np.float16): F16}[np.dtype(t)]
+
+
+@dataclass
+class KvCacheView:
+    """Where the per-sequence K/V rows live: one allocation with a per-sequence stride, or device
+    arrays of per-sequence pointers (see ``shady_kv_cache``)."""
+
+    dtype: int
+    k_base: object = None
+    v_base: object = None
+    seq_stride: int = 0          # elements
+    k_ptrs: object = None        # device array of device pointers (uint64) [num_seqs]
+    v_ptrs: object = None
+
+    def c_struct(self) -> KvCache:
+        return KvCache(_addr(self.k_base) or None, _addr(self.v_base) or None, self.seq_stride,
+                       _addr(self.k_ptrs) or None, _addr(self.v_ptrs) or None, self.dtype)
+
+
+def kv_append_rope(gpu: GpuContext, *, q_proj_full, k_proj, v_proj, q_out, q_gate, cache: KvCacheView, pos_start,
+                   num_heads: int, num_kv_heads: int, head_dim: int, rope_theta: float, rotary_dim: int,
+                   interleaved: bool = True, eps: float = 1e-6, qk_norm_bf16=None, num_seqs: int = 1,
+                   tokens_per_seq: int = 1, in_dtype: int = F32, q_dtype: int = F32, has_gate: bool = True,
+                   write_k_back: bool = True, pos_h=None, pos_w=None, s1_limit: int | None = None,
+                   s2_limit: int | None = None) -> None:
+    p = AppendParams(num_heads, num_kv_heads, head_dim, eps, rope_theta, rotary_dim,
+                     rotary_dim // 2 if s1_limit is None else s1_limit,
+                     rotary_dim // 2 if s2_limit is None else s2_limit, int(interleaved), num_seqs,
+                     tokens_per_seq, in_dtype, q_dtype, int(has_gate), int(write_k_back), 0)
+    c = cache.c_struct()
+    gpu._check(gpu._L.shady_kv_append_rope(gpu.handle, C.byref(p), _addr(q_proj_full), _addr(k_proj), _addr(v_proj),
+                                           _addr(q_out), _addr(q_gate) or None, C.byref(c),
+                                           _addr(qk_norm_bf16) or None, _addr(pos_start), _addr(pos_h) or None,
+                                           _addr(pos_w) or None))
+
+
+def decode_workspace_size(*, head_dim: int, num_kv_heads: int, num_q_heads: int, num_splits: int, num_seqs: int) -> int:
+    p = DecodeParams(head_dim, num_kv_heads, num_q_heads, num_q_heads // num_kv_heads, num_splits, num_seqs, F32, F32)
+    n = C.c_size_t()
+    st = _lib.load().shady_decode_workspace_size(C.byref(p), C.byref(n))
+    if st != _lib.OK:
+        raise _lib.ShadyError(st, "decode_workspace_size")
+    return n.value
+
+
+def _host_lens(seq_lens_host):
+    if seq_lens_host is None:
+        return None, None
+    arr = np.ascontiguousarray(seq_lens_host, dtype=np.uint32)
+    return arr, arr.ctypes.data_as(C.POINTER(C.c_uint32))
+
+
+def attn_decode(gpu: GpuContext, *, q, cache: KvCacheView, seq_lens, out, head_dim: int, num_kv_heads: int,
+                num_q_heads: int, num_seqs: int = 1, num_splits: int = 0, seq_lens_host=None, q_dtype: int = F32,
+                out_dtype: int = F32, lse=None, gate=None, workspace=None, workspace_bytes: int = 0) -> None:
+    p = DecodeParams(head_dim, num_kv_heads, num_q_heads, num_q_heads // num_kv_heads, num_splits, num_seqs, q_dtype,
+                     out_dtype)
+    c = cache.c_struct()
+    keep, hl = _host_lens(seq_lens_host)
+    gpu._check(gpu._L.shady_attn_decode(gpu.handle, C.byref(p), _addr(q), C.byref(c), _addr(seq_lens), hl, _addr(out),
+                                        _addr(lse) or None, _addr(gate) or None, _addr(workspace) or None,
+                                        workspace_bytes))
+    del keep
+
+
+def attn_decode_partials(gpu: GpuContext, *, q, cache: KvCacheView, seq_lens, partials, head_dim: int,
+                         num_kv_heads: int, num_q_heads: int, num_splits: int, q_dtype: int = F32) -> None:
+    p = DecodeParams(head_dim, num_kv_heads, num_q_heads, num_q_heads // num_kv_heads, num_splits, 1, q_dtype, F32)
+    c = cache.c_struct()
+    gpu._check(gpu._L.shady_attn_decode_partials(gpu.handle, C.byref(p), _addr(q), C.byref(c), _addr(seq_lens),
+                                                 _addr(partials)))
+
+
+def attn_reduce(gpu: GpuContext, *, partials, out, head_dim: int, num_splits: int, num_heads: int,
+                split_stride: int | None = None, head_stride: int | None = None, out_dtype: int = F32,
+                gate=None) -> None:
+    """Defaults to the reference layout [nh][ns][hd+2] (gqa_reduce.wgsl:7-12)."""
+    ss = head_dim + 2 if split_stride is None else split_stride
+    hs = num_splits * (head_dim + 2) if head_stride is None else head_stride
+    gpu._check(gpu._L.shady_attn_reduce(gpu.handle, head_dim, num_splits, num_heads, ss, hs, _addr(partials),
+                                        _addr(out), out_dtype, _addr(gate) or None))
+
+
+def attn_prefill(gpu: GpuContext, *, q, cache: KvCacheView, out, head_dim: int, num_kv_heads: int, num_q_heads: int,
+                 num_seqs: int, seq_len: int, dtype: int = BF16) -> None:
+    p = PrefillParams(head_dim, num_kv_heads, num_q_heads, num_seqs, seq_len, dtype)
+    c = cache.c_struct()
+    gpu._check(gpu._L.shady_attn_prefill(gpu.handle, C.byref(p), _addr(q), C.byref(c), _addr(out)))
+
+
+def sigmoid_mul(gpu: GpuContext, x, gate, n: int) -> None:
+    gpu._check(gpu._L.shady_sigmoid_mul(gpu.handle, _addr(x), _addr(gate), n))
+
+
+def fill_randn(gpu: GpuContext, dst, n: int, dtype: int, seed: int, tensor_id: int, first_idx: int = 0) -> None:
+    gpu._check(gpu._L.shady_fill_randn(gpu.handle, _addr(dst), n, dtype, seed, tensor_id, first_idx))

@@ -1,0 +1,74 @@
+"""The reference's call surface end to end: Model.fused_split_qknorm_kvstore -> gqa_attention ->
+sigmoid_mul_gate per token (model.rs:723-725), driven like generate_tokens (inference.rs:89-99),
+against the oracle's token loop."""
+import numpy as np
+import pytest
+
+from _util import ATOL_F32, RTOL_16, rel_err
+from shady_thinker_b200._lib import BF16, F16, F32
+from shady_thinker_b200.model import Model, ModelConfig
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("kv_dt,splits", [(F32, 1), (F32, 0), (F16, 0), (BF16, 2)])
+def test_token_loop_matches_oracle(gpu_ctx, oracle, kv_dt, splits):
+    cfg = ModelConfig(num_attention_heads=16, num_key_value_heads=2, num_hidden_layers=2, head_dim=128,
+                      rope_theta=1e6, partial_rotary_factor=0.25)
+    nh, nkv, hd, T = 16, 2, 128, 24
+    m = Model(gpu_ctx, cfg, max_seq_len=64, kv_dtype=kv_dt, num_attn_splits=splits)
+    w = [oracle.bf16_bits(oracle.randn((2 * hd,), 3, 90 + l) * np.float32(0.02)) for l in range(2)]
+    for l in range(2):
+        m.init_qknorm_params(gpu_ctx, l, w[l][:hd].tobytes(), w[l][hd:].tobytes())
+    okc = [np.zeros((64, nkv, hd), np.float32) for _ in range(2)]
+    ovc = [np.zeros((64, nkv, hd), np.float32) for _ in range(2)]
+    m.seq_len = 0                                              # inference.rs:89
+    for t in range(T):
+        for l in range(2):
+            qf = oracle.randn((nh, 2, hd), 3, 1000 + 10 * t + l)
+            kp = oracle.randn((nkv, hd), 3, 2000 + 10 * t + l)
+            vp = oracle.randn((nkv, hd), 3, 3000 + 10 * t + l)
+            gpu_ctx.write_buffer(m.state.q_out, 0, qf.tobytes())
+            gpu_ctx.write_buffer(m.state.k_out, 0, kp.tobytes())
+            gpu_ctx.write_buffer(m.state.v_out, 0, vp.tobytes())
+            m.attention_step(gpu_ctx, l)
+            got = np.frombuffer(gpu_ctx.read_buffer(m.state.attn_output, nh * hd * 4), np.float32).reshape(nh, hd)
+            oq, og, _ = oracle.fused_split_qknorm_kvstore(qf, kp, vp, okc[l], ovc[l], t, rope_theta=1e6,
+                                                          rotary_dim=32, qk_norm_bf16=w[l])
+            want = oracle.sigmoid_mul(oracle.gqa_attention_head(oq, okc[l], ovc[l], t + 1), og).reshape(nh, hd)
+            if kv_dt == F32:
+                assert np.abs(got - want).max() <= ATOL_F32, (t, l)
+            else:
+                assert rel_err(got, want) <= RTOL_16, (t, l)
+        m.seq_len += 1                                          # model.rs:837
+
+
+def test_cache_slot_swap_keeps_two_sequences_apart(gpu_ctx, oracle):
+    cfg = ModelConfig(num_attention_heads=4, num_key_value_heads=2, head_dim=64, rope_theta=1e6)
+    m = Model(gpu_ctx, cfg, max_seq_len=8, num_attn_splits=1)
+    slot = m.alloc_cache_slot(gpu_ctx)
+    outs = {}
+    for name, seed in (("a", 1), ("b", 2), ("a2", 1)):
+        if name == "b":
+            m.swap_cache(slot)
+        if name == "a2":
+            m.swap_cache(slot)                                  # back to sequence a, continue it
+        for t in range(2):
+            step = t if name != "a2" else t + 2
+            gpu_ctx.write_buffer(m.state.q_out, 0, oracle.randn((4, 2, 64), seed, 10 + step).tobytes())
+            gpu_ctx.write_buffer(m.state.k_out, 0, oracle.randn((2, 64), seed, 20 + step).tobytes())
+            gpu_ctx.write_buffer(m.state.v_out, 0, oracle.randn((2, 64), seed, 30 + step).tobytes())
+            m.attention_step(gpu_ctx, 0)
+            m.seq_len += 1
+        outs[name] = np.frombuffer(gpu_ctx.read_buffer(m.state.attn_output, 4 * 64 * 4), np.float32).copy()
+    assert m.seq_len == 4 and slot.seq_len == 2
+    # continuing a after b must equal running a's four tokens without interruption
+    m2 = Model(gpu_ctx, cfg, max_seq_len=8, num_attn_splits=1)
+    for step in range(4):
+        gpu_ctx.write_buffer(m2.state.q_out, 0, oracle.randn((4, 2, 64), 1, 10 + step).tobytes())
+        gpu_ctx.write_buffer(m2.state.k_out, 0, oracle.randn((2, 64), 1, 20 + step).tobytes())
+        gpu_ctx.write_buffer(m2.state.v_out, 0, oracle.randn((2, 64), 1, 30 + step).tobytes())
+        m2.attention_step(gpu_ctx, 0)
+        m2.seq_len += 1
+    ref = np.frombuffer(gpu_ctx.read_buffer(m2.state.attn_output, 4 * 64 * 4), np.float32)
+    np.testing.assert_array_equal(outs["a2"], ref)
