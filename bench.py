@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+Default workload ("cfg2", BASELINE config 2): batched ragged decode attention, one layer —
+32 sequences per GPU with context lengths uniform in [1024, 8192], 32 query heads, 8 KV
+heads, head_dim 128, fp16 KV cache (contiguous per sequence) and fp16 Q with RoPE, fp32
+accumulation.  One step = append one token per sequence (RoPE + cache store) and attend.
+Metric: algorithmic KV bytes read per second (GB/s).  Sequences are sharded over GPUs with
+no data-path collective (weak scaling: every GPU holds its own 32 sequences).
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the
+reference shaders (the oracle port; the WGSL itself cannot run here) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SEED = 0x5EED
+NH, NKV, HD = 32, 8, 128
+SEQS_PER_GPU = 32
+LMIN, LMAX = 1024, 8192
+N_SETS = 3            # rotating cache sets so no step finds its KV rows in L2
+# DRAM bytes per algorithmic byte of the decode kernel, from the ncu capture summarised in
+# profiles/ (None until a capture exists).
+TRAFFIC_PER_ALGO_BYTE = None
+
+
+def draw_lengths(rank: int) -> np.ndarray:
+    """Lengths *including* the token appended in the step."""
+    rng = np.random.default_rng(SEED + 7919 * rank)
+    return rng.integers(LMIN, LMAX + 1, SEQS_PER_GPU).astype(np.uint32)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Polls NVML (read-only) for SM clock and throttle reasons while the timed region runs."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, device_index: int):
+        super().__init__(daemon=True)
+        self.samples = []
+        self.stop_flag = False
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = device_index
+            if vis:
+                try:
+                    idx = int(vis.split(",")[device_index])
+                except ValueError:
+                    idx = device_index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.max_mhz = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    rs = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    rs = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                self.samples.append((time.perf_counter(), mhz, rs))
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def summary(self, t0: float, t1: float) -> dict:
+        inside = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        bits = 0
+        for s in inside:
+            bits |= s[2]
+        return {"sm_mhz": float(np.median([s[1] for s in inside])), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(v for k, v in self.REASONS.items() if bits & k), "samples": len(inside)}
+
+
+def host_set(O, lens: np.ndarray, row_off: np.ndarray, set_id: int, rank: int, seqs):
+    """The fp16-rounded K/V rows and activations of the chosen sequences, regenerated on the host
+    from the same counter-based generator the device fill uses."""
+    row = NKV * HD
+    base = 1000 * rank + 10 * set_id
+    ks, vs = [], []
+    for s in seqs:
+        L = int(lens[s])
+        ks.append(O.round_f16(O.randn((L, NKV, HD), SEED, base + 1, first_idx=int(row_off[s]) * row)))
+        vs.append(O.round_f16(O.randn((L, NKV, HD), SEED, base + 2, first_idx=int(row_off[s]) * row)))
+    return ks, vs
+
+
+def run_reference(args, rank: int) -> None:
+    """CPU arm: the oracle's f32-faithful decode (one task per sequence, all host threads) on a bounded
+    sample of the cfg2 batch.  The rows are post-RoPE; the append is O(1) rows and not part of the sample."""
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build()
+    threads = O.num_threads()
+    lens = draw_lengths(0)
+    row_off = np.concatenate([[0], np.cumsum((lens.astype(np.int64) + 15) // 16 * 16)])
+    # calibrate on one mid-sized sequence, then size the sample so the whole run stays within ~2 minutes
+    order = np.argsort(lens)
+    probe = int(order[len(order) // 2])
+    ks, vs = host_set(O, lens, row_off, 0, 0, [probe])
+    q = O.round_f16(O.randn((SEQS_PER_GPU, NH, HD), SEED, 5))
+    t0 = time.perf_counter()
+    O.gqa_attention_head(q[probe], ks[0], vs[0], int(lens[probe]), threads=threads)
+    per_pos = (time.perf_counter() - t0) / int(lens[probe])          # one sequence uses the head-parallel form
+    budget = 100.0 / max(args.steps + args.warmup, 1)
+    # sequences run in parallel over threads: est. time ~ sum(L)*per_pos*threads_used/threads
+    seqs, tot = [], 0
+    for s in order[::-1]:
+        est = (tot + int(lens[s])) * per_pos
+        if seqs and est > budget:
+            break
+        seqs.append(int(s))
+        tot += int(lens[s])
+    ks, vs = host_set(O, lens, row_off, 0, 0, seqs)
+    use_lens = [int(lens[s]) for s in seqs]
+    if len(seqs) == 1 and tot * per_pos > budget:                     # even one sequence is too long: truncate it
+        use_lens = [max(LMIN // 4, int(budget / per_pos))]
+    qs = q[seqs]
+    nbytes = sum(use_lens) * NKV * HD * 2 * 2
+
+    def step():
+        if len(seqs) == 1:
+            O.gqa_attention_head(qs[0], ks[0], vs[0], use_lens[0], threads=threads)
+        else:
+            O.batched_decode(qs, ks, vs, use_lens, threads=threads)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    val = nbytes * args.steps / dt / 1e9
+    sample = f"{len(seqs)} of {SEQS_PER_GPU} cfg2 sequences ({sum(use_lens)} positions, {nbytes / 1e6:.1f} MB of fp16-rounded KV as f32) per step"
+    print(json.dumps({
+        "impl": "reference", "metric": "decode_attn_kv_bandwidth", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of gqa_attention_head.wgsl (oracle port); the WGSL through wgpu is unavailable on this box",
+    }))
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": "cfg2: batched ragged decode attention, one layer, append+attend per step",
+            "seqs_per_gpu": SEQS_PER_GPU, "context": f"uniform[{LMIN},{LMAX}] (seeded)", "num_q_heads": NH,
+            "num_kv_heads": NKV, "head_dim": HD, "kv_dtype": "fp16", "q_dtype": "fp16", "accumulate": "fp32",
+            "rope_theta": 1e6, "sharding": f"sequences over {n_gpus} GPU(s), no collective",
+            "l2": f"KV per step > L2 and {N_SETS} cache sets rotate between steps"}
+
+
+def cpu_baseline(rank: int, dec, lens: np.ndarray) -> dict:
+    """Oracle (f32-faithful port) on a bounded sample of the same batch, all host threads."""
+    from oracle import oracle as O
+    O.build()
+    threads = O.num_threads()
+    order = np.argsort(lens)[::-1]
+    seqs = [int(s) for s in order[:8]]
+    ks, vs = host_set(O, lens, dec.row_off, 0, rank, seqs)
+    q = O.round_f16(O.randn((8, NH, HD), SEED, 5))
+    use = [int(lens[s]) for s in seqs]
+    nbytes = sum(use) * NKV * HD * 2 * 2
+    best, t_total, reps = None, 0.0, 0
+    while t_total < 8.0 and reps < 20:
+        t0 = time.perf_counter()
+        O.batched_decode(q, ks, vs, use, threads=threads)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+        t_total += dt
+        reps += 1
+    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"8 longest of {SEQS_PER_GPU} cfg2 sequences ({sum(use)} positions, {nbytes / 1e6:.1f} MB of KV), best of {reps}"}
+
+
+def run_ours(args, rank: int, world: int, local_rank: int) -> None:
+    import torch
+
+    from shady_thinker_b200._lib import F16
+    from shady_thinker_b200.batch import BatchedDecoder
+    from shady_thinker_b200.gpu import GpuContext
+    from shady_thinker_b200 import ops
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.Stream()
+    gpu = GpuContext(local_rank, stream=stream.cuda_stream)
+    lens = draw_lengths(rank)
+    sets = []
+    for i in range(N_SETS):
+        d = BatchedDecoder(gpu, num_seqs=SEQS_PER_GPU, capacities=lens, num_heads=NH, num_kv_heads=NKV, head_dim=HD,
+                           kv_dtype=F16, rope_theta=1e6, rotary_dim=HD, has_gate=False, num_splits=0)
+        d.set_lengths(lens - 1)
+        base = 1000 * rank + 10 * i
+        n = d.layer_bytes // 2
+        ops.fill_randn(gpu, d.k_cache[0], n, F16, SEED, base + 1)
+        ops.fill_randn(gpu, d.v_cache[0], n, F16, SEED, base + 2)
+        ops.fill_randn(gpu, d.q_in, SEQS_PER_GPU * NH * HD, F16, SEED, base + 3)
+        ops.fill_randn(gpu, d.k_in, SEQS_PER_GPU * NKV * HD, F16, SEED, base + 4)
+        ops.fill_randn(gpu, d.v_in, SEQS_PER_GPU * NKV * HD, F16, SEED, base + 5)
+        sets.append(d)
+    gpu.synchronize()
+    step_bytes = sets[0].kv_bytes_per_step()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    with torch.cuda.stream(stream):
+        # ---------------- device-resident throughput ----------------
+        for i in range(args.warmup):
+            sets[i % N_SETS].step()
+        ev_a = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        launches0 = gpu.launch_count
+        t_wall0 = time.perf_counter()
+        e0.record(stream)
+        for i in range(args.steps):
+            d = sets[i % N_SETS]
+            d.append()
+            ev_a[i].record(stream)
+            d.attend()
+            ev_b[i].record(stream)
+        e1.record(stream)
+        barrier()
+        t_wall1 = time.perf_counter()
+        launches = gpu.launch_count - launches0
+        total_ms = e0.elapsed_time(e1)
+        attend_ms = sum(a.elapsed_time(b) for a, b in zip(ev_a, ev_b)) / args.steps
+
+        # ---------------- end to end with host buffers ----------------
+        d0 = sets[0]
+        asz = 2
+        hq = torch.empty(SEQS_PER_GPU * NH * HD, dtype=torch.float16).pin_memory()
+        hk = torch.empty(SEQS_PER_GPU * NKV * HD, dtype=torch.float16).pin_memory()
+        hv = torch.empty(SEQS_PER_GPU * NKV * HD, dtype=torch.float16).pin_memory()
+        ho = torch.empty(SEQS_PER_GPU * NH * HD, dtype=torch.float16).pin_memory()
+        hq.normal_(); hk.normal_(); hv.normal_()
+        e2e_steps = max(10, min(args.steps, 2000))
+        for i in range(max(3, args.warmup)):
+            sets[i % N_SETS].step_from_host(hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), ho.data_ptr())
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        for i in range(e2e_steps):
+            sets[i % N_SETS].step_from_host(hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), ho.data_ptr())
+        f1.record(stream)
+        barrier()
+        e2e_ms = f0.elapsed_time(f1)
+        assert torch.isfinite(ho.float()).all(), "e2e output is not finite"
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+
+    # ---------------- reduce over ranks: max time, sum bytes ----------------
+    t = torch.tensor([total_ms, e2e_ms, attend_ms], dtype=torch.float64, device="cuda")
+    b = torch.tensor([float(step_bytes)], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(b, op=dist.ReduceOp.SUM)
+    total_ms, e2e_ms, attend_ms_max = [float(x) for x in t.tolist()]
+    all_bytes = float(b.item())
+
+    if rank == 0:
+        peak, peak_src = measured_peaks()
+        achieved = step_bytes / (attend_ms * 1e-3) / 1e9          # this rank's decode op: algorithmic bytes / duration
+        line = {
+            "metric": "decode_attn_kv_bandwidth", "value": all_bytes * args.steps / (total_ms * 1e-3) / 1e9, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": workload_config(world),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": (TRAFFIC_PER_ALGO_BYTE * step_bytes) if TRAFFIC_PER_ALGO_BYTE else None,
+                         "peak_source": f"{peak_src} (copy bandwidth)",
+                         "kernel": "decode16_kernel<half,128> + its split merge, per attend call",
+                         "algorithmic_bytes_per_launch": step_bytes, "avg_launch_ms": attend_ms},
+            "e2e": {"value": all_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": d0.in_bytes, "d2h_bytes_per_step": d0.out_bytes, "steps": e2e_steps,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": sampler.summary(t_wall0, t_wall1),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(rank, sets[0], lens)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    gpu.close()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        sys.exit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

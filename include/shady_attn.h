@@ -158,8 +158,14 @@ typedef struct {
 } shady_decode_params;
 
 /* Bytes of scratch `shady_attn_decode` needs for these parameters (upper bound over any
- * sequence lengths; 0 when num_splits == 1). */
+ * sequence lengths; 0 when num_splits == 1).  It replaces the reference's `attn_partials`
+ * buffer (model.rs:219-224, 236). */
 int shady_decode_workspace_size(const shady_decode_params *p, size_t *bytes);
+/* The workspace starts with arrival counters that must be zero before its first use: call this
+ * once after allocating it (stream-ordered memset).  Every decode call leaves them zero again, so
+ * no further clearing is needed unless a call was interrupted by an error. */
+int shady_decode_workspace_init(shady_ctx *ctx, const shady_decode_params *p, void *d_workspace,
+                                size_t workspace_bytes);
 
 /* d_q [num_seqs][nh][hd]; d_seq_lens [num_seqs] u32 = rows to attend to, *including* the
  * token just appended (model.rs:521).  d_out [num_seqs][nh][hd].  d_lse: optional
@@ -168,7 +174,8 @@ int shady_decode_workspace_size(const shady_decode_params *p, size_t *bytes);
  * the output is multiplied by sigmoid(gate) (fuses Model::sigmoid_mul_gate, model.rs:576).
  * seq_lens_host: the same lengths in host memory, used only to balance the split plan when
  * num_splits == 0 (may be NULL otherwise).  A sequence of length 0 yields zeros and
- * lse = -inf. */
+ * lse = -inf.  Splits are merged inside the same launch by the last CTA to arrive
+ * (gqa_reduce.wgsl math); calls that share one workspace must not overlap on the GPU. */
 int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
                       const shady_kv_cache *cache, const uint32_t *d_seq_lens,
                       const uint32_t *seq_lens_host, void *d_out, float *d_lse, const float *d_gate,

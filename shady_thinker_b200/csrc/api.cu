@@ -15,7 +15,8 @@ int fail(shady_ctx *ctx, int code, const std::string &msg) {
 }
 
 // launchers implemented in the kernel translation units
-size_t decode_workspace_bytes(const shady_ctx *ctx, const shady_decode_params *p, uint32_t kv_dtype);
+size_t decode_workspace_bytes(const shady_decode_params *p);
+int init_decode_workspace(shady_ctx *, const shady_decode_params *, void *, size_t);
 int launch_decode(shady_ctx *, const shady_decode_params *, const void *, const shady_kv_cache *, const uint32_t *,
                   const uint32_t *, void *, float *, const float *, void *, size_t, float *);
 int launch_reduce(shady_ctx *, uint32_t, uint32_t, uint32_t, uint64_t, uint64_t, const float *, void *, uint32_t,
@@ -156,8 +157,13 @@ int shady_kv_append_rope(shady_ctx *ctx, const shady_append_params *p, const voi
 
 int shady_decode_workspace_size(const shady_decode_params *p, size_t *bytes) {
     if (!p || !bytes) return SHADY_ERR_BAD_ARG;
-    *bytes = decode_workspace_bytes(nullptr, p, SHADY_F16);
+    *bytes = decode_workspace_bytes(p);
     return SHADY_OK;
+}
+
+int shady_decode_workspace_init(shady_ctx *ctx, const shady_decode_params *p, void *d_workspace, size_t workspace_bytes) {
+    CTX_ENTER(ctx);
+    return init_decode_workspace(ctx, p, d_workspace, workspace_bytes);
 }
 
 int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,

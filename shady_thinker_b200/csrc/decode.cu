@@ -13,14 +13,20 @@
 //   * fp32 caches (the reference's native format): lanes span head_dim with 128-bit
 //     loads, warp-shuffle dot products, fp32 FMA;
 //   * ranges come either from an explicit num_splits (ceil(L/ns) ranges, wgsl:46-48) or
-//     from a length-balanced chunking that every CTA re-derives from the device-side
-//     lengths with a warp scan, so no plan has to be uploaded.
+//     from a balanced partition: all sequences laid end to end are cut into as many equal
+//     spans as there are resident CTAs (one wave, no tail); every CTA re-derives its span
+//     from the device-side lengths with a warp scan, so no plan has to be uploaded;
+//   * the splits of a sequence are merged inside the same launch by the CTA that arrives
+//     last (self-resetting arrival counters), not by a second kernel.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace shady {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+constexpr uint32_t kBlkPos = 16;  // positions per row-block: unit of the work line and of the MMA pipeline
 
 struct DecodeArgs {
     const void *q;
@@ -29,102 +35,253 @@ struct DecodeArgs {
     const float *gate;
     KvAddr kv;
     const uint32_t *seq_lens;
-    float *partials;     // workspace: per sequence [nh][ns][hd+2]
-    uint2 *seq_info;     // workspace: per sequence {ns, first split index}
+    float *partials;     // workspace: split records of (hd+2) floats
+    uint32_t *counters;  // workspace: arrivals per (sequence, kv head, head group); zero between calls
+    uint32_t gz;         // head groups per kv head (folded into blockIdx.x)
     uint32_t num_seqs, nkv, nh, G, hd;
-    uint32_t num_splits; // >0 explicit, 0 = chunked
-    uint32_t chunk;      // positions per split in chunked mode
+    uint32_t num_splits; // >0: every sequence is cut into ceil(L/ns) ranges (wgsl:46-48); 0: balanced spans
+    uint32_t line_blocks; // balanced mode: total row-blocks of the batch, sum_i max(1, ceil(L_i/16))
+    uint32_t spans;       // balanced mode: number of equal spans the line is cut into
     uint32_t q_dtype, out_dtype;
     uint32_t force_partials;  // 1: always write the partial record (shady_attn_decode_partials)
     float scale_log2;         // 1/sqrt(hd) * log2(e)
 };
 
-__device__ __forceinline__ uint32_t splits_of(const DecodeArgs &a, uint32_t L) {
-    if (a.num_splits) return a.num_splits;
-    return L == 0 ? 1u : (L + a.chunk - 1u) / a.chunk;
+// ---- balanced ("stream-K") partition of the batch -------------------------------------------
+// All sequences are laid end to end on a line of 16-position row-blocks; span c owns blocks
+// [ceil(c*T/C), ceil((c+1)*T/C)).  A span may end one sequence, hold several whole ones and start
+// another; each intersection is a "piece".  Every CTA streams the same number of rows, so there is
+// one full wave and no tail.
+__device__ __forceinline__ uint32_t span_begin(const DecodeArgs &a, uint32_t c) {
+    return (uint32_t)(((unsigned long long)c * a.line_blocks + a.spans - 1) / a.spans);
+}
+__device__ __forceinline__ uint32_t span_of(const DecodeArgs &a, uint32_t u) {
+    return (uint32_t)(((unsigned long long)u * a.spans) / a.line_blocks);
+}
+__device__ __forceinline__ uint32_t blocks_of(uint32_t L) { return L == 0 ? 1u : (L + kBlkPos - 1) / kBlkPos; }
+
+struct Piece {
+    uint32_t seq, L, start, end;  // positions [start, end) of sequence seq
+    uint32_t nrec;                // records this sequence is split into (1 => written directly)
+    uint32_t my_rec;              // which of them this piece is
+    uint32_t c0;                  // balanced: first span of the sequence; explicit: seq * ns
+    uint32_t B;                   // balanced: first row-block of the sequence on the line
+};
+struct Cursor {
+    uint32_t seq, B, u, u1, span, done;
+};
+
+// Record r of `head` for the sequence a piece belongs to.
+__device__ __forceinline__ float *rec_ptr(const DecodeArgs &a, const Piece &p, uint32_t head, uint32_t r) {
+    if (a.num_splits || a.force_partials)  // reference layout [nh][ns][hd+2] per sequence (wgsl:112-123)
+        return a.partials + ((size_t)p.c0 * a.nh + (size_t)head * p.nrec + r) * (a.hd + 2);
+    // balanced: two slots per span — slot 0 if the piece starts at the span's first block, else slot 1
+    const uint32_t c = p.c0 + r;
+    const uint32_t slot = span_begin(a, c) >= p.B ? 0u : 1u;
+    return a.partials + (((size_t)c * 2 + slot) * a.nh + head) * (a.hd + 2);
 }
 
-// Map blockIdx.x -> (sequence, split, splits of that sequence, splits before it).
-// Executed by warp 0; result broadcast through shared memory by the caller.
-__device__ __forceinline__ void resolve_item(const DecodeArgs &a, uint32_t item, uint32_t lane,
-                                             uint32_t *res /*[4]*/) {
+// Position the cursor at this CTA's first piece.  Warp 0 scans the lengths; res is shared memory.
+__device__ __forceinline__ void cursor_init(const DecodeArgs &a, uint32_t work, uint32_t lane, uint32_t *res) {
     if (a.num_splits) {
-        if (lane == 0) {
-            res[0] = item / a.num_splits;
-            res[1] = item % a.num_splits;
-            res[2] = a.num_splits;
-            res[3] = (item / a.num_splits) * a.num_splits;
-        }
+        if (lane == 0) { res[0] = work / a.num_splits; res[1] = 0; res[2] = work % a.num_splits; res[3] = 0; res[4] = 0; }
         return;
     }
+    const uint32_t u0 = span_begin(a, work), u1 = span_begin(a, work + 1);
     uint32_t pref = 0;
     bool found = false;
     for (uint32_t base = 0; base < a.num_seqs && !found; base += 32) {
         const uint32_t j = base + lane;
-        const uint32_t ns = j < a.num_seqs ? splits_of(a, a.seq_lens[j]) : 0u;
-        uint32_t incl = ns;
+        const uint32_t nb = j < a.num_seqs ? blocks_of(a.seq_lens[j]) : 0u;
+        uint32_t incl = nb;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
             if (lane >= (uint32_t)o) incl += n;
         }
         const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-        if (item < pref + total) {
-            const uint32_t mask = __ballot_sync(0xffffffffu, pref + incl > item);
+        if (u0 < pref + total) {
+            const uint32_t mask = __ballot_sync(0xffffffffu, pref + incl > u0);
             const uint32_t f = __ffs(mask) - 1;
-            const uint32_t ns_f = __shfl_sync(0xffffffffu, ns, f);
-            const uint32_t excl = __shfl_sync(0xffffffffu, incl, f) - ns_f;
-            if (lane == 0) {
-                res[0] = base + f;
-                res[1] = item - pref - excl;
-                res[2] = ns_f;
-                res[3] = pref + excl;
-            }
+            const uint32_t excl = __shfl_sync(0xffffffffu, incl, f) - __shfl_sync(0xffffffffu, nb, f);
+            if (lane == 0) { res[0] = base + f; res[1] = pref + excl; res[2] = u0; res[3] = u1; res[4] = 0; }
             found = true;
         }
         pref += total;
     }
-    if (!found && lane == 0) res[0] = 0xffffffffu;  // grid larger than the work: idle CTA
+    if (!found && lane == 0) { res[0] = a.num_seqs; res[1] = 0; res[2] = 0; res[3] = 0; res[4] = 1; }
 }
 
-// Merge the per-warp (m, l, O) states of one CTA and write either the final rows or the
-// split's partial record ([hd] = lse, [hd+1] = running max as in wgsl:112-123).
-template <int R, int HD, int NW>
-__device__ __forceinline__ void finish_cta(const DecodeArgs &a, const float *sm_m, const float *sm_l,
-                                           const float *sm_o, uint32_t seq, uint32_t split, uint32_t ns,
-                                           uint32_t pref, uint32_t head0, uint32_t rows_valid) {
-    const bool direct = (ns == 1u) && !a.force_partials;
-    for (uint32_t idx = threadIdx.x; idx < rows_valid * HD; idx += NW * 32) {
-        const uint32_t r = idx / HD, d = idx % HD;
+__device__ __forceinline__ bool next_piece(const DecodeArgs &a, Cursor &cur, Piece &p) {
+    if (cur.done) return false;
+    if (a.num_splits) {
+        cur.done = 1;
+        const uint32_t ns = a.num_splits, split = cur.u;
+        p.seq = cur.seq; p.L = a.seq_lens[cur.seq];
+        const uint32_t pps = (p.L + ns - 1u) / ns;  // wgsl:46
+        p.start = min(split * pps, p.L); p.end = min(p.start + pps, p.L);
+        p.nrec = ns; p.my_rec = split; p.c0 = cur.seq * ns; p.B = 0;
+        return true;
+    }
+    if (cur.u >= cur.u1 || cur.seq >= a.num_seqs) return false;
+    const uint32_t L = a.seq_lens[cur.seq], nb = blocks_of(L);
+    const uint32_t ub1 = min(cur.u1, cur.B + nb);
+    p.seq = cur.seq; p.L = L;
+    p.start = min((cur.u - cur.B) * kBlkPos, L);
+    p.end = min((ub1 - cur.B) * kBlkPos, L);
+    p.B = cur.B; p.c0 = span_of(a, cur.B);
+    p.nrec = span_of(a, cur.B + nb - 1) - p.c0 + 1;
+    p.my_rec = cur.span - p.c0;
+    cur.u = ub1;
+    if (ub1 == cur.B + nb) { cur.B += nb; cur.seq++; }
+    return true;
+}
+
+// Merge the per-warp (m, l, O) states of one CTA for one piece and write either the final rows or
+// the piece's record ([hd] = lse, [hd+1] = running max as in wgsl:112-123).  When the sequence has
+// several records, the CTA that arrives last for its (sequence, kv head, head group) merges all of
+// them (gqa_reduce.wgsl:20-65) — no second launch.
+// Warp w's O tile starts at sm_o + w*WSTRIDE floats, rows of HD floats.
+// The CTA serves KPC kv heads (kvh_base + k); warps k, k+KPC, k+2*KPC, ... share kv head k.
+template <int R, int HD, int NW, int WSTRIDE, int KPC>
+__device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p, const float *sm_m, const float *sm_l,
+                                             const float *sm_o, uint32_t *sm_flag, uint32_t *scratch,
+                                             uint32_t scratch_words, uint32_t kvh_base, uint32_t row0,
+                                             uint32_t rows_valid, uint32_t counter_idx) {
+    const bool direct = (p.nrec == 1u) && !a.force_partials;
+    for (uint32_t idx = threadIdx.x; idx < KPC * rows_valid * HD; idx += NW * 32) {
+        const uint32_t d = idx % HD, r = (idx / HD) % rows_valid, kvl = idx / (HD * rows_valid);
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) M = fmaxf(M, sm_m[w * R + r]);
+        for (int w = 0; w < NW; ++w)
+            if (w % KPC == (int)kvl) M = fmaxf(M, sm_m[w * R + r]);
         float L = 0.f, o = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
+            if (w % KPC != (int)kvl) continue;
             const float mw = sm_m[w * R + r];
             if (mw > -INFINITY) {
                 const float e = exp2f(mw - M);
                 L += sm_l[w * R + r] * e;
-                o += sm_o[((size_t)w * R + r) * HD + d] * e;
+                o += sm_o[(size_t)w * WSTRIDE + r * HD + d] * e;
             }
         }
         float val = L > 0.f ? o / L : 0.f;
         const float lse = L > 0.f ? logf(L) + M * kLn2 : -INFINITY;
-        const uint32_t head = head0 + r;
+        const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
         if (direct) {
-            const size_t oi = ((size_t)seq * a.nh + head) * HD + d;
+            const size_t oi = ((size_t)p.seq * a.nh + head) * HD + d;
             if (a.gate) val *= sigmoidf_ref(a.gate[oi]);
             store_from_f32(a.out, oi, a.out_dtype, val);
-            if (d == 0 && a.lse) a.lse[(size_t)seq * a.nh + head] = lse;
+            if (d == 0 && a.lse) a.lse[(size_t)p.seq * a.nh + head] = lse;
         } else {
-            float *rec = a.partials + ((size_t)pref * a.nh + (size_t)head * ns + split) * (HD + 2);
+            float *rec = rec_ptr(a, p, head, p.my_rec);
             rec[d] = val;
             if (d == 0) {
                 rec[HD] = lse;
                 rec[HD + 1] = L > 0.f ? M * kLn2 : -INFINITY;
             }
         }
+    }
+    if (direct || a.force_partials) return;
+    // ---- last-arriving CTA merges the records ----
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // atomicInc wraps to 0 when the old value is nrec-1, so the counter is zero again for the next call
+        const uint32_t old = atomicInc(&a.counters[counter_idx], p.nrec - 1u);
+        *sm_flag = (old == p.nrec - 1u);
+    }
+    __syncthreads();
+    if (!*sm_flag) return;
+    __threadfence();
+    // scratch: [nrec] record bases | [rows] gmax | [rows] wsum | [RG][nrec] weights
+    const uint32_t nrec = p.nrec, rows_total = KPC * rows_valid;
+    uint32_t *sm_rec = scratch;
+    float *sm_gmax = reinterpret_cast<float *>(scratch + nrec);
+    float *sm_wsum = sm_gmax + rows_total;
+    float *sm_w = sm_wsum + rows_total;
+    const uint32_t RG = min(rows_total, (scratch_words - nrec - 2 * rows_total) / nrec);  // >= 1 by construction
+    // record s of head h lives at partials + (sm_rec[s] + h*hmul) * (HD+2)
+    const uint32_t hmul = (a.num_splits || a.force_partials) ? nrec : 1u;
+    for (uint32_t s = threadIdx.x; s < nrec; s += NW * 32) {
+        if (a.num_splits) sm_rec[s] = p.c0 * a.nh + s;
+        else {
+            const uint32_t c = p.c0 + s;
+            sm_rec[s] = (c * 2 + (span_begin(a, c) >= p.B ? 0u : 1u)) * a.nh;
+        }
+    }
+    __syncthreads();
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t rg0 = 0; rg0 < rows_total; rg0 += RG) {
+        const uint32_t nrows = min(RG, rows_total - rg0);
+        // weights of every record for each head row: w_s = exp(lse_s - max lse)  (gqa_reduce.wgsl:33-56)
+        for (uint32_t row = warp; row < nrows; row += NW) {
+            const uint32_t hr = rg0 + row, r = hr % rows_valid, kvl = hr / rows_valid;
+            const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
+            float gmax = -INFINITY;
+            for (uint32_t s = lane; s < nrec; s += 32) {
+                const float l = __ldcg(a.partials + ((size_t)sm_rec[s] + (size_t)head * hmul) * (HD + 2) + HD);
+                sm_w[row * nrec + s] = l;
+                if (l > -INFINITY) gmax = fmaxf(gmax, l);  // false for -inf and NaN: empty ranges
+            }
+            gmax = warp_max(gmax);
+            float wsum = 0.f;
+            for (uint32_t s = lane; s < nrec; s += 32) {
+                const float l = sm_w[row * nrec + s];
+                const float w = l > -INFINITY ? expf(l - gmax) : 0.f;
+                sm_w[row * nrec + s] = w;
+                wsum += w;
+            }
+            wsum = warp_sum(wsum);
+            if (lane == 0) { sm_gmax[hr] = gmax; sm_wsum[hr] = wsum; }
+        }
+        __syncthreads();
+        // EU independent elements per thread keep EU record loads in flight: the merge is L2-latency bound
+        constexpr uint32_t EU = 4, NT = NW * 32;
+        const uint32_t nelem = nrows * HD;
+        for (uint32_t idx0 = threadIdx.x; idx0 < nelem; idx0 += NT * EU) {
+            float acc[EU];
+            const float *src[EU];
+            const float *wrow[EU];
+#pragma unroll
+            for (uint32_t k = 0; k < EU; ++k) {
+                const uint32_t idx = min(idx0 + k * NT, nelem - 1);   // clamped lanes recompute a valid element
+                const uint32_t d = idx % HD, row = idx / HD;
+                const uint32_t hr = rg0 + row, r = hr % rows_valid, kvl = hr / rows_valid;
+                const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
+                src[k] = a.partials + (size_t)head * hmul * (HD + 2) + d;
+                wrow[k] = sm_w + row * nrec;
+                acc[k] = 0.f;
+            }
+#pragma unroll 2
+            for (uint32_t s = 0; s < nrec; ++s) {
+                const size_t off = (size_t)sm_rec[s] * (HD + 2);
+                float v[EU];
+#pragma unroll
+                for (uint32_t k = 0; k < EU; ++k) v[k] = __ldcg(src[k] + off);
+#pragma unroll
+                for (uint32_t k = 0; k < EU; ++k) {
+                    const float w = wrow[k][s];
+                    acc[k] += w > 0.f ? w * v[k] : 0.f;   // weight 0 also hides NaN payloads of empty ranges
+                }
+            }
+#pragma unroll
+            for (uint32_t k = 0; k < EU; ++k) {
+                const uint32_t idx = idx0 + k * NT;
+                if (idx >= nelem) break;
+                const uint32_t d = idx % HD, row = idx / HD;
+                const uint32_t hr = rg0 + row, r = hr % rows_valid, kvl = hr / rows_valid;
+                const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
+                const float wsum = sm_wsum[hr];
+                float val = wsum > 0.f ? acc[k] / wsum : 0.f;
+                const size_t oi = ((size_t)p.seq * a.nh + head) * HD + d;
+                if (a.gate) val *= sigmoidf_ref(a.gate[oi]);
+                store_from_f32(a.out, oi, a.out_dtype, val);
+                if (d == 0 && a.lse) a.lse[(size_t)p.seq * a.nh + head] = wsum > 0.f ? sm_gmax[hr] + logf(wsum) : -INFINITY;
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -171,239 +328,226 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
-constexpr int kBlk = 16;  // positions per warp block (one MMA k-step of P·V)
+constexpr int kBlk = (int)kBlkPos;  // positions per warp block (one MMA k-step of P·V)
 
-template <int HD, int NW, int STAGES> struct Decode16Smem {
+template <int HD, int NW, int STAGES, int KPC> struct Decode16Smem {
     static constexpr int kRowBytes = HD * 2;
     static constexpr int kTileBytes = kBlk * kRowBytes;          // one K or V block
     static constexpr int kStageBytes = 2 * kTileBytes;           // K + V
     static constexpr int kWarpBytes = STAGES * kStageBytes;
-    static constexpr int kQBytes = 16 * kRowBytes;
+    static constexpr int kQTile = 16 * kRowBytes;                // Q rows of one kv head
+    static constexpr int kQBytes = KPC * kQTile;
     static constexpr int kStatBytes = 2 * NW * 16 * 4;           // merge m and l
-    static constexpr int kTotal = kQBytes + NW * kWarpBytes + kStatBytes + 16;
+    static constexpr int kTotal = kQBytes + NW * kWarpBytes + kStatBytes + 32;
     static_assert(kWarpBytes >= 16 * HD * 4, "merge tile must fit in the warp's pipeline memory");
 };
 
-template <typename T, int HD, int NW, int STAGES>
-__global__ void __launch_bounds__(NW * 32) decode16_kernel(const DecodeArgs a) {
-    using S = Decode16Smem<HD, NW, STAGES>;
-    constexpr int CH = HD / 8;  // 16-byte chunks per row
+// Resident CTAs per SM each configuration is built for (bounds the registers per thread).
+constexpr int decode16_min_blocks(int HD, int NW, int STAGES) {
+    return HD > 128 ? 1 : (NW == 4 ? (STAGES <= 3 ? 2 : 1) : 1);
+}
+
+// KPC kv heads per CTA: warp w streams kv head (w % KPC) of the CTA's rows, and the WPK = NW/KPC warps
+// that share a kv head take alternate 16-position blocks.  With KPC == nkv a CTA reads whole cache rows.
+template <typename T, int HD, int NW, int STAGES, int KPC>
+__global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) decode16_kernel(const DecodeArgs a) {
+    using S = Decode16Smem<HD, NW, STAGES, KPC>;
+    constexpr int WPK = NW / KPC;
+    static_assert(NW % KPC == 0, "warps must divide evenly over the kv heads of a CTA");
+    constexpr int CH = HD / 8;            // 16-byte chunks per row
+    constexpr bool QREG = HD <= 128;      // keep the Q fragments in registers (else re-read them from shared memory)
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char *sm_q = smem;
     unsigned char *sm_pipe = smem + S::kQBytes;
     float *sm_m = reinterpret_cast<float *>(smem + S::kQBytes + NW * S::kWarpBytes);
     float *sm_l = sm_m + NW * 16;
-    uint32_t *sm_item = reinterpret_cast<uint32_t *>(sm_l + NW * 16);
+    uint32_t *sm_item = reinterpret_cast<uint32_t *>(sm_l + NW * 16);  // 8 words
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (warp == 0) resolve_item(a, blockIdx.x, lane, sm_item);
+    // blockIdx.x = (work * KG + kg) * gz + z, KG = nkv / KPC groups of kv heads
+    const uint32_t KG = a.nkv / KPC;
+    const uint32_t zi = blockIdx.x % a.gz, kg = (blockIdx.x / a.gz) % KG;
+    const uint32_t work = blockIdx.x / (a.gz * KG);
+    if (warp == 0) cursor_init(a, work, lane, sm_item);
     __syncthreads();
-    const uint32_t seq = sm_item[0], split = sm_item[1], ns = sm_item[2], pref = sm_item[3];
-    if (seq == 0xffffffffu) return;
-    const uint32_t kvh = blockIdx.y;
-    const uint32_t row0 = blockIdx.z * 16;                         // first head of the group handled here
+    Cursor cur{sm_item[0], sm_item[1], sm_item[2], sm_item[3], work, sm_item[4]};
+    __syncthreads();  // sm_item[7] is reused as the merge flag below
+    const uint32_t kvl = warp % KPC, sub = warp / KPC;             // kv head within the CTA, block phase
+    const uint32_t kvh = kg * KPC + kvl;
+    const uint32_t row0 = zi * 16;                                 // first head of the group handled here
     const uint32_t rows_valid = min(16u, a.G - row0);
-    const uint32_t head0 = kvh * a.G + row0;
-    const uint32_t L = a.seq_lens[seq];
-    const uint32_t pps = (L + ns - 1u) / ns;                       // wgsl:46
-    const uint32_t start = min(split * pps, L);
-    const uint32_t end = min(start + pps, L);
-    if (split == 0 && kvh == 0 && blockIdx.z == 0 && tid == 0 && a.seq_info) a.seq_info[seq] = make_uint2(ns, pref);
-
-    // ---- stage Q (rows >= rows_valid are zero) as T, swizzled ----
-    for (uint32_t idx = tid; idx < 16 * CH; idx += NW * 32) {
-        const uint32_t r = idx / CH, c = idx % CH;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < rows_valid) {
-            const size_t e0 = ((size_t)seq * a.nh + head0 + r) * HD + c * 8;
-            if (a.q_dtype == SHADY_F32) {
-                const float4 f0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(a.q) + e0);
-                const float4 f1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(a.q) + e0 + 4);
-                v.x = pack2<T>(f0.x, f0.y); v.y = pack2<T>(f0.z, f0.w);
-                v.z = pack2<T>(f1.x, f1.y); v.w = pack2<T>(f1.z, f1.w);
-            } else {
-                v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.q) + e0);
-            }
-        }
-        *reinterpret_cast<uint4 *>(sm_q + r * S::kRowBytes + ((c ^ (r & 7)) << 4)) = v;
-    }
-    __syncthreads();
 
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t mat = lane >> 3, rin = lane & 7;
-    const uint32_t sm_q_addr = (uint32_t)__cvta_generic_to_shared(sm_q);
-    // Q fragments (A operand), one ldmatrix.x4 per k-step: mats = (rows0-7,c), (rows8-15,c), (rows0-7,c+1), (rows8-15,c+1)
-    uint32_t qa[HD / 16][4];
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint32_t row = (mat & 1) * 8 + rin, chunk = 2 * ks + (mat >> 1);
-        ldsm_x4(qa[ks], sm_q_addr + row * S::kRowBytes + ((chunk ^ rin) << 4));
-    }
-
-    const char *kbase = kv_seq_ptr(a.kv.k_base, a.kv.k_ptrs, a.kv.seq_stride_bytes, seq) + (size_t)kvh * S::kRowBytes;
-    const char *vbase = kv_seq_ptr(a.kv.v_base, a.kv.v_ptrs, a.kv.seq_stride_bytes, seq) + (size_t)kvh * S::kRowBytes;
-    const size_t pos_stride = (size_t)a.nkv * S::kRowBytes;
-
-    const uint32_t nblk = (end - start + kBlk - 1) / kBlk;
-    const uint32_t my_n = nblk > warp ? (nblk - warp + NW - 1) / NW : 0;
+    const uint32_t sm_q_addr = (uint32_t)__cvta_generic_to_shared(sm_q) + kvl * S::kQTile;
     const uint32_t warp_smem = (uint32_t)__cvta_generic_to_shared(sm_pipe + warp * S::kWarpBytes);
-
+    const size_t pos_stride = (size_t)a.nkv * S::kRowBytes;
     // per-lane load geometry: a warp instruction copies 512 bytes = 512/kRowBytes rows
     constexpr int RPI = 512 / S::kRowBytes;          // rows per instruction (2 for hd128, 1 for hd256)
     constexpr int NI = kBlk / RPI;                   // instructions per tile
     const uint32_t l_row = lane / CH * (RPI > 1), l_chunk = lane % CH;
-    auto issue = [&](uint32_t bi) {
-        const uint32_t pos0 = start + (warp + bi * NW) * kBlk;
-        const uint32_t st = warp_smem + (bi % STAGES) * S::kStageBytes;
-#pragma unroll
-        for (int i = 0; i < NI; ++i) {
-            const uint32_t r = i * RPI + l_row;
-            const bool ok = pos0 + r < end;
-            const size_t goff = (size_t)(pos0 + r) * pos_stride + l_chunk * 16;
-            const uint32_t soff = r * S::kRowBytes + ((l_chunk ^ (r & 7)) << 4);
-            cp_async16(st + soff, kbase + (ok ? goff : 0), ok);
-            cp_async16(st + S::kTileBytes + soff, vbase + (ok ? goff : 0), ok);
-        }
-    };
 
-    float o[HD / 8][4];
+    Piece p;
+    while (next_piece(a, cur, p)) {
+        const uint32_t start = p.start, end = p.end;
+        const char *kbase = kv_seq_ptr(a.kv.k_base, a.kv.k_ptrs, a.kv.seq_stride_bytes, p.seq) + (size_t)kvh * S::kRowBytes;
+        const char *vbase = kv_seq_ptr(a.kv.v_base, a.kv.v_ptrs, a.kv.seq_stride_bytes, p.seq) + (size_t)kvh * S::kRowBytes;
+        const uint32_t nblk = (end - start + kBlk - 1) / kBlk;
+        const uint32_t my_n = nblk > sub ? (nblk - sub + WPK - 1) / WPK : 0;
+        auto issue = [&](uint32_t bi) {
+            const uint32_t pos0 = start + (sub + bi * WPK) * kBlk;
+            const uint32_t st = warp_smem + (bi % STAGES) * S::kStageBytes;
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if ((uint32_t)s < my_n) issue(s);
-        cp_async_commit();
-    }
-    for (uint32_t i = 0; i < my_n; ++i) {
-        cp_async_wait<STAGES - 2>();
-        __syncwarp();
-        if (i + STAGES - 1 < my_n) issue(i + STAGES - 1);
-        cp_async_commit();
-
-        const uint32_t st = warp_smem + (i % STAGES) * S::kStageBytes;
-        const uint32_t pos0 = start + (warp + i * NW) * kBlk;
-        // ---- S = Q K^T : heads x 16 positions ----
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-            uint32_t kb[4];
-            const uint32_t row = (mat >> 1) * 8 + rin, chunk = 2 * ks + (mat & 1);
-            ldsm_x4(kb, st + row * S::kRowBytes + ((chunk ^ rin) << 4));
-            mma16816<T>(s[0], qa[ks], kb[0], kb[1]);
-            mma16816<T>(s[1], qa[ks], kb[2], kb[3]);
-        }
-        // ---- online softmax (log2 domain), rows g and g+8 ----
-        float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint32_t pos = pos0 + 8 * j + 2 * t + (c & 1);
-                s[j][c] = pos < end ? s[j][c] * a.scale_log2 : -INFINITY;
-                mx[c >> 1] = fmaxf(mx[c >> 1], s[j][c]);
+            for (int i = 0; i < NI; ++i) {
+                const uint32_t r = i * RPI + l_row;
+                const bool ok = pos0 + r < end;
+                const size_t goff = (size_t)(pos0 + r) * pos_stride + l_chunk * 16;
+                const uint32_t soff = r * S::kRowBytes + ((l_chunk ^ (r & 7)) << 4);
+                cp_async16(st + soff, kbase + (ok ? goff : 0), ok);
+                cp_async16(st + S::kTileBytes + soff, vbase + (ok ? goff : 0), ok);
             }
-        float corr[2];
+        };
+        // ---- start the K/V stream first, then fetch Q underneath it ----
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if ((uint32_t)s < my_n) issue(s);
+            cp_async_commit();
+        }
+        // stage Q of the CTA's kv heads (rows >= rows_valid are zero) as T, swizzled
+        for (uint32_t idx = tid; idx < KPC * 16 * CH; idx += NW * 32) {
+            const uint32_t c = idx % CH, r = (idx / CH) % 16, k = idx / (CH * 16);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < rows_valid) {
+                const size_t e0 = ((size_t)p.seq * a.nh + (kg * KPC + k) * a.G + row0 + r) * HD + c * 8;
+                if (a.q_dtype == SHADY_F32) {
+                    const float4 f0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(a.q) + e0);
+                    const float4 f1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(a.q) + e0 + 4);
+                    v.x = pack2<T>(f0.x, f0.y); v.y = pack2<T>(f0.z, f0.w);
+                    v.z = pack2<T>(f1.x, f1.y); v.w = pack2<T>(f1.z, f1.w);
+                } else {
+                    v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.q) + e0);
+                }
+            }
+            *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kRowBytes + ((c ^ (r & 7)) << 4)) = v;
+        }
+        __syncthreads();
+        // Q fragments (A operand), one ldmatrix.x4 per k-step: mats = (rows0-7,c), (rows8-15,c), (rows0-7,c+1), (rows8-15,c+1)
+        uint32_t qa[QREG ? HD / 16 : 1][4];
+        if constexpr (QREG) {
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                const uint32_t row = (mat & 1) * 8 + rin, chunk = 2 * ks + (mat >> 1);
+                ldsm_x4(qa[ks], sm_q_addr + row * S::kRowBytes + ((chunk ^ rin) << 4));
+            }
+        }
+
+        float o[HD / 8][4];
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+        for (uint32_t i = 0; i < my_n; ++i) {
+            cp_async_wait<STAGES - 2>();
+            __syncwarp();
+            if (i + STAGES - 1 < my_n) issue(i + STAGES - 1);
+            cp_async_commit();
+
+            const uint32_t st = warp_smem + (i % STAGES) * S::kStageBytes;
+            const uint32_t pos0 = start + (sub + i * WPK) * kBlk;
+            // ---- S = Q K^T : heads x 16 positions ----
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                uint32_t kb[4];
+                const uint32_t row = (mat >> 1) * 8 + rin, chunk = 2 * ks + (mat & 1);
+                ldsm_x4(kb, st + row * S::kRowBytes + ((chunk ^ rin) << 4));
+                if constexpr (QREG) {
+                    mma16816<T>(s[0], qa[ks], kb[0], kb[1]);
+                    mma16816<T>(s[1], qa[ks], kb[2], kb[3]);
+                } else {
+                    const uint32_t qrow = (mat & 1) * 8 + rin, qchunk = 2 * ks + (mat >> 1);
+                    ldsm_x4(qa[0], sm_q_addr + qrow * S::kRowBytes + ((qchunk ^ rin) << 4));
+                    mma16816<T>(s[0], qa[0], kb[0], kb[1]);
+                    mma16816<T>(s[1], qa[0], kb[2], kb[3]);
+                }
+            }
+            // ---- online softmax (log2 domain), rows g and g+8 ----
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t pos = pos0 + 8 * j + 2 * t + (c & 1);
+                    s[j][c] = pos < end ? s[j][c] * a.scale_log2 : -INFINITY;
+                    mx[c >> 1] = fmaxf(mx[c >> 1], s[j][c]);
+                }
+            float corr[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);   // finite: every block holds >= 1 valid position
+                corr[r] = exp2f(m_run[r] - m_new);
+                m_run[r] = m_new;
+            }
+            float psum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    s[j][c] = exp2f(s[j][c] - m_run[c >> 1]);
+                    psum[c >> 1] += s[j][c];
+                }
+            l_run[0] = l_run[0] * corr[0] + psum[0];
+            l_run[1] = l_run[1] * corr[1] + psum[1];
+            uint32_t pa[4];
+            pa[0] = pack2<T>(s[0][0], s[0][1]);
+            pa[1] = pack2<T>(s[0][2], s[0][3]);
+            pa[2] = pack2<T>(s[1][0], s[1][1]);
+            pa[3] = pack2<T>(s[1][2], s[1][3]);
+            // ---- O = O*corr + P V ----
+#pragma unroll
+            for (int jn = 0; jn < HD / 8; jn += 2) {
+                uint32_t vb[4];
+                const uint32_t row = (mat & 1) * 8 + rin, chunk = jn + (mat >> 1);
+                ldsm_x4_t(vb, st + S::kTileBytes + row * S::kRowBytes + ((chunk ^ rin) << 4));
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    o[jn + u][0] *= corr[0]; o[jn + u][1] *= corr[0];
+                    o[jn + u][2] *= corr[1]; o[jn + u][3] *= corr[1];
+                }
+                mma16816<T>(o[jn], pa, vb[0], vb[1]);
+                mma16816<T>(o[jn + 1], pa, vb[2], vb[3]);
+            }
+        }
+        cp_async_wait<0>();
+        __syncthreads();  // every warp is done with its pipeline memory: reuse it for the merge
+
+        // ---- per-warp state -> shared ----
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m_run[r], mx[r]);   // finite: every block holds >= 1 valid position
-            corr[r] = exp2f(m_run[r] - m_new);
-            m_run[r] = m_new;
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
         }
-        float psum[2] = {0.f, 0.f};
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                s[j][c] = exp2f(s[j][c] - m_run[c >> 1]);
-                psum[c >> 1] += s[j][c];
-            }
-        l_run[0] = l_run[0] * corr[0] + psum[0];
-        l_run[1] = l_run[1] * corr[1] + psum[1];
-        uint32_t pa[4];
-        pa[0] = pack2<T>(s[0][0], s[0][1]);
-        pa[1] = pack2<T>(s[0][2], s[0][3]);
-        pa[2] = pack2<T>(s[1][0], s[1][1]);
-        pa[3] = pack2<T>(s[1][2], s[1][3]);
-        // ---- O = O*corr + P V ----
-#pragma unroll
-        for (int jn = 0; jn < HD / 8; jn += 2) {
-            uint32_t vb[4];
-            const uint32_t row = (mat & 1) * 8 + rin, chunk = jn + (mat >> 1);
-            ldsm_x4_t(vb, st + S::kTileBytes + row * S::kRowBytes + ((chunk ^ rin) << 4));
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                o[jn + u][0] *= corr[0]; o[jn + u][1] *= corr[0];
-                o[jn + u][2] *= corr[1]; o[jn + u][3] *= corr[1];
-            }
-            mma16816<T>(o[jn], pa, vb[0], vb[1]);
-            mma16816<T>(o[jn + 1], pa, vb[2], vb[3]);
+        float *sm_o = reinterpret_cast<float *>(sm_pipe);  // warp w's [16][HD] tile at w*kWarpBytes
+        float *my_o = reinterpret_cast<float *>(sm_pipe + warp * S::kWarpBytes);
+        if (t == 0) {
+            sm_m[warp * 16 + g] = m_run[0];
+            sm_m[warp * 16 + g + 8] = m_run[1];
+            sm_l[warp * 16 + g] = l_run[0];
+            sm_l[warp * 16 + g + 8] = l_run[1];
         }
-    }
-    cp_async_wait<0>();
-    __syncthreads();  // every warp is done with its pipeline memory: reuse it for the merge
-
-    // ---- per-warp state -> shared ----
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-    }
-    float *sm_o = reinterpret_cast<float *>(sm_pipe);  // [NW][16][HD], warp w at w*kWarpBytes
-    static_assert(S::kWarpBytes % 4 == 0, "");
-    float *my_o = reinterpret_cast<float *>(sm_pipe + warp * S::kWarpBytes);
-    if (t == 0) {
-        sm_m[warp * 16 + g] = m_run[0];
-        sm_m[warp * 16 + g + 8] = m_run[1];
-        sm_l[warp * 16 + g] = l_run[0];
-        sm_l[warp * 16 + g + 8] = l_run[1];
-    }
-#pragma unroll
-    for (int jn = 0; jn < HD / 8; ++jn) {
-        *reinterpret_cast<float2 *>(my_o + g * HD + jn * 8 + 2 * t) = make_float2(o[jn][0], o[jn][1]);
-        *reinterpret_cast<float2 *>(my_o + (g + 8) * HD + jn * 8 + 2 * t) = make_float2(o[jn][2], o[jn][3]);
-    }
-    __syncthreads();
-    // finish_cta indexes warp w's tile at sm_o + w*16*HD floats; the tiles sit kWarpBytes apart,
-    // so merge through a strided view.
-    {
-        const bool direct = (ns == 1u) && !a.force_partials;
-        constexpr int WSTRIDE = S::kWarpBytes / 4;
-        for (uint32_t idx = tid; idx < rows_valid * HD; idx += NW * 32) {
-            const uint32_t r = idx / HD, d = idx % HD;
-            float M = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) M = fmaxf(M, sm_m[w * 16 + r]);
-            float Ls = 0.f, acc = 0.f;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) {
-                const float mw = sm_m[w * 16 + r];
-                if (mw > -INFINITY) {
-                    const float e = exp2f(mw - M);
-                    Ls += sm_l[w * 16 + r] * e;
-                    acc += sm_o[(size_t)w * WSTRIDE + r * HD + d] * e;
-                }
-            }
-            float val = Ls > 0.f ? acc / Ls : 0.f;
-            const float lse = Ls > 0.f ? logf(Ls) + M * kLn2 : -INFINITY;
-            const uint32_t head = head0 + r;
-            if (direct) {
-                const size_t oi = ((size_t)seq * a.nh + head) * HD + d;
-                if (a.gate) val *= sigmoidf_ref(a.gate[oi]);
-                store_from_f32(a.out, oi, a.out_dtype, val);
-                if (d == 0 && a.lse) a.lse[(size_t)seq * a.nh + head] = lse;
-            } else {
-                float *rec = a.partials + ((size_t)pref * a.nh + (size_t)head * ns + split) * (HD + 2);
-                rec[d] = val;
-                if (d == 0) {
-                    rec[HD] = lse;
-                    rec[HD + 1] = Ls > 0.f ? M * kLn2 : -INFINITY;
-                }
-            }
+        for (int jn = 0; jn < HD / 8; ++jn) {
+            *reinterpret_cast<float2 *>(my_o + g * HD + jn * 8 + 2 * t) = make_float2(o[jn][0], o[jn][1]);
+            *reinterpret_cast<float2 *>(my_o + (g + 8) * HD + jn * 8 + 2 * t) = make_float2(o[jn][2], o[jn][3]);
         }
+        __syncthreads();
+        // after its first loop finish_piece no longer reads the O tiles: the pipeline memory doubles as merge scratch
+        finish_piece<16, HD, NW, S::kWarpBytes / 4, KPC>(a, p, sm_m, sm_l, sm_o, sm_item + 7,
+                                                         reinterpret_cast<uint32_t *>(sm_pipe), NW * S::kWarpBytes / 4,
+                                                         kg * KPC, row0, rows_valid, (p.seq * KG + kg) * a.gz + zi);
+        __syncthreads();  // the next piece overwrites Q and the pipeline memory
     }
 }
 
@@ -418,146 +562,136 @@ __global__ void __launch_bounds__(NW * 32) decode32_kernel(const DecodeArgs a) {
     constexpr int U = 4;                         // positions in flight per warp
     __shared__ float sm_m[NW * GT], sm_l[NW * GT];
     __shared__ float sm_o[NW * GT * HD];
-    __shared__ uint32_t sm_item[4];
+    __shared__ uint32_t sm_item[8];
+    constexpr uint32_t kScratchWords = 3072;   // merge scratch: >= 2*spans + 2*GT for any balanced launch
+    __shared__ uint32_t sm_scratch[kScratchWords];
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (warp == 0) resolve_item(a, blockIdx.x, lane, sm_item);
+    const uint32_t zi = blockIdx.x % a.gz, kvh = (blockIdx.x / a.gz) % a.nkv;
+    const uint32_t work = blockIdx.x / (a.gz * a.nkv);
+    if (warp == 0) cursor_init(a, work, lane, sm_item);
     __syncthreads();
-    const uint32_t seq = sm_item[0], split = sm_item[1], ns = sm_item[2], pref = sm_item[3];
-    if (seq == 0xffffffffu) return;
-    const uint32_t kvh = blockIdx.y;
-    const uint32_t row0 = blockIdx.z * GT;
+    Cursor cur{sm_item[0], sm_item[1], sm_item[2], sm_item[3], work, sm_item[4]};
+    __syncthreads();
+    const uint32_t row0 = zi * GT;
     const uint32_t rows_valid = min((uint32_t)GT, a.G - row0);
     const uint32_t head0 = kvh * a.G + row0;
-    const uint32_t L = a.seq_lens[seq];
-    const uint32_t pps = (L + ns - 1u) / ns;
-    const uint32_t start = min(split * pps, L);
-    const uint32_t end = min(start + pps, L);
-    if (split == 0 && kvh == 0 && blockIdx.z == 0 && tid == 0 && a.seq_info) a.seq_info[seq] = make_uint2(ns, pref);
-
-    // lane owns dims (i*32 + lane)*VEC + e
-    float q[GT][EPL];
-#pragma unroll
-    for (int h = 0; h < GT; ++h)
-#pragma unroll
-        for (int i = 0; i < NV; ++i)
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) {
-                const uint32_t d = (i * 32 + lane) * VEC + e;
-                q[h][i * VEC + e] = (uint32_t)h < rows_valid
-                                        ? load_as_f32(a.q, ((size_t)seq * a.nh + head0 + h) * HD + d, a.q_dtype) * a.scale_log2
-                                        : 0.f;
-            }
-    float acc[GT][EPL];
-    float m_run[GT], l_run[GT];
-#pragma unroll
-    for (int h = 0; h < GT; ++h) {
-        m_run[h] = -INFINITY;
-        l_run[h] = 0.f;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[h][e] = 0.f;
-    }
-    const float *kbase = reinterpret_cast<const float *>(kv_seq_ptr(a.kv.k_base, a.kv.k_ptrs, a.kv.seq_stride_bytes, seq)) + (size_t)kvh * HD;
-    const float *vbase = reinterpret_cast<const float *>(kv_seq_ptr(a.kv.v_base, a.kv.v_ptrs, a.kv.seq_stride_bytes, seq)) + (size_t)kvh * HD;
     const size_t pos_stride = (size_t)a.nkv * HD;
 
-    for (uint32_t p0 = start + warp * U; p0 < end; p0 += NW * U) {
-        float kr[U][EPL], vr[U][EPL];
+    Piece p;
+    while (next_piece(a, cur, p)) {
+        const uint32_t start = p.start, end = p.end;
+        // lane owns dims (i*32 + lane)*VEC + e
+        float q[GT][EPL];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const uint32_t pos = min(p0 + u, end - 1);
+        for (int h = 0; h < GT; ++h)
 #pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                const size_t off = (size_t)pos * pos_stride + (i * 32 + lane) * VEC;
-                if constexpr (VEC == 4) {
-                    const float4 kk = __ldcs(reinterpret_cast<const float4 *>(kbase + off));
-                    const float4 vv = __ldcs(reinterpret_cast<const float4 *>(vbase + off));
-                    kr[u][i * 4 + 0] = kk.x; kr[u][i * 4 + 1] = kk.y; kr[u][i * 4 + 2] = kk.z; kr[u][i * 4 + 3] = kk.w;
-                    vr[u][i * 4 + 0] = vv.x; vr[u][i * 4 + 1] = vv.y; vr[u][i * 4 + 2] = vv.z; vr[u][i * 4 + 3] = vv.w;
-                } else {
+            for (int i = 0; i < NV; ++i)
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) {
-                        kr[u][i * VEC + e] = __ldcs(kbase + off + e);
-                        vr[u][i * VEC + e] = __ldcs(vbase + off + e);
+                for (int e = 0; e < VEC; ++e) {
+                    const uint32_t d = (i * 32 + lane) * VEC + e;
+                    q[h][i * VEC + e] = (uint32_t)h < rows_valid
+                                            ? load_as_f32(a.q, ((size_t)p.seq * a.nh + head0 + h) * HD + d, a.q_dtype) * a.scale_log2
+                                            : 0.f;
+                }
+        float acc[GT][EPL];
+        float m_run[GT], l_run[GT];
+#pragma unroll
+        for (int h = 0; h < GT; ++h) {
+            m_run[h] = -INFINITY;
+            l_run[h] = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) acc[h][e] = 0.f;
+        }
+        const float *kbase = reinterpret_cast<const float *>(kv_seq_ptr(a.kv.k_base, a.kv.k_ptrs, a.kv.seq_stride_bytes, p.seq)) + (size_t)kvh * HD;
+        const float *vbase = reinterpret_cast<const float *>(kv_seq_ptr(a.kv.v_base, a.kv.v_ptrs, a.kv.seq_stride_bytes, p.seq)) + (size_t)kvh * HD;
+
+        for (uint32_t p0 = start + warp * U; p0 < end; p0 += NW * U) {
+            float kr[U][EPL], vr[U][EPL];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t pos = min(p0 + u, end - 1);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    const size_t off = (size_t)pos * pos_stride + (i * 32 + lane) * VEC;
+                    if constexpr (VEC == 4) {
+                        const float4 kk = __ldcs(reinterpret_cast<const float4 *>(kbase + off));
+                        const float4 vv = __ldcs(reinterpret_cast<const float4 *>(vbase + off));
+                        kr[u][i * 4 + 0] = kk.x; kr[u][i * 4 + 1] = kk.y; kr[u][i * 4 + 2] = kk.z; kr[u][i * 4 + 3] = kk.w;
+                        vr[u][i * 4 + 0] = vv.x; vr[u][i * 4 + 1] = vv.y; vr[u][i * 4 + 2] = vv.z; vr[u][i * 4 + 3] = vv.w;
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) {
+                            kr[u][i * VEC + e] = __ldcs(kbase + off + e);
+                            vr[u][i * VEC + e] = __ldcs(vbase + off + e);
+                        }
                     }
                 }
             }
-        }
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (p0 + u >= end) break;
+            for (int u = 0; u < U; ++u) {
+                if (p0 + u >= end) break;
 #pragma unroll
-            for (int h = 0; h < GT; ++h) {
-                float dot = 0.f;
+                for (int h = 0; h < GT; ++h) {
+                    float dot = 0.f;
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) dot = fmaf(q[h][e], kr[u][e], dot);
-                dot = warp_sum(dot);  // already in log2 units (q carries scale*log2e)
-                const float m_new = fmaxf(m_run[h], dot);
-                const float corr = exp2f(m_run[h] - m_new);
-                const float p = exp2f(dot - m_new);
-                l_run[h] = l_run[h] * corr + p;
+                    for (int e = 0; e < EPL; ++e) dot = fmaf(q[h][e], kr[u][e], dot);
+                    dot = warp_sum(dot);  // already in log2 units (q carries scale*log2e)
+                    const float m_new = fmaxf(m_run[h], dot);
+                    const float corr = exp2f(m_run[h] - m_new);
+                    const float pr = exp2f(dot - m_new);
+                    l_run[h] = l_run[h] * corr + pr;
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(p, vr[u][e], acc[h][e] * corr);
-                m_run[h] = m_new;
+                    for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(pr, vr[u][e], acc[h][e] * corr);
+                    m_run[h] = m_new;
+                }
             }
         }
-    }
-    // ---- merge the warps ----
+        // ---- merge the warps ----
 #pragma unroll
-    for (int h = 0; h < GT; ++h) {
-        if (lane == 0) {
-            sm_m[warp * GT + h] = m_run[h];
-            sm_l[warp * GT + h] = l_run[h];
+        for (int h = 0; h < GT; ++h) {
+            if (lane == 0) {
+                sm_m[warp * GT + h] = m_run[h];
+                sm_l[warp * GT + h] = l_run[h];
+            }
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e)
+                    sm_o[((size_t)warp * GT + h) * HD + (i * 32 + lane) * VEC + e] = acc[h][i * VEC + e];
         }
-#pragma unroll
-        for (int i = 0; i < NV; ++i)
-#pragma unroll
-            for (int e = 0; e < VEC; ++e)
-                sm_o[((size_t)warp * GT + h) * HD + (i * 32 + lane) * VEC + e] = acc[h][i * VEC + e];
+        __syncthreads();
+        finish_piece<GT, HD, NW, GT * HD, 1>(a, p, sm_m, sm_l, sm_o, sm_item + 7, sm_scratch, kScratchWords, kvh, row0,
+                                             rows_valid, (p.seq * a.nkv + kvh) * a.gz + zi);
+        __syncthreads();
     }
-    __syncthreads();
-    finish_cta<GT, HD, NW>(a, sm_m, sm_l, sm_o, seq, split, ns, pref, head0, rows_valid);
 }
 
 // ---------------------------------------------------------------------------------------
-// Merge of split records (gqa_reduce.wgsl:20-65), batched and stride-generalised
+// Stand-alone merge of split records (gqa_reduce.wgsl:20-65), stride-generalised
 // ---------------------------------------------------------------------------------------
 struct ReduceArgs {
     const float *partials;
     void *out;
-    float *lse;
     const float *gate;
-    const uint2 *seq_info;   // batched decode: per-sequence {ns, first split}; else NULL
     uint32_t ns, nh, hd;
-    unsigned long long split_stride, head_stride, seq_stride;  // floats
+    unsigned long long split_stride, head_stride;  // floats
     uint32_t out_dtype;
-    uint32_t skip_single;    // batched decode: ns == 1 rows were written by the decode kernel itself
 };
 
 __global__ void __launch_bounds__(128) reduce_kernel(const ReduceArgs a) {
-    const uint32_t head = blockIdx.x, seq = blockIdx.y;
-    uint32_t ns = a.ns;
-    unsigned long long sstr = a.split_stride, hstr = a.head_stride;
-    const float *base = a.partials + (size_t)seq * a.seq_stride;
-    if (a.seq_info) {
-        const uint2 info = a.seq_info[seq];
-        ns = info.x;
-        if (ns == 1 && a.skip_single) return;
-        base = a.partials + (size_t)info.y * a.nh * (a.hd + 2);
-        sstr = a.hd + 2;
-        hstr = (unsigned long long)ns * (a.hd + 2);
-    }
-    const float *hb = base + (size_t)head * hstr;
+    const uint32_t head = blockIdx.x;
+    const float *hb = a.partials + (size_t)head * a.head_stride;
     // wgsl:33-43 (a thread-0 loop there; every thread repeats it here, it is ns loads)
     float gmax = -INFINITY;
-    for (uint32_t s = 0; s < ns; ++s) {
-        const float l = hb[(size_t)s * sstr + a.hd];
+    for (uint32_t s = 0; s < a.ns; ++s) {
+        const float l = hb[(size_t)s * a.split_stride + a.hd];
         if (l > -INFINITY) gmax = fmaxf(gmax, l);  // false for -inf and NaN: empty splits
     }
     for (uint32_t d = threadIdx.x; d < a.hd; d += blockDim.x) {
         float acc = 0.f, wsum = 0.f;
-        for (uint32_t s = 0; s < ns; ++s) {
-            const float *rec = hb + (size_t)s * sstr;
+        for (uint32_t s = 0; s < a.ns; ++s) {
+            const float *rec = hb + (size_t)s * a.split_stride;
             const float l = rec[a.hd];
             if (!(l > -INFINITY)) continue;
             const float w = expf(l - gmax);  // wgsl:56
@@ -565,10 +699,9 @@ __global__ void __launch_bounds__(128) reduce_kernel(const ReduceArgs a) {
             wsum += w;
         }
         float val = wsum > 0.f ? acc / wsum : 0.f;
-        const size_t oi = ((size_t)seq * a.nh + head) * a.hd + d;
+        const size_t oi = (size_t)head * a.hd + d;
         if (a.gate) val *= sigmoidf_ref(a.gate[oi]);
         store_from_f32(a.out, oi, a.out_dtype, val);
-        if (d == 0 && a.lse) a.lse[(size_t)seq * a.nh + head] = wsum > 0.f ? gmax + logf(wsum) : -INFINITY;
     }
 }
 
@@ -580,69 +713,98 @@ __global__ void sigmoid_mul_kernel(float *x, const float *gate, uint32_t n) {
 // ---------------------------------------------------------------------------------------
 // Host launchers
 // ---------------------------------------------------------------------------------------
-template <typename T, int HD, int NW, int STAGES>
-static int launch16(shady_ctx *ctx, const DecodeArgs &a, dim3 grid) {
-    using S = Decode16Smem<HD, NW, STAGES>;
-    auto kern = decode16_kernel<T, HD, NW, STAGES>;
+template <typename T, int HD, int NW, int STAGES, int KPC>
+static int launch16(shady_ctx *ctx, const DecodeArgs &a, uint32_t blocks) {
+    using S = Decode16Smem<HD, NW, STAGES, KPC>;
+    static_assert(S::kTotal <= 232448, "shared memory of this configuration exceeds 227 KB");
+    auto kern = decode16_kernel<T, HD, NW, STAGES, KPC>;
     static thread_local int configured_dev = -1;
     if (configured_dev != ctx->device) {
         SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
         configured_dev = ctx->device;
     }
-    kern<<<grid, NW * 32, S::kTotal, ctx->stream>>>(a);
+    kern<<<blocks, NW * 32, S::kTotal, ctx->stream>>>(a);
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
+}
+
+// Dispatch on dtype and on the kv heads per CTA (a power of two that divides nkv, at most NW).
+template <int HD, int NW, int STAGES>
+static int launch16_kpc(shady_ctx *ctx, const DecodeArgs &a, uint32_t kpc, bool half, uint32_t blocks) {
+#define SHADY_L16(K_) \
+    (half ? launch16<__half, HD, NW, STAGES, K_>(ctx, a, blocks) : launch16<__nv_bfloat16, HD, NW, STAGES, K_>(ctx, a, blocks))
+    if constexpr (NW >= 8) {
+        if (kpc == 8) return SHADY_L16(8);
+    }
+    if (kpc == 4) return SHADY_L16(4);
+    if (kpc == 2) return SHADY_L16(2);
+    return SHADY_L16(1);
+#undef SHADY_L16
+}
+
+struct Variant16 {
+    uint32_t nw, stages, ctas_per_sm;
+};
+// head_dim 128: {4 warps, 3 stages} at two CTAs per SM measured best on the ragged fp16 batch
+// (8 warps per SM, 128 KB of K/V in flight per SM, every SM slot filled when nkv divides 2*SMs).
+static Variant16 variant16(uint32_t hd, uint32_t v) {
+    if (hd > 128) return v == 1 ? Variant16{4, 2, 1} : Variant16{4, 3, 1};
+    switch (v) {
+        case 1: return Variant16{8, 2, 1};
+        case 2: return Variant16{8, 3, 1};
+        default: return Variant16{4, 3, 2};
+    }
+}
+static uint32_t kv_heads_per_cta(uint32_t nkv, uint32_t nw) {
+    uint32_t k = 1;
+    while (k * 2 <= nw && k * 2 <= nkv && nkv % (k * 2) == 0) k *= 2;
+    return k;
 }
 
 template <int HD, int NW>
-static int launch32(shady_ctx *ctx, const DecodeArgs &a, uint32_t items) {
-    const uint32_t G = a.G;
-    const uint32_t GT = G >= 8 ? 8 : (G >= 4 ? 4 : (G >= 2 ? 2 : 1));
-    dim3 grid(items, a.nkv, (G + GT - 1) / GT);
+static int launch32(shady_ctx *ctx, const DecodeArgs &a, uint32_t blocks, uint32_t GT) {
     switch (GT) {
-        case 8: decode32_kernel<HD, 8, NW><<<grid, NW * 32, 0, ctx->stream>>>(a); break;
-        case 4: decode32_kernel<HD, 4, NW><<<grid, NW * 32, 0, ctx->stream>>>(a); break;
-        case 2: decode32_kernel<HD, 2, NW><<<grid, NW * 32, 0, ctx->stream>>>(a); break;
-        default: decode32_kernel<HD, 1, NW><<<grid, NW * 32, 0, ctx->stream>>>(a); break;
+        case 8: decode32_kernel<HD, 8, NW><<<blocks, NW * 32, 0, ctx->stream>>>(a); break;
+        case 4: decode32_kernel<HD, 4, NW><<<blocks, NW * 32, 0, ctx->stream>>>(a); break;
+        case 2: decode32_kernel<HD, 2, NW><<<blocks, NW * 32, 0, ctx->stream>>>(a); break;
+        default: decode32_kernel<HD, 1, NW><<<blocks, NW * 32, 0, ctx->stream>>>(a); break;
     }
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
 }
 
-// Work-size policy for the chunked mode: aim at `waves` full waves of resident CTAs.
-struct DecodePolicy {
-    uint32_t min_chunk, ctas_per_sm, waves;
-};
-static DecodePolicy policy_for(uint32_t kv_dtype, uint32_t hd) {
-    if (kv_dtype == SHADY_F32) return {32u, 4u, 2u};
-    return hd > 128 ? DecodePolicy{128u, 1u, 4u} : DecodePolicy{128u, 2u, 4u};
-}
-static uint32_t target_items(const shady_ctx *ctx, const DecodePolicy &pol) {
-    return (uint32_t)ctx->num_sms * pol.ctas_per_sm * pol.waves;
+static uint32_t group_rows_f32(uint32_t G) { return G >= 8 ? 8u : (G >= 4 ? 4u : (G >= 2 ? 2u : 1u)); }
+static uint32_t head_groups(uint32_t kv_dtype, uint32_t G) {
+    if (kv_dtype == SHADY_F32) {
+        const uint32_t gt = group_rows_f32(G);
+        return (G + gt - 1) / gt;
+    }
+    return (G + 15) / 16;
 }
 
-size_t decode_workspace_bytes(const shady_ctx *ctx, const shady_decode_params *p, uint32_t kv_dtype) {
+// Tuning overrides for experiments: SHADY_DECODE_VARIANT picks the {warps, stages} configuration,
+// SHADY_DECODE_CTAS_PER_SM the number of spans per SM, SHADY_DECODE_MIN_SPAN the smallest span (row-blocks).
+static uint32_t env_u32(const char *name, uint32_t dflt) {
+    const char *v = getenv(name);
+    return v && *v ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
+}
+constexpr uint32_t kMaxSlots = 148u * 8u;  // bound on resident CTAs used by the workspace size
+
+// Workspace layout: [arrival counters: num_seqs*nkv*gz u32, padded to 256 B][partial records].
+static size_t counters_bytes(const shady_decode_params *p) {
+    const size_t n = (size_t)p->num_seqs * p->num_kv_heads * ((p->heads_per_kv + 15) / 16 + p->heads_per_kv);
+    return (n * sizeof(uint32_t) + 255) / 256 * 256;
+}
+size_t decode_workspace_bytes(const shady_decode_params *p) {
+    if (p->num_splits == 1) return 0;
     const size_t rec = (size_t)p->num_q_heads * (p->head_dim + 2) * sizeof(float);
-    const size_t info = (size_t)p->num_seqs * sizeof(uint2);
-    size_t splits;
-    if (p->num_splits >= 1) {
-        if (p->num_splits == 1) return 0;
-        splits = (size_t)p->num_seqs * p->num_splits;
-    } else {
-        // sum_i ceil(L_i/chunk) <= sum(L)/chunk + S and chunk >= sum(L)*nkv*gz/target
-        const int sms = ctx ? ctx->num_sms : 148;
-        uint32_t worst = 0;
-        for (uint32_t dt = 0; dt < 3; ++dt)
-            for (uint32_t hd : {128u, 256u}) {
-                const DecodePolicy pol = policy_for(dt, hd);
-                worst = worst > (uint32_t)sms * pol.ctas_per_sm * pol.waves ? worst : (uint32_t)sms * pol.ctas_per_sm * pol.waves;
-            }
-        (void)kv_dtype;
-        splits = (size_t)worst / (p->num_kv_heads ? p->num_kv_heads : 1) + p->num_seqs + 1;
-    }
-    return ((info + 255) / 256) * 256 + splits * rec;
+    size_t recs;
+    if (p->num_splits > 1) recs = (size_t)p->num_seqs * p->num_splits;
+    // balanced: two record slots per span; spans <= resident CTAs (one CTA may serve all kv heads)
+    else recs = 2 * ((size_t)kMaxSlots + 1);
+    return counters_bytes(p) + recs * rec;
 }
 
 int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
@@ -677,68 +839,82 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
     a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;
     a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e;
     a.num_splits = p->num_splits;
+    a.gz = head_groups(cache->dtype, p->heads_per_kv);
+    const Variant16 var = variant16(hd, env_u32("SHADY_DECODE_VARIANT", 0));
+    // One kv head per CTA measured fastest (sibling CTAs of the other kv heads run next to each other in
+    // the grid and fetch the rest of each cache row); SHADY_DECODE_KPC packs more kv heads into a CTA.
+    uint32_t kpc = 1u;
+    {
+        const uint32_t want = env_u32("SHADY_DECODE_KPC", 0);
+        if (!f32 && want && want <= kv_heads_per_cta(p->num_kv_heads, var.nw) && (want & (want - 1)) == 0) kpc = want;
+    }
+    const uint32_t kv_groups = p->num_kv_heads / kpc;
+    uint32_t ctas_per_sm = env_u32("SHADY_DECODE_CTAS_PER_SM", f32 ? 4u : var.ctas_per_sm);
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    if (ctas_per_sm > 8) ctas_per_sm = 8;
+    uint32_t min_span = env_u32("SHADY_DECODE_MIN_SPAN", f32 ? 2u : 4u * (var.nw / kpc));
+    if (min_span < 1) min_span = 1;
 
-    uint32_t items;
-    bool need_reduce;
+    unsigned long long items;
+    bool need_ws;
     if (d_force_partials) {
         SHADY_REQUIRE(ctx, p->num_seqs == 1 && p->num_splits >= 2, SHADY_ERR_BAD_ARG,
                       "decode_partials: needs num_seqs == 1 and num_splits >= 2");
-        a.force_partials = 1; a.partials = d_force_partials; a.seq_info = nullptr;
-        items = p->num_splits; need_reduce = false;
+        a.force_partials = 1; a.partials = d_force_partials;
+        items = p->num_splits; need_ws = false;
     } else if (p->num_splits >= 1) {
-        items = p->num_seqs * p->num_splits;
-        need_reduce = p->num_splits > 1;
+        items = (unsigned long long)p->num_seqs * p->num_splits;
+        need_ws = p->num_splits > 1;
     } else {
         SHADY_REQUIRE(ctx, seq_lens_host, SHADY_ERR_BAD_ARG, "decode: num_splits == 0 needs seq_lens_host");
-        const DecodePolicy pol = policy_for(cache->dtype, hd);
-        const uint32_t gz = f32 ? 1u : (p->heads_per_kv + 15u) / 16u;
-        unsigned long long total = 0;
-        for (uint32_t i = 0; i < p->num_seqs; ++i) total += seq_lens_host[i];
-        const unsigned long long tgt = target_items(ctx, pol);
-        unsigned long long chunk = (total * p->num_kv_heads * gz + tgt - 1) / tgt;
-        if (chunk < pol.min_chunk) chunk = pol.min_chunk;
-        chunk = (chunk + 15) / 16 * 16;
-        a.chunk = (uint32_t)chunk;
-        items = 0; need_reduce = false;
-        for (uint32_t i = 0; i < p->num_seqs; ++i) {
-            const uint32_t ns = seq_lens_host[i] == 0 ? 1u : (uint32_t)((seq_lens_host[i] + chunk - 1) / chunk);
-            items += ns;
-            need_reduce |= ns > 1;
-        }
+        unsigned long long line = 0;
+        for (uint32_t i = 0; i < p->num_seqs; ++i) line += seq_lens_host[i] == 0 ? 1 : (seq_lens_host[i] + kBlkPos - 1) / kBlkPos;
+        SHADY_REQUIRE(ctx, line <= 0xffffffffull, SHADY_ERR_UNSUPPORTED, "decode: batch too long for one launch");
+        unsigned long long slots = (unsigned long long)ctx->num_sms * ctas_per_sm;
+        if (slots > kMaxSlots) slots = kMaxSlots;
+        unsigned long long spans = slots / ((unsigned long long)kv_groups * a.gz);
+        const unsigned long long by_size = (line + min_span - 1) / min_span;
+        if (spans > by_size) spans = by_size;
+        if (spans < 1) spans = 1;
+        a.line_blocks = (uint32_t)line;
+        a.spans = (uint32_t)spans;
+        items = spans;
+        need_ws = spans > 1;  // a sequence may straddle spans whenever there is more than one
     }
-    if (!d_force_partials && (need_reduce || p->num_splits == 0)) {
-        const size_t need = decode_workspace_bytes(ctx, p, cache->dtype);
-        if (need_reduce) {
-            SHADY_REQUIRE(ctx, d_ws && ws_bytes >= need, SHADY_ERR_WORKSPACE, "decode: workspace missing or too small");
-        }
-        if (d_ws && ws_bytes >= need && need > 0) {
-            const size_t info = (((size_t)p->num_seqs * sizeof(uint2)) + 255) / 256 * 256;
-            a.seq_info = reinterpret_cast<uint2 *>(d_ws);
-            a.partials = reinterpret_cast<float *>(reinterpret_cast<char *>(d_ws) + info);
-        }
+    if (need_ws) {
+        const size_t need = decode_workspace_bytes(p);
+        SHADY_REQUIRE(ctx, d_ws && ws_bytes >= need, SHADY_ERR_WORKSPACE, "decode: workspace missing or too small");
+        a.counters = reinterpret_cast<uint32_t *>(d_ws);
+        a.partials = reinterpret_cast<float *>(reinterpret_cast<char *>(d_ws) + counters_bytes(p));
     }
+    const unsigned long long blocks64 = items * kv_groups * a.gz;
+    SHADY_REQUIRE(ctx, blocks64 <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "decode: too many work items for one launch");
+    const uint32_t blocks = (uint32_t)blocks64;
 
-    int rc;
     if (f32) {
-        if (hd == 64) rc = launch32<64, 8>(ctx, a, items);
-        else if (hd == 128) rc = launch32<128, 8>(ctx, a, items);
-        else rc = launch32<256, 4>(ctx, a, items);
-    } else {
-        dim3 grid(items, p->num_kv_heads, (p->heads_per_kv + 15) / 16);
-        const bool h = cache->dtype == SHADY_F16;
-        if (hd == 128) rc = h ? launch16<__half, 128, 4, 3>(ctx, a, grid) : launch16<__nv_bfloat16, 128, 4, 3>(ctx, a, grid);
-        else rc = h ? launch16<__half, 256, 4, 3>(ctx, a, grid) : launch16<__nv_bfloat16, 256, 4, 3>(ctx, a, grid);
+        const uint32_t gt = group_rows_f32(p->heads_per_kv);
+        if (hd == 64) return launch32<64, 8>(ctx, a, blocks, gt);
+        if (hd == 128) return launch32<128, 8>(ctx, a, blocks, gt);
+        return launch32<256, 4>(ctx, a, blocks, gt);
     }
-    if (rc != SHADY_OK) return rc;
-    if (need_reduce) {
-        ReduceArgs r{};
-        r.partials = a.partials; r.out = d_out; r.lse = d_lse; r.gate = d_gate;
-        r.seq_info = a.seq_info; r.ns = p->num_splits; r.nh = p->num_q_heads; r.hd = hd;
-        r.out_dtype = p->out_dtype; r.skip_single = 1;
-        reduce_kernel<<<dim3(p->num_q_heads, p->num_seqs), 128, 0, ctx->stream>>>(r);
-        ctx->launches++;
-        SHADY_CUDA_OK(ctx, cudaGetLastError());
+    const bool h = cache->dtype == SHADY_F16;
+    if (hd == 128) {
+        if (var.nw == 8 && var.stages == 3) return launch16_kpc<128, 8, 3>(ctx, a, kpc, h, blocks);
+        if (var.nw == 8) return launch16_kpc<128, 8, 2>(ctx, a, kpc, h, blocks);
+        return launch16_kpc<128, 4, 3>(ctx, a, kpc, h, blocks);
     }
+    if (var.stages == 3) return launch16_kpc<256, 4, 3>(ctx, a, kpc, h, blocks);
+    return launch16_kpc<256, 4, 2>(ctx, a, kpc, h, blocks);
+}
+
+// The workspace must hold zeros in its counter area before the first call; the kernels
+// leave it zeroed again.
+int init_decode_workspace(shady_ctx *ctx, const shady_decode_params *p, void *d_ws, size_t ws_bytes) {
+    SHADY_REQUIRE(ctx, p, SHADY_ERR_BAD_ARG, "decode_workspace_init: null params");
+    const size_t need = decode_workspace_bytes(p);
+    if (need == 0) return SHADY_OK;
+    SHADY_REQUIRE(ctx, d_ws && ws_bytes >= need, SHADY_ERR_WORKSPACE, "decode_workspace_init: workspace missing or too small");
+    SHADY_CUDA_OK(ctx, cudaMemsetAsync(d_ws, 0, counters_bytes(p), ctx->stream));
     return SHADY_OK;
 }
 
@@ -748,8 +924,8 @@ int launch_reduce(shady_ctx *ctx, uint32_t hd, uint32_t ns, uint32_t nh, uint64_
     SHADY_REQUIRE(ctx, out_dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "reduce: bad out dtype");
     ReduceArgs r{};
     r.partials = d_partials; r.out = d_out; r.gate = d_gate; r.ns = ns; r.nh = nh; r.hd = hd;
-    r.split_stride = split_stride; r.head_stride = head_stride; r.seq_stride = 0; r.out_dtype = out_dtype;
-    reduce_kernel<<<dim3(nh, 1), 128, 0, ctx->stream>>>(r);
+    r.split_stride = split_stride; r.head_stride = head_stride; r.out_dtype = out_dtype;
+    reduce_kernel<<<nh, 128, 0, ctx->stream>>>(r);
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;

@@ -94,6 +94,8 @@ class Model:
             k_cache=[mk(f"k_cache_{i}", max_seq_len * nkv * hd * esz) for i in range(nl)],
             v_cache=[mk(f"v_cache_{i}", max_seq_len * nkv * hd * esz) for i in range(nl)],
             qknorm_params=[None] * nl, position=mk("position", 4), seq_len_dev=mk("seq_len", 4), partials_bytes=ws)
+        ops.decode_workspace_init(gpu, self.state.attn_partials, ws, head_dim=hd, num_kv_heads=nkv, num_q_heads=nh,
+                                  num_splits=num_attn_splits, num_seqs=1)
 
     # model.rs:337-346 — the reference packs a 5,152-byte uniform; only the bf16 weights
     # (q then k) are data, the header fields travel by value here.

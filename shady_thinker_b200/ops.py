@@ -70,6 +70,13 @@ def decode_workspace_size(*, head_dim: int, num_kv_heads: int, num_q_heads: int,
     return n.value
 
 
+def decode_workspace_init(gpu: GpuContext, workspace, workspace_bytes: int, *, head_dim: int, num_kv_heads: int,
+                          num_q_heads: int, num_splits: int, num_seqs: int) -> None:
+    """Zero the arrival counters at the head of a freshly allocated decode workspace (once)."""
+    p = DecodeParams(head_dim, num_kv_heads, num_q_heads, num_q_heads // num_kv_heads, num_splits, num_seqs, F32, F32)
+    gpu._check(gpu._L.shady_decode_workspace_init(gpu.handle, C.byref(p), _addr(workspace) or None, workspace_bytes))
+
+
 def _host_lens(seq_lens_host):
     if seq_lens_host is None:
         return None, None

@@ -48,7 +48,9 @@ def run_decode(gpu, q, cache_view, lens, *, nh, nkv, hd, num_splits, q_dt=F32, o
     d_out = torch.full((S, nh, hd), float("nan"), dtype=TORCH_DT[out_dt], device="cuda")
     d_lse = torch.full((S, nh), float("nan"), dtype=torch.float32, device="cuda") if want_lse else None
     ws_bytes = ops.decode_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_splits=num_splits, num_seqs=S)
-    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device="cuda")
+    ws = torch.full((max(ws_bytes, 4),), 0xAB, dtype=torch.uint8, device="cuda")   # garbage until initialised
+    ops.decode_workspace_init(gpu, ws, ws_bytes, head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_splits=num_splits,
+                              num_seqs=S)
     torch.cuda.synchronize()
     ops.attn_decode(gpu, q=d_q, cache=cache_view, seq_lens=d_lens, out=d_out, head_dim=hd, num_kv_heads=nkv,
                     num_q_heads=nh, num_seqs=S, num_splits=num_splits, seq_lens_host=lens, q_dtype=q_dt,
