@@ -32,8 +32,8 @@ SEQS_PER_GPU = 32
 LMIN, LMAX = 1024, 8192
 N_SETS = 3            # rotating cache sets so no step finds its KV rows in L2
 # DRAM bytes per algorithmic byte of the decode kernel, from the ncu capture summarised in
-# profiles/ (None until a capture exists).
-TRAFFIC_PER_ALGO_BYTE = None
+# profiles/decode16_f16_hd128_cfg2.md (read + write bytes of one launch over its algorithmic bytes).
+TRAFFIC_PER_ALGO_BYTE = 1.010
 
 
 def draw_lengths(rank: int) -> np.ndarray:
