@@ -181,6 +181,21 @@ int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *
                       const uint32_t *seq_lens_host, void *d_out, float *d_lse, const float *d_gate,
                       void *d_workspace, size_t workspace_bytes);
 
+/* No counterpart in the reference.  The same decode as shady_attn_decode for callers that cannot
+ * hand over a workspace: a server that gave all device memory to its KV-cache arena at start-up, or
+ * a decode loop that cannot take the device-wide stall of an allocation.  The arrival counters and
+ * split records live in a 4 MiB array built into the library (every GPU that loads the library
+ * holds it until the process exits); nothing is allocated or freed, by this call or below it.
+ *  - A launch that needs more scratch than 4 MiB returns SHADY_ERR_WORKSPACE and runs nothing; the
+ *    message names both sizes.  (cfg-2-sized batches need about 1.2 MiB.)
+ *  - The first call on a device looks up the array's device address; make that call before any
+ *    stream capture begins on that device.
+ *  - Every call on a device shares the one array and clears its counters on the stream first, so two
+ *    calls that overlap on the GPU (different streams or contexts) race; keep them stream-ordered. */
+int shady_attn_decode_static(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
+                             const shady_kv_cache *cache, const uint32_t *d_seq_lens,
+                             const uint32_t *seq_lens_host, void *d_out, float *d_lse, const float *d_gate);
+
 /* Split-level output of the decode kernel without the merge: d_partials receives the
  * reference layout [nh][num_splits][hd+2] ([hd] = lse, [hd+1] = running max) for ONE
  * sequence (gqa_attention_head.wgsl:112-123).  Requires num_seqs == 1, num_splits >= 2. */

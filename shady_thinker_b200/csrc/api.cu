@@ -19,6 +19,8 @@ size_t decode_workspace_bytes(const shady_decode_params *p);
 int init_decode_workspace(shady_ctx *, const shady_decode_params *, void *, size_t);
 int launch_decode(shady_ctx *, const shady_decode_params *, const void *, const shady_kv_cache *, const uint32_t *,
                   const uint32_t *, void *, float *, const float *, void *, size_t, float *);
+int launch_decode_static(shady_ctx *, const shady_decode_params *, const void *, const shady_kv_cache *, const uint32_t *,
+                         const uint32_t *, void *, float *, const float *);
 int launch_reduce(shady_ctx *, uint32_t, uint32_t, uint32_t, uint64_t, uint64_t, const float *, void *, uint32_t,
                   const float *);
 int launch_sigmoid_mul(shady_ctx *, float *, const float *, uint32_t);
@@ -172,6 +174,13 @@ int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *
     CTX_ENTER(ctx);
     return launch_decode(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, d_out, d_lse, d_gate, d_workspace,
                          workspace_bytes, nullptr);
+}
+
+int shady_attn_decode_static(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
+                             const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, void *d_out, float *d_lse,
+                             const float *d_gate) {
+    CTX_ENTER(ctx);
+    return launch_decode_static(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, d_out, d_lse, d_gate);
 }
 
 int shady_attn_decode_partials(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,

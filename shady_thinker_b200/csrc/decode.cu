@@ -918,6 +918,116 @@ int init_decode_workspace(shady_ctx *ctx, const shady_decode_params *p, void *d_
     return SHADY_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// Decode with built-in scratch (no counterpart in the reference)
+// ---------------------------------------------------------------------------------------
+// Some hosts cannot give this library a workspace allocated at call time: an inference server that
+// hands all device memory to its KV-cache arena at start-up has nothing left for cudaMalloc, and a
+// decode loop that must not stall cannot afford cudaMalloc's implicit device synchronisation.  For them
+// the arrival counters and split records live in this fixed array, which every GPU that loads the
+// library holds until the process exits.  Launches that need more than kStaticScratchBytes are refused.
+constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+static unsigned char *g_static_scratch_addr[kMaxDevices] = {};  // device address of the array, per device
+
+// `g_static_scratch` in host code is only a handle; the device address comes from the runtime, once per
+// device, with that device current.
+static int static_scratch_ptr(shady_ctx *ctx, unsigned char **out) {
+    SHADY_REQUIRE(ctx, ctx->device >= 0 && ctx->device < kMaxDevices, SHADY_ERR_UNSUPPORTED,
+                  "decode_static: device ordinal out of range");
+    if (!g_static_scratch_addr[ctx->device]) {
+        unsigned char *ptr = nullptr;
+        SHADY_CUDA_OK(ctx, cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_scratch));
+        SHADY_REQUIRE(ctx, ptr != nullptr, SHADY_ERR_CUDA, "decode_static: cudaGetSymbolAddress returned a null address");
+        g_static_scratch_addr[ctx->device] = ptr;
+    }
+    *out = g_static_scratch_addr[ctx->device];
+    return SHADY_OK;
+}
+
+int launch_decode_static(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
+                         const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, void *d_out, float *d_lse,
+                         const float *d_gate) {
+    SHADY_REQUIRE(ctx, p && d_q && cache && d_seq_lens && d_out, SHADY_ERR_BAD_ARG, "decode_static: null argument");
+    SHADY_REQUIRE(ctx, p->num_seqs > 0 && p->num_kv_heads > 0 && p->heads_per_kv > 0, SHADY_ERR_BAD_ARG,
+                  "decode_static: zero-sized problem");
+    SHADY_REQUIRE(ctx, p->num_q_heads == p->num_kv_heads * p->heads_per_kv, SHADY_ERR_BAD_ARG,
+                  "decode_static: num_q_heads != num_kv_heads * heads_per_kv");
+    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "decode_static: bad cache dtype");
+    SHADY_REQUIRE(ctx, (cache->d_k_ptrs && cache->d_v_ptrs) || (cache->d_k_base && cache->d_v_base),
+                  SHADY_ERR_BAD_ARG, "decode_static: cache has neither base pointers nor pointer arrays");
+    SHADY_REQUIRE(ctx, p->q_dtype == SHADY_F32 || p->q_dtype == cache->dtype, SHADY_ERR_UNSUPPORTED,
+                  "decode_static: q_dtype must be f32 or the cache dtype");
+    SHADY_REQUIRE(ctx, p->out_dtype == SHADY_F32 || p->out_dtype == cache->dtype, SHADY_ERR_UNSUPPORTED,
+                  "decode_static: out_dtype must be f32 or the cache dtype");
+    const uint32_t hd = p->head_dim;
+    const bool f32 = cache->dtype == SHADY_F32;
+    if (f32) SHADY_REQUIRE(ctx, hd == 64 || hd == 128 || hd == 256, SHADY_ERR_UNSUPPORTED, "decode_static: f32 cache needs head_dim 64/128/256");
+    else SHADY_REQUIRE(ctx, hd == 128 || hd == 256, SHADY_ERR_UNSUPPORTED, "decode_static: 16-bit cache needs head_dim 128/256");
+
+    DecodeArgs a{};
+    a.q = d_q; a.out = d_out; a.lse = d_lse; a.gate = d_gate;
+    a.kv.k_base = (const char *)cache->d_k_base; a.kv.v_base = (const char *)cache->d_v_base;
+    a.kv.seq_stride_bytes = cache->seq_stride * dtype_size(cache->dtype);
+    a.kv.k_ptrs = cache->d_k_ptrs; a.kv.v_ptrs = cache->d_v_ptrs;
+    a.seq_lens = d_seq_lens;
+    a.num_seqs = p->num_seqs; a.nkv = p->num_kv_heads; a.nh = p->num_q_heads; a.G = p->heads_per_kv; a.hd = hd;
+    a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;
+    a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e;
+    a.num_splits = p->num_splits;
+    a.gz = head_groups(cache->dtype, p->heads_per_kv);
+    const Variant16 var = variant16(hd, 0);
+    const uint32_t kv_groups = p->num_kv_heads;           // one kv head per CTA
+    unsigned long long items, recs;
+    if (p->num_splits >= 1) {
+        items = (unsigned long long)p->num_seqs * p->num_splits;
+        recs = p->num_splits > 1 ? items : 0;
+    } else {
+        SHADY_REQUIRE(ctx, seq_lens_host, SHADY_ERR_BAD_ARG, "decode_static: num_splits == 0 needs seq_lens_host");
+        unsigned long long line = 0;
+        for (uint32_t i = 0; i < p->num_seqs; ++i) line += seq_lens_host[i] == 0 ? 1 : (seq_lens_host[i] + kBlkPos - 1) / kBlkPos;
+        SHADY_REQUIRE(ctx, line <= 0xffffffffull, SHADY_ERR_UNSUPPORTED, "decode_static: batch too long for one launch");
+        const unsigned long long slots = (unsigned long long)ctx->num_sms * (f32 ? 4u : var.ctas_per_sm);
+        unsigned long long spans = slots / ((unsigned long long)kv_groups * a.gz);
+        const unsigned long long min_span = f32 ? 2u : 4u * var.nw;
+        const unsigned long long by_size = (line + min_span - 1) / min_span;
+        if (spans > by_size) spans = by_size;
+        if (spans < 1) spans = 1;
+        a.line_blocks = (uint32_t)line;
+        a.spans = (uint32_t)spans;
+        items = spans;
+        recs = spans > 1 ? 2 * spans : 0;
+    }
+    if (recs) {
+        const size_t counters = ((size_t)p->num_seqs * kv_groups * a.gz * sizeof(uint32_t) + 255) / 256 * 256;
+        const size_t need = counters + (size_t)recs * p->num_q_heads * (hd + 2) * sizeof(float);
+        if (need > kStaticScratchBytes)
+            return fail(ctx, SHADY_ERR_WORKSPACE,
+                        "decode_static: this launch needs " + std::to_string(need) + " bytes of scratch but the built-in array holds " +
+                            std::to_string(kStaticScratchBytes) + "; use shady_attn_decode with a caller-provided workspace");
+        unsigned char *scratch = nullptr;
+        const int rc = static_scratch_ptr(ctx, &scratch);
+        if (rc != SHADY_OK) return rc;
+        // the array keeps whatever the previous call left: the arrival counters must start at zero
+        SHADY_CUDA_OK(ctx, cudaMemsetAsync(scratch, 0, counters, ctx->stream));
+        a.counters = reinterpret_cast<uint32_t *>(scratch);
+        a.partials = reinterpret_cast<float *>(scratch + counters);
+    }
+    const unsigned long long blocks64 = items * kv_groups * a.gz;
+    SHADY_REQUIRE(ctx, blocks64 <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "decode_static: too many work items for one launch");
+    const uint32_t blocks = (uint32_t)blocks64;
+    if (f32) {
+        const uint32_t gt = group_rows_f32(p->heads_per_kv);
+        if (hd == 64) return launch32<64, 8>(ctx, a, blocks, gt);
+        if (hd == 128) return launch32<128, 8>(ctx, a, blocks, gt);
+        return launch32<256, 4>(ctx, a, blocks, gt);
+    }
+    const bool h = cache->dtype == SHADY_F16;
+    if (hd == 128) return launch16_kpc<128, 4, 3>(ctx, a, 1u, h, blocks);
+    return launch16_kpc<256, 4, 3>(ctx, a, 1u, h, blocks);
+}
+
 int launch_reduce(shady_ctx *ctx, uint32_t hd, uint32_t ns, uint32_t nh, uint64_t split_stride, uint64_t head_stride,
                   const float *d_partials, void *d_out, uint32_t out_dtype, const float *d_gate) {
     SHADY_REQUIRE(ctx, d_partials && d_out && hd && ns && nh, SHADY_ERR_BAD_ARG, "reduce: null or zero argument");

@@ -97,6 +97,21 @@ def attn_decode(gpu: GpuContext, *, q, cache: KvCacheView, seq_lens, out, head_d
     del keep
 
 
+def attn_decode_static(gpu: GpuContext, *, q, cache: KvCacheView, seq_lens, out, head_dim: int, num_kv_heads: int,
+                       num_q_heads: int, num_seqs: int = 1, num_splits: int = 0, seq_lens_host=None,
+                       q_dtype: int = F32, out_dtype: int = F32, lse=None, gate=None) -> None:
+    """``attn_decode`` for callers that cannot supply a workspace: the scratch is a 4 MiB array inside the
+    library.  Raises ``ShadyError`` (status 4) when the launch would need more.  Calls must not overlap on
+    the GPU, and the first call on a device should come before any stream capture."""
+    p = DecodeParams(head_dim, num_kv_heads, num_q_heads, num_q_heads // num_kv_heads, num_splits, num_seqs, q_dtype,
+                     out_dtype)
+    c = cache.c_struct()
+    keep, hl = _host_lens(seq_lens_host)
+    gpu._check(gpu._L.shady_attn_decode_static(gpu.handle, C.byref(p), _addr(q), C.byref(c), _addr(seq_lens), hl,
+                                               _addr(out), _addr(lse) or None, _addr(gate) or None))
+    del keep
+
+
 def attn_decode_partials(gpu: GpuContext, *, q, cache: KvCacheView, seq_lens, partials, head_dim: int,
                          num_kv_heads: int, num_q_heads: int, num_splits: int, q_dtype: int = F32) -> None:
     p = DecodeParams(head_dim, num_kv_heads, num_q_heads, num_q_heads // num_kv_heads, num_splits, 1, q_dtype, F32)
