@@ -27,6 +27,7 @@ int launch_sigmoid_mul(shady_ctx *, float *, const float *, uint32_t);
 int launch_append(shady_ctx *, const shady_append_params *, const void *, void *, const void *, void *, float *,
                   const shady_kv_cache *, const uint16_t *, const uint32_t *, const uint32_t *, const uint32_t *);
 int launch_prefill(shady_ctx *, const shady_prefill_params *, const void *, const shady_kv_cache *, void *);
+int prefill_status(shady_ctx *, int *);
 
 // ---- counter-based N(0,1): the device twin of oracle_randn_at ---------------------------
 __host__ __device__ inline unsigned long long mix64(unsigned long long z) {
@@ -145,7 +146,8 @@ int shady_flush(shady_ctx *ctx) {
 int shady_synchronize(shady_ctx *ctx) {
     CTX_ENTER(ctx);
     SHADY_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
-    return SHADY_OK;
+    int code = 0;
+    return prefill_status(ctx, &code);  // SHADY_ERR_TIMEOUT if a bounded device-side wait gave up
 }
 
 int shady_kv_append_rope(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,
