@@ -155,6 +155,11 @@ __device__ __forceinline__ uint32_t make_idesc(uint32_t fmt, bool b_mn_major) {
     return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 template <typename T> __device__ __forceinline__ uint32_t pack16(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack16<__half>(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
@@ -308,21 +313,31 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (!ok) break;
             tc_fence_after();
             const bool diag = (j == nq - 1);
-            const uint32_t col0 = j * kPN;
-            // ---- pass 1: row maximum ----
-            float mx = -INFINITY;
+            // columns of this tile a row may see: all 128, or 0..lim on the diagonal tile
+            const int lim = diag ? (int)(row - j * kPN) : 127;
+            // ---- pass 1: row maximum (two batches of 64 columns, four independent chains) ----
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(t_s + c * 32, v);
+            for (int hb = 0; hb < 2; ++hb) {
+                uint32_t va[32], vb[32];
+                tmem_ld32(t_s + hb * 64, va);
+                tmem_ld32(t_s + hb * 64 + 32, vb);
                 tmem_wait_ld();
+                if (!diag) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float sv = __uint_as_float(v[i]);
-                    if (!diag || col0 + c * 32 + i <= row) mx = fmaxf(mx, sv);
+                    for (int i = 0; i < 32; ++i) {
+                        mx4[i & 1] = fmaxf(mx4[i & 1], __uint_as_float(va[i]));
+                        mx4[2 + (i & 1)] = fmaxf(mx4[2 + (i & 1)], __uint_as_float(vb[i]));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (hb * 64 + i <= lim) mx4[i & 1] = fmaxf(mx4[i & 1], __uint_as_float(va[i]));
+                        if (hb * 64 + 32 + i <= lim) mx4[2 + (i & 1)] = fmaxf(mx4[2 + (i & 1)], __uint_as_float(vb[i]));
+                    }
                 }
             }
-            mx *= a.scale_log2;   // scale > 0: max commutes with it
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // scale > 0
             // ---- lazy rescale of O and l ----
             float corr = 1.f;
             if (j == 0) {
@@ -343,27 +358,31 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     tmem_st32(t_o + c * 32, v);
                 }
             }
-            // ---- pass 2: P = exp2(s*scale - m_ref), row sum, pack, store over S ----
+            // ---- pass 2: P = exp2(s*scale - m_ref), row sum, pack, store over S; next chunk's load in flight ----
             const float neg_m = -m_ref;
+            float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t vbuf[2][32];
+            tmem_ld32(t_s, vbuf[0]);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(t_s + c * 32, v);
                 tmem_wait_ld();
+                if (c < 3) tmem_ld32(t_s + (c + 1) * 32, vbuf[(c + 1) & 1]);
+                const uint32_t(&v)[32] = vbuf[c & 1];
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = exp2f(fmaf(__uint_as_float(v[i]), a.scale_log2, neg_m));
-                    float p1 = exp2f(fmaf(__uint_as_float(v[i + 1]), a.scale_log2, neg_m));
+                    float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), a.scale_log2, neg_m));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), a.scale_log2, neg_m));
                     if (diag) {
-                        if (col0 + c * 32 + i > row) p0 = 0.f;
-                        if (col0 + c * 32 + i + 1 > row) p1 = 0.f;
+                        if (c * 32 + i > lim) p0 = 0.f;
+                        if (c * 32 + i + 1 > lim) p1 = 0.f;
                     }
-                    l_sum += p0 + p1;
+                    ls4[(i >> 1) & 3] += p0 + p1;
                     pk[i >> 1] = pack16<T>(p0, p1);
                 }
                 tmem_st16(t_s + c * 16, pk);
             }
+            l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(BAR_PFULL + q));
