@@ -51,6 +51,16 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def measured_tensor_peaks():
+    """(burst, sustained) dense bf16 TFLOP/s and where they come from."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops"]), float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
 class ClockSampler(threading.Thread):
     """Polls NVML (read-only) for SM clock and throttle reasons while the timed region runs."""
 
@@ -333,6 +343,205 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     gpu.close()
 
 
+# ------------------------------------------------------------------------------------------------
+# cfg3: causal prefill attention (BASELINE config 3): batch 4, T 4096, 32 query heads, 8 KV heads,
+# head_dim 128, bf16 Q/K/V, RoPE theta 1e6, fp32 softmax statistics; the step also writes K/V into
+# the cache (append kernel) and then runs the tcgen05 attention kernel over the cache.
+# ------------------------------------------------------------------------------------------------
+P_B, P_T, P_NH, P_NKV, P_HD = 4, 4096, 32, 8, 128
+
+
+def prefill_flops(B=P_B, T=P_T, nh=P_NH, hd=P_HD) -> float:
+    return 4.0 * B * nh * hd * T * (T + 1) / 2
+
+
+def prefill_config(n_gpus: int) -> dict:
+    return {"workload": "cfg3: causal prefill attention, one layer, RoPE+cache write then attention per step",
+            "batch_per_gpu": P_B, "seq_len": P_T, "num_q_heads": P_NH, "num_kv_heads": P_NKV, "head_dim": P_HD,
+            "dtype": "bf16", "softmax": "fp32", "rope_theta": 1e6,
+            "sharding": f"batch items over {n_gpus} GPU(s), no collective",
+            "l2": "Q+K+V+out per step (403 MB) exceed L2"}
+
+
+def prefill_cpu_sample(O, threads: int, T: int, nh: int, nkv: int):
+    q = O.round_bf16(O.randn((T, nh, P_HD), SEED, 31))
+    k = O.round_bf16(O.randn((T, nkv, P_HD), SEED, 32))
+    v = O.round_bf16(O.randn((T, nkv, P_HD), SEED, 33))
+    t0 = time.perf_counter()
+    O.causal_prefill(q, k, v, threads=threads)
+    dt = time.perf_counter() - t0
+    return prefill_flops(1, T, nh) / dt / 1e12, dt
+
+
+def run_reference_prefill(args, rank: int) -> None:
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build()
+    threads = O.num_threads()
+    # bounded sample: one batch item, one KV group (4 query heads), T sized to the step count
+    T = 1024
+    val, dt = prefill_cpu_sample(O, threads, T, 4, 1)
+    budget = 100.0 / max(args.steps + args.warmup, 1)
+    while dt * 4 < budget and T < P_T:
+        T *= 2
+        val, dt = prefill_cpu_sample(O, threads, T, 4, 1)
+    for _ in range(args.warmup):
+        prefill_cpu_sample(O, threads, T, 4, 1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        prefill_cpu_sample(O, threads, T, 4, 1)
+    wall = time.perf_counter() - t0
+    val = prefill_flops(1, T, 4) * args.steps / wall / 1e12
+    sample = f"1 batch item x 4 query heads (1 KV group) x T={T} of cfg3, token loop of gqa_attention_head.wgsl in f32"
+    print(json.dumps({
+        "impl": "reference", "metric": "prefill_attn_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": prefill_config(args.gpus),
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of the reference's per-token prefill loop (oracle port); the WGSL through wgpu is unavailable on this box",
+    }))
+
+
+def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
+    import torch
+
+    from shady_thinker_b200 import ops
+    from shady_thinker_b200._lib import BF16
+    from shady_thinker_b200.gpu import GpuContext
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    B, T, nh, nkv, hd = P_B, P_T, P_NH, P_NKV, P_HD
+    stream = torch.cuda.Stream()
+    gpu = GpuContext(local_rank, stream=stream.cuda_stream)
+    nq, nk = B * T * nh * hd, B * T * nkv * hd
+    mk = gpu.create_storage_buffer
+    q_in, k_in, v_in = mk("q_in", nq * 2), mk("k_in", nk * 2), mk("v_in", nk * 2)
+    q_rot, out = mk("q_rot", nq * 2), mk("out", nq * 2)
+    k_cache, v_cache = mk("k_cache", nk * 2), mk("v_cache", nk * 2)
+    pos = gpu.upload_buffer("pos", np.zeros(B, np.uint32).tobytes())
+    base = 5000 + 10 * rank
+    ops.fill_randn(gpu, q_in, nq, BF16, SEED, base + 1)
+    ops.fill_randn(gpu, k_in, nk, BF16, SEED, base + 2)
+    ops.fill_randn(gpu, v_in, nk, BF16, SEED, base + 3)
+    view = ops.KvCacheView(BF16, k_cache, v_cache, T * nkv * hd)
+
+    def append():
+        ops.kv_append_rope(gpu, q_proj_full=q_in, k_proj=k_in, v_proj=v_in, q_out=q_rot, q_gate=None, cache=view,
+                           pos_start=pos, num_heads=nh, num_kv_heads=nkv, head_dim=hd, rope_theta=1e6, rotary_dim=hd,
+                           num_seqs=B, tokens_per_seq=T, in_dtype=BF16, q_dtype=BF16, has_gate=False,
+                           write_k_back=False)
+
+    def attend():
+        ops.attn_prefill(gpu, q=q_rot, cache=view, out=out, head_dim=hd, num_kv_heads=nkv, num_q_heads=nh,
+                         num_seqs=B, seq_len=T, dtype=BF16)
+
+    gpu.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            append(); attend()
+        ev_a = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        launches0 = gpu.launch_count
+        t_wall0 = time.perf_counter()
+        e0.record(stream)
+        for i in range(args.steps):
+            append()
+            ev_a[i].record(stream)
+            attend()
+            ev_b[i].record(stream)
+        e1.record(stream)
+        barrier()
+        t_wall1 = time.perf_counter()
+        gpu.synchronize()   # also surfaces a bounded-wait expiry of the prefill kernel
+        launches = gpu.launch_count - launches0
+        total_ms = e0.elapsed_time(e1)
+        attend_ms = sum(x.elapsed_time(y) for x, y in zip(ev_a, ev_b)) / args.steps
+        # ---- end to end: host activations in, output back ----
+        hq = torch.empty(nq, dtype=torch.bfloat16).pin_memory().normal_()
+        hk = torch.empty(nk, dtype=torch.bfloat16).pin_memory().normal_()
+        hv = torch.empty(nk, dtype=torch.bfloat16).pin_memory().normal_()
+        ho = torch.empty(nq, dtype=torch.bfloat16).pin_memory()
+        import ctypes as C
+        L = gpu._L
+
+        def e2e_step():
+            gpu._check(L.shady_buffer_write(gpu.handle, C.c_void_p(q_in.ptr), 0, C.c_void_p(hq.data_ptr()), nq * 2))
+            gpu._check(L.shady_buffer_write(gpu.handle, C.c_void_p(k_in.ptr), 0, C.c_void_p(hk.data_ptr()), nk * 2))
+            gpu._check(L.shady_buffer_write(gpu.handle, C.c_void_p(v_in.ptr), 0, C.c_void_p(hv.data_ptr()), nk * 2))
+            append(); attend()
+            gpu._check(L.shady_buffer_read(gpu.handle, C.c_void_p(out.ptr), 0, C.c_void_p(ho.data_ptr()), nq * 2))
+
+        e2e_steps = max(3, min(args.steps, 20))
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        f1.record(stream)
+        barrier()
+        e2e_ms = f0.elapsed_time(f1)
+        assert torch.isfinite(ho.float()).all(), "e2e output is not finite"
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+
+    t = torch.tensor([total_ms, e2e_ms, attend_ms], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, _ = [float(x) for x in t.tolist()]
+    flops = prefill_flops()
+    if rank == 0:
+        burst, sustained, src = measured_tensor_peaks()
+        long_loop = total_ms > 1000.0
+        peak = sustained if long_loop else burst
+        achieved = flops / (attend_ms * 1e-3) / 1e12
+        line = {
+            "metric": "prefill_attn_tflops", "value": flops * world * args.steps / (total_ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": prefill_config(world),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": None,
+                         "peak_source": f"{src} cuBLAS bf16, {'sustained' if long_loop else 'burst'} figure "
+                                        f"(burst {burst}, sustained {sustained})",
+                         "kernel": "prefill_kernel<bf16> per attend call", "algorithmic_flops_per_launch": flops,
+                         "avg_launch_ms": attend_ms},
+            "e2e": {"value": flops * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": (nq + 2 * nk) * 2, "d2h_bytes_per_step": nq * 2, "steps": e2e_steps,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": sampler.summary(t_wall0, t_wall1),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import oracle as O
+            O.build()
+            val, dt = prefill_cpu_sample(O, O.num_threads(), 2048, 8, 2)
+            line["cpu_baseline"] = {"value": val, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
+                                    "sample": f"1 batch item x 8 query heads (2 KV groups) x T=2048 of cfg3, {dt:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    gpu.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -340,17 +549,21 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3"],
+                    help="cfg2 = batched ragged decode (default, the headline); cfg3 = causal prefill")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload == "cfg3" and args.steps == 2000:
+        args.steps = 200   # a prefill step is ~0.7 ms of attention plus the append
     if args.impl == "reference":
-        run_reference(args, rank)
+        (run_reference_prefill if args.workload == "cfg3" else run_reference)(args, rank)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         sys.exit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
-    run_ours(args, rank, world, local_rank)
+    (run_prefill if args.workload == "cfg3" else run_ours)(args, rank, world, local_rank)
 
 
 if __name__ == "__main__":

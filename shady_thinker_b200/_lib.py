@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libshady_attn.so")
+# SHADY_ATTN_LIB points at another build of the same library (kernel tuning experiments)
+LIB_PATH = os.environ.get("SHADY_ATTN_LIB") or os.path.join(_PKG, "libshady_attn.so")
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT = range(6)
 F32, F16, BF16 = 0, 1, 2
