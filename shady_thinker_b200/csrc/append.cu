@@ -31,6 +31,7 @@ struct AppendArgs {
     uint32_t rd, s1, s2, interleaved;
     uint32_t num_seqs, T;
     uint32_t in_dtype, q_dtype, kv_dtype, has_gate, write_k_back;
+    uint32_t head_slices;     // vectorised path: warps that share one token's heads (small batches need the parallelism)
     float inv_freq[128];      // [rd/2]
 };
 
@@ -120,6 +121,164 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(const AppendA
     }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Vectorised path (interleaved RoPE pairs, head_dim 128 or 256): one warp per token.
+// cos/sin depend only on (position, pair index), so a lane evaluates its four pairs once and
+// reuses them for every Q and K head of the token; each lane moves 8 contiguous elements per
+// head with 16/32-byte accesses, and a warp covers 32*8/HD heads per iteration.
+// ---------------------------------------------------------------------------------------
+template <typename T> struct Vec8 {
+    static __device__ __forceinline__ void load(const T *p, float (&v)[8]) {
+        const uint4 u = *reinterpret_cast<const uint4 *>(p);
+        const T *e = reinterpret_cast<const T *>(&u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = to_f32<T>(e[i]);
+    }
+    static __device__ __forceinline__ void store(T *p, const float (&v)[8]) {
+        uint4 u;
+        T *e = reinterpret_cast<T *>(&u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(v[i]);
+        *reinterpret_cast<uint4 *>(p) = u;
+    }
+};
+template <> struct Vec8<float> {
+    static __device__ __forceinline__ void load(const float *p, float (&v)[8]) {
+        const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float *p, const float (&v)[8]) {
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+
+template <typename TIn, typename TQ, typename TKV, int HD>
+__global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const AppendArgs a) {
+    constexpr int LPH = HD / 8;       // lanes per head
+    constexpr int HPI = 32 / LPH;     // heads per warp iteration
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const unsigned long long wid = (unsigned long long)blockIdx.x * kAppendWarps + warp;
+    const unsigned long long tok = wid / a.head_slices;
+    const uint32_t slice = (uint32_t)(wid % a.head_slices);
+    if (tok >= (unsigned long long)a.num_seqs * a.T) return;
+    const uint32_t s = (uint32_t)(tok / a.T), j = (uint32_t)(tok % a.T);
+    const uint32_t sub = lane / LPH, dl = lane % LPH, d0 = dl * 8;
+    // ---- cos/sin of this lane's four pairs (wgsl:56-68) ----
+    const uint32_t p_t = a.pos_start[s] + j;
+    const uint32_t p_h = a.pos_h ? a.pos_h[s] + j : p_t;
+    const uint32_t p_w = a.pos_w ? a.pos_w[s] + j : p_t;
+    float cs[4], sn[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t i = dl * 4 + k;
+        cs[k] = 1.f; sn[k] = 0.f;
+        if (i < a.rd / 2) {
+            uint32_t pos = p_t;
+            if ((i % 3u) == 1u && i < a.s1) pos = p_h;
+            else if ((i % 3u) == 2u && i < a.s2) pos = p_w;
+            sincosf((float)pos * a.inv_freq[i], &sn[k], &cs[k]);
+        }
+    }
+    float wq[8], wk[8];
+    if (a.norm_w) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            wq[e] = 1.0f + __uint_as_float(((uint32_t)a.norm_w[d0 + e]) << 16);
+            wk[e] = 1.0f + __uint_as_float(((uint32_t)a.norm_w[HD + d0 + e]) << 16);
+        }
+    }
+    auto norm_rope = [&](float (&v)[8], const float (&w)[8]) {
+        if (a.norm_w) {
+            float ssq = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ssq += v[e] * v[e];
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+            const float rms = 1.0f / sqrtf(ssq / (float)HD + a.eps);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = v[e] * rms * w[e];
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float x = v[2 * k], y = v[2 * k + 1];
+            v[2 * k] = x * cs[k] - y * sn[k];
+            v[2 * k + 1] = y * cs[k] + x * sn[k];
+        }
+    };
+    // ---- Q heads ----
+    const uint32_t qrow = a.has_gate ? 2 * HD : HD;
+    const TIn *q_in = reinterpret_cast<const TIn *>(a.q_in) + tok * a.nh * (size_t)qrow;
+    TQ *q_out = reinterpret_cast<TQ *>(a.q_out) + tok * a.nh * (size_t)HD;
+    for (uint32_t h0 = slice * HPI; h0 < a.nh; h0 += HPI * a.head_slices) {   // every lane takes every trip: the norm shuffles are warp-wide
+        const uint32_t h = h0 + sub;
+        const bool valid = h < a.nh;
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (valid) Vec8<TIn>::load(q_in + (size_t)h * qrow + d0, v);
+        if (valid && a.has_gate && a.q_gate) {
+            float gt[8];
+            Vec8<TIn>::load(q_in + (size_t)h * qrow + HD + d0, gt);
+            Vec8<float>::store(a.q_gate + (tok * a.nh + h) * (size_t)HD + d0, gt);
+        }
+        norm_rope(v, wq);
+        if (valid) Vec8<TQ>::store(q_out + (size_t)h * HD + d0, v);
+    }
+    // ---- K heads (+ V copy) ----
+    TIn *k_io = reinterpret_cast<TIn *>(a.k_io) + tok * a.nkv * (size_t)HD;
+    const TIn *v_in = reinterpret_cast<const TIn *>(a.v_in) + tok * a.nkv * (size_t)HD;
+    char *kc = a.k_ptrs ? reinterpret_cast<char *>(a.k_ptrs[s]) : a.k_base + a.seq_stride_bytes * s;
+    char *vc = a.v_ptrs ? reinterpret_cast<char *>(a.v_ptrs[s]) : a.v_base + a.seq_stride_bytes * s;
+    TKV *k_row = reinterpret_cast<TKV *>(kc) + (size_t)p_t * a.nkv * HD;   // cache_position == position (model.rs:493-496)
+    TKV *v_row = reinterpret_cast<TKV *>(vc) + (size_t)p_t * a.nkv * HD;
+    for (uint32_t kh0 = slice * HPI; kh0 < a.nkv; kh0 += HPI * a.head_slices) {
+        const uint32_t kh = kh0 + sub;
+        const bool valid = kh < a.nkv;
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, vv[8];
+        if (valid) {
+            Vec8<TIn>::load(k_io + (size_t)kh * HD + d0, v);
+            Vec8<TIn>::load(v_in + (size_t)kh * HD + d0, vv);
+        }
+        norm_rope(v, wk);
+        if (valid) {
+            if (a.write_k_back) Vec8<TIn>::store(k_io + (size_t)kh * HD + d0, v);
+            Vec8<TKV>::store(k_row + (size_t)kh * HD + d0, v);
+            Vec8<TKV>::store(v_row + (size_t)kh * HD + d0, vv);
+        }
+    }
+}
+
+template <typename TIn, typename TQ, typename TKV>
+static void launch_append_fast(shady_ctx *ctx, AppendArgs &a) {
+    const unsigned long long toks = (unsigned long long)a.num_seqs * a.T;
+    // enough warps to fill the GPU: split a token's heads over several warps when there are few tokens
+    const uint32_t hpi = 32 / (a.hd / 8);
+    const uint32_t max_slices = (a.nh + hpi - 1) / hpi;
+    unsigned long long want = ((unsigned long long)ctx->num_sms * 8 + toks - 1) / toks;
+    a.head_slices = (uint32_t)(want < 1 ? 1 : (want > max_slices ? max_slices : want));
+    const unsigned blocks = (unsigned)((toks * a.head_slices + kAppendWarps - 1) / kAppendWarps);
+    if (a.hd == 128) append_fast_kernel<TIn, TQ, TKV, 128><<<blocks, kAppendWarps * 32, 0, ctx->stream>>>(a);
+    else append_fast_kernel<TIn, TQ, TKV, 256><<<blocks, kAppendWarps * 32, 0, ctx->stream>>>(a);
+}
+
+// true if a vectorised instantiation covers this call (and launches it)
+static bool try_append_fast(shady_ctx *ctx, AppendArgs &a, const void *q_in, const void *k_io, const void *v_in,
+                            const void *q_out) {
+    if (!(a.hd == 128 || a.hd == 256) || !a.interleaved || (a.rd % 2)) return false;
+    if ((unsigned long long)a.num_seqs * a.T > 0x3fffffffull) return false;
+    if ((((uintptr_t)q_in | (uintptr_t)k_io | (uintptr_t)v_in | (uintptr_t)q_out | (uintptr_t)a.q_gate | (uintptr_t)a.k_base |
+          (uintptr_t)a.v_base) & 15) || (a.seq_stride_bytes & 15))
+        return false;   // 16-byte vector accesses (per-sequence pointers are required to be 16-byte aligned too)
+    const uint32_t i = a.in_dtype, q = a.q_dtype, k = a.kv_dtype;
+    if (i == SHADY_F32 && q == SHADY_F32 && k == SHADY_F32) launch_append_fast<float, float, float>(ctx, a);
+    else if (i == SHADY_F32 && q == SHADY_F32 && k == SHADY_F16) launch_append_fast<float, float, __half>(ctx, a);
+    else if (i == SHADY_F32 && q == SHADY_F32 && k == SHADY_BF16) launch_append_fast<float, float, __nv_bfloat16>(ctx, a);
+    else if (i == SHADY_F16 && q == SHADY_F16 && k == SHADY_F16) launch_append_fast<__half, __half, __half>(ctx, a);
+    else if (i == SHADY_BF16 && q == SHADY_BF16 && k == SHADY_BF16) launch_append_fast<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(ctx, a);
+    else return false;
+    return true;
+}
+
 int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,
                   const void *d_v_proj, void *d_q_out, float *d_q_gate, const shady_kv_cache *cache,
                   const uint16_t *d_qk_norm_bf16, const uint32_t *d_pos_start, const uint32_t *d_pos_h,
@@ -154,7 +313,8 @@ int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_
     const unsigned long long warps = (unsigned long long)p->num_seqs * p->tokens_per_seq * (p->num_heads + p->num_kv_heads);
     const unsigned long long blocks = (warps + kAppendWarps - 1) / kAppendWarps;
     SHADY_REQUIRE(ctx, blocks <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "kv_append_rope: too many tokens for one launch");
-    append_kernel<<<(unsigned)blocks, kAppendWarps * 32, 0, ctx->stream>>>(a);
+    if (!try_append_fast(ctx, a, d_q_proj_full, d_k_proj, d_v_proj, d_q_out))
+        append_kernel<<<(unsigned)blocks, kAppendWarps * 32, 0, ctx->stream>>>(a);
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
