@@ -61,6 +61,15 @@ def measured_tensor_peaks():
     return 1590.0, 1400.0, "fallback"
 
 
+def host_threads(O) -> int:
+    """Threads for the CPU legs: all host cores, even when the launcher (torchrun) pinned OMP_NUM_THREADS to 1."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(n, O.num_threads())
+
+
 class ClockSampler(threading.Thread):
     """Polls NVML (read-only) for SM clock and throttle reasons while the timed region runs."""
 
@@ -136,7 +145,7 @@ def run_reference(args, rank: int) -> None:
         return
     from oracle import oracle as O
     O.build()
-    threads = O.num_threads()
+    threads = host_threads(O)
     lens = draw_lengths(0)
     row_off = np.concatenate([[0], np.cumsum((lens.astype(np.int64) + 15) // 16 * 16)])
     # calibrate on one mid-sized sequence, then size the sample so the whole run stays within ~2 minutes
@@ -200,7 +209,7 @@ def cpu_baseline(rank: int, dec, lens: np.ndarray) -> dict:
     """Oracle (f32-faithful port) on a bounded sample of the same batch, all host threads."""
     from oracle import oracle as O
     O.build()
-    threads = O.num_threads()
+    threads = host_threads(O)
     order = np.argsort(lens)[::-1]
     seqs = [int(s) for s in order[:8]]
     ks, vs = host_set(O, lens, dec.row_off, 0, rank, seqs)
@@ -378,7 +387,7 @@ def run_reference_prefill(args, rank: int) -> None:
         return
     from oracle import oracle as O
     O.build()
-    threads = O.num_threads()
+    threads = host_threads(O)
     # bounded sample: one batch item, one KV group (4 query heads), T sized to the step count
     T = 1024
     val, dt = prefill_cpu_sample(O, threads, T, 4, 1)
@@ -532,8 +541,8 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle as O
             O.build()
-            val, dt = prefill_cpu_sample(O, O.num_threads(), 2048, 8, 2)
-            line["cpu_baseline"] = {"value": val, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
+            val, dt = prefill_cpu_sample(O, host_threads(O), 2048, 8, 2)
+            line["cpu_baseline"] = {"value": val, "unit": "TFLOP/s", "cores": host_threads(O), "kind": "port",
                                     "sample": f"1 batch item x 8 query heads (2 KV groups) x T=2048 of cfg3, {dt:.1f} s"}
         print(json.dumps(line), flush=True)
     if dist is not None:
