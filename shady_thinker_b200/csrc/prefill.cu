@@ -239,7 +239,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t nkv = n_tiles[1] ? n_tiles[1] : n_tiles[0];
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
-    if (tid == 0) {
+    if (warp == 8 && lane == 0) {   // the producer sets the barriers up and starts the first loads before anyone else is ready
         mbar_init(bar(BAR_QFULL + 0), 1); mbar_init(bar(BAR_QFULL + 1), 1);
         for (int s = 0; s < kKvStages; ++s) {
             mbar_init(bar(BAR_KFULL + s), 1); mbar_init(bar(BAR_KEMPTY + s), 1);
@@ -250,6 +250,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int q = 0; q < 2; ++q) {
+            if (!n_tiles[q]) continue;
+            mbar_expect_tx(bar(BAR_QFULL + q), kTileBytes);
+            const uint32_t dst = smem_base + kSmemQ + q * kTileBytes;
+            tma_load_4d(dst, &map_q, bar(BAR_QFULL + q), 0, (int)h, (int)(q0 + q * kPM), (int)b);
+            tma_load_4d(dst + kSlabBytes, &map_q, bar(BAR_QFULL + q), 64, (int)h, (int)(q0 + q * kPM), (int)b);
+        }
+        for (uint32_t j = 0; j < nkv && j < (uint32_t)kKvStages; ++j) {
+            mbar_expect_tx(bar(BAR_KFULL + j), kTileBytes);
+            const uint32_t kd = smem_base + kSmemK + j * kTileBytes;
+            tma_load_4d(kd, &map_k, bar(BAR_KFULL + j), 0, (int)kvh, (int)(j * kPN), (int)b);
+            tma_load_4d(kd + kSlabBytes, &map_k, bar(BAR_KFULL + j), 64, (int)kvh, (int)(j * kPN), (int)b);
+            mbar_expect_tx(bar(BAR_VFULL + j), kTileBytes);
+            const uint32_t vd = smem_base + kSmemV + j * kTileBytes;
+            tma_load_4d(vd, &map_v, bar(BAR_VFULL + j), 0, (int)kvh, (int)(j * kPN), (int)b);
+            tma_load_4d(vd + kSlabBytes, &map_v, bar(BAR_VFULL + j), 64, (int)kvh, (int)(j * kPN), (int)b);
+        }
     }
     if (warp == 9) {  // TMEM owner
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"(kTmemCols) : "memory");
@@ -264,15 +281,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (warp == 8) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
-            bool ok = true;
-            for (int q = 0; q < 2 && ok; ++q) {
-                if (!n_tiles[q]) continue;
-                mbar_expect_tx(bar(BAR_QFULL + q), kTileBytes);
-                const uint32_t dst = smem_base + kSmemQ + q * kTileBytes;
-                tma_load_4d(dst, &map_q, bar(BAR_QFULL + q), 0, (int)h, (int)(q0 + q * kPM), (int)b);
-                tma_load_4d(dst + kSlabBytes, &map_q, bar(BAR_QFULL + q), 64, (int)h, (int)(q0 + q * kPM), (int)b);
-            }
-            for (uint32_t j = 0; j < nkv && ok; ++j) {
+            bool ok = true;   // Q and the first kKvStages K/V tiles were requested before the CTA-wide sync
+            for (uint32_t j = kKvStages; j < nkv && ok; ++j) {
                 const uint32_t s = j % kKvStages, ph = (j / kKvStages) & 1;
                 if (j >= kKvStages) ok = mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_word, a.error, 1);
                 if (!ok) break;
@@ -357,112 +367,117 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (j > 0 && ok) ok = mbar_wait(bar(BAR_OFULL + q), (j - 1) & 1, abort_word, a.error, 10);
             if (!ok) break;
             tc_fence_after();
-            const bool diag = (j == nq - 1);
-            // columns of this tile a row may see: all 128, or 0..lim on the diagonal tile
-            const int lim = diag ? (int)(row - j * kPN) : 127;
-            // ---- pass 1: row maximum (two batches of 64 columns, four independent chains) ----
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int hb = 0; hb < 2; ++hb) {
-                uint32_t va[32], vb[32];
-                tmem_ld32(t_s + hb * 64, va);
-                tmem_ld32(t_s + hb * 64 + 32, vb);
-                tmem_wait_ld();
-                if (!diag) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        mx4[0] = max3(mx4[0], __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
-                        mx4[1] = max3(mx4[1], __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
-                        mx4[2] = max3(mx4[2], __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
-                        mx4[3] = max3(mx4[3], __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (hb * 64 + i <= lim) mx4[i & 1] = fmaxf(mx4[i & 1], __uint_as_float(va[i]));
-                        if (hb * 64 + 32 + i <= lim) mx4[2 + (i & 1)] = fmaxf(mx4[2 + (i & 1)], __uint_as_float(vb[i]));
-                    }
-                }
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // scale > 0
-            // ---- lazy rescale of O and l ----
-            float corr = 1.f;
-            if (j == 0) {
-                m_ref = mx;
-            } else if (mx > m_ref + kRescaleThreshold) {
-                corr = exp2f(m_ref - mx);
-                m_ref = mx;
-            }
-            if (__any_sync(0xffffffffu, corr != 1.f)) {
-                l_sum *= corr;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(t_o + c * 32, v);
+            // one tile of the online softmax; the diagonal tile (the last one) is a second instantiation
+            auto tile_body = [&](auto diag_c) {
+                constexpr bool diag = decltype(diag_c)::value;   // compile-time: the common path carries no mask code
+                // columns of this tile a row may see: all 128, or 0..lim on the diagonal tile
+                const int lim = diag ? (int)(row - j * kPN) : 127;
+                // ---- pass 1: row maximum (two batches of 64 columns, four independent chains) ----
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    #pragma unroll
+                for (int hb = 0; hb < 2; ++hb) {
+                    uint32_t va[32], vb[32];
+                    tmem_ld32(t_s + hb * 64, va);
+                    tmem_ld32(t_s + hb * 64 + 32, vb);
                     tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                    tmem_st32(t_o + c * 32, v);
-                }
-            }
-            // ---- pass 2: P = exp2(s*scale - m_ref), row sum, pack, store over S; next chunk's load in flight ----
-            const float neg_m = -m_ref;
-            float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-#if SHADY_PF_FMA2
-            const unsigned long long scale2 = pack_f32x2(a.scale_log2, a.scale_log2), negm2 = pack_f32x2(neg_m, neg_m);
-            unsigned long long ls2[2] = {0ull, 0ull};
-#endif
-            uint32_t vbuf[2][32];
-            tmem_ld32(t_s, vbuf[0]);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                tmem_wait_ld();
-                if (c < 3) tmem_ld32(t_s + (c + 1) * 32, vbuf[(c + 1) & 1]);
-                const uint32_t(&v)[32] = vbuf[c & 1];
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float x0, x1;
-#if SHADY_PF_FMA2
-                    fma_f32x2(x0, x1, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), scale2, negm2);
-#else
-                    x0 = fmaf(__uint_as_float(v[i]), a.scale_log2, neg_m);
-                    x1 = fmaf(__uint_as_float(v[i + 1]), a.scale_log2, neg_m);
-#endif
-                    float p0, p1;
-                    if (SHADY_PF_POLY > 0 && ((i >> 1) % (SHADY_PF_POLY > 0 ? SHADY_PF_POLY : 1)) == 0) {
-                        p0 = poly_exp2(x0);
-                        p1 = poly_exp2(x1);
+                    if (!diag) {
+    #pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            mx4[0] = max3(mx4[0], __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
+                            mx4[1] = max3(mx4[1], __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
+                            mx4[2] = max3(mx4[2], __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
+                            mx4[3] = max3(mx4[3], __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
+                        }
                     } else {
-                        p0 = fast_exp2(x0);
-                        p1 = fast_exp2(x1);
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (hb * 64 + i <= lim) mx4[i & 1] = fmaxf(mx4[i & 1], __uint_as_float(va[i]));
+                            if (hb * 64 + 32 + i <= lim) mx4[2 + (i & 1)] = fmaxf(mx4[2 + (i & 1)], __uint_as_float(vb[i]));
+                        }
                     }
-                    if (diag) {
-                        if (c * 32 + i > lim) p0 = 0.f;
-                        if (c * 32 + i + 1 > lim) p1 = 0.f;
-                    }
-#if SHADY_PF_FMA2
-                    ls2[(i >> 1) & 1] = add_f32x2(ls2[(i >> 1) & 1], pack_f32x2(p0, p1));
-#else
-                    ls4[(i >> 1) & 3] += p0 + p1;
-#endif
-                    pk[i >> 1] = pack16<T>(p0, p1);
                 }
-                tmem_st16(t_s + c * 16, pk);
-            }
-#if SHADY_PF_FMA2
-            {
-                float s0, s1, s2, s3;
-                asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(ls2[0]));
-                asm("mov.b64 {%0, %1}, %2;" : "=f"(s2), "=f"(s3) : "l"(ls2[1]));
-                ls4[0] = s0 + s1;
-                ls4[1] = s2 + s3;
-            }
-#endif
-            l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(BAR_PFULL + q));
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // scale > 0
+                // ---- lazy rescale of O and l ----
+                float corr = 1.f;
+                if (j == 0) {
+                    m_ref = mx;
+                } else if (mx > m_ref + kRescaleThreshold) {
+                    corr = exp2f(m_ref - mx);
+                    m_ref = mx;
+                }
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+                    l_sum *= corr;
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(t_o + c * 32, v);
+                        tmem_wait_ld();
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                        tmem_st32(t_o + c * 32, v);
+                    }
+                }
+                // ---- pass 2: P = exp2(s*scale - m_ref), row sum, pack, store over S; next chunk's load in flight ----
+                const float neg_m = -m_ref;
+                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+    #if SHADY_PF_FMA2
+                const unsigned long long scale2 = pack_f32x2(a.scale_log2, a.scale_log2), negm2 = pack_f32x2(neg_m, neg_m);
+                unsigned long long ls2[2] = {0ull, 0ull};
+    #endif
+                uint32_t vbuf[2][32];
+                tmem_ld32(t_s, vbuf[0]);
+    #pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    tmem_wait_ld();
+                    if (c < 3) tmem_ld32(t_s + (c + 1) * 32, vbuf[(c + 1) & 1]);
+                    const uint32_t(&v)[32] = vbuf[c & 1];
+                    uint32_t pk[16];
+    #pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float x0, x1;
+    #if SHADY_PF_FMA2
+                        fma_f32x2(x0, x1, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), scale2, negm2);
+    #else
+                        x0 = fmaf(__uint_as_float(v[i]), a.scale_log2, neg_m);
+                        x1 = fmaf(__uint_as_float(v[i + 1]), a.scale_log2, neg_m);
+    #endif
+                        float p0, p1;
+                        if (SHADY_PF_POLY > 0 && ((i >> 1) % (SHADY_PF_POLY > 0 ? SHADY_PF_POLY : 1)) == 0) {
+                            p0 = poly_exp2(x0);
+                            p1 = poly_exp2(x1);
+                        } else {
+                            p0 = fast_exp2(x0);
+                            p1 = fast_exp2(x1);
+                        }
+                        if (diag) {
+                            if (c * 32 + i > lim) p0 = 0.f;
+                            if (c * 32 + i + 1 > lim) p1 = 0.f;
+                        }
+    #if SHADY_PF_FMA2
+                        ls2[(i >> 1) & 1] = add_f32x2(ls2[(i >> 1) & 1], pack_f32x2(p0, p1));
+    #else
+                        ls4[(i >> 1) & 3] += p0 + p1;
+    #endif
+                        pk[i >> 1] = pack16<T>(p0, p1);
+                    }
+                    tmem_st16(t_s + c * 16, pk);
+                }
+    #if SHADY_PF_FMA2
+                {
+                    float s0, s1, s2, s3;
+                    asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(ls2[0]));
+                    asm("mov.b64 {%0, %1}, %2;" : "=f"(s2), "=f"(s3) : "l"(ls2[1]));
+                    ls4[0] = s0 + s1;
+                    ls4[1] = s2 + s3;
+                }
+    #endif
+                l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar(BAR_PFULL + q));
+            };
+            if (j == nq - 1) tile_body(std::true_type{});
+            else tile_body(std::false_type{});
         }
         // ---- epilogue: O / l -> global ----
         if (nq && ok) ok = mbar_wait(bar(BAR_OFULL + q), (nq - 1) & 1, abort_word, a.error, 11);
