@@ -45,7 +45,7 @@ constexpr uint32_t kSpinLimit = 1u << 20;  // bounded waits: on the order of a s
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 enum { BAR_QFULL = 0, BAR_KFULL = 2, BAR_KEMPTY = 4, BAR_VFULL = 6, BAR_VEMPTY = 8, BAR_SFULL = 10, BAR_PFULL = 12,
-       BAR_OFULL = 14, BAR_COUNT = 16 };
+       BAR_OFULL = 14, BAR_QEMPTY = 16, BAR_COUNT = 18 };
 
 struct PrefillArgs {
     void *out;
@@ -230,10 +230,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (*reinterpret_cast<volatile int *>(a.error)) return;   // an earlier CTA's wait expired: do not start
     // heaviest (latest rows) first
-    const uint32_t bh_count = a.B * a.nh;
-    const uint32_t m = a.m_tiles - 1 - blockIdx.x / bh_count;
-    const uint32_t bh = blockIdx.x % bh_count;
-    const uint32_t b = bh / a.nh, h = bh % a.nh, kvh = h / a.G;
+    // One CTA serves the G query heads of a KV group one after the other ("items"): they read the same K/V
+    // tiles, and chaining them lets the producer and the MMA issuer run ahead into the next head while the
+    // softmax warps finish the current one, so the pipeline fill/drain is paid once per CTA, not per head.
+    const uint32_t bk_count = a.B * a.nkv;
+    const uint32_t m = a.m_tiles - 1 - blockIdx.x / bk_count;
+    const uint32_t bk = blockIdx.x % bk_count;
+    const uint32_t b = bk / a.nkv, kvh = bk % a.nkv;
+    const uint32_t items = a.G;
     const uint32_t q0 = m * 256;
     const uint32_t n_tiles[2] = {2 * m + 1, (q0 + kPM < a.T) ? 2 * m + 2 : 0u};   // kv tiles of the two query tiles
     const uint32_t nkv = n_tiles[1] ? n_tiles[1] : n_tiles[0];
@@ -247,6 +251,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         for (int q = 0; q < 2; ++q) {
             mbar_init(bar(BAR_SFULL + q), 1); mbar_init(bar(BAR_PFULL + q), 128); mbar_init(bar(BAR_OFULL + q), 1);
+            mbar_init(bar(BAR_QEMPTY + q), 1);
         }
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -254,8 +259,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (!n_tiles[q]) continue;
             mbar_expect_tx(bar(BAR_QFULL + q), kTileBytes);
             const uint32_t dst = smem_base + kSmemQ + q * kTileBytes;
-            tma_load_4d(dst, &map_q, bar(BAR_QFULL + q), 0, (int)h, (int)(q0 + q * kPM), (int)b);
-            tma_load_4d(dst + kSlabBytes, &map_q, bar(BAR_QFULL + q), 64, (int)h, (int)(q0 + q * kPM), (int)b);
+            tma_load_4d(dst, &map_q, bar(BAR_QFULL + q), 0, (int)(kvh * a.G), (int)(q0 + q * kPM), (int)b);
+            tma_load_4d(dst + kSlabBytes, &map_q, bar(BAR_QFULL + q), 64, (int)(kvh * a.G), (int)(q0 + q * kPM), (int)b);
         }
         for (uint32_t j = 0; j < nkv && j < (uint32_t)kKvStages; ++j) {
             mbar_expect_tx(bar(BAR_KFULL + j), kTileBytes);
@@ -281,21 +286,35 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (warp == 8) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
-            bool ok = true;   // Q and the first kKvStages K/V tiles were requested before the CTA-wide sync
-            for (uint32_t j = kKvStages; j < nkv && ok; ++j) {
-                const uint32_t s = j % kKvStages, ph = (j / kKvStages) & 1;
-                if (j >= kKvStages) ok = mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_word, a.error, 1);
-                if (!ok) break;
-                mbar_expect_tx(bar(BAR_KFULL + s), kTileBytes);
-                const uint32_t kd = smem_base + kSmemK + s * kTileBytes;
-                tma_load_4d(kd, &map_k, bar(BAR_KFULL + s), 0, (int)kvh, (int)(j * kPN), (int)b);
-                tma_load_4d(kd + kSlabBytes, &map_k, bar(BAR_KFULL + s), 64, (int)kvh, (int)(j * kPN), (int)b);
-                if (j >= kKvStages) ok = mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_word, a.error, 2);
-                if (!ok) break;
-                mbar_expect_tx(bar(BAR_VFULL + s), kTileBytes);
-                const uint32_t vd = smem_base + kSmemV + s * kTileBytes;
-                tma_load_4d(vd, &map_v, bar(BAR_VFULL + s), 0, (int)kvh, (int)(j * kPN), (int)b);
-                tma_load_4d(vd + kSlabBytes, &map_v, bar(BAR_VFULL + s), 64, (int)kvh, (int)(j * kPN), (int)b);
+            bool ok = true;   // item 0's Q and its first kKvStages K/V tiles were requested before the CTA-wide sync
+            for (uint32_t it = 0; it < items && ok; ++it) {
+                if (it > 0) {
+                    for (int q = 0; q < 2 && ok; ++q) {   // Q of the next head, once the last QK of the previous one is done
+                        if (!n_tiles[q]) continue;
+                        ok = mbar_wait(bar(BAR_QEMPTY + q), (it - 1) & 1, abort_word, a.error, 12);
+                        if (!ok) break;
+                        mbar_expect_tx(bar(BAR_QFULL + q), kTileBytes);
+                        const uint32_t dst = smem_base + kSmemQ + q * kTileBytes;
+                        tma_load_4d(dst, &map_q, bar(BAR_QFULL + q), 0, (int)(kvh * a.G + it), (int)(q0 + q * kPM), (int)b);
+                        tma_load_4d(dst + kSlabBytes, &map_q, bar(BAR_QFULL + q), 64, (int)(kvh * a.G + it), (int)(q0 + q * kPM), (int)b);
+                    }
+                }
+                for (uint32_t j = (it == 0 ? min(nkv, (uint32_t)kKvStages) : 0u); j < nkv && ok; ++j) {
+                    const uint32_t gi = it * nkv + j;          // running tile count: the K/V ring runs through the items
+                    const uint32_t s = gi % kKvStages, ph = (gi / kKvStages) & 1;
+                    if (gi >= kKvStages) ok = mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_word, a.error, 1);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(BAR_KFULL + s), kTileBytes);
+                    const uint32_t kd = smem_base + kSmemK + s * kTileBytes;
+                    tma_load_4d(kd, &map_k, bar(BAR_KFULL + s), 0, (int)kvh, (int)(j * kPN), (int)b);
+                    tma_load_4d(kd + kSlabBytes, &map_k, bar(BAR_KFULL + s), 64, (int)kvh, (int)(j * kPN), (int)b);
+                    if (gi >= kKvStages) ok = mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_word, a.error, 2);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(BAR_VFULL + s), kTileBytes);
+                    const uint32_t vd = smem_base + kSmemV + s * kTileBytes;
+                    tma_load_4d(vd, &map_v, bar(BAR_VFULL + s), 0, (int)kvh, (int)(j * kPN), (int)b);
+                    tma_load_4d(vd + kSlabBytes, &map_v, bar(BAR_VFULL + s), 64, (int)kvh, (int)(j * kPN), (int)b);
+                }
             }
         }
     } else if (warp == 9) {
@@ -303,8 +322,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (lane == 0) {
             const uint32_t idesc_qk = make_idesc(kFmt, false), idesc_pv = make_idesc(kFmt, true);
             bool ok = true;
-            auto issue_qk = [&](uint32_t q, uint32_t j) {
-                const uint32_t s = j % kKvStages;
+            auto issue_qk = [&](uint32_t q, uint32_t s) {          // S_q = Q_q * K(stage s)^T
                 const uint32_t qa = smem_base + kSmemQ + q * kTileBytes, kb = smem_base + kSmemK + s * kTileBytes;
 #pragma unroll
                 for (uint32_t ks = 0; ks < kPD / 16; ++ks) {
@@ -313,42 +331,52 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
                 tc_commit(bar(BAR_SFULL + q));
             };
-            auto issue_pv = [&](uint32_t q, uint32_t j) {
-                const uint32_t s = j % kKvStages;
+            auto issue_pv = [&](uint32_t q, uint32_t s, bool first) {   // O_q (+)= P_q * V(stage s)
                 const uint32_t vb = smem_base + kSmemV + s * kTileBytes;
 #pragma unroll
                 for (uint32_t ks = 0; ks < kPN / 16; ++ks)
-                    mma_ts(tmem + 256 + q * 128, tmem + q * 128 + ks * 8, desc_mnmajor(vb + ks * 2048), idesc_pv, (j > 0) || (ks > 0));
+                    mma_ts(tmem + 256 + q * 128, tmem + q * 128 + ks * 8, desc_mnmajor(vb + ks * 2048), idesc_pv, !first || (ks > 0));
                 tc_commit(bar(BAR_OFULL + q));
             };
-            for (int q = 0; q < 2 && ok; ++q)
-                if (n_tiles[q]) ok = mbar_wait(bar(BAR_QFULL + q), 0, abort_word, a.error, 3);
-            for (uint32_t j = 0; j <= nkv && ok; ++j) {
-                const uint32_t s = j % kKvStages, ph = (j / kKvStages) & 1;
-                if (j < nkv) {
-                    ok = mbar_wait(bar(BAR_KFULL + s), ph, abort_word, a.error, 4);
-                    if (!ok) break;
-                    tc_fence_after();
-                }
-                if (j < n_tiles[0]) issue_qk(0, j);
-                if (j >= 1 && j - 1 < n_tiles[1]) {
-                    const uint32_t jp = j - 1, sp = jp % kKvStages, pp = (jp / kKvStages) & 1;
-                    ok = mbar_wait(bar(BAR_VFULL + sp), pp, abort_word, a.error, 5) &&
-                         mbar_wait(bar(BAR_PFULL + 1), jp & 1, abort_word, a.error, 6);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_pv(1, jp);
-                    tc_commit(bar(BAR_VEMPTY + sp));   // PV1(jp) is the last reader of V(jp)
-                }
-                if (j < n_tiles[1]) issue_qk(1, j);
-                if (j < nkv) tc_commit(bar(BAR_KEMPTY + s));   // both tiles' QK(j) are issued
-                if (j < n_tiles[0]) {
-                    ok = mbar_wait(bar(BAR_VFULL + s), ph, abort_word, a.error, 7) &&
-                         mbar_wait(bar(BAR_PFULL + 0), j & 1, abort_word, a.error, 8);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_pv(0, j);
-                    if (j >= n_tiles[1]) tc_commit(bar(BAR_VEMPTY + s));   // no PV1(j) will follow
+            for (uint32_t it = 0; it < items && ok; ++it) {
+                for (int q = 0; q < 2 && ok; ++q)
+                    if (n_tiles[q]) ok = mbar_wait(bar(BAR_QFULL + q), it & 1, abort_word, a.error, 3);
+                for (uint32_t j = 0; j <= nkv && ok; ++j) {
+                    const uint32_t gi = it * nkv + j;
+                    const uint32_t s = gi % kKvStages, ph = (gi / kKvStages) & 1;
+                    if (j < nkv) {
+                        ok = mbar_wait(bar(BAR_KFULL + s), ph, abort_word, a.error, 4);
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
+                    if (j < n_tiles[0]) {
+                        issue_qk(0, s);
+                        if (j == n_tiles[0] - 1) tc_commit(bar(BAR_QEMPTY + 0));   // Q0 of this head is no longer needed
+                    }
+                    if (j >= 1 && j - 1 < n_tiles[1]) {
+                        const uint32_t gp = gi - 1, sp = gp % kKvStages, pp = (gp / kKvStages) & 1;
+                        ok = mbar_wait(bar(BAR_VFULL + sp), pp, abort_word, a.error, 5) &&
+                             mbar_wait(bar(BAR_PFULL + 1), (it * n_tiles[1] + j - 1) & 1, abort_word, a.error, 6);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_pv(1, sp, j - 1 == 0);
+                        tc_commit(bar(BAR_VEMPTY + sp));   // PV1 is the last reader of that V tile
+                    }
+                    if (j < n_tiles[1]) {
+                        issue_qk(1, s);
+                        if (j == n_tiles[1] - 1) tc_commit(bar(BAR_QEMPTY + 1));
+                    }
+                    if (j < nkv) tc_commit(bar(BAR_KEMPTY + s));   // both tiles' QK on this K tile are issued
+                    if (j < n_tiles[0]) {
+                        ok = mbar_wait(bar(BAR_VFULL + s), ph, abort_word, a.error, 7) &&
+                             mbar_wait(bar(BAR_PFULL + 0), (it * n_tiles[0] + j) & 1, abort_word, a.error, 8);
+                        if (!ok) break;
+                        tc_fence_after();
+                        // (the softmax warps read O of the previous head before they arrive on this P barrier,
+                        //  so overwriting O here with the first tile of the next head is safe)
+                        issue_pv(0, s, j == 0);
+                        if (j >= n_tiles[1]) tc_commit(bar(BAR_VEMPTY + s));   // no PV1 on this tile will follow
+                    }
                 }
             }
         }
@@ -360,11 +388,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint32_t lane_base = ((warp & 3) * 32) << 16;
         const uint32_t t_s = tmem + lane_base + q * 128, t_o = tmem + lane_base + 256 + q * 128;
         const uint32_t nq = n_tiles[q];
-        float m_ref = -INFINITY, l_sum = 0.f;
         bool ok = true;
+        for (uint32_t it = 0; it < items && ok && nq; ++it) {
+        const uint32_t h = kvh * a.G + it;              // the query head of this item
+        const uint32_t c0 = it * nq;                    // tiles of this row block finished before this item (barrier phases)
+        float m_ref = -INFINITY, l_sum = 0.f;
         for (uint32_t j = 0; j < nq && ok; ++j) {
-            ok = mbar_wait(bar(BAR_SFULL + q), j & 1, abort_word, a.error, 9);
-            if (j > 0 && ok) ok = mbar_wait(bar(BAR_OFULL + q), (j - 1) & 1, abort_word, a.error, 10);
+            ok = mbar_wait(bar(BAR_SFULL + q), (c0 + j) & 1, abort_word, a.error, 9);
+            if (j > 0 && ok) ok = mbar_wait(bar(BAR_OFULL + q), (c0 + j - 1) & 1, abort_word, a.error, 10);
             if (!ok) break;
             tc_fence_after();
             // one tile of the online softmax; the diagonal tile (the last one) is a second instantiation
@@ -480,7 +511,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             else tile_body(std::false_type{});
         }
         // ---- epilogue: O / l -> global ----
-        if (nq && ok) ok = mbar_wait(bar(BAR_OFULL + q), (nq - 1) & 1, abort_word, a.error, 11);
+        if (nq && ok) ok = mbar_wait(bar(BAR_OFULL + q), (c0 + nq - 1) & 1, abort_word, a.error, 11);
         if (nq && ok) {
             tc_fence_after();
             const float inv = 1.0f / l_sum;
@@ -503,6 +534,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
             }
         }
+        }   // items
     }
     // ---- teardown: everyone arrives, TMEM goes back ----
     tc_fence_before();
@@ -571,7 +603,7 @@ int launch_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_
     a.B = B; a.T = T; a.nh = nh; a.nkv = nkv; a.G = nh / nkv;
     a.m_tiles = (T + 255) / 256;
     a.scale_log2 = (1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
-    const unsigned long long blocks = (unsigned long long)a.m_tiles * B * nh;
+    const unsigned long long blocks = (unsigned long long)a.m_tiles * B * nkv;   // one CTA per (row block, sequence, KV group)
     SHADY_REQUIRE(ctx, blocks <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "attn_prefill: too many tiles for one launch");
     static thread_local int configured_dev = -1;
     if (configured_dev != ctx->device) {
