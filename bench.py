@@ -551,6 +551,117 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
     gpu.close()
 
 
+# ------------------------------------------------------------------------------------------------
+# Other BASELINE configs (reported in DESIGN.md; the default line stays cfg2)
+# ------------------------------------------------------------------------------------------------
+def _dist_setup(world: int, local_rank: int):
+    import torch
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+    return torch, dist, barrier
+
+
+def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
+    """cfg4: one sequence of 131072 rows, nh16/nkv2/hd256, bf16 KV, rows split over the ranks; every rank decodes its
+    rows into records, NCCL all-gathers them (16.5 KB per rank) and every rank merges them (gqa_reduce math)."""
+    torch, dist, barrier = _dist_setup(world, local_rank)
+    from shady_thinker_b200 import ops
+    from shady_thinker_b200._lib import BF16, F32
+    from shady_thinker_b200.gpu import GpuContext
+    from shady_thinker_b200.sharding import merge_args, shard_rows
+    L, nh, nkv, hd = 131072, 16, 2, 256
+    lo, hi = shard_rows(L, world, rank)
+    rows = hi - lo
+    stream = torch.cuda.Stream()
+    gpu = GpuContext(local_rank, stream=stream.cuda_stream)
+    row_bytes = nkv * hd * 2
+    n_sets = max(3, -(-320_000_000 // max(2 * rows * row_bytes, 1)))    # rotate through > 2x L2 of distinct rows
+    with torch.cuda.stream(stream):
+        ks = [torch.empty((max(rows, 1), nkv, hd), dtype=torch.bfloat16, device="cuda") for _ in range(n_sets)]
+        vs = [torch.empty_like(k) for k in ks]
+        for i in range(n_sets):
+            ops.fill_randn(gpu, ks[i], ks[i].numel(), BF16, SEED, 7000 + 100 * i + 1, first_idx=lo * nkv * hd)
+            ops.fill_randn(gpu, vs[i], vs[i].numel(), BF16, SEED, 7000 + 100 * i + 2, first_idx=lo * nkv * hd)
+        q = torch.empty((1, nh, hd), dtype=torch.bfloat16, device="cuda")
+        ops.fill_randn(gpu, q, q.numel(), BF16, SEED, 7999)
+        lens = torch.tensor([rows], dtype=torch.int32, device="cuda")
+        rec = torch.zeros((1, nh, hd + 2), device="cuda")
+        gathered = torch.zeros((world, 1, nh, hd + 2), device="cuda")
+        out = torch.zeros((1, nh, hd), device="cuda")
+        ws_n = ops.decode_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_splits=0, num_seqs=1)
+        ws = torch.zeros(ws_n, dtype=torch.uint8, device="cuda")
+        views = [ops.KvCacheView(BF16, ks[i], vs[i], 0) for i in range(n_sets)]
+        ev = []
+
+        def step(i, timed=False):
+            view = views[i % n_sets]
+            if world == 1:
+                a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                ops.attn_decode(gpu, q=q, cache=view, seq_lens=lens, out=out, head_dim=hd, num_kv_heads=nkv,
+                                num_q_heads=nh, num_splits=0, seq_lens_host=[rows], q_dtype=BF16, workspace=ws,
+                                workspace_bytes=ws_n)
+                b.record(stream)
+            else:
+                a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                ops.attn_decode_shard(gpu, q=q, cache=view, seq_lens=lens, records=rec, head_dim=hd, num_kv_heads=nkv,
+                                      num_q_heads=nh, num_splits=0, seq_lens_host=[rows], q_dtype=BF16, workspace=ws,
+                                      workspace_bytes=ws_n)
+                b.record(stream)
+                dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
+                ops.attn_reduce(gpu, partials=gathered, out=out, **merge_args(1, nh, hd, world))
+            if timed:
+                ev.append((a, b))
+
+        for i in range(args.warmup):
+            step(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        l0 = gpu.launch_count
+        e0.record(stream)
+        for i in range(args.steps):
+            step(i, True)
+        e1.record(stream)
+        barrier()
+        launches = gpu.launch_count - l0
+        total_ms = e0.elapsed_time(e1)
+        dec_ms = sum(a.elapsed_time(b) for a, b in ev) / len(ev)
+        assert torch.isfinite(out).all()
+    t = torch.tensor([total_ms, dec_ms], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, dec_ms_max = [float(x) for x in t.tolist()]
+    if rank == 0:
+        peak, src = measured_peaks()
+        total_bytes = 2.0 * L * row_bytes
+        ach = 2.0 * rows * row_bytes / (dec_ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "decode_attn_kv_bandwidth", "value": total_bytes * args.steps / (total_ms * 1e-3) / 1e9, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "cfg4: long-context single-sequence decode, rows split over GPUs, LSE merge over NCCL",
+                       "context": L, "num_q_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "kv_dtype": "bf16",
+                       "rows_per_gpu": rows, "combine": "none" if world == 1 else "all-gather of 16.5 KB records + local merge",
+                       "l2": f"{n_sets} cache sets rotate between steps"},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "peak_source": f"{src} (copy bandwidth)", "kernel": "decode16_kernel<bf16,256> on this rank's rows",
+                         "algorithmic_bytes_per_launch": 2.0 * rows * row_bytes, "avg_launch_ms": dec_ms},
+            "gpu_launches": int(launches)}), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    gpu.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -558,21 +669,26 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3"],
-                    help="cfg2 = batched ragged decode (default, the headline); cfg3 = causal prefill")
+    ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
+                    help="cfg2 = batched ragged decode (default, the headline); cfg3 = causal prefill; "
+                         "cfg1/cfg4/cfg5 = the other BASELINE configs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.workload == "cfg3" and args.steps == 2000:
-        args.steps = 200   # a prefill step is ~0.7 ms of attention plus the append
+    if args.steps == 2000:   # the default suits cfg2 (0.1 ms steps); scale it for the others
+        args.steps = {"cfg1": 300, "cfg3": 200, "cfg5": 5}.get(args.workload, 2000)
     if args.impl == "reference":
-        (run_reference_prefill if args.workload == "cfg3" else run_reference)(args, rank)
+        (run_reference_prefill if args.workload == "cfg3" else run_reference)(args, rank)   # decode configs share the cfg2 sample
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         sys.exit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
-    (run_prefill if args.workload == "cfg3" else run_ours)(args, rank, world, local_rank)
+    runner = {"cfg2": run_ours, "cfg3": run_prefill, "cfg4": run_cfg4}.get(args.workload)
+    if runner is None:
+        from shady_thinker_b200 import extra_workloads
+        runner = getattr(extra_workloads, "run_" + args.workload)
+    runner(args, rank, world, local_rank)
 
 
 if __name__ == "__main__":

@@ -181,6 +181,17 @@ int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *
                       const uint32_t *seq_lens_host, void *d_out, float *d_lse, const float *d_gate,
                       void *d_workspace, size_t workspace_bytes);
 
+/* One shard of a sequence-split decode (rows of one sequence spread over several GPUs): the same
+ * kernels as shady_attn_decode, but the result is written as records d_records[seq][nh][hd+2] in the
+ * layout of the reference's partials ([hd] = log-sum-exp, gqa_attention_head.wgsl:112-123), ready to be
+ * gathered rank-major and merged with shady_attn_reduce(split_stride = num_seqs*nh*(hd+2),
+ * head_stride = hd+2) — gqa_reduce.wgsl across GPUs.  d_seq_lens counts this shard's rows only; a shard
+ * with no rows yields lse = -inf and gets weight 0 in the merge. */
+int shady_attn_decode_shard(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
+                            const shady_kv_cache *cache, const uint32_t *d_seq_lens,
+                            const uint32_t *seq_lens_host, float *d_records, void *d_workspace,
+                            size_t workspace_bytes);
+
 /* No counterpart in the reference.  The same decode as shady_attn_decode for callers that cannot
  * hand over a workspace: a server that gave all device memory to its KV-cache arena at start-up, or
  * a decode loop that cannot take the device-wide stall of an allocation.  The arrival counters and

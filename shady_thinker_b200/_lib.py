@@ -19,7 +19,7 @@ EXPORTS = [
     "shady_ctx_create", "shady_ctx_destroy", "shady_last_error", "shady_ctx_stream", "shady_ctx_launch_count",
     "shady_buffer_create", "shady_buffer_free", "shady_buffer_write", "shady_buffer_read", "shady_buffer_copy",
     "shady_flush", "shady_synchronize", "shady_kv_append_rope", "shady_decode_workspace_size", "shady_decode_workspace_init",
-    "shady_attn_decode", "shady_attn_decode_static", "shady_attn_decode_partials", "shady_attn_reduce", "shady_attn_prefill",
+    "shady_attn_decode", "shady_attn_decode_static", "shady_attn_decode_shard", "shady_attn_decode_partials", "shady_attn_reduce", "shady_attn_prefill",
     "shady_sigmoid_mul", "shady_fill_randn",
 ]
 
@@ -91,6 +91,8 @@ def load() -> C.CDLL:
                                     C.POINTER(C.c_uint32), vp, f32p, f32p, vp, sz]
     L.shady_attn_decode_static.argtypes = [vp, C.POINTER(DecodeParams), vp, C.POINTER(KvCache), u32p,
                                            C.POINTER(C.c_uint32), vp, f32p, f32p]
+    L.shady_attn_decode_shard.argtypes = [vp, C.POINTER(DecodeParams), vp, C.POINTER(KvCache), u32p,
+                                          C.POINTER(C.c_uint32), f32p, vp, sz]
     L.shady_attn_decode_partials.argtypes = [vp, C.POINTER(DecodeParams), vp, C.POINTER(KvCache), u32p, f32p]
     L.shady_attn_reduce.argtypes = [vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64, f32p, vp,
                                     C.c_uint32, f32p]

@@ -44,6 +44,8 @@ struct DecodeArgs {
     uint32_t spans;       // balanced mode: number of equal spans the line is cut into
     uint32_t q_dtype, out_dtype;
     uint32_t force_partials;  // 1: always write the partial record (shady_attn_decode_partials)
+    uint32_t out_row_stride;  // elements between consecutive head rows of `out` (hd, or hd+2 when out is a record buffer)
+    uint32_t lse_stride;      // elements between consecutive entries of `lse` (1, or hd+2 inside a record buffer)
     float scale_log2;         // 1/sqrt(hd) * log2(e)
 };
 
@@ -170,10 +172,11 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
         const float lse = L > 0.f ? logf(L) + M * kLn2 : -INFINITY;
         const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
         if (direct) {
-            const size_t oi = ((size_t)p.seq * a.nh + head) * HD + d;
-            if (a.gate) val *= sigmoidf_ref(a.gate[oi]);
+            const size_t gi = ((size_t)p.seq * a.nh + head) * HD + d;                 // gate index
+                const size_t oi = ((size_t)p.seq * a.nh + head) * a.out_row_stride + d;
+            if (a.gate) val *= sigmoidf_ref(a.gate[gi]);
             store_from_f32(a.out, oi, a.out_dtype, val);
-            if (d == 0 && a.lse) a.lse[(size_t)p.seq * a.nh + head] = lse;
+            if (d == 0 && a.lse) a.lse[((size_t)p.seq * a.nh + head) * a.lse_stride] = lse;
         } else {
             float *rec = rec_ptr(a, p, head, p.my_rec);
             rec[d] = val;
@@ -275,10 +278,11 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
                 const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
                 const float wsum = sm_wsum[hr];
                 float val = wsum > 0.f ? acc[k] / wsum : 0.f;
-                const size_t oi = ((size_t)p.seq * a.nh + head) * HD + d;
-                if (a.gate) val *= sigmoidf_ref(a.gate[oi]);
+                const size_t gi = ((size_t)p.seq * a.nh + head) * HD + d;                 // gate index
+                const size_t oi = ((size_t)p.seq * a.nh + head) * a.out_row_stride + d;
+                if (a.gate) val *= sigmoidf_ref(a.gate[gi]);
                 store_from_f32(a.out, oi, a.out_dtype, val);
-                if (d == 0 && a.lse) a.lse[(size_t)p.seq * a.nh + head] = wsum > 0.f ? sm_gmax[hr] + logf(wsum) : -INFINITY;
+                if (d == 0 && a.lse) a.lse[((size_t)p.seq * a.nh + head) * a.lse_stride] = wsum > 0.f ? sm_gmax[hr] + logf(wsum) : -INFINITY;
             }
         }
         __syncthreads();
@@ -809,9 +813,9 @@ size_t decode_workspace_bytes(const shady_decode_params *p) {
 
 int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
                   const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, void *d_out, float *d_lse,
-                  const float *d_gate, void *d_ws, size_t ws_bytes, float *d_force_partials) {
+                  const float *d_gate, void *d_ws, size_t ws_bytes, float *d_force_partials, float *d_shard_records) {
     SHADY_REQUIRE(ctx, p && d_q && cache && d_seq_lens, SHADY_ERR_BAD_ARG, "decode: null argument");
-    SHADY_REQUIRE(ctx, d_out || d_force_partials, SHADY_ERR_BAD_ARG, "decode: null output");
+    SHADY_REQUIRE(ctx, d_out || d_force_partials || d_shard_records, SHADY_ERR_BAD_ARG, "decode: null output");
     SHADY_REQUIRE(ctx, p->num_seqs > 0 && p->num_kv_heads > 0 && p->heads_per_kv > 0, SHADY_ERR_BAD_ARG,
                   "decode: zero-sized problem");
     SHADY_REQUIRE(ctx, p->num_q_heads == p->num_kv_heads * p->heads_per_kv, SHADY_ERR_BAD_ARG,
@@ -839,6 +843,11 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
     a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;
     a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e;
     a.num_splits = p->num_splits;
+    a.out_row_stride = hd; a.lse_stride = 1;
+    if (d_shard_records) {   // rank-local result of one shard as records [seq][nh][hd+2]: out, lse, (unused)
+        a.out = d_shard_records; a.out_dtype = SHADY_F32; a.out_row_stride = hd + 2;
+        a.lse = d_shard_records + hd; a.lse_stride = hd + 2; a.gate = nullptr;
+    }
     a.gz = head_groups(cache->dtype, p->heads_per_kv);
     const Variant16 var = variant16(hd, env_u32("SHADY_DECODE_VARIANT", 0));
     // One kv head per CTA measured fastest (sibling CTAs of the other kv heads run next to each other in
@@ -976,6 +985,7 @@ int launch_decode_static(shady_ctx *ctx, const shady_decode_params *p, const voi
     a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;
     a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e;
     a.num_splits = p->num_splits;
+    a.out_row_stride = hd; a.lse_stride = 1;
     a.gz = head_groups(cache->dtype, p->heads_per_kv);
     const Variant16 var = variant16(hd, 0);
     const uint32_t kv_groups = p->num_kv_heads;           // one kv head per CTA

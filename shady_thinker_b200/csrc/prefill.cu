@@ -554,13 +554,32 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }
 
 // ---- host side -----------------------------------------------------------------------------
+// cuTensorMapEncodeTiled is a driver API; it is looked up through the runtime so that the library does not link
+// against libcuda (and still loads on a machine without a driver, where only the host-side entry points work).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
 static bool make_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
                         uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3) {
     cuuint64_t dims[4] = {d0, d1, d2, d3};
     cuuint64_t strides[3] = {s1, s2, s3};  // bytes, dims 1..3
     cuuint32_t box[4] = {64, 1, 128, 1};   // 64 elements (128 B, the swizzle span) x 128 rows
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    return cuTensorMapEncodeTiled(map, dt, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return false;
+    return encode(map, dt, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }

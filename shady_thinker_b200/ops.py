@@ -112,6 +112,19 @@ def attn_decode_static(gpu: GpuContext, *, q, cache: KvCacheView, seq_lens, out,
     del keep
 
 
+def attn_decode_shard(gpu: GpuContext, *, q, cache: KvCacheView, seq_lens, records, head_dim: int, num_kv_heads: int,
+                      num_q_heads: int, num_seqs: int = 1, num_splits: int = 0, seq_lens_host=None, q_dtype: int = F32,
+                      workspace=None, workspace_bytes: int = 0) -> None:
+    """Decode over this rank's rows of each sequence; result as records [num_seqs][nh][hd+2] (out, lse, unused)."""
+    p = DecodeParams(head_dim, num_kv_heads, num_q_heads, num_q_heads // num_kv_heads, num_splits, num_seqs, q_dtype,
+                     F32)
+    c = cache.c_struct()
+    keep, hl = _host_lens(seq_lens_host)
+    gpu._check(gpu._L.shady_attn_decode_shard(gpu.handle, C.byref(p), _addr(q), C.byref(c), _addr(seq_lens), hl,
+                                              _addr(records), _addr(workspace) or None, workspace_bytes))
+    del keep
+
+
 def attn_decode_partials(gpu: GpuContext, *, q, cache: KvCacheView, seq_lens, partials, head_dim: int,
                          num_kv_heads: int, num_q_heads: int, num_splits: int, q_dtype: int = F32) -> None:
     p = DecodeParams(head_dim, num_kv_heads, num_q_heads, num_q_heads // num_kv_heads, num_splits, 1, q_dtype, F32)

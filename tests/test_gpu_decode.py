@@ -215,3 +215,38 @@ def test_bad_arguments_return_status_not_abort(gpu_ctx):
                         num_splits=4)
     assert e.value.code == 4
     gpu_ctx.synchronize()   # the context is still usable
+
+
+def test_decode_shard_records_merge_rank_major(gpu_ctx, oracle):
+    """shady_attn_decode_shard on each 'rank' range of one sequence + the rank-major merge == unsharded decode."""
+    from shady_thinker_b200.sharding import merge_args, shard_rows
+    nh, nkv, hd, L, P = 16, 2, 256, 5000, 4
+    q = rounded(oracle, oracle.randn((1, nh, hd), 73, 1), BF16)
+    k = rounded(oracle, oracle.randn((L, nkv, hd), 73, 2), BF16)
+    v = rounded(oracle, oracle.randn((L, nkv, hd), 73, 3), BF16)
+    gathered = torch.full((P, 1, nh, hd + 2), float("nan"), device="cuda")
+    ws_n = ops.decode_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_splits=0, num_seqs=1)
+    ws = torch.zeros(ws_n, dtype=torch.uint8, device="cuda")
+    d_q = to_dev(q, BF16)
+    for r in range(P):
+        lo, hi = shard_rows(L, P, r)
+        kk, vv = k[lo:max(hi, lo + 1)], v[lo:max(hi, lo + 1)]
+        view = ops.KvCacheView(BF16, to_dev(kk, BF16), to_dev(vv, BF16), 0)
+        lens = torch.tensor([hi - lo], dtype=torch.int32).cuda()
+        ops.attn_decode_shard(gpu_ctx, q=d_q, cache=view, seq_lens=lens, records=gathered[r], head_dim=hd,
+                              num_kv_heads=nkv, num_q_heads=nh, num_seqs=1, num_splits=0, seq_lens_host=[hi - lo],
+                              q_dtype=BF16, workspace=ws, workspace_bytes=ws_n)
+        gpu_ctx.synchronize()
+    d_out = torch.empty((nh, hd), device="cuda")
+    ops.attn_reduce(gpu_ctx, partials=gathered, out=d_out, **merge_args(1, nh, hd, P))
+    gpu_ctx.synchronize()
+    assert rel_err(to_host(d_out), oracle.attention_f64(q[0], k, v, L)) <= RTOL_16
+    # an empty shard: lse = -inf, zeros
+    view = ops.KvCacheView(BF16, to_dev(k[:1], BF16), to_dev(v[:1], BF16), 0)
+    rec = torch.full((1, nh, hd + 2), float("nan"), device="cuda")
+    ops.attn_decode_shard(gpu_ctx, q=d_q, cache=view, seq_lens=torch.zeros(1, dtype=torch.int32).cuda(), records=rec,
+                          head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_seqs=1, num_splits=0, seq_lens_host=[0],
+                          q_dtype=BF16, workspace=ws, workspace_bytes=ws_n)
+    gpu_ctx.synchronize()
+    rh = to_host(rec)
+    assert np.isneginf(rh[0, :, hd]).all() and not rh[0, :, :hd].any()
