@@ -26,6 +26,7 @@ namespace shady {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+constexpr uint32_t kMaxSlots = 148u * 8u;  // bound on resident CTAs (spans); sizes the workspace and the merge tables
 constexpr uint32_t kBlkPos = 16;  // positions per row-block: unit of the work line and of the MMA pipeline
 
 struct DecodeArgs {
@@ -44,6 +45,7 @@ struct DecodeArgs {
     uint32_t spans;       // balanced mode: number of equal spans the line is cut into
     uint32_t q_dtype, out_dtype;
     uint32_t force_partials;  // 1: always write the partial record (shady_attn_decode_partials)
+    uint32_t defer_merge;     // 1: CTAs only write records; balanced_merge_kernel merges them (sequences cut into many spans)
     uint32_t out_row_stride;  // elements between consecutive head rows of `out` (hd, or hd+2 when out is a record buffer)
     uint32_t lse_stride;      // elements between consecutive entries of `lse` (1, or hd+2 inside a record buffer)
     float scale_log2;         // 1/sqrt(hd) * log2(e)
@@ -186,7 +188,7 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
             }
         }
     }
-    if (direct || a.force_partials) return;
+    if (direct || a.force_partials || a.defer_merge) return;
     // ---- last-arriving CTA merges the records ----
     __threadfence();
     __syncthreads();
@@ -337,8 +339,7 @@ constexpr int kBlk = (int)kBlkPos;  // positions per warp block (one MMA k-step 
 template <int HD, int NW, int STAGES, int KPC> struct Decode16Smem {
     static constexpr int kRowBytes = HD * 2;
     static constexpr int kTileBytes = kBlk * kRowBytes;          // one K or V block
-    static constexpr int kStageBytes = 2 * kTileBytes;           // K + V
-    static constexpr int kWarpBytes = STAGES * kStageBytes;
+    static constexpr int kWarpBytes = STAGES * kTileBytes;       // ring of STAGES tile slots; K and V tiles alternate in it
     static constexpr int kQTile = 16 * kRowBytes;                // Q rows of one kv head
     static constexpr int kQBytes = KPC * kQTile;
     static constexpr int kStatBytes = 2 * NW * 16 * 4;           // merge m and l
@@ -348,7 +349,7 @@ template <int HD, int NW, int STAGES, int KPC> struct Decode16Smem {
 
 // Resident CTAs per SM each configuration is built for (bounds the registers per thread).
 constexpr int decode16_min_blocks(int HD, int NW, int STAGES) {
-    return HD > 128 ? 1 : (NW == 4 ? (STAGES <= 3 ? 2 : 1) : 1);
+    return HD > 128 ? 1 : (NW == 4 ? (STAGES <= 6 ? 2 : 1) : 1);
 }
 
 // KPC kv heads per CTA: warp w streams kv head (w % KPC) of the CTA's rows, and the WPK = NW/KPC warps
@@ -398,23 +399,26 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
         const char *vbase = kv_seq_ptr(a.kv.v_base, a.kv.v_ptrs, a.kv.seq_stride_bytes, p.seq) + (size_t)kvh * S::kRowBytes;
         const uint32_t nblk = (end - start + kBlk - 1) / kBlk;
         const uint32_t my_n = nblk > sub ? (nblk - sub + WPK - 1) / WPK : 0;
-        auto issue = [&](uint32_t bi) {
-            const uint32_t pos0 = start + (sub + bi * WPK) * kBlk;
-            const uint32_t st = warp_smem + (bi % STAGES) * S::kStageBytes;
+        // The pipeline moves single tiles: item 2i is the K tile of the warp's i-th block, item 2i+1 its V tile,
+        // item t lives in slot t % STAGES, and STAGES-1 items are in flight while one is being consumed.
+        const uint32_t n_items = 2 * my_n;
+        auto issue = [&](uint32_t t) {
+            const uint32_t pos0 = start + (sub + (t >> 1) * WPK) * kBlk;
+            const uint32_t st = warp_smem + (t % STAGES) * S::kTileBytes;
+            const char *src = (t & 1) ? vbase : kbase;
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
                 const uint32_t r = i * RPI + l_row;
                 const bool ok = pos0 + r < end;
                 const size_t goff = (size_t)(pos0 + r) * pos_stride + l_chunk * 16;
                 const uint32_t soff = r * S::kRowBytes + ((l_chunk ^ (r & 7)) << 4);
-                cp_async16(st + soff, kbase + (ok ? goff : 0), ok);
-                cp_async16(st + S::kTileBytes + soff, vbase + (ok ? goff : 0), ok);
+                cp_async16(st + soff, src + (ok ? goff : 0), ok);
             }
         };
         // ---- start the K/V stream first, then fetch Q underneath it ----
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
-            if ((uint32_t)s < my_n) issue(s);
+            if ((uint32_t)s < n_items) issue(s);
             cp_async_commit();
         }
         // stage Q of the CTA's kv heads (rows >= rows_valid are zero) as T, swizzled
@@ -451,12 +455,12 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
         float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
         for (uint32_t i = 0; i < my_n; ++i) {
-            cp_async_wait<STAGES - 2>();
+            cp_async_wait<STAGES - 2>();   // this block's K tile has landed
             __syncwarp();
-            if (i + STAGES - 1 < my_n) issue(i + STAGES - 1);
+            if (2 * i + STAGES - 1 < n_items) issue(2 * i + STAGES - 1);
             cp_async_commit();
 
-            const uint32_t st = warp_smem + (i % STAGES) * S::kStageBytes;
+            const uint32_t st = warp_smem + ((2 * i) % STAGES) * S::kTileBytes;
             const uint32_t pos0 = start + (sub + i * WPK) * kBlk;
             // ---- S = Q K^T : heads x 16 positions ----
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -510,11 +514,16 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             pa[2] = pack2<T>(s[1][0], s[1][1]);
             pa[3] = pack2<T>(s[1][2], s[1][3]);
             // ---- O = O*corr + P V ----
+            cp_async_wait<STAGES - 2>();   // this block's V tile has landed
+            __syncwarp();
+            if (2 * i + STAGES < n_items) issue(2 * i + STAGES);   // into the slot of the K tile just consumed
+            cp_async_commit();
+            const uint32_t stv = warp_smem + ((2 * i + 1) % STAGES) * S::kTileBytes;
 #pragma unroll
             for (int jn = 0; jn < HD / 8; jn += 2) {
                 uint32_t vb[4];
                 const uint32_t row = (mat & 1) * 8 + rin, chunk = jn + (mat >> 1);
-                ldsm_x4_t(vb, st + S::kTileBytes + row * S::kRowBytes + ((chunk ^ rin) << 4));
+                ldsm_x4_t(vb, stv + row * S::kRowBytes + ((chunk ^ rin) << 4));
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
                     o[jn + u][0] *= corr[0]; o[jn + u][1] *= corr[0];
@@ -672,6 +681,55 @@ __global__ void __launch_bounds__(NW * 32) decode32_kernel(const DecodeArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------
+// Merge of balanced-mode records as its own launch.  A sequence that is cut into many spans (one long
+// context spread over every SM) would leave its whole merge to the single CTA that arrives last — a
+// serial tail of L2 round trips; here every (sequence, head, 64-dim chunk) gets its own CTA instead.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(64) balanced_merge_kernel(const DecodeArgs a) {
+    const uint32_t seq = blockIdx.x, head = blockIdx.y, d = blockIdx.z * 64 + threadIdx.x;
+    __shared__ uint32_t sm_b;
+    if (threadIdx.x < 32) {   // first row-block of this sequence on the line
+        uint32_t acc = 0;
+        for (uint32_t j = threadIdx.x; j < seq; j += 32) acc += blocks_of(a.seq_lens[j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (threadIdx.x == 0) sm_b = acc;
+    }
+    __syncthreads();
+    const uint32_t B = sm_b, nb = blocks_of(a.seq_lens[seq]);
+    const uint32_t c0 = span_of(a, B), nrec = span_of(a, B + nb - 1) - c0 + 1;
+    if (nrec == 1) return;   // written directly by its only CTA (uniform for the CTA)
+    const uint32_t rs = a.hd + 2;
+    // record rows of this sequence, resolved once per CTA (span_begin is a 64-bit division)
+    __shared__ uint32_t sm_row[kMaxSlots];
+    __shared__ float sm_w[kMaxSlots];
+    for (uint32_t s = threadIdx.x; s < nrec; s += 64) {
+        const uint32_t c = c0 + s;
+        sm_row[s] = (c * 2 + (span_begin(a, c) >= B ? 0u : 1u)) * a.nh + head;
+        sm_w[s] = __ldcg(a.partials + (size_t)sm_row[s] * rs + a.hd);   // lse of record s
+    }
+    __syncthreads();
+    float gmax = -INFINITY;
+    for (uint32_t s = 0; s < nrec; ++s)
+        if (sm_w[s] > -INFINITY) gmax = fmaxf(gmax, sm_w[s]);
+    float acc = 0.f, wsum = 0.f;
+#pragma unroll 8
+    for (uint32_t s = 0; s < nrec; ++s) {
+        const float v = __ldcg(a.partials + (size_t)sm_row[s] * rs + d);
+        const float l = sm_w[s];
+        const float w = l > -INFINITY ? expf(l - gmax) : 0.f;   // gqa_reduce.wgsl:56; empty ranges weigh nothing
+        acc += w > 0.f ? w * v : 0.f;
+        wsum += w;
+    }
+    if (d >= a.hd) return;
+    float val = wsum > 0.f ? acc / wsum : 0.f;
+    const size_t gi = ((size_t)seq * a.nh + head) * a.hd + d;
+    if (a.gate) val *= sigmoidf_ref(a.gate[gi]);
+    store_from_f32(a.out, ((size_t)seq * a.nh + head) * a.out_row_stride + d, a.out_dtype, val);
+    if (d == 0 && a.lse) a.lse[((size_t)seq * a.nh + head) * a.lse_stride] = wsum > 0.f ? gmax + logf(wsum) : -INFINITY;
+}
+
+// ---------------------------------------------------------------------------------------
 // Stand-alone merge of split records (gqa_reduce.wgsl:20-65), stride-generalised
 // ---------------------------------------------------------------------------------------
 struct ReduceArgs {
@@ -738,7 +796,7 @@ template <int HD, int NW, int STAGES>
 static int launch16_kpc(shady_ctx *ctx, const DecodeArgs &a, uint32_t kpc, bool half, uint32_t blocks) {
 #define SHADY_L16(K_) \
     (half ? launch16<__half, HD, NW, STAGES, K_>(ctx, a, blocks) : launch16<__nv_bfloat16, HD, NW, STAGES, K_>(ctx, a, blocks))
-    if constexpr (NW >= 8) {
+    if constexpr (NW >= 8 && HD <= 128) {   // eight Q tiles of head_dim 256 would not fit next to the pipeline
         if (kpc == 8) return SHADY_L16(8);
     }
     if (kpc == 4) return SHADY_L16(4);
@@ -750,14 +808,15 @@ static int launch16_kpc(shady_ctx *ctx, const DecodeArgs &a, uint32_t kpc, bool 
 struct Variant16 {
     uint32_t nw, stages, ctas_per_sm;
 };
-// head_dim 128: {4 warps, 3 stages} at two CTAs per SM measured best on the ragged fp16 batch
-// (8 warps per SM, 128 KB of K/V in flight per SM, every SM slot filled when nkv divides 2*SMs).
+// {warps, tile slots per warp, CTAs per SM}.  head_dim 128: 4 warps x 6 slots at two CTAs per SM measured best on the
+// ragged fp16 batch (8 warps and 128 KB of K/V in flight per SM).  head_dim 256: tiles are twice as large and a block
+// costs twice the math, so one CTA of 8 warps x 3 slots keeps the same number of warps and bytes in flight per SM.
 static Variant16 variant16(uint32_t hd, uint32_t v) {
-    if (hd > 128) return v == 1 ? Variant16{4, 2, 1} : Variant16{4, 3, 1};
+    if (hd > 128) return v == 1 ? Variant16{4, 6, 1} : (v == 2 ? Variant16{8, 2, 1} : Variant16{8, 3, 1});
     switch (v) {
-        case 1: return Variant16{8, 2, 1};
-        case 2: return Variant16{8, 3, 1};
-        default: return Variant16{4, 3, 2};
+        case 1: return Variant16{8, 4, 1};
+        case 2: return Variant16{8, 6, 1};
+        default: return Variant16{4, 6, 2};
     }
 }
 static uint32_t kv_heads_per_cta(uint32_t nkv, uint32_t nw) {
@@ -794,7 +853,7 @@ static uint32_t env_u32(const char *name, uint32_t dflt) {
     const char *v = getenv(name);
     return v && *v ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
 }
-constexpr uint32_t kMaxSlots = 148u * 8u;  // bound on resident CTAs used by the workspace size
+constexpr uint32_t kDeferMergeRecords = 12;  // more records than this per sequence: merge in a second launch
 
 // Workspace layout: [arrival counters: num_seqs*nkv*gz u32, padded to 256 B][partial records].
 static size_t counters_bytes(const shady_decode_params *p) {
@@ -855,7 +914,7 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
     uint32_t kpc = 1u;
     {
         const uint32_t want = env_u32("SHADY_DECODE_KPC", 0);
-        if (!f32 && want && want <= kv_heads_per_cta(p->num_kv_heads, var.nw) && (want & (want - 1)) == 0) kpc = want;
+        if (!f32 && want && want <= kv_heads_per_cta(p->num_kv_heads, hd > 128 ? 4u : var.nw) && (want & (want - 1)) == 0) kpc = want;
     }
     const uint32_t kv_groups = p->num_kv_heads / kpc;
     uint32_t ctas_per_sm = env_u32("SHADY_DECODE_CTAS_PER_SM", f32 ? 4u : var.ctas_per_sm);
@@ -889,6 +948,14 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
         a.spans = (uint32_t)spans;
         items = spans;
         need_ws = spans > 1;  // a sequence may straddle spans whenever there is more than one
+        // a sequence cut into many spans is merged by a wide second launch instead of by its last CTA
+        unsigned long long u = 0;
+        for (uint32_t i = 0; i < p->num_seqs && !a.defer_merge; ++i) {
+            const unsigned long long nb = seq_lens_host[i] == 0 ? 1 : (seq_lens_host[i] + kBlkPos - 1) / kBlkPos;
+            const unsigned long long nrec = ((u + nb - 1) * spans) / line - (u * spans) / line + 1;
+            if (nrec > kDeferMergeRecords) a.defer_merge = 1;
+            u += nb;
+        }
     }
     if (need_ws) {
         const size_t need = decode_workspace_bytes(p);
@@ -900,20 +967,27 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
     SHADY_REQUIRE(ctx, blocks64 <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "decode: too many work items for one launch");
     const uint32_t blocks = (uint32_t)blocks64;
 
+    int rc;
     if (f32) {
         const uint32_t gt = group_rows_f32(p->heads_per_kv);
-        if (hd == 64) return launch32<64, 8>(ctx, a, blocks, gt);
-        if (hd == 128) return launch32<128, 8>(ctx, a, blocks, gt);
-        return launch32<256, 4>(ctx, a, blocks, gt);
+        if (hd == 64) rc = launch32<64, 8>(ctx, a, blocks, gt);
+        else if (hd == 128) rc = launch32<128, 8>(ctx, a, blocks, gt);
+        else rc = launch32<256, 4>(ctx, a, blocks, gt);
+    } else {
+        const bool h = cache->dtype == SHADY_F16;
+        if (hd == 128) {
+            if (var.nw == 8 && var.stages == 6) rc = launch16_kpc<128, 8, 6>(ctx, a, kpc, h, blocks);
+            else if (var.nw == 8) rc = launch16_kpc<128, 8, 4>(ctx, a, kpc, h, blocks);
+            else rc = launch16_kpc<128, 4, 6>(ctx, a, kpc, h, blocks);
+        } else if (var.nw == 4) rc = launch16_kpc<256, 4, 6>(ctx, a, kpc, h, blocks);
+        else if (var.stages == 2) rc = launch16_kpc<256, 8, 2>(ctx, a, kpc, h, blocks);
+        else rc = launch16_kpc<256, 8, 3>(ctx, a, kpc, h, blocks);
     }
-    const bool h = cache->dtype == SHADY_F16;
-    if (hd == 128) {
-        if (var.nw == 8 && var.stages == 3) return launch16_kpc<128, 8, 3>(ctx, a, kpc, h, blocks);
-        if (var.nw == 8) return launch16_kpc<128, 8, 2>(ctx, a, kpc, h, blocks);
-        return launch16_kpc<128, 4, 3>(ctx, a, kpc, h, blocks);
-    }
-    if (var.stages == 3) return launch16_kpc<256, 4, 3>(ctx, a, kpc, h, blocks);
-    return launch16_kpc<256, 4, 2>(ctx, a, kpc, h, blocks);
+    if (rc != SHADY_OK || !a.defer_merge) return rc;
+    balanced_merge_kernel<<<dim3(p->num_seqs, p->num_q_heads, (hd + 63) / 64), 64, 0, ctx->stream>>>(a);
+    ctx->launches++;
+    SHADY_CUDA_OK(ctx, cudaGetLastError());
+    return SHADY_OK;
 }
 
 // The workspace must hold zeros in its counter area before the first call; the kernels
@@ -1034,8 +1108,8 @@ int launch_decode_static(shady_ctx *ctx, const shady_decode_params *p, const voi
         return launch32<256, 4>(ctx, a, blocks, gt);
     }
     const bool h = cache->dtype == SHADY_F16;
-    if (hd == 128) return launch16_kpc<128, 4, 3>(ctx, a, 1u, h, blocks);
-    return launch16_kpc<256, 4, 3>(ctx, a, 1u, h, blocks);
+    if (hd == 128) return launch16_kpc<128, 4, 6>(ctx, a, 1u, h, blocks);
+    return launch16_kpc<256, 8, 3>(ctx, a, 1u, h, blocks);
 }
 
 int launch_reduce(shady_ctx *ctx, uint32_t hd, uint32_t ns, uint32_t nh, uint64_t split_stride, uint64_t head_stride,
