@@ -600,6 +600,12 @@ def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
         ws = torch.zeros(ws_n, dtype=torch.uint8, device="cuda")
         views = [ops.KvCacheView(BF16, ks[i], vs[i], 0) for i in range(n_sets)]
         ev = []
+        # merge across ranks: the fused peer-memory kernel, or (SHADY_CFG4_COMBINE=nccl) all-gather + merge kernel
+        use_nccl = os.environ.get("SHADY_CFG4_COMBINE", "p2p") == "nccl"
+        comb = None
+        if world > 1 and not use_nccl:
+            from shady_thinker_b200.p2p import ShardCombiner
+            comb = ShardCombiner(gpu, rank=rank, world=world, num_heads=nh, head_dim=hd)
 
         def step(i, timed=False):
             view = views[i % n_sets]
@@ -617,8 +623,11 @@ def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
                                       num_q_heads=nh, num_splits=0, seq_lens_host=[rows], q_dtype=BF16, workspace=ws,
                                       workspace_bytes=ws_n)
                 b.record(stream)
-                dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
-                ops.attn_reduce(gpu, partials=gathered, out=out, **merge_args(1, nh, hd, world))
+                if comb is not None:
+                    comb.combine(rec, out)
+                else:
+                    dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
+                    ops.attn_reduce(gpu, partials=gathered, out=out, **merge_args(1, nh, hd, world))
             if timed:
                 ev.append((a, b))
 
@@ -650,12 +659,15 @@ def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "cfg4: long-context single-sequence decode, rows split over GPUs, LSE merge over NCCL",
                        "context": L, "num_q_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "kv_dtype": "bf16",
-                       "rows_per_gpu": rows, "combine": "none" if world == 1 else "all-gather of 16.5 KB records + local merge",
+                       "rows_per_gpu": rows, "combine": "none" if world == 1 else ("NCCL all-gather of 16.5 KB records + merge kernel" if use_nccl else
+                                   "one kernel: peer stores of 16.5 KB records over NVLink + flags + merge"),
                        "l2": f"{n_sets} cache sets rotate between steps"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
                          "peak_source": f"{src} (copy bandwidth)", "kernel": "decode16_kernel<bf16,256> on this rank's rows",
                          "algorithmic_bytes_per_launch": 2.0 * rows * row_bytes, "avg_launch_ms": dec_ms},
             "gpu_launches": int(launches)}), flush=True)
+    if comb is not None:
+        comb.close()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

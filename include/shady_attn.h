@@ -192,6 +192,26 @@ int shady_attn_decode_shard(shady_ctx *ctx, const shady_decode_params *p, const 
                             const uint32_t *seq_lens_host, float *d_records, void *d_workspace,
                             size_t workspace_bytes);
 
+/* ---- merging the shards of one sequence across GPUs over NVLink peer memory (no reference counterpart:
+ * the reference is single-device; the math is gqa_reduce.wgsl:33-64) ---------------------------------- */
+/* Share a buffer made with shady_buffer_create with the other processes of the box (CUDA IPC): export a
+ * 64-byte handle here, send it by any host channel, open it there.  Close before the owner frees it. */
+int shady_ipc_export(shady_ctx *ctx, void *d_buf, unsigned char handle[64]);
+int shady_ipc_open(shady_ctx *ctx, const unsigned char handle[64], void **d_peer);
+int shady_ipc_close(shady_ctx *ctx, void *d_peer);
+/* Size of the per-rank exchange buffer (flags + two generations of `world` records per head).  It must be
+ * zero before the first call. */
+int shady_combine_p2p_buffer_size(uint32_t world, uint32_t num_heads, uint32_t head_dim, size_t *bytes);
+/* One kernel = exchange + merge: every rank calls it with its own records d_records[nh][hd+2] (from
+ * shady_attn_decode_shard, num_seqs == 1).  d_peer_table is a device array [world] of the ranks' exchange
+ * buffers as mapped into this process (entry `rank` is the local one).  `epoch` starts at 1 and grows by 1
+ * per call on every rank.  The kernel stores its records into every peer's buffer, raises per-head flags,
+ * waits (bounded) for the other ranks' flags and writes the merged rows to d_out[nh][hd].  If a peer never
+ * arrives the wait expires and the next shady_synchronize returns SHADY_ERR_TIMEOUT. */
+int shady_attn_combine_p2p(shady_ctx *ctx, uint32_t world, uint32_t rank, uint32_t num_heads, uint32_t head_dim,
+                           uint32_t epoch, void *const *d_peer_table, const float *d_records, void *d_out,
+                           uint32_t out_dtype, const float *d_gate);
+
 /* No counterpart in the reference.  The same decode as shady_attn_decode for callers that cannot
  * hand over a workspace: a server that gave all device memory to its KV-cache arena at start-up, or
  * a decode loop that cannot take the device-wide stall of an allocation.  The arrival counters and

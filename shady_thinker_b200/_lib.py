@@ -20,7 +20,8 @@ EXPORTS = [
     "shady_buffer_create", "shady_buffer_free", "shady_buffer_write", "shady_buffer_read", "shady_buffer_copy",
     "shady_flush", "shady_synchronize", "shady_kv_append_rope", "shady_decode_workspace_size", "shady_decode_workspace_init",
     "shady_attn_decode", "shady_attn_decode_static", "shady_attn_decode_shard", "shady_attn_decode_partials", "shady_attn_reduce", "shady_attn_prefill",
-    "shady_sigmoid_mul", "shady_fill_randn",
+    "shady_sigmoid_mul", "shady_fill_randn", "shady_ipc_export", "shady_ipc_open", "shady_ipc_close",
+    "shady_combine_p2p_buffer_size", "shady_attn_combine_p2p",
 ]
 
 
@@ -97,6 +98,12 @@ def load() -> C.CDLL:
     L.shady_attn_reduce.argtypes = [vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64, f32p, vp,
                                     C.c_uint32, f32p]
     L.shady_attn_prefill.argtypes = [vp, C.POINTER(PrefillParams), vp, C.POINTER(KvCache), vp]
+    L.shady_ipc_export.argtypes = [vp, vp, C.c_char_p]
+    L.shady_ipc_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
+    L.shady_ipc_close.argtypes = [vp, vp]
+    L.shady_combine_p2p_buffer_size.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(sz)]
+    L.shady_attn_combine_p2p.argtypes = [vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp, f32p, vp,
+                                         C.c_uint32, f32p]
     L.shady_sigmoid_mul.argtypes = [vp, f32p, f32p, C.c_uint32]
     L.shady_fill_randn.argtypes = [vp, vp, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint64]
     for name in EXPORTS:

@@ -1,6 +1,7 @@
 // extern "C" surface of libshady_attn.so: context, buffers and op entry points declared in
 // include/shady_attn.h.  No torch types, no exceptions across the boundary.
 #include <math.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -28,6 +29,10 @@ int launch_append(shady_ctx *, const shady_append_params *, const void *, void *
                   const shady_kv_cache *, const uint16_t *, const uint32_t *, const uint32_t *, const uint32_t *);
 int launch_prefill(shady_ctx *, const shady_prefill_params *, const void *, const shady_kv_cache *, void *);
 int prefill_status(shady_ctx *, int *);
+int p2p_status(shady_ctx *, int *);
+unsigned long long p2p_buffer_bytes(uint32_t world, uint32_t nh, uint32_t hd);
+int launch_combine_p2p(shady_ctx *, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, void *const *, const float *, void *,
+                       uint32_t, const float *);
 
 // ---- counter-based N(0,1): the device twin of oracle_randn_at ---------------------------
 __host__ __device__ inline unsigned long long mix64(unsigned long long z) {
@@ -146,8 +151,10 @@ int shady_flush(shady_ctx *ctx) {
 int shady_synchronize(shady_ctx *ctx) {
     CTX_ENTER(ctx);
     SHADY_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
-    int code = 0;
-    return prefill_status(ctx, &code);  // SHADY_ERR_TIMEOUT if a bounded device-side wait gave up
+    int code = 0;   // SHADY_ERR_TIMEOUT if a bounded device-side wait gave up
+    const int rc = prefill_status(ctx, &code);
+    if (rc != SHADY_OK) return rc;
+    return p2p_status(ctx, &code);
 }
 
 int shady_kv_append_rope(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,
@@ -213,6 +220,41 @@ int shady_attn_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void
                        void *d_out) {
     CTX_ENTER(ctx);
     return launch_prefill(ctx, p, d_q, cache, d_out);
+}
+
+int shady_ipc_export(shady_ctx *ctx, void *d_buf, unsigned char handle[64]) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, d_buf && handle, SHADY_ERR_BAD_ARG, "ipc_export: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    SHADY_CUDA_OK(ctx, cudaIpcGetMemHandle(&h, d_buf));
+    memcpy(handle, &h, 64);
+    return SHADY_OK;
+}
+int shady_ipc_open(shady_ctx *ctx, const unsigned char handle[64], void **d_peer) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, handle && d_peer, SHADY_ERR_BAD_ARG, "ipc_open: null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    *d_peer = nullptr;
+    SHADY_CUDA_OK(ctx, cudaIpcOpenMemHandle(d_peer, h, cudaIpcMemLazyEnablePeerAccess));
+    return SHADY_OK;
+}
+int shady_ipc_close(shady_ctx *ctx, void *d_peer) {
+    CTX_ENTER(ctx);
+    if (d_peer) SHADY_CUDA_OK(ctx, cudaIpcCloseMemHandle(d_peer));
+    return SHADY_OK;
+}
+int shady_combine_p2p_buffer_size(uint32_t world, uint32_t num_heads, uint32_t head_dim, size_t *bytes) {
+    if (!bytes || !world || !num_heads || !head_dim) return SHADY_ERR_BAD_ARG;
+    *bytes = (size_t)p2p_buffer_bytes(world, num_heads, head_dim);
+    return SHADY_OK;
+}
+int shady_attn_combine_p2p(shady_ctx *ctx, uint32_t world, uint32_t rank, uint32_t num_heads, uint32_t head_dim,
+                           uint32_t epoch, void *const *d_peer_table, const float *d_records, void *d_out,
+                           uint32_t out_dtype, const float *d_gate) {
+    CTX_ENTER(ctx);
+    return launch_combine_p2p(ctx, world, rank, num_heads, head_dim, epoch, d_peer_table, d_records, d_out, out_dtype, d_gate);
 }
 
 int shady_sigmoid_mul(shady_ctx *ctx, float *d_x, const float *d_gate, uint32_t n) {

@@ -1,0 +1,145 @@
+// Cross-GPU merge of a row-sharded decode over NVLink peer memory — exchange and merge in ONE kernel.
+//
+// Each rank has decoded its rows of the sequence(s) into records [nh][hd+2] (output, log-sum-exp, unused;
+// the layout of gqa_attention_head.wgsl:112-123).  Instead of an NCCL all-gather followed by a merge kernel,
+// one CTA per query head
+//   1. stores this rank's record of its head into every peer's receive buffer with plain peer stores
+//      (no TMA, no multicast), fences at system scope and raises one flag per (rank, head) on every peer;
+//   2. waits — bounded — until the flags of all ranks for its head have arrived in its own buffer;
+//   3. merges the `world` records with the gqa_reduce.wgsl:33-64 math and writes the final rows.
+// Receive buffers and flags are double-buffered by the parity of the call's epoch: a rank can be at most one
+// call ahead of its slowest peer (it needs that peer's flags of the current call to finish), so the buffer it
+// overwrites is never the one a peer is still merging.  Every wait has an iteration limit; on expiry the kernel
+// records an error code and returns, and the next shady_synchronize reports SHADY_ERR_TIMEOUT.
+#include "common.cuh"
+
+namespace shady {
+
+constexpr uint32_t kP2PSpinLimit = 1u << 22;
+constexpr uint32_t kP2PMaxWorld = 16;
+
+static __device__ int g_p2p_error_word;
+static int *g_p2p_error[64] = {};
+
+struct P2PArgs {
+    char *const *peer_bases;   // device array [world]: every rank's shared buffer as mapped into this process
+    const float *rec;          // this rank's records [nh][hd+2]
+    void *out;
+    const float *gate;
+    int *error;
+    uint32_t rank, world, nh, hd, epoch, out_dtype;
+    unsigned long long flags_bytes;   // size of the flag region at the head of a shared buffer
+};
+
+// shared buffer: flags [2 parities][world][nh] u32 (padded to 256 B), then records [2][world][nh][hd+2] f32
+__host__ __device__ inline unsigned long long p2p_flags_bytes(uint32_t world, uint32_t nh) {
+    return ((unsigned long long)2 * world * nh * sizeof(uint32_t) + 255ull) / 256ull * 256ull;
+}
+unsigned long long p2p_buffer_bytes(uint32_t world, uint32_t nh, uint32_t hd) {
+    return p2p_flags_bytes(world, nh) + (unsigned long long)2 * world * nh * (hd + 2) * sizeof(float);
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(128) p2p_combine_kernel(const P2PArgs a) {
+    const uint32_t h = blockIdx.x, tid = threadIdx.x;
+    const uint32_t rs = a.hd + 2, par = a.epoch & 1u;
+    __shared__ float sm_lse[kP2PMaxWorld];
+    __shared__ int sm_fail;
+    if (tid == 0) sm_fail = 0;
+    // ---- 1. my record of head h -> every rank's receive slot [par][my rank][h] ----
+    const float *src = a.rec + (size_t)h * rs;
+    for (uint32_t r = 0; r < a.world; ++r) {
+        float *dst = reinterpret_cast<float *>(a.peer_bases[r] + a.flags_bytes) +
+                     (((size_t)par * a.world + a.rank) * a.nh + h) * rs;
+        for (uint32_t d = tid; d < rs; d += blockDim.x) dst[d] = src[d];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < a.world) {
+        uint32_t *flag = reinterpret_cast<uint32_t *>(a.peer_bases[tid]) + ((size_t)par * a.world + a.rank) * a.nh + h;
+        st_release_sys(flag, a.epoch);
+    }
+    // ---- 2. bounded wait for every rank's flag of this head in my own buffer ----
+    if (tid < a.world) {
+        const uint32_t *flag = reinterpret_cast<const uint32_t *>(a.peer_bases[a.rank]) + ((size_t)par * a.world + tid) * a.nh + h;
+        bool ok = false;
+        for (uint32_t i = 0; i < kP2PSpinLimit; ++i) {
+            if ((int32_t)(ld_acquire_sys(flag) - a.epoch) >= 0) { ok = true; break; }
+            if ((i & 4095u) == 4095u && *reinterpret_cast<volatile int *>(a.error)) break;   // somebody already gave up
+        }
+        if (!ok) {
+            sm_fail = 1;
+            atomicCAS(a.error, 0, 100 + (int)tid);
+        }
+    }
+    __syncthreads();
+    if (sm_fail) return;
+    // ---- 3. merge the world records of head h (gqa_reduce.wgsl:33-64; empty shards weigh nothing) ----
+    const float *mine = reinterpret_cast<const float *>(a.peer_bases[a.rank] + a.flags_bytes) + ((size_t)par * a.world * a.nh) * rs;
+    if (tid < a.world) sm_lse[tid] = __ldcg(mine + ((size_t)tid * a.nh + h) * rs + a.hd);
+    __syncthreads();
+    float gmax = -INFINITY;
+    for (uint32_t r = 0; r < a.world; ++r)
+        if (sm_lse[r] > -INFINITY) gmax = fmaxf(gmax, sm_lse[r]);
+    for (uint32_t d = tid; d < a.hd; d += blockDim.x) {
+        float acc = 0.f, wsum = 0.f;
+        for (uint32_t r = 0; r < a.world; ++r) {
+            const float l = sm_lse[r];
+            if (!(l > -INFINITY)) continue;
+            const float w = expf(l - gmax);
+            acc += w * __ldcg(mine + ((size_t)r * a.nh + h) * rs + d);
+            wsum += w;
+        }
+        float val = wsum > 0.f ? acc / wsum : 0.f;
+        const size_t oi = (size_t)h * a.hd + d;
+        if (a.gate) val *= sigmoidf_ref(a.gate[oi]);
+        store_from_f32(a.out, oi, a.out_dtype, val);
+    }
+}
+
+int launch_combine_p2p(shady_ctx *ctx, uint32_t world, uint32_t rank, uint32_t nh, uint32_t hd, uint32_t epoch,
+                       void *const *d_peer_table, const float *d_rec, void *d_out, uint32_t out_dtype, const float *d_gate) {
+    SHADY_REQUIRE(ctx, d_peer_table && d_rec && d_out && nh && hd, SHADY_ERR_BAD_ARG, "combine_p2p: null or zero argument");
+    SHADY_REQUIRE(ctx, world >= 1 && world <= kP2PMaxWorld && rank < world, SHADY_ERR_BAD_ARG, "combine_p2p: bad world/rank");
+    SHADY_REQUIRE(ctx, epoch != 0, SHADY_ERR_BAD_ARG, "combine_p2p: epoch must start at 1 (flags start at 0)");
+    SHADY_REQUIRE(ctx, out_dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "combine_p2p: bad out dtype");
+    SHADY_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, SHADY_ERR_UNSUPPORTED, "combine_p2p: device ordinal out of range");
+    if (!g_p2p_error[ctx->device]) {
+        int *w = nullptr;
+        SHADY_CUDA_OK(ctx, cudaGetSymbolAddress(reinterpret_cast<void **>(&w), g_p2p_error_word));
+        SHADY_CUDA_OK(ctx, cudaMemsetAsync(w, 0, sizeof(int), ctx->stream));
+        g_p2p_error[ctx->device] = w;
+    }
+    P2PArgs a{};
+    a.peer_bases = reinterpret_cast<char *const *>(d_peer_table);
+    a.rec = d_rec; a.out = d_out; a.gate = d_gate; a.error = g_p2p_error[ctx->device];
+    a.rank = rank; a.world = world; a.nh = nh; a.hd = hd; a.epoch = epoch; a.out_dtype = out_dtype;
+    a.flags_bytes = p2p_flags_bytes(world, nh);
+    p2p_combine_kernel<<<nh, 128, 0, ctx->stream>>>(a);
+    ctx->launches++;
+    SHADY_CUDA_OK(ctx, cudaGetLastError());
+    return SHADY_OK;
+}
+
+// Reads (and clears) the bounded-wait status of the combine kernel; the stream must be idle.
+int p2p_status(shady_ctx *ctx, int *code) {
+    *code = 0;
+    if (ctx->device < 0 || ctx->device >= 64 || !g_p2p_error[ctx->device]) return SHADY_OK;
+    SHADY_CUDA_OK(ctx, cudaMemcpyAsync(code, g_p2p_error[ctx->device], sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    SHADY_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*code) {
+        SHADY_CUDA_OK(ctx, cudaMemsetAsync(g_p2p_error[ctx->device], 0, sizeof(int), ctx->stream));
+        return fail(ctx, SHADY_ERR_TIMEOUT, "combine_p2p: the flag of rank " + std::to_string(*code - 100) + " did not arrive in time");
+    }
+    return SHADY_OK;
+}
+
+}  // namespace shady

@@ -1,0 +1,65 @@
+"""Row-sharded decode of one sequence across the GPUs of a box with the merge done over NVLink peer memory.
+
+``ShardCombiner`` owns this rank's exchange buffer, shares it with the other ranks (CUDA IPC handles travel
+through ``torch.distributed`` object collectives — host plumbing only) and launches the fused exchange+merge
+kernel (``shady_attn_combine_p2p``).  The reference has no counterpart (it is single-device).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from .gpu import Buffer, GpuContext, _addr
+
+
+class ShardCombiner:
+    def __init__(self, gpu: GpuContext, *, rank: int, world: int, num_heads: int, head_dim: int, group=None):
+        self.gpu, self.rank, self.world, self.nh, self.hd = gpu, rank, world, num_heads, head_dim
+        L = gpu._L
+        n = C.c_size_t()
+        st = L.shady_combine_p2p_buffer_size(world, num_heads, head_dim, C.byref(n))
+        if st != _lib.OK:
+            raise _lib.ShadyError(st, "combine_p2p_buffer_size")
+        self.bytes = n.value
+        self.buf = gpu.create_storage_buffer("p2p_exchange", self.bytes)
+        gpu.write_buffer(self.buf, 0, bytes(self.bytes))          # flags start at zero
+        gpu.synchronize()
+        self._opened: list[int] = []
+        ptrs = [0] * world
+        ptrs[rank] = self.buf.ptr
+        if world > 1:
+            import torch.distributed as dist
+            h = C.create_string_buffer(64)
+            gpu._check(L.shady_ipc_export(gpu.handle, C.c_void_p(self.buf.ptr), h))
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(h.raw), group=group)
+            for r in range(world):
+                if r == rank:
+                    continue
+                p = C.c_void_p()
+                gpu._check(L.shady_ipc_open(gpu.handle, handles[r], C.byref(p)))
+                ptrs[r] = p.value
+                self._opened.append(p.value)
+            dist.barrier(group=group)                              # every buffer is zeroed and mapped everywhere
+        self.table = gpu.upload_buffer("p2p_peer_table", np.asarray(ptrs, dtype=np.uint64).tobytes())
+        self.epoch = 0
+
+    def combine(self, records, out, out_dtype: int = _lib.F32, gate=None) -> None:
+        """records: this rank's [nh][hd+2] f32 (``ops.attn_decode_shard``); out: [nh][hd].  Every rank must call
+        this the same number of times."""
+        self.epoch += 1
+        g = self.gpu
+        g._check(g._L.shady_attn_combine_p2p(g.handle, self.world, self.rank, self.nh, self.hd, self.epoch,
+                                             C.c_void_p(self.table.ptr), _addr(records), _addr(out), out_dtype,
+                                             _addr(gate) or None))
+
+    def close(self, group=None) -> None:
+        if self.world > 1:
+            import torch.distributed as dist
+            self.gpu.synchronize()
+            dist.barrier(group=group)                              # nobody still writes into a peer's buffer
+        for p in self._opened:
+            self.gpu._L.shady_ipc_close(self.gpu.handle, C.c_void_p(p))
+        self._opened.clear()
