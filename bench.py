@@ -281,9 +281,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         e0.record(stream)
         for i in range(args.steps):
             d = sets[i % N_SETS]
-            d.append()
             ev_a[i].record(stream)
-            d.attend()
+            d.step()            # one fused launch: RoPE + cache append + split-KV decode + merge
             ev_b[i].record(stream)
         e1.record(stream)
         barrier()
@@ -335,7 +334,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": (TRAFFIC_PER_ALGO_BYTE * step_bytes) if TRAFFIC_PER_ALGO_BYTE else None,
                          "peak_source": f"{peak_src} (copy bandwidth)",
-                         "kernel": "decode16_kernel<half,128> + its split merge, per attend call",
+                         "kernel": "decode16_kernel<half,128> with the fused append and split merge (the whole step is this one launch)",
                          "algorithmic_bytes_per_launch": step_bytes, "avg_launch_ms": attend_ms},
             "e2e": {"value": all_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": d0.in_bytes, "d2h_bytes_per_step": d0.out_bytes, "steps": e2e_steps,

@@ -181,6 +181,19 @@ int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *
                       const uint32_t *seq_lens_host, void *d_out, float *d_lse, const float *d_gate,
                       void *d_workspace, size_t workspace_bytes);
 
+/* Append and attend in ONE launch — the three calls of a self-attention layer (model.rs:723-725:
+ * fused_split_qknorm_kvstore, gqa_attention, sigmoid_mul_gate) for a batch of sequences with 16-bit caches.
+ * Q is normed/rotated while it is staged; the CTA that owns the tail of a sequence norms/rotates the new K row,
+ * stores it and the V row at row seq_len-1 of the cache, then streams them with the rest.  `ap` describes the
+ * projections as in shady_kv_append_rope (tokens_per_seq must be 1, interleaved RoPE, one position per token:
+ * the position is seq_len-1); with ap->has_gate the output is multiplied by sigmoid(gate) from q_proj_full.
+ * d_seq_lens counts the new token, as in shady_attn_decode.  Neither q_out nor q_gate nor k_proj is written. */
+int shady_attn_decode_append(shady_ctx *ctx, const shady_append_params *ap, const shady_decode_params *p,
+                             const void *d_q_proj_full, const void *d_k_proj, const void *d_v_proj,
+                             const uint16_t *d_qk_norm_bf16, const shady_kv_cache *cache, const uint32_t *d_seq_lens,
+                             const uint32_t *seq_lens_host, void *d_out, float *d_lse, void *d_workspace,
+                             size_t workspace_bytes);
+
 /* One shard of a sequence-split decode (rows of one sequence spread over several GPUs): the same
  * kernels as shady_attn_decode, but the result is written as records d_records[seq][nh][hd+2] in the
  * layout of the reference's partials ([hd] = log-sum-exp, gqa_attention_head.wgsl:112-123), ready to be

@@ -19,7 +19,7 @@ EXPORTS = [
     "shady_ctx_create", "shady_ctx_destroy", "shady_last_error", "shady_ctx_stream", "shady_ctx_launch_count",
     "shady_buffer_create", "shady_buffer_free", "shady_buffer_write", "shady_buffer_read", "shady_buffer_copy",
     "shady_flush", "shady_synchronize", "shady_kv_append_rope", "shady_decode_workspace_size", "shady_decode_workspace_init",
-    "shady_attn_decode", "shady_attn_decode_static", "shady_attn_decode_shard", "shady_attn_decode_partials", "shady_attn_reduce", "shady_attn_prefill",
+    "shady_attn_decode", "shady_attn_decode_static", "shady_attn_decode_shard", "shady_attn_decode_append", "shady_attn_decode_partials", "shady_attn_reduce", "shady_attn_prefill",
     "shady_sigmoid_mul", "shady_fill_randn", "shady_ipc_export", "shady_ipc_open", "shady_ipc_close",
     "shady_combine_p2p_buffer_size", "shady_attn_combine_p2p",
 ]
@@ -92,6 +92,8 @@ def load() -> C.CDLL:
                                     C.POINTER(C.c_uint32), vp, f32p, f32p, vp, sz]
     L.shady_attn_decode_static.argtypes = [vp, C.POINTER(DecodeParams), vp, C.POINTER(KvCache), u32p,
                                            C.POINTER(C.c_uint32), vp, f32p, f32p]
+    L.shady_attn_decode_append.argtypes = [vp, C.POINTER(AppendParams), C.POINTER(DecodeParams), vp, vp, vp, vp,
+                                           C.POINTER(KvCache), u32p, C.POINTER(C.c_uint32), vp, f32p, vp, sz]
     L.shady_attn_decode_shard.argtypes = [vp, C.POINTER(DecodeParams), vp, C.POINTER(KvCache), u32p,
                                           C.POINTER(C.c_uint32), f32p, vp, sz]
     L.shady_attn_decode_partials.argtypes = [vp, C.POINTER(DecodeParams), vp, C.POINTER(KvCache), u32p, f32p]

@@ -10,6 +10,7 @@ API; host buffers passed to :meth:`step_from_host` should be pinned for asynchro
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -31,6 +32,7 @@ class BatchedDecoder:
         self.theta, self.rd = rope_theta, head_dim if rotary_dim is None else rotary_dim
         self.interleaved, self.eps, self.has_gate = interleaved, eps, has_gate
         self.num_layers, self.num_splits = num_layers, num_splits
+        self.fused = not os.environ.get("SHADY_NO_FUSED_APPEND") and kv_dtype != F32 and interleaved and (kv_dtype if act_dtype is None else act_dtype) in (F32, kv_dtype)
         caps = np.asarray(capacities, dtype=np.int64)
         assert caps.shape == (num_seqs,)
         row = num_kv_heads * head_dim
@@ -93,9 +95,21 @@ class BatchedDecoder:
                         out_dtype=self.act_dtype, gate=self.q_gate, workspace=self.ws, workspace_bytes=self.ws_bytes)
 
     def step(self, layer: int = 0) -> None:
-        """Device-resident step: activations already in q_in/k_in/v_in."""
-        self.append(layer)
-        self.attend(layer)
+        """Device-resident step: activations already in q_in/k_in/v_in.  16-bit caches take the single fused
+        launch (append + attend + gate); fp32 caches the reference's sequence of calls."""
+        if self.fused:
+            self.step_fused(layer)
+        else:
+            self.append(layer)
+            self.attend(layer)
+
+    def step_fused(self, layer: int = 0) -> None:
+        ops.attn_decode_append(self.gpu, q_proj_full=self.q_in, k_proj=self.k_in, v_proj=self.v_in,
+                               cache=self.views[layer], seq_lens=self.lens, out=self.out, num_heads=self.nh,
+                               num_kv_heads=self.nkv, head_dim=self.hd, rope_theta=self.theta, rotary_dim=self.rd,
+                               num_seqs=self.S, eps=self.eps, in_dtype=self.act_dtype, out_dtype=self.act_dtype,
+                               has_gate=self.has_gate, seq_lens_host=self.lens_after, workspace=self.ws,
+                               workspace_bytes=self.ws_bytes, num_splits=self.num_splits)
 
     def step_from_host(self, q_host: int, k_host: int, v_host: int, out_host: int, layer: int = 0) -> None:
         """Full step with host buffers (addresses of pinned memory): H2D activations, append, attend,

@@ -19,7 +19,12 @@ int fail(shady_ctx *ctx, int code, const std::string &msg) {
 size_t decode_workspace_bytes(const shady_decode_params *p);
 int init_decode_workspace(shady_ctx *, const shady_decode_params *, void *, size_t);
 int launch_decode(shady_ctx *, const shady_decode_params *, const void *, const shady_kv_cache *, const uint32_t *,
-                  const uint32_t *, void *, float *, const float *, void *, size_t, float *, float *);
+                  const uint32_t *, void *, float *, const float *, void *, size_t, float *, float *, const struct FusedAppendIn *);
+struct FusedAppendIn {
+    const shady_append_params *ap;
+    const void *q_full, *k_proj, *v_proj;
+    const uint16_t *norm_w;
+};
 int launch_decode_static(shady_ctx *, const shady_decode_params *, const void *, const shady_kv_cache *, const uint32_t *,
                          const uint32_t *, void *, float *, const float *);
 int launch_reduce(shady_ctx *, uint32_t, uint32_t, uint32_t, uint64_t, uint64_t, const float *, void *, uint32_t,
@@ -182,7 +187,7 @@ int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *
                       const float *d_gate, void *d_workspace, size_t workspace_bytes) {
     CTX_ENTER(ctx);
     return launch_decode(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, d_out, d_lse, d_gate, d_workspace,
-                         workspace_bytes, nullptr, nullptr);
+                         workspace_bytes, nullptr, nullptr, nullptr);
 }
 
 int shady_attn_decode_static(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
@@ -192,20 +197,31 @@ int shady_attn_decode_static(shady_ctx *ctx, const shady_decode_params *p, const
     return launch_decode_static(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, d_out, d_lse, d_gate);
 }
 
+int shady_attn_decode_append(shady_ctx *ctx, const shady_append_params *ap, const shady_decode_params *p,
+                             const void *d_q_proj_full, const void *d_k_proj, const void *d_v_proj,
+                             const uint16_t *d_qk_norm_bf16, const shady_kv_cache *cache, const uint32_t *d_seq_lens,
+                             const uint32_t *seq_lens_host, void *d_out, float *d_lse, void *d_workspace,
+                             size_t workspace_bytes) {
+    CTX_ENTER(ctx);
+    FusedAppendIn fa{ap, d_q_proj_full, d_k_proj, d_v_proj, d_qk_norm_bf16};
+    return launch_decode(ctx, p, nullptr, cache, d_seq_lens, seq_lens_host, d_out, d_lse, nullptr, d_workspace,
+                         workspace_bytes, nullptr, nullptr, &fa);
+}
+
 int shady_attn_decode_shard(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
                             const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, float *d_records, void *d_workspace,
                             size_t workspace_bytes) {
     CTX_ENTER(ctx);
     SHADY_REQUIRE(ctx, d_records, SHADY_ERR_BAD_ARG, "decode_shard: null output");
     return launch_decode(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, nullptr, nullptr, nullptr, d_workspace,
-                         workspace_bytes, nullptr, d_records);
+                         workspace_bytes, nullptr, d_records, nullptr);
 }
 
 int shady_attn_decode_partials(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
                                const shady_kv_cache *cache, const uint32_t *d_seq_lens, float *d_partials) {
     CTX_ENTER(ctx);
     SHADY_REQUIRE(ctx, d_partials, SHADY_ERR_BAD_ARG, "decode_partials: null output");
-    return launch_decode(ctx, p, d_q, cache, d_seq_lens, nullptr, nullptr, nullptr, nullptr, nullptr, 0, d_partials, nullptr);
+    return launch_decode(ctx, p, d_q, cache, d_seq_lens, nullptr, nullptr, nullptr, nullptr, nullptr, 0, d_partials, nullptr, nullptr);
 }
 
 int shady_attn_reduce(shady_ctx *ctx, uint32_t head_dim, uint32_t num_splits, uint32_t num_heads, uint64_t split_stride,

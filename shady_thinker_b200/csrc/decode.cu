@@ -49,7 +49,44 @@ struct DecodeArgs {
     uint32_t out_row_stride;  // elements between consecutive head rows of `out` (hd, or hd+2 when out is a record buffer)
     uint32_t lse_stride;      // elements between consecutive entries of `lse` (1, or hd+2 inside a record buffer)
     float scale_log2;         // 1/sqrt(hd) * log2(e)
+    // fused append (16-bit caches): Q comes raw from the projection and is normed/rotated while it is staged, and
+    // the CTA that owns the tail of a sequence norms/rotates the new K row and writes it and the V row to the cache
+    // (fused_split_qknorm_kvstore.wgsl:106-230) before it streams them — one launch per layer instead of three.
+    uint32_t fuse_append;
+    const void *ap_q, *ap_k, *ap_v;   // q_proj_full [seq][nh][(1+gate)*hd], k_proj / v_proj [seq][nkv][hd]
+    const uint16_t *ap_norm_w;        // bf16 bits q[hd] then k[hd], or NULL
+    uint32_t ap_in_dtype, ap_has_gate, ap_rd;
+    float ap_eps;
+    float ap_inv_freq[128];
 };
+
+// 8 consecutive elements (16-byte aligned for 16-bit types, 32-byte for f32) of a buffer of run-time dtype
+__device__ __forceinline__ void load8_as_f32(const void *p, size_t i, uint32_t dt, float (&v)[8]) {
+    if (dt == SHADY_F32) {
+        const float4 x = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p) + i);
+        const float4 y = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p) + i + 4);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+    } else {
+        const uint4 u = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p) + i);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (dt == SHADY_F16) {
+                const __half2 h = *reinterpret_cast<const __half2 *>(&w[k]);
+                v[2 * k] = __low2float(h); v[2 * k + 1] = __high2float(h);
+            } else {
+                v[2 * k] = __uint_as_float(w[k] << 16); v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ float gate_value(const DecodeArgs &a, uint32_t seq, uint32_t head, uint32_t d) {
+    if (a.fuse_append)   // the gate is the second half of the token's q_proj_full row (wgsl:122-135)
+        return load_as_f32(a.ap_q, ((size_t)seq * a.nh + head) * 2 * a.hd + a.hd + d, a.ap_in_dtype);
+    return a.gate[((size_t)seq * a.nh + head) * a.hd + d];
+}
+__device__ __forceinline__ bool has_gate(const DecodeArgs &a) { return a.fuse_append ? a.ap_has_gate != 0 : a.gate != nullptr; }
 
 // ---- balanced ("stream-K") partition of the batch -------------------------------------------
 // All sequences are laid end to end on a line of 16-position row-blocks; span c owns blocks
@@ -174,9 +211,8 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
         const float lse = L > 0.f ? logf(L) + M * kLn2 : -INFINITY;
         const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
         if (direct) {
-            const size_t gi = ((size_t)p.seq * a.nh + head) * HD + d;                 // gate index
                 const size_t oi = ((size_t)p.seq * a.nh + head) * a.out_row_stride + d;
-            if (a.gate) val *= sigmoidf_ref(a.gate[gi]);
+            if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, p.seq, head, d));
             store_from_f32(a.out, oi, a.out_dtype, val);
             if (d == 0 && a.lse) a.lse[((size_t)p.seq * a.nh + head) * a.lse_stride] = lse;
         } else {
@@ -280,9 +316,8 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
                 const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
                 const float wsum = sm_wsum[hr];
                 float val = wsum > 0.f ? acc[k] / wsum : 0.f;
-                const size_t gi = ((size_t)p.seq * a.nh + head) * HD + d;                 // gate index
-                const size_t oi = ((size_t)p.seq * a.nh + head) * a.out_row_stride + d;
-                if (a.gate) val *= sigmoidf_ref(a.gate[gi]);
+                    const size_t oi = ((size_t)p.seq * a.nh + head) * a.out_row_stride + d;
+                if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, p.seq, head, d));
                 store_from_f32(a.out, oi, a.out_dtype, val);
                 if (d == 0 && a.lse) a.lse[((size_t)p.seq * a.nh + head) * a.lse_stride] = wsum > 0.f ? sm_gmax[hr] + logf(wsum) : -INFINITY;
             }
@@ -342,7 +377,7 @@ template <int HD, int NW, int STAGES, int KPC> struct Decode16Smem {
     static constexpr int kWarpBytes = STAGES * kTileBytes;       // ring of STAGES tile slots; K and V tiles alternate in it
     static constexpr int kQTile = 16 * kRowBytes;                // Q rows of one kv head
     static constexpr int kQBytes = KPC * kQTile;
-    static constexpr int kStatBytes = 2 * NW * 16 * 4;           // merge m and l
+    static constexpr int kStatBytes = (2 * NW * 16 * 4 > HD * 4) ? 2 * NW * 16 * 4 : HD * 4;   // merge m and l; cos/sin table of the fused append
     static constexpr int kTotal = kQBytes + NW * kWarpBytes + kStatBytes + 32;
     static_assert(kWarpBytes >= 16 * HD * 4, "merge tile must fit in the warp's pipeline memory");
 };
@@ -366,7 +401,7 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
     unsigned char *sm_pipe = smem + S::kQBytes;
     float *sm_m = reinterpret_cast<float *>(smem + S::kQBytes + NW * S::kWarpBytes);
     float *sm_l = sm_m + NW * 16;
-    uint32_t *sm_item = reinterpret_cast<uint32_t *>(sm_l + NW * 16);  // 8 words
+    uint32_t *sm_item = reinterpret_cast<uint32_t *>(smem + S::kQBytes + NW * S::kWarpBytes + S::kStatBytes);  // 8 words
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // blockIdx.x = (work * KG + kg) * gz + z, KG = nkv / KPC groups of kv heads
@@ -402,6 +437,24 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
         // The pipeline moves single tiles: item 2i is the K tile of the warp's i-th block, item 2i+1 its V tile,
         // item t lives in slot t % STAGES, and STAGES-1 items are in flight while one is being consumed.
         const uint32_t n_items = 2 * my_n;
+        constexpr int NIT = (2 * CH + 31) / 32;   // K and V chunks per lane
+        const bool tail = a.fuse_append && p.L > 0 && p.end == p.L;
+        const bool owner = tail && ((nblk - 1) % WPK == sub) && KPC == 1;
+        uint4 newrow[NIT];
+        // put the kept row into the tile that was just fetched (the copy in flight may predate the store above)
+        auto patch_tile = [&](uint32_t tile_addr, uint32_t pos0, uint32_t want_v) {
+            const uint32_t r = p.L - 1 - pos0;
+#pragma unroll
+            for (int it = 0; it < NIT; ++it) {
+                const uint32_t tt = lane + 32 * it;
+                if (tt < 2 * CH && tt / CH == want_v) {
+                    const uint32_t c = tt % CH;
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_addr + r * S::kRowBytes + ((c ^ (r & 7)) << 4)),
+                                 "r"(newrow[it].x), "r"(newrow[it].y), "r"(newrow[it].z), "r"(newrow[it].w) : "memory");
+                }
+            }
+            __syncwarp();
+        };
         auto issue = [&](uint32_t t) {
             const uint32_t pos0 = start + (sub + (t >> 1) * WPK) * kBlk;
             const uint32_t st = warp_smem + (t % STAGES) * S::kTileBytes;
@@ -421,7 +474,90 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             if ((uint32_t)s < n_items) issue(s);
             cp_async_commit();
         }
+        // ---- fused append: the warp that will process the block holding row L-1 builds that row of K (norm + RoPE)
+        //      and of V, stores both in the cache for later steps and keeps them to patch its shared-memory tiles ----
+        if (owner) {
+            const uint32_t pos = p.L - 1;
+#pragma unroll
+            for (int it = 0; it < NIT; ++it) {
+                const uint32_t tt = lane + 32 * it;
+                const bool act = tt < 2 * CH;
+                const uint32_t is_v = act ? tt / CH : 1u, c = tt % CH;
+                float v8[8];
+                load8_as_f32(is_v ? a.ap_v : a.ap_k, ((size_t)p.seq * a.nkv + kvh) * HD + c * 8, a.ap_in_dtype, v8);
+                if (a.ap_norm_w && it == 0) {   // K chunks sit in item set 0 (all lanes, or the first CH of them)
+                    float ssq = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ssq += v8[e] * v8[e];
+#pragma unroll
+                    for (int o = CH / 2; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o, CH);
+                    if (!is_v) {
+                        const float rms = 1.0f / sqrtf(ssq / (float)HD + a.ap_eps);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            v8[e] = v8[e] * rms * (1.0f + __uint_as_float(((uint32_t)a.ap_norm_w[HD + c * 8 + e]) << 16));
+                    }
+                }
+                if (!is_v) {
+#pragma unroll
+                    for (int k2 = 0; k2 < 4; ++k2) {
+                        const uint32_t i2 = c * 4 + k2;
+                        if (i2 < a.ap_rd / 2) {
+                            float sn, cs;
+                            sincosf((float)pos * a.ap_inv_freq[i2], &sn, &cs);
+                            const float x = v8[2 * k2], y = v8[2 * k2 + 1];
+                            v8[2 * k2] = x * cs - y * sn;
+                            v8[2 * k2 + 1] = y * cs + x * sn;
+                        }
+                    }
+                }
+                newrow[it].x = pack2<T>(v8[0], v8[1]); newrow[it].y = pack2<T>(v8[2], v8[3]);
+                newrow[it].z = pack2<T>(v8[4], v8[5]); newrow[it].w = pack2<T>(v8[6], v8[7]);
+                if (act)
+                    *reinterpret_cast<uint4 *>(const_cast<char *>(is_v ? vbase : kbase) + (size_t)pos * pos_stride + c * 16) = newrow[it];
+            }
+        }
         // stage Q of the CTA's kv heads (rows >= rows_valid are zero) as T, swizzled
+        if (a.fuse_append) {
+            // raw Q row -> RMSNorm(1+w) -> RoPE at position L-1 (wgsl:126-166); CH consecutive threads share a row.
+            // cos/sin of the rotary pairs are the same for all rows: one table per piece in the merge-statistics area
+            const uint32_t pos = p.L ? p.L - 1 : 0;
+            float2 *sm_cs = reinterpret_cast<float2 *>(sm_m);   // HD/2 pairs; sm_m/sm_l are free until the piece ends
+            for (uint32_t i2 = tid; i2 < HD / 2; i2 += NW * 32) {
+                float sn = 0.f, cs = 1.f;
+                if (i2 < a.ap_rd / 2) sincosf((float)pos * a.ap_inv_freq[i2], &sn, &cs);
+                sm_cs[i2] = make_float2(cs, sn);
+            }
+            __syncthreads();
+            for (uint32_t idx = tid; idx < KPC * 16 * CH; idx += NW * 32) {
+                const uint32_t c = idx % CH, r = (idx / CH) % 16, k = idx / (CH * 16);
+                float v8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (r < rows_valid) {
+                    const size_t e0 = ((size_t)p.seq * a.nh + (kg * KPC + k) * a.G + row0 + r) * (a.ap_has_gate ? 2 * HD : HD) + c * 8;
+                    load8_as_f32(a.ap_q, e0, a.ap_in_dtype, v8);
+                }
+                if (a.ap_norm_w) {
+                    float ssq = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ssq += v8[e] * v8[e];
+#pragma unroll
+                    for (int o = CH / 2; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o, CH);
+                    const float rms = 1.0f / sqrtf(ssq / (float)HD + a.ap_eps);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v8[e] = v8[e] * rms * (1.0f + __uint_as_float(((uint32_t)a.ap_norm_w[c * 8 + e]) << 16));
+                }
+#pragma unroll
+                for (int k2 = 0; k2 < 4; ++k2) {
+                    const float2 t2 = sm_cs[c * 4 + k2];   // (1, 0) beyond the rotary dims
+                    const float x = v8[2 * k2], y = v8[2 * k2 + 1];
+                    v8[2 * k2] = x * t2.x - y * t2.y;
+                    v8[2 * k2 + 1] = y * t2.x + x * t2.y;
+                }
+                uint4 v;
+                v.x = pack2<T>(v8[0], v8[1]); v.y = pack2<T>(v8[2], v8[3]); v.z = pack2<T>(v8[4], v8[5]); v.w = pack2<T>(v8[6], v8[7]);
+                *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kRowBytes + ((c ^ (r & 7)) << 4)) = v;
+            }
+        } else
         for (uint32_t idx = tid; idx < KPC * 16 * CH; idx += NW * 32) {
             const uint32_t c = idx % CH, r = (idx / CH) % 16, k = idx / (CH * 16);
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -462,6 +598,7 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
 
             const uint32_t st = warp_smem + ((2 * i) % STAGES) * S::kTileBytes;
             const uint32_t pos0 = start + (sub + i * WPK) * kBlk;
+            if (owner && i == my_n - 1) patch_tile(st, pos0, 0u);
             // ---- S = Q K^T : heads x 16 positions ----
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -519,6 +656,7 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             if (2 * i + STAGES < n_items) issue(2 * i + STAGES);   // into the slot of the K tile just consumed
             cp_async_commit();
             const uint32_t stv = warp_smem + ((2 * i + 1) % STAGES) * S::kTileBytes;
+            if (owner && i == my_n - 1) patch_tile(stv, pos0, 1u);
 #pragma unroll
             for (int jn = 0; jn < HD / 8; jn += 2) {
                 uint32_t vb[4];
@@ -870,10 +1008,18 @@ size_t decode_workspace_bytes(const shady_decode_params *p) {
     return counters_bytes(p) + recs * rec;
 }
 
+// Inputs of the fused append (NULL = plain decode).
+struct FusedAppendIn {
+    const shady_append_params *ap;
+    const void *q_full, *k_proj, *v_proj;
+    const uint16_t *norm_w;
+};
+
 int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
                   const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, void *d_out, float *d_lse,
-                  const float *d_gate, void *d_ws, size_t ws_bytes, float *d_force_partials, float *d_shard_records) {
-    SHADY_REQUIRE(ctx, p && d_q && cache && d_seq_lens, SHADY_ERR_BAD_ARG, "decode: null argument");
+                  const float *d_gate, void *d_ws, size_t ws_bytes, float *d_force_partials, float *d_shard_records,
+                  const FusedAppendIn *fa) {
+    SHADY_REQUIRE(ctx, p && (d_q || fa) && cache && d_seq_lens, SHADY_ERR_BAD_ARG, "decode: null argument");
     SHADY_REQUIRE(ctx, d_out || d_force_partials || d_shard_records, SHADY_ERR_BAD_ARG, "decode: null output");
     SHADY_REQUIRE(ctx, p->num_seqs > 0 && p->num_kv_heads > 0 && p->heads_per_kv > 0, SHADY_ERR_BAD_ARG,
                   "decode: zero-sized problem");
@@ -908,13 +1054,31 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
         a.lse = d_shard_records + hd; a.lse_stride = hd + 2; a.gate = nullptr;
     }
     a.gz = head_groups(cache->dtype, p->heads_per_kv);
+    if (fa) {
+        const shady_append_params *ap = fa->ap;
+        SHADY_REQUIRE(ctx, ap && fa->q_full && fa->k_proj && fa->v_proj, SHADY_ERR_BAD_ARG, "decode_append: null argument");
+        SHADY_REQUIRE(ctx, !f32, SHADY_ERR_UNSUPPORTED, "decode_append: needs a 16-bit cache (use the two calls for fp32)");
+        SHADY_REQUIRE(ctx, ap->num_heads == p->num_q_heads && ap->num_kv_heads == p->num_kv_heads && ap->head_dim == hd &&
+                               ap->num_seqs == p->num_seqs && ap->tokens_per_seq == 1,
+                      SHADY_ERR_BAD_ARG, "decode_append: append and decode parameters disagree");
+        SHADY_REQUIRE(ctx, ap->interleaved && ap->rotary_dim <= hd && (ap->rotary_dim % 2) == 0 &&
+                               ap->s1_limit == ap->rotary_dim / 2 && ap->s2_limit == ap->rotary_dim / 2,
+                      SHADY_ERR_UNSUPPORTED, "decode_append: interleaved RoPE with one position per token only");
+        SHADY_REQUIRE(ctx, ap->in_dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "decode_append: bad input dtype");
+        a.fuse_append = 1;
+        a.ap_q = fa->q_full; a.ap_k = fa->k_proj; a.ap_v = fa->v_proj; a.ap_norm_w = fa->norm_w;
+        a.ap_in_dtype = ap->in_dtype; a.ap_has_gate = ap->has_gate; a.ap_rd = ap->rotary_dim; a.ap_eps = ap->eps;
+        for (uint32_t i = 0; i < ap->rotary_dim / 2; ++i)   // same libm call as the stand-alone append and the oracle
+            a.ap_inv_freq[i] = 1.0f / powf(ap->rope_theta, 2.0f * (float)i / (float)ap->rotary_dim);
+        a.gate = nullptr;
+    }
     const Variant16 var = variant16(hd, env_u32("SHADY_DECODE_VARIANT", 0));
     // One kv head per CTA measured fastest (sibling CTAs of the other kv heads run next to each other in
     // the grid and fetch the rest of each cache row); SHADY_DECODE_KPC packs more kv heads into a CTA.
     uint32_t kpc = 1u;
     {
         const uint32_t want = env_u32("SHADY_DECODE_KPC", 0);
-        if (!f32 && want && want <= kv_heads_per_cta(p->num_kv_heads, hd > 128 ? 4u : var.nw) && (want & (want - 1)) == 0) kpc = want;
+        if (!f32 && !fa && want && want <= kv_heads_per_cta(p->num_kv_heads, hd > 128 ? 4u : var.nw) && (want & (want - 1)) == 0) kpc = want;
     }
     const uint32_t kv_groups = p->num_kv_heads / kpc;
     uint32_t ctas_per_sm = env_u32("SHADY_DECODE_CTAS_PER_SM", f32 ? 4u : var.ctas_per_sm);

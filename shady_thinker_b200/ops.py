@@ -112,6 +112,25 @@ def attn_decode_static(gpu: GpuContext, *, q, cache: KvCacheView, seq_lens, out,
     del keep
 
 
+def attn_decode_append(gpu: GpuContext, *, q_proj_full, k_proj, v_proj, cache: KvCacheView, seq_lens, out,
+                       num_heads: int, num_kv_heads: int, head_dim: int, rope_theta: float, rotary_dim: int,
+                       num_seqs: int = 1, eps: float = 1e-6, qk_norm_bf16=None, in_dtype: int = F32,
+                       out_dtype: int = F32, has_gate: bool = True, seq_lens_host=None, lse=None, workspace=None,
+                       workspace_bytes: int = 0, num_splits: int = 0) -> None:
+    """One launch for append + attend (+ gate): ``seq_lens`` count the token being appended."""
+    ap = AppendParams(num_heads, num_kv_heads, head_dim, eps, rope_theta, rotary_dim, rotary_dim // 2, rotary_dim // 2,
+                      1, num_seqs, 1, in_dtype, in_dtype, int(has_gate), 0, 0)
+    p = DecodeParams(head_dim, num_kv_heads, num_heads, num_heads // num_kv_heads, num_splits, num_seqs, in_dtype,
+                     out_dtype)
+    c = cache.c_struct()
+    keep, hl = _host_lens(seq_lens_host)
+    gpu._check(gpu._L.shady_attn_decode_append(gpu.handle, C.byref(ap), C.byref(p), _addr(q_proj_full), _addr(k_proj),
+                                               _addr(v_proj), _addr(qk_norm_bf16) or None, C.byref(c), _addr(seq_lens),
+                                               hl, _addr(out), _addr(lse) or None, _addr(workspace) or None,
+                                               workspace_bytes))
+    del keep
+
+
 def attn_decode_shard(gpu: GpuContext, *, q, cache: KvCacheView, seq_lens, records, head_dim: int, num_kv_heads: int,
                       num_q_heads: int, num_seqs: int = 1, num_splits: int = 0, seq_lens_host=None, q_dtype: int = F32,
                       workspace=None, workspace_bytes: int = 0) -> None:

@@ -250,3 +250,54 @@ def test_decode_shard_records_merge_rank_major(gpu_ctx, oracle):
     gpu_ctx.synchronize()
     rh = to_host(rec)
     assert np.isneginf(rh[0, :, hd]).all() and not rh[0, :, :hd].any()
+
+
+@pytest.mark.parametrize("dt,in_dt,norm,gate,rd", [(F16, F16, False, False, 128), (BF16, F32, True, True, 32),
+                                                   (F16, F32, True, False, 64)])
+def test_fused_append_decode_equals_the_two_calls(gpu_ctx, oracle, dt, in_dt, norm, gate, rd):
+    """shady_attn_decode_append == shady_kv_append_rope followed by shady_attn_decode (+ gate), cache rows included."""
+    from _util import TORCH_DT
+    nh, nkv, hd = 32, 8, 128
+    lens = [1, 16, 17, 700, 2500, 33]                      # lengths INCLUDING the appended token
+    S = len(lens)
+    qmul = 2 if gate else 1
+    q_full = rounded(oracle, oracle.randn((S, nh, qmul * hd), 81, 1), in_dt)
+    k_new = rounded(oracle, oracle.randn((S, nkv, hd), 81, 2), in_dt)
+    v_new = rounded(oracle, oracle.randn((S, nkv, hd), 81, 3), in_dt)
+    w = oracle.bf16_bits(oracle.randn((2 * hd,), 81, 4) * np.float32(0.02)) if norm else None
+    d_w = torch.from_numpy(w.view(np.int16)).cuda() if norm else None
+    ks = [rounded(oracle, oracle.randn((L, nkv, hd), 81, 10 + i), dt) for i, L in enumerate(lens)]
+    vs = [rounded(oracle, oracle.randn((L, nkv, hd), 81, 50 + i), dt) for i, L in enumerate(lens)]
+    d_lens = torch.tensor(lens, dtype=torch.int32).cuda()
+    d_pos = torch.tensor([L - 1 for L in lens], dtype=torch.int32).cuda()
+    ws_n = ops.decode_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_splits=0, num_seqs=S)
+    ws = torch.zeros(ws_n, dtype=torch.uint8, device="cuda")
+    # --- reference: two calls ---
+    c1 = RaggedCache(ks, vs, dt)
+    d_q = torch.empty((S, nh, hd), dtype=TORCH_DT[in_dt], device="cuda")
+    d_g = torch.empty((S, nh, hd), device="cuda") if gate else None
+    ops.kv_append_rope(gpu_ctx, q_proj_full=to_dev(q_full, in_dt), k_proj=to_dev(k_new, in_dt), v_proj=to_dev(v_new, in_dt),
+                       q_out=d_q, q_gate=d_g, cache=c1.view, pos_start=d_pos, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                       rope_theta=1e6, rotary_dim=rd, qk_norm_bf16=d_w, num_seqs=S, in_dtype=in_dt, q_dtype=in_dt,
+                       has_gate=gate, write_k_back=False)
+    want = torch.empty((S, nh, hd), device="cuda")
+    ops.attn_decode(gpu_ctx, q=d_q, cache=c1.view, seq_lens=d_lens, out=want, head_dim=hd, num_kv_heads=nkv,
+                    num_q_heads=nh, num_seqs=S, num_splits=0, seq_lens_host=lens, q_dtype=in_dt, gate=d_g, workspace=ws,
+                    workspace_bytes=ws_n)
+    gpu_ctx.synchronize()
+    # --- fused: one call on a fresh copy of the caches ---
+    c2 = RaggedCache(ks, vs, dt)
+    got = torch.full((S, nh, hd), float("nan"), device="cuda")
+    ops.attn_decode_append(gpu_ctx, q_proj_full=to_dev(q_full, in_dt), k_proj=to_dev(k_new, in_dt),
+                           v_proj=to_dev(v_new, in_dt), cache=c2.view, seq_lens=d_lens, out=got, num_heads=nh,
+                           num_kv_heads=nkv, head_dim=hd, rope_theta=1e6, rotary_dim=rd, num_seqs=S, qk_norm_bf16=d_w,
+                           in_dtype=in_dt, has_gate=gate, seq_lens_host=lens, workspace=ws, workspace_bytes=ws_n)
+    gpu_ctx.synchronize()
+    for i, L in enumerate(lens):
+        ulp = 2.0 ** -10 if dt == F16 else 2.0 ** -7       # the two kernels may contract their FMAs differently
+        k1, k2 = to_host(c1.k[i])[L - 1], to_host(c2.k[i])[L - 1]
+        assert np.abs(k2 - k1).max() <= ulp * np.abs(k1).max(), (i, L)
+        np.testing.assert_array_equal(to_host(c2.v[i])[L - 1], to_host(c1.v[i])[L - 1])   # V is a pure copy
+        np.testing.assert_array_equal(to_host(c2.k[i])[:L - 1], ks[i][:L - 1])            # older rows untouched
+        # Q is rounded to the cache dtype when staged in both paths only if in_dt == dt; allow the 16-bit tolerance
+        assert rel_err(to_host(got)[i], to_host(want)[i]) <= RTOL_16, (i, L)
