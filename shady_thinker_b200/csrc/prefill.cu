@@ -5,9 +5,11 @@
 // one batched causal flash-attention pass over rows [0,T) of each sequence's cache.
 //
 // Shape of the kernel (head_dim 128, 16-bit Q/K/V/out, fp32 softmax statistics):
-//   * one CTA = 256 query rows of one (sequence, query head): two 128-row tiles that share every
-//     K/V tile; K/V tiles of 128 rows arrive through non-multicast 4-D TMA (128-byte swizzle) into
-//     a 2-stage ring, completion on mbarriers;
+//   * persistent CTAs (one per SM) walk a heaviest-first list of work items; an item = 256 query rows
+//     of one (sequence, query head): two 128-row tiles that share every K/V tile; K/V tiles of 128
+//     rows arrive through non-multicast 4-D TMA (128-byte swizzle) into a 2-stage ring, completion
+//     on mbarriers whose phases run on through the items, so loads and MMAs of the next item start
+//     while the softmax of the current one drains;
 //   * TMEM (512 columns): S0, S1 (fp32 scores of the two tiles) and O0, O1 (fp32 outputs).
 //     P overwrites the first 64 columns of its S as packed 16-bit and is the A operand of the
 //     second MMA straight from TMEM;
@@ -17,8 +19,8 @@
 //     tile while the other is in its softmax;
 //   * online softmax in the log2 domain with lazy rescaling: O is only rescaled when the running
 //     maximum grew by more than 2^8, so the TMEM round trip of O is rare;
-//   * causal structure: tile i of the CTA with row base q0 visits kv tiles 0..(q0+128i)/128 and
-//     masks only the last (diagonal) one; CTAs are launched heaviest first.
+//   * causal structure: tile i of the item with row base q0 visits kv tiles 0..(q0+128i)/128 and
+//     masks only the last (diagonal) one.
 // Every mbarrier wait is bounded: on expiry the kernel records an error code, skips the rest of
 // its work, releases TMEM and returns (the host reports SHADY_ERR_TIMEOUT).
 #include <cuda.h>
@@ -229,21 +231,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (*reinterpret_cast<volatile int *>(a.error)) return;   // an earlier CTA's wait expired: do not start
-    // heaviest (latest rows) first
-    // One CTA serves the G query heads of a KV group one after the other ("items"): they read the same K/V
-    // tiles, and chaining them lets the producer and the MMA issuer run ahead into the next head while the
-    // softmax warps finish the current one, so the pipeline fill/drain is paid once per CTA, not per head.
-    const uint32_t bk_count = a.B * a.nkv;
-    const uint32_t m = a.m_tiles - 1 - blockIdx.x / bk_count;
-    const uint32_t bk = blockIdx.x % bk_count;
-    const uint32_t b = bk / a.nkv, kvh = bk % a.nkv;
-    const uint32_t items = a.G;
-    const uint32_t q0 = m * 256;
-    const uint32_t n_tiles[2] = {2 * m + 1, (q0 + kPM < a.T) ? 2 * m + 2 : 0u};   // kv tiles of the two query tiles
-    const uint32_t nkv = n_tiles[1] ? n_tiles[1] : n_tiles[0];
+    // Persistent CTAs: work items are (256-row block, sequence, query head), ordered heaviest (latest rows) first;
+    // CTA c takes items c, c + grid, c + 2*grid, ... so every CTA gets about one item of each weight, and because
+    // all roles walk the same list with running barrier phases, the producer and the MMA issuer run ahead into the
+    // next item while the softmax warps finish the current one (pipeline fill/drain overlap instead of adding up).
+    struct Item {
+        uint32_t b, h, kvh, q0, n[2], nkv;
+    };
+    const uint32_t bh_count = a.B * a.nh;
+    const uint32_t total_items = a.m_tiles * bh_count;
+    auto get_item = [&](uint32_t w) {
+        Item it;
+        const uint32_t m = a.m_tiles - 1 - w / bh_count, bh = w % bh_count;
+        it.b = bh / a.nh; it.h = bh % a.nh; it.kvh = it.h / a.G; it.q0 = m * 256;
+        it.n[0] = 2 * m + 1;                                   // kv tiles of the two 128-row query tiles
+        it.n[1] = (it.q0 + kPM < a.T) ? 2 * m + 2 : 0u;
+        it.nkv = it.n[1] ? it.n[1] : it.n[0];
+        return it;
+    };
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
-    if (warp == 8 && lane == 0) {   // the producer sets the barriers up and starts the first loads before anyone else is ready
+    if (warp == 8 && lane == 0) {
         mbar_init(bar(BAR_QFULL + 0), 1); mbar_init(bar(BAR_QFULL + 1), 1);
         for (int s = 0; s < kKvStages; ++s) {
             mbar_init(bar(BAR_KFULL + s), 1); mbar_init(bar(BAR_KEMPTY + s), 1);
@@ -255,23 +263,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        for (int q = 0; q < 2; ++q) {
-            if (!n_tiles[q]) continue;
-            mbar_expect_tx(bar(BAR_QFULL + q), kTileBytes);
-            const uint32_t dst = smem_base + kSmemQ + q * kTileBytes;
-            tma_load_4d(dst, &map_q, bar(BAR_QFULL + q), 0, (int)(kvh * a.G), (int)(q0 + q * kPM), (int)b);
-            tma_load_4d(dst + kSlabBytes, &map_q, bar(BAR_QFULL + q), 64, (int)(kvh * a.G), (int)(q0 + q * kPM), (int)b);
-        }
-        for (uint32_t j = 0; j < nkv && j < (uint32_t)kKvStages; ++j) {
-            mbar_expect_tx(bar(BAR_KFULL + j), kTileBytes);
-            const uint32_t kd = smem_base + kSmemK + j * kTileBytes;
-            tma_load_4d(kd, &map_k, bar(BAR_KFULL + j), 0, (int)kvh, (int)(j * kPN), (int)b);
-            tma_load_4d(kd + kSlabBytes, &map_k, bar(BAR_KFULL + j), 64, (int)kvh, (int)(j * kPN), (int)b);
-            mbar_expect_tx(bar(BAR_VFULL + j), kTileBytes);
-            const uint32_t vd = smem_base + kSmemV + j * kTileBytes;
-            tma_load_4d(vd, &map_v, bar(BAR_VFULL + j), 0, (int)kvh, (int)(j * kPN), (int)b);
-            tma_load_4d(vd + kSlabBytes, &map_v, bar(BAR_VFULL + j), 64, (int)kvh, (int)(j * kPN), (int)b);
-        }
     }
     if (warp == 9) {  // TMEM owner
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"(kTmemCols) : "memory");
@@ -286,35 +277,37 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (warp == 8) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
-            bool ok = true;   // item 0's Q and its first kKvStages K/V tiles were requested before the CTA-wide sync
-            for (uint32_t it = 0; it < items && ok; ++it) {
-                if (it > 0) {
-                    for (int q = 0; q < 2 && ok; ++q) {   // Q of the next head, once the last QK of the previous one is done
-                        if (!n_tiles[q]) continue;
-                        ok = mbar_wait(bar(BAR_QEMPTY + q), (it - 1) & 1, abort_word, a.error, 12);
-                        if (!ok) break;
-                        mbar_expect_tx(bar(BAR_QFULL + q), kTileBytes);
-                        const uint32_t dst = smem_base + kSmemQ + q * kTileBytes;
-                        tma_load_4d(dst, &map_q, bar(BAR_QFULL + q), 0, (int)(kvh * a.G + it), (int)(q0 + q * kPM), (int)b);
-                        tma_load_4d(dst + kSlabBytes, &map_q, bar(BAR_QFULL + q), 64, (int)(kvh * a.G + it), (int)(q0 + q * kPM), (int)b);
-                    }
+            bool ok = true;
+            uint32_t gk = 0, qc[2] = {0, 0};   // K/V tiles and Q tiles requested so far (barrier phases run through the items)
+            for (uint32_t w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+                const Item it = get_item(w);
+                for (int q = 0; q < 2 && ok; ++q) {   // Q of this item, once the last QK of the previous user of the buffer is done
+                    if (!it.n[q]) continue;
+                    if (qc[q] > 0) ok = mbar_wait(bar(BAR_QEMPTY + q), (qc[q] - 1) & 1, abort_word, a.error, 12);
+                    if (!ok) break;
+                    ++qc[q];
+                    mbar_expect_tx(bar(BAR_QFULL + q), kTileBytes);
+                    const uint32_t dst = smem_base + kSmemQ + q * kTileBytes;
+                    tma_load_4d(dst, &map_q, bar(BAR_QFULL + q), 0, (int)it.h, (int)(it.q0 + q * kPM), (int)it.b);
+                    tma_load_4d(dst + kSlabBytes, &map_q, bar(BAR_QFULL + q), 64, (int)it.h, (int)(it.q0 + q * kPM), (int)it.b);
                 }
-                for (uint32_t j = (it == 0 ? min(nkv, (uint32_t)kKvStages) : 0u); j < nkv && ok; ++j) {
-                    const uint32_t gi = it * nkv + j;          // running tile count: the K/V ring runs through the items
+                for (uint32_t j = 0; j < it.nkv && ok; ++j) {
+                    const uint32_t gi = gk + j;
                     const uint32_t s = gi % kKvStages, ph = (gi / kKvStages) & 1;
                     if (gi >= kKvStages) ok = mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_word, a.error, 1);
                     if (!ok) break;
                     mbar_expect_tx(bar(BAR_KFULL + s), kTileBytes);
                     const uint32_t kd = smem_base + kSmemK + s * kTileBytes;
-                    tma_load_4d(kd, &map_k, bar(BAR_KFULL + s), 0, (int)kvh, (int)(j * kPN), (int)b);
-                    tma_load_4d(kd + kSlabBytes, &map_k, bar(BAR_KFULL + s), 64, (int)kvh, (int)(j * kPN), (int)b);
+                    tma_load_4d(kd, &map_k, bar(BAR_KFULL + s), 0, (int)it.kvh, (int)(j * kPN), (int)it.b);
+                    tma_load_4d(kd + kSlabBytes, &map_k, bar(BAR_KFULL + s), 64, (int)it.kvh, (int)(j * kPN), (int)it.b);
                     if (gi >= kKvStages) ok = mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_word, a.error, 2);
                     if (!ok) break;
                     mbar_expect_tx(bar(BAR_VFULL + s), kTileBytes);
                     const uint32_t vd = smem_base + kSmemV + s * kTileBytes;
-                    tma_load_4d(vd, &map_v, bar(BAR_VFULL + s), 0, (int)kvh, (int)(j * kPN), (int)b);
-                    tma_load_4d(vd + kSlabBytes, &map_v, bar(BAR_VFULL + s), 64, (int)kvh, (int)(j * kPN), (int)b);
+                    tma_load_4d(vd, &map_v, bar(BAR_VFULL + s), 0, (int)it.kvh, (int)(j * kPN), (int)it.b);
+                    tma_load_4d(vd + kSlabBytes, &map_v, bar(BAR_VFULL + s), 64, (int)it.kvh, (int)(j * kPN), (int)it.b);
                 }
+                gk += it.nkv;
             }
         }
     } else if (warp == 9) {
@@ -338,60 +331,68 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     mma_ts(tmem + 256 + q * 128, tmem + q * 128 + ks * 8, desc_mnmajor(vb + ks * 2048), idesc_pv, !first || (ks > 0));
                 tc_commit(bar(BAR_OFULL + q));
             };
-            for (uint32_t it = 0; it < items && ok; ++it) {
+            uint32_t gk = 0, qc[2] = {0, 0}, tc[2] = {0, 0};   // running counts: K/V tiles, Q loads, score tiles per row tile
+            for (uint32_t w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+                const Item it = get_item(w);
+                const uint32_t nkv = it.nkv;
                 for (int q = 0; q < 2 && ok; ++q)
-                    if (n_tiles[q]) ok = mbar_wait(bar(BAR_QFULL + q), it & 1, abort_word, a.error, 3);
+                    if (it.n[q]) {
+                        ok = mbar_wait(bar(BAR_QFULL + q), qc[q] & 1, abort_word, a.error, 3);
+                        ++qc[q];
+                    }
                 for (uint32_t j = 0; j <= nkv && ok; ++j) {
-                    const uint32_t gi = it * nkv + j;
+                    const uint32_t gi = gk + j;
                     const uint32_t s = gi % kKvStages, ph = (gi / kKvStages) & 1;
                     if (j < nkv) {
                         ok = mbar_wait(bar(BAR_KFULL + s), ph, abort_word, a.error, 4);
                         if (!ok) break;
                         tc_fence_after();
                     }
-                    if (j < n_tiles[0]) {
+                    if (j < it.n[0]) {
                         issue_qk(0, s);
-                        if (j == n_tiles[0] - 1) tc_commit(bar(BAR_QEMPTY + 0));   // Q0 of this head is no longer needed
+                        if (j == it.n[0] - 1) tc_commit(bar(BAR_QEMPTY + 0));   // Q0 of this item is no longer needed
                     }
-                    if (j >= 1 && j - 1 < n_tiles[1]) {
+                    if (j >= 1 && j - 1 < it.n[1]) {
                         const uint32_t gp = gi - 1, sp = gp % kKvStages, pp = (gp / kKvStages) & 1;
                         ok = mbar_wait(bar(BAR_VFULL + sp), pp, abort_word, a.error, 5) &&
-                             mbar_wait(bar(BAR_PFULL + 1), (it * n_tiles[1] + j - 1) & 1, abort_word, a.error, 6);
+                             mbar_wait(bar(BAR_PFULL + 1), (tc[1] + j - 1) & 1, abort_word, a.error, 6);
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(1, sp, j - 1 == 0);
                         tc_commit(bar(BAR_VEMPTY + sp));   // PV1 is the last reader of that V tile
                     }
-                    if (j < n_tiles[1]) {
+                    if (j < it.n[1]) {
                         issue_qk(1, s);
-                        if (j == n_tiles[1] - 1) tc_commit(bar(BAR_QEMPTY + 1));
+                        if (j == it.n[1] - 1) tc_commit(bar(BAR_QEMPTY + 1));
                     }
                     if (j < nkv) tc_commit(bar(BAR_KEMPTY + s));   // both tiles' QK on this K tile are issued
-                    if (j < n_tiles[0]) {
+                    if (j < it.n[0]) {
                         ok = mbar_wait(bar(BAR_VFULL + s), ph, abort_word, a.error, 7) &&
-                             mbar_wait(bar(BAR_PFULL + 0), (it * n_tiles[0] + j) & 1, abort_word, a.error, 8);
+                             mbar_wait(bar(BAR_PFULL + 0), (tc[0] + j) & 1, abort_word, a.error, 8);
                         if (!ok) break;
                         tc_fence_after();
-                        // (the softmax warps read O of the previous head before they arrive on this P barrier,
-                        //  so overwriting O here with the first tile of the next head is safe)
+                        // (the softmax warps read O of the previous item before they arrive on this P barrier,
+                        //  so overwriting O here with the first tile of the next item is safe)
                         issue_pv(0, s, j == 0);
-                        if (j >= n_tiles[1]) tc_commit(bar(BAR_VEMPTY + s));   // no PV1 on this tile will follow
+                        if (j >= it.n[1]) tc_commit(bar(BAR_VEMPTY + s));   // no PV1 on this tile will follow
                     }
                 }
+                gk += nkv; tc[0] += it.n[0]; tc[1] += it.n[1];
             }
         }
     } else {
         // =============================== softmax (one thread per query row) ===============================
         const uint32_t q = warp >> 2;                   // which 128-row tile
         const uint32_t r = tid & 127;                   // row in the tile == TMEM lane
-        const uint32_t row = q0 + q * kPM + r;          // global query row == its causal limit
         const uint32_t lane_base = ((warp & 3) * 32) << 16;
         const uint32_t t_s = tmem + lane_base + q * 128, t_o = tmem + lane_base + 256 + q * 128;
-        const uint32_t nq = n_tiles[q];
         bool ok = true;
-        for (uint32_t it = 0; it < items && ok && nq; ++it) {
-        const uint32_t h = kvh * a.G + it;              // the query head of this item
-        const uint32_t c0 = it * nq;                    // tiles of this row block finished before this item (barrier phases)
+        uint32_t c0 = 0;                                // score tiles of this row tile finished before the current item (barrier phases)
+        for (uint32_t w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+        const Item item = get_item(w);
+        const uint32_t nq = item.n[q], h = item.h, b = item.b;
+        const uint32_t row = item.q0 + q * kPM + r;     // global query row == its causal limit
+        if (!nq) continue;
         float m_ref = -INFINITY, l_sum = 0.f;
         for (uint32_t j = 0; j < nq && ok; ++j) {
             ok = mbar_wait(bar(BAR_SFULL + q), (c0 + j) & 1, abort_word, a.error, 9);
@@ -534,6 +535,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
             }
         }
+        c0 += nq;
         }   // items
     }
     // ---- teardown: everyone arrives, TMEM goes back ----
@@ -622,7 +624,9 @@ int launch_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_
     a.B = B; a.T = T; a.nh = nh; a.nkv = nkv; a.G = nh / nkv;
     a.m_tiles = (T + 255) / 256;
     a.scale_log2 = (1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
-    const unsigned long long blocks = (unsigned long long)a.m_tiles * B * nkv;   // one CTA per (row block, sequence, KV group)
+    const unsigned long long total_items = (unsigned long long)a.m_tiles * B * nh;
+    SHADY_REQUIRE(ctx, total_items <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "attn_prefill: too many tiles for one launch");
+    const unsigned long long blocks = total_items < (unsigned long long)ctx->num_sms ? total_items : (unsigned long long)ctx->num_sms;   // persistent: one CTA per SM
     SHADY_REQUIRE(ctx, blocks <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "attn_prefill: too many tiles for one launch");
     static thread_local int configured_dev = -1;
     if (configured_dev != ctx->device) {
