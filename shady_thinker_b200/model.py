@@ -80,6 +80,7 @@ class Model:
         self.kv_dtype = kv_dtype
         self.num_attn_splits = num_attn_splits
         self.seq_len = 0
+        self._pos_on_device = self._len_on_device = None   # host copies of the two device counters
         nh, nkv, hd, nl = (config.num_attention_heads, config.num_key_value_heads, config.head_dim,
                            config.num_hidden_layers)
         f = 4
@@ -114,7 +115,9 @@ class Model:
         c, s = self.config, self.state
         if self.seq_len >= self.max_seq_len:
             raise IndexError("KV cache is full")
-        gpu.write_buffer(s.position, 0, struct.pack("I", self.seq_len))  # model.rs:493-496
+        if self._pos_on_device != self.seq_len:      # model.rs:493-496 writes it per layer; once per token is enough
+            gpu.write_buffer(s.position, 0, struct.pack("I", self.seq_len))
+            self._pos_on_device = self.seq_len
         ops.kv_append_rope(gpu, q_proj_full=s.q_out, k_proj=s.k_out, v_proj=s.v_out, q_out=s.q_proj, q_gate=s.q_gate,
                            cache=self._cache(layer_idx), pos_start=s.position, num_heads=c.num_attention_heads,
                            num_kv_heads=c.num_key_value_heads, head_dim=c.head_dim, rope_theta=c.rope_theta,
@@ -125,7 +128,9 @@ class Model:
         """model.rs:516-573.  ``fuse_gate`` folds the following ``sigmoid_mul_gate`` into the epilogue."""
         c, s = self.config, self.state
         seq_len = self.seq_len + 1  # include current token (model.rs:521)
-        gpu.write_buffer(s.seq_len_dev, 0, struct.pack("I", seq_len))
+        if self._len_on_device != seq_len:
+            gpu.write_buffer(s.seq_len_dev, 0, struct.pack("I", seq_len))
+            self._len_on_device = seq_len
         ops.attn_decode(gpu, q=s.q_proj, cache=self._cache(layer_idx), seq_lens=s.seq_len_dev, out=s.attn_output,
                         head_dim=c.head_dim, num_kv_heads=c.num_key_value_heads, num_q_heads=c.num_attention_heads,
                         num_seqs=1, num_splits=self.num_attn_splits, seq_lens_host=[seq_len],
