@@ -1084,7 +1084,7 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
     uint32_t ctas_per_sm = env_u32("SHADY_DECODE_CTAS_PER_SM", f32 ? 4u : var.ctas_per_sm);
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     if (ctas_per_sm > 8) ctas_per_sm = 8;
-    uint32_t min_span = env_u32("SHADY_DECODE_MIN_SPAN", f32 ? 4u : 4u * (var.nw / kpc));
+    uint32_t min_span = env_u32("SHADY_DECODE_MIN_SPAN", f32 ? 2u : 4u * (var.nw / kpc));
     if (min_span < 1) min_span = 1;
 
     unsigned long long items;
@@ -1238,7 +1238,7 @@ int launch_decode_static(shady_ctx *ctx, const shady_decode_params *p, const voi
         SHADY_REQUIRE(ctx, line <= 0xffffffffull, SHADY_ERR_UNSUPPORTED, "decode_static: batch too long for one launch");
         const unsigned long long slots = (unsigned long long)ctx->num_sms * (f32 ? 4u : var.ctas_per_sm);
         unsigned long long spans = slots / ((unsigned long long)kv_groups * a.gz);
-        const unsigned long long min_span = f32 ? 4u : 4u * var.nw;
+        const unsigned long long min_span = f32 ? 2u : 4u * var.nw;
         const unsigned long long by_size = (line + min_span - 1) / min_span;
         if (spans > by_size) spans = by_size;
         if (spans < 1) spans = 1;
