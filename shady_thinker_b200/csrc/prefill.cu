@@ -46,8 +46,8 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSpinLimit = 1u << 20;  // bounded waits: on the order of a second at worst, then give up
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
-enum { BAR_QFULL = 0, BAR_KFULL = 2, BAR_KEMPTY = 4, BAR_VFULL = 6, BAR_VEMPTY = 8, BAR_SFULL = 10, BAR_PFULL = 12,
-       BAR_OFULL = 14, BAR_QEMPTY = 16, BAR_COUNT = 18 };
+enum { BAR_QFULL = 0, BAR_KVFULL = 2, BAR_KVEMPTY = 4, BAR_SFULL = 6, BAR_PFULL = 8, BAR_OFULL = 10, BAR_QEMPTY = 12,
+       BAR_COUNT = 14 };
 
 struct PrefillArgs {
     void *out;
@@ -259,8 +259,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (warp == 8 && lane == 0) {
         mbar_init(bar(BAR_QFULL + 0), 1); mbar_init(bar(BAR_QFULL + 1), 1);
         for (int s = 0; s < kKvStages; ++s) {
-            mbar_init(bar(BAR_KFULL + s), 1); mbar_init(bar(BAR_KEMPTY + s), 1);
-            mbar_init(bar(BAR_VFULL + s), 1); mbar_init(bar(BAR_VEMPTY + s), 1);
+            mbar_init(bar(BAR_KVFULL + s), 1); mbar_init(bar(BAR_KVEMPTY + s), 1);
         }
         for (int q = 0; q < 2; ++q) {
             mbar_init(bar(BAR_SFULL + q), 1); mbar_init(bar(BAR_PFULL + q), 128); mbar_init(bar(BAR_OFULL + q), 1);
@@ -298,21 +297,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     tma_load_4d(dst, &map_q, bar(BAR_QFULL + q), 0, (int)it.h, (int)(it.q0 + q * kPM), (int)it.b);
                     tma_load_4d(dst + kSlabBytes, &map_q, bar(BAR_QFULL + q), 64, (int)it.h, (int)(it.q0 + q * kPM), (int)it.b);
                 }
-                for (uint32_t j = 0; j < it.nkv && ok; ++j) {
+                for (uint32_t j = 0; j < it.nkv && ok; ++j) {   // K and V tile j travel together: one stage, one barrier
                     const uint32_t gi = gk + j;
                     const uint32_t s = gi % kKvStages, ph = (gi / kKvStages) & 1;
-                    if (gi >= kKvStages) ok = mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1, abort_word, a.error, 1);
+                    if (gi >= kKvStages) ok = mbar_wait(bar(BAR_KVEMPTY + s), ph ^ 1, abort_word, a.error, 1);
                     if (!ok) break;
-                    mbar_expect_tx(bar(BAR_KFULL + s), kTileBytes);
-                    const uint32_t kd = smem_base + kSmemK + s * kTileBytes;
-                    tma_load_4d(kd, &map_k, bar(BAR_KFULL + s), 0, (int)it.kvh, (int)(j * kPN), (int)it.b);
-                    tma_load_4d(kd + kSlabBytes, &map_k, bar(BAR_KFULL + s), 64, (int)it.kvh, (int)(j * kPN), (int)it.b);
-                    if (gi >= kKvStages) ok = mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1, abort_word, a.error, 2);
-                    if (!ok) break;
-                    mbar_expect_tx(bar(BAR_VFULL + s), kTileBytes);
-                    const uint32_t vd = smem_base + kSmemV + s * kTileBytes;
-                    tma_load_4d(vd, &map_v, bar(BAR_VFULL + s), 0, (int)it.kvh, (int)(j * kPN), (int)it.b);
-                    tma_load_4d(vd + kSlabBytes, &map_v, bar(BAR_VFULL + s), 64, (int)it.kvh, (int)(j * kPN), (int)it.b);
+                    mbar_expect_tx(bar(BAR_KVFULL + s), 2 * kTileBytes);
+                    const uint32_t kd = smem_base + kSmemK + s * kTileBytes, vd = smem_base + kSmemV + s * kTileBytes;
+                    tma_load_4d(kd, &map_k, bar(BAR_KVFULL + s), 0, (int)it.kvh, (int)(j * kPN), (int)it.b);
+                    tma_load_4d(kd + kSlabBytes, &map_k, bar(BAR_KVFULL + s), 64, (int)it.kvh, (int)(j * kPN), (int)it.b);
+                    tma_load_4d(vd, &map_v, bar(BAR_KVFULL + s), 0, (int)it.kvh, (int)(j * kPN), (int)it.b);
+                    tma_load_4d(vd + kSlabBytes, &map_v, bar(BAR_KVFULL + s), 64, (int)it.kvh, (int)(j * kPN), (int)it.b);
                 }
                 gk += it.nkv;
             }
@@ -336,7 +331,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
                 for (uint32_t ks = 0; ks < kPN / 16; ++ks)
                     mma_ts(tmem + 256 + q * 128, tmem + q * 128 + ks * 8, desc_mnmajor(vb + ks * 2048), idesc_pv, !first || (ks > 0));
-                tc_commit(bar(BAR_OFULL + q));
             };
             uint32_t gk = 0, qc[2] = {0, 0}, tc[2] = {0, 0};   // running counts: K/V tiles, Q loads, score tiles per row tile
             for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
@@ -349,11 +343,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         ok = mbar_wait(bar(BAR_QFULL + q), qc[q] & 1, abort_word, a.error, 3);
                         ++qc[q];
                     }
+                // Per K/V tile the issuer stops three times (K/V landed, P1 stored, P0 stored) and commits three
+                // times (S0, S1, stage free): every stop drains the short MMA queue, so there are as few as the
+                // dependencies allow.  O needs no barrier of its own inside an item: a commit covers every MMA the
+                // thread issued before it, so "S(j) complete" already says "PV(j-1) complete".
                 for (uint32_t j = 0; j <= nkv && ok; ++j) {
                     const uint32_t gi = gk + j;
                     const uint32_t s = gi % kKvStages, ph = (gi / kKvStages) & 1;
                     if (j < nkv) {
-                        ok = mbar_wait(bar(BAR_KFULL + s), ph, abort_word, a.error, 4);
+                        ok = mbar_wait(bar(BAR_KVFULL + s), ph, abort_word, a.error, 4);
                         if (!ok) break;
                         tc_fence_after();
                     }
@@ -362,28 +360,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         if (j == it.n[0] - 1) tc_commit(bar(BAR_QEMPTY + 0));   // Q0 of this item is no longer needed
                     }
                     if (j >= 1 && j - 1 < it.n[1]) {
-                        const uint32_t gp = gi - 1, sp = gp % kKvStages, pp = (gp / kKvStages) & 1;
-                        ok = mbar_wait(bar(BAR_VFULL + sp), pp, abort_word, a.error, 5) &&
-                             mbar_wait(bar(BAR_PFULL + 1), (tc[1] + j - 1) & 1, abort_word, a.error, 6);
+                        const uint32_t sp = (gi - 1) % kKvStages;
+                        ok = mbar_wait(bar(BAR_PFULL + 1), (tc[1] + j - 1) & 1, abort_word, a.error, 6);
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(1, sp, j - 1 == 0);
-                        tc_commit(bar(BAR_VEMPTY + sp));   // PV1 is the last reader of that V tile
+                        tc_commit(bar(BAR_KVEMPTY + sp));   // PV1 is the last reader of that stage
+                        if (j == it.n[1]) tc_commit(bar(BAR_OFULL + 1));   // the item's last PV of tile 1
                     }
                     if (j < it.n[1]) {
                         issue_qk(1, s);
                         if (j == it.n[1] - 1) tc_commit(bar(BAR_QEMPTY + 1));
                     }
-                    if (j < nkv) tc_commit(bar(BAR_KEMPTY + s));   // both tiles' QK on this K tile are issued
                     if (j < it.n[0]) {
-                        ok = mbar_wait(bar(BAR_VFULL + s), ph, abort_word, a.error, 7) &&
-                             mbar_wait(bar(BAR_PFULL + 0), (tc[0] + j) & 1, abort_word, a.error, 8);
+                        ok = mbar_wait(bar(BAR_PFULL + 0), (tc[0] + j) & 1, abort_word, a.error, 8);
                         if (!ok) break;
                         tc_fence_after();
                         // (the softmax warps read O of the previous item before they arrive on this P barrier,
                         //  so overwriting O here with the first tile of the next item is safe)
                         issue_pv(0, s, j == 0);
-                        if (j >= it.n[1]) tc_commit(bar(BAR_VEMPTY + s));   // no PV1 on this tile will follow
+                        if (j >= it.n[1]) tc_commit(bar(BAR_KVEMPTY + s));   // no PV1 on this tile will follow
+                        if (j == it.n[0] - 1) tc_commit(bar(BAR_OFULL + 0));
                     }
                 }
                 gk += nkv; tc[0] += it.n[0]; tc[1] += it.n[1];
@@ -396,7 +393,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint32_t lane_base = ((warp & 3) * 32) << 16;
         const uint32_t t_s = tmem + lane_base + q * 128, t_o = tmem + lane_base + 256 + q * 128;
         bool ok = true;
-        uint32_t c0 = 0;                                // score tiles of this row tile finished before the current item (barrier phases)
+        uint32_t c0 = 0, oc = 0;                        // score tiles / items of this row tile finished before the current item (barrier phases)
         for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
         const uint32_t w = item_of_round(rnd);
         if (w >= total_items) continue;
@@ -407,7 +404,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         float m_ref = -INFINITY, l_sum = 0.f;
         for (uint32_t j = 0; j < nq && ok; ++j) {
             ok = mbar_wait(bar(BAR_SFULL + q), (c0 + j) & 1, abort_word, a.error, 9);
-            if (j > 0 && ok) ok = mbar_wait(bar(BAR_OFULL + q), (c0 + j - 1) & 1, abort_word, a.error, 10);
             if (!ok) break;
             tc_fence_after();
             // one tile of the online softmax; the diagonal tile (the last one) is a second instantiation
@@ -523,7 +519,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             else tile_body(std::false_type{});
         }
         // ---- epilogue: O / l -> global ----
-        if (nq && ok) ok = mbar_wait(bar(BAR_OFULL + q), (c0 + nq - 1) & 1, abort_word, a.error, 11);
+        if (nq && ok) ok = mbar_wait(bar(BAR_OFULL + q), oc & 1, abort_word, a.error, 11);
         if (nq && ok) {
             tc_fence_after();
             const float inv = 1.0f / l_sum;
@@ -547,6 +543,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             }
         }
         c0 += nq;
+        ++oc;
         }   // items
     }
     // ---- teardown: everyone arrives, TMEM goes back ----
@@ -557,7 +554,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // shared memory is handed back
         for (int s = 0; s < kKvStages; ++s)
             for (uint32_t i = 0; i < (1u << 16); ++i)
-                if (mbar_try(bar(BAR_KFULL + s), 0) && mbar_try(bar(BAR_VFULL + s), 0)) break;
+                if (mbar_try(bar(BAR_KVFULL + s), 0)) break;
     }
     __syncthreads();
     if (warp == 9) {
