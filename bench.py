@@ -33,7 +33,7 @@ LMIN, LMAX = 1024, 8192
 N_SETS = 3            # rotating cache sets so no step finds its KV rows in L2
 # DRAM bytes per algorithmic byte of the decode kernel, from the ncu capture summarised in
 # profiles/decode16_f16_hd128_cfg2.md (read + write bytes of one launch over its algorithmic bytes).
-TRAFFIC_PER_ALGO_BYTE = 1.010
+TRAFFIC_PER_ALGO_BYTE = 1.011
 
 
 def draw_lengths(rank: int) -> np.ndarray:
@@ -197,8 +197,10 @@ def run_reference(args, rank: int) -> None:
     }))
 
 
-def workload_config(n_gpus: int) -> dict:
-    return {"workload": "cfg2: batched ragged decode attention, one layer, append+attend per step",
+def workload_config(n_gpus: int, shape: str = "plain") -> dict:
+    rope = ("full rotary (rotary_dim = head_dim), no QK-norm, no gate" if shape == "plain" else
+            "reference-shaped: rotary_dim = head_dim/4 interleaved, QK RMSNorm with bf16 weights, sigmoid gate")
+    return {"workload": "cfg2: batched ragged decode attention, one layer, append+attend per step", "rope": rope,
             "seqs_per_gpu": SEQS_PER_GPU, "context": f"uniform[{LMIN},{LMAX}] (seeded)", "num_q_heads": NH,
             "num_kv_heads": NKV, "head_dim": HD, "kv_dtype": "fp16", "q_dtype": "fp16", "accumulate": "fp32",
             "rope_theta": 1e6, "sharding": f"sequences over {n_gpus} GPU(s), no collective",
@@ -251,15 +253,23 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     gpu = GpuContext(local_rank, stream=stream.cuda_stream)
     lens = draw_lengths(rank)
     sets = []
+    ref_shape = args.shape == "reference"
+    qrow = NH * HD * (2 if ref_shape else 1)
+    d_norm = None
+    if ref_shape:       # bf16 q_norm[hd] then k_norm[hd], N(0, 0.02) (the uniform of model.rs:140-168)
+        wf = (np.random.default_rng(SEED).standard_normal(2 * HD) * 0.02).astype(np.float32).view(np.uint32)
+        wbits = ((wf + 0x7FFF + ((wf >> 16) & 1)) >> 16).astype(np.uint16)
+        d_norm = gpu.upload_buffer("qknorm_weights", wbits.tobytes())
     for i in range(N_SETS):
         d = BatchedDecoder(gpu, num_seqs=SEQS_PER_GPU, capacities=lens, num_heads=NH, num_kv_heads=NKV, head_dim=HD,
-                           kv_dtype=F16, rope_theta=1e6, rotary_dim=HD, has_gate=False, num_splits=0)
+                           kv_dtype=F16, rope_theta=1e6, rotary_dim=HD // 4 if ref_shape else HD, has_gate=ref_shape,
+                           num_splits=0, qk_norm_bf16=d_norm)
         d.set_lengths(lens - 1)
         base = 1000 * rank + 10 * i
         n = d.layer_bytes // 2
         ops.fill_randn(gpu, d.k_cache[0], n, F16, SEED, base + 1)
         ops.fill_randn(gpu, d.v_cache[0], n, F16, SEED, base + 2)
-        ops.fill_randn(gpu, d.q_in, SEQS_PER_GPU * NH * HD, F16, SEED, base + 3)
+        ops.fill_randn(gpu, d.q_in, SEQS_PER_GPU * qrow, F16, SEED, base + 3)
         ops.fill_randn(gpu, d.k_in, SEQS_PER_GPU * NKV * HD, F16, SEED, base + 4)
         ops.fill_randn(gpu, d.v_in, SEQS_PER_GPU * NKV * HD, F16, SEED, base + 5)
         sets.append(d)
@@ -272,8 +282,11 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         # ---------------- device-resident throughput ----------------
         for i in range(args.warmup):
             sets[i % N_SETS].step()
-        ev_a = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        # the launch itself is timed on every ev_stride-th step only: an event pair around each launch costs
+        # the whole-step figure a few microseconds of gap per step
+        ev_stride = 1 if args.steps <= 16 else 8
+        ev_a = [torch.cuda.Event(enable_timing=True) for _ in range(0, args.steps, ev_stride)]
+        ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(0, args.steps, ev_stride)]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         launches0 = gpu.launch_count
@@ -281,20 +294,23 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         e0.record(stream)
         for i in range(args.steps):
             d = sets[i % N_SETS]
-            ev_a[i].record(stream)
+            timed = i % ev_stride == 0
+            if timed:
+                ev_a[i // ev_stride].record(stream)
             d.step()            # one fused launch: RoPE + cache append + split-KV decode + merge
-            ev_b[i].record(stream)
+            if timed:
+                ev_b[i // ev_stride].record(stream)
         e1.record(stream)
         barrier()
         t_wall1 = time.perf_counter()
         launches = gpu.launch_count - launches0
         total_ms = e0.elapsed_time(e1)
-        attend_ms = sum(a.elapsed_time(b) for a, b in zip(ev_a, ev_b)) / args.steps
+        attend_ms = sum(a.elapsed_time(b) for a, b in zip(ev_a, ev_b)) / len(ev_a)
 
         # ---------------- end to end with host buffers ----------------
         d0 = sets[0]
         asz = 2
-        hq = torch.empty(SEQS_PER_GPU * NH * HD, dtype=torch.float16).pin_memory()
+        hq = torch.empty(SEQS_PER_GPU * qrow, dtype=torch.float16).pin_memory()
         hk = torch.empty(SEQS_PER_GPU * NKV * HD, dtype=torch.float16).pin_memory()
         hv = torch.empty(SEQS_PER_GPU * NKV * HD, dtype=torch.float16).pin_memory()
         ho = torch.empty(SEQS_PER_GPU * NH * HD, dtype=torch.float16).pin_memory()
@@ -330,7 +346,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "metric": "decode_attn_kv_bandwidth", "value": all_bytes * args.steps / (total_ms * 1e-3) / 1e9, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": workload_config(world),
+            "config": workload_config(world, args.shape),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": (TRAFFIC_PER_ALGO_BYTE * step_bytes) if TRAFFIC_PER_ALGO_BYTE else None,
                          "peak_source": f"{peak_src} (copy bandwidth)",
@@ -680,6 +696,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    ap.add_argument("--shape", default="plain", choices=["plain", "reference"],
+                    help="cfg2 only: plain = full rotary, no norm, no gate; reference = the reference's defaults "
+                         "(rotary_dim = head_dim/4, QK RMSNorm, sigmoid gate)")
     ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
                     help="cfg2 = batched ragged decode (default, the headline); cfg3 = causal prefill; "
                          "cfg1/cfg4/cfg5 = the other BASELINE configs")

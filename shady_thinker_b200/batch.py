@@ -25,13 +25,14 @@ class BatchedDecoder:
     def __init__(self, gpu: GpuContext, *, num_seqs: int, capacities, num_heads: int, num_kv_heads: int,
                  head_dim: int, kv_dtype: int = F16, act_dtype: int | None = None, rope_theta: float = 1e6,
                  rotary_dim: int | None = None, interleaved: bool = True, eps: float = 1e-6, has_gate: bool = False,
-                 num_layers: int = 1, num_splits: int = 0):
+                 num_layers: int = 1, num_splits: int = 0, qk_norm_bf16=None):
         self.gpu, self.S, self.nh, self.nkv, self.hd = gpu, num_seqs, num_heads, num_kv_heads, head_dim
         self.kv_dtype = kv_dtype
         self.act_dtype = kv_dtype if act_dtype is None else act_dtype
         self.theta, self.rd = rope_theta, head_dim if rotary_dim is None else rotary_dim
         self.interleaved, self.eps, self.has_gate = interleaved, eps, has_gate
         self.num_layers, self.num_splits = num_layers, num_splits
+        self.qk_norm = qk_norm_bf16   # device buffer: bf16 q_norm[hd] then k_norm[hd] (model.rs:140-168), or None
         self.fused = not os.environ.get("SHADY_NO_FUSED_APPEND") and kv_dtype != F32 and interleaved and (kv_dtype if act_dtype is None else act_dtype) in (F32, kv_dtype)
         caps = np.asarray(capacities, dtype=np.int64)
         assert caps.shape == (num_seqs,)
@@ -86,7 +87,8 @@ class BatchedDecoder:
                            q_gate=self.q_gate, cache=self.views[layer], pos_start=self.pos, num_heads=self.nh,
                            num_kv_heads=self.nkv, head_dim=self.hd, rope_theta=self.theta, rotary_dim=self.rd,
                            interleaved=self.interleaved, eps=self.eps, num_seqs=self.S, tokens_per_seq=1,
-                           in_dtype=self.act_dtype, q_dtype=self.act_dtype, has_gate=self.has_gate, write_k_back=False)
+                           in_dtype=self.act_dtype, q_dtype=self.act_dtype, has_gate=self.has_gate, write_k_back=False,
+                           qk_norm_bf16=self.qk_norm)
 
     def attend(self, layer: int = 0) -> None:
         ops.attn_decode(self.gpu, q=self.q_rot, cache=self.views[layer], seq_lens=self.lens, out=self.out,
@@ -107,7 +109,8 @@ class BatchedDecoder:
         ops.attn_decode_append(self.gpu, q_proj_full=self.q_in, k_proj=self.k_in, v_proj=self.v_in,
                                cache=self.views[layer], seq_lens=self.lens, out=self.out, num_heads=self.nh,
                                num_kv_heads=self.nkv, head_dim=self.hd, rope_theta=self.theta, rotary_dim=self.rd,
-                               num_seqs=self.S, eps=self.eps, in_dtype=self.act_dtype, out_dtype=self.act_dtype,
+                               num_seqs=self.S, eps=self.eps, qk_norm_bf16=self.qk_norm, in_dtype=self.act_dtype,
+                               out_dtype=self.act_dtype,
                                has_gate=self.has_gate, seq_lens_host=self.lens_after, workspace=self.ws,
                                workspace_bytes=self.ws_bytes, num_splits=self.num_splits)
 
