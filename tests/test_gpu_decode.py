@@ -175,6 +175,42 @@ def test_long_context_bf16_hd256(gpu_ctx, oracle):
     assert rel_err(out[0], oracle.attention_f64(q[0], k, v, L, threads=8)) <= RTOL_16
 
 
+def test_cfg4_full_size_against_f64_and_shard_merge(gpu_ctx, oracle):
+    """BASELINE config 4 at full size (one sequence of 131072 rows, nh16/nkv2/hd256, bf16): three heads against
+    f64 attention over the same device-filled rows, and a size-independent property — the rows cut into 8 shards,
+    each decoded to (output, lse) records and merged rank-major, give the single-pass result."""
+    nh, nkv, hd, L, P = 16, 2, 256, 131072, 8
+    d_k = torch.empty((L, nkv, hd), dtype=torch.bfloat16, device="cuda")
+    d_v = torch.empty((L, nkv, hd), dtype=torch.bfloat16, device="cuda")
+    ops.fill_randn(gpu_ctx, d_k, d_k.numel(), BF16, 0x5EED, 41)
+    ops.fill_randn(gpu_ctx, d_v, d_v.numel(), BF16, 0x5EED, 42)
+    q = rounded(oracle, oracle.randn((1, nh, hd), 0x5EED, 43), BF16)
+    view = ops.KvCacheView(BF16, d_k, d_v, 0)
+    out = run_decode(gpu_ctx, q, view, [L], nh=nh, nkv=nkv, hd=hd, num_splits=0, q_dt=BF16, out_dt=F32)[0]
+    k = d_k.float().cpu().numpy()
+    v = d_v.float().cpu().numpy()
+    for h in (0, 7, 15):
+        kvh = h // (nh // nkv)
+        sc = (k[:, kvh].astype(np.float64) @ q[0, h].astype(np.float64)) / np.sqrt(hd)
+        pr = np.exp(sc - sc.max())
+        ref = (pr[:, None] * v[:, kvh]).sum(0) / pr.sum()
+        assert rel_err(out[h], ref) <= RTOL_16, h
+    recs = torch.zeros((P, nh, hd + 2), device="cuda")
+    for r in range(P):
+        lo, hi = r * L // P, (r + 1) * L // P
+        sv = ops.KvCacheView(BF16, d_k[lo:hi], d_v[lo:hi], 0)
+        o, lse = run_decode(gpu_ctx, q, sv, [hi - lo], nh=nh, nkv=nkv, hd=hd, num_splits=0, q_dt=BF16, want_lse=True)
+        recs[r, :, :hd] = torch.from_numpy(o[0]).cuda()
+        recs[r, :, hd] = torch.from_numpy(lse[0]).cuda()
+    d_out = torch.empty((nh, hd), device="cuda")
+    ops.attn_reduce(gpu_ctx, partials=recs, out=d_out, head_dim=hd, num_splits=P, num_heads=nh,
+                    split_stride=nh * (hd + 2), head_stride=hd + 2)
+    gpu_ctx.synchronize()
+    # both sides round P to bf16 over different row ranges: they agree to that rounding, not bit for bit
+    err = rel_err(to_host(d_out), out)
+    assert err <= 5e-3, err
+
+
 def test_shards_merge_like_one_pass(gpu_ctx, oracle):
     """Split one sequence's rows over 4 'ranks', decode each shard with lse, merge rank-major records with
     shady_attn_reduce: equals the unsharded result (the cross-GPU combine run on one GPU)."""

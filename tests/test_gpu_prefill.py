@@ -70,3 +70,47 @@ def test_unsupported_shapes_return_status(gpu_ctx):
         ops.attn_prefill(gpu_ctx, q=d, cache=ops.KvCacheView(BF16, d, d, 0), out=d, head_dim=64, num_kv_heads=1,
                          num_q_heads=1, num_seqs=1, seq_len=8, dtype=BF16)
     assert e.value.code == 2
+
+
+def test_cfg3_full_size_sampled_rows_and_linearity_in_v(gpu_ctx, oracle):
+    """BASELINE config 3 at full size (B4, T4096, nh32/nkv8/hd128, bf16): sampled output rows against f64
+    attention over the same rounded inputs, and two size-independent properties — doubling V doubles every output
+    bit for bit (the softmax weights do not depend on V, and x2 is exact in bf16 and fp32), and a second run
+    reproduces the first bit for bit."""
+    B, T, nh, nkv, hd = 4, 4096, 32, 8, 128
+    d_q = torch.empty((B, T, nh, hd), dtype=torch.bfloat16, device="cuda")
+    d_k = torch.empty((B, T, nkv, hd), dtype=torch.bfloat16, device="cuda")
+    d_v = torch.empty((B, T, nkv, hd), dtype=torch.bfloat16, device="cuda")
+    ops.fill_randn(gpu_ctx, d_q, d_q.numel(), BF16, 0x5EED, 31)
+    ops.fill_randn(gpu_ctx, d_k, d_k.numel(), BF16, 0x5EED, 32)
+    ops.fill_randn(gpu_ctx, d_v, d_v.numel(), BF16, 0x5EED, 33)
+
+    def run(v):
+        d_out = torch.full((B, T, nh, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        view = ops.KvCacheView(BF16, d_k, v, T * nkv * hd)
+        ops.attn_prefill(gpu_ctx, q=d_q, cache=view, out=d_out, head_dim=hd, num_kv_heads=nkv, num_q_heads=nh,
+                         num_seqs=B, seq_len=T, dtype=BF16)
+        gpu_ctx.synchronize()
+        return d_out
+
+    out = run(d_v)
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out, run(d_v))
+    assert torch.equal(run(d_v * 2), out * 2)
+    # sampled (batch, row, head) triples: tile edges, the diagonal tiles, first and last rows
+    rows = [0, 1, 127, 128, 129, 255, 256, 1000, 2047, 2048, 3071, 4000, 4094, 4095]
+    scale = 1.0 / np.sqrt(hd)
+    worst = 0.0
+    for b in (0, 3):
+        k = d_k[b].float().cpu().numpy().astype(np.float64)
+        v = d_v[b].float().cpu().numpy().astype(np.float64)
+        for r in rows:
+            for h in (0, 5, 31):
+                kvh = h // (nh // nkv)
+                qv = d_q[b, r, h].float().cpu().numpy().astype(np.float64)
+                s = (k[: r + 1, kvh] @ qv) * scale
+                p = np.exp(s - s.max())
+                ref = (p[:, None] * v[: r + 1, kvh]).sum(0) / p.sum()
+                got = out[b, r, h].float().cpu().numpy()
+                worst = max(worst, float(np.abs(got - ref).max() / np.abs(ref).max()))
+    assert worst <= RTOL_16, worst
