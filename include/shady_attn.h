@@ -73,6 +73,13 @@ int shady_buffer_write(shady_ctx *ctx, void *d_buf, size_t offset, const void *s
 int shady_buffer_read(shady_ctx *ctx, const void *d_buf, size_t offset, void *dst, size_t bytes);
 /* copy_buffer (gpu.rs:245). */
 int shady_buffer_copy(shady_ctx *ctx, const void *d_src, void *d_dst, size_t bytes);
+/* Zero-copy alternative to write_buffer/read_buffer (gpu.rs:278, 252) for page-locked host memory
+ * (cudaHostAlloc, cudaHostRegister, a pinned torch tensor): *d_ptr receives the address under which
+ * kernels read and write that memory directly, so the activations and the result of a step cross the
+ * host link inside the launch instead of in copies of their own.  SHADY_ERR_BAD_ARG if host_ptr is
+ * not page-locked, device-accessible host memory.  The host reads results after shady_synchronize.
+ * No reference counterpart: wgpu buffers cannot be mapped while a dispatch uses them. */
+int shady_host_device_ptr(shady_ctx *ctx, const void *host_ptr, void **d_ptr);
 /* flush (gpu.rs:237): launches are already submitted, so this only reports a pending
  * asynchronous error. */
 int shady_flush(shady_ctx *ctx);

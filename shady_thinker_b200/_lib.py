@@ -18,6 +18,7 @@ F32, F16, BF16 = 0, 1, 2
 EXPORTS = [
     "shady_ctx_create", "shady_ctx_destroy", "shady_last_error", "shady_ctx_stream", "shady_ctx_launch_count",
     "shady_buffer_create", "shady_buffer_free", "shady_buffer_write", "shady_buffer_read", "shady_buffer_copy",
+    "shady_host_device_ptr",
     "shady_flush", "shady_synchronize", "shady_kv_append_rope", "shady_decode_workspace_size", "shady_decode_workspace_init",
     "shady_attn_decode", "shady_attn_decode_static", "shady_attn_decode_shard", "shady_attn_decode_append", "shady_attn_decode_partials", "shady_attn_reduce", "shady_attn_prefill",
     "shady_sigmoid_mul", "shady_fill_randn", "shady_ipc_export", "shady_ipc_open", "shady_ipc_close",
@@ -82,6 +83,7 @@ def load() -> C.CDLL:
     L.shady_buffer_write.argtypes = [vp, vp, sz, vp, sz]
     L.shady_buffer_read.argtypes = [vp, vp, sz, vp, sz]
     L.shady_buffer_copy.argtypes = [vp, vp, vp, sz]
+    L.shady_host_device_ptr.argtypes = [vp, vp, C.POINTER(vp)]
     L.shady_flush.argtypes = [vp]
     L.shady_synchronize.argtypes = [vp]
     L.shady_kv_append_rope.argtypes = [vp, C.POINTER(AppendParams), vp, vp, vp, vp, f32p, C.POINTER(KvCache), vp,

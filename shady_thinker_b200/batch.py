@@ -114,6 +114,25 @@ class BatchedDecoder:
                                has_gate=self.has_gate, seq_lens_host=self.lens_after, workspace=self.ws,
                                workspace_bytes=self.ws_bytes, num_splits=self.num_splits)
 
+    def step_from_pinned(self, q_host: int, k_host: int, v_host: int, out_host: int, layer: int = 0) -> None:
+        """Full step on page-locked host buffers without copies: the fused launch reads the activations from host
+        memory and writes the output rows there itself (the bytes still cross the host link, inside the kernel);
+        returns when the output has arrived.  16-bit caches only (needs the fused launch)."""
+        if not self.fused:
+            raise ValueError("step_from_pinned needs the fused append+attend launch (16-bit cache, interleaved RoPE)")
+        key = (q_host, k_host, v_host, out_host)
+        if getattr(self, "_pinned_key", None) != key:
+            self._pinned = tuple(self.gpu.host_device_ptr(a) for a in key)
+            self._pinned_key = key
+        dq, dk, dv, do = self._pinned
+        ops.attn_decode_append(self.gpu, q_proj_full=dq, k_proj=dk, v_proj=dv, cache=self.views[layer],
+                               seq_lens=self.lens, out=do, num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.hd,
+                               rope_theta=self.theta, rotary_dim=self.rd, num_seqs=self.S, eps=self.eps,
+                               qk_norm_bf16=self.qk_norm, in_dtype=self.act_dtype, out_dtype=self.act_dtype,
+                               has_gate=self.has_gate, seq_lens_host=self.lens_after, workspace=self.ws,
+                               workspace_bytes=self.ws_bytes, num_splits=self.num_splits)
+        self.gpu.synchronize()
+
     def step_from_host(self, q_host: int, k_host: int, v_host: int, out_host: int, layer: int = 0) -> None:
         """Full step with host buffers (addresses of pinned memory): H2D activations, append, attend,
         D2H output; returns when the output has arrived."""

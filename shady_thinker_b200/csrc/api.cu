@@ -146,6 +146,17 @@ int shady_buffer_copy(shady_ctx *ctx, const void *d_src, void *d_dst, size_t byt
     if (bytes) SHADY_CUDA_OK(ctx, cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     return SHADY_OK;
 }
+int shady_host_device_ptr(shady_ctx *ctx, const void *host_ptr, void **d_ptr) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, host_ptr && d_ptr, SHADY_ERR_BAD_ARG, "host_device_ptr: null argument");
+    *d_ptr = nullptr;
+    cudaPointerAttributes at{};
+    SHADY_CUDA_OK(ctx, cudaPointerGetAttributes(&at, host_ptr));
+    SHADY_REQUIRE(ctx, at.type == cudaMemoryTypeHost && at.devicePointer, SHADY_ERR_BAD_ARG,
+                  "host_device_ptr: not page-locked host memory the device can address");
+    *d_ptr = at.devicePointer;
+    return SHADY_OK;
+}
 int shady_flush(shady_ctx *ctx) {
     CTX_ENTER(ctx);
     const cudaError_t e = cudaStreamQuery(ctx->stream);

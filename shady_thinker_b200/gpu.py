@@ -121,6 +121,12 @@ class GpuContext:
     def copy_buffer(self, src, dst, size: int) -> None:
         self._check(self._L.shady_buffer_copy(self.handle, C.c_void_p(_addr(src)), C.c_void_p(_addr(dst)), size))
 
+    def host_device_ptr(self, host_addr: int) -> int:
+        """Device-side address of page-locked host memory (zero-copy alternative to write_buffer/read_buffer)."""
+        out = C.c_void_p()
+        self._check(self._L.shady_host_device_ptr(self.handle, C.c_void_p(host_addr), C.byref(out)))
+        return int(out.value)
+
     def flush(self) -> None:
         self._check(self._L.shady_flush(self.handle))
 

@@ -72,3 +72,38 @@ def test_cache_slot_swap_keeps_two_sequences_apart(gpu_ctx, oracle):
         m2.seq_len += 1
     ref = np.frombuffer(gpu_ctx.read_buffer(m2.state.attn_output, 4 * 64 * 4), np.float32)
     np.testing.assert_array_equal(outs["a2"], ref)
+
+
+def test_step_from_pinned_equals_step_from_host(gpu_ctx):
+    """The zero-copy step (kernel reads activations from, and writes the output to, page-locked host memory)
+    gives the bytes of the copy-based step; pageable memory is refused with a status, not a fault."""
+    import torch
+    from shady_thinker_b200 import ops
+    from shady_thinker_b200._lib import F16, ShadyError
+    from shady_thinker_b200.batch import BatchedDecoder
+    S, nh, nkv, hd = 5, 8, 2, 128
+    lens = np.array([17, 300, 1, 64, 1000], np.uint32)
+
+    def make():
+        d = BatchedDecoder(gpu_ctx, num_seqs=S, capacities=lens + 4, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                           kv_dtype=F16, rope_theta=1e6, rotary_dim=hd // 4, has_gate=True, num_splits=0)
+        d.set_lengths(lens - 1)
+        n = d.layer_bytes // 2
+        ops.fill_randn(gpu_ctx, d.k_cache[0], n, F16, 7, 1)
+        ops.fill_randn(gpu_ctx, d.v_cache[0], n, F16, 7, 2)
+        return d
+
+    g = torch.Generator().manual_seed(3)
+    hq = torch.randn(S * nh * hd * 2, generator=g).half().pin_memory()
+    hk = torch.randn(S * nkv * hd, generator=g).half().pin_memory()
+    hv = torch.randn(S * nkv * hd, generator=g).half().pin_memory()
+    out_a = torch.zeros(S * nh * hd, dtype=torch.float16).pin_memory()
+    out_b = torch.zeros(S * nh * hd, dtype=torch.float16).pin_memory()
+    make().step_from_host(hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), out_a.data_ptr())
+    make().step_from_pinned(hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), out_b.data_ptr())
+    assert torch.isfinite(out_a.float()).all() and out_a.abs().sum() > 0
+    assert torch.equal(out_a, out_b)
+    pageable = torch.zeros(16)
+    with pytest.raises(ShadyError) as e:
+        gpu_ctx.host_device_ptr(pageable.data_ptr())
+    assert e.value.code == 1
