@@ -93,7 +93,16 @@ int shady_synchronize(shady_ctx *ctx);
 /* Each sequence's cache is rows [pos][num_kv_heads][head_dim], contiguous, K and V in
  * separate buffers — the reference layout (gqa_attention_head.wgsl:64,
  * fused_split_qknorm_kvstore.wgsl:220).  Sequence s lives at d_k_ptrs[s] when the pointer
- * arrays are given, else at d_k_base + s * seq_stride elements. */
+ * arrays are given, else at d_k_base + s * seq_stride elements.
+ *
+ * Paged cache (no reference counterpart: the reference reserves max_seq_len rows per layer up
+ * front, model.rs:241-256): with d_page_table set, d_k_base / d_v_base are pools of pages
+ * [page][page_rows][num_kv_heads][head_dim] and row r of sequence s is row r % page_rows of
+ * page d_page_table[s * max_pages_per_seq + r / page_rows]; page_rows is a multiple of 16.
+ * Sequences then grow a page at a time and share one pool.  Paged 16-bit caches are taken by
+ * shady_kv_append_rope, shady_attn_decode / _static / _shard (num_splits 0 or 1) and
+ * shady_attn_decode_append; the other entry points return SHADY_ERR_UNSUPPORTED for them.
+ * Zero the struct before filling it: fields added later default to "off". */
 typedef struct {
     void *d_k_base;
     void *d_v_base;
@@ -101,6 +110,10 @@ typedef struct {
     void *const *d_k_ptrs;   /* device array [num_seqs] of device pointers, or NULL */
     void *const *d_v_ptrs;
     uint32_t dtype;          /* SHADY_F32 / SHADY_F16 / SHADY_BF16 */
+    uint32_t page_rows;      /* paged: rows per page (multiple of 16); else 0 */
+    const uint32_t *d_page_table;   /* paged: device array [num_seqs][max_pages_per_seq]; else NULL */
+    uint32_t max_pages_per_seq;
+    uint32_t _pad;
 } shady_kv_cache;
 
 /* ===================================================================================== */

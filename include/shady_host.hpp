@@ -65,6 +65,12 @@ public:
     }
     // gpu.rs:245
     void copy_buffer(const Buffer &src, const Buffer &dst, size_t size) { check(shady_buffer_copy(ctx_, src.ptr, dst.ptr, size)); }
+    // no gpu.rs counterpart: device-side address of page-locked host memory (zero-copy instead of write/read_buffer)
+    void *host_device_ptr(const void *pinned_host) {
+        void *d = nullptr;
+        check(shady_host_device_ptr(ctx_, pinned_host, &d));
+        return d;
+    }
     // gpu.rs:237
     void flush() { check(shady_flush(ctx_)); }
     void synchronize() { check(shady_synchronize(ctx_)); }

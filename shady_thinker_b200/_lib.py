@@ -34,7 +34,9 @@ class ShadyError(RuntimeError):
 
 class KvCache(C.Structure):
     _fields_ = [("d_k_base", C.c_void_p), ("d_v_base", C.c_void_p), ("seq_stride", C.c_uint64),
-                ("d_k_ptrs", C.c_void_p), ("d_v_ptrs", C.c_void_p), ("dtype", C.c_uint32)]
+                ("d_k_ptrs", C.c_void_p), ("d_v_ptrs", C.c_void_p), ("dtype", C.c_uint32),
+                ("page_rows", C.c_uint32), ("d_page_table", C.c_void_p), ("max_pages_per_seq", C.c_uint32),
+                ("_pad", C.c_uint32)]
 
 
 class AppendParams(C.Structure):

@@ -15,6 +15,30 @@ int fail(shady_ctx *ctx, int code, const std::string &msg) {
     return code;
 }
 
+int fill_kv_addr(shady_ctx *ctx, const shady_kv_cache *cache, uint32_t nkv, uint32_t hd, const char *who, KvAddr *out) {
+    const std::string w(who);
+    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, w + ": bad cache dtype");
+    KvAddr kv{};
+    kv.k_base = (const char *)cache->d_k_base; kv.v_base = (const char *)cache->d_v_base;
+    kv.seq_stride_bytes = cache->seq_stride * dtype_size(cache->dtype);
+    kv.k_ptrs = cache->d_k_ptrs; kv.v_ptrs = cache->d_v_ptrs;
+    if (cache->d_page_table) {
+        SHADY_REQUIRE(ctx, cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs && !cache->d_v_ptrs, SHADY_ERR_BAD_ARG,
+                      w + ": a paged cache takes the two pool bases and no pointer arrays");
+        SHADY_REQUIRE(ctx, cache->page_rows && cache->page_rows % 16 == 0 && cache->max_pages_per_seq, SHADY_ERR_BAD_ARG,
+                      w + ": page_rows must be a positive multiple of 16 and max_pages_per_seq positive");
+        SHADY_REQUIRE(ctx, cache->dtype != SHADY_F32, SHADY_ERR_UNSUPPORTED, w + ": paged caches are 16-bit");
+        kv.page_table = cache->d_page_table;
+        kv.page_rows = cache->page_rows; kv.max_pages = cache->max_pages_per_seq;
+        kv.page_bytes = (unsigned long long)cache->page_rows * nkv * hd * dtype_size(cache->dtype);
+    } else {
+        SHADY_REQUIRE(ctx, (cache->d_k_ptrs && cache->d_v_ptrs) || (cache->d_k_base && cache->d_v_base), SHADY_ERR_BAD_ARG,
+                      w + ": cache needs base pointers or pointer arrays");
+    }
+    *out = kv;
+    return SHADY_OK;
+}
+
 // launchers implemented in the kernel translation units
 size_t decode_workspace_bytes(const shady_decode_params *p);
 int init_decode_workspace(shady_ctx *, const shady_decode_params *, void *, size_t);

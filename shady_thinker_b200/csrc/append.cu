@@ -21,9 +21,7 @@ struct AppendArgs {
     const void *v_in;
     void *q_out;
     float *q_gate;
-    char *k_base, *v_base;
-    unsigned long long seq_stride_bytes;
-    void *const *k_ptrs, *const *v_ptrs;
+    KvAddr kv;                // where the cache rows go (per-sequence bases, pointer arrays or pages)
     const uint16_t *norm_w;   // bf16 bits: q[hd] then k[hd]; NULL = no norm
     const uint32_t *pos_start, *pos_h, *pos_w;
     uint32_t nh, nkv, hd;
@@ -107,11 +105,11 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(const AppendA
         for (uint32_t d = lane; d < hd; d += 32) store_from_f32(a.q_out, row + d, a.q_dtype, vals[d]);
     } else {
         const size_t esz = a.kv_dtype == SHADY_F32 ? 4 : 2;
-        char *kc = a.k_ptrs ? reinterpret_cast<char *>(a.k_ptrs[s]) : a.k_base + a.seq_stride_bytes * s;
-        char *vc = a.v_ptrs ? reinterpret_cast<char *>(a.v_ptrs[s]) : a.v_base + a.seq_stride_bytes * s;
-        const size_t crow = ((size_t)p_t * a.nkv + kh) * hd;   // cache_position == position (model.rs:493-496)
+        // cache_position == position (model.rs:493-496)
+        char *kc = const_cast<char *>(kv_row_ptr(a.kv, false, s, p_t, (size_t)a.nkv * hd * esz));
+        char *vc = const_cast<char *>(kv_row_ptr(a.kv, true, s, p_t, (size_t)a.nkv * hd * esz));
+        const size_t crow = (size_t)kh * hd;
         const size_t row = (tok * a.nkv + kh) * (size_t)hd;
-        (void)esz;
         for (uint32_t d = lane; d < hd; d += 32) {
             const float kv = vals[d];
             if (a.write_k_back) store_from_f32(a.k_io, row + d, a.in_dtype, kv);
@@ -227,10 +225,9 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
     // ---- K heads (+ V copy) ----
     TIn *k_io = reinterpret_cast<TIn *>(a.k_io) + tok * a.nkv * (size_t)HD;
     const TIn *v_in = reinterpret_cast<const TIn *>(a.v_in) + tok * a.nkv * (size_t)HD;
-    char *kc = a.k_ptrs ? reinterpret_cast<char *>(a.k_ptrs[s]) : a.k_base + a.seq_stride_bytes * s;
-    char *vc = a.v_ptrs ? reinterpret_cast<char *>(a.v_ptrs[s]) : a.v_base + a.seq_stride_bytes * s;
-    TKV *k_row = reinterpret_cast<TKV *>(kc) + (size_t)p_t * a.nkv * HD;   // cache_position == position (model.rs:493-496)
-    TKV *v_row = reinterpret_cast<TKV *>(vc) + (size_t)p_t * a.nkv * HD;
+    // cache_position == position (model.rs:493-496)
+    TKV *k_row = reinterpret_cast<TKV *>(const_cast<char *>(kv_row_ptr(a.kv, false, s, p_t, (size_t)a.nkv * HD * sizeof(TKV))));
+    TKV *v_row = reinterpret_cast<TKV *>(const_cast<char *>(kv_row_ptr(a.kv, true, s, p_t, (size_t)a.nkv * HD * sizeof(TKV))));
     for (uint32_t kh0 = slice * HPI; kh0 < a.nkv; kh0 += HPI * a.head_slices) {
         const uint32_t kh = kh0 + sub;
         const bool valid = kh < a.nkv;
@@ -266,8 +263,8 @@ static bool try_append_fast(shady_ctx *ctx, AppendArgs &a, const void *q_in, con
                             const void *q_out) {
     if (!(a.hd == 128 || a.hd == 256) || !a.interleaved || (a.rd % 2)) return false;
     if ((unsigned long long)a.num_seqs * a.T > 0x3fffffffull) return false;
-    if ((((uintptr_t)q_in | (uintptr_t)k_io | (uintptr_t)v_in | (uintptr_t)q_out | (uintptr_t)a.q_gate | (uintptr_t)a.k_base |
-          (uintptr_t)a.v_base) & 15) || (a.seq_stride_bytes & 15))
+    if ((((uintptr_t)q_in | (uintptr_t)k_io | (uintptr_t)v_in | (uintptr_t)q_out | (uintptr_t)a.q_gate | (uintptr_t)a.kv.k_base |
+          (uintptr_t)a.kv.v_base) & 15) || (a.kv.seq_stride_bytes & 15) || (a.kv.page_bytes & 15))
         return false;   // 16-byte vector accesses (per-sequence pointers are required to be 16-byte aligned too)
     const uint32_t i = a.in_dtype, q = a.q_dtype, k = a.kv_dtype;
     if (i == SHADY_F32 && q == SHADY_F32 && k == SHADY_F32) launch_append_fast<float, float, float>(ctx, a);
@@ -297,9 +294,7 @@ int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_
                   SHADY_ERR_BAD_ARG, "kv_append_rope: cache has neither base pointers nor pointer arrays");
     AppendArgs a{};
     a.q_in = d_q_proj_full; a.k_io = d_k_proj; a.v_in = d_v_proj; a.q_out = d_q_out; a.q_gate = d_q_gate;
-    a.k_base = (char *)cache->d_k_base; a.v_base = (char *)cache->d_v_base;
-    a.seq_stride_bytes = cache->seq_stride * dtype_size(cache->dtype);
-    a.k_ptrs = cache->d_k_ptrs; a.v_ptrs = cache->d_v_ptrs;
+    if (const int st = fill_kv_addr(ctx, cache, p->num_kv_heads, p->head_dim, "kv_append_rope", &a.kv)) return st;
     a.norm_w = d_qk_norm_bf16;
     a.pos_start = d_pos_start; a.pos_h = d_pos_h; a.pos_w = d_pos_w;
     a.nh = p->num_heads; a.nkv = p->num_kv_heads; a.hd = p->head_dim; a.eps = p->eps;

@@ -79,10 +79,25 @@ struct KvAddr {
     unsigned long long seq_stride_bytes;
     const void *const *k_ptrs;
     const void *const *v_ptrs;
+    // paged cache: k_base / v_base are page pools, page_table [num_seqs][max_pages], page_bytes = one page of K (or V)
+    const uint32_t *page_table;
+    unsigned long long page_bytes;
+    uint32_t page_rows, max_pages;
 };
 __device__ __forceinline__ const char *kv_seq_ptr(const char *base, const void *const *ptrs,
                                                   unsigned long long stride_bytes, uint32_t s) {
     return ptrs ? reinterpret_cast<const char *>(ptrs[s]) : base + stride_bytes * s;
 }
+// Address of cache row `pos` (all kv heads, row_bytes = nkv * hd * element size) of sequence s, paged or not.
+__device__ __forceinline__ const char *kv_row_ptr(const KvAddr &kv, bool want_v, uint32_t s, uint32_t pos, size_t row_bytes) {
+    if (kv.page_table) {
+        const uint32_t pg = kv.page_table[(size_t)s * kv.max_pages + pos / kv.page_rows];
+        return (want_v ? kv.v_base : kv.k_base) + (size_t)pg * kv.page_bytes + (size_t)(pos % kv.page_rows) * row_bytes;
+    }
+    return kv_seq_ptr(want_v ? kv.v_base : kv.k_base, want_v ? kv.v_ptrs : kv.k_ptrs, kv.seq_stride_bytes, s) +
+           (size_t)pos * row_bytes;
+}
+// Checks a caller's cache description and turns it into the device-side form (defined in api.cu).
+int fill_kv_addr(shady_ctx *ctx, const shady_kv_cache *cache, uint32_t nkv, uint32_t hd, const char *who, KvAddr *out);
 
 }  // namespace shady

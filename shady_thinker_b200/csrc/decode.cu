@@ -430,8 +430,11 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
     Piece p;
     while (next_piece(a, cur, p)) {
         const uint32_t start = p.start, end = p.end;
-        const char *kbase = kv_seq_ptr(a.kv.k_base, a.kv.k_ptrs, a.kv.seq_stride_bytes, p.seq) + (size_t)kvh * S::kRowBytes;
-        const char *vbase = kv_seq_ptr(a.kv.v_base, a.kv.v_ptrs, a.kv.seq_stride_bytes, p.seq) + (size_t)kvh * S::kRowBytes;
+        // paged cache: kbase/vbase are the pools and every 16-row block takes its page number from the table; the
+        // number of the warp's next block is fetched one block ahead so that its latency never meets a cp.async
+        const uint32_t *ptab = a.kv.page_table ? a.kv.page_table + (size_t)p.seq * a.kv.max_pages : nullptr;
+        const char *kbase = (ptab ? a.kv.k_base : kv_seq_ptr(a.kv.k_base, a.kv.k_ptrs, a.kv.seq_stride_bytes, p.seq)) + (size_t)kvh * S::kRowBytes;
+        const char *vbase = (ptab ? a.kv.v_base : kv_seq_ptr(a.kv.v_base, a.kv.v_ptrs, a.kv.seq_stride_bytes, p.seq)) + (size_t)kvh * S::kRowBytes;
         const uint32_t nblk = (end - start + kBlk - 1) / kBlk;
         const uint32_t my_n = nblk > sub ? (nblk - sub + WPK - 1) / WPK : 0;
         // The pipeline moves single tiles: item 2i is the K tile of the warp's i-th block, item 2i+1 its V tile,
@@ -455,15 +458,27 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             }
             __syncwarp();
         };
-        auto issue = [&](uint32_t t) {
+        uint32_t pg_cur = 0, pg_nxt = 0;
+        auto page_of_block = [&](uint32_t bi) {
+            const uint32_t pos0 = start + (sub + bi * WPK) * kBlk;
+            return pos0 < end ? ptab[pos0 / a.kv.page_rows] : 0u;
+        };
+        if (ptab) pg_nxt = page_of_block(0);
+        auto issue = [&](uint32_t t) {   // called with t = 0, 1, 2, ... in order: the K tile of a block, then its V tile
             const uint32_t pos0 = start + (sub + (t >> 1) * WPK) * kBlk;
             const uint32_t st = warp_smem + (t % STAGES) * S::kTileBytes;
             const char *src = (t & 1) ? vbase : kbase;
+            uint32_t row0_src = pos0;     // row of the block's first position relative to src
+            if (ptab) {
+                if (!(t & 1)) { pg_cur = pg_nxt; pg_nxt = page_of_block((t >> 1) + 1); }
+                src += (size_t)pg_cur * a.kv.page_bytes;
+                row0_src = pos0 % a.kv.page_rows;
+            }
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
                 const uint32_t r = i * RPI + l_row;
                 const bool ok = pos0 + r < end;
-                const size_t goff = (size_t)(pos0 + r) * pos_stride + l_chunk * 16;
+                const size_t goff = (size_t)(row0_src + r) * pos_stride + l_chunk * 16;
                 const uint32_t soff = r * S::kRowBytes + ((l_chunk ^ (r & 7)) << 4);
                 cp_async16(st + soff, src + (ok ? goff : 0), ok);
             }
@@ -513,8 +528,10 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
                 }
                 newrow[it].x = pack2<T>(v8[0], v8[1]); newrow[it].y = pack2<T>(v8[2], v8[3]);
                 newrow[it].z = pack2<T>(v8[4], v8[5]); newrow[it].w = pack2<T>(v8[6], v8[7]);
-                if (act)
-                    *reinterpret_cast<uint4 *>(const_cast<char *>(is_v ? vbase : kbase) + (size_t)pos * pos_stride + c * 16) = newrow[it];
+                if (act) {
+                    char *dst = const_cast<char *>(kv_row_ptr(a.kv, is_v != 0, p.seq, pos, pos_stride)) + (size_t)kvh * S::kRowBytes;
+                    *reinterpret_cast<uint4 *>(dst + c * 16) = newrow[it];
+                }
             }
         }
         // stage Q of the CTA's kv heads (rows >= rows_valid are zero) as T, swizzled
@@ -1040,9 +1057,9 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
 
     DecodeArgs a{};
     a.q = d_q; a.out = d_out; a.lse = d_lse; a.gate = d_gate;
-    a.kv.k_base = (const char *)cache->d_k_base; a.kv.v_base = (const char *)cache->d_v_base;
-    a.kv.seq_stride_bytes = cache->seq_stride * dtype_size(cache->dtype);
-    a.kv.k_ptrs = cache->d_k_ptrs; a.kv.v_ptrs = cache->d_v_ptrs;
+    if (const int st = fill_kv_addr(ctx, cache, p->num_kv_heads, hd, "decode", &a.kv)) return st;
+    SHADY_REQUIRE(ctx, !a.kv.page_table || p->num_splits <= 1, SHADY_ERR_UNSUPPORTED,
+                  "decode: a paged cache needs num_splits 0 or 1 (16-row blocks must not straddle pages)");
     a.seq_lens = d_seq_lens;
     a.num_seqs = p->num_seqs; a.nkv = p->num_kv_heads; a.nh = p->num_q_heads; a.G = p->heads_per_kv; a.hd = hd;
     a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;
@@ -1215,9 +1232,9 @@ int launch_decode_static(shady_ctx *ctx, const shady_decode_params *p, const voi
 
     DecodeArgs a{};
     a.q = d_q; a.out = d_out; a.lse = d_lse; a.gate = d_gate;
-    a.kv.k_base = (const char *)cache->d_k_base; a.kv.v_base = (const char *)cache->d_v_base;
-    a.kv.seq_stride_bytes = cache->seq_stride * dtype_size(cache->dtype);
-    a.kv.k_ptrs = cache->d_k_ptrs; a.kv.v_ptrs = cache->d_v_ptrs;
+    if (const int st = fill_kv_addr(ctx, cache, p->num_kv_heads, hd, "decode", &a.kv)) return st;
+    SHADY_REQUIRE(ctx, !a.kv.page_table || p->num_splits <= 1, SHADY_ERR_UNSUPPORTED,
+                  "decode: a paged cache needs num_splits 0 or 1 (16-row blocks must not straddle pages)");
     a.seq_lens = d_seq_lens;
     a.num_seqs = p->num_seqs; a.nkv = p->num_kv_heads; a.nh = p->num_q_heads; a.G = p->heads_per_kv; a.hd = hd;
     a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;

@@ -605,8 +605,8 @@ int launch_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_
     SHADY_REQUIRE(ctx, cache->dtype == p->dtype, SHADY_ERR_UNSUPPORTED, "attn_prefill: cache dtype must equal the Q dtype");
     SHADY_REQUIRE(ctx, p->num_seqs && p->seq_len && p->num_kv_heads && p->num_q_heads % p->num_kv_heads == 0, SHADY_ERR_BAD_ARG,
                   "attn_prefill: bad shape");
-    SHADY_REQUIRE(ctx, cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs, SHADY_ERR_UNSUPPORTED,
-                  "attn_prefill: needs base + seq_stride cache addressing (TMA tensor maps)");
+    SHADY_REQUIRE(ctx, cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs && !cache->d_page_table, SHADY_ERR_UNSUPPORTED,
+                  "attn_prefill: needs base + seq_stride cache addressing (TMA tensor maps), not pointer arrays or pages");
     SHADY_REQUIRE(ctx, p->num_seqs == 1 || cache->seq_stride >= (uint64_t)p->seq_len * p->num_kv_heads * 128, SHADY_ERR_BAD_ARG,
                   "attn_prefill: seq_stride smaller than one sequence");
     SHADY_REQUIRE(ctx, ((uintptr_t)d_q | (uintptr_t)cache->d_k_base | (uintptr_t)cache->d_v_base | (uintptr_t)d_out) % 16 == 0 &&

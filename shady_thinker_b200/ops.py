@@ -38,10 +38,14 @@ class KvCacheView:
     seq_stride: int = 0          # elements
     k_ptrs: object = None        # device array of device pointers (uint64) [num_seqs]
     v_ptrs: object = None
+    page_table: object = None    # paged cache: device u32 [num_seqs][max_pages_per_seq]; k_base / v_base are the pools
+    page_rows: int = 0
+    max_pages_per_seq: int = 0
 
     def c_struct(self) -> KvCache:
         return KvCache(_addr(self.k_base) or None, _addr(self.v_base) or None, self.seq_stride,
-                       _addr(self.k_ptrs) or None, _addr(self.v_ptrs) or None, self.dtype)
+                       _addr(self.k_ptrs) or None, _addr(self.v_ptrs) or None, self.dtype, self.page_rows,
+                       _addr(self.page_table) or None, self.max_pages_per_seq, 0)
 
 
 def kv_append_rope(gpu: GpuContext, *, q_proj_full, k_proj, v_proj, q_out, q_gate, cache: KvCacheView, pos_start,
