@@ -628,8 +628,11 @@ def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
         ws = torch.zeros(ws_n, dtype=torch.uint8, device="cuda")
         views = [ops.KvCacheView(BF16, ks[i], vs[i], 0) for i in range(n_sets)]
         ev = []
-        # merge across ranks: the fused peer-memory kernel, or (SHADY_CFG4_COMBINE=nccl) all-gather + merge kernel
-        use_nccl = os.environ.get("SHADY_CFG4_COMBINE", "p2p") == "nccl"
+        # merge across ranks (SHADY_CFG4_COMBINE): "fused" = decode, then one kernel that merges the rank's records,
+        # exchanges over NVLink and merges across ranks; "p2p" = decode, rank-local merge, exchange+merge kernel;
+        # "nccl" = decode, rank-local merge, all-gather, merge kernel
+        mode = os.environ.get("SHADY_CFG4_COMBINE", "fused")
+        use_nccl = mode == "nccl"
         comb = None
         if world > 1 and not use_nccl:
             from shady_thinker_b200.p2p import ShardCombiner
@@ -647,6 +650,13 @@ def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
             else:
                 a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
                 a.record(stream)
+                if comb is not None and mode == "fused":
+                    comb.decode_and_combine(q=q, cache=view, seq_lens=lens, seq_len_host=rows, records=rec, out=out,
+                                            num_kv_heads=nkv, q_dtype=BF16, workspace=ws, workspace_bytes=ws_n)
+                    b.record(stream)
+                    if timed:
+                        ev.append((a, b))
+                    return
                 ops.attn_decode_shard(gpu, q=q, cache=view, seq_lens=lens, records=rec, head_dim=hd, num_kv_heads=nkv,
                                       num_q_heads=nh, num_splits=0, seq_lens_host=[rows], q_dtype=BF16, workspace=ws,
                                       workspace_bytes=ws_n)
@@ -688,10 +698,13 @@ def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
             "config": {"workload": "cfg4: long-context single-sequence decode, rows split over GPUs, LSE merge over NCCL",
                        "context": L, "num_q_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "kv_dtype": "bf16",
                        "rows_per_gpu": rows, "combine": "none" if world == 1 else ("NCCL all-gather of 16.5 KB records + merge kernel" if use_nccl else
-                                   "one kernel: peer stores of 16.5 KB records over NVLink + flags + merge"),
+                                   ("two launches per step: decode, then one kernel = rank-local merge + peer stores over NVLink + flags + merge"
+                                    if mode == "fused" else "one kernel: peer stores of 16.5 KB records over NVLink + flags + merge")),
                        "l2": f"{n_sets} cache sets rotate between steps"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                         "peak_source": f"{src} (copy bandwidth)", "kernel": "decode16_kernel<bf16,256> on this rank's rows",
+                         "peak_source": f"{src} (copy bandwidth)",
+                         "kernel": ("decode16_kernel<bf16,256> on this rank's rows + merge/exchange kernel (the rank's whole step)"
+                                    if world > 1 and mode == "fused" and not use_nccl else "decode16_kernel<bf16,256> on this rank's rows"),
                          "algorithmic_bytes_per_launch": 2.0 * rows * row_bytes, "avg_launch_ms": dec_ms},
             "gpu_launches": int(launches)}), flush=True)
     if comb is not None:

@@ -244,6 +244,17 @@ int shady_combine_p2p_buffer_size(uint32_t world, uint32_t num_heads, uint32_t h
 int shady_attn_combine_p2p(shady_ctx *ctx, uint32_t world, uint32_t rank, uint32_t num_heads, uint32_t head_dim,
                            uint32_t epoch, void *const *d_peer_table, const float *d_records, void *d_out,
                            uint32_t out_dtype, const float *d_gate);
+/* The whole sharded step in two launches: the decode kernel over this rank's rows, then ONE kernel that merges
+ * the rank's split records, stores the result into every peer's exchange buffer, raises per-(head, 64-dim chunk)
+ * flags, waits (bounded) for the peers' flags and merges across ranks into d_out[nh][hd] — the work of
+ * shady_attn_decode_shard + shady_attn_combine_p2p with one launch and one pass over the records less.
+ * Arguments as in those two calls (one sequence, num_splits == 0; d_records [nh][hd+2] is scratch).  An exchange
+ * buffer serves either this call or shady_attn_combine_p2p, not both in turn. */
+int shady_attn_decode_shard_p2p(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
+                                const shady_kv_cache *cache, const uint32_t *d_seq_lens,
+                                const uint32_t *seq_lens_host, uint32_t world, uint32_t rank, uint32_t epoch,
+                                void *const *d_peer_table, float *d_records, void *d_out, uint32_t out_dtype,
+                                const float *d_gate, void *d_workspace, size_t workspace_bytes);
 
 /* No counterpart in the reference.  The same decode as shady_attn_decode for callers that cannot
  * hand over a workspace: a server that gave all device memory to its KV-cache arena at start-up, or

@@ -22,7 +22,7 @@ EXPORTS = [
     "shady_flush", "shady_synchronize", "shady_kv_append_rope", "shady_decode_workspace_size", "shady_decode_workspace_init",
     "shady_attn_decode", "shady_attn_decode_static", "shady_attn_decode_shard", "shady_attn_decode_append", "shady_attn_decode_partials", "shady_attn_reduce", "shady_attn_prefill",
     "shady_sigmoid_mul", "shady_fill_randn", "shady_ipc_export", "shady_ipc_open", "shady_ipc_close",
-    "shady_combine_p2p_buffer_size", "shady_attn_combine_p2p",
+    "shady_combine_p2p_buffer_size", "shady_attn_combine_p2p", "shady_attn_decode_shard_p2p",
 ]
 
 
@@ -110,6 +110,9 @@ def load() -> C.CDLL:
     L.shady_combine_p2p_buffer_size.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(sz)]
     L.shady_attn_combine_p2p.argtypes = [vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp, f32p, vp,
                                          C.c_uint32, f32p]
+    L.shady_attn_decode_shard_p2p.argtypes = [vp, C.POINTER(DecodeParams), vp, C.POINTER(KvCache), u32p,
+                                              C.POINTER(C.c_uint32), C.c_uint32, C.c_uint32, C.c_uint32, vp, f32p, vp,
+                                              C.c_uint32, f32p, vp, sz]
     L.shady_sigmoid_mul.argtypes = [vp, f32p, f32p, C.c_uint32]
     L.shady_fill_randn.argtypes = [vp, vp, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint64]
     for name in EXPORTS:

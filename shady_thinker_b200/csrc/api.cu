@@ -43,11 +43,18 @@ int fill_kv_addr(shady_ctx *ctx, const shady_kv_cache *cache, uint32_t nkv, uint
 size_t decode_workspace_bytes(const shady_decode_params *p);
 int init_decode_workspace(shady_ctx *, const shady_decode_params *, void *, size_t);
 int launch_decode(shady_ctx *, const shady_decode_params *, const void *, const shady_kv_cache *, const uint32_t *,
-                  const uint32_t *, void *, float *, const float *, void *, size_t, float *, float *, const struct FusedAppendIn *);
+                  const uint32_t *, void *, float *, const float *, void *, size_t, float *, float *, const struct FusedAppendIn *,
+                  const struct ShardExchangeIn *);
 struct FusedAppendIn {
     const shady_append_params *ap;
     const void *q_full, *k_proj, *v_proj;
     const uint16_t *norm_w;
+};
+struct ShardExchangeIn {
+    uint32_t world, rank, epoch, out_dtype;
+    void *const *d_peer_table;
+    void *d_out;
+    const float *d_gate;
 };
 int launch_decode_static(shady_ctx *, const shady_decode_params *, const void *, const shady_kv_cache *, const uint32_t *,
                          const uint32_t *, void *, float *, const float *);
@@ -222,7 +229,7 @@ int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *
                       const float *d_gate, void *d_workspace, size_t workspace_bytes) {
     CTX_ENTER(ctx);
     return launch_decode(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, d_out, d_lse, d_gate, d_workspace,
-                         workspace_bytes, nullptr, nullptr, nullptr);
+                         workspace_bytes, nullptr, nullptr, nullptr, nullptr);
 }
 
 int shady_attn_decode_static(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
@@ -240,7 +247,7 @@ int shady_attn_decode_append(shady_ctx *ctx, const shady_append_params *ap, cons
     CTX_ENTER(ctx);
     FusedAppendIn fa{ap, d_q_proj_full, d_k_proj, d_v_proj, d_qk_norm_bf16};
     return launch_decode(ctx, p, nullptr, cache, d_seq_lens, seq_lens_host, d_out, d_lse, nullptr, d_workspace,
-                         workspace_bytes, nullptr, nullptr, &fa);
+                         workspace_bytes, nullptr, nullptr, &fa, nullptr);
 }
 
 int shady_attn_decode_shard(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
@@ -249,14 +256,25 @@ int shady_attn_decode_shard(shady_ctx *ctx, const shady_decode_params *p, const 
     CTX_ENTER(ctx);
     SHADY_REQUIRE(ctx, d_records, SHADY_ERR_BAD_ARG, "decode_shard: null output");
     return launch_decode(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, nullptr, nullptr, nullptr, d_workspace,
-                         workspace_bytes, nullptr, d_records, nullptr);
+                         workspace_bytes, nullptr, d_records, nullptr, nullptr);
+}
+
+int shady_attn_decode_shard_p2p(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
+                                const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, uint32_t world, uint32_t rank,
+                                uint32_t epoch, void *const *d_peer_table, float *d_records, void *d_out, uint32_t out_dtype,
+                                const float *d_gate, void *d_workspace, size_t workspace_bytes) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, d_records && d_out && d_peer_table, SHADY_ERR_BAD_ARG, "decode_shard_p2p: null argument");
+    const ShardExchangeIn px{world, rank, epoch, out_dtype, d_peer_table, d_out, d_gate};
+    return launch_decode(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, nullptr, nullptr, nullptr, d_workspace,
+                         workspace_bytes, nullptr, d_records, nullptr, &px);
 }
 
 int shady_attn_decode_partials(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
                                const shady_kv_cache *cache, const uint32_t *d_seq_lens, float *d_partials) {
     CTX_ENTER(ctx);
     SHADY_REQUIRE(ctx, d_partials, SHADY_ERR_BAD_ARG, "decode_partials: null output");
-    return launch_decode(ctx, p, d_q, cache, d_seq_lens, nullptr, nullptr, nullptr, nullptr, nullptr, 0, d_partials, nullptr, nullptr);
+    return launch_decode(ctx, p, d_q, cache, d_seq_lens, nullptr, nullptr, nullptr, nullptr, nullptr, 0, d_partials, nullptr, nullptr, nullptr);
 }
 
 int shady_attn_reduce(shady_ctx *ctx, uint32_t head_dim, uint32_t num_splits, uint32_t num_heads, uint64_t split_stride,

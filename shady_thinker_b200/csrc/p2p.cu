@@ -11,12 +11,9 @@
 // call ahead of its slowest peer (it needs that peer's flags of the current call to finish), so the buffer it
 // overwrites is never the one a peer is still merging.  Every wait has an iteration limit; on expiry the kernel
 // records an error code and returns, and the next shady_synchronize reports SHADY_ERR_TIMEOUT.
-#include "common.cuh"
+#include "p2p.cuh"
 
 namespace shady {
-
-constexpr uint32_t kP2PSpinLimit = 1u << 22;
-constexpr uint32_t kP2PMaxWorld = 16;
 
 static __device__ int g_p2p_error_word;
 static int *g_p2p_error[64] = {};
@@ -31,21 +28,23 @@ struct P2PArgs {
     unsigned long long flags_bytes;   // size of the flag region at the head of a shared buffer
 };
 
-// shared buffer: flags [2 parities][world][nh] u32 (padded to 256 B), then records [2][world][nh][hd+2] f32
-__host__ __device__ inline unsigned long long p2p_flags_bytes(uint32_t world, uint32_t nh) {
-    return ((unsigned long long)2 * world * nh * sizeof(uint32_t) + 255ull) / 256ull * 256ull;
-}
 unsigned long long p2p_buffer_bytes(uint32_t world, uint32_t nh, uint32_t hd) {
-    return p2p_flags_bytes(world, nh) + (unsigned long long)2 * world * nh * (hd + 2) * sizeof(float);
+    const unsigned long long whole = p2p_flags_bytes(world, nh) + (unsigned long long)2 * world * nh * (hd + 2) * sizeof(float);
+    const unsigned long long chunked = p2p_chunk_flags_bytes(world, nh, hd) +
+                                       (unsigned long long)2 * world * nh * p2p_chunks(hd) * kP2PSlotFloats * sizeof(float);
+    return whole > chunked ? whole : chunked;
 }
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+int p2p_error_word(shady_ctx *ctx, int **out) {
+    SHADY_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, SHADY_ERR_UNSUPPORTED, "combine_p2p: device ordinal out of range");
+    if (!g_p2p_error[ctx->device]) {
+        int *w = nullptr;
+        SHADY_CUDA_OK(ctx, cudaGetSymbolAddress(reinterpret_cast<void **>(&w), g_p2p_error_word));
+        SHADY_CUDA_OK(ctx, cudaMemsetAsync(w, 0, sizeof(int), ctx->stream));
+        g_p2p_error[ctx->device] = w;
+    }
+    *out = g_p2p_error[ctx->device];
+    return SHADY_OK;
 }
 
 __global__ void __launch_bounds__(128) p2p_combine_kernel(const P2PArgs a) {
@@ -111,16 +110,11 @@ int launch_combine_p2p(shady_ctx *ctx, uint32_t world, uint32_t rank, uint32_t n
     SHADY_REQUIRE(ctx, world >= 1 && world <= kP2PMaxWorld && rank < world, SHADY_ERR_BAD_ARG, "combine_p2p: bad world/rank");
     SHADY_REQUIRE(ctx, epoch != 0, SHADY_ERR_BAD_ARG, "combine_p2p: epoch must start at 1 (flags start at 0)");
     SHADY_REQUIRE(ctx, out_dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "combine_p2p: bad out dtype");
-    SHADY_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, SHADY_ERR_UNSUPPORTED, "combine_p2p: device ordinal out of range");
-    if (!g_p2p_error[ctx->device]) {
-        int *w = nullptr;
-        SHADY_CUDA_OK(ctx, cudaGetSymbolAddress(reinterpret_cast<void **>(&w), g_p2p_error_word));
-        SHADY_CUDA_OK(ctx, cudaMemsetAsync(w, 0, sizeof(int), ctx->stream));
-        g_p2p_error[ctx->device] = w;
-    }
+    int *err_word = nullptr;
+    if (const int st = p2p_error_word(ctx, &err_word)) return st;
     P2PArgs a{};
     a.peer_bases = reinterpret_cast<char *const *>(d_peer_table);
-    a.rec = d_rec; a.out = d_out; a.gate = d_gate; a.error = g_p2p_error[ctx->device];
+    a.rec = d_rec; a.out = d_out; a.gate = d_gate; a.error = err_word;
     a.rank = rank; a.world = world; a.nh = nh; a.hd = hd; a.epoch = epoch; a.out_dtype = out_dtype;
     a.flags_bytes = p2p_flags_bytes(world, nh);
     p2p_combine_kernel<<<nh, 128, 0, ctx->stream>>>(a);

@@ -55,6 +55,23 @@ class ShardCombiner:
                                              C.c_void_p(self.table.ptr), _addr(records), _addr(out), out_dtype,
                                              _addr(gate) or None))
 
+    def decode_and_combine(self, *, q, cache, seq_lens, seq_len_host: int, records, out, num_kv_heads: int,
+                           q_dtype: int = _lib.F32, out_dtype: int = _lib.F32, gate=None, workspace=None,
+                           workspace_bytes: int = 0) -> None:
+        """The whole sharded step in two launches (``shady_attn_decode_shard_p2p``): decode over this rank's rows,
+        then one kernel that merges the rank's records, exchanges the result over NVLink and merges across ranks.
+        Do not mix with :meth:`combine` on the same combiner (the exchange buffer is laid out differently)."""
+        from . import ops
+        self.epoch += 1
+        g = self.gpu
+        p = _lib.DecodeParams(self.hd, num_kv_heads, self.nh, self.nh // num_kv_heads, 0, 1, q_dtype, _lib.F32)
+        c = cache.c_struct()
+        hl = (C.c_uint32 * 1)(seq_len_host)
+        g._check(g._L.shady_attn_decode_shard_p2p(g.handle, C.byref(p), _addr(q), C.byref(c), _addr(seq_lens), hl,
+                                                  self.world, self.rank, self.epoch, C.c_void_p(self.table.ptr),
+                                                  _addr(records), _addr(out), out_dtype, _addr(gate) or None,
+                                                  _addr(workspace) or None, workspace_bytes))
+
     def close(self, group=None) -> None:
         if self.world > 1:
             import torch.distributed as dist

@@ -32,6 +32,34 @@ def test_world_of_one_is_a_copy_with_gate(gpu_ctx, oracle):
     comb.close()
 
 
+@pytest.mark.parametrize("L", [100, 20000])
+def test_world_of_one_fused_step_equals_plain_decode(gpu_ctx, oracle, L):
+    """decode + (merge, exchange, merge) in two launches with a world of one gives what shady_attn_decode gives:
+    a single span (record written directly) and many spans (records merged by the exchange kernel)."""
+    from _util import rounded, run_decode
+    from shady_thinker_b200 import ops
+    from shady_thinker_b200.p2p import ShardCombiner
+    nh, nkv, hd = 16, 2, 256
+    q = rounded(oracle, oracle.randn((1, nh, hd), 21, 1), BF16)
+    k = rounded(oracle, oracle.randn((L, nkv, hd), 21, 2), BF16)
+    v = rounded(oracle, oracle.randn((L, nkv, hd), 21, 3), BF16)
+    gate = oracle.randn((nh, hd), 21, 4)
+    view = ops.KvCacheView(BF16, to_dev(k, BF16), to_dev(v, BF16), 0)
+    want = run_decode(gpu_ctx, q, view, [L], nh=nh, nkv=nkv, hd=hd, num_splits=0, q_dt=BF16, gate=to_dev(gate)[None])[0]
+    comb = ShardCombiner(gpu_ctx, rank=0, world=1, num_heads=nh, head_dim=hd)
+    ws_n = ops.decode_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_splits=0, num_seqs=1)
+    ws = torch.zeros(max(ws_n, 4), dtype=torch.uint8, device="cuda")
+    rec = torch.zeros((1, nh, hd + 2), device="cuda")
+    lens = torch.tensor([L], dtype=torch.int32).cuda()
+    for step in range(3):
+        d_out = torch.full((nh, hd), float("nan"), device="cuda")
+        comb.decode_and_combine(q=to_dev(q, BF16), cache=view, seq_lens=lens, seq_len_host=L, records=rec, out=d_out,
+                                num_kv_heads=nkv, q_dtype=BF16, gate=to_dev(gate), workspace=ws, workspace_bytes=ws_n)
+        gpu_ctx.synchronize()
+        assert np.abs(to_host(d_out) - want).max() <= 2e-6 * max(1.0, float(np.abs(want).max()))
+    comb.close()
+
+
 def _rank_main(rank, world, port, q_out):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -72,6 +100,20 @@ def _rank_main(rank, world, port, q_out):
         got = out.cpu().numpy()
         worst = max(worst, float(np.abs(got - ref).max() / np.abs(ref).max()))
     comb.close()
+    # the same step as decode + fused merge/exchange kernel (its own exchange buffer)
+    comb2 = ShardCombiner(gpu, rank=rank, world=world, num_heads=nh, head_dim=hd)
+    for step in range(4):
+        q = O.round_bf16(O.randn((1, nh, hd), 9, 200 + step))
+        d_q = torch.from_numpy(q).cuda().bfloat16()
+        out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        comb2.decode_and_combine(q=d_q, cache=view, seq_lens=lens, seq_len_host=hi - lo, records=rec, out=out,
+                                 num_kv_heads=nkv, q_dtype=BF16, workspace=ws, workspace_bytes=ws_n)
+        gpu.synchronize()
+        ref = O.attention_f64(q[0], k, v, L)
+        got = out.cpu().numpy()
+        worst = max(worst, float(np.abs(got - ref).max() / np.abs(ref).max()))
+    comb2.close()
     if rank == 0:
         q_out.put(worst)
     dist.barrier()
