@@ -15,8 +15,8 @@ import os
 import numpy as np
 
 from . import ops
-from ._lib import BF16, F16, F32
-from .gpu import GpuContext
+from ._lib import BF16, F16, F32, AppendParams, DecodeParams
+from .gpu import GpuContext, _addr
 
 _ESZ = {F32: 4, F16: 2, BF16: 2}
 
@@ -69,12 +69,15 @@ class BatchedDecoder:
                                   num_q_heads=num_heads, num_splits=num_splits, num_seqs=num_seqs)
         self.in_bytes = (num_seqs * qrow + 2 * num_seqs * row) * asz
         self.out_bytes = num_seqs * num_heads * head_dim * asz
+        self._lens_host = (C.c_uint32 * num_seqs)()
+        self._fused_calls: dict = {}
         self.set_lengths(np.zeros(num_seqs, np.uint32))
 
     def set_lengths(self, lens_before) -> None:
         """Rows already in each sequence's cache; the next step appends at these positions."""
         self.lens_before = np.ascontiguousarray(lens_before, dtype=np.uint32)
         self.lens_after = (self.lens_before + 1).astype(np.uint32)
+        self._lens_host[:] = self.lens_after.tolist()   # the array the prepared fused calls point at
         self.gpu.write_buffer(self.pos, 0, self.lens_before.tobytes())
         self.gpu.write_buffer(self.lens, 0, self.lens_after.tobytes())
 
@@ -105,14 +108,28 @@ class BatchedDecoder:
             self.append(layer)
             self.attend(layer)
 
+    def _fused(self, layer: int, q: int, k: int, v: int, out: int) -> None:
+        """One fused launch on raw addresses.  The ctypes argument list is built once per (layer, addresses) and
+        reused: a decode step is short enough for per-call marshalling to show up in the host-side latency."""
+        key = (layer, q, k, v, out)
+        call = self._fused_calls.get(key)
+        if call is None:
+            ap = AppendParams(self.nh, self.nkv, self.hd, self.eps, self.theta, self.rd, self.rd // 2, self.rd // 2, 1,
+                              self.S, 1, self.act_dtype, self.act_dtype, int(self.has_gate), 0, 0)
+            p = DecodeParams(self.hd, self.nkv, self.nh, self.nh // self.nkv, self.num_splits, self.S, self.act_dtype,
+                             self.act_dtype)
+            cs = self.views[layer].c_struct()
+            vp = C.c_void_p
+            args = (self.gpu.handle, C.byref(ap), C.byref(p), vp(q), vp(k), vp(v),
+                    vp(_addr(self.qk_norm) or None), C.byref(cs), vp(self.lens.ptr),
+                    C.cast(self._lens_host, C.POINTER(C.c_uint32)), vp(out), None, vp(self.ws.ptr), self.ws_bytes)
+            call = self._fused_calls[key] = (args, (ap, p, cs))
+        st = self.gpu._L.shady_attn_decode_append(*call[0])
+        if st:
+            self.gpu._check(st)
+
     def step_fused(self, layer: int = 0) -> None:
-        ops.attn_decode_append(self.gpu, q_proj_full=self.q_in, k_proj=self.k_in, v_proj=self.v_in,
-                               cache=self.views[layer], seq_lens=self.lens, out=self.out, num_heads=self.nh,
-                               num_kv_heads=self.nkv, head_dim=self.hd, rope_theta=self.theta, rotary_dim=self.rd,
-                               num_seqs=self.S, eps=self.eps, qk_norm_bf16=self.qk_norm, in_dtype=self.act_dtype,
-                               out_dtype=self.act_dtype,
-                               has_gate=self.has_gate, seq_lens_host=self.lens_after, workspace=self.ws,
-                               workspace_bytes=self.ws_bytes, num_splits=self.num_splits)
+        self._fused(layer, self.q_in.ptr, self.k_in.ptr, self.v_in.ptr, self.out.ptr)
 
     def step_from_pinned(self, q_host: int, k_host: int, v_host: int, out_host: int, layer: int = 0) -> None:
         """Full step on page-locked host buffers without copies: the fused launch reads the activations from host
@@ -125,12 +142,7 @@ class BatchedDecoder:
             self._pinned = tuple(self.gpu.host_device_ptr(a) for a in key)
             self._pinned_key = key
         dq, dk, dv, do = self._pinned
-        ops.attn_decode_append(self.gpu, q_proj_full=dq, k_proj=dk, v_proj=dv, cache=self.views[layer],
-                               seq_lens=self.lens, out=do, num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.hd,
-                               rope_theta=self.theta, rotary_dim=self.rd, num_seqs=self.S, eps=self.eps,
-                               qk_norm_bf16=self.qk_norm, in_dtype=self.act_dtype, out_dtype=self.act_dtype,
-                               has_gate=self.has_gate, seq_lens_host=self.lens_after, workspace=self.ws,
-                               workspace_bytes=self.ws_bytes, num_splits=self.num_splits)
+        self._fused(layer, dq, dk, dv, do)
         self.gpu.synchronize()
 
     def step_from_host(self, q_host: int, k_host: int, v_host: int, out_host: int, layer: int = 0) -> None:

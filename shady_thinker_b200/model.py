@@ -9,13 +9,14 @@ touch (model.rs:57-86, 226-256), and the helpers themselves with their reference
 """
 from __future__ import annotations
 
+import ctypes as C
 import struct
 from dataclasses import dataclass, field
 
 import numpy as np
 
 from . import ops
-from ._lib import BF16, F16, F32  # noqa: F401
+from ._lib import BF16, F16, F32, AppendParams, DecodeParams  # noqa: F401
 from .gpu import Buffer, GpuContext
 
 #: model.rs:89 fixes this at 1 at compile time; here it is a run-time value and 0 means
@@ -81,6 +82,8 @@ class Model:
         self.num_attn_splits = num_attn_splits
         self.seq_len = 0
         self._pos_on_device = self._len_on_device = None   # host copies of the two device counters
+        self._len_host = (C.c_uint32 * 1)()                 # seq_lens_host of the prepared decode calls
+        self._calls: dict = {}
         nh, nkv, hd, nl = (config.num_attention_heads, config.num_key_value_heads, config.head_dim,
                            config.num_hidden_layers)
         f = 4
@@ -118,11 +121,23 @@ class Model:
         if self._pos_on_device != self.seq_len:      # model.rs:493-496 writes it per layer; once per token is enough
             gpu.write_buffer(s.position, 0, struct.pack("I", self.seq_len))
             self._pos_on_device = self.seq_len
-        ops.kv_append_rope(gpu, q_proj_full=s.q_out, k_proj=s.k_out, v_proj=s.v_out, q_out=s.q_proj, q_gate=s.q_gate,
-                           cache=self._cache(layer_idx), pos_start=s.position, num_heads=c.num_attention_heads,
-                           num_kv_heads=c.num_key_value_heads, head_dim=c.head_dim, rope_theta=c.rope_theta,
-                           rotary_dim=c.rotary_dim, interleaved=c.mrope_interleaved, eps=c.rms_norm_eps,
-                           qk_norm_bf16=s.qknorm_params[layer_idx])
+        # the argument list is marshalled once per layer and cache binding: a single-sequence step is a few
+        # microseconds of GPU work, and building ctypes structures per call would cost more than that
+        key = ("append", layer_idx, s.k_cache[layer_idx].ptr, s.v_cache[layer_idx].ptr,
+               s.qknorm_params[layer_idx].ptr if s.qknorm_params[layer_idx] else 0)
+        call = self._calls.get(key)
+        if call is None:
+            rd = c.rotary_dim
+            p = AppendParams(c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rms_norm_eps, c.rope_theta, rd,
+                             rd // 2, rd // 2, int(c.mrope_interleaved), 1, 1, F32, F32, 1, 1, 0)
+            cs = self._cache(layer_idx).c_struct()
+            vp = C.c_void_p
+            args = (gpu.handle, C.byref(p), vp(s.q_out.ptr), vp(s.k_out.ptr), vp(s.v_out.ptr), vp(s.q_proj.ptr),
+                    vp(s.q_gate.ptr), C.byref(cs), vp(key[4] or None), vp(s.position.ptr), None, None)
+            call = self._calls[key] = (args, (p, cs))
+        st = gpu._L.shady_kv_append_rope(*call[0])
+        if st:
+            gpu._check(st)
 
     def gqa_attention(self, gpu: GpuContext, layer_idx: int, fuse_gate: bool = False) -> None:
         """model.rs:516-573.  ``fuse_gate`` folds the following ``sigmoid_mul_gate`` into the epilogue."""
@@ -131,11 +146,21 @@ class Model:
         if self._len_on_device != seq_len:
             gpu.write_buffer(s.seq_len_dev, 0, struct.pack("I", seq_len))
             self._len_on_device = seq_len
-        ops.attn_decode(gpu, q=s.q_proj, cache=self._cache(layer_idx), seq_lens=s.seq_len_dev, out=s.attn_output,
-                        head_dim=c.head_dim, num_kv_heads=c.num_key_value_heads, num_q_heads=c.num_attention_heads,
-                        num_seqs=1, num_splits=self.num_attn_splits, seq_lens_host=[seq_len],
-                        gate=s.q_gate if fuse_gate else None, workspace=s.attn_partials,
-                        workspace_bytes=s.partials_bytes)
+        key = ("attend", layer_idx, s.k_cache[layer_idx].ptr, s.v_cache[layer_idx].ptr, bool(fuse_gate))
+        call = self._calls.get(key)
+        if call is None:
+            p = DecodeParams(c.head_dim, c.num_key_value_heads, c.num_attention_heads,
+                             c.num_attention_heads // c.num_key_value_heads, self.num_attn_splits, 1, F32, F32)
+            cs = self._cache(layer_idx).c_struct()
+            vp = C.c_void_p
+            args = (gpu.handle, C.byref(p), vp(s.q_proj.ptr), C.byref(cs), vp(s.seq_len_dev.ptr),
+                    C.cast(self._len_host, C.POINTER(C.c_uint32)), vp(s.attn_output.ptr), None,
+                    vp(s.q_gate.ptr if fuse_gate else None), vp(s.attn_partials.ptr), s.partials_bytes)
+            call = self._calls[key] = (args, (p, cs))
+        self._len_host[0] = seq_len
+        st = gpu._L.shady_attn_decode(*call[0])
+        if st:
+            gpu._check(st)
 
     def sigmoid_mul_gate(self, gpu: GpuContext) -> None:
         """model.rs:576-593 (in place; no temp buffer + copy)."""

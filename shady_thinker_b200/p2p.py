@@ -45,6 +45,7 @@ class ShardCombiner:
             dist.barrier(group=group)                              # every buffer is zeroed and mapped everywhere
         self.table = gpu.upload_buffer("p2p_peer_table", np.asarray(ptrs, dtype=np.uint64).tobytes())
         self.epoch = 0
+        self._calls: dict = {}
 
     def combine(self, records, out, out_dtype: int = _lib.F32, gate=None) -> None:
         """records: this rank's [nh][hd+2] f32 (``ops.attn_decode_shard``); out: [nh][hd].  Every rank must call
@@ -61,16 +62,23 @@ class ShardCombiner:
         """The whole sharded step in two launches (``shady_attn_decode_shard_p2p``): decode over this rank's rows,
         then one kernel that merges the rank's records, exchanges the result over NVLink and merges across ranks.
         Do not mix with :meth:`combine` on the same combiner (the exchange buffer is laid out differently)."""
-        from . import ops
         self.epoch += 1
         g = self.gpu
-        p = _lib.DecodeParams(self.hd, num_kv_heads, self.nh, self.nh // num_kv_heads, 0, 1, q_dtype, _lib.F32)
-        c = cache.c_struct()
-        hl = (C.c_uint32 * 1)(seq_len_host)
-        g._check(g._L.shady_attn_decode_shard_p2p(g.handle, C.byref(p), _addr(q), C.byref(c), _addr(seq_lens), hl,
-                                                  self.world, self.rank, self.epoch, C.c_void_p(self.table.ptr),
-                                                  _addr(records), _addr(out), out_dtype, _addr(gate) or None,
-                                                  _addr(workspace) or None, workspace_bytes))
+        key = (id(cache), _addr(q), _addr(seq_lens), seq_len_host, _addr(records), _addr(out), _addr(gate), _addr(workspace))
+        call = self._calls.get(key)
+        if call is None:     # marshal once per distinct argument set: at N >= 4 a shard's step is shorter than that takes
+            p = _lib.DecodeParams(self.hd, num_kv_heads, self.nh, self.nh // num_kv_heads, 0, 1, q_dtype, _lib.F32)
+            c = cache.c_struct()
+            hl = (C.c_uint32 * 1)(seq_len_host)
+            vp = C.c_void_p
+            args = [g.handle, C.byref(p), vp(_addr(q)), C.byref(c), vp(_addr(seq_lens)), hl, self.world, self.rank, 0,
+                    vp(self.table.ptr), vp(_addr(records)), vp(_addr(out)), out_dtype, vp(_addr(gate) or None),
+                    vp(_addr(workspace) or None), workspace_bytes]
+            call = self._calls[key] = (args, (p, c, hl, cache))
+        call[0][8] = self.epoch
+        st = g._L.shady_attn_decode_shard_p2p(*call[0])
+        if st:
+            g._check(st)
 
     def close(self, group=None) -> None:
         if self.world > 1:
