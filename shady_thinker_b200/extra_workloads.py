@@ -72,6 +72,28 @@ def run_cfg1(args, rank: int, world: int, local_rank: int) -> None:
             gpu.synchronize()
             if i >= args.warmup:
                 times.append(a.elapsed_time(b) * 1e3)
+        # the same two launches replayed from a CUDA graph (captured on the context's stream): what the kernels cost
+        # once the CPU's per-launch latency is out of the picture
+        graph_us = None
+        try:
+            gpu.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                m.fused_split_qknorm_kvstore(gpu, 0)
+                m.gqa_attention(gpu, 0, fuse_gate=True)
+            gt = []
+            for i in range(args.warmup + args.steps):
+                flush.fill_(i & 0xFF)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                g.replay()
+                b.record(stream)
+                gpu.synchronize()
+                if i >= args.warmup:
+                    gt.append(a.elapsed_time(b) * 1e3)
+            graph_us = float(np.median(gt))
+        except Exception as e:      # capture is optional: the figure is informational
+            graph_us = f"unavailable: {type(e).__name__}"
     barrier()
     if rank == 0:
         us = float(np.median(times))
@@ -83,7 +105,8 @@ def run_cfg1(args, rank: int, world: int, local_rank: int) -> None:
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "cfg1: single decode step, fp32 KV, batch 1, nh16/nkv2/hd128, context 512, full rotary",
                        "l2": "256 MB flush write between steps", "p10_us": float(np.percentile(times, 10)),
-                       "p90_us": float(np.percentile(times, 90)), "includes": "position/length uploads, append, attend+gate"},
+                       "p90_us": float(np.percentile(times, 90)), "includes": "position/length uploads, append, attend+gate",
+                       "graph_replay_us": graph_us},
             "roofline": {"bound": "hbm", "achieved": kv_bytes / (us * 1e-6) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": kv_bytes / (us * 1e-6) / 1e9 / peak, "traffic": None,
                          "peak_source": f"{src} (copy bandwidth); informational: 1 MiB of KV is latency-bound"},
