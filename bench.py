@@ -42,6 +42,16 @@ def draw_lengths(rank: int) -> np.ndarray:
     return rng.integers(LMIN, LMAX + 1, SEQS_PER_GPU).astype(np.uint32)
 
 
+def rank_lengths(rank: int, world: int) -> np.ndarray:
+    """The job's batch is 32 sequences per GPU; on several GPUs they are dealt to the ranks longest first, each to
+    the rank with the fewest rows so far (sharding.shard_sequences), so every rank streams about the same bytes."""
+    if world == 1:
+        return draw_lengths(0)
+    from shady_thinker_b200.sharding import shard_sequences
+    all_lens = np.concatenate([draw_lengths(r) for r in range(world)])
+    return all_lens[shard_sequences(all_lens, world)[rank]]
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -203,7 +213,8 @@ def workload_config(n_gpus: int, shape: str = "plain") -> dict:
     return {"workload": "cfg2: batched ragged decode attention, one layer, append+attend per step", "rope": rope,
             "seqs_per_gpu": SEQS_PER_GPU, "context": f"uniform[{LMIN},{LMAX}] (seeded)", "num_q_heads": NH,
             "num_kv_heads": NKV, "head_dim": HD, "kv_dtype": "fp16", "q_dtype": "fp16", "accumulate": "fp32",
-            "rope_theta": 1e6, "sharding": f"sequences over {n_gpus} GPU(s), no collective",
+            "rope_theta": 1e6, "sharding": (f"{SEQS_PER_GPU * n_gpus} sequences dealt to {n_gpus} GPU(s) longest first to the rank with the fewest rows, "
+                         "no collective"),
             "l2": f"KV per step > L2 and {N_SETS} cache sets rotate between steps"}
 
 
@@ -251,7 +262,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 
     stream = torch.cuda.Stream()
     gpu = GpuContext(local_rank, stream=stream.cuda_stream)
-    lens = draw_lengths(rank)
+    lens = rank_lengths(rank, world)
+    S = len(lens)
     sets = []
     ref_shape = args.shape == "reference"
     qrow = NH * HD * (2 if ref_shape else 1)
@@ -261,7 +273,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         wbits = ((wf + 0x7FFF + ((wf >> 16) & 1)) >> 16).astype(np.uint16)
         d_norm = gpu.upload_buffer("qknorm_weights", wbits.tobytes())
     for i in range(N_SETS):
-        d = BatchedDecoder(gpu, num_seqs=SEQS_PER_GPU, capacities=lens, num_heads=NH, num_kv_heads=NKV, head_dim=HD,
+        d = BatchedDecoder(gpu, num_seqs=S, capacities=lens, num_heads=NH, num_kv_heads=NKV, head_dim=HD,
                            kv_dtype=F16, rope_theta=1e6, rotary_dim=HD // 4 if ref_shape else HD, has_gate=ref_shape,
                            num_splits=0, qk_norm_bf16=d_norm)
         d.set_lengths(lens - 1)
@@ -269,9 +281,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         n = d.layer_bytes // 2
         ops.fill_randn(gpu, d.k_cache[0], n, F16, SEED, base + 1)
         ops.fill_randn(gpu, d.v_cache[0], n, F16, SEED, base + 2)
-        ops.fill_randn(gpu, d.q_in, SEQS_PER_GPU * qrow, F16, SEED, base + 3)
-        ops.fill_randn(gpu, d.k_in, SEQS_PER_GPU * NKV * HD, F16, SEED, base + 4)
-        ops.fill_randn(gpu, d.v_in, SEQS_PER_GPU * NKV * HD, F16, SEED, base + 5)
+        ops.fill_randn(gpu, d.q_in, S * qrow, F16, SEED, base + 3)
+        ops.fill_randn(gpu, d.k_in, S * NKV * HD, F16, SEED, base + 4)
+        ops.fill_randn(gpu, d.v_in, S * NKV * HD, F16, SEED, base + 5)
         sets.append(d)
     gpu.synchronize()
     step_bytes = sets[0].kv_bytes_per_step()
@@ -310,10 +322,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         # ---------------- end to end with host buffers ----------------
         d0 = sets[0]
         asz = 2
-        hq = torch.empty(SEQS_PER_GPU * qrow, dtype=torch.float16).pin_memory()
-        hk = torch.empty(SEQS_PER_GPU * NKV * HD, dtype=torch.float16).pin_memory()
-        hv = torch.empty(SEQS_PER_GPU * NKV * HD, dtype=torch.float16).pin_memory()
-        ho = torch.empty(SEQS_PER_GPU * NH * HD, dtype=torch.float16).pin_memory()
+        hq = torch.empty(S * qrow, dtype=torch.float16).pin_memory()
+        hk = torch.empty(S * NKV * HD, dtype=torch.float16).pin_memory()
+        hv = torch.empty(S * NKV * HD, dtype=torch.float16).pin_memory()
+        ho = torch.empty(S * NH * HD, dtype=torch.float16).pin_memory()
         hq.normal_(); hk.normal_(); hv.normal_()
         e2e_steps = max(10, min(args.steps, 2000))
         # The public call for host buffers: with the fused launch the kernel itself reads the pinned activations
