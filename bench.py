@@ -592,7 +592,7 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
-# Other BASELINE configs (reported in DESIGN.md; the default line stays cfg2)
+# Other configurations of the baseline file (the default line stays cfg2)
 # ------------------------------------------------------------------------------------------------
 def _dist_setup(world: int, local_rank: int):
     import torch
