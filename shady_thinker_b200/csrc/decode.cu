@@ -497,48 +497,16 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             cp_async_commit();
         }
         // ---- fused append: the warp that will process the block holding row L-1 builds that row of K (norm + RoPE)
-        //      and of V, stores both in the cache for later steps and keeps them to patch its shared-memory tiles ----
+        //      and of V, stores both in the cache for later steps and keeps them to patch its shared-memory tiles.
+        //      Here it only requests the projected rows; the arithmetic follows once Q is staged, so the latency of
+        //      these loads passes under the staging and the cos/sin table built for Q serves K as well ----
+        float own_raw[NIT][8];
         if (owner) {
-            const uint32_t pos = p.L - 1;
 #pragma unroll
             for (int it = 0; it < NIT; ++it) {
                 const uint32_t tt = lane + 32 * it;
-                const bool act = tt < 2 * CH;
-                const uint32_t is_v = act ? tt / CH : 1u, c = tt % CH;
-                float v8[8];
-                load8_as_f32(is_v ? a.ap_v : a.ap_k, ((size_t)p.seq * a.nkv + kvh) * HD + c * 8, a.ap_in_dtype, v8);
-                if (a.ap_norm_w && it == 0) {   // K chunks sit in item set 0 (all lanes, or the first CH of them)
-                    float ssq = 0.f;
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) ssq += v8[e] * v8[e];
-#pragma unroll
-                    for (int o = CH / 2; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o, CH);
-                    if (!is_v) {
-                        const float rms = 1.0f / sqrtf(ssq / (float)HD + a.ap_eps);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e)
-                            v8[e] = v8[e] * rms * (1.0f + __uint_as_float(((uint32_t)a.ap_norm_w[HD + c * 8 + e]) << 16));
-                    }
-                }
-                if (!is_v) {
-#pragma unroll
-                    for (int k2 = 0; k2 < 4; ++k2) {
-                        const uint32_t i2 = c * 4 + k2;
-                        if (i2 < a.ap_rd / 2) {
-                            float sn, cs;
-                            sincosf((float)pos * a.ap_inv_freq[i2], &sn, &cs);
-                            const float x = v8[2 * k2], y = v8[2 * k2 + 1];
-                            v8[2 * k2] = x * cs - y * sn;
-                            v8[2 * k2 + 1] = y * cs + x * sn;
-                        }
-                    }
-                }
-                newrow[it].x = pack2<T>(v8[0], v8[1]); newrow[it].y = pack2<T>(v8[2], v8[3]);
-                newrow[it].z = pack2<T>(v8[4], v8[5]); newrow[it].w = pack2<T>(v8[6], v8[7]);
-                if (act) {
-                    char *dst = const_cast<char *>(kv_row_ptr(a.kv, is_v != 0, p.seq, pos, pos_stride)) + (size_t)kvh * S::kRowBytes;
-                    *reinterpret_cast<uint4 *>(dst + c * 16) = newrow[it];
-                }
+                const uint32_t is_v = tt < 2 * CH ? tt / CH : 1u, c = tt % CH;
+                load8_as_f32(is_v ? a.ap_v : a.ap_k, ((size_t)p.seq * a.nkv + kvh) * HD + c * 8, a.ap_in_dtype, own_raw[it]);
             }
         }
         // stage Q of the CTA's kv heads (rows >= rows_valid are zero) as T, swizzled
@@ -599,6 +567,45 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kRowBytes + ((c ^ (r & 7)) << 4)) = v;
         }
         __syncthreads();
+        if (owner) {   // (fused append, second half) norm + RoPE of the new K row, V as it is; cache stores; kept for the patch
+            const uint32_t pos = p.L - 1;
+            const float2 *sm_cs = reinterpret_cast<const float2 *>(sm_m);   // this piece's table: (cos, sin) per pair, (1, 0) past rd
+#pragma unroll
+            for (int it = 0; it < NIT; ++it) {
+                const uint32_t tt = lane + 32 * it;
+                const bool act = tt < 2 * CH;
+                const uint32_t is_v = act ? tt / CH : 1u, c = tt % CH;
+                float (&v8)[8] = own_raw[it];
+                if (a.ap_norm_w && it == 0) {   // K chunks sit in item set 0 (all lanes, or the first CH of them)
+                    float ssq = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ssq += v8[e] * v8[e];
+#pragma unroll
+                    for (int o = CH / 2; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o, CH);
+                    if (!is_v) {
+                        const float rms = 1.0f / sqrtf(ssq / (float)HD + a.ap_eps);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            v8[e] = v8[e] * rms * (1.0f + __uint_as_float(((uint32_t)a.ap_norm_w[HD + c * 8 + e]) << 16));
+                    }
+                }
+                if (!is_v) {
+#pragma unroll
+                    for (int k2 = 0; k2 < 4; ++k2) {
+                        const float2 t2 = sm_cs[c * 4 + k2];
+                        const float x = v8[2 * k2], y = v8[2 * k2 + 1];
+                        v8[2 * k2] = x * t2.x - y * t2.y;
+                        v8[2 * k2 + 1] = y * t2.x + x * t2.y;
+                    }
+                }
+                newrow[it].x = pack2<T>(v8[0], v8[1]); newrow[it].y = pack2<T>(v8[2], v8[3]);
+                newrow[it].z = pack2<T>(v8[4], v8[5]); newrow[it].w = pack2<T>(v8[6], v8[7]);
+                if (act) {
+                    char *dst = const_cast<char *>(kv_row_ptr(a.kv, is_v != 0, p.seq, pos, pos_stride)) + (size_t)kvh * S::kRowBytes;
+                    *reinterpret_cast<uint4 *>(dst + c * 16) = newrow[it];
+                }
+            }
+        }
         // Q fragments (A operand), one ldmatrix.x4 per k-step: mats = (rows0-7,c), (rows8-15,c), (rows0-7,c+1), (rows8-15,c+1)
         uint32_t qa[QREG ? HD / 16 : 1][4];
         if constexpr (QREG) {
