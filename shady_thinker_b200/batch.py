@@ -123,6 +123,8 @@ class BatchedDecoder:
             args = (self.gpu.handle, C.byref(ap), C.byref(p), vp(q), vp(k), vp(v),
                     vp(_addr(self.qk_norm) or None), C.byref(cs), vp(self.lens.ptr),
                     C.cast(self._lens_host, C.POINTER(C.c_uint32)), vp(out), None, vp(self.ws.ptr), self.ws_bytes)
+            if len(self._fused_calls) >= 64:      # callers that keep changing buffers must not grow this without bound
+                self._fused_calls.clear()
             call = self._fused_calls[key] = (args, (ap, p, cs))
         st = self.gpu._L.shady_attn_decode_append(*call[0])
         if st:

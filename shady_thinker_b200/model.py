@@ -134,6 +134,8 @@ class Model:
             vp = C.c_void_p
             args = (gpu.handle, C.byref(p), vp(s.q_out.ptr), vp(s.k_out.ptr), vp(s.v_out.ptr), vp(s.q_proj.ptr),
                     vp(s.q_gate.ptr), C.byref(cs), vp(key[4] or None), vp(s.position.ptr), None, None)
+            if len(self._calls) >= 4 * max(1, c.num_hidden_layers) + 16:   # cache swaps rebind buffers
+                self._calls.clear()
             call = self._calls[key] = (args, (p, cs))
         st = gpu._L.shady_kv_append_rope(*call[0])
         if st:
@@ -156,6 +158,8 @@ class Model:
             args = (gpu.handle, C.byref(p), vp(s.q_proj.ptr), C.byref(cs), vp(s.seq_len_dev.ptr),
                     C.cast(self._len_host, C.POINTER(C.c_uint32)), vp(s.attn_output.ptr), None,
                     vp(s.q_gate.ptr if fuse_gate else None), vp(s.attn_partials.ptr), s.partials_bytes)
+            if len(self._calls) >= 4 * max(1, c.num_hidden_layers) + 16:   # cache swaps rebind buffers
+                self._calls.clear()
             call = self._calls[key] = (args, (p, cs))
         self._len_host[0] = seq_len
         st = gpu._L.shady_attn_decode(*call[0])

@@ -74,6 +74,8 @@ class ShardCombiner:
             args = [g.handle, C.byref(p), vp(_addr(q)), C.byref(c), vp(_addr(seq_lens)), hl, self.world, self.rank, 0,
                     vp(self.table.ptr), vp(_addr(records)), vp(_addr(out)), out_dtype, vp(_addr(gate) or None),
                     vp(_addr(workspace) or None), workspace_bytes]
+            if len(self._calls) >= 64:
+                self._calls.clear()
             call = self._calls[key] = (args, (p, c, hl, cache))
         call[0][8] = self.epoch
         st = g._L.shady_attn_decode_shard_p2p(*call[0])
