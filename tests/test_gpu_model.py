@@ -107,3 +107,56 @@ def test_step_from_pinned_equals_step_from_host(gpu_ctx):
     with pytest.raises(ShadyError) as e:
         gpu_ctx.host_device_ptr(pageable.data_ptr())
     assert e.value.code == 1
+
+
+def test_batched_decoder_many_steps_reuse_one_workspace(gpu_ctx):
+    """Forty fused steps of a ragged batch through one BatchedDecoder (one workspace whose arrival counters reset
+    themselves, lengths growing every step): the last step's output equals f64 attention over the cache rows the
+    steps wrote, read back from the device."""
+    import torch
+    from shady_thinker_b200 import ops
+    from shady_thinker_b200._lib import F16
+    from shady_thinker_b200.batch import BatchedDecoder
+    S, nh, nkv, hd, steps = 6, 8, 2, 128, 40
+    start = np.array([0, 3, 100, 1000, 15, 2047], np.uint32)
+    d = BatchedDecoder(gpu_ctx, num_seqs=S, capacities=start + steps, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                       kv_dtype=F16, rope_theta=1e6, rotary_dim=hd, has_gate=False, num_splits=0)
+    n = d.layer_bytes // 2
+    ops.fill_randn(gpu_ctx, d.k_cache[0], n, F16, 11, 1)
+    ops.fill_randn(gpu_ctx, d.v_cache[0], n, F16, 11, 2)
+    g = torch.Generator().manual_seed(5)
+    for t in range(steps):
+        d.set_lengths(start + t)
+        q = torch.randn(S * nh * hd, generator=g).half().cuda()
+        k = torch.randn(S * nkv * hd, generator=g).half().cuda()
+        v = torch.randn(S * nkv * hd, generator=g).half().cuda()
+        gpu_ctx.copy_buffer(q, d.q_in, q.numel() * 2)
+        gpu_ctx.copy_buffer(k, d.k_in, k.numel() * 2)
+        gpu_ctx.copy_buffer(v, d.v_in, v.numel() * 2)
+        d.step()
+    gpu_ctx.synchronize()
+    out = np.frombuffer(gpu_ctx.read_buffer(d.out, d.out_bytes), np.float16).astype(np.float64).reshape(S, nh, hd)
+    # the rotated q of the last step, recomputed on the host: full rotary, interleaved pairs, position L-1
+    kc = np.frombuffer(gpu_ctx.read_buffer(d.k_cache[0], d.layer_bytes), np.float16).astype(np.float64)
+    vc = np.frombuffer(gpu_ctx.read_buffer(d.v_cache[0], d.layer_bytes), np.float16).astype(np.float64)
+    qh = q.cpu().numpy().astype(np.float64).reshape(S, nh, hd)
+    i = np.arange(hd // 2)
+    inv = (1.0 / np.power(np.float32(1e6), (2.0 * i / hd).astype(np.float32))).astype(np.float32)
+    worst = 0.0
+    for s in range(S):
+        L = int(start[s]) + steps
+        ang = (np.float32(L - 1) * inv).astype(np.float32).astype(np.float64)
+        cs, sn = np.cos(ang), np.sin(ang)
+        qr = qh[s].copy()
+        qr[:, 0::2] = qh[s][:, 0::2] * cs - qh[s][:, 1::2] * sn
+        qr[:, 1::2] = qh[s][:, 1::2] * cs + qh[s][:, 0::2] * sn
+        qr = qr.astype(np.float16).astype(np.float64)          # the kernel stages Q in the cache dtype
+        off = int(d.row_off[s]) * nkv * hd
+        kk = kc[off:off + L * nkv * hd].reshape(L, nkv, hd)
+        vv = vc[off:off + L * nkv * hd].reshape(L, nkv, hd)
+        for h in range(nh):
+            sc = kk[:, h // (nh // nkv)] @ qr[h] / np.sqrt(hd)
+            pr = np.exp(sc - sc.max())
+            ref = (pr[:, None] * vv[:, h // (nh // nkv)]).sum(0) / pr.sum()
+            worst = max(worst, float(np.abs(out[s, h] - ref).max() / np.abs(ref).max()))
+    assert worst <= RTOL_16, worst
