@@ -192,8 +192,9 @@ int shady_decode_workspace_init(shady_ctx *ctx, const shady_decode_params *p, vo
  * [num_seqs][nh] f32 log-sum-exp of each output row (needed to merge shards of one
  * sequence across GPUs); NULL to skip.  d_gate: optional [num_seqs][nh][hd] f32; when given
  * the output is multiplied by sigmoid(gate) (fuses Model::sigmoid_mul_gate, model.rs:576).
- * seq_lens_host: the same lengths in host memory, used only to balance the split plan when
- * num_splits == 0 (may be NULL otherwise).  A sequence of length 0 yields zeros and
+ * seq_lens_host: the same lengths in host memory (they must equal the device values): needed to
+ * balance the split plan when num_splits == 0, may be NULL otherwise; for batches of up to 32
+ * sequences the kernels also take the lengths from it by value instead of loading them.  A sequence of length 0 yields zeros and
  * lse = -inf.  Splits are merged inside the same launch by the last CTA to arrive
  * (gqa_reduce.wgsl math); calls that share one workspace must not overlap on the GPU. */
 int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,

@@ -65,7 +65,14 @@ struct DecodeArgs {
     void *px_out;                 // final rows [nh][hd]
     const float *px_gate;         // optional [nh][hd] f32
     uint32_t px_world, px_rank, px_epoch, px_out_dtype;
+    // the lengths by value (small batches whose caller gave them on the host): a kernel-parameter read instead of a
+    // global load at the head of every dependent chain (span search, piece set-up, record merge); lens_n == 0: off
+    uint32_t lens_n;
+    uint32_t lens_v[32];
 };
+__device__ __forceinline__ uint32_t seq_len_at(const DecodeArgs &a, uint32_t i) {
+    return i < a.lens_n ? a.lens_v[i] : a.seq_lens[i];
+}
 
 // 8 consecutive elements (16-byte aligned for 16-bit types, 32-byte for f32) of a buffer of run-time dtype
 __device__ __forceinline__ void load8_as_f32(const void *p, size_t i, uint32_t dt, float (&v)[8]) {
@@ -140,7 +147,7 @@ __device__ __forceinline__ void cursor_init(const DecodeArgs &a, uint32_t work, 
     bool found = false;
     for (uint32_t base = 0; base < a.num_seqs && !found; base += 32) {
         const uint32_t j = base + lane;
-        const uint32_t nb = j < a.num_seqs ? blocks_of(a.seq_lens[j]) : 0u;
+        const uint32_t nb = j < a.num_seqs ? blocks_of(seq_len_at(a, j)) : 0u;
         uint32_t incl = nb;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -165,14 +172,14 @@ __device__ __forceinline__ bool next_piece(const DecodeArgs &a, Cursor &cur, Pie
     if (a.num_splits) {
         cur.done = 1;
         const uint32_t ns = a.num_splits, split = cur.u;
-        p.seq = cur.seq; p.L = a.seq_lens[cur.seq];
+        p.seq = cur.seq; p.L = seq_len_at(a, cur.seq);
         const uint32_t pps = (p.L + ns - 1u) / ns;  // wgsl:46
         p.start = min(split * pps, p.L); p.end = min(p.start + pps, p.L);
         p.nrec = ns; p.my_rec = split; p.c0 = cur.seq * ns; p.B = 0;
         return true;
     }
     if (cur.u >= cur.u1 || cur.seq >= a.num_seqs) return false;
-    const uint32_t L = a.seq_lens[cur.seq], nb = blocks_of(L);
+    const uint32_t L = seq_len_at(a, cur.seq), nb = blocks_of(L);
     const uint32_t ub1 = min(cur.u1, cur.B + nb);
     p.seq = cur.seq; p.L = L;
     p.start = min((cur.u - cur.B) * kBlkPos, L);
@@ -513,6 +520,20 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
         if (a.fuse_append) {
             // raw Q row -> RMSNorm(1+w) -> RoPE at position L-1 (wgsl:126-166); CH consecutive threads share a row.
             // cos/sin of the rotary pairs are the same for all rows: one table per piece in the merge-statistics area
+            // the raw rows are requested first: their latency passes under the cos/sin table, not after it
+            constexpr int QIT = (KPC * 16 * CH + NW * 32 - 1) / (NW * 32);
+            float qraw[QIT][8];
+#pragma unroll
+            for (int qi = 0; qi < QIT; ++qi) {
+                const uint32_t idx = tid + qi * NW * 32;
+                const uint32_t c = idx % CH, r = (idx / CH) % 16, k = idx / (CH * 16);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) qraw[qi][e] = 0.f;
+                if (idx < KPC * 16 * CH && r < rows_valid) {
+                    const size_t e0 = ((size_t)p.seq * a.nh + (kg * KPC + k) * a.G + row0 + r) * (a.ap_has_gate ? 2 * HD : HD) + c * 8;
+                    load8_as_f32(a.ap_q, e0, a.ap_in_dtype, qraw[qi]);
+                }
+            }
             const uint32_t pos = p.L ? p.L - 1 : 0;
             float2 *sm_cs = reinterpret_cast<float2 *>(sm_m);   // HD/2 pairs; sm_m/sm_l are free until the piece ends
             for (uint32_t i2 = tid; i2 < HD / 2; i2 += NW * 32) {
@@ -521,13 +542,12 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
                 sm_cs[i2] = make_float2(cs, sn);
             }
             __syncthreads();
-            for (uint32_t idx = tid; idx < KPC * 16 * CH; idx += NW * 32) {
+#pragma unroll
+            for (int qi = 0; qi < QIT; ++qi) {
+                const uint32_t idx = tid + qi * NW * 32;
+                if (idx >= KPC * 16 * CH) break;
                 const uint32_t c = idx % CH, r = (idx / CH) % 16, k = idx / (CH * 16);
-                float v8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                if (r < rows_valid) {
-                    const size_t e0 = ((size_t)p.seq * a.nh + (kg * KPC + k) * a.G + row0 + r) * (a.ap_has_gate ? 2 * HD : HD) + c * 8;
-                    load8_as_f32(a.ap_q, e0, a.ap_in_dtype, v8);
-                }
+                float (&v8)[8] = qraw[qi];
                 if (a.ap_norm_w) {
                     float ssq = 0.f;
 #pragma unroll
@@ -868,13 +888,13 @@ __device__ __forceinline__ void merge_balanced_records(const DecodeArgs &a, uint
     const uint32_t tid = threadIdx.x, g = tid >> 6, t = tid & 63u;
     if (tid < 32) {   // first row-block of this sequence on the line
         uint32_t acc = 0;
-        for (uint32_t j = tid; j < seq; j += 32) acc += blocks_of(a.seq_lens[j]);
+        for (uint32_t j = tid; j < seq; j += 32) acc += blocks_of(seq_len_at(a, j));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (tid == 0) sm_b = acc;
     }
     __syncthreads();
-    const uint32_t B = sm_b, nb = blocks_of(a.seq_lens[seq]);
+    const uint32_t B = sm_b, nb = blocks_of(seq_len_at(a, seq));
     const uint32_t c0 = span_of(a, B), nrec = span_of(a, B + nb - 1) - c0 + 1;
     const uint32_t dd = min(d, a.hd - 1);
     single = nrec == 1;       // uniform for the CTA
@@ -1183,6 +1203,10 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
     SHADY_REQUIRE(ctx, !a.kv.page_table || p->num_splits <= 1, SHADY_ERR_UNSUPPORTED,
                   "decode: a paged cache needs num_splits 0 or 1 (16-row blocks must not straddle pages)");
     a.seq_lens = d_seq_lens;
+    if (seq_lens_host && p->num_seqs <= 32) {
+        a.lens_n = p->num_seqs;
+        for (uint32_t i = 0; i < p->num_seqs; ++i) a.lens_v[i] = seq_lens_host[i];
+    }
     a.num_seqs = p->num_seqs; a.nkv = p->num_kv_heads; a.nh = p->num_q_heads; a.G = p->heads_per_kv; a.hd = hd;
     a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;
     a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e;
@@ -1374,6 +1398,10 @@ int launch_decode_static(shady_ctx *ctx, const shady_decode_params *p, const voi
     SHADY_REQUIRE(ctx, !a.kv.page_table || p->num_splits <= 1, SHADY_ERR_UNSUPPORTED,
                   "decode: a paged cache needs num_splits 0 or 1 (16-row blocks must not straddle pages)");
     a.seq_lens = d_seq_lens;
+    if (seq_lens_host && p->num_seqs <= 32) {
+        a.lens_n = p->num_seqs;
+        for (uint32_t i = 0; i < p->num_seqs; ++i) a.lens_v[i] = seq_lens_host[i];
+    }
     a.num_seqs = p->num_seqs; a.nkv = p->num_kv_heads; a.nh = p->num_q_heads; a.G = p->heads_per_kv; a.hd = hd;
     a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;
     a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e;
