@@ -199,43 +199,65 @@ __device__ __forceinline__ bool next_piece(const DecodeArgs &a, Cursor &cur, Pie
 // Warp w's O tile starts at sm_o + w*WSTRIDE floats, rows of HD floats.
 // The CTA serves KPC kv heads (kvh_base + k); warps k, k+KPC, k+2*KPC, ... share kv head k.
 template <int R, int HD, int NW, int WSTRIDE, int KPC>
-__device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p, const float *sm_m, const float *sm_l,
+__device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p, float *sm_m, float *sm_l,
                                              const float *sm_o, uint32_t *sm_flag, uint32_t *scratch,
                                              uint32_t scratch_words, uint32_t kvh_base, uint32_t row0,
                                              uint32_t rows_valid, uint32_t counter_idx) {
     const bool direct = (p.nrec == 1u) && !a.force_partials;
-    for (uint32_t idx = threadIdx.x; idx < KPC * rows_valid * HD; idx += NW * 32) {
-        const uint32_t d = idx % HD, r = (idx / HD) % rows_valid, kvl = idx / (HD * rows_valid);
+    // ---- per head row, once: the warps' weights e_w = 2^(m_w - M) (left in sm_m in place of m_w), the row's sum L
+    //      (left in sm_l of the head's first warp) and its log-sum-exp.  Which record slot the piece writes is one
+    //      64-bit division (rec_ptr) for the whole piece: it is resolved here, not per element ----
+    const bool ref_layout = a.num_splits || a.force_partials;
+    uint32_t rec_row0 = 0;
+    if (!direct && !ref_layout) {
+        const uint32_t c = p.c0 + p.my_rec;
+        rec_row0 = (c * 2 + (span_begin(a, c) >= p.B ? 0u : 1u)) * a.nh;
+    }
+    auto rec_of = [&](uint32_t head) {
+        return ref_layout ? a.partials + ((size_t)p.c0 * a.nh + (size_t)head * p.nrec + p.my_rec) * (a.hd + 2)
+                          : a.partials + ((size_t)rec_row0 + head) * (a.hd + 2);
+    };
+    if (threadIdx.x < KPC * rows_valid) {
+        const uint32_t r = threadIdx.x % rows_valid, kvl = threadIdx.x / rows_valid;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NW; ++w)
             if (w % KPC == (int)kvl) M = fmaxf(M, sm_m[w * R + r]);
-        float L = 0.f, o = 0.f;
+        float L = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
             if (w % KPC != (int)kvl) continue;
             const float mw = sm_m[w * R + r];
-            if (mw > -INFINITY) {
-                const float e = exp2f(mw - M);
-                L += sm_l[w * R + r] * e;
-                o += sm_o[(size_t)w * WSTRIDE + r * HD + d] * e;
-            }
+            const float e = mw > -INFINITY ? exp2f(mw - M) : 0.f;
+            if (mw > -INFINITY) L += sm_l[w * R + r] * e;
+            sm_m[w * R + r] = e;
         }
-        float val = L > 0.f ? o / L : 0.f;
+        sm_l[kvl * R + r] = L;
         const float lse = L > 0.f ? logf(L) + M * kLn2 : -INFINITY;
         const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
         if (direct) {
-                const size_t oi = ((size_t)p.seq * a.nh + head) * a.out_row_stride + d;
-            if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, p.seq, head, d));
-            store_from_f32(a.out, oi, a.out_dtype, val);
-            if (d == 0 && a.lse) a.lse[((size_t)p.seq * a.nh + head) * a.lse_stride] = lse;
+            if (a.lse) a.lse[((size_t)p.seq * a.nh + head) * a.lse_stride] = lse;
         } else {
-            float *rec = rec_ptr(a, p, head, p.my_rec);
-            rec[d] = val;
-            if (d == 0) {
-                rec[HD] = lse;
-                rec[HD + 1] = L > 0.f ? M * kLn2 : -INFINITY;
-            }
+            float *rec = rec_of(head);
+            rec[HD] = lse;
+            rec[HD + 1] = L > 0.f ? M * kLn2 : -INFINITY;
+        }
+    }
+    __syncthreads();
+    for (uint32_t idx = threadIdx.x; idx < KPC * rows_valid * HD; idx += NW * 32) {
+        const uint32_t d = idx % HD, hr = idx / HD, r = hr % rows_valid, kvl = hr / rows_valid;
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w)
+            if (w % KPC == (int)kvl) o += sm_o[(size_t)w * WSTRIDE + r * HD + d] * sm_m[w * R + r];   // empty warps: 0 * 0
+        const float L = sm_l[kvl * R + r];
+        float val = L > 0.f ? o / L : 0.f;
+        const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
+        if (direct) {
+            if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, p.seq, head, d));
+            store_from_f32(a.out, ((size_t)p.seq * a.nh + head) * a.out_row_stride + d, a.out_dtype, val);
+        } else {
+            rec_of(head)[d] = val;
         }
     }
     if (direct || a.force_partials || a.defer_merge) return;
@@ -766,7 +788,7 @@ __global__ void __launch_bounds__(NW * 32) decode32_kernel(const DecodeArgs a) {
     __shared__ float sm_o[NW * GT * HD];
     __shared__ uint32_t sm_item[8];
     constexpr uint32_t kScratchWords = 3072;   // merge scratch: >= 2*spans + 2*GT for any balanced launch
-    __shared__ uint32_t sm_scratch[kScratchWords];
+    __shared__ __align__(16) uint32_t sm_scratch[kScratchWords];   // finish_piece keeps 64-bit row addresses at its head
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t zi = blockIdx.x % a.gz, kvh = (blockIdx.x / a.gz) % a.nkv;
