@@ -198,7 +198,8 @@ __device__ __forceinline__ bool next_piece(const DecodeArgs &a, Cursor &cur, Pie
 // them (gqa_reduce.wgsl:20-65) — no second launch.
 // Warp w's O tile starts at sm_o + w*WSTRIDE floats, rows of HD floats.
 // The CTA serves KPC kv heads (kvh_base + k); warps k, k+KPC, k+2*KPC, ... share kv head k.
-template <int R, int HD, int NW, int WSTRIDE, int KPC>
+// OSTRIDE: floats between consecutive head rows of a warp's O tile (padded by the 16-bit kernel against bank conflicts)
+template <int R, int HD, int NW, int WSTRIDE, int KPC, int OSTRIDE = HD>
 __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p, float *sm_m, float *sm_l,
                                              const float *sm_o, uint32_t *sm_flag, uint32_t *scratch,
                                              uint32_t scratch_words, uint32_t kvh_base, uint32_t row0,
@@ -244,20 +245,28 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
         }
     }
     __syncthreads();
-    for (uint32_t idx = threadIdx.x; idx < KPC * rows_valid * HD; idx += NW * 32) {
-        const uint32_t d = idx % HD, hr = idx / HD, r = hr % rows_valid, kvl = hr / rows_valid;
-        float o = 0.f;
+    // rows outside, head dims across the threads: no index arithmetic with run-time divisors per element
+    {
+        uint32_t r = 0, kvl = 0;
+#pragma unroll 4
+        for (uint32_t hr = 0; hr < KPC * rows_valid; ++hr) {
+            const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
+            const float L = sm_l[kvl * R + r];
+            float *rec = direct ? nullptr : rec_of(head);
+            for (uint32_t d = threadIdx.x; d < HD; d += NW * 32) {
+                float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < NW; ++w)
-            if (w % KPC == (int)kvl) o += sm_o[(size_t)w * WSTRIDE + r * HD + d] * sm_m[w * R + r];   // empty warps: 0 * 0
-        const float L = sm_l[kvl * R + r];
-        float val = L > 0.f ? o / L : 0.f;
-        const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
-        if (direct) {
-            if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, p.seq, head, d));
-            store_from_f32(a.out, ((size_t)p.seq * a.nh + head) * a.out_row_stride + d, a.out_dtype, val);
-        } else {
-            rec_of(head)[d] = val;
+                for (int w = 0; w < NW; ++w)
+                    if (w % KPC == (int)kvl) o += sm_o[(size_t)w * WSTRIDE + r * OSTRIDE + d] * sm_m[w * R + r];   // empty warps: 0 * 0
+                float val = L > 0.f ? o / L : 0.f;
+                if (direct) {
+                    if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, p.seq, head, d));
+                    store_from_f32(a.out, ((size_t)p.seq * a.nh + head) * a.out_row_stride + d, a.out_dtype, val);
+                } else {
+                    rec[d] = val;
+                }
+            }
+            if (++r == rows_valid) { r = 0; ++kvl; }
         }
     }
     if (direct || a.force_partials || a.defer_merge) return;
@@ -289,6 +298,50 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
         }
     }
     __syncthreads();
+    if (nrec <= 4) {
+        // Few records (the usual case of a batch: a sequence cut by one or two span boundaries): every thread requests
+        // the log-sum-exps and the values of its elements in one go — one L2 round trip instead of three with two
+        // CTA barriers in between.
+        // four head rows at a time, all their loads requested before the first is used
+        for (uint32_t d = threadIdx.x; d < HD; d += NW * 32) {
+            for (uint32_t hr0 = 0; hr0 < rows_total; hr0 += 4) {
+                float l[4][4], v[4][4];
+                uint32_t heads[4];
+#pragma unroll
+                for (uint32_t k = 0; k < 4; ++k) {
+                    const uint32_t hr = min(hr0 + k, rows_total - 1);           // clamped rows recompute a valid row
+                    heads[k] = (kvh_base + hr / rows_valid) * a.G + row0 + hr % rows_valid;
+#pragma unroll
+                    for (uint32_t s2 = 0; s2 < 4; ++s2) {
+                        const float *rp = a.partials + ((size_t)sm_rec[min(s2, nrec - 1)] + (size_t)heads[k] * hmul) * (HD + 2);
+                        l[k][s2] = s2 < nrec ? __ldcg(rp + HD) : -INFINITY;
+                        v[k][s2] = s2 < nrec ? __ldcg(rp + d) : 0.f;
+                    }
+                }
+#pragma unroll
+                for (uint32_t k = 0; k < 4; ++k) {
+                    if (hr0 + k >= rows_total) break;
+                    float gmax = -INFINITY;
+#pragma unroll
+                    for (uint32_t s2 = 0; s2 < 4; ++s2)
+                        if (l[k][s2] > -INFINITY) gmax = fmaxf(gmax, l[k][s2]);
+                    float acc = 0.f, wsum = 0.f;
+#pragma unroll
+                    for (uint32_t s2 = 0; s2 < 4; ++s2) {
+                        const float w = l[k][s2] > -INFINITY ? expf(l[k][s2] - gmax) : 0.f;   // gqa_reduce.wgsl:56; empty ranges weigh nothing
+                        acc += w > 0.f ? w * v[k][s2] : 0.f;
+                        wsum += w;
+                    }
+                    float val = wsum > 0.f ? acc / wsum : 0.f;
+                    const uint32_t head = heads[k];
+                    if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, p.seq, head, d));
+                    store_from_f32(a.out, ((size_t)p.seq * a.nh + head) * a.out_row_stride + d, a.out_dtype, val);
+                    if (d == 0 && a.lse) a.lse[((size_t)p.seq * a.nh + head) * a.lse_stride] = wsum > 0.f ? gmax + logf(wsum) : -INFINITY;
+                }
+            }
+        }
+        return;
+    }
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (uint32_t rg0 = 0; rg0 < rows_total; rg0 += RG) {
         const uint32_t nrows = min(RG, rows_total - rg0);
@@ -415,7 +468,10 @@ template <int HD, int NW, int STAGES, int KPC> struct Decode16Smem {
     static constexpr int kQBytes = KPC * kQTile;
     static constexpr int kStatBytes = (2 * NW * 16 * 4 > HD * 4) ? 2 * NW * 16 * 4 : HD * 4;   // merge m and l; cos/sin table of the fused append
     static constexpr int kTotal = kQBytes + NW * kWarpBytes + kStatBytes + 32;
-    static_assert(kWarpBytes >= 16 * HD * 4, "merge tile must fit in the warp's pipeline memory");
+    // floats per head row of a warp's O tile: 8 pad floats put the eight rows a store instruction touches on different
+    // banks (where the warp's pipeline memory has room for them)
+    static constexpr int kORow = kWarpBytes >= 16 * (HD + 8) * 4 ? HD + 8 : HD;
+    static_assert(kWarpBytes >= 16 * kORow * 4, "merge tile must fit in the warp's pipeline memory");
 };
 
 // Resident CTAs per SM each configuration is built for (bounds the registers per thread).
@@ -761,14 +817,19 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             sm_l[warp * 16 + g] = l_run[0];
             sm_l[warp * 16 + g + 8] = l_run[1];
         }
+        if (g < rows_valid) {          // only the head rows that exist go to shared memory
 #pragma unroll
-        for (int jn = 0; jn < HD / 8; ++jn) {
-            *reinterpret_cast<float2 *>(my_o + g * HD + jn * 8 + 2 * t) = make_float2(o[jn][0], o[jn][1]);
-            *reinterpret_cast<float2 *>(my_o + (g + 8) * HD + jn * 8 + 2 * t) = make_float2(o[jn][2], o[jn][3]);
+            for (int jn = 0; jn < HD / 8; ++jn)
+                *reinterpret_cast<float2 *>(my_o + g * S::kORow + jn * 8 + 2 * t) = make_float2(o[jn][0], o[jn][1]);
+        }
+        if (g + 8 < rows_valid) {
+#pragma unroll
+            for (int jn = 0; jn < HD / 8; ++jn)
+                *reinterpret_cast<float2 *>(my_o + (g + 8) * S::kORow + jn * 8 + 2 * t) = make_float2(o[jn][2], o[jn][3]);
         }
         __syncthreads();
         // after its first loop finish_piece no longer reads the O tiles: the pipeline memory doubles as merge scratch
-        finish_piece<16, HD, NW, S::kWarpBytes / 4, KPC>(a, p, sm_m, sm_l, sm_o, sm_item + 7,
+        finish_piece<16, HD, NW, S::kWarpBytes / 4, KPC, S::kORow>(a, p, sm_m, sm_l, sm_o, sm_item + 7,
                                                          reinterpret_cast<uint32_t *>(sm_pipe), NW * S::kWarpBytes / 4,
                                                          kg * KPC, row0, rows_valid, (p.seq * KG + kg) * a.gz + zi);
         __syncthreads();  // the next piece overwrites Q and the pipeline memory
