@@ -43,6 +43,7 @@ struct DecodeArgs {
     uint32_t num_splits; // >0: every sequence is cut into ceil(L/ns) ranges (wgsl:46-48); 0: balanced spans
     uint32_t line_blocks; // balanced mode: total row-blocks of the batch, sum_i max(1, ceil(L_i/16))
     uint32_t spans;       // balanced mode: number of equal spans the line is cut into
+    uint32_t span_math32; // (spans + 1) * line_blocks + spans < 2^32: span arithmetic in 32 bits
     uint32_t q_dtype, out_dtype;
     uint32_t force_partials;  // 1: always write the partial record (shady_attn_decode_partials)
     uint32_t defer_merge;     // 1: CTAs only write records; balanced_merge_kernel merges them (sequences cut into many spans)
@@ -107,10 +108,14 @@ __device__ __forceinline__ bool has_gate(const DecodeArgs &a) { return a.fuse_ap
 // [ceil(c*T/C), ceil((c+1)*T/C)).  A span may end one sequence, hold several whole ones and start
 // another; each intersection is a "piece".  Every CTA streams the same number of rows, so there is
 // one full wave and no tail.
+// (products that fit 32 bits — every batch short of some 50 million rows — take the 32-bit divider: the 64-bit one
+//  is a long dependent instruction sequence, and these sit at the head of every piece)
 __device__ __forceinline__ uint32_t span_begin(const DecodeArgs &a, uint32_t c) {
+    if (a.span_math32) return (c * a.line_blocks + a.spans - 1) / a.spans;
     return (uint32_t)(((unsigned long long)c * a.line_blocks + a.spans - 1) / a.spans);
 }
 __device__ __forceinline__ uint32_t span_of(const DecodeArgs &a, uint32_t u) {
+    if (a.span_math32) return (u * a.spans) / a.line_blocks;
     return (uint32_t)(((unsigned long long)u * a.spans) / a.line_blocks);
 }
 __device__ __forceinline__ uint32_t blocks_of(uint32_t L) { return L == 0 ? 1u : (L + kBlkPos - 1) / kBlkPos; }
@@ -271,9 +276,9 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
     }
     if (direct || a.force_partials || a.defer_merge) return;
     // ---- last-arriving CTA merges the records ----
-    __threadfence();
-    __syncthreads();
+    __syncthreads();   // every thread's record stores are issued ...
     if (threadIdx.x == 0) {
+        __threadfence();   // ... and this fence, being cumulative over what the barrier ordered before it, publishes them all
         // atomicInc wraps to 0 when the old value is nrec-1, so the counter is zero again for the next call
         const uint32_t old = atomicInc(&a.counters[counter_idx], p.nrec - 1u);
         *sm_flag = (old == p.nrec - 1u);
@@ -1370,6 +1375,7 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
         if (spans < 1) spans = 1;
         a.line_blocks = (uint32_t)line;
         a.spans = (uint32_t)spans;
+        a.span_math32 = (spans + 1) * line + spans < 0xffffffffull ? 1u : 0u;
         items = spans;
         need_ws = spans > 1;  // a sequence may straddle spans whenever there is more than one
         // a sequence cut into many spans is merged by a wide second launch instead of by its last CTA
@@ -1510,6 +1516,7 @@ int launch_decode_static(shady_ctx *ctx, const shady_decode_params *p, const voi
         if (spans < 1) spans = 1;
         a.line_blocks = (uint32_t)line;
         a.spans = (uint32_t)spans;
+        a.span_math32 = (spans + 1) * line + spans < 0xffffffffull ? 1u : 0u;
         items = spans;
         recs = spans > 1 ? 2 * spans : 0;
     }
