@@ -96,6 +96,35 @@ __device__ __forceinline__ void load8_as_f32(const void *p, size_t i, uint32_t d
     }
 }
 
+// The same access in two halves: the request (raw 16 or 32 bytes, nothing depends on them yet) and the conversion.
+// A thread stalls at the first use of loaded data, so requests that should overlap other work must stay raw.
+__device__ __forceinline__ void load8_raw(const void *p, size_t i, uint32_t dt, uint4 (&r)[2]) {
+    if (dt == SHADY_F32) {
+        r[0] = *reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(p) + i);
+        r[1] = *reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(p) + i + 4);
+    } else {
+        r[0] = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p) + i);
+        r[1] = make_uint4(0, 0, 0, 0);
+    }
+}
+__device__ __forceinline__ void cvt8_raw(const uint4 (&r)[2], uint32_t dt, float (&v)[8]) {
+    if (dt == SHADY_F32) {
+        v[0] = __uint_as_float(r[0].x); v[1] = __uint_as_float(r[0].y); v[2] = __uint_as_float(r[0].z); v[3] = __uint_as_float(r[0].w);
+        v[4] = __uint_as_float(r[1].x); v[5] = __uint_as_float(r[1].y); v[6] = __uint_as_float(r[1].z); v[7] = __uint_as_float(r[1].w);
+    } else {
+        const uint32_t w[4] = {r[0].x, r[0].y, r[0].z, r[0].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (dt == SHADY_F16) {
+                const __half2 h = *reinterpret_cast<const __half2 *>(&w[k]);
+                v[2 * k] = __low2float(h); v[2 * k + 1] = __high2float(h);
+            } else {
+                v[2 * k] = __uint_as_float(w[k] << 16); v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ float gate_value(const DecodeArgs &a, uint32_t seq, uint32_t head, uint32_t d) {
     if (a.fuse_append)   // the gate is the second half of the token's q_proj_full row (wgsl:122-135)
         return load_as_f32(a.ap_q, ((size_t)seq * a.nh + head) * 2 * a.hd + a.hd + d, a.ap_in_dtype);
@@ -580,7 +609,31 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
                 cp_async16(st + soff, src + (ok ? goff : 0), ok);
             }
         };
-        // ---- start the K/V stream first, then fetch Q underneath it ----
+        // ---- fused append: the projected rows of this piece are requested before the K/V stream.  Behind the burst of
+        //      tile copies they waited two microseconds in the memory queues, and nothing can be computed without Q ----
+        constexpr int QIT = (KPC * 16 * CH + NW * 32 - 1) / (NW * 32);
+        uint4 q_req[QIT][2], own_req[NIT][2];
+        if (a.fuse_append) {
+#pragma unroll
+            for (int qi = 0; qi < QIT; ++qi) {
+                const uint32_t idx = tid + qi * NW * 32;
+                const uint32_t c = idx % CH, r = (idx / CH) % 16, k = idx / (CH * 16);
+                q_req[qi][0] = q_req[qi][1] = make_uint4(0, 0, 0, 0);
+                if (idx < KPC * 16 * CH && r < rows_valid) {
+                    const size_t e0 = ((size_t)p.seq * a.nh + (kg * KPC + k) * a.G + row0 + r) * (a.ap_has_gate ? 2 * HD : HD) + c * 8;
+                    load8_raw(a.ap_q, e0, a.ap_in_dtype, q_req[qi]);
+                }
+            }
+            if (owner) {
+#pragma unroll
+                for (int it = 0; it < NIT; ++it) {
+                    const uint32_t tt = lane + 32 * it;
+                    const uint32_t is_v = tt < 2 * CH ? tt / CH : 1u, c = tt % CH;
+                    load8_raw(is_v ? a.ap_v : a.ap_k, ((size_t)p.seq * a.nkv + kvh) * HD + c * 8, a.ap_in_dtype, own_req[it]);
+                }
+            }
+        }
+        // ---- start the K/V stream, the rest of the prologue runs underneath it ----
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
             if ((uint32_t)s < n_items) issue(s);
@@ -596,27 +649,17 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             for (int it = 0; it < NIT; ++it) {
                 const uint32_t tt = lane + 32 * it;
                 const uint32_t is_v = tt < 2 * CH ? tt / CH : 1u, c = tt % CH;
-                load8_as_f32(is_v ? a.ap_v : a.ap_k, ((size_t)p.seq * a.nkv + kvh) * HD + c * 8, a.ap_in_dtype, own_raw[it]);
+                (void)is_v; (void)c;
+                cvt8_raw(own_req[it], a.ap_in_dtype, own_raw[it]);
             }
         }
         // stage Q of the CTA's kv heads (rows >= rows_valid are zero) as T, swizzled
         if (a.fuse_append) {
             // raw Q row -> RMSNorm(1+w) -> RoPE at position L-1 (wgsl:126-166); CH consecutive threads share a row.
             // cos/sin of the rotary pairs are the same for all rows: one table per piece in the merge-statistics area
-            // the raw rows are requested first: their latency passes under the cos/sin table, not after it
-            constexpr int QIT = (KPC * 16 * CH + NW * 32 - 1) / (NW * 32);
             float qraw[QIT][8];
 #pragma unroll
-            for (int qi = 0; qi < QIT; ++qi) {
-                const uint32_t idx = tid + qi * NW * 32;
-                const uint32_t c = idx % CH, r = (idx / CH) % 16, k = idx / (CH * 16);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) qraw[qi][e] = 0.f;
-                if (idx < KPC * 16 * CH && r < rows_valid) {
-                    const size_t e0 = ((size_t)p.seq * a.nh + (kg * KPC + k) * a.G + row0 + r) * (a.ap_has_gate ? 2 * HD : HD) + c * 8;
-                    load8_as_f32(a.ap_q, e0, a.ap_in_dtype, qraw[qi]);
-                }
-            }
+            for (int qi = 0; qi < QIT; ++qi) cvt8_raw(q_req[qi], a.ap_in_dtype, qraw[qi]);
             const uint32_t pos = p.L ? p.L - 1 : 0;
             float2 *sm_cs = reinterpret_cast<float2 *>(sm_m);   // HD/2 pairs; sm_m/sm_l are free until the piece ends
             for (uint32_t i2 = tid; i2 < HD / 2; i2 += NW * 32) {
