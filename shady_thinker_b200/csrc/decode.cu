@@ -47,6 +47,8 @@ struct DecodeArgs {
     uint32_t q_dtype, out_dtype;
     uint32_t force_partials;  // 1: always write the partial record (shady_attn_decode_partials)
     uint32_t defer_merge;     // 1: CTAs only write records; balanced_merge_kernel merges them (sequences cut into many spans)
+    uint32_t grid_merge;      // 1 (with defer_merge, cooperative launch): the decode grid meets at a barrier and merges the records itself
+    uint32_t *grid_sync;      // workspace: {arrivals, departures} of that barrier; zero between calls
     uint32_t out_row_stride;  // elements between consecutive head rows of `out` (hd, or hd+2 when out is a record buffer)
     uint32_t lse_stride;      // elements between consecutive entries of `lse` (1, or hd+2 inside a record buffer)
     float scale_log2;         // 1/sqrt(hd) * log2(e)
@@ -508,6 +510,116 @@ template <int HD, int NW, int STAGES, int KPC> struct Decode16Smem {
     static_assert(kWarpBytes >= 16 * kORow * 4, "merge tile must fit in the warp's pipeline memory");
 };
 
+// ---------------------------------------------------------------------------------------
+// Record merge by the decode grid itself (cooperative launch, a.grid_merge).  A sequence that is cut into many
+// spans would leave its merge to a second launch; ~10 us behind a 50 us kernel, most of it launch gap and
+// ramp-up.  Here every CTA, after its last record, arrives at a grid barrier (the launch is cooperative, so all
+// CTAs are resident; the wait is bounded all the same and raises the status word if it runs out), and the grid
+// then merges the records: a work item is 32 dims of one head, warp g of the CTA takes the records g, g + NW, ...
+// with a running maximum of its own (values and log-sum-exps of a batch requested together: one L2 round trip),
+// and the warps are rescaled to a common maximum and summed through shared memory.  The last CTA
+// to leave zeroes the barrier for the next launch.
+// ---------------------------------------------------------------------------------------
+constexpr uint32_t kGridSpinLimit = 1u << 21;
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+constexpr int kTailBatch = 12;   // records whose value and log-sum-exp one thread requests together
+
+template <int NW>
+__device__ __noinline__ void grid_merge_tail(const DecodeArgs &a, uint32_t *scratch) {
+    const uint32_t tid = threadIdx.x, g = tid >> 5, t = tid & 31u;
+    float *sm_acc = reinterpret_cast<float *>(scratch);                // [NW][32] weighted sums of each warp's records
+    float *sm_ws = sm_acc + NW * 32;                                   // [NW] sums of weights
+    float *sm_mx = sm_ws + NW;                                         // [NW] the maximum each warp's weights refer to
+    uint32_t *sm_misc = reinterpret_cast<uint32_t *>(sm_mx + NW);      // {barrier passed, first row-block of the sequence}
+    if (tid == 0) {
+        __threadfence();   // cumulative over the record stores the CTA barrier before this call ordered
+        atomicAdd(a.grid_sync, 1u);
+        uint32_t ok = 0;
+        for (uint32_t i = 0; i < kGridSpinLimit; ++i)
+            if (ld_acquire_gpu(a.grid_sync) >= gridDim.x) { ok = 1; break; }
+        if (!ok && a.px_error) atomicCAS(a.px_error, 0, 90);
+        sm_misc[0] = ok;
+    }
+    __syncthreads();
+    if (!sm_misc[0]) return;   // the barrier words stay dirty: the status word tells the host to re-initialise the workspace
+    const uint32_t chunks = a.hd / 32, items = a.num_seqs * a.nh * chunks, rs = a.hd + 2;
+    for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
+        const uint32_t chunk = it % chunks, head = (it / chunks) % a.nh, seq = it / (chunks * a.nh);
+        const uint32_t d = chunk * 32 + t;
+        if (tid < 32) {   // first row-block of this sequence on the line
+            uint32_t acc = 0;
+            for (uint32_t j = tid; j < seq; j += 32) acc += blocks_of(seq_len_at(a, j));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (tid == 0) sm_misc[1] = acc;
+        }
+        __syncthreads();
+        const uint32_t B = sm_misc[1], nb = blocks_of(seq_len_at(a, seq));
+        const uint32_t c0 = span_of(a, B), nrec = span_of(a, B + nb - 1) - c0 + 1;
+        if (nrec > 1) {       // a single record went straight to a.out / a.lse
+            // only the sequence's first span can have begun before the sequence: its record is in slot 1 then
+            const uint32_t first_slot = span_begin(a, c0) >= B ? 0u : 1u;
+            float m = -INFINITY, acc = 0.f, wsum = 0.f;
+            for (uint32_t base = g; base < nrec; base += kTailBatch * NW) {
+                float v[kTailBatch], l[kTailBatch];
+#pragma unroll
+                for (int i = 0; i < kTailBatch; ++i) {   // one round trip for the whole batch, values and weights together
+                    const uint32_t s = base + i * NW;
+                    v[i] = 0.f; l[i] = -INFINITY;
+                    if (s < nrec) {
+                        const float *row = a.partials + ((size_t)((c0 + s) * 2 + (s == 0 ? first_slot : 0u)) * a.nh + head) * rs;
+                        v[i] = __ldcg(row + d);
+                        l[i] = __ldcg(row + a.hd);
+                    }
+                }
+                float bm = m;
+#pragma unroll
+                for (int i = 0; i < kTailBatch; ++i) bm = fmaxf(bm, l[i]);
+                if (bm > -INFINITY) {
+                    const float sc = expf(m - bm);           // 0 while nothing has been accumulated (m = -inf)
+                    acc *= sc; wsum *= sc;
+#pragma unroll
+                    for (int i = 0; i < kTailBatch; ++i)
+                        if (l[i] > -INFINITY) {              // gqa_reduce.wgsl:56; empty ranges weigh nothing
+                            const float w = expf(l[i] - bm);
+                            acc += w * v[i];
+                            wsum += w;
+                        }
+                    m = bm;
+                }
+            }
+            sm_acc[g * 32 + t] = acc;
+            if (t == 0) { sm_ws[g] = wsum; sm_mx[g] = m; }
+            __syncthreads();
+            if (g == 0) {
+                float gmax = -INFINITY;
+#pragma unroll
+                for (int k = 0; k < NW; ++k) gmax = fmaxf(gmax, sm_mx[k]);
+                acc = 0.f; wsum = 0.f;
+#pragma unroll
+                for (int k = 0; k < NW; ++k)
+                    if (sm_mx[k] > -INFINITY) {
+                        const float sc = expf(sm_mx[k] - gmax);
+                        acc += sc * sm_acc[k * 32 + t];
+                        wsum += sc * sm_ws[k];
+                    }
+                float val = wsum > 0.f ? acc / wsum : 0.f;
+                if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, seq, head, d));
+                store_from_f32(a.out, ((size_t)seq * a.nh + head) * a.out_row_stride + d, a.out_dtype, val);
+                if (d == 0 && a.lse) a.lse[((size_t)seq * a.nh + head) * a.lse_stride] = wsum > 0.f ? gmax + logf(wsum) : -INFINITY;
+            }
+        }
+        __syncthreads();   // the scratch words are rewritten for the next item
+    }
+    if (tid == 0 && atomicInc(a.grid_sync + 1, gridDim.x - 1) == gridDim.x - 1) *a.grid_sync = 0;   // every CTA is past the wait
+}
+
 // Resident CTAs per SM each configuration is built for (bounds the registers per thread).
 constexpr int decode16_min_blocks(int HD, int NW, int STAGES) {
     return HD > 128 ? 1 : (NW == 4 ? (STAGES <= 6 ? 2 : 1) : 1);
@@ -516,7 +628,7 @@ constexpr int decode16_min_blocks(int HD, int NW, int STAGES) {
 // KPC kv heads per CTA: warp w streams kv head (w % KPC) of the CTA's rows, and the WPK = NW/KPC warps
 // that share a kv head take alternate 16-position blocks.  With KPC == nkv a CTA reads whole cache rows.
 template <typename T, int HD, int NW, int STAGES, int KPC>
-__global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) decode16_kernel(const DecodeArgs a) {
+__global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) decode16_kernel(const __grid_constant__ DecodeArgs a) {
     using S = Decode16Smem<HD, NW, STAGES, KPC>;
     constexpr int WPK = NW / KPC;
     static_assert(NW % KPC == 0, "warps must divide evenly over the kv heads of a CTA");
@@ -882,6 +994,7 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
                                                          kg * KPC, row0, rows_valid, (p.seq * KG + kg) * a.gz + zi);
         __syncthreads();  // the next piece overwrites Q and the pipeline memory
     }
+    if (a.grid_merge) grid_merge_tail<NW>(a, reinterpret_cast<uint32_t *>(sm_pipe));
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1075,8 +1188,7 @@ __global__ void __launch_bounds__(kMergeThreads) balanced_merge_kernel(const Dec
     bool single;
     merge_balanced_records(a, seq, head, d, val, lse, single);
     if (single || threadIdx.x >= 64 || d >= a.hd) return;   // a single record is already in place
-    const size_t gi = ((size_t)seq * a.nh + head) * a.hd + d;
-    if (a.gate) val *= sigmoidf_ref(a.gate[gi]);
+    if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, seq, head, d));
     store_from_f32(a.out, ((size_t)seq * a.nh + head) * a.out_row_stride + d, a.out_dtype, val);
     if (d == 0 && a.lse) a.lse[((size_t)seq * a.nh + head) * a.lse_stride] = lse;
 }
@@ -1205,7 +1317,13 @@ static int launch16(shady_ctx *ctx, const DecodeArgs &a, uint32_t blocks) {
         SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
         configured_dev = ctx->device;
     }
-    kern<<<blocks, NW * 32, S::kTotal, ctx->stream>>>(a);
+    if (a.grid_merge) {   // the grid barrier needs every CTA resident: a cooperative launch, refused if they would not fit
+        void *params[] = {const_cast<DecodeArgs *>(&a)};
+        SHADY_CUDA_OK(ctx, cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kern), dim3(blocks), dim3(NW * 32), params,
+                                                       S::kTotal, ctx->stream));
+    } else {
+        kern<<<blocks, NW * 32, S::kTotal, ctx->stream>>>(a);
+    }
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
@@ -1275,10 +1393,12 @@ static uint32_t env_u32(const char *name, uint32_t dflt) {
 }
 constexpr uint32_t kDeferMergeRecords = 12;  // more records than this per sequence: merge in a second launch
 
-// Workspace layout: [arrival counters: num_seqs*nkv*gz u32, padded to 256 B][partial records].
+// Workspace layout: [arrival counters: num_seqs*nkv*gz u32][grid barrier: 2 u32], padded to 256 B, [partial records].
+static size_t counter_words(const shady_decode_params *p) {
+    return (size_t)p->num_seqs * p->num_kv_heads * ((p->heads_per_kv + 15) / 16 + p->heads_per_kv);
+}
 static size_t counters_bytes(const shady_decode_params *p) {
-    const size_t n = (size_t)p->num_seqs * p->num_kv_heads * ((p->heads_per_kv + 15) / 16 + p->heads_per_kv);
-    return (n * sizeof(uint32_t) + 255) / 256 * 256;
+    return ((counter_words(p) + 2) * sizeof(uint32_t) + 255) / 256 * 256;   // + the two words of the grid barrier
 }
 size_t decode_workspace_bytes(const shady_decode_params *p) {
     if (p->num_splits == 1) return 0;
@@ -1435,10 +1555,17 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
         SHADY_REQUIRE(ctx, d_ws && ws_bytes >= need, SHADY_ERR_WORKSPACE, "decode: workspace missing or too small");
         a.counters = reinterpret_cast<uint32_t *>(d_ws);
         a.partials = reinterpret_cast<float *>(reinterpret_cast<char *>(d_ws) + counters_bytes(p));
+        a.grid_sync = a.counters + counter_words(p);
     }
     const unsigned long long blocks64 = items * kv_groups * a.gz;
     SHADY_REQUIRE(ctx, blocks64 <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "decode: too many work items for one launch");
     const uint32_t blocks = (uint32_t)blocks64;
+    // one launch instead of two when the grid is one resident wave (it is sized from the SM count above) and nothing
+    // is exchanged with peers; SHADY_DECODE_GRID_MERGE=0 keeps the second launch
+    if (a.defer_merge && !px && !f32 && env_u32("SHADY_DECODE_GRID_MERGE", 1)) {
+        if (const int st = p2p_error_word(ctx, &a.px_error)) return st;
+        a.grid_merge = 1;
+    }
 
     int rc;
     if (f32) {
@@ -1456,7 +1583,7 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
         else if (var.stages == 2) rc = launch16_kpc<256, 8, 2>(ctx, a, kpc, h, blocks);
         else rc = launch16_kpc<256, 8, 3>(ctx, a, kpc, h, blocks);
     }
-    if (rc != SHADY_OK || !a.defer_merge) return rc;
+    if (rc != SHADY_OK || !a.defer_merge || a.grid_merge) return rc;
     // (launching the merge as a programmatic dependent of the decode grid measured slower: 72.7 vs 67.4 us per step)
     if (px) shard_merge_p2p_kernel<<<dim3(1, p->num_q_heads, p2p_chunks(hd)), kMergeThreads, 0, ctx->stream>>>(a);
     else balanced_merge_kernel<<<dim3(p->num_seqs, p->num_q_heads, (hd + 63) / 64), kMergeThreads, 0, ctx->stream>>>(a);

@@ -131,6 +131,8 @@ int p2p_status(shady_ctx *ctx, int *code) {
     SHADY_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
     if (*code) {
         SHADY_CUDA_OK(ctx, cudaMemsetAsync(g_p2p_error[ctx->device], 0, sizeof(int), ctx->stream));
+        if (*code == 90)
+            return fail(ctx, SHADY_ERR_TIMEOUT, "decode: the grid barrier before the record merge ran out; re-initialise the workspace");
         return fail(ctx, SHADY_ERR_TIMEOUT, "combine_p2p: the flag of rank " + std::to_string(*code - 100) + " did not arrive in time");
     }
     return SHADY_OK;

@@ -288,14 +288,14 @@ def test_decode_shard_records_merge_rank_major(gpu_ctx, oracle):
     assert np.isneginf(rh[0, :, hd]).all() and not rh[0, :, :hd].any()
 
 
+@pytest.mark.parametrize("lens", [[1, 16, 17, 700, 2500, 33], [20000, 50]], ids=["short", "deferred-merge"])
 @pytest.mark.parametrize("dt,in_dt,norm,gate,rd", [(F16, F16, False, False, 128), (BF16, F32, True, True, 32),
                                                    (F16, F32, True, False, 64)])
-def test_fused_append_decode_equals_the_two_calls(gpu_ctx, oracle, dt, in_dt, norm, gate, rd):
+def test_fused_append_decode_equals_the_two_calls(gpu_ctx, oracle, dt, in_dt, norm, gate, rd, lens):
     """shady_attn_decode_append == shady_kv_append_rope followed by shady_attn_decode (+ gate), cache rows included."""
     from _util import TORCH_DT
     nh, nkv, hd = 32, 8, 128
-    lens = [1, 16, 17, 700, 2500, 33]                      # lengths INCLUDING the appended token
-    S = len(lens)
+    S = len(lens)                                          # lengths INCLUDE the appended token
     qmul = 2 if gate else 1
     q_full = rounded(oracle, oracle.randn((S, nh, qmul * hd), 81, 1), in_dt)
     k_new = rounded(oracle, oracle.randn((S, nkv, hd), 81, 2), in_dt)
@@ -337,3 +337,36 @@ def test_fused_append_decode_equals_the_two_calls(gpu_ctx, oracle, dt, in_dt, no
         np.testing.assert_array_equal(to_host(c2.k[i])[:L - 1], ks[i][:L - 1])            # older rows untouched
         # Q is rounded to the cache dtype when staged in both paths only if in_dt == dt; allow the 16-bit tolerance
         assert rel_err(to_host(got)[i], to_host(want)[i]) <= RTOL_16, (i, L)
+
+
+@pytest.mark.parametrize("dt,nh,nkv,hd,lens", [(BF16, 16, 2, 256, [40000]), (F16, 32, 8, 128, [30000, 100, 5000, 1])])
+def test_merge_by_the_decode_grid_equals_the_second_launch(gpu_ctx, oracle, monkeypatch, dt, nh, nkv, hd, lens):
+    """Sequences cut into more spans than their last CTA merges alone: by default the decode grid meets at a barrier
+    and merges the records itself (one cooperative launch); SHADY_DECODE_GRID_MERGE=0 keeps the second launch.  Both
+    must give the reference's merge (gqa_reduce.wgsl:33-64) of the same records, gate included, launch after launch
+    (the barrier words zero themselves)."""
+    S = len(lens)
+    q = rounded(oracle, oracle.randn((S, nh, hd), 71, 1), dt)
+    gate = torch.from_numpy(oracle.randn((S, nh, hd), 71, 2)).cuda()
+    ks = [rounded(oracle, oracle.randn((L, nkv, hd), 71, 10 + i), dt) for i, L in enumerate(lens)]
+    vs = [rounded(oracle, oracle.randn((L, nkv, hd), 71, 50 + i), dt) for i, L in enumerate(lens)]
+    cache = RaggedCache(ks, vs, dt)
+    n0 = gpu_ctx.launch_count
+    outs = [run_decode(gpu_ctx, q, cache.view, lens, nh=nh, nkv=nkv, hd=hd, num_splits=0, q_dt=dt, out_dt=F32,
+                       want_lse=True, gate=gate) for _ in range(3)]
+    assert gpu_ctx.launch_count - n0 == 3            # one launch per decode
+    for o, l in outs[1:]:
+        np.testing.assert_array_equal(o, outs[0][0])
+        np.testing.assert_array_equal(l, outs[0][1])
+    monkeypatch.setenv("SHADY_DECODE_GRID_MERGE", "0")
+    n0 = gpu_ctx.launch_count
+    two, two_lse = run_decode(gpu_ctx, q, cache.view, lens, nh=nh, nkv=nkv, hd=hd, num_splits=0, q_dt=dt, out_dt=F32,
+                              want_lse=True, gate=gate)
+    assert gpu_ctx.launch_count - n0 == 2
+    one, one_lse = outs[0]
+    assert np.abs(one - two).max() <= 2e-6 * max(1.0, np.abs(two).max())
+    assert np.abs(one_lse - two_lse).max() <= 1e-5
+    sig = 1.0 / (1.0 + np.exp(-to_host(gate).astype(np.float64)))
+    for i, L in enumerate(lens):
+        want = oracle.attention_f64(q[i], ks[i], vs[i], L, threads=8) * sig[i]
+        assert rel_err(one[i], want) <= RTOL_16, (i, L)
