@@ -241,8 +241,8 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
                                              uint32_t scratch_words, uint32_t kvh_base, uint32_t row0,
                                              uint32_t rows_valid, uint32_t counter_idx) {
     const bool direct = (p.nrec == 1u) && !a.force_partials;
-    // ---- per head row, once: the warps' weights e_w = 2^(m_w - M) (left in sm_m in place of m_w), the row's sum L
-    //      (left in sm_l of the head's first warp) and its log-sum-exp.  Which record slot the piece writes is one
+    // ---- per head row, once: the warps' weights e_w = 2^(m_w - M), the row's sum L, the normalised weights e_w / L
+    //      (left in sm_m in place of m_w) and the row's log-sum-exp.  Which record slot the piece writes is one
     //      64-bit division (rec_ptr) for the whole piece: it is resolved here, not per element ----
     const bool ref_layout = a.num_splits || a.force_partials;
     uint32_t rec_row0 = 0;
@@ -269,7 +269,11 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
             if (mw > -INFINITY) L += sm_l[w * R + r] * e;
             sm_m[w * R + r] = e;
         }
-        sm_l[kvl * R + r] = L;
+        // the element loop below multiplies by e_w / L: one division per head row here instead of one per element there
+        const float inv_l = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w)
+            if (w % KPC == (int)kvl) sm_m[w * R + r] *= inv_l;
         const float lse = L > 0.f ? logf(L) + M * kLn2 : -INFINITY;
         const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
         if (direct) {
@@ -287,14 +291,12 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
 #pragma unroll 4
         for (uint32_t hr = 0; hr < KPC * rows_valid; ++hr) {
             const uint32_t head = (kvh_base + kvl) * a.G + row0 + r;
-            const float L = sm_l[kvl * R + r];
             float *rec = direct ? nullptr : rec_of(head);
             for (uint32_t d = threadIdx.x; d < HD; d += NW * 32) {
-                float o = 0.f;
+                float val = 0.f;
 #pragma unroll
                 for (int w = 0; w < NW; ++w)
-                    if (w % KPC == (int)kvl) o += sm_o[(size_t)w * WSTRIDE + r * OSTRIDE + d] * sm_m[w * R + r];   // empty warps: 0 * 0
-                float val = L > 0.f ? o / L : 0.f;
+                    if (w % KPC == (int)kvl) val += sm_o[(size_t)w * WSTRIDE + r * OSTRIDE + d] * sm_m[w * R + r];   // empty warps and rows: 0 * 0
                 if (direct) {
                     if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, p.seq, head, d));
                     store_from_f32(a.out, ((size_t)p.seq * a.nh + head) * a.out_row_stride + d, a.out_dtype, val);
@@ -530,8 +532,26 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
 
 constexpr int kTailBatch = 12;   // records whose value and log-sum-exp one thread requests together
 
+// What the tail reads in its dependent chains, by value: the function is not inlined (inlined, it cost the
+// streaming loop registers), and through the reference every field of the kernel's parameter block is a
+// generic-address load, several of them in a row ahead of the first record request.
+struct TailArgs {
+    const float *partials;
+    void *out;
+    float *lse;
+    uint32_t *grid_sync;
+    int *status;
+    uint32_t nh, hd, num_seqs, out_row_stride, lse_stride, out_dtype, spans, line_blocks, span_math32, gated;
+    uint32_t len0;   // length of sequence 0 (the others are read through the reference)
+};
+__device__ __forceinline__ TailArgs tail_args(const DecodeArgs &a) {
+    return TailArgs{a.partials, a.out, a.lse, a.grid_sync, a.px_error, a.nh, a.hd, a.num_seqs, a.out_row_stride,
+                    a.lse_stride, a.out_dtype, a.spans, a.line_blocks, a.span_math32, has_gate(a) ? 1u : 0u,
+                    seq_len_at(a, 0)};
+}
+
 template <int NW>
-__device__ __noinline__ void grid_merge_tail(const DecodeArgs &a, uint32_t *scratch) {
+__device__ __noinline__ void grid_merge_tail(const DecodeArgs &a, const TailArgs ta, uint32_t *scratch) {
     const uint32_t tid = threadIdx.x, g = tid >> 5, t = tid & 31u;
     float *sm_acc = reinterpret_cast<float *>(scratch);                // [NW][32] weighted sums of each warp's records
     float *sm_ws = sm_acc + NW * 32;                                   // [NW] sums of weights
@@ -539,32 +559,60 @@ __device__ __noinline__ void grid_merge_tail(const DecodeArgs &a, uint32_t *scra
     uint32_t *sm_misc = reinterpret_cast<uint32_t *>(sm_mx + NW);      // {barrier passed, first row-block of the sequence}
     if (tid == 0) {
         __threadfence();   // cumulative over the record stores the CTA barrier before this call ordered
-        atomicAdd(a.grid_sync, 1u);
+        atomicAdd(ta.grid_sync, 1u);
+    }
+    auto first_block_of_span = [&](uint32_t c) {   // span_begin / span_of on the by-value fields
+        return ta.span_math32 ? (c * ta.line_blocks + ta.spans - 1) / ta.spans
+                              : (uint32_t)(((unsigned long long)c * ta.line_blocks + ta.spans - 1) / ta.spans);
+    };
+    auto span_of_block = [&](uint32_t u) {
+        return ta.span_math32 ? (u * ta.spans) / ta.line_blocks : (uint32_t)(((unsigned long long)u * ta.spans) / ta.line_blocks);
+    };
+    const uint32_t chunks = ta.hd / 32, items = ta.num_seqs * ta.nh * chunks, rs = ta.hd + 2;
+    // Where an item's records are: three integer divisions and, past the first sequence, a sum over the lengths.
+    // A long dependent chain, so the first item's is worked out before the wait below, not after it.
+    struct Item { uint32_t seq, head, d, nrec; const float *row0; uint32_t skip0; };
+    auto locate = [&](uint32_t it) {
+        Item x;
+        const uint32_t chunk = it % chunks;
+        x.head = (it / chunks) % ta.nh; x.seq = it / (chunks * ta.nh); x.d = chunk * 32 + t;
+        uint32_t B = 0;
+        if (x.seq) {   // first row-block of this sequence on the line
+            __syncthreads();
+            if (tid < 32) {
+                uint32_t acc = 0;
+                for (uint32_t j = tid; j < x.seq; j += 32) acc += blocks_of(seq_len_at(a, j));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (tid == 0) sm_misc[1] = acc;
+            }
+            __syncthreads();
+            B = sm_misc[1];
+        }
+        const uint32_t nb = blocks_of(x.seq ? seq_len_at(a, x.seq) : ta.len0);
+        const uint32_t c0 = span_of_block(B);
+        x.nrec = span_of_block(B + nb - 1) - c0 + 1;
+        // only the sequence's first span can have begun before the sequence: its record is in slot 1 then
+        x.skip0 = first_block_of_span(c0) >= B ? 0u : 1u;
+        x.row0 = ta.partials + ((size_t)(c0 * 2) * ta.nh + x.head) * rs;     // slot 0 of the sequence's first span
+        return x;
+    };
+    Item cur{};
+    if (blockIdx.x < items) cur = locate(blockIdx.x);
+    if (tid == 0) {
         uint32_t ok = 0;
         for (uint32_t i = 0; i < kGridSpinLimit; ++i)
-            if (ld_acquire_gpu(a.grid_sync) >= gridDim.x) { ok = 1; break; }
-        if (!ok && a.px_error) atomicCAS(a.px_error, 0, 90);
+            if (ld_acquire_gpu(ta.grid_sync) >= gridDim.x) { ok = 1; break; }
+        if (!ok && ta.status) atomicCAS(ta.status, 0, 90);
         sm_misc[0] = ok;
     }
     __syncthreads();
     if (!sm_misc[0]) return;   // the barrier words stay dirty: the status word tells the host to re-initialise the workspace
-    const uint32_t chunks = a.hd / 32, items = a.num_seqs * a.nh * chunks, rs = a.hd + 2;
     for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
-        const uint32_t chunk = it % chunks, head = (it / chunks) % a.nh, seq = it / (chunks * a.nh);
-        const uint32_t d = chunk * 32 + t;
-        if (tid < 32) {   // first row-block of this sequence on the line
-            uint32_t acc = 0;
-            for (uint32_t j = tid; j < seq; j += 32) acc += blocks_of(seq_len_at(a, j));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (tid == 0) sm_misc[1] = acc;
-        }
-        __syncthreads();
-        const uint32_t B = sm_misc[1], nb = blocks_of(seq_len_at(a, seq));
-        const uint32_t c0 = span_of(a, B), nrec = span_of(a, B + nb - 1) - c0 + 1;
-        if (nrec > 1) {       // a single record went straight to a.out / a.lse
-            // only the sequence's first span can have begun before the sequence: its record is in slot 1 then
-            const uint32_t first_slot = span_begin(a, c0) >= B ? 0u : 1u;
+        const uint32_t seq = cur.seq, head = cur.head, d = cur.d, nrec = cur.nrec;
+        if (nrec > 1) {       // a single record went straight to the output
+            const size_t span_stride = (size_t)2 * ta.nh * rs;               // floats between the slot-0 records of two spans
+            const float *row_first = cur.row0 + (cur.skip0 ? (size_t)ta.nh * rs : 0);
             float m = -INFINITY, acc = 0.f, wsum = 0.f;
             for (uint32_t base = g; base < nrec; base += kTailBatch * NW) {
                 float v[kTailBatch], l[kTailBatch];
@@ -573,9 +621,9 @@ __device__ __noinline__ void grid_merge_tail(const DecodeArgs &a, uint32_t *scra
                     const uint32_t s = base + i * NW;
                     v[i] = 0.f; l[i] = -INFINITY;
                     if (s < nrec) {
-                        const float *row = a.partials + ((size_t)((c0 + s) * 2 + (s == 0 ? first_slot : 0u)) * a.nh + head) * rs;
+                        const float *row = s == 0 ? row_first : cur.row0 + s * span_stride;
                         v[i] = __ldcg(row + d);
-                        l[i] = __ldcg(row + a.hd);
+                        l[i] = __ldcg(row + ta.hd);
                     }
                 }
                 float bm = m;
@@ -610,14 +658,17 @@ __device__ __noinline__ void grid_merge_tail(const DecodeArgs &a, uint32_t *scra
                         wsum += sc * sm_ws[k];
                     }
                 float val = wsum > 0.f ? acc / wsum : 0.f;
-                if (has_gate(a)) val *= sigmoidf_ref(gate_value(a, seq, head, d));
-                store_from_f32(a.out, ((size_t)seq * a.nh + head) * a.out_row_stride + d, a.out_dtype, val);
-                if (d == 0 && a.lse) a.lse[((size_t)seq * a.nh + head) * a.lse_stride] = wsum > 0.f ? gmax + logf(wsum) : -INFINITY;
+                if (ta.gated) val *= sigmoidf_ref(gate_value(a, seq, head, d));
+                store_from_f32(ta.out, ((size_t)seq * ta.nh + head) * ta.out_row_stride + d, ta.out_dtype, val);
+                if (d == 0 && ta.lse) ta.lse[((size_t)seq * ta.nh + head) * ta.lse_stride] = wsum > 0.f ? gmax + logf(wsum) : -INFINITY;
             }
         }
-        __syncthreads();   // the scratch words are rewritten for the next item
+        if (it + gridDim.x < items) {
+            __syncthreads();   // the scratch words are rewritten for the next item
+            cur = locate(it + gridDim.x);
+        }
     }
-    if (tid == 0 && atomicInc(a.grid_sync + 1, gridDim.x - 1) == gridDim.x - 1) *a.grid_sync = 0;   // every CTA is past the wait
+    if (tid == 0 && atomicInc(ta.grid_sync + 1, gridDim.x - 1) == gridDim.x - 1) *ta.grid_sync = 0;   // every CTA is past the wait
 }
 
 // Resident CTAs per SM each configuration is built for (bounds the registers per thread).
@@ -994,7 +1045,7 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
                                                          kg * KPC, row0, rows_valid, (p.seq * KG + kg) * a.gz + zi);
         __syncthreads();  // the next piece overwrites Q and the pipeline memory
     }
-    if (a.grid_merge) grid_merge_tail<NW>(a, reinterpret_cast<uint32_t *>(sm_pipe));
+    if (a.grid_merge) grid_merge_tail<NW>(a, tail_args(a), reinterpret_cast<uint32_t *>(sm_pipe));
 }
 
 // ---------------------------------------------------------------------------------------
