@@ -286,7 +286,34 @@ __device__ __forceinline__ void finish_piece(const DecodeArgs &a, const Piece &p
     }
     __syncthreads();
     // rows outside, head dims across the threads: no index arithmetic with run-time divisors per element
-    {
+    if constexpr (KPC == 1) {
+        // four head rows per round: all their shared-memory reads first, then the stores (a store to global memory
+        // in between keeps the compiler from moving the next row's reads above it, and the rows ran one after another)
+        for (uint32_t d = threadIdx.x; d < HD; d += NW * 32) {
+            for (uint32_t r0 = 0; r0 < rows_valid; r0 += 4) {
+                float val[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t r = min(r0 + j, rows_valid - 1);   // past the last row: a valid read, never stored
+                    val[j] = 0.f;
+#pragma unroll
+                    for (int w = 0; w < NW; ++w) val[j] += sm_o[(size_t)w * WSTRIDE + r * OSTRIDE + d] * sm_m[w * R + r];   // empty warps and rows: 0 * 0
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (r0 + j >= rows_valid) break;
+                    const uint32_t head = kvh_base * a.G + row0 + r0 + j;
+                    if (direct) {
+                        float v = val[j];
+                        if (has_gate(a)) v *= sigmoidf_ref(gate_value(a, p.seq, head, d));
+                        store_from_f32(a.out, ((size_t)p.seq * a.nh + head) * a.out_row_stride + d, a.out_dtype, v);
+                    } else {
+                        rec_of(head)[d] = val[j];
+                    }
+                }
+            }
+        }
+    } else {
         uint32_t r = 0, kvl = 0;
 #pragma unroll 4
         for (uint32_t hr = 0; hr < KPC * rows_valid; ++hr) {
