@@ -720,12 +720,12 @@ def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
             "config": {"workload": "cfg4: long-context single-sequence decode, rows split over GPUs, LSE merge over NCCL",
                        "context": L, "num_q_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "kv_dtype": "bf16",
                        "rows_per_gpu": rows, "combine": "none" if world == 1 else ("NCCL all-gather of 16.5 KB records + merge kernel" if use_nccl else
-                                   ("two launches per step: decode, then one kernel = rank-local merge + peer stores over NVLink + flags + merge"
+                                   ("one cooperative launch per step: decode, grid barrier, rank-local merge + peer stores over NVLink + flags + merge across ranks"
                                     if mode == "fused" else "one kernel: peer stores of 16.5 KB records over NVLink + flags + merge")),
                        "l2": f"{n_sets} cache sets rotate between steps"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
                          "peak_source": f"{src} (copy bandwidth)",
-                         "kernel": ("decode16_kernel<bf16,256> on this rank's rows + merge/exchange kernel (the rank's whole step)"
+                         "kernel": ("decode16_kernel<bf16,256> on this rank's rows with the merge and the NVLink exchange in its tail (the rank's whole step)"
                                     if world > 1 and mode == "fused" and not use_nccl else "decode16_kernel<bf16,256> on this rank's rows"),
                          "algorithmic_bytes_per_launch": 2.0 * rows * row_bytes, "avg_launch_ms": dec_ms},
             "gpu_launches": int(launches)}), flush=True)

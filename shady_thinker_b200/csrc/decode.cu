@@ -698,6 +698,162 @@ __device__ __noinline__ void grid_merge_tail(const DecodeArgs &a, const TailArgs
     if (tid == 0 && atomicInc(ta.grid_sync + 1, gridDim.x - 1) == gridDim.x - 1) *ta.grid_sync = 0;   // every CTA is past the wait
 }
 
+// The same tail for a row-sharded sequence (one process per GPU): after the grid barrier a CTA merges 64 dims of one
+// head from this rank's records (two groups of NW/2 warps, 32 dims each) and the two finishing warps then do what
+// shard_merge_p2p_kernel does — slice and log-sum-exp into every rank's exchange buffer with plain peer stores, a
+// system-scope release flag per (rank, head, chunk), a bounded wait for the peers' flags, the merge across ranks.
+// One launch per step instead of two.
+template <int NW>
+__device__ __noinline__ void grid_exchange_tail(const DecodeArgs &a, const TailArgs ta, uint32_t *scratch) {
+    constexpr int HW = NW / 2;   // warps per 32-dim half
+    static_assert(NW >= 2 && NW % 2 == 0, "two groups of warps");
+    const uint32_t tid = threadIdx.x, g = tid >> 5, t = tid & 31u, half = g / HW, gw = g % HW;
+    float *sm_acc = reinterpret_cast<float *>(scratch);                // [NW][32]
+    float *sm_ws = sm_acc + NW * 32;                                   // [NW]
+    float *sm_mx = sm_ws + NW;                                         // [NW]
+    float *sm_lse = sm_mx + NW;                                        // [kP2PMaxWorld]
+    uint32_t *sm_misc = reinterpret_cast<uint32_t *>(sm_lse + kP2PMaxWorld);   // {barrier passed, a flag wait ran out}
+    if (tid == 0) {
+        __threadfence();
+        atomicAdd(ta.grid_sync, 1u);
+        sm_misc[1] = 0;
+    }
+    // everything the exchange needs from the parameter block and the peer table, read while the barrier fills
+    const uint32_t world = a.px_world, rank = a.px_rank, epoch = a.px_epoch, par = epoch & 1u, out_dt = a.px_out_dtype;
+    char *const *bases = a.px_peer_bases;
+    void *const final_out = a.px_out;
+    const float *const final_gate = a.px_gate;
+    const uint32_t xt = half * 32 + t;                                 // 0..63 within the two finishing warps
+    char *const my_base = bases[rank];
+    char *const peer_base = xt < world ? bases[xt] : nullptr;
+    const uint32_t nb = blocks_of(ta.len0);
+    const uint32_t nrec = (ta.span_math32 ? ((nb - 1) * ta.spans) / ta.line_blocks
+                                          : (uint32_t)(((unsigned long long)(nb - 1) * ta.spans) / ta.line_blocks)) + 1;
+    const uint32_t chunks = p2p_chunks(ta.hd), items = ta.nh * chunks, rs = ta.hd + 2;
+    const unsigned long long flags_bytes = p2p_chunk_flags_bytes(world, ta.nh, ta.hd);
+    if (tid == 0) {
+        uint32_t ok = 0;
+        for (uint32_t i = 0; i < kGridSpinLimit; ++i)
+            if (ld_acquire_gpu(ta.grid_sync) >= gridDim.x) { ok = 1; break; }
+        if (!ok && ta.status) atomicCAS(ta.status, 0, 90);
+        sm_misc[0] = ok;
+    }
+    __syncthreads();
+    if (!sm_misc[0]) return;
+    auto bar64 = [] { asm volatile("bar.sync 1, 64;" ::: "memory"); };
+    for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
+        const uint32_t head = it / chunks, chunk = it % chunks;
+        const uint32_t d = chunk * kP2PChunk + xt, dd = min(d, ta.hd - 1);
+        float val, lse;
+        if (nrec == 1) {   // the only record went straight to the rank's record buffer (ta.out / ta.lse)
+            val = __ldcg(reinterpret_cast<const float *>(ta.out) + (size_t)head * ta.out_row_stride + dd);
+            lse = ta.lse ? __ldcg(ta.lse + (size_t)head * ta.lse_stride) : 0.f;
+        } else {
+            const float *row0 = ta.partials + (size_t)head * rs;      // slot 0 of span 0 (the sequence starts the line)
+            const size_t span_stride = (size_t)2 * ta.nh * rs;
+            float m = -INFINITY, acc = 0.f, wsum = 0.f;
+            for (uint32_t base = gw; base < nrec; base += kTailBatch * HW) {
+                float v[kTailBatch], l[kTailBatch];
+#pragma unroll
+                for (int i = 0; i < kTailBatch; ++i) {
+                    const uint32_t s = base + i * HW;
+                    v[i] = 0.f; l[i] = -INFINITY;
+                    if (s < nrec) {
+                        const float *row = row0 + s * span_stride;
+                        v[i] = __ldcg(row + dd);
+                        l[i] = __ldcg(row + ta.hd);
+                    }
+                }
+                float bm = m;
+#pragma unroll
+                for (int i = 0; i < kTailBatch; ++i) bm = fmaxf(bm, l[i]);
+                if (bm > -INFINITY) {
+                    const float sc = expf(m - bm);
+                    acc *= sc; wsum *= sc;
+#pragma unroll
+                    for (int i = 0; i < kTailBatch; ++i)
+                        if (l[i] > -INFINITY) {              // gqa_reduce.wgsl:56; empty ranges weigh nothing
+                            const float w = expf(l[i] - bm);
+                            acc += w * v[i];
+                            wsum += w;
+                        }
+                    m = bm;
+                }
+            }
+            sm_acc[g * 32 + t] = acc;
+            if (t == 0) { sm_ws[g] = wsum; sm_mx[g] = m; }
+            __syncthreads();
+            float gmax = -INFINITY;
+#pragma unroll
+            for (int k = 0; k < HW; ++k) gmax = fmaxf(gmax, sm_mx[half * HW + k]);
+            acc = 0.f; wsum = 0.f;
+#pragma unroll
+            for (int k = 0; k < HW; ++k) {
+                const float mk = sm_mx[half * HW + k];
+                if (mk > -INFINITY) {
+                    const float sc = expf(mk - gmax);
+                    acc += sc * sm_acc[(half * HW + k) * 32 + t];
+                    wsum += sc * sm_ws[half * HW + k];
+                }
+            }
+            val = wsum > 0.f ? acc / wsum : 0.f;
+            lse = wsum > 0.f ? gmax + logf(wsum) : -INFINITY;
+        }
+        if (gw == 0) {   // the first warp of each half: 64 threads, meeting at a named barrier of their own
+            const size_t my_slot = (((size_t)par * world + rank) * ta.nh + head) * chunks + chunk;
+            for (uint32_t r = 0; r < world; ++r) {
+                float *dst = reinterpret_cast<float *>(bases[r] + flags_bytes) + my_slot * kP2PSlotFloats;
+                dst[xt] = val;
+                if (xt == 0) dst[kP2PChunk] = lse;
+            }
+            // the barrier orders the 64 threads' slot stores before the flag stores of threads 0..world-1, and a release
+            // at system scope is cumulative over what happened before it
+            bar64();
+            if (xt < world) {
+                st_release_sys(reinterpret_cast<uint32_t *>(peer_base) + my_slot, epoch);
+                const uint32_t *flag = reinterpret_cast<const uint32_t *>(my_base) +
+                                       (((size_t)par * world + xt) * ta.nh + head) * chunks + chunk;
+                bool ok = false;
+                for (uint32_t i = 0; i < kP2PSpinLimit; ++i) {
+                    if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) { ok = true; break; }
+                    if ((i & 4095u) == 4095u && *reinterpret_cast<volatile int *>(ta.status)) break;   // somebody already gave up
+                }
+                if (!ok) {
+                    sm_misc[1] = 1;
+                    atomicCAS(ta.status, 0, 100 + (int)xt);
+                }
+            }
+            bar64();
+            if (!sm_misc[1]) {
+                const float *mine = reinterpret_cast<const float *>(my_base + flags_bytes);
+                auto slot_of = [&](uint32_t r) { return mine + ((((size_t)par * world + r) * ta.nh + head) * chunks + chunk) * kP2PSlotFloats; };
+                if (xt < world) sm_lse[xt] = __ldcg(slot_of(xt) + kP2PChunk);
+                bar64();
+                if (d < ta.hd) {
+                    float gmax = -INFINITY;
+                    for (uint32_t r = 0; r < world; ++r)
+                        if (sm_lse[r] > -INFINITY) gmax = fmaxf(gmax, sm_lse[r]);
+                    float acc = 0.f, wsum = 0.f;
+                    for (uint32_t r = 0; r < world; ++r) {
+                        const float l = sm_lse[r];
+                        if (!(l > -INFINITY)) continue;
+                        const float w = expf(l - gmax);
+                        acc += w * __ldcg(slot_of(r) + xt);
+                        wsum += w;
+                    }
+                    float out = wsum > 0.f ? acc / wsum : 0.f;
+                    const size_t oi = (size_t)head * ta.hd + d;
+                    if (final_gate) out *= sigmoidf_ref(final_gate[oi]);
+                    store_from_f32(final_out, oi, out_dt, out);
+                }
+            }
+        }
+        __syncthreads();   // scratch and sm_lse are rewritten by the next item
+        if (sm_misc[1]) break;
+    }
+    if (tid == 0 && atomicInc(ta.grid_sync + 1, gridDim.x - 1) == gridDim.x - 1) *ta.grid_sync = 0;
+}
+
 // Resident CTAs per SM each configuration is built for (bounds the registers per thread).
 constexpr int decode16_min_blocks(int HD, int NW, int STAGES) {
     return HD > 128 ? 1 : (NW == 4 ? (STAGES <= 6 ? 2 : 1) : 1);
@@ -1072,7 +1228,10 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
                                                          kg * KPC, row0, rows_valid, (p.seq * KG + kg) * a.gz + zi);
         __syncthreads();  // the next piece overwrites Q and the pipeline memory
     }
-    if (a.grid_merge) grid_merge_tail<NW>(a, tail_args(a), reinterpret_cast<uint32_t *>(sm_pipe));
+    if (a.grid_merge) {
+        if (a.px_world) grid_exchange_tail<NW>(a, tail_args(a), reinterpret_cast<uint32_t *>(sm_pipe));
+        else grid_merge_tail<NW>(a, tail_args(a), reinterpret_cast<uint32_t *>(sm_pipe));
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1638,9 +1797,9 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
     const unsigned long long blocks64 = items * kv_groups * a.gz;
     SHADY_REQUIRE(ctx, blocks64 <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "decode: too many work items for one launch");
     const uint32_t blocks = (uint32_t)blocks64;
-    // one launch instead of two when the grid is one resident wave (it is sized from the SM count above) and nothing
-    // is exchanged with peers; SHADY_DECODE_GRID_MERGE=0 keeps the second launch
-    if (a.defer_merge && !px && !f32 && env_u32("SHADY_DECODE_GRID_MERGE", 1)) {
+    // one launch instead of two: the grid is one resident wave (it is sized from the SM count above), so it can meet
+    // at a barrier and merge (and, row-sharded, exchange) itself; SHADY_DECODE_GRID_MERGE=0 keeps the second launch
+    if (a.defer_merge && a.grid_sync && !f32 && env_u32("SHADY_DECODE_GRID_MERGE", 1)) {   // (a single span has no workspace)
         if (const int st = p2p_error_word(ctx, &a.px_error)) return st;
         a.grid_merge = 1;
     }

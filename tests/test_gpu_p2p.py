@@ -32,10 +32,13 @@ def test_world_of_one_is_a_copy_with_gate(gpu_ctx, oracle):
     comb.close()
 
 
+@pytest.mark.parametrize("grid_merge", ["1", "0"])
 @pytest.mark.parametrize("L", [100, 20000])
-def test_world_of_one_fused_step_equals_plain_decode(gpu_ctx, oracle, L):
-    """decode + (merge, exchange, merge) in two launches with a world of one gives what shady_attn_decode gives:
-    a single span (record written directly) and many spans (records merged by the exchange kernel)."""
+def test_world_of_one_fused_step_equals_plain_decode(gpu_ctx, oracle, monkeypatch, L, grid_merge):
+    """decode + (merge, exchange, merge) with a world of one gives what shady_attn_decode gives: a single span (record
+    written directly) and many spans (records merged before the exchange), both as one cooperative launch (merge and
+    exchange in the decode kernel's tail, the default) and as two launches (SHADY_DECODE_GRID_MERGE=0)."""
+    monkeypatch.setenv("SHADY_DECODE_GRID_MERGE", grid_merge)
     from _util import rounded, run_decode
     from shady_thinker_b200 import ops
     from shady_thinker_b200.p2p import ShardCombiner
@@ -51,12 +54,14 @@ def test_world_of_one_fused_step_equals_plain_decode(gpu_ctx, oracle, L):
     ws = torch.zeros(max(ws_n, 4), dtype=torch.uint8, device="cuda")
     rec = torch.zeros((1, nh, hd + 2), device="cuda")
     lens = torch.tensor([L], dtype=torch.int32).cuda()
+    n0 = gpu_ctx.launch_count
     for step in range(3):
         d_out = torch.full((nh, hd), float("nan"), device="cuda")
         comb.decode_and_combine(q=to_dev(q, BF16), cache=view, seq_lens=lens, seq_len_host=L, records=rec, out=d_out,
                                 num_kv_heads=nkv, q_dtype=BF16, gate=to_dev(gate), workspace=ws, workspace_bytes=ws_n)
         gpu_ctx.synchronize()
         assert np.abs(to_host(d_out) - want).max() <= 2e-6 * max(1.0, float(np.abs(want).max()))
+    assert gpu_ctx.launch_count - n0 == (3 if grid_merge == "1" and L > 512 else 6)   # a single span keeps two launches
     comb.close()
 
 
