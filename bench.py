@@ -31,9 +31,11 @@ NH, NKV, HD = 32, 8, 128
 SEQS_PER_GPU = 32
 LMIN, LMAX = 1024, 8192
 N_SETS = 3            # rotating cache sets so no step finds its KV rows in L2
-# DRAM bytes per algorithmic byte of the decode kernel, from the ncu capture summarised in
-# profiles/decode16_f16_hd128_cfg2.md (read + write bytes of one launch over its algorithmic bytes).
+# DRAM bytes (read + write, one launch) per algorithmic byte of the headline decode kernel, as ncu counted them on
+# this workload, and the commit whose kernel was captured; the ratio is a property of the kernel's access pattern,
+# so a launch timed here is credited with its own algorithmic bytes times this figure.
 TRAFFIC_PER_ALGO_BYTE = 1.011
+TRAFFIC_MEASURED_AT = "5c1021b (ncu --set full, decode16_kernel<half,128,4,6,1>, 528.8 MB DRAM for 523.3 MB algorithmic)"
 
 
 def draw_lengths(rank: int) -> np.ndarray:
@@ -218,14 +220,14 @@ def workload_config(n_gpus: int, shape: str = "plain") -> dict:
             "l2": f"KV per step > L2 and {N_SETS} cache sets rotate between steps"}
 
 
-def cpu_baseline(rank: int, dec, lens: np.ndarray) -> dict:
+def cpu_baseline(rank: int, row_off, lens: np.ndarray) -> dict:
     """Oracle (f32-faithful port) on a bounded sample of the same batch, all host threads."""
     from oracle import oracle as O
     O.build()
     threads = host_threads(O)
     order = np.argsort(lens)[::-1]
     seqs = [int(s) for s in order[:8]]
-    ks, vs = host_set(O, lens, dec.row_off, 0, rank, seqs)
+    ks, vs = host_set(O, lens, row_off, 0, rank, seqs)
     q = O.round_f16(O.randn((8, NH, HD), SEED, 5))
     use = [int(lens[s]) for s in seqs]
     nbytes = sum(use) * NKV * HD * 2 * 2
@@ -287,6 +289,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         sets.append(d)
     gpu.synchronize()
     step_bytes = sets[0].kv_bytes_per_step()
+    row_off0 = sets[0].row_off
 
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -343,8 +346,29 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         barrier()
         e2e_ms = f0.elapsed_time(f1)
         assert torch.isfinite(ho.float()).all(), "e2e output is not finite"
+        # ---------------- a longer witness of the same launch: 100 blocks of 20 back-to-back launches ----------------
+        long_blocks, long_per = 100, 20
+        lb = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(long_blocks)]
+        k = 0
+        for a_ev, b_ev in lb:
+            a_ev.record(stream)
+            for _ in range(long_per):
+                sets[k % N_SETS].step()
+                k += 1
+            b_ev.record(stream)
+        barrier()
+        long_ms = np.array([a_ev.elapsed_time(b_ev) / long_per for a_ev, b_ev in lb])
     sampler.stop_flag = True
     sampler.join(timeout=2)
+    headline_clocks = sampler.summary(t_wall0, t_wall1)
+
+    # ---------------- the other half of the metric and the cross-GPU kernel, after the headline ----------------
+    extra = {}
+    if not args.no_extra:
+        for d in sets:
+            d.close()
+        extra["cfg3"] = measure_cfg3(gpu, stream, rank, world, local_rank, dist, barrier, steps=30, warmup=3)
+        extra["cfg4"] = measure_cfg4(gpu, stream, rank, world, local_rank, dist, barrier, steps=200, warmup=10)
 
     # ---------------- reduce over ranks: max time, sum bytes ----------------
     t = torch.tensor([total_ms, e2e_ms, attend_ms], dtype=torch.float64, device="cuda")
@@ -372,8 +396,13 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                          "traffic": (TRAFFIC_PER_ALGO_BYTE * step_bytes) if TRAFFIC_PER_ALGO_BYTE else None,
                          "peak_source": f"{peak_src} (copy bandwidth)",
                          "kernel": "decode16_kernel<half,128> with the fused append and split merge (the whole step is this one launch)",
+                         "traffic_source": f"algorithmic bytes x {TRAFFIC_PER_ALGO_BYTE}, the DRAM-byte ratio ncu measured at {TRAFFIC_MEASURED_AT}",
                          "algorithmic_bytes_per_launch": step_bytes, "avg_launch_ms": attend_ms,
-                         "avg_launch_ms_single_bracketed": bracketed_ms},
+                         "avg_launch_ms_single_bracketed": bracketed_ms,
+                         "avg_launch_ms_long": {"launches": int(long_blocks * long_per), "median": float(np.median(long_ms)),
+                                                "p10": float(np.percentile(long_ms, 10)), "p90": float(np.percentile(long_ms, 90)),
+                                                "frac_at_median": step_bytes / (float(np.median(long_ms)) * 1e-3) / 1e9 / peak,
+                                                "how": "100 event-bracketed blocks of 20 back-to-back launches, per-launch time of each block"}},
             "e2e": {"value": all_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": d0.in_bytes, "d2h_bytes_per_step": d0.out_bytes, "steps": e2e_steps,
                     "ms_per_step": e2e_ms / e2e_steps,
@@ -381,10 +410,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                              "pinned output over the host link itself, then one stream sync") if d0.fused else
                             "BatchedDecoder.step_from_host: H2D copies, launches, D2H copy, one stream sync"},
             "gpu_launches": int(launches),
-            "clocks": sampler.summary(t_wall0, t_wall1),
+            "clocks": headline_clocks,
         }
+        if extra:
+            line["extra"] = extra
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(rank, sets[0], lens)
+            line["cpu_baseline"] = cpu_baseline(rank, row_off0, lens)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -405,7 +436,7 @@ def prefill_flops(B=P_B, T=P_T, nh=P_NH, hd=P_HD) -> float:
 
 
 def prefill_config(n_gpus: int) -> dict:
-    return {"workload": "cfg3: causal prefill attention, one layer, RoPE+cache write then attention per step",
+    return {"workload": "cfg3: causal prefill attention, one layer; a step = K/V norm+RoPE+cache write, then attention with Q normed/rotated in the kernel",
             "batch_per_gpu": P_B, "seq_len": P_T, "num_q_heads": P_NH, "num_kv_heads": P_NKV, "head_dim": P_HD,
             "dtype": "bf16", "softmax": "fp32", "rope_theta": 1e6,
             "sharding": f"batch items over {n_gpus} GPU(s), no collective",
@@ -453,74 +484,137 @@ def run_reference_prefill(args, rank: int) -> None:
     }))
 
 
-def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
-    import torch
+class _Cfg3:
+    """Buffers and the two calls of a cfg3 step (append with RoPE + cache write, then the tcgen05 attention)."""
 
-    from shady_thinker_b200 import ops
-    from shady_thinker_b200._lib import BF16
-    from shady_thinker_b200.gpu import GpuContext
+    def __init__(self, gpu, rank: int):
+        from shady_thinker_b200 import ops
+        from shady_thinker_b200._lib import BF16
+        B, T, nh, nkv, hd = P_B, P_T, P_NH, P_NKV, P_HD
+        self.gpu, self.ops, self.BF16 = gpu, ops, BF16
+        self.nq, self.nk = B * T * nh * hd, B * T * nkv * hd
+        mk = gpu.create_storage_buffer
+        self.bufs = {n: mk(n, (self.nq if n in ("q_in", "q_rot", "out") else self.nk) * 2)
+                     for n in ("q_in", "k_in", "v_in", "q_rot", "out", "k_cache", "v_cache")}
+        self.pos = gpu.upload_buffer("pos", np.zeros(B, np.uint32).tobytes())
+        base = 5000 + 10 * rank
+        b = self.bufs
+        ops.fill_randn(gpu, b["q_in"], self.nq, BF16, SEED, base + 1)
+        ops.fill_randn(gpu, b["k_in"], self.nk, BF16, SEED, base + 2)
+        ops.fill_randn(gpu, b["v_in"], self.nk, BF16, SEED, base + 3)
+        self.view = ops.KvCacheView(BF16, b["k_cache"], b["v_cache"], T * nkv * hd)
+        self.ws_n = ops.prefill_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_seqs=B, seq_len=T, dtype=BF16)
+        self.ws = mk("prefill_ws", self.ws_n)
 
-    torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    def append(self):
+        b = self.bufs
+        self.ops.kv_append_rope(self.gpu, q_proj_full=b["q_in"], k_proj=b["k_in"], v_proj=b["v_in"], q_out=b["q_rot"],
+                                q_gate=None, cache=self.view, pos_start=self.pos, num_heads=P_NH, num_kv_heads=P_NKV,
+                                head_dim=P_HD, rope_theta=1e6, rotary_dim=P_HD, num_seqs=P_B, tokens_per_seq=P_T,
+                                in_dtype=self.BF16, q_dtype=self.BF16, has_gate=False, write_k_back=False)
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    def attend(self):
+        b = self.bufs
+        self.ops.attn_prefill(self.gpu, q=b["q_rot"], cache=self.view, out=b["out"], head_dim=P_HD, num_kv_heads=P_NKV,
+                              num_q_heads=P_NH, num_seqs=P_B, seq_len=P_T, dtype=self.BF16)
 
-    B, T, nh, nkv, hd = P_B, P_T, P_NH, P_NKV, P_HD
-    stream = torch.cuda.Stream()
-    gpu = GpuContext(local_rank, stream=stream.cuda_stream)
-    nq, nk = B * T * nh * hd, B * T * nkv * hd
-    mk = gpu.create_storage_buffer
-    q_in, k_in, v_in = mk("q_in", nq * 2), mk("k_in", nk * 2), mk("v_in", nk * 2)
-    q_rot, out = mk("q_rot", nq * 2), mk("out", nq * 2)
-    k_cache, v_cache = mk("k_cache", nk * 2), mk("v_cache", nk * 2)
-    pos = gpu.upload_buffer("pos", np.zeros(B, np.uint32).tobytes())
-    base = 5000 + 10 * rank
-    ops.fill_randn(gpu, q_in, nq, BF16, SEED, base + 1)
-    ops.fill_randn(gpu, k_in, nk, BF16, SEED, base + 2)
-    ops.fill_randn(gpu, v_in, nk, BF16, SEED, base + 3)
-    view = ops.KvCacheView(BF16, k_cache, v_cache, T * nkv * hd)
+    def step(self):
+        """The whole step through the public call: K/V pass (norm, RoPE, cache rows), then the attention kernel that
+        takes Q raw from the projection (norm + RoPE per tile in shared memory)."""
+        b = self.bufs
+        self.ops.attn_prefill_append(self.gpu, q_proj_full=b["q_in"], k_proj=b["k_in"], v_proj=b["v_in"], cache=self.view,
+                                     out=b["out"], workspace=self.ws, workspace_bytes=self.ws_n, num_heads=P_NH,
+                                     num_kv_heads=P_NKV, head_dim=P_HD, num_seqs=P_B, seq_len=P_T, rope_theta=1e6,
+                                     rotary_dim=P_HD, dtype=self.BF16)
 
-    def append():
-        ops.kv_append_rope(gpu, q_proj_full=q_in, k_proj=k_in, v_proj=v_in, q_out=q_rot, q_gate=None, cache=view,
-                           pos_start=pos, num_heads=nh, num_kv_heads=nkv, head_dim=hd, rope_theta=1e6, rotary_dim=hd,
-                           num_seqs=B, tokens_per_seq=T, in_dtype=BF16, q_dtype=BF16, has_gate=False,
-                           write_k_back=False)
+    def close(self):
+        for b in list(self.bufs.values()) + [self.pos, self.ws]:
+            self.gpu.destroy_buffer(b)
+        self.bufs = {}
 
-    def attend():
-        ops.attn_prefill(gpu, q=q_rot, cache=view, out=out, head_dim=hd, num_kv_heads=nkv, num_q_heads=nh,
-                         num_seqs=B, seq_len=T, dtype=BF16)
 
-    gpu.synchronize()
+def _time_cfg3(torch, c: "_Cfg3", gpu, stream, barrier, steps: int, warmup: int, local_rank: int):
+    """(total_ms, attend_ms, launches, clocks, two_call_ms): `steps` whole steps through shady_attn_prefill_append
+    (total_ms), then `steps` steps of the two-call form (append, then the attention kernel on the rotated Q) with the
+    attention launch bracketed (attend_ms per launch, two_call_ms per step)."""
     sampler = ClockSampler(local_rank)
     sampler.start()
+    for _ in range(warmup):
+        c.step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    launches0 = gpu.launch_count
+    t_wall0 = time.perf_counter()
+    e0.record(stream)
+    for i in range(steps):
+        c.step()
+    e1.record(stream)
+    barrier()
+    t_wall1 = time.perf_counter()
+    launches = gpu.launch_count - launches0
+    for _ in range(min(warmup, 3)):
+        c.append(); c.attend()
+    ev_a = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    g0.record(stream)
+    for i in range(steps):
+        c.append()
+        ev_a[i].record(stream)
+        c.attend()
+        ev_b[i].record(stream)
+    g1.record(stream)
+    barrier()
+    gpu.synchronize()   # also surfaces a bounded-wait expiry of the prefill kernel
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    attend_ms = sum(x.elapsed_time(y) for x, y in zip(ev_a, ev_b)) / steps
+    return e0.elapsed_time(e1), attend_ms, launches, sampler.summary(t_wall0, t_wall1), g0.elapsed_time(g1) / steps
+
+
+def measure_cfg3(gpu, stream, rank, world, local_rank, dist, barrier, steps: int, warmup: int) -> dict:
+    """The prefill half of the metric as a short leg of the default line: attention-launch TFLOP/s and whole-step
+    TFLOP/s (append included) against the measured bf16 peak, with its own clock sample.  Frees its memory."""
+    import torch
     with torch.cuda.stream(stream):
-        for _ in range(args.warmup):
-            append(); attend()
-        ev_a = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        launches0 = gpu.launch_count
-        t_wall0 = time.perf_counter()
-        e0.record(stream)
-        for i in range(args.steps):
-            append()
-            ev_a[i].record(stream)
-            attend()
-            ev_b[i].record(stream)
-        e1.record(stream)
-        barrier()
-        t_wall1 = time.perf_counter()
-        gpu.synchronize()   # also surfaces a bounded-wait expiry of the prefill kernel
-        launches = gpu.launch_count - launches0
-        total_ms = e0.elapsed_time(e1)
-        attend_ms = sum(x.elapsed_time(y) for x, y in zip(ev_a, ev_b)) / args.steps
+        c = _Cfg3(gpu, rank)
+        gpu.synchronize()
+        total_ms, attend_ms, launches, clocks, two_call_ms = _time_cfg3(torch, c, gpu, stream, barrier, steps, warmup, local_rank)
+        c.close()
+    t = torch.tensor([total_ms, attend_ms, two_call_ms], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, attend_ms, two_call_ms = [float(x) for x in t.tolist()]
+    flops = prefill_flops()
+    burst, sustained, src = measured_tensor_peaks()
+    attn = flops / (attend_ms * 1e-3) / 1e12
+    step = flops / (total_ms / steps * 1e-3) / 1e12
+    return {"workload": prefill_config(world)["workload"], "metric": "prefill_attn_tflops", "unit": "TFLOP/s",
+            "steps": steps, "warmup": warmup, "n_gpus": world, "per_gpu": True,
+            "attention_launch": {"tflops": attn, "ms": attend_ms, "what": "prefill_kernel alone, on Q rotated beforehand"},
+            "whole_step": {"tflops": step, "ms": total_ms / steps,
+                           "includes": "shady_attn_prefill_append: K/V pass (norm, RoPE, cache rows) + attention kernel that norms/rotates Q itself"},
+            "whole_step_two_calls": {"tflops": flops / (two_call_ms * 1e-3) / 1e12, "ms": two_call_ms,
+                                     "includes": "shady_kv_append_rope (Q, K, V) + shady_attn_prefill"},
+            "roofline": {"bound": "tensor", "achieved": attn, "peak": burst, "unit": "TFLOP/s", "frac": attn / burst,
+                         "frac_whole_step": step / burst, "peak_source": f"{src} cuBLAS bf16 burst figure (sustained {sustained})",
+                         "algorithmic_flops_per_launch": flops},
+            "gpu_launches": int(launches), "clocks": clocks}
+
+
+def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
+    torch, dist, barrier = _dist_setup(world, local_rank)
+    from shady_thinker_b200.gpu import GpuContext
+
+    stream = torch.cuda.Stream()
+    gpu = GpuContext(local_rank, stream=stream.cuda_stream)
+    with torch.cuda.stream(stream):
+        c = _Cfg3(gpu, rank)
+        nq, nk = c.nq, c.nk
+        q_in, k_in, v_in, out = (c.bufs[n] for n in ("q_in", "k_in", "v_in", "out"))
+        gpu.synchronize()
+        total_ms, attend_ms, launches, clocks, _two = _time_cfg3(torch, c, gpu, stream, barrier, args.steps, args.warmup, local_rank)
         # ---- end to end: host activations in, output back ----
         hq = torch.empty(nq, dtype=torch.bfloat16).pin_memory().normal_()
         hk = torch.empty(nk, dtype=torch.bfloat16).pin_memory().normal_()
@@ -533,7 +627,7 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
             gpu._check(L.shady_buffer_write(gpu.handle, C.c_void_p(q_in.ptr), 0, C.c_void_p(hq.data_ptr()), nq * 2))
             gpu._check(L.shady_buffer_write(gpu.handle, C.c_void_p(k_in.ptr), 0, C.c_void_p(hk.data_ptr()), nk * 2))
             gpu._check(L.shady_buffer_write(gpu.handle, C.c_void_p(v_in.ptr), 0, C.c_void_p(hv.data_ptr()), nk * 2))
-            append(); attend()
+            c.step()
             gpu._check(L.shady_buffer_read(gpu.handle, C.c_void_p(out.ptr), 0, C.c_void_p(ho.data_ptr()), nq * 2))
 
         e2e_steps = max(3, min(args.steps, 20))
@@ -548,8 +642,6 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
         barrier()
         e2e_ms = f0.elapsed_time(f1)
         assert torch.isfinite(ho.float()).all(), "e2e output is not finite"
-    sampler.stop_flag = True
-    sampler.join(timeout=2)
 
     t = torch.tensor([total_ms, e2e_ms, attend_ms], dtype=torch.float64, device="cuda")
     if dist is not None:
@@ -570,13 +662,14 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
                          "traffic": None,
                          "peak_source": f"{src} cuBLAS bf16, {'sustained' if long_loop else 'burst'} figure "
                                         f"(burst {burst}, sustained {sustained})",
-                         "kernel": "prefill_kernel<bf16> per attend call", "algorithmic_flops_per_launch": flops,
+                         "kernel": "prefill_kernel<bf16> alone (Q rotated beforehand); `value` is the whole step through shady_attn_prefill_append",
+                         "algorithmic_flops_per_launch": flops,
                          "avg_launch_ms": attend_ms},
             "e2e": {"value": flops * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": (nq + 2 * nk) * 2, "d2h_bytes_per_step": nq * 2, "steps": e2e_steps,
                     "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": int(launches),
-            "clocks": sampler.summary(t_wall0, t_wall1),
+            "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle as O
@@ -609,21 +702,28 @@ def _dist_setup(world: int, local_rank: int):
     return torch, dist, barrier
 
 
-def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
-    """cfg4: one sequence of 131072 rows, nh16/nkv2/hd256, bf16 KV, rows split over the ranks; every rank decodes its
-    rows into records, NCCL all-gathers them (16.5 KB per rank) and every rank merges them (gqa_reduce math)."""
-    torch, dist, barrier = _dist_setup(world, local_rank)
+C4_L, C4_NH, C4_NKV, C4_HD = 131072, 16, 2, 256
+
+
+def measure_cfg4(gpu, stream, rank, world, local_rank, dist, barrier, steps: int, warmup: int) -> dict:
+    """cfg4: one sequence of 131072 rows, nh16/nkv2/hd256, bf16 KV.  One GPU: the whole sequence in one cooperative
+    launch (decode, grid barrier, record merge).  Several GPUs: rows cut contiguously over the ranks, every rank runs
+    the same launch on its rows and the launch's tail exchanges the merged slices over NVLink peer memory and merges
+    across ranks (`ShardCombiner.decode_and_combine`; SHADY_CFG4_COMBINE=p2p / nccl select the older forms for
+    comparison).  Before timing, the merged rows are checked against the same sequence decoded by rank 0 alone.
+    Returns the figures of the leg (rank 0's view after the max over ranks) and frees its memory."""
+    import torch
     from shady_thinker_b200 import ops
-    from shady_thinker_b200._lib import BF16, F32
-    from shady_thinker_b200.gpu import GpuContext
+    from shady_thinker_b200._lib import BF16
     from shady_thinker_b200.sharding import merge_args, shard_rows
-    L, nh, nkv, hd = 131072, 16, 2, 256
+    L, nh, nkv, hd = C4_L, C4_NH, C4_NKV, C4_HD
     lo, hi = shard_rows(L, world, rank)
     rows = hi - lo
-    stream = torch.cuda.Stream()
-    gpu = GpuContext(local_rank, stream=stream.cuda_stream)
     row_bytes = nkv * hd * 2
     n_sets = max(3, -(-320_000_000 // max(2 * rows * row_bytes, 1)))    # rotate through > 2x L2 of distinct rows
+    mode = os.environ.get("SHADY_CFG4_COMBINE", "fused")
+    use_nccl = mode == "nccl"
+    comb = None
     with torch.cuda.stream(stream):
         ks = [torch.empty((max(rows, 1), nkv, hd), dtype=torch.bfloat16, device="cuda") for _ in range(n_sets)]
         vs = [torch.empty_like(k) for k in ks]
@@ -640,67 +740,81 @@ def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
         ws = torch.zeros(ws_n, dtype=torch.uint8, device="cuda")
         views = [ops.KvCacheView(BF16, ks[i], vs[i], 0) for i in range(n_sets)]
         ev = []
-        # merge across ranks (SHADY_CFG4_COMBINE): "fused" = decode, then one kernel that merges the rank's records,
-        # exchanges over NVLink and merges across ranks; "p2p" = decode, rank-local merge, exchange+merge kernel;
-        # "nccl" = decode, rank-local merge, all-gather, merge kernel
-        mode = os.environ.get("SHADY_CFG4_COMBINE", "fused")
-        use_nccl = mode == "nccl"
-        comb = None
         if world > 1 and not use_nccl:
             from shady_thinker_b200.p2p import ShardCombiner
             comb = ShardCombiner(gpu, rank=rank, world=world, num_heads=nh, head_dim=hd)
 
         def step(i, timed=False):
             view = views[i % n_sets]
+            # the launch is bracketed on every 8th step only: two event records per step cost ~5 us of a 50 us step
+            bracket = timed and i % 8 == 0
+            a = b = None
+            if bracket:
+                a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+                a.record(stream)
             if world == 1:
-                # the launch is bracketed on every 8th step only: two event records per step cost ~5 us of a 55 us step
-                bracket = timed and i % 8 == 0
-                if bracket:
-                    a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
-                    a.record(stream)
                 ops.attn_decode(gpu, q=q, cache=view, seq_lens=lens, out=out, head_dim=hd, num_kv_heads=nkv,
                                 num_q_heads=nh, num_splits=0, seq_lens_host=[rows], q_dtype=BF16, workspace=ws,
                                 workspace_bytes=ws_n)
-                if bracket:
-                    b.record(stream)
-                    ev.append((a, b))
-                return
+            elif comb is not None and mode == "fused":
+                comb.decode_and_combine(q=q, cache=view, seq_lens=lens, seq_len_host=rows, records=rec, out=out,
+                                        num_kv_heads=nkv, q_dtype=BF16, workspace=ws, workspace_bytes=ws_n)
             else:
-                if comb is not None and mode == "fused":
-                    bracket = timed and i % 8 == 0
-                    if bracket:
-                        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
-                        a.record(stream)
-                    comb.decode_and_combine(q=q, cache=view, seq_lens=lens, seq_len_host=rows, records=rec, out=out,
-                                            num_kv_heads=nkv, q_dtype=BF16, workspace=ws, workspace_bytes=ws_n)
-                    if bracket:
-                        b.record(stream)
-                        ev.append((a, b))
-                    return
-                a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
-                a.record(stream)
                 ops.attn_decode_shard(gpu, q=q, cache=view, seq_lens=lens, records=rec, head_dim=hd, num_kv_heads=nkv,
                                       num_q_heads=nh, num_splits=0, seq_lens_host=[rows], q_dtype=BF16, workspace=ws,
                                       workspace_bytes=ws_n)
-                b.record(stream)
                 if comb is not None:
                     comb.combine(rec, out)
                 else:
                     dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1))
                     ops.attn_reduce(gpu, partials=gathered, out=out, **merge_args(1, nh, hd, world))
-            if timed:
+            if bracket:
+                b.record(stream)
                 ev.append((a, b))
 
-        for i in range(args.warmup):
+        # ---- self-check of the merged rows (set 0) against the whole sequence decoded by one rank ----
+        check = {"self_check": "ok", "against": "n/a (one GPU: the whole sequence is one rank's)"}
+        if world > 1:
+            step(0)
+            gpu.synchronize()
+            merged = out.clone()
+            err = torch.zeros(1, dtype=torch.float64, device="cuda")
+            if rank == 0:
+                fk = torch.empty((L, nkv, hd), dtype=torch.bfloat16, device="cuda")
+                fv = torch.empty_like(fk)
+                ops.fill_randn(gpu, fk, fk.numel(), BF16, SEED, 7001)
+                ops.fill_randn(gpu, fv, fv.numel(), BF16, SEED, 7002)
+                whole = torch.zeros((1, nh, hd), device="cuda")
+                ops.attn_decode(gpu, q=q, cache=ops.KvCacheView(BF16, fk, fv, 0),
+                                seq_lens=torch.tensor([L], dtype=torch.int32, device="cuda"), out=whole, head_dim=hd,
+                                num_kv_heads=nkv, num_q_heads=nh, num_splits=0, seq_lens_host=[L], q_dtype=BF16,
+                                workspace=ws, workspace_bytes=ws_n)
+                gpu.synchronize()
+                err[0] = float((merged - whole).abs().max() / whole.abs().max())
+                del fk, fv
+            dist.all_reduce(err, op=dist.ReduceOp.MAX)
+            rel = float(err.item())
+            check = {"self_check": "ok" if rel <= 2e-2 and bool(torch.isfinite(merged).all()) else "FAILED",
+                     "rel_err_vs_one_rank": rel, "tolerance": 2e-2,
+                     "against": "rank 0 decoding all 131072 rows in one launch (same seeded rows and Q)"}
+
+        for i in range(warmup):
             step(i)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         l0 = gpu.launch_count
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        t_wall0 = time.perf_counter()
         e0.record(stream)
-        for i in range(args.steps):
+        for i in range(steps):
             step(i, True)
         e1.record(stream)
         barrier()
+        t_wall1 = time.perf_counter()
+        sampler.stop_flag = True
+        sampler.join(timeout=2)
+        gpu.synchronize()       # surfaces a bounded wait (grid barrier, peer flag) that ran out
         launches = gpu.launch_count - l0
         total_ms = e0.elapsed_time(e1)
         dec_ms = sum(a.elapsed_time(b) for a, b in ev) / len(ev)
@@ -708,29 +822,51 @@ def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
     t = torch.tensor([total_ms, dec_ms], dtype=torch.float64, device="cuda")
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, dec_ms_max = [float(x) for x in t.tolist()]
-    if rank == 0:
-        peak, src = measured_peaks()
-        total_bytes = 2.0 * L * row_bytes
-        ach = 2.0 * rows * row_bytes / (dec_ms * 1e-3) / 1e9
-        print(json.dumps({
-            "metric": "decode_attn_kv_bandwidth", "value": total_bytes * args.steps / (total_ms * 1e-3) / 1e9, "unit": "GB/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "cfg4: long-context single-sequence decode, rows split over GPUs, LSE merge over NCCL",
-                       "context": L, "num_q_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "kv_dtype": "bf16",
-                       "rows_per_gpu": rows, "combine": "none" if world == 1 else ("NCCL all-gather of 16.5 KB records + merge kernel" if use_nccl else
-                                   ("one cooperative launch per step: decode, grid barrier, rank-local merge + peer stores over NVLink + flags + merge across ranks"
-                                    if mode == "fused" else "one kernel: peer stores of 16.5 KB records over NVLink + flags + merge")),
-                       "l2": f"{n_sets} cache sets rotate between steps"},
+    total_ms, dec_ms = [float(x) for x in t.tolist()]
+    if comb is not None:
+        comb.close()
+    del ks, vs, views
+    torch.cuda.empty_cache()
+    peak, src = measured_peaks()
+    total_bytes = 2.0 * L * row_bytes
+    step_ms = total_ms / steps
+    # one launch per step: when the back-to-back region divided by its launches is the smaller figure, that is the launch
+    launch_ms = min(dec_ms, step_ms) if launches == steps else dec_ms
+    ach = 2.0 * rows * row_bytes / (launch_ms * 1e-3) / 1e9
+    combine = ("none (one GPU)" if world == 1 else
+               "NCCL all-gather of 16.5 KB records + merge kernel" if use_nccl else
+               "one cooperative launch per step: decode, grid barrier, rank-local merge + peer stores over NVLink + flags + merge across ranks"
+               if mode == "fused" else "one kernel: peer stores of 16.5 KB records over NVLink + flags + merge")
+    return {"workload": "cfg4: long-context single-sequence decode, rows split over the GPUs, log-sum-exp merge across ranks",
+            "metric": "decode_attn_kv_bandwidth", "unit": "GB/s", "value": total_bytes / (step_ms * 1e-3) / 1e9,
+            "scaling": "strong", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": step_ms,
+            "context": L, "num_q_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "kv_dtype": "bf16",
+            "rows_per_gpu": rows, "combine": combine, "l2": f"{n_sets} cache sets rotate between steps",
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
                          "peak_source": f"{src} (copy bandwidth)",
                          "kernel": ("decode16_kernel<bf16,256> on this rank's rows with the merge and the NVLink exchange in its tail (the rank's whole step)"
-                                    if world > 1 and mode == "fused" and not use_nccl else "decode16_kernel<bf16,256> on this rank's rows"),
-                         "algorithmic_bytes_per_launch": 2.0 * rows * row_bytes, "avg_launch_ms": dec_ms},
-            "gpu_launches": int(launches)}), flush=True)
-    if comb is not None:
-        comb.close()
+                                    if world > 1 and mode == "fused" and not use_nccl else
+                                    "decode16_kernel<bf16,256>, blocks interleaved over all warps, record merge after the grid barrier"),
+                         "algorithmic_bytes_per_launch": 2.0 * rows * row_bytes, "avg_launch_ms": launch_ms,
+                         "avg_launch_ms_bracketed": dec_ms,
+                         "frac_of_whole_job_hbm_time": (total_bytes / world / (peak * 1e9)) / (step_ms * 1e-3)},
+            "gpu_launches": int(launches), "clocks": sampler.summary(t_wall0, t_wall1), **check}
+
+
+def run_cfg4(args, rank: int, world: int, local_rank: int) -> None:
+    torch, dist, barrier = _dist_setup(world, local_rank)
+    from shady_thinker_b200.gpu import GpuContext
+    stream = torch.cuda.Stream()
+    gpu = GpuContext(local_rank, stream=stream.cuda_stream)
+    m = measure_cfg4(gpu, stream, rank, world, local_rank, dist, barrier, args.steps, args.warmup)
+    if rank == 0:
+        cfg_keys = ("workload", "context", "num_q_heads", "num_kv_heads", "head_dim", "kv_dtype", "rows_per_gpu", "combine", "l2")
+        print(json.dumps({
+            "metric": m["metric"], "value": m["value"], "unit": m["unit"], "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": m["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": {k: m[k] for k in cfg_keys},
+            "roofline": m["roofline"], "gpu_launches": m["gpu_launches"], "clocks": m["clocks"],
+            "self_check": {k: m[k] for k in m if k in ("self_check", "rel_err_vs_one_rank", "tolerance", "against")}}), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -744,6 +880,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="cfg2 only: skip the short cfg3 (prefill) and cfg4 (long context) legs added to the line as `extra`")
     ap.add_argument("--shape", default="plain", choices=["plain", "reference"],
                     help="cfg2 only: plain = full rotary, no norm, no gate; reference = the reference's defaults "
                          "(rotary_dim = head_dim/4, QK RMSNorm, sigmoid gate)")

@@ -63,6 +63,15 @@ const char *shady_last_error(const shady_ctx *ctx);
 void *shady_ctx_stream(const shady_ctx *ctx);
 /* Number of kernels this context has launched so far (bookkeeping for benchmarks). */
 uint64_t shady_ctx_launch_count(const shady_ctx *ctx);
+/* Iteration limits of the bounded device-side waits of this context's later launches (0 keeps a limit as it is):
+ * the grid barrier ahead of the in-launch record merge of shady_attn_decode* (default 2^21 polls), a peer's NVLink
+ * flag in shady_attn_combine_p2p / shady_attn_decode_shard_p2p (2^22), an mbarrier of shady_attn_prefill (2^20).
+ * A wait that runs out makes its kernel skip the rest of its work and return; the next shady_synchronize then
+ * returns SHADY_ERR_TIMEOUT once (the message names the wait), outputs of launches since the previous successful
+ * shady_synchronize are undefined, and until the status has been collected every launch on the context is refused
+ * with SHADY_ERR_TIMEOUT.  Nothing else is left behind: the workspace counters are clean again when the kernel ends.
+ * No reference counterpart (wgpu has no device-side waits; a lost device panics, gpu.rs:43). */
+int shady_ctx_set_wait_limits(shady_ctx *ctx, uint32_t grid_polls, uint32_t peer_polls, uint32_t mbarrier_polls);
 
 /* create_storage_buffer (gpu.rs:95); size is rounded up to 4 bytes as in gpu.rs:86. */
 int shady_buffer_create(shady_ctx *ctx, size_t bytes, void **d_out);
@@ -182,8 +191,8 @@ typedef struct {
  * buffer (model.rs:219-224, 236). */
 int shady_decode_workspace_size(const shady_decode_params *p, size_t *bytes);
 /* The workspace starts with arrival counters that must be zero before its first use: call this
- * once after allocating it (stream-ordered memset).  Every decode call leaves them zero again, so
- * no further clearing is needed unless a call was interrupted by an error. */
+ * once after allocating it (stream-ordered memset).  Every decode call leaves them zero again (also one
+ * whose bounded wait ran out), so no further clearing is needed. */
 int shady_decode_workspace_init(shady_ctx *ctx, const shady_decode_params *p, void *d_workspace,
                                 size_t workspace_bytes);
 
@@ -195,8 +204,10 @@ int shady_decode_workspace_init(shady_ctx *ctx, const shady_decode_params *p, vo
  * seq_lens_host: the same lengths in host memory (they must equal the device values): needed to
  * balance the split plan when num_splits == 0, may be NULL otherwise; for batches of up to 32
  * sequences the kernels also take the lengths from it by value instead of loading them.  A sequence of length 0 yields zeros and
- * lse = -inf.  Splits are merged inside the same launch by the last CTA to arrive
- * (gqa_reduce.wgsl math); calls that share one workspace must not overlap on the GPU. */
+ * lse = -inf.  Splits are merged inside the same launch (gqa_reduce.wgsl math): by the last CTA to arrive for a
+ * sequence, or — when a 16-bit sequence is cut into more than 12 spans — by the whole grid after a bounded grid
+ * barrier (a cooperative launch; see shady_ctx_set_wait_limits).  Calls that share one workspace must not overlap
+ * on the GPU. */
 int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
                       const shady_kv_cache *cache, const uint32_t *d_seq_lens,
                       const uint32_t *seq_lens_host, void *d_out, float *d_lse, const float *d_gate,
@@ -245,12 +256,14 @@ int shady_combine_p2p_buffer_size(uint32_t world, uint32_t num_heads, uint32_t h
 int shady_attn_combine_p2p(shady_ctx *ctx, uint32_t world, uint32_t rank, uint32_t num_heads, uint32_t head_dim,
                            uint32_t epoch, void *const *d_peer_table, const float *d_records, void *d_out,
                            uint32_t out_dtype, const float *d_gate);
-/* The whole sharded step in two launches: the decode kernel over this rank's rows, then ONE kernel that merges
- * the rank's split records, stores the result into every peer's exchange buffer, raises per-(head, 64-dim chunk)
- * flags, waits (bounded) for the peers' flags and merges across ranks into d_out[nh][hd] — the work of
- * shady_attn_decode_shard + shady_attn_combine_p2p with one launch and one pass over the records less.
- * Arguments as in those two calls (one sequence, num_splits == 0; d_records [nh][hd+2] is scratch).  An exchange
- * buffer serves either this call or shady_attn_combine_p2p, not both in turn. */
+/* The whole sharded step in ONE cooperative launch: the decode kernel streams this rank's rows, its CTAs meet at a
+ * bounded grid barrier, and the grid then merges the rank's split records, stores each (head, 64-dim chunk) slice
+ * into every peer's exchange buffer with plain NVLink stores, raises a flag per slice, waits (bounded) for the
+ * peers' flags and merges across ranks into d_out[nh][hd] — the work of shady_attn_decode_shard +
+ * shady_attn_combine_p2p without their two extra launches.  A shard short enough for a single span keeps two
+ * launches (decode, then one merge+exchange kernel).  Arguments as in those two calls (one sequence,
+ * num_splits == 0; d_records [nh][hd+2] is scratch).  An exchange buffer serves either this call or
+ * shady_attn_combine_p2p, not both in turn. */
 int shady_attn_decode_shard_p2p(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
                                 const shady_kv_cache *cache, const uint32_t *d_seq_lens,
                                 const uint32_t *seq_lens_host, uint32_t world, uint32_t rank, uint32_t epoch,
@@ -267,7 +280,8 @@ int shady_attn_decode_shard_p2p(shady_ctx *ctx, const shady_decode_params *p, co
  *  - The first call on a device looks up the array's device address; make that call before any
  *    stream capture begins on that device.
  *  - Every call on a device shares the one array and clears its counters on the stream first, so two
- *    calls that overlap on the GPU (different streams or contexts) race; keep them stream-ordered. */
+ *    calls that overlap on the GPU (different streams or contexts) race; keep them stream-ordered.
+ *  - Checks, span plan and kernels are those of shady_attn_decode; only the scratch differs. */
 int shady_attn_decode_static(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
                              const shady_kv_cache *cache, const uint32_t *d_seq_lens,
                              const uint32_t *seq_lens_host, void *d_out, float *d_lse, const float *d_gate);
@@ -307,6 +321,23 @@ typedef struct {
  * seq_stride (one allocation) because the tiles are fetched through TMA tensor maps. */
 int shady_attn_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_q,
                        const shady_kv_cache *cache, void *d_out);
+
+/* The whole prefill step from the projections, i.e. what T iterations of model.rs:723-725 (fused_split_qknorm_kvstore,
+ * gqa_attention, sigmoid_mul_gate) compute for T new tokens of each of num_seqs empty caches (inference.rs:93-95):
+ * K is normed and rotated and K/V are stored in cache rows [0, T) (positions 0..T-1) by one small pass; the
+ * attention kernel then takes Q straight from d_q_proj_full, applies RMSNorm(1+w) and RoPE to each Q tile in shared
+ * memory, attends causally and multiplies by sigmoid(gate) in its epilogue — the rotated Q and the gate never make a
+ * round trip through device memory.  `ap` as in shady_kv_append_rope with tokens_per_seq == p->seq_len,
+ * in_dtype == p->dtype (bf16 or f16), interleaved RoPE with one position per token; q_out, q_gate and k_proj are not
+ * written.  d_q_proj_full [num_seqs][T][nh][(1+has_gate)*hd]; d_k_proj / d_v_proj [num_seqs][T][nkv][hd];
+ * d_out [num_seqs][T][nh][hd].  Cache addressing as in shady_attn_prefill.  d_workspace: at least
+ * shady_prefill_workspace_size bytes, 16-byte aligned (a cos/sin table of the T positions; no initialisation
+ * needed).  Replaces the prompt loop of src/inference.rs:93-95 for 16-bit caches. */
+int shady_prefill_workspace_size(const shady_prefill_params *p, size_t *bytes);
+int shady_attn_prefill_append(shady_ctx *ctx, const shady_append_params *ap, const shady_prefill_params *p,
+                              const void *d_q_proj_full, const void *d_k_proj, const void *d_v_proj,
+                              const uint16_t *d_qk_norm_bf16, const shady_kv_cache *cache, void *d_out,
+                              void *d_workspace, size_t workspace_bytes);
 
 /* ===================================================================================== */
 /* Output gate — replaces Model::sigmoid_mul_gate (model.rs:576-593), sigmoid_mul.wgsl    */

@@ -17,10 +17,12 @@ F32, F16, BF16 = 0, 1, 2
 # every symbol include/shady_attn.h declares
 EXPORTS = [
     "shady_ctx_create", "shady_ctx_destroy", "shady_last_error", "shady_ctx_stream", "shady_ctx_launch_count",
+    "shady_ctx_set_wait_limits",
     "shady_buffer_create", "shady_buffer_free", "shady_buffer_write", "shady_buffer_read", "shady_buffer_copy",
     "shady_host_device_ptr",
     "shady_flush", "shady_synchronize", "shady_kv_append_rope", "shady_decode_workspace_size", "shady_decode_workspace_init",
     "shady_attn_decode", "shady_attn_decode_static", "shady_attn_decode_shard", "shady_attn_decode_append", "shady_attn_decode_partials", "shady_attn_reduce", "shady_attn_prefill",
+    "shady_prefill_workspace_size", "shady_attn_prefill_append",
     "shady_sigmoid_mul", "shady_fill_randn", "shady_ipc_export", "shady_ipc_open", "shady_ipc_close",
     "shady_combine_p2p_buffer_size", "shady_attn_combine_p2p", "shady_attn_decode_shard_p2p",
 ]
@@ -80,6 +82,7 @@ def load() -> C.CDLL:
     L.shady_ctx_stream.restype = vp
     L.shady_ctx_launch_count.argtypes = [vp]
     L.shady_ctx_launch_count.restype = C.c_uint64
+    L.shady_ctx_set_wait_limits.argtypes = [vp, C.c_uint32, C.c_uint32, C.c_uint32]
     L.shady_buffer_create.argtypes = [vp, sz, C.POINTER(vp)]
     L.shady_buffer_free.argtypes = [vp, vp]
     L.shady_buffer_write.argtypes = [vp, vp, sz, vp, sz]
@@ -104,6 +107,9 @@ def load() -> C.CDLL:
     L.shady_attn_reduce.argtypes = [vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64, f32p, vp,
                                     C.c_uint32, f32p]
     L.shady_attn_prefill.argtypes = [vp, C.POINTER(PrefillParams), vp, C.POINTER(KvCache), vp]
+    L.shady_prefill_workspace_size.argtypes = [C.POINTER(PrefillParams), C.POINTER(sz)]
+    L.shady_attn_prefill_append.argtypes = [vp, C.POINTER(AppendParams), C.POINTER(PrefillParams), vp, vp, vp, vp,
+                                            C.POINTER(KvCache), vp, vp, sz]
     L.shady_ipc_export.argtypes = [vp, vp, C.c_char_p]
     L.shady_ipc_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
     L.shady_ipc_close.argtypes = [vp, vp]

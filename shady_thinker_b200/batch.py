@@ -73,6 +73,17 @@ class BatchedDecoder:
         self._fused_calls: dict = {}
         self.set_lengths(np.zeros(num_seqs, np.uint32))
 
+    def close(self) -> None:
+        """Free every device buffer of this decoder (the context frees what is left when it is closed)."""
+        bufs = self.k_cache + self.v_cache + self._ptr_bufs + [self.q_in, self.k_in, self.v_in, self.q_rot, self.q_gate,
+                                                               self.out, self.pos, self.lens, self.ws]
+        for b in bufs:
+            if b is not None:
+                self.gpu.destroy_buffer(b)
+        self.k_cache, self.v_cache, self._ptr_bufs, self.views = [], [], [], []
+        self.q_in = self.k_in = self.v_in = self.q_rot = self.q_gate = self.out = self.pos = self.lens = self.ws = None
+        self._fused_calls.clear()
+
     def set_lengths(self, lens_before) -> None:
         """Rows already in each sequence's cache; the next step appends at these positions."""
         self.lens_before = np.ascontiguousarray(lens_before, dtype=np.uint32)

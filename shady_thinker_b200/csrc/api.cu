@@ -1,6 +1,7 @@
 // extern "C" surface of libshady_attn.so: context, buffers and op entry points declared in
 // include/shady_attn.h.  No torch types, no exceptions across the boundary.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -13,6 +14,28 @@ int fail(shady_ctx *ctx, int code, const std::string &msg) {
     if (ctx) ctx->err = msg;
     else g_create_error = msg;
     return code;
+}
+
+int pending_timeout(shady_ctx *ctx, const char *who) {
+    if (ctx->status_host && *reinterpret_cast<volatile int *>(ctx->status_host))
+        return fail(ctx, SHADY_ERR_TIMEOUT, std::string(who) + ": an earlier launch on this context gave up a bounded wait; call "
+                                            "shady_synchronize to collect the status before launching again");
+    return SHADY_OK;
+}
+
+// Text of a wait code: 1..12 = mbarriers of the prefill kernel, 90 = the decode grid barrier, 100 + r = the NVLink
+// flag of rank r.
+std::string timeout_message(int code) {
+    if (code >= 100)
+        return "combine_p2p: the flag of rank " + std::to_string(code - 100) + " did not arrive in time";
+    if (code == 90)
+        return "decode: the grid barrier before the record merge ran out; the workspace counters are cleared again before the next launch";
+    return "attn_prefill: a device-side wait expired (code " + std::to_string(code) + ")";
+}
+
+static uint32_t env_u32(const char *name, uint32_t dflt) {
+    const char *v = getenv(name);
+    return v && *v ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
 }
 
 int fill_kv_addr(shady_ctx *ctx, const shady_kv_cache *cache, uint32_t nkv, uint32_t hd, const char *who, KvAddr *out) {
@@ -64,8 +87,9 @@ int launch_sigmoid_mul(shady_ctx *, float *, const float *, uint32_t);
 int launch_append(shady_ctx *, const shady_append_params *, const void *, void *, const void *, void *, float *,
                   const shady_kv_cache *, const uint16_t *, const uint32_t *, const uint32_t *, const uint32_t *);
 int launch_prefill(shady_ctx *, const shady_prefill_params *, const void *, const shady_kv_cache *, void *);
-int prefill_status(shady_ctx *, int *);
-int p2p_status(shady_ctx *, int *);
+size_t prefill_workspace_bytes(const shady_prefill_params *p);
+int launch_prefill_append(shady_ctx *, const shady_append_params *, const shady_prefill_params *, const void *, const void *,
+                          const void *, const uint16_t *, const shady_kv_cache *, void *, void *, size_t);
 unsigned long long p2p_buffer_bytes(uint32_t world, uint32_t nh, uint32_t hd);
 int launch_combine_p2p(shady_ctx *, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, void *const *, const float *, void *,
                        uint32_t, const float *);
@@ -122,6 +146,27 @@ int shady_ctx_create(int device, void *stream, shady_ctx **out) {
         }
         c->owns_stream = true;
     }
+    // status words of the bounded waits: 4 bytes of device memory and one page-locked host word the kernels can write
+    auto drop = [&](const char *what, cudaError_t err) {
+        if (c->status_dev) cudaFree(c->status_dev);
+        if (c->status_host) cudaFreeHost(c->status_host);
+        if (c->owns_stream) cudaStreamDestroy(c->stream);
+        delete c;
+        return fail(nullptr, SHADY_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(err));
+    };
+    if ((e = cudaMalloc(reinterpret_cast<void **>(&c->status_dev), 256)) != cudaSuccess) return drop("cudaMalloc(status word)", e);
+    if ((e = cudaMemset(c->status_dev, 0, 256)) != cudaSuccess) return drop("cudaMemset(status word)", e);
+    if ((e = cudaHostAlloc(reinterpret_cast<void **>(&c->status_host), 64, cudaHostAllocMapped)) != cudaSuccess)
+        return drop("cudaHostAlloc(status word)", e);
+    *c->status_host = 0;
+    if ((e = cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->status_host_dev), c->status_host, 0)) != cudaSuccess)
+        return drop("cudaHostGetDevicePointer(status word)", e);
+    c->knobs.variant = env_u32("SHADY_DECODE_VARIANT", 0);
+    c->knobs.ctas_per_sm = env_u32("SHADY_DECODE_CTAS_PER_SM", 0);
+    c->knobs.kpc = env_u32("SHADY_DECODE_KPC", 0);
+    c->knobs.min_span = env_u32("SHADY_DECODE_MIN_SPAN", 0);
+    c->knobs.grid_merge = env_u32("SHADY_DECODE_GRID_MERGE", 1);
+    c->knobs.interleave = env_u32("SHADY_DECODE_INTERLEAVE", 1);
     *out = c;
     return SHADY_OK;
 }
@@ -132,8 +177,20 @@ int shady_ctx_destroy(shady_ctx *ctx) {
         cudaSetDevice(ctx->device);
         cudaStreamSynchronize(ctx->stream);
         cudaStreamDestroy(ctx->stream);
+    } else {
+        cudaSetDevice(ctx->device);
     }
+    if (ctx->status_dev) cudaFree(ctx->status_dev);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
     delete ctx;
+    return SHADY_OK;
+}
+
+int shady_ctx_set_wait_limits(shady_ctx *ctx, uint32_t grid_polls, uint32_t peer_polls, uint32_t mbarrier_polls) {
+    if (!ctx) return SHADY_ERR_BAD_ARG;
+    if (grid_polls) ctx->wait_grid = grid_polls;
+    if (peer_polls) ctx->wait_peer = peer_polls;
+    if (mbarrier_polls) ctx->wait_mbar = mbarrier_polls;
     return SHADY_OK;
 }
 
@@ -198,10 +255,16 @@ int shady_flush(shady_ctx *ctx) {
 int shady_synchronize(shady_ctx *ctx) {
     CTX_ENTER(ctx);
     SHADY_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
-    int code = 0;   // SHADY_ERR_TIMEOUT if a bounded device-side wait gave up
-    const int rc = prefill_status(ctx, &code);
-    if (rc != SHADY_OK) return rc;
-    return p2p_status(ctx, &code);
+    // a kernel whose bounded wait ran out wrote its code into the page-locked status word before it ended
+    const int code = *reinterpret_cast<volatile int *>(ctx->status_host);
+    if (code) {
+        *ctx->status_host = 0;
+        SHADY_CUDA_OK(ctx, cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), ctx->stream));
+        SHADY_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+        ctx->rezero_workspace = true;
+        return fail(ctx, SHADY_ERR_TIMEOUT, timeout_message(code));
+    }
+    return SHADY_OK;
 }
 
 int shady_kv_append_rope(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,
@@ -289,6 +352,21 @@ int shady_attn_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void
                        void *d_out) {
     CTX_ENTER(ctx);
     return launch_prefill(ctx, p, d_q, cache, d_out);
+}
+
+int shady_prefill_workspace_size(const shady_prefill_params *p, size_t *bytes) {
+    if (!p || !bytes) return SHADY_ERR_BAD_ARG;
+    *bytes = prefill_workspace_bytes(p);
+    return SHADY_OK;
+}
+
+int shady_attn_prefill_append(shady_ctx *ctx, const shady_append_params *ap, const shady_prefill_params *p,
+                              const void *d_q_proj_full, const void *d_k_proj, const void *d_v_proj,
+                              const uint16_t *d_qk_norm_bf16, const shady_kv_cache *cache, void *d_out, void *d_workspace,
+                              size_t workspace_bytes) {
+    CTX_ENTER(ctx);
+    return launch_prefill_append(ctx, ap, p, d_q_proj_full, d_k_proj, d_v_proj, d_qk_norm_bf16, cache, d_out, d_workspace,
+                                 workspace_bytes);
 }
 
 int shady_ipc_export(shady_ctx *ctx, void *d_buf, unsigned char handle[64]) {

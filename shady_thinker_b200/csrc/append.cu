@@ -30,6 +30,8 @@ struct AppendArgs {
     uint32_t num_seqs, T;
     uint32_t in_dtype, q_dtype, kv_dtype, has_gate, write_k_back;
     uint32_t head_slices;     // vectorised path: warps that share one token's heads (small batches need the parallelism)
+    uint32_t skip_q;          // vectorised path: K/V only (Q is normed and rotated by the prefill attention kernel itself)
+    float2 *cs_table;         // vectorised path, optional: (cos, sin) of [token j][pair i < hd/2] of sequence 0, (1, 0) past rd/2
     float inv_freq[128];      // [rd/2]
 };
 
@@ -81,7 +83,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(const AppendA
     }
     __syncwarp();
     // ---- (m)RoPE on the first rd dims (wgsl:56-104) ----
-    const uint32_t p_t = a.pos_start[s] + j;
+    const uint32_t p_t = (a.pos_start ? a.pos_start[s] : 0u) + j;
     const uint32_t p_h = a.pos_h ? a.pos_h[s] + j : p_t;
     const uint32_t p_w = a.pos_w ? a.pos_w[s] + j : p_t;
     const uint32_t half = a.rd / 2;
@@ -164,7 +166,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
     const uint32_t s = (uint32_t)(tok / a.T), j = (uint32_t)(tok % a.T);
     const uint32_t sub = lane / LPH, dl = lane % LPH, d0 = dl * 8;
     // ---- cos/sin of this lane's four pairs (wgsl:56-68) ----
-    const uint32_t p_t = a.pos_start[s] + j;
+    const uint32_t p_t = (a.pos_start ? a.pos_start[s] : 0u) + j;
     const uint32_t p_h = a.pos_h ? a.pos_h[s] + j : p_t;
     const uint32_t p_w = a.pos_w ? a.pos_w[s] + j : p_t;
     float cs[4], sn[4];
@@ -178,6 +180,11 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
             else if ((i % 3u) == 2u && i < a.s2) pos = p_w;
             sincosf((float)pos * a.inv_freq[i], &sn[k], &cs[k]);
         }
+    }
+    if (a.cs_table && s == 0 && slice == 0 && sub == 0) {   // one 16-lane group per token writes the token's table row
+        float4 *row = reinterpret_cast<float4 *>(a.cs_table + (size_t)j * (HD / 2) + dl * 4);
+        row[0] = make_float4(cs[0], sn[0], cs[1], sn[1]);
+        row[1] = make_float4(cs[2], sn[2], cs[3], sn[3]);
     }
     float wq[8], wk[8];
     if (a.norm_w) {
@@ -209,7 +216,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
     const uint32_t qrow = a.has_gate ? 2 * HD : HD;
     const TIn *q_in = reinterpret_cast<const TIn *>(a.q_in) + tok * a.nh * (size_t)qrow;
     TQ *q_out = reinterpret_cast<TQ *>(a.q_out) + tok * a.nh * (size_t)HD;
-    for (uint32_t h0 = slice * HPI; h0 < a.nh; h0 += HPI * a.head_slices) {   // every lane takes every trip: the norm shuffles are warp-wide
+    for (uint32_t h0 = slice * HPI; h0 < a.nh && !a.skip_q; h0 += HPI * a.head_slices) {   // every lane takes every trip: the norm shuffles are warp-wide
         const uint32_t h = h0 + sub;
         const bool valid = h < a.nh;
         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -250,7 +257,7 @@ static void launch_append_fast(shady_ctx *ctx, AppendArgs &a) {
     const unsigned long long toks = (unsigned long long)a.num_seqs * a.T;
     // enough warps to fill the GPU: split a token's heads over several warps when there are few tokens
     const uint32_t hpi = 32 / (a.hd / 8);
-    const uint32_t max_slices = (a.nh + hpi - 1) / hpi;
+    const uint32_t max_slices = ((a.skip_q ? a.nkv : a.nh) + hpi - 1) / hpi;
     unsigned long long want = ((unsigned long long)ctx->num_sms * 8 + toks - 1) / toks;
     a.head_slices = (uint32_t)(want < 1 ? 1 : (want > max_slices ? max_slices : want));
     const unsigned blocks = (unsigned)((toks * a.head_slices + kAppendWarps - 1) / kAppendWarps);
@@ -274,6 +281,32 @@ static bool try_append_fast(shady_ctx *ctx, AppendArgs &a, const void *q_in, con
     else if (i == SHADY_BF16 && q == SHADY_BF16 && k == SHADY_BF16) launch_append_fast<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(ctx, a);
     else return false;
     return true;
+}
+
+int launch_append_kv_table(shady_ctx *ctx, const shady_append_params *p, const void *d_k_proj, const void *d_v_proj,
+                           const shady_kv_cache *cache, const uint16_t *d_qk_norm_bf16, float2 *d_cs_table) {
+    SHADY_REQUIRE(ctx, p->head_dim == 128 && p->in_dtype == cache->dtype && p->in_dtype != SHADY_F32, SHADY_ERR_UNSUPPORTED,
+                  "attn_prefill_append: head_dim 128 and 16-bit projections in the cache dtype");
+    AppendArgs a{};
+    a.k_io = const_cast<void *>(d_k_proj); a.v_in = d_v_proj;
+    if (const int st = fill_kv_addr(ctx, cache, p->num_kv_heads, p->head_dim, "attn_prefill_append", &a.kv)) return st;
+    a.norm_w = d_qk_norm_bf16;
+    a.nh = p->num_heads; a.nkv = p->num_kv_heads; a.hd = p->head_dim; a.eps = p->eps;
+    a.rd = p->rotary_dim; a.s1 = p->s1_limit; a.s2 = p->s2_limit; a.interleaved = 1;
+    a.num_seqs = p->num_seqs; a.T = p->tokens_per_seq;
+    a.in_dtype = a.q_dtype = a.kv_dtype = p->in_dtype;
+    a.skip_q = 1; a.cs_table = d_cs_table;
+    for (uint32_t i = 0; i < p->rotary_dim / 2; ++i)   // wgsl:57, same libm call as everywhere else
+        a.inv_freq[i] = 1.0f / powf(p->rope_theta, 2.0f * (float)i / (float)p->rotary_dim);
+    SHADY_REQUIRE(ctx, (unsigned long long)a.num_seqs * a.T <= 0x3fffffffull, SHADY_ERR_UNSUPPORTED, "attn_prefill_append: too many tokens for one launch");
+    SHADY_REQUIRE(ctx, !((((uintptr_t)d_k_proj | (uintptr_t)d_v_proj | (uintptr_t)a.kv.k_base | (uintptr_t)a.kv.v_base) & 15) ||
+                         (a.kv.seq_stride_bytes & 15)),
+                  SHADY_ERR_BAD_ARG, "attn_prefill_append: buffers must be 16-byte aligned");
+    if (p->in_dtype == SHADY_F16) launch_append_fast<__half, __half, __half>(ctx, a);
+    else launch_append_fast<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(ctx, a);
+    ctx->launches++;
+    SHADY_CUDA_OK(ctx, cudaGetLastError());
+    return SHADY_OK;
 }
 
 int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,

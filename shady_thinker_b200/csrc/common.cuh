@@ -9,6 +9,17 @@
 
 #include "../../include/shady_attn.h"
 
+// Tuning overrides of the decode launcher, read from the environment once, when the context is created
+// (0 = the measured default).  They exist for experiments; nothing on the launch path calls getenv.
+struct DecodeKnobs {
+    uint32_t variant = 0;       // SHADY_DECODE_VARIANT: {warps, tile slots} configuration
+    uint32_t ctas_per_sm = 0;   // SHADY_DECODE_CTAS_PER_SM: spans per SM
+    uint32_t kpc = 0;           // SHADY_DECODE_KPC: kv heads per CTA
+    uint32_t min_span = 0;      // SHADY_DECODE_MIN_SPAN: smallest span in 16-row blocks
+    uint32_t grid_merge = 1;    // SHADY_DECODE_GRID_MERGE=0: merge many-span sequences in a second launch
+    uint32_t interleave = 1;    // SHADY_DECODE_INTERLEAVE=0: fixed spans for a single long sequence
+};
+
 struct shady_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -16,12 +27,41 @@ struct shady_ctx {
     int num_sms = 148;
     uint64_t launches = 0;
     std::string err;
+    DecodeKnobs knobs;
+    // Bounded device-side waits.  A kernel whose wait runs out latches a code into status_dev (which later waits
+    // of the same context poll, so that they give up early) and into status_host, one word of page-locked host
+    // memory: shady_synchronize reads it after its single stream sync, and every launcher reads it before it
+    // launches, without any device round trip.
+    int *status_dev = nullptr;       // device memory, zero while all is well
+    int *status_host = nullptr;      // the host word ...
+    int *status_host_dev = nullptr;  // ... under the address kernels write it through
+    uint32_t wait_grid = 1u << 21;   // polls of the decode grid barrier
+    uint32_t wait_peer = 1u << 22;   // polls of a peer's NVLink flag
+    uint32_t wait_mbar = 1u << 20;   // polls of an mbarrier in the prefill kernel
+    bool rezero_workspace = false;   // a wait ran out: the next decode launch clears its workspace's counters first
 };
+
+// What a kernel needs to report (and notice) an expired wait.
+struct StatusRef {
+    int *dev;    // polled by bounded waits: non-zero = somebody already gave up
+    int *host;   // page-locked host word (device-side address)
+};
+__device__ __forceinline__ void report_timeout(const StatusRef &st, int code) {
+    if (atomicCAS(st.dev, 0, code) == 0) {
+        *reinterpret_cast<volatile int *>(st.host) = code;
+        __threadfence_system();
+    }
+}
+__device__ __forceinline__ bool gave_up(const StatusRef &st) { return *reinterpret_cast<volatile int *>(st.dev) != 0; }
 
 namespace shady {
 
 // ---- status plumbing ------------------------------------------------------------------
 int fail(shady_ctx *ctx, int code, const std::string &msg);
+// SHADY_ERR_TIMEOUT if an earlier launch of this context gave up a bounded wait and the status has not been
+// collected by shady_synchronize yet (launchers call it first: results after such a launch are undefined).
+int pending_timeout(shady_ctx *ctx, const char *who);
+inline StatusRef status_ref(const shady_ctx *ctx) { return StatusRef{ctx->status_dev, ctx->status_host_dev}; }
 #define SHADY_CUDA_OK(ctx, expr)                                                             \
     do {                                                                                     \
         cudaError_t e__ = (expr);                                                            \

@@ -48,6 +48,7 @@ struct DecodeArgs {
     uint32_t force_partials;  // 1: always write the partial record (shady_attn_decode_partials)
     uint32_t defer_merge;     // 1: CTAs only write records; balanced_merge_kernel merges them (sequences cut into many spans)
     uint32_t grid_merge;      // 1 (with defer_merge, cooperative launch): the decode grid meets at a barrier and merges the records itself
+    uint32_t interleave;      // 1 (with grid_merge, one sequence): the warps of all CTAs take the sequence's 16-row blocks in turn
     uint32_t *grid_sync;      // workspace: {arrivals, departures} of that barrier; zero between calls
     uint32_t out_row_stride;  // elements between consecutive head rows of `out` (hd, or hd+2 when out is a record buffer)
     uint32_t lse_stride;      // elements between consecutive entries of `lse` (1, or hd+2 inside a record buffer)
@@ -64,7 +65,8 @@ struct DecodeArgs {
     // row-sharded sequence (one process per GPU): the launch that merges this rank's records also exchanges the
     // result with the peers over NVLink and merges across ranks (shard_merge_p2p_kernel); px_world == 0: off
     char *const *px_peer_bases;   // device array [world] of every rank's exchange buffer as mapped into this process
-    int *px_error;                // status word of the bounded flag wait
+    StatusRef status;             // where a bounded wait that ran out is reported (grid barrier, peer flags)
+    uint32_t wait_grid, wait_peer;   // poll limits of the two waits
     void *px_out;                 // final rows [nh][hd]
     const float *px_gate;         // optional [nh][hd] f32
     uint32_t px_world, px_rank, px_epoch, px_out_dtype;
@@ -549,8 +551,6 @@ template <int HD, int NW, int STAGES, int KPC> struct Decode16Smem {
 // and the warps are rescaled to a common maximum and summed through shared memory.  The last CTA
 // to leave zeroes the barrier for the next launch.
 // ---------------------------------------------------------------------------------------
-constexpr uint32_t kGridSpinLimit = 1u << 21;
-
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -567,14 +567,31 @@ struct TailArgs {
     void *out;
     float *lse;
     uint32_t *grid_sync;
-    int *status;
+    StatusRef status;
+    uint32_t wait_grid, wait_peer;
     uint32_t nh, hd, num_seqs, out_row_stride, lse_stride, out_dtype, spans, line_blocks, span_math32, gated;
     uint32_t len0;   // length of sequence 0 (the others are read through the reference)
 };
 __device__ __forceinline__ TailArgs tail_args(const DecodeArgs &a) {
-    return TailArgs{a.partials, a.out, a.lse, a.grid_sync, a.px_error, a.nh, a.hd, a.num_seqs, a.out_row_stride,
+    return TailArgs{a.partials, a.out, a.lse, a.grid_sync, a.status, a.wait_grid, a.wait_peer, a.nh, a.hd, a.num_seqs, a.out_row_stride,
                     a.lse_stride, a.out_dtype, a.spans, a.line_blocks, a.span_math32, has_gate(a) ? 1u : 0u,
                     seq_len_at(a, 0)};
+}
+
+// The two halves of the grid barrier, both called by thread 0 of every CTA after its arrival (atomicAdd on
+// grid_sync[0]).  The wait is bounded (ta.wait_grid polls) and is skipped when an earlier wait of this context has
+// already run out; a CTA that does not get through skips the merge but still leaves, so the barrier words are
+// clean again when the kernel ends, whatever happened.
+__device__ __forceinline__ uint32_t grid_barrier_wait(const TailArgs &ta) {
+    uint32_t ok = 0;
+    if (!gave_up(ta.status))
+        for (uint32_t i = 0; i < ta.wait_grid; ++i)
+            if (ld_acquire_gpu(ta.grid_sync) >= gridDim.x) { ok = 1; break; }
+    if (!ok) report_timeout(ta.status, 90);
+    return ok;
+}
+__device__ __forceinline__ void grid_barrier_leave(const TailArgs &ta) {
+    if (atomicInc(ta.grid_sync + 1, gridDim.x - 1) == gridDim.x - 1) *ta.grid_sync = 0;   // every CTA is past the wait
 }
 
 template <int NW>
@@ -626,16 +643,9 @@ __device__ __noinline__ void grid_merge_tail(const DecodeArgs &a, const TailArgs
     };
     Item cur{};
     if (blockIdx.x < items) cur = locate(blockIdx.x);
-    if (tid == 0) {
-        uint32_t ok = 0;
-        for (uint32_t i = 0; i < kGridSpinLimit; ++i)
-            if (ld_acquire_gpu(ta.grid_sync) >= gridDim.x) { ok = 1; break; }
-        if (!ok && ta.status) atomicCAS(ta.status, 0, 90);
-        sm_misc[0] = ok;
-    }
+    if (tid == 0) sm_misc[0] = grid_barrier_wait(ta);
     __syncthreads();
-    if (!sm_misc[0]) return;   // the barrier words stay dirty: the status word tells the host to re-initialise the workspace
-    for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
+    for (uint32_t it = blockIdx.x; it < items && sm_misc[0]; it += gridDim.x) {
         const uint32_t seq = cur.seq, head = cur.head, d = cur.d, nrec = cur.nrec;
         if (nrec > 1) {       // a single record went straight to the output
             const size_t span_stride = (size_t)2 * ta.nh * rs;               // floats between the slot-0 records of two spans
@@ -695,7 +705,7 @@ __device__ __noinline__ void grid_merge_tail(const DecodeArgs &a, const TailArgs
             cur = locate(it + gridDim.x);
         }
     }
-    if (tid == 0 && atomicInc(ta.grid_sync + 1, gridDim.x - 1) == gridDim.x - 1) *ta.grid_sync = 0;   // every CTA is past the wait
+    if (tid == 0) grid_barrier_leave(ta);
 }
 
 // The same tail for a row-sharded sequence (one process per GPU): after the grid barrier a CTA merges 64 dims of one
@@ -731,17 +741,10 @@ __device__ __noinline__ void grid_exchange_tail(const DecodeArgs &a, const TailA
                                           : (uint32_t)(((unsigned long long)(nb - 1) * ta.spans) / ta.line_blocks)) + 1;
     const uint32_t chunks = p2p_chunks(ta.hd), items = ta.nh * chunks, rs = ta.hd + 2;
     const unsigned long long flags_bytes = p2p_chunk_flags_bytes(world, ta.nh, ta.hd);
-    if (tid == 0) {
-        uint32_t ok = 0;
-        for (uint32_t i = 0; i < kGridSpinLimit; ++i)
-            if (ld_acquire_gpu(ta.grid_sync) >= gridDim.x) { ok = 1; break; }
-        if (!ok && ta.status) atomicCAS(ta.status, 0, 90);
-        sm_misc[0] = ok;
-    }
+    if (tid == 0) sm_misc[0] = grid_barrier_wait(ta);
     __syncthreads();
-    if (!sm_misc[0]) return;
     auto bar64 = [] { asm volatile("bar.sync 1, 64;" ::: "memory"); };
-    for (uint32_t it = blockIdx.x; it < items; it += gridDim.x) {
+    for (uint32_t it = blockIdx.x; it < items && sm_misc[0]; it += gridDim.x) {
         const uint32_t head = it / chunks, chunk = it % chunks;
         const uint32_t d = chunk * kP2PChunk + xt, dd = min(d, ta.hd - 1);
         float val, lse;
@@ -814,13 +817,13 @@ __device__ __noinline__ void grid_exchange_tail(const DecodeArgs &a, const TailA
                 const uint32_t *flag = reinterpret_cast<const uint32_t *>(my_base) +
                                        (((size_t)par * world + xt) * ta.nh + head) * chunks + chunk;
                 bool ok = false;
-                for (uint32_t i = 0; i < kP2PSpinLimit; ++i) {
+                for (uint32_t i = 0; i < ta.wait_peer; ++i) {
                     if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) { ok = true; break; }
-                    if ((i & 4095u) == 4095u && *reinterpret_cast<volatile int *>(ta.status)) break;   // somebody already gave up
+                    if ((i & 4095u) == 4095u && gave_up(ta.status)) break;   // somebody already gave up
                 }
                 if (!ok) {
                     sm_misc[1] = 1;
-                    atomicCAS(ta.status, 0, 100 + (int)xt);
+                    report_timeout(ta.status, 100 + (int)xt);
                 }
             }
             bar64();
@@ -851,7 +854,7 @@ __device__ __noinline__ void grid_exchange_tail(const DecodeArgs &a, const TailA
         __syncthreads();   // scratch and sm_lse are rewritten by the next item
         if (sm_misc[1]) break;
     }
-    if (tid == 0 && atomicInc(ta.grid_sync + 1, gridDim.x - 1) == gridDim.x - 1) *ta.grid_sync = 0;
+    if (tid == 0) grid_barrier_leave(ta);
 }
 
 // Resident CTAs per SM each configuration is built for (bounds the registers per thread).
@@ -861,10 +864,22 @@ constexpr int decode16_min_blocks(int HD, int NW, int STAGES) {
 
 // KPC kv heads per CTA: warp w streams kv head (w % KPC) of the CTA's rows, and the WPK = NW/KPC warps
 // that share a kv head take alternate 16-position blocks.  With KPC == nkv a CTA reads whole cache rows.
-template <typename T, int HD, int NW, int STAGES, int KPC>
+// ILV (one sequence, merged by the grid): instead of walking a span of its own, warp g of the W warps that serve a
+// kv head takes the sequence's 16-row blocks g, g + W, g + 2W, ...  Equal spans do not finish together — CTAs whose
+// span lies in memory that is far from their SM stream several microseconds longer over a 40 us launch, and the grid
+// barrier waits for the slowest — whereas interleaved every warp sees the same mix of memory and they end within a
+// block of each other (long-context step 53.8 -> 51.7 us).  Taking the blocks from a shared atomic counter instead
+// measured slower (59.9 us: the counter's answer is one more dependent memory round trip per block, and under load
+// a round trip is a whole iteration).  Which rows a warp saw does not matter to the result: its (m, l, O) state is
+// merged by log-sum-exp like any other.
+template <typename T, int HD, int NW, int STAGES, int KPC, bool ILV = false>
 __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) decode16_kernel(const __grid_constant__ DecodeArgs a) {
     using S = Decode16Smem<HD, NW, STAGES, KPC>;
     constexpr int WPK = NW / KPC;
+    static_assert(!ILV || KPC == 1, "the interleaved mode serves one kv head per CTA");
+    // a tile is requested STAGES-1 tiles ahead of its use: the K-phase of iteration i requests a tile of block
+    // i + kOffK, the V-phase one of block i + kOffV
+    constexpr int kOffK = (STAGES - 1) / 2, kOffV = STAGES / 2;
     static_assert(NW % KPC == 0, "warps must divide evenly over the kv heads of a CTA");
     constexpr int CH = HD / 8;            // 16-byte chunks per row
     constexpr bool QREG = HD <= 128;      // keep the Q fragments in registers (else re-read them from shared memory)
@@ -880,10 +895,13 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
     const uint32_t KG = a.nkv / KPC;
     const uint32_t zi = blockIdx.x % a.gz, kg = (blockIdx.x / a.gz) % KG;
     const uint32_t work = blockIdx.x / (a.gz * KG);
-    if (warp == 0) cursor_init(a, work, lane, sm_item);
-    __syncthreads();
-    Cursor cur{sm_item[0], sm_item[1], sm_item[2], sm_item[3], work, sm_item[4]};
-    __syncthreads();  // sm_item[7] is reused as the merge flag below
+    Cursor cur{};
+    if constexpr (!ILV) {
+        if (warp == 0) cursor_init(a, work, lane, sm_item);
+        __syncthreads();
+        cur = Cursor{sm_item[0], sm_item[1], sm_item[2], sm_item[3], work, sm_item[4]};
+        __syncthreads();  // sm_item[7] is reused as the merge flag below
+    }
     const uint32_t kvl = warp % KPC, sub = warp / KPC;             // kv head within the CTA, block phase
     const uint32_t kvh = kg * KPC + kvl;
     const uint32_t row0 = zi * 16;                                 // first head of the group handled here
@@ -900,7 +918,12 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
     const uint32_t l_row = lane / CH * (RPI > 1), l_chunk = lane % CH;
 
     Piece p;
-    while (next_piece(a, cur, p)) {
+    bool ilv_todo = ILV;
+    if constexpr (ILV) {   // the whole sequence is this CTA's piece; its record is number `work` of a.spans
+        p.seq = 0; p.L = seq_len_at(a, 0); p.start = 0; p.end = p.L; p.nrec = a.spans; p.my_rec = work; p.c0 = 0; p.B = 0;
+    }
+    while (ILV ? ilv_todo : next_piece(a, cur, p)) {
+        ilv_todo = false;
         const uint32_t start = p.start, end = p.end;
         // paged cache: kbase/vbase are the pools and every 16-row block takes its page number from the table; the
         // number of the warp's next block is fetched one block ahead so that its latency never meets a cp.async
@@ -913,8 +936,11 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
         // item t lives in slot t % STAGES, and STAGES-1 items are in flight while one is being consumed.
         const uint32_t n_items = 2 * my_n;
         constexpr int NIT = (2 * CH + 31) / 32;   // K and V chunks per lane
-        const bool tail = a.fuse_append && p.L > 0 && p.end == p.L;
+        const bool tail = !ILV && a.fuse_append && p.L > 0 && p.end == p.L;
         const bool owner = tail && ((nblk - 1) % WPK == sub) && KPC == 1;
+        // interleaved mode: the warp's i-th block is block ilv_g + i * ilv_w of the sequence
+        const uint32_t ilv_w = a.spans * NW, ilv_g = work * NW + warp;
+        const uint32_t ilv_n = nblk > ilv_g ? (nblk - ilv_g + ilv_w - 1) / ilv_w : 0;
         uint4 newrow[NIT];
         // put the kept row into the tile that was just fetched (the copy in flight may predate the store above)
         auto patch_tile = [&](uint32_t tile_addr, uint32_t pos0, uint32_t want_v) {
@@ -936,8 +962,9 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             return pos0 < end ? ptab[pos0 / a.kv.page_rows] : 0u;
         };
         if (ptab) pg_nxt = page_of_block(0);
-        auto issue = [&](uint32_t t) {   // called with t = 0, 1, 2, ... in order: the K tile of a block, then its V tile
-            const uint32_t pos0 = start + (sub + (t >> 1) * WPK) * kBlk;
+        // called with t = 0, 1, 2, ... in order: the K tile of a block, then its V tile; blk = the block's number in the piece
+        auto issue = [&](uint32_t t, uint32_t blk) {
+            const uint32_t pos0 = start + blk * kBlk;
             const uint32_t st = warp_smem + (t % STAGES) * S::kTileBytes;
             const char *src = (t & 1) ? vbase : kbase;
             uint32_t row0_src = pos0;     // row of the block's first position relative to src
@@ -981,8 +1008,11 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
         }
         // ---- start the K/V stream, the rest of the prologue runs underneath it ----
 #pragma unroll
+        // block number (within the piece) of the warp's i-th block, and how many it has
+        auto block_of = [&](uint32_t i) { return ILV ? ilv_g + i * ilv_w : sub + i * WPK; };
+        const uint32_t w_n = ILV ? ilv_n : my_n, w_items = 2 * w_n;
         for (int s = 0; s < STAGES - 1; ++s) {
-            if ((uint32_t)s < n_items) issue(s);
+            if ((uint32_t)s < w_items) issue(s, block_of(s >> 1));
             cp_async_commit();
         }
         // ---- fused append: the warp that will process the block holding row L-1 builds that row of K (norm + RoPE)
@@ -1113,15 +1143,15 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
         for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
         float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-        for (uint32_t i = 0; i < my_n; ++i) {
+        for (uint32_t i = 0; i < w_n; ++i) {
             cp_async_wait<STAGES - 2>();   // this block's K tile has landed
             __syncwarp();
-            if (2 * i + STAGES - 1 < n_items) issue(2 * i + STAGES - 1);
+            if (2 * i + STAGES - 1 < w_items) issue(2 * i + STAGES - 1, block_of(i + kOffK));
             cp_async_commit();
 
             const uint32_t st = warp_smem + ((2 * i) % STAGES) * S::kTileBytes;
-            const uint32_t pos0 = start + (sub + i * WPK) * kBlk;
-            if (owner && i == my_n - 1) patch_tile(st, pos0, 0u);
+            const uint32_t pos0 = start + block_of(i) * kBlk;
+            if (owner && i == w_n - 1) patch_tile(st, pos0, 0u);
             // ---- S = Q K^T : heads x 16 positions ----
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -1176,10 +1206,10 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             // ---- O = O*corr + P V ----
             cp_async_wait<STAGES - 2>();   // this block's V tile has landed
             __syncwarp();
-            if (2 * i + STAGES < n_items) issue(2 * i + STAGES);   // into the slot of the K tile just consumed
+            if (2 * i + STAGES < w_items) issue(2 * i + STAGES, block_of(i + kOffV));   // into the slot of the K tile just consumed
             cp_async_commit();
             const uint32_t stv = warp_smem + ((2 * i + 1) % STAGES) * S::kTileBytes;
-            if (owner && i == my_n - 1) patch_tile(stv, pos0, 1u);
+            if (owner && i == w_n - 1) patch_tile(stv, pos0, 1u);
 #pragma unroll
             for (int jn = 0; jn < HD / 8; jn += 2) {
                 uint32_t vb[4];
@@ -1465,13 +1495,13 @@ __global__ void __launch_bounds__(kMergeThreads) shard_merge_p2p_kernel(const De
         const uint32_t *flag = reinterpret_cast<const uint32_t *>(a.px_peer_bases[a.px_rank]) +
                                (((size_t)par * world + tid) * a.nh + head) * chunks + chunk;
         bool ok = false;
-        for (uint32_t i = 0; i < kP2PSpinLimit; ++i) {
+        for (uint32_t i = 0; i < a.wait_peer; ++i) {
             if ((int32_t)(ld_acquire_sys(flag) - a.px_epoch) >= 0) { ok = true; break; }
-            if ((i & 4095u) == 4095u && *reinterpret_cast<volatile int *>(a.px_error)) break;   // somebody already gave up
+            if ((i & 4095u) == 4095u && gave_up(a.status)) break;   // somebody already gave up
         }
         if (!ok) {
             sm_fail = 1;
-            atomicCAS(a.px_error, 0, 100 + (int)tid);
+            report_timeout(a.status, 100 + (int)tid);
         }
     }
     bar64();
@@ -1544,11 +1574,11 @@ __global__ void sigmoid_mul_kernel(float *x, const float *gate, uint32_t n) {
 // ---------------------------------------------------------------------------------------
 // Host launchers
 // ---------------------------------------------------------------------------------------
-template <typename T, int HD, int NW, int STAGES, int KPC>
+template <typename T, int HD, int NW, int STAGES, int KPC, bool ILV = false>
 static int launch16(shady_ctx *ctx, const DecodeArgs &a, uint32_t blocks) {
     using S = Decode16Smem<HD, NW, STAGES, KPC>;
     static_assert(S::kTotal <= 232448, "shared memory of this configuration exceeds 227 KB");
-    auto kern = decode16_kernel<T, HD, NW, STAGES, KPC>;
+    auto kern = decode16_kernel<T, HD, NW, STAGES, KPC, ILV>;
     static thread_local int configured_dev = -1;
     if (configured_dev != ctx->device) {
         SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
@@ -1578,6 +1608,12 @@ static int launch16_kpc(shady_ctx *ctx, const DecodeArgs &a, uint32_t kpc, bool 
     if (kpc == 2) return SHADY_L16(2);
     return SHADY_L16(1);
 #undef SHADY_L16
+}
+// The interleaved mode exists for the default configuration of each head_dim only.
+template <int HD, int NW, int STAGES>
+static int launch16_ilv(shady_ctx *ctx, const DecodeArgs &a, bool half, uint32_t blocks) {
+    return half ? launch16<__half, HD, NW, STAGES, 1, true>(ctx, a, blocks)
+                : launch16<__nv_bfloat16, HD, NW, STAGES, 1, true>(ctx, a, blocks);
 }
 
 struct Variant16 {
@@ -1622,13 +1658,7 @@ static uint32_t head_groups(uint32_t kv_dtype, uint32_t G) {
     return (G + 15) / 16;
 }
 
-// Tuning overrides for experiments: SHADY_DECODE_VARIANT picks the {warps, stages} configuration,
-// SHADY_DECODE_CTAS_PER_SM the number of spans per SM, SHADY_DECODE_MIN_SPAN the smallest span (row-blocks).
-static uint32_t env_u32(const char *name, uint32_t dflt) {
-    const char *v = getenv(name);
-    return v && *v ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
-}
-constexpr uint32_t kDeferMergeRecords = 12;  // more records than this per sequence: merge in a second launch
+constexpr uint32_t kDeferMergeRecords = 12;  // more records than this per sequence: merged by the whole grid, not by its last CTA
 
 // Workspace layout: [arrival counters: num_seqs*nkv*gz u32][grid barrier: 2 u32], padded to 256 B, [partial records].
 static size_t counter_words(const shady_decode_params *p) {
@@ -1654,7 +1684,7 @@ struct FusedAppendIn {
     const uint16_t *norm_w;
 };
 
-// Cross-GPU tail of a row-sharded decode (NULL = none): merge + exchange + merge across ranks in the second launch.
+// Cross-GPU tail of a row-sharded decode (NULL = none): merge + exchange + merge across ranks in the same launch.
 struct ShardExchangeIn {
     uint32_t world, rank, epoch, out_dtype;
     void *const *d_peer_table;
@@ -1662,10 +1692,24 @@ struct ShardExchangeIn {
     const float *d_gate;
 };
 
-int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
-                  const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, void *d_out, float *d_lse,
-                  const float *d_gate, void *d_ws, size_t ws_bytes, float *d_force_partials, float *d_shard_records,
-                  const FusedAppendIn *fa, const ShardExchangeIn *px) {
+// Everything a decode launch needs except the scratch memory: checked arguments, the span plan, which kernel
+// variant runs and how much scratch this particular launch touches.  Both entry points that launch a decode (with
+// the caller's workspace, with the built-in array) go through plan_decode and run_decode, so they cannot drift.
+struct DecodePlan {
+    DecodeArgs a;
+    Variant16 var;
+    uint32_t kpc, blocks;
+    bool f32, half, need_ws, second_launch;
+    size_t counters_bytes;   // arrival counters + barrier words at the head of the scratch
+    size_t scratch_bytes;    // counters + the records this launch writes (<= decode_workspace_bytes)
+    dim3 merge_grid;         // second launch (no grid merge): balanced_merge_kernel / shard_merge_p2p_kernel
+    bool exchange;
+};
+
+static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
+                       const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, void *d_out, float *d_lse,
+                       const float *d_gate, float *d_force_partials, float *d_shard_records, const FusedAppendIn *fa,
+                       const ShardExchangeIn *px, DecodePlan *plan) {
     SHADY_REQUIRE(ctx, p && (d_q || fa) && cache && d_seq_lens, SHADY_ERR_BAD_ARG, "decode: null argument");
     SHADY_REQUIRE(ctx, d_out || d_force_partials || d_shard_records, SHADY_ERR_BAD_ARG, "decode: null output");
     SHADY_REQUIRE(ctx, p->num_seqs > 0 && p->num_kv_heads > 0 && p->heads_per_kv > 0, SHADY_ERR_BAD_ARG,
@@ -1679,13 +1723,15 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
                   "decode: q_dtype must be f32 or the cache dtype");
     SHADY_REQUIRE(ctx, p->out_dtype == SHADY_F32 || p->out_dtype == cache->dtype, SHADY_ERR_UNSUPPORTED,
                   "decode: out_dtype must be f32 or the cache dtype");
+    if (const int st = pending_timeout(ctx, "decode")) return st;
     const uint32_t hd = p->head_dim;
     SHADY_REQUIRE(ctx, hd <= 256, SHADY_ERR_UNSUPPORTED, "decode: head_dim > 256 (the reference shader's limit)");
     const bool f32 = cache->dtype == SHADY_F32;
     if (f32) SHADY_REQUIRE(ctx, hd == 64 || hd == 128 || hd == 256, SHADY_ERR_UNSUPPORTED, "decode: f32 cache needs head_dim 64/128/256");
     else SHADY_REQUIRE(ctx, hd == 128 || hd == 256, SHADY_ERR_UNSUPPORTED, "decode: 16-bit cache needs head_dim 128/256");
 
-    DecodeArgs a{};
+    DecodeArgs &a = plan->a;
+    a = DecodeArgs{};
     a.q = d_q; a.out = d_out; a.lse = d_lse; a.gate = d_gate;
     if (const int st = fill_kv_addr(ctx, cache, p->num_kv_heads, hd, "decode", &a.kv)) return st;
     SHADY_REQUIRE(ctx, !a.kv.page_table || p->num_splits <= 1, SHADY_ERR_UNSUPPORTED,
@@ -1700,11 +1746,13 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
     a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e;
     a.num_splits = p->num_splits;
     a.out_row_stride = hd; a.lse_stride = 1;
+    a.status = status_ref(ctx); a.wait_grid = ctx->wait_grid; a.wait_peer = ctx->wait_peer;
     if (d_shard_records) {   // rank-local result of one shard as records [seq][nh][hd+2]: out, lse, (unused)
         a.out = d_shard_records; a.out_dtype = SHADY_F32; a.out_row_stride = hd + 2;
         a.lse = d_shard_records + hd; a.lse_stride = hd + 2; a.gate = nullptr;
     }
     a.gz = head_groups(cache->dtype, p->heads_per_kv);
+    plan->exchange = px != nullptr;
     if (px) {
         SHADY_REQUIRE(ctx, d_shard_records && px->d_peer_table && px->d_out && !fa, SHADY_ERR_BAD_ARG, "decode_shard_p2p: null argument");
         SHADY_REQUIRE(ctx, p->num_seqs == 1 && p->num_splits == 0, SHADY_ERR_UNSUPPORTED,
@@ -1713,11 +1761,10 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
                       "decode_shard_p2p: bad world/rank");
         SHADY_REQUIRE(ctx, px->epoch != 0, SHADY_ERR_BAD_ARG, "decode_shard_p2p: epoch must start at 1 (flags start at 0)");
         SHADY_REQUIRE(ctx, px->out_dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "decode_shard_p2p: bad out dtype");
-        if (const int st = p2p_error_word(ctx, &a.px_error)) return st;
         a.px_peer_bases = reinterpret_cast<char *const *>(px->d_peer_table);
         a.px_out = px->d_out; a.px_gate = px->d_gate; a.px_out_dtype = px->out_dtype;
         a.px_world = px->world; a.px_rank = px->rank; a.px_epoch = px->epoch;
-        a.defer_merge = 1;   // the decode CTAs only write records; the second launch merges and exchanges
+        a.defer_merge = 1;   // the decode CTAs only write records; the tail (or the second launch) merges and exchanges
     }
     if (fa) {
         const shady_append_params *ap = fa->ap;
@@ -1737,31 +1784,30 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
             a.ap_inv_freq[i] = 1.0f / powf(ap->rope_theta, 2.0f * (float)i / (float)ap->rotary_dim);
         a.gate = nullptr;
     }
-    const Variant16 var = variant16(hd, env_u32("SHADY_DECODE_VARIANT", 0));
+    const DecodeKnobs &kn = ctx->knobs;
+    const Variant16 var = variant16(hd, kn.variant);
     // One kv head per CTA measured fastest (sibling CTAs of the other kv heads run next to each other in
-    // the grid and fetch the rest of each cache row); SHADY_DECODE_KPC packs more kv heads into a CTA.
+    // the grid and fetch the rest of each cache row); the kpc knob packs more kv heads into a CTA.
     uint32_t kpc = 1u;
-    {
-        const uint32_t want = env_u32("SHADY_DECODE_KPC", 0);
-        if (!f32 && !fa && want && want <= kv_heads_per_cta(p->num_kv_heads, hd > 128 ? 4u : var.nw) && (want & (want - 1)) == 0) kpc = want;
-    }
+    if (!f32 && !fa && kn.kpc && kn.kpc <= kv_heads_per_cta(p->num_kv_heads, hd > 128 ? 4u : var.nw) && (kn.kpc & (kn.kpc - 1)) == 0)
+        kpc = kn.kpc;
     const uint32_t kv_groups = p->num_kv_heads / kpc;
-    uint32_t ctas_per_sm = env_u32("SHADY_DECODE_CTAS_PER_SM", f32 ? 4u : var.ctas_per_sm);
-    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    uint32_t ctas_per_sm = kn.ctas_per_sm ? kn.ctas_per_sm : (f32 ? 4u : var.ctas_per_sm);
     if (ctas_per_sm > 8) ctas_per_sm = 8;
-    uint32_t min_span = env_u32("SHADY_DECODE_MIN_SPAN", f32 ? 2u : 4u * (var.nw / kpc));
-    if (min_span < 1) min_span = 1;
+    uint32_t min_span = kn.min_span ? kn.min_span : (f32 ? 2u : 4u * (var.nw / kpc));
 
-    unsigned long long items;
-    bool need_ws;
+    const size_t rec_bytes = (size_t)p->num_q_heads * (hd + 2) * sizeof(float);
+    unsigned long long items, recs = 0;
+    plan->need_ws = false;
     if (d_force_partials) {
         SHADY_REQUIRE(ctx, p->num_seqs == 1 && p->num_splits >= 2, SHADY_ERR_BAD_ARG,
                       "decode_partials: needs num_seqs == 1 and num_splits >= 2");
         a.force_partials = 1; a.partials = d_force_partials;
-        items = p->num_splits; need_ws = false;
+        items = p->num_splits;
     } else if (p->num_splits >= 1) {
         items = (unsigned long long)p->num_seqs * p->num_splits;
-        need_ws = p->num_splits > 1;
+        plan->need_ws = p->num_splits > 1;
+        recs = items;
     } else {
         SHADY_REQUIRE(ctx, seq_lens_host, SHADY_ERR_BAD_ARG, "decode: num_splits == 0 needs seq_lens_host");
         unsigned long long line = 0;
@@ -1777,8 +1823,9 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
         a.spans = (uint32_t)spans;
         a.span_math32 = (spans + 1) * line + spans < 0xffffffffull ? 1u : 0u;
         items = spans;
-        need_ws = spans > 1;  // a sequence may straddle spans whenever there is more than one
-        // a sequence cut into many spans is merged by a wide second launch instead of by its last CTA
+        plan->need_ws = spans > 1;  // a sequence may straddle spans whenever there is more than one
+        recs = 2 * spans;           // two record slots per span
+        // a sequence cut into many spans is merged by the grid (or a wide second launch) instead of by its last CTA
         unsigned long long u = 0;
         for (uint32_t i = 0; i < p->num_seqs && !a.defer_merge; ++i) {
             const unsigned long long nb = seq_lens_host[i] == 0 ? 1 : (seq_lens_host[i] + kBlkPos - 1) / kBlkPos;
@@ -1787,46 +1834,72 @@ int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q,
             u += nb;
         }
     }
-    if (need_ws) {
-        const size_t need = decode_workspace_bytes(p);
-        SHADY_REQUIRE(ctx, d_ws && ws_bytes >= need, SHADY_ERR_WORKSPACE, "decode: workspace missing or too small");
-        a.counters = reinterpret_cast<uint32_t *>(d_ws);
-        a.partials = reinterpret_cast<float *>(reinterpret_cast<char *>(d_ws) + counters_bytes(p));
-        a.grid_sync = a.counters + counter_words(p);
-    }
+    plan->counters_bytes = counters_bytes(p);
+    plan->scratch_bytes = plan->need_ws ? plan->counters_bytes + (size_t)recs * rec_bytes : 0;
     const unsigned long long blocks64 = items * kv_groups * a.gz;
     SHADY_REQUIRE(ctx, blocks64 <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "decode: too many work items for one launch");
-    const uint32_t blocks = (uint32_t)blocks64;
+    plan->blocks = (uint32_t)blocks64;
     // one launch instead of two: the grid is one resident wave (it is sized from the SM count above), so it can meet
-    // at a barrier and merge (and, row-sharded, exchange) itself; SHADY_DECODE_GRID_MERGE=0 keeps the second launch
-    if (a.defer_merge && a.grid_sync && !f32 && env_u32("SHADY_DECODE_GRID_MERGE", 1)) {   // (a single span has no workspace)
-        if (const int st = p2p_error_word(ctx, &a.px_error)) return st;
+    // at a barrier and merge (and, row-sharded, exchange) itself; the grid_merge knob set to 0 keeps the second
+    // launch, and so does an experimental CTAs-per-SM override, which may ask for more CTAs than can be resident
+    if (a.defer_merge && plan->need_ws && !f32 && kn.grid_merge && !kn.ctas_per_sm) {   // (a single span has no workspace)
         a.grid_merge = 1;
+        // one sequence of many spans in the default configuration: its blocks are interleaved over all warps
+        if (kn.interleave && p->num_seqs == 1 && !fa && !a.kv.page_table && kpc == 1 && kn.variant == 0) a.interleave = 1;
     }
+    plan->var = var; plan->kpc = kpc; plan->f32 = f32; plan->half = cache->dtype == SHADY_F16;
+    plan->second_launch = a.defer_merge && !a.grid_merge;
+    plan->merge_grid = px ? dim3(1, p->num_q_heads, p2p_chunks(hd)) : dim3(p->num_seqs, p->num_q_heads, (hd + 63) / 64);
+    return SHADY_OK;
+}
 
+// Launches a planned decode on `scratch` (counters zeroed, at least plan.scratch_bytes; NULL when the plan needs none).
+static int run_decode(shady_ctx *ctx, const shady_decode_params *p, DecodePlan &plan, void *scratch) {
+    DecodeArgs &a = plan.a;
+    const uint32_t hd = p->head_dim, blocks = plan.blocks;
+    if (plan.need_ws) {
+        a.counters = reinterpret_cast<uint32_t *>(scratch);
+        a.partials = reinterpret_cast<float *>(reinterpret_cast<char *>(scratch) + plan.counters_bytes);
+        a.grid_sync = a.counters + counter_words(p);
+    }
     int rc;
-    if (f32) {
+    if (plan.f32) {
         const uint32_t gt = group_rows_f32(p->heads_per_kv);
         if (hd == 64) rc = launch32<64, 8>(ctx, a, blocks, gt);
         else if (hd == 128) rc = launch32<128, 8>(ctx, a, blocks, gt);
         else rc = launch32<256, 4>(ctx, a, blocks, gt);
     } else {
-        const bool h = cache->dtype == SHADY_F16;
-        if (hd == 128) {
-            if (var.nw == 8 && var.stages == 6) rc = launch16_kpc<128, 8, 6>(ctx, a, kpc, h, blocks);
-            else if (var.nw == 8) rc = launch16_kpc<128, 8, 4>(ctx, a, kpc, h, blocks);
-            else rc = launch16_kpc<128, 4, 6>(ctx, a, kpc, h, blocks);
-        } else if (var.nw == 4) rc = launch16_kpc<256, 4, 6>(ctx, a, kpc, h, blocks);
-        else if (var.stages == 2) rc = launch16_kpc<256, 8, 2>(ctx, a, kpc, h, blocks);
-        else rc = launch16_kpc<256, 8, 3>(ctx, a, kpc, h, blocks);
+        const bool h = plan.half;
+        const Variant16 &var = plan.var;
+        if (a.interleave) rc = hd == 128 ? launch16_ilv<128, 4, 6>(ctx, a, h, blocks) : launch16_ilv<256, 8, 3>(ctx, a, h, blocks);
+        else if (hd == 128) {
+            if (var.nw == 8 && var.stages == 6) rc = launch16_kpc<128, 8, 6>(ctx, a, plan.kpc, h, blocks);
+            else if (var.nw == 8) rc = launch16_kpc<128, 8, 4>(ctx, a, plan.kpc, h, blocks);
+            else rc = launch16_kpc<128, 4, 6>(ctx, a, plan.kpc, h, blocks);
+        } else if (var.nw == 4) rc = launch16_kpc<256, 4, 6>(ctx, a, plan.kpc, h, blocks);
+        else if (var.stages == 2) rc = launch16_kpc<256, 8, 2>(ctx, a, plan.kpc, h, blocks);
+        else rc = launch16_kpc<256, 8, 3>(ctx, a, plan.kpc, h, blocks);
     }
-    if (rc != SHADY_OK || !a.defer_merge || a.grid_merge) return rc;
+    if (rc != SHADY_OK || !plan.second_launch) return rc;
     // (launching the merge as a programmatic dependent of the decode grid measured slower: 72.7 vs 67.4 us per step)
-    if (px) shard_merge_p2p_kernel<<<dim3(1, p->num_q_heads, p2p_chunks(hd)), kMergeThreads, 0, ctx->stream>>>(a);
-    else balanced_merge_kernel<<<dim3(p->num_seqs, p->num_q_heads, (hd + 63) / 64), kMergeThreads, 0, ctx->stream>>>(a);
+    if (plan.exchange) shard_merge_p2p_kernel<<<plan.merge_grid, kMergeThreads, 0, ctx->stream>>>(a);
+    else balanced_merge_kernel<<<plan.merge_grid, kMergeThreads, 0, ctx->stream>>>(a);
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
+}
+
+int launch_decode(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
+                  const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, void *d_out, float *d_lse,
+                  const float *d_gate, void *d_ws, size_t ws_bytes, float *d_force_partials, float *d_shard_records,
+                  const FusedAppendIn *fa, const ShardExchangeIn *px) {
+    DecodePlan plan;
+    if (const int st = plan_decode(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, d_out, d_lse, d_gate, d_force_partials,
+                                   d_shard_records, fa, px, &plan))
+        return st;
+    if (plan.need_ws)   // the documented size is the bound over any lengths, so that one allocation serves every step
+        SHADY_REQUIRE(ctx, d_ws && ws_bytes >= decode_workspace_bytes(p), SHADY_ERR_WORKSPACE, "decode: workspace missing or too small");
+    return run_decode(ctx, p, plan, d_ws);
 }
 
 // The workspace must hold zeros in its counter area before the first call; the kernels
@@ -1868,92 +1941,28 @@ static int static_scratch_ptr(shady_ctx *ctx, unsigned char **out) {
     return SHADY_OK;
 }
 
+// Same checks, same span plan and same kernels as launch_decode (plan_decode / run_decode); only the scratch differs:
+// what this particular launch touches must fit the array, and the counters are cleared on the stream first because
+// every call on the device shares it.
 int launch_decode_static(shady_ctx *ctx, const shady_decode_params *p, const void *d_q, const shady_kv_cache *cache,
                          const uint32_t *d_seq_lens, const uint32_t *seq_lens_host, void *d_out, float *d_lse,
                          const float *d_gate) {
-    SHADY_REQUIRE(ctx, p && d_q && cache && d_seq_lens && d_out, SHADY_ERR_BAD_ARG, "decode_static: null argument");
-    SHADY_REQUIRE(ctx, p->num_seqs > 0 && p->num_kv_heads > 0 && p->heads_per_kv > 0, SHADY_ERR_BAD_ARG,
-                  "decode_static: zero-sized problem");
-    SHADY_REQUIRE(ctx, p->num_q_heads == p->num_kv_heads * p->heads_per_kv, SHADY_ERR_BAD_ARG,
-                  "decode_static: num_q_heads != num_kv_heads * heads_per_kv");
-    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "decode_static: bad cache dtype");
-    SHADY_REQUIRE(ctx, (cache->d_k_ptrs && cache->d_v_ptrs) || (cache->d_k_base && cache->d_v_base),
-                  SHADY_ERR_BAD_ARG, "decode_static: cache has neither base pointers nor pointer arrays");
-    SHADY_REQUIRE(ctx, p->q_dtype == SHADY_F32 || p->q_dtype == cache->dtype, SHADY_ERR_UNSUPPORTED,
-                  "decode_static: q_dtype must be f32 or the cache dtype");
-    SHADY_REQUIRE(ctx, p->out_dtype == SHADY_F32 || p->out_dtype == cache->dtype, SHADY_ERR_UNSUPPORTED,
-                  "decode_static: out_dtype must be f32 or the cache dtype");
-    const uint32_t hd = p->head_dim;
-    const bool f32 = cache->dtype == SHADY_F32;
-    if (f32) SHADY_REQUIRE(ctx, hd == 64 || hd == 128 || hd == 256, SHADY_ERR_UNSUPPORTED, "decode_static: f32 cache needs head_dim 64/128/256");
-    else SHADY_REQUIRE(ctx, hd == 128 || hd == 256, SHADY_ERR_UNSUPPORTED, "decode_static: 16-bit cache needs head_dim 128/256");
-
-    DecodeArgs a{};
-    a.q = d_q; a.out = d_out; a.lse = d_lse; a.gate = d_gate;
-    if (const int st = fill_kv_addr(ctx, cache, p->num_kv_heads, hd, "decode", &a.kv)) return st;
-    SHADY_REQUIRE(ctx, !a.kv.page_table || p->num_splits <= 1, SHADY_ERR_UNSUPPORTED,
-                  "decode: a paged cache needs num_splits 0 or 1 (16-row blocks must not straddle pages)");
-    a.seq_lens = d_seq_lens;
-    if (seq_lens_host && p->num_seqs <= 32) {
-        a.lens_n = p->num_seqs;
-        for (uint32_t i = 0; i < p->num_seqs; ++i) a.lens_v[i] = seq_lens_host[i];
-    }
-    a.num_seqs = p->num_seqs; a.nkv = p->num_kv_heads; a.nh = p->num_q_heads; a.G = p->heads_per_kv; a.hd = hd;
-    a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;
-    a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e;
-    a.num_splits = p->num_splits;
-    a.out_row_stride = hd; a.lse_stride = 1;
-    a.gz = head_groups(cache->dtype, p->heads_per_kv);
-    const Variant16 var = variant16(hd, 0);
-    const uint32_t kv_groups = p->num_kv_heads;           // one kv head per CTA
-    unsigned long long items, recs;
-    if (p->num_splits >= 1) {
-        items = (unsigned long long)p->num_seqs * p->num_splits;
-        recs = p->num_splits > 1 ? items : 0;
-    } else {
-        SHADY_REQUIRE(ctx, seq_lens_host, SHADY_ERR_BAD_ARG, "decode_static: num_splits == 0 needs seq_lens_host");
-        unsigned long long line = 0;
-        for (uint32_t i = 0; i < p->num_seqs; ++i) line += seq_lens_host[i] == 0 ? 1 : (seq_lens_host[i] + kBlkPos - 1) / kBlkPos;
-        SHADY_REQUIRE(ctx, line <= 0xffffffffull, SHADY_ERR_UNSUPPORTED, "decode_static: batch too long for one launch");
-        const unsigned long long slots = (unsigned long long)ctx->num_sms * (f32 ? 4u : var.ctas_per_sm);
-        unsigned long long spans = slots / ((unsigned long long)kv_groups * a.gz);
-        const unsigned long long min_span = f32 ? 2u : 4u * var.nw;
-        const unsigned long long by_size = (line + min_span - 1) / min_span;
-        if (spans > by_size) spans = by_size;
-        if (spans < 1) spans = 1;
-        a.line_blocks = (uint32_t)line;
-        a.spans = (uint32_t)spans;
-        a.span_math32 = (spans + 1) * line + spans < 0xffffffffull ? 1u : 0u;
-        items = spans;
-        recs = spans > 1 ? 2 * spans : 0;
-    }
-    if (recs) {
-        const size_t counters = ((size_t)p->num_seqs * kv_groups * a.gz * sizeof(uint32_t) + 255) / 256 * 256;
-        const size_t need = counters + (size_t)recs * p->num_q_heads * (hd + 2) * sizeof(float);
-        if (need > kStaticScratchBytes)
+    SHADY_REQUIRE(ctx, d_q && d_out, SHADY_ERR_BAD_ARG, "decode_static: null argument");
+    DecodePlan plan;
+    if (const int st = plan_decode(ctx, p, d_q, cache, d_seq_lens, seq_lens_host, d_out, d_lse, d_gate, nullptr, nullptr,
+                                   nullptr, nullptr, &plan))
+        return st;
+    unsigned char *scratch = nullptr;
+    if (plan.need_ws) {
+        if (plan.scratch_bytes > kStaticScratchBytes)
             return fail(ctx, SHADY_ERR_WORKSPACE,
-                        "decode_static: this launch needs " + std::to_string(need) + " bytes of scratch but the built-in array holds " +
+                        "decode_static: this launch needs " + std::to_string(plan.scratch_bytes) + " bytes of scratch but the built-in array holds " +
                             std::to_string(kStaticScratchBytes) + "; use shady_attn_decode with a caller-provided workspace");
-        unsigned char *scratch = nullptr;
-        const int rc = static_scratch_ptr(ctx, &scratch);
-        if (rc != SHADY_OK) return rc;
-        // the array keeps whatever the previous call left: the arrival counters must start at zero
-        SHADY_CUDA_OK(ctx, cudaMemsetAsync(scratch, 0, counters, ctx->stream));
-        a.counters = reinterpret_cast<uint32_t *>(scratch);
-        a.partials = reinterpret_cast<float *>(scratch + counters);
+        if (const int rc = static_scratch_ptr(ctx, &scratch)) return rc;
+        // the array keeps whatever the previous call left: the arrival counters and barrier words must start at zero
+        SHADY_CUDA_OK(ctx, cudaMemsetAsync(scratch, 0, plan.counters_bytes, ctx->stream));
     }
-    const unsigned long long blocks64 = items * kv_groups * a.gz;
-    SHADY_REQUIRE(ctx, blocks64 <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "decode_static: too many work items for one launch");
-    const uint32_t blocks = (uint32_t)blocks64;
-    if (f32) {
-        const uint32_t gt = group_rows_f32(p->heads_per_kv);
-        if (hd == 64) return launch32<64, 8>(ctx, a, blocks, gt);
-        if (hd == 128) return launch32<128, 8>(ctx, a, blocks, gt);
-        return launch32<256, 4>(ctx, a, blocks, gt);
-    }
-    const bool h = cache->dtype == SHADY_F16;
-    if (hd == 128) return launch16_kpc<128, 4, 6>(ctx, a, 1u, h, blocks);
-    return launch16_kpc<256, 8, 3>(ctx, a, 1u, h, blocks);
+    return run_decode(ctx, p, plan, scratch);
 }
 
 int launch_reduce(shady_ctx *ctx, uint32_t hd, uint32_t ns, uint32_t nh, uint64_t split_stride, uint64_t head_stride,

@@ -9,21 +9,20 @@
 //   3. merges the `world` records with the gqa_reduce.wgsl:33-64 math and writes the final rows.
 // Receive buffers and flags are double-buffered by the parity of the call's epoch: a rank can be at most one
 // call ahead of its slowest peer (it needs that peer's flags of the current call to finish), so the buffer it
-// overwrites is never the one a peer is still merging.  Every wait has an iteration limit; on expiry the kernel
-// records an error code and returns, and the next shady_synchronize reports SHADY_ERR_TIMEOUT.
+// overwrites is never the one a peer is still merging.  Every wait has an iteration limit (shady_ctx_set_wait_limits);
+// on expiry the kernel records a code in the context's status words and returns, and the next shady_synchronize
+// reports SHADY_ERR_TIMEOUT.
 #include "p2p.cuh"
 
 namespace shady {
-
-static __device__ int g_p2p_error_word;
-static int *g_p2p_error[64] = {};
 
 struct P2PArgs {
     char *const *peer_bases;   // device array [world]: every rank's shared buffer as mapped into this process
     const float *rec;          // this rank's records [nh][hd+2]
     void *out;
     const float *gate;
-    int *error;
+    StatusRef status;
+    uint32_t wait_peer;        // poll limit of the flag wait
     uint32_t rank, world, nh, hd, epoch, out_dtype;
     unsigned long long flags_bytes;   // size of the flag region at the head of a shared buffer
 };
@@ -33,18 +32,6 @@ unsigned long long p2p_buffer_bytes(uint32_t world, uint32_t nh, uint32_t hd) {
     const unsigned long long chunked = p2p_chunk_flags_bytes(world, nh, hd) +
                                        (unsigned long long)2 * world * nh * p2p_chunks(hd) * kP2PSlotFloats * sizeof(float);
     return whole > chunked ? whole : chunked;
-}
-
-int p2p_error_word(shady_ctx *ctx, int **out) {
-    SHADY_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, SHADY_ERR_UNSUPPORTED, "combine_p2p: device ordinal out of range");
-    if (!g_p2p_error[ctx->device]) {
-        int *w = nullptr;
-        SHADY_CUDA_OK(ctx, cudaGetSymbolAddress(reinterpret_cast<void **>(&w), g_p2p_error_word));
-        SHADY_CUDA_OK(ctx, cudaMemsetAsync(w, 0, sizeof(int), ctx->stream));
-        g_p2p_error[ctx->device] = w;
-    }
-    *out = g_p2p_error[ctx->device];
-    return SHADY_OK;
 }
 
 __global__ void __launch_bounds__(128) p2p_combine_kernel(const P2PArgs a) {
@@ -70,13 +57,13 @@ __global__ void __launch_bounds__(128) p2p_combine_kernel(const P2PArgs a) {
     if (tid < a.world) {
         const uint32_t *flag = reinterpret_cast<const uint32_t *>(a.peer_bases[a.rank]) + ((size_t)par * a.world + tid) * a.nh + h;
         bool ok = false;
-        for (uint32_t i = 0; i < kP2PSpinLimit; ++i) {
+        for (uint32_t i = 0; i < a.wait_peer; ++i) {
             if ((int32_t)(ld_acquire_sys(flag) - a.epoch) >= 0) { ok = true; break; }
-            if ((i & 4095u) == 4095u && *reinterpret_cast<volatile int *>(a.error)) break;   // somebody already gave up
+            if ((i & 4095u) == 4095u && gave_up(a.status)) break;   // somebody already gave up
         }
         if (!ok) {
             sm_fail = 1;
-            atomicCAS(a.error, 0, 100 + (int)tid);
+            report_timeout(a.status, 100 + (int)tid);
         }
     }
     __syncthreads();
@@ -110,31 +97,15 @@ int launch_combine_p2p(shady_ctx *ctx, uint32_t world, uint32_t rank, uint32_t n
     SHADY_REQUIRE(ctx, world >= 1 && world <= kP2PMaxWorld && rank < world, SHADY_ERR_BAD_ARG, "combine_p2p: bad world/rank");
     SHADY_REQUIRE(ctx, epoch != 0, SHADY_ERR_BAD_ARG, "combine_p2p: epoch must start at 1 (flags start at 0)");
     SHADY_REQUIRE(ctx, out_dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "combine_p2p: bad out dtype");
-    int *err_word = nullptr;
-    if (const int st = p2p_error_word(ctx, &err_word)) return st;
+    if (const int st = pending_timeout(ctx, "combine_p2p")) return st;
     P2PArgs a{};
     a.peer_bases = reinterpret_cast<char *const *>(d_peer_table);
-    a.rec = d_rec; a.out = d_out; a.gate = d_gate; a.error = err_word;
+    a.rec = d_rec; a.out = d_out; a.gate = d_gate; a.status = status_ref(ctx); a.wait_peer = ctx->wait_peer;
     a.rank = rank; a.world = world; a.nh = nh; a.hd = hd; a.epoch = epoch; a.out_dtype = out_dtype;
     a.flags_bytes = p2p_flags_bytes(world, nh);
     p2p_combine_kernel<<<nh, 128, 0, ctx->stream>>>(a);
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
-    return SHADY_OK;
-}
-
-// Reads (and clears) the bounded-wait status of the combine kernel; the stream must be idle.
-int p2p_status(shady_ctx *ctx, int *code) {
-    *code = 0;
-    if (ctx->device < 0 || ctx->device >= 64 || !g_p2p_error[ctx->device]) return SHADY_OK;
-    SHADY_CUDA_OK(ctx, cudaMemcpyAsync(code, g_p2p_error[ctx->device], sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
-    SHADY_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
-    if (*code) {
-        SHADY_CUDA_OK(ctx, cudaMemsetAsync(g_p2p_error[ctx->device], 0, sizeof(int), ctx->stream));
-        if (*code == 90)
-            return fail(ctx, SHADY_ERR_TIMEOUT, "decode: the grid barrier before the record merge ran out; re-initialise the workspace");
-        return fail(ctx, SHADY_ERR_TIMEOUT, "combine_p2p: the flag of rank " + std::to_string(*code - 100) + " did not arrive in time");
-    }
     return SHADY_OK;
 }
 

@@ -4,7 +4,6 @@
 
 namespace shady {
 
-constexpr uint32_t kP2PSpinLimit = 1u << 22;
 constexpr uint32_t kP2PMaxWorld = 16;
 constexpr uint32_t kP2PChunk = 64;            // head dims per CTA of the fused merge + exchange kernel
 constexpr uint32_t kP2PSlotFloats = kP2PChunk + 2;   // 64 values, the head's log-sum-exp, one unused
@@ -30,8 +29,5 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-
-// Device address of the status word the cross-GPU kernels latch an expired wait into (p2p.cu); zeroed on first use.
-int p2p_error_word(shady_ctx *ctx, int **out);
 
 }  // namespace shady

@@ -23,6 +23,14 @@
 //     masks only the last (diagonal) one.
 // Every mbarrier wait is bounded: on expiry the kernel records an error code, skips the rest of
 // its work, releases TMEM and returns (the host reports SHADY_ERR_TIMEOUT).
+//
+// FUSED variant (shady_attn_prefill_append): Q comes straight from the projection (q_proj_full, Q and gate halves
+// per head) instead of from a buffer a separate append pass has normed and rotated.  The raw Q tile lands by TMA in
+// one of three rotating shared-memory buffers; two extra warps apply RMSNorm(1+w) and RoPE to it in place
+// (fused_split_qknorm_kvstore.wgsl:126-166; cos/sin of (position, pair) from a table the K/V pass of the same step
+// wrote), make it visible to the tensor core's proxy and only then signal the MMA issuer; the epilogue multiplies
+// by sigmoid(gate) (sigmoid_mul.wgsl).  The 2 x 134 MB round trip of the rotated Q of a 16k-token step never
+// happens, and with three buffers a tile of the next item is transformed while the current item still computes.
 #include <cuda.h>
 
 #include <type_traits>
@@ -37,24 +45,34 @@ constexpr int kPD = 128;                 // head_dim
 constexpr int kKvStages = 2;
 constexpr uint32_t kSlabBytes = 128 * 64 * 2;   // [128 rows][64 elements] 16-bit, 128B-swizzled
 constexpr uint32_t kTileBytes = 2 * kSlabBytes; // 128 x 128 elements
+// shared memory: [Q buffers: nqb tiles][K stages][V stages][barriers]; nqb = 2 (tile q of an item lives in buffer
+// q) or, fused, 3 rotating buffers
 constexpr uint32_t kSmemQ = 0;
-constexpr uint32_t kSmemK = kSmemQ + 2 * kTileBytes;
-constexpr uint32_t kSmemV = kSmemK + kKvStages * kTileBytes;
-constexpr uint32_t kSmemBar = kSmemV + kKvStages * kTileBytes;
-constexpr uint32_t kPrefillSmem = kSmemBar + 256 + 1024;  // + barriers + slack for 1024-byte alignment
+constexpr uint32_t smem_k_off(uint32_t nqb) { return kSmemQ + nqb * kTileBytes; }
+constexpr uint32_t smem_v_off(uint32_t nqb) { return smem_k_off(nqb) + kKvStages * kTileBytes; }
+constexpr uint32_t smem_bar_off(uint32_t nqb) { return smem_v_off(nqb) + kKvStages * kTileBytes; }
+constexpr uint32_t prefill_smem(uint32_t nqb) { return smem_bar_off(nqb) + 256 + 1024; }  // + barriers + slack for 1024-byte alignment
+static_assert(prefill_smem(3) <= 232448, "three Q buffers must fit in 227 KB");
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSpinLimit = 1u << 20;  // bounded waits: on the order of a second at worst, then give up
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
-enum { BAR_QFULL = 0, BAR_KVFULL = 2, BAR_KVEMPTY = 4, BAR_SFULL = 6, BAR_PFULL = 8, BAR_OFULL = 10, BAR_QEMPTY = 12,
-       BAR_COUNT = 14 };
+enum { BAR_QFULL = 0, BAR_QEMPTY = 3, BAR_QRAW = 6, BAR_KVFULL = 9, BAR_KVEMPTY = 11, BAR_SFULL = 13, BAR_PFULL = 15,
+       BAR_OFULL = 17, BAR_COUNT = 19 };
+constexpr uint32_t kQWarps = 2;   // fused: warps that norm and rotate the raw Q tiles
 
 struct PrefillArgs {
     void *out;
-    int *error;          // device word: 0 = ok, else the code of the wait that expired
+    StatusRef status;    // where a wait that ran out is reported (code 1..12 = which barrier)
+    uint32_t wait_mbar;  // poll limit of every mbarrier wait
     uint32_t B, T, nh, nkv, G;
     uint32_t m_tiles;    // ceil(T / 256)
     float scale_log2;
+    // fused variant: the raw projection rows [B][T][nh][qrow] (Q half first, then the gate half when has_gate)
+    const void *q_src;
+    const float2 *cs_table;   // [T][64] (cos, sin) of (position, rotary pair); (1, 0) beyond the rotary dims
+    const uint16_t *norm_w;   // bf16 bits of the Q RMSNorm weights [128], or NULL
+    uint32_t qrow, has_gate;
+    float eps;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -79,14 +97,19 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and latches `code` into *error and the CTA's abort word) on expiry or
 // when another role has already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_word, int *error, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+struct WaitCtx {
+    volatile uint32_t *abort_word;   // shared memory: a role of this CTA gave up
+    StatusRef status;
+    uint32_t limit;
+};
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx &w, int code) {
+    for (uint32_t i = 0; i < w.limit; ++i) {
         if (mbar_try(bar, parity)) return true;
         // another role of this CTA, or any CTA of the grid, has already given up: stop waiting
-        if ((i & 1023u) == 1023u && (*abort_word || *reinterpret_cast<volatile int *>(error))) return false;
+        if ((i & 1023u) == 1023u && (*w.abort_word || gave_up(w.status))) return false;
     }
-    *abort_word = 1;
-    atomicCAS(error, 0, code);
+    *w.abort_word = 1;
+    report_timeout(w.status, code);
     return false;
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
@@ -217,10 +240,12 @@ template <> __device__ __forceinline__ uint32_t pack16<__nv_bfloat16>(float lo, 
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(320, 1)
+template <typename T, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? 320 + 32 * kQWarps : 320, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
+    constexpr uint32_t NQB = FUSED ? 3u : 2u;   // Q buffers; tile number tq of this CTA lives in buffer tq % NQB
+    constexpr uint32_t kSmemK = smem_k_off(NQB), kSmemV = smem_v_off(NQB), kSmemBar = smem_bar_off(NQB);
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
     unsigned char *smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -230,7 +255,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     volatile uint32_t *abort_word = tmem_slot + 1;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (*reinterpret_cast<volatile int *>(a.error)) return;   // an earlier CTA's wait expired: do not start
+    if (gave_up(a.status)) return;   // an earlier wait of this context expired: do not start
+    const WaitCtx wc{abort_word, a.status, a.wait_mbar};
     // Persistent CTAs: work items are (256-row block, sequence, query head), ordered heaviest (latest rows) first.
     // The list is dealt out in rounds of gridDim.x items, left to right in even rounds and right to left in odd
     // ones, so the CTA that got the heaviest item of one round gets the lightest of the next (a plain stride left
@@ -257,13 +283,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
     if (warp == 8 && lane == 0) {
-        mbar_init(bar(BAR_QFULL + 0), 1); mbar_init(bar(BAR_QFULL + 1), 1);
+        for (uint32_t b = 0; b < NQB; ++b) {
+            // fused: every thread of the Q warps arrives once its part of the tile is transformed and fenced
+            mbar_init(bar(BAR_QFULL + b), FUSED ? 32 * kQWarps : 1); mbar_init(bar(BAR_QEMPTY + b), 1);
+            mbar_init(bar(BAR_QRAW + b), 1);
+        }
         for (int s = 0; s < kKvStages; ++s) {
             mbar_init(bar(BAR_KVFULL + s), 1); mbar_init(bar(BAR_KVEMPTY + s), 1);
         }
         for (int q = 0; q < 2; ++q) {
             mbar_init(bar(BAR_SFULL + q), 1); mbar_init(bar(BAR_PFULL + q), 128); mbar_init(bar(BAR_OFULL + q), 1);
-            mbar_init(bar(BAR_QEMPTY + q), 1);
         }
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -282,25 +311,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // =============================== TMA producer ===============================
         if (lane == 0) {
             bool ok = true;
-            uint32_t gk = 0, qc[2] = {0, 0};   // K/V tiles and Q tiles requested so far (barrier phases run through the items)
+            uint32_t gk = 0, tq = 0;   // K/V tiles and Q tiles requested so far (barrier phases run through the items)
             for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
                 const uint32_t w = item_of_round(rnd);
                 if (w >= total_items) continue;
                 const Item it = get_item(w);
                 for (int q = 0; q < 2 && ok; ++q) {   // Q of this item, once the last QK of the previous user of the buffer is done
                     if (!it.n[q]) continue;
-                    if (qc[q] > 0) ok = mbar_wait(bar(BAR_QEMPTY + q), (qc[q] - 1) & 1, abort_word, a.error, 12);
+                    const uint32_t buf = tq % NQB, use = tq / NQB;
+                    if (use > 0) ok = mbar_wait(bar(BAR_QEMPTY + buf), (use - 1) & 1, wc, 12);
                     if (!ok) break;
-                    ++qc[q];
-                    mbar_expect_tx(bar(BAR_QFULL + q), kTileBytes);
-                    const uint32_t dst = smem_base + kSmemQ + q * kTileBytes;
-                    tma_load_4d(dst, &map_q, bar(BAR_QFULL + q), 0, (int)it.h, (int)(it.q0 + q * kPM), (int)it.b);
-                    tma_load_4d(dst + kSlabBytes, &map_q, bar(BAR_QFULL + q), 64, (int)it.h, (int)(it.q0 + q * kPM), (int)it.b);
+                    ++tq;
+                    // fused: the tile arrives raw (the Q half of the projection rows) and the Q warps pass it on
+                    const uint32_t landed = bar((FUSED ? BAR_QRAW : BAR_QFULL) + buf);
+                    mbar_expect_tx(landed, kTileBytes);
+                    const uint32_t dst = smem_base + kSmemQ + buf * kTileBytes;
+                    tma_load_4d(dst, &map_q, landed, 0, (int)it.h, (int)(it.q0 + q * kPM), (int)it.b);
+                    tma_load_4d(dst + kSlabBytes, &map_q, landed, 64, (int)it.h, (int)(it.q0 + q * kPM), (int)it.b);
                 }
                 for (uint32_t j = 0; j < it.nkv && ok; ++j) {   // K and V tile j travel together: one stage, one barrier
                     const uint32_t gi = gk + j;
                     const uint32_t s = gi % kKvStages, ph = (gi / kKvStages) & 1;
-                    if (gi >= kKvStages) ok = mbar_wait(bar(BAR_KVEMPTY + s), ph ^ 1, abort_word, a.error, 1);
+                    if (gi >= kKvStages) ok = mbar_wait(bar(BAR_KVEMPTY + s), ph ^ 1, wc, 1);
                     if (!ok) break;
                     mbar_expect_tx(bar(BAR_KVFULL + s), 2 * kTileBytes);
                     const uint32_t kd = smem_base + kSmemK + s * kTileBytes, vd = smem_base + kSmemV + s * kTileBytes;
@@ -317,8 +349,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (lane == 0) {
             const uint32_t idesc_qk = make_idesc(kFmt, false), idesc_pv = make_idesc(kFmt, true);
             bool ok = true;
+            uint32_t qbuf[2] = {0, 0};                             // Q buffers of the current item's two tiles
             auto issue_qk = [&](uint32_t q, uint32_t s) {          // S_q = Q_q * K(stage s)^T
-                const uint32_t qa = smem_base + kSmemQ + q * kTileBytes, kb = smem_base + kSmemK + s * kTileBytes;
+                const uint32_t qa = smem_base + kSmemQ + qbuf[q] * kTileBytes, kb = smem_base + kSmemK + s * kTileBytes;
 #pragma unroll
                 for (uint32_t ks = 0; ks < kPD / 16; ++ks) {
                     const uint32_t off = (ks >> 2) * kSlabBytes + (ks & 3) * 32;
@@ -332,17 +365,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 for (uint32_t ks = 0; ks < kPN / 16; ++ks)
                     mma_ts(tmem + 256 + q * 128, tmem + q * 128 + ks * 8, desc_mnmajor(vb + ks * 2048), idesc_pv, !first || (ks > 0));
             };
-            uint32_t gk = 0, qc[2] = {0, 0}, tc[2] = {0, 0};   // running counts: K/V tiles, Q loads, score tiles per row tile
+            uint32_t gk = 0, tq = 0, tc[2] = {0, 0};   // running counts: K/V tiles, Q tiles, score tiles per row tile
             for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
                 const uint32_t w = item_of_round(rnd);
                 if (w >= total_items) continue;
                 const Item it = get_item(w);
                 const uint32_t nkv = it.nkv;
-                for (int q = 0; q < 2 && ok; ++q)
+                uint32_t qpar[2] = {0, 0};
+                for (int q = 0; q < 2; ++q)
                     if (it.n[q]) {
-                        ok = mbar_wait(bar(BAR_QFULL + q), qc[q] & 1, abort_word, a.error, 3);
-                        ++qc[q];
+                        qbuf[q] = tq % NQB; qpar[q] = (tq / NQB) & 1;
+                        ++tq;
                     }
+                // tile 0 must be there before anything is issued; tile 1 only ahead of its own first S (fused: it may
+                // still be under the Q warps' hands while S0 of the first K/V tile is computed)
+                ok = mbar_wait(bar(BAR_QFULL + qbuf[0]), qpar[0], wc, 3);
                 // Per K/V tile the issuer stops three times (K/V landed, P1 stored, P0 stored) and commits three
                 // times (S0, S1, stage free): every stop drains the short MMA queue, so there are as few as the
                 // dependencies allow.  O needs no barrier of its own inside an item: a commit covers every MMA the
@@ -351,17 +388,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     const uint32_t gi = gk + j;
                     const uint32_t s = gi % kKvStages, ph = (gi / kKvStages) & 1;
                     if (j < nkv) {
-                        ok = mbar_wait(bar(BAR_KVFULL + s), ph, abort_word, a.error, 4);
+                        ok = mbar_wait(bar(BAR_KVFULL + s), ph, wc, 4);
                         if (!ok) break;
                         tc_fence_after();
                     }
                     if (j < it.n[0]) {
                         issue_qk(0, s);
-                        if (j == it.n[0] - 1) tc_commit(bar(BAR_QEMPTY + 0));   // Q0 of this item is no longer needed
+                        if (j == it.n[0] - 1) tc_commit(bar(BAR_QEMPTY + qbuf[0]));   // Q0 of this item is no longer needed
                     }
                     if (j >= 1 && j - 1 < it.n[1]) {
                         const uint32_t sp = (gi - 1) % kKvStages;
-                        ok = mbar_wait(bar(BAR_PFULL + 1), (tc[1] + j - 1) & 1, abort_word, a.error, 6);
+                        ok = mbar_wait(bar(BAR_PFULL + 1), (tc[1] + j - 1) & 1, wc, 6);
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(1, sp, j - 1 == 0);
@@ -369,11 +406,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         if (j == it.n[1]) tc_commit(bar(BAR_OFULL + 1));   // the item's last PV of tile 1
                     }
                     if (j < it.n[1]) {
+                        if (j == 0) {
+                            ok = mbar_wait(bar(BAR_QFULL + qbuf[1]), qpar[1], wc, 2);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
                         issue_qk(1, s);
-                        if (j == it.n[1] - 1) tc_commit(bar(BAR_QEMPTY + 1));
+                        if (j == it.n[1] - 1) tc_commit(bar(BAR_QEMPTY + qbuf[1]));
                     }
                     if (j < it.n[0]) {
-                        ok = mbar_wait(bar(BAR_PFULL + 0), (tc[0] + j) & 1, abort_word, a.error, 8);
+                        ok = mbar_wait(bar(BAR_PFULL + 0), (tc[0] + j) & 1, wc, 8);
                         if (!ok) break;
                         tc_fence_after();
                         // (the softmax warps read O of the previous item before they arrive on this P barrier,
@@ -384,6 +426,90 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     }
                 }
                 gk += nkv; tc[0] += it.n[0]; tc[1] += it.n[1];
+            }
+        }
+    } else if (FUSED && warp >= 10) {
+        // =============================== Q warps (fused): RMSNorm(1+w) + RoPE of the raw tile, in place ===============================
+        // 16 lanes share a row (8 elements = 16 bytes each), two rows per warp instruction, four per pass of the two
+        // warps.  A lane always owns the same 8 head dims, hence the same four rotary pairs and norm weights.
+        const uint32_t qt = tid - 320;                      // 0..63
+        const uint32_t c = qt & 15, rsub = qt >> 4;         // 16-byte chunk of the row, row within a pass
+        float wq[8];
+        if (a.norm_w) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) wq[e] = 1.0f + __uint_as_float(((uint32_t)a.norm_w[c * 8 + e]) << 16);
+        }
+        bool ok = true;
+        uint32_t tq = 0;
+        constexpr int kBatch = 4;                           // rows a thread has in flight
+        for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
+            const uint32_t w = item_of_round(rnd);
+            if (w >= total_items) continue;
+            const Item it = get_item(w);
+            for (int q = 0; q < 2 && ok; ++q) {
+                if (!it.n[q]) continue;
+                const uint32_t buf = tq % NQB, par = (tq / NQB) & 1;
+                ++tq;
+                const uint32_t row_base = it.q0 + q * kPM;   // position of the tile's first row (prefill starts at position 0)
+                // the table rows of the first batch are requested before the wait: they do not depend on the tile
+                float4 tab[kBatch][2];
+                auto load_tab = [&](uint32_t pass0) {
+#pragma unroll
+                    for (int u = 0; u < kBatch; ++u) {
+                        const uint32_t pos = min(row_base + (pass0 + u) * 4 + rsub, a.T - 1);
+                        const float4 *tp = reinterpret_cast<const float4 *>(a.cs_table + (size_t)pos * 64 + c * 4);
+                        tab[u][0] = __ldg(tp);
+                        tab[u][1] = __ldg(tp + 1);
+                    }
+                };
+                load_tab(0);
+                ok = mbar_wait(bar(BAR_QRAW + buf), par, wc, 7);
+                if (!ok) break;
+                unsigned char *tile = smem + kSmemQ + buf * kTileBytes;
+                for (uint32_t pass0 = 0; pass0 < 32; pass0 += kBatch) {
+                    uint4 raw[kBatch];
+                    uint32_t off[kBatch];
+#pragma unroll
+                    for (int u = 0; u < kBatch; ++u) {
+                        const uint32_t r = (pass0 + u) * 4 + rsub;
+                        off[u] = (c >> 3) * kSlabBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+                        raw[u] = *reinterpret_cast<const uint4 *>(tile + off[u]);
+                    }
+                    float4 cur[kBatch][2];
+#pragma unroll
+                    for (int u = 0; u < kBatch; ++u) { cur[u][0] = tab[u][0]; cur[u][1] = tab[u][1]; }
+                    if (pass0 + kBatch < 32) load_tab(pass0 + kBatch);   // next batch's table rows travel under this batch's math
+#pragma unroll
+                    for (int u = 0; u < kBatch; ++u) {
+                        float v[8];
+                        const T *e = reinterpret_cast<const T *>(&raw[u]);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) v[k] = to_f32<T>(e[k]);
+                        if (a.norm_w) {
+                            float ssq = 0.f;
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) ssq += v[k] * v[k];
+#pragma unroll
+                            for (int o = 8; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+                            const float rms = 1.0f / sqrtf(ssq / (float)kPD + a.eps);
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) v[k] = v[k] * rms * wq[k];
+                        }
+                        const float cs[4] = {cur[u][0].x, cur[u][0].z, cur[u][1].x, cur[u][1].z};
+                        const float sn[4] = {cur[u][0].y, cur[u][0].w, cur[u][1].y, cur[u][1].w};
+                        uint4 o4;
+                        uint32_t *ow = reinterpret_cast<uint32_t *>(&o4);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float x = v[2 * k], y = v[2 * k + 1];
+                            ow[k] = pack16<T>(x * cs[k] - y * sn[k], y * cs[k] + x * sn[k]);
+                        }
+                        *reinterpret_cast<uint4 *>(tile + off[u]) = o4;
+                    }
+                }
+                // generic-proxy writes to shared memory -> visible to the tensor core's (async) proxy, then signal
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(bar(BAR_QFULL + buf));
             }
         }
     } else {
@@ -403,7 +529,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!nq) continue;
         float m_ref = -INFINITY, l_sum = 0.f;
         for (uint32_t j = 0; j < nq && ok; ++j) {
-            ok = mbar_wait(bar(BAR_SFULL + q), (c0 + j) & 1, abort_word, a.error, 9);
+            ok = mbar_wait(bar(BAR_SFULL + q), (c0 + j) & 1, wc, 9);
             if (!ok) break;
             tc_fence_after();
             // one tile of the online softmax; the diagonal tile (the last one) is a second instantiation
@@ -519,16 +645,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             else tile_body(std::false_type{});
         }
         // ---- epilogue: O / l -> global ----
-        if (nq && ok) ok = mbar_wait(bar(BAR_OFULL + q), oc & 1, abort_word, a.error, 11);
+        if (nq && ok) ok = mbar_wait(bar(BAR_OFULL + q), oc & 1, wc, 11);
         if (nq && ok) {
             tc_fence_after();
             const float inv = 1.0f / l_sum;
             T *dst = reinterpret_cast<T *>(a.out) + (((size_t)b * a.T + row) * a.nh + h) * kPD;
+            // fused: the gate half of the row's projection (fused_split_qknorm_kvstore.wgsl:122-135) scales the output
+            const T *gate = (FUSED && a.has_gate && row < a.T)
+                                ? reinterpret_cast<const T *>(a.q_src) + (((size_t)b * a.T + row) * a.nh + h) * a.qrow + kPD : nullptr;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t v[32];
                 tmem_ld32(t_o + c * 32, v);
                 tmem_wait_ld();
+                if (FUSED && gate) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        const uint4 g4 = *reinterpret_cast<const uint4 *>(gate + c * 32 + i);
+                        const T *ge = reinterpret_cast<const T *>(&g4);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            v[i + k] = __float_as_uint(__uint_as_float(v[i + k]) * sigmoidf_ref(to_f32<T>(ge[k])));
+                    }
+                }
                 if (row < a.T) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -594,75 +733,103 @@ static bool make_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *ba
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Status word of the bounded waits (0 = ok).  A device-resident global, so nothing is allocated for it.
-static __device__ int g_prefill_error_word;
-static int *g_prefill_error[64] = {};   // its device address, per device
-
-int launch_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_q, const shady_kv_cache *cache, void *d_out) {
-    SHADY_REQUIRE(ctx, p && d_q && cache && d_out, SHADY_ERR_BAD_ARG, "attn_prefill: null argument");
-    SHADY_REQUIRE(ctx, p->head_dim == 128, SHADY_ERR_UNSUPPORTED, "attn_prefill: head_dim must be 128");
-    SHADY_REQUIRE(ctx, p->dtype == SHADY_BF16 || p->dtype == SHADY_F16, SHADY_ERR_UNSUPPORTED, "attn_prefill: dtype must be bf16 or f16");
-    SHADY_REQUIRE(ctx, cache->dtype == p->dtype, SHADY_ERR_UNSUPPORTED, "attn_prefill: cache dtype must equal the Q dtype");
+// What the two entry points share: argument checks, tensor maps, the launch.  q_base/qrow describe where Q tiles
+// are fetched from: [B][T][nh][qrow] elements with the Q half in the first 128 of every head's qrow elements.
+struct FusedQ {
+    const float2 *cs_table;
+    const uint16_t *norm_w;
+    uint32_t has_gate;
+    float eps;
+};
+static int launch_prefill_impl(shady_ctx *ctx, const char *who, const shady_prefill_params *p, const void *d_q, uint32_t qrow,
+                               const shady_kv_cache *cache, void *d_out, const FusedQ *fq) {
+    const std::string w(who);
+    SHADY_REQUIRE(ctx, p && d_q && cache && d_out, SHADY_ERR_BAD_ARG, w + ": null argument");
+    SHADY_REQUIRE(ctx, p->head_dim == 128, SHADY_ERR_UNSUPPORTED, w + ": head_dim must be 128");
+    SHADY_REQUIRE(ctx, p->dtype == SHADY_BF16 || p->dtype == SHADY_F16, SHADY_ERR_UNSUPPORTED, w + ": dtype must be bf16 or f16");
+    SHADY_REQUIRE(ctx, cache->dtype == p->dtype, SHADY_ERR_UNSUPPORTED, w + ": cache dtype must equal the Q dtype");
     SHADY_REQUIRE(ctx, p->num_seqs && p->seq_len && p->num_kv_heads && p->num_q_heads % p->num_kv_heads == 0, SHADY_ERR_BAD_ARG,
-                  "attn_prefill: bad shape");
+                  w + ": bad shape");
     SHADY_REQUIRE(ctx, cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs && !cache->d_page_table, SHADY_ERR_UNSUPPORTED,
-                  "attn_prefill: needs base + seq_stride cache addressing (TMA tensor maps), not pointer arrays or pages");
+                  w + ": needs base + seq_stride cache addressing (TMA tensor maps), not pointer arrays or pages");
     SHADY_REQUIRE(ctx, p->num_seqs == 1 || cache->seq_stride >= (uint64_t)p->seq_len * p->num_kv_heads * 128, SHADY_ERR_BAD_ARG,
-                  "attn_prefill: seq_stride smaller than one sequence");
+                  w + ": seq_stride smaller than one sequence");
     SHADY_REQUIRE(ctx, ((uintptr_t)d_q | (uintptr_t)cache->d_k_base | (uintptr_t)cache->d_v_base | (uintptr_t)d_out) % 16 == 0 &&
                            (cache->seq_stride * 2) % 16 == 0,
-                  SHADY_ERR_BAD_ARG, "attn_prefill: buffers must be 16-byte aligned");
-    SHADY_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, SHADY_ERR_UNSUPPORTED, "attn_prefill: device ordinal out of range");
+                  SHADY_ERR_BAD_ARG, w + ": buffers must be 16-byte aligned");
+    if (const int st = pending_timeout(ctx, who)) return st;
     const uint32_t B = p->num_seqs, T = p->seq_len, nh = p->num_q_heads, nkv = p->num_kv_heads;
     const CUtensorMapDataType dt = p->dtype == SHADY_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap mq, mk, mv;
     const uint64_t seq_stride_b = (B == 1 ? (uint64_t)T * nkv * 128 : cache->seq_stride) * 2;
-    const bool maps_ok = make_map_4d(&mq, dt, d_q, 128, nh, T, B, 128 * 2, (uint64_t)nh * 128 * 2, (uint64_t)T * nh * 128 * 2) &&
+    // the Q map sees 128 of the qrow elements of every head: the gate half (if any) is skipped by the head stride
+    const bool maps_ok = make_map_4d(&mq, dt, d_q, 128, nh, T, B, (uint64_t)qrow * 2, (uint64_t)nh * qrow * 2, (uint64_t)T * nh * qrow * 2) &&
                          make_map_4d(&mk, dt, cache->d_k_base, 128, nkv, T, B, 128 * 2, (uint64_t)nkv * 128 * 2, seq_stride_b) &&
                          make_map_4d(&mv, dt, cache->d_v_base, 128, nkv, T, B, 128 * 2, (uint64_t)nkv * 128 * 2, seq_stride_b);
-    SHADY_REQUIRE(ctx, maps_ok, SHADY_ERR_CUDA, "attn_prefill: cuTensorMapEncodeTiled failed");
-    if (!g_prefill_error[ctx->device]) {
-        int *w = nullptr;
-        SHADY_CUDA_OK(ctx, cudaGetSymbolAddress(reinterpret_cast<void **>(&w), g_prefill_error_word));
-        SHADY_CUDA_OK(ctx, cudaMemsetAsync(w, 0, sizeof(int), ctx->stream));
-        g_prefill_error[ctx->device] = w;
-    }
+    SHADY_REQUIRE(ctx, maps_ok, SHADY_ERR_CUDA, w + ": cuTensorMapEncodeTiled failed");
     PrefillArgs a{};
-    a.out = d_out; a.error = g_prefill_error[ctx->device];
+    a.out = d_out; a.status = status_ref(ctx); a.wait_mbar = ctx->wait_mbar;
     a.B = B; a.T = T; a.nh = nh; a.nkv = nkv; a.G = nh / nkv;
     a.m_tiles = (T + 255) / 256;
     a.scale_log2 = (1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
+    a.q_src = d_q; a.qrow = qrow;
+    if (fq) { a.cs_table = fq->cs_table; a.norm_w = fq->norm_w; a.has_gate = fq->has_gate; a.eps = fq->eps; }
     const unsigned long long total_items = (unsigned long long)a.m_tiles * B * nh;
-    SHADY_REQUIRE(ctx, total_items <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "attn_prefill: too many tiles for one launch");
-    const unsigned long long blocks = total_items < (unsigned long long)ctx->num_sms ? total_items : (unsigned long long)ctx->num_sms;   // persistent: one CTA per SM
-    SHADY_REQUIRE(ctx, blocks <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "attn_prefill: too many tiles for one launch");
+    SHADY_REQUIRE(ctx, total_items <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, w + ": too many tiles for one launch");
+    const unsigned blocks = (unsigned)(total_items < (unsigned long long)ctx->num_sms ? total_items : (unsigned long long)ctx->num_sms);   // persistent: one CTA per SM
     static thread_local int configured_dev = -1;
     if (configured_dev != ctx->device) {
-        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
-        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem(2)));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill_kernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem(2)));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem(3)));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem(3)));
         configured_dev = ctx->device;
     }
-    if (p->dtype == SHADY_BF16) {
-        prefill_kernel<__nv_bfloat16><<<(unsigned)blocks, 320, kPrefillSmem, ctx->stream>>>(mq, mk, mv, a);
+    const bool bf = p->dtype == SHADY_BF16;
+    if (fq) {
+        constexpr unsigned threads = 320 + 32 * kQWarps;
+        if (bf) prefill_kernel<__nv_bfloat16, true><<<blocks, threads, prefill_smem(3), ctx->stream>>>(mq, mk, mv, a);
+        else prefill_kernel<__half, true><<<blocks, threads, prefill_smem(3), ctx->stream>>>(mq, mk, mv, a);
     } else {
-        prefill_kernel<__half><<<(unsigned)blocks, 320, kPrefillSmem, ctx->stream>>>(mq, mk, mv, a);
+        if (bf) prefill_kernel<__nv_bfloat16, false><<<blocks, 320, prefill_smem(2), ctx->stream>>>(mq, mk, mv, a);
+        else prefill_kernel<__half, false><<<blocks, 320, prefill_smem(2), ctx->stream>>>(mq, mk, mv, a);
     }
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
 }
 
-// Reads (and clears) the bounded-wait status of the prefill kernel; blocks until the stream is idle.
-int prefill_status(shady_ctx *ctx, int *code) {
-    *code = 0;
-    if (ctx->device < 0 || ctx->device >= 64 || !g_prefill_error[ctx->device]) return SHADY_OK;
-    SHADY_CUDA_OK(ctx, cudaMemcpyAsync(code, g_prefill_error[ctx->device], sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
-    SHADY_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
-    if (*code) {
-        SHADY_CUDA_OK(ctx, cudaMemsetAsync(g_prefill_error[ctx->device], 0, sizeof(int), ctx->stream));
-        return fail(ctx, SHADY_ERR_TIMEOUT, "attn_prefill: a device-side wait expired (code " + std::to_string(*code) + ")");
-    }
-    return SHADY_OK;
+int launch_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_q, const shady_kv_cache *cache, void *d_out) {
+    return launch_prefill_impl(ctx, "attn_prefill", p, d_q, 128, cache, d_out, nullptr);
+}
+
+// K/V half of the append (norm + RoPE of K, cache rows of K and V) plus the cos/sin table of positions [0, T)
+// (append.cu); Q is left to the attention kernel.
+int launch_append_kv_table(shady_ctx *ctx, const shady_append_params *ap, const void *d_k_proj, const void *d_v_proj,
+                           const shady_kv_cache *cache, const uint16_t *d_qk_norm_bf16, float2 *d_cs_table);
+
+size_t prefill_workspace_bytes(const shady_prefill_params *p) { return (size_t)p->seq_len * 64 * sizeof(float2); }
+
+// The whole prefill step from the projections: one pass writes K (normed, rotated) and V into rows [0, T) of every
+// sequence's cache and the cos/sin table; the attention kernel then takes Q raw, norms and rotates it tile by tile in
+// shared memory and applies the gate in its epilogue.
+int launch_prefill_append(shady_ctx *ctx, const shady_append_params *ap, const shady_prefill_params *p, const void *d_q_proj_full,
+                          const void *d_k_proj, const void *d_v_proj, const uint16_t *d_qk_norm_bf16, const shady_kv_cache *cache,
+                          void *d_out, void *d_ws, size_t ws_bytes) {
+    SHADY_REQUIRE(ctx, ap && p && d_q_proj_full && d_k_proj && d_v_proj && cache && d_out, SHADY_ERR_BAD_ARG, "attn_prefill_append: null argument");
+    SHADY_REQUIRE(ctx, ap->num_heads == p->num_q_heads && ap->num_kv_heads == p->num_kv_heads && ap->head_dim == p->head_dim &&
+                           ap->num_seqs == p->num_seqs && ap->tokens_per_seq == p->seq_len,
+                  SHADY_ERR_BAD_ARG, "attn_prefill_append: append and prefill parameters disagree");
+    SHADY_REQUIRE(ctx, ap->in_dtype == p->dtype, SHADY_ERR_UNSUPPORTED, "attn_prefill_append: the projections must have the cache dtype (bf16 or f16)");
+    SHADY_REQUIRE(ctx, ap->interleaved && ap->rotary_dim <= p->head_dim && (ap->rotary_dim % 2) == 0 &&
+                           ap->s1_limit == ap->rotary_dim / 2 && ap->s2_limit == ap->rotary_dim / 2,
+                  SHADY_ERR_UNSUPPORTED, "attn_prefill_append: interleaved RoPE with one position per token only");
+    SHADY_REQUIRE(ctx, d_ws && ws_bytes >= prefill_workspace_bytes(p) && ((uintptr_t)d_ws % 16) == 0, SHADY_ERR_WORKSPACE,
+                  "attn_prefill_append: workspace missing, too small or not 16-byte aligned");
+    float2 *table = reinterpret_cast<float2 *>(d_ws);
+    if (const int st = launch_append_kv_table(ctx, ap, d_k_proj, d_v_proj, cache, d_qk_norm_bf16, table)) return st;
+    const FusedQ fq{table, d_qk_norm_bf16, ap->has_gate, ap->eps};
+    return launch_prefill_impl(ctx, "attn_prefill_append", p, d_q_proj_full, ap->has_gate ? 256u : 128u, cache, d_out, &fq);
 }
 
 }  // namespace shady

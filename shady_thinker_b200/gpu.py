@@ -86,6 +86,10 @@ class GpuContext:
     def _check(self, st: int) -> None:
         check(self.handle, st)
 
+    def set_wait_limits(self, grid_polls: int = 0, peer_polls: int = 0, mbarrier_polls: int = 0) -> None:
+        """Iteration limits of the bounded device-side waits of later launches (0 keeps a limit)."""
+        self._check(self._L.shady_ctx_set_wait_limits(self.handle, grid_polls, peer_polls, mbarrier_polls))
+
     # -- buffers (gpu.rs:80-124, 245-280) -------------------------------------------------------
     def create_storage_buffer(self, label: str, size: int) -> Buffer:
         p = C.c_void_p()

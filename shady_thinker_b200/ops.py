@@ -173,6 +173,31 @@ def attn_prefill(gpu: GpuContext, *, q, cache: KvCacheView, out, head_dim: int, 
     gpu._check(gpu._L.shady_attn_prefill(gpu.handle, C.byref(p), _addr(q), C.byref(c), _addr(out)))
 
 
+def prefill_workspace_size(*, head_dim: int, num_kv_heads: int, num_q_heads: int, num_seqs: int, seq_len: int,
+                           dtype: int = BF16) -> int:
+    p = PrefillParams(head_dim, num_kv_heads, num_q_heads, num_seqs, seq_len, dtype)
+    n = C.c_size_t()
+    st = _lib.load().shady_prefill_workspace_size(C.byref(p), C.byref(n))
+    if st != _lib.OK:
+        raise _lib.ShadyError(st, "prefill_workspace_size")
+    return n.value
+
+
+def attn_prefill_append(gpu: GpuContext, *, q_proj_full, k_proj, v_proj, cache: KvCacheView, out, workspace,
+                        workspace_bytes: int, num_heads: int, num_kv_heads: int, head_dim: int, num_seqs: int,
+                        seq_len: int, rope_theta: float, rotary_dim: int, dtype: int = BF16, eps: float = 1e-6,
+                        qk_norm_bf16=None, has_gate: bool = False) -> None:
+    """The prefill step from the projections: K/V rows [0, seq_len) of every cache written (K normed + rotated),
+    Q normed + rotated inside the attention kernel, causal attention, sigmoid gate."""
+    ap = AppendParams(num_heads, num_kv_heads, head_dim, eps, rope_theta, rotary_dim, rotary_dim // 2, rotary_dim // 2,
+                      1, num_seqs, seq_len, dtype, dtype, int(has_gate), 0, 0)
+    p = PrefillParams(head_dim, num_kv_heads, num_heads, num_seqs, seq_len, dtype)
+    c = cache.c_struct()
+    gpu._check(gpu._L.shady_attn_prefill_append(gpu.handle, C.byref(ap), C.byref(p), _addr(q_proj_full), _addr(k_proj),
+                                                _addr(v_proj), _addr(qk_norm_bf16) or None, C.byref(c), _addr(out),
+                                                _addr(workspace), workspace_bytes))
+
+
 def sigmoid_mul(gpu: GpuContext, x, gate, n: int) -> None:
     gpu._check(gpu._L.shady_sigmoid_mul(gpu.handle, _addr(x), _addr(gate), n))
 

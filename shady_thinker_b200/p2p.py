@@ -15,7 +15,11 @@ from .gpu import Buffer, GpuContext, _addr
 
 
 class ShardCombiner:
-    def __init__(self, gpu: GpuContext, *, rank: int, world: int, num_heads: int, head_dim: int, group=None):
+    def __init__(self, gpu: GpuContext, *, rank: int, world: int, num_heads: int, head_dim: int, group=None,
+                 loopback: bool = False):
+        """``loopback=True`` builds a combiner of ``world`` ranks inside ONE process on one GPU: every entry of the
+        peer table is this rank's own buffer and no other rank exists, so the flags of the other ranks never
+        arrive.  It exists to exercise the bounded flag wait and its status path without a second process."""
         self.gpu, self.rank, self.world, self.nh, self.hd = gpu, rank, world, num_heads, head_dim
         L = gpu._L
         n = C.c_size_t()
@@ -29,7 +33,10 @@ class ShardCombiner:
         self._opened: list[int] = []
         ptrs = [0] * world
         ptrs[rank] = self.buf.ptr
-        if world > 1:
+        self._dist = world > 1 and not loopback
+        if loopback:
+            ptrs = [self.buf.ptr] * world
+        if self._dist:
             import torch.distributed as dist
             h = C.create_string_buffer(64)
             gpu._check(L.shady_ipc_export(gpu.handle, C.c_void_p(self.buf.ptr), h))
@@ -50,19 +57,19 @@ class ShardCombiner:
     def combine(self, records, out, out_dtype: int = _lib.F32, gate=None) -> None:
         """records: this rank's [nh][hd+2] f32 (``ops.attn_decode_shard``); out: [nh][hd].  Every rank must call
         this the same number of times."""
-        self.epoch += 1
         g = self.gpu
-        g._check(g._L.shady_attn_combine_p2p(g.handle, self.world, self.rank, self.nh, self.hd, self.epoch,
+        g._check(g._L.shady_attn_combine_p2p(g.handle, self.world, self.rank, self.nh, self.hd, self.epoch + 1,
                                              C.c_void_p(self.table.ptr), _addr(records), _addr(out), out_dtype,
                                              _addr(gate) or None))
+        self.epoch += 1      # only a call that was launched counts: a refused one must not run ahead of the peers
 
     def decode_and_combine(self, *, q, cache, seq_lens, seq_len_host: int, records, out, num_kv_heads: int,
                            q_dtype: int = _lib.F32, out_dtype: int = _lib.F32, gate=None, workspace=None,
                            workspace_bytes: int = 0) -> None:
-        """The whole sharded step in two launches (``shady_attn_decode_shard_p2p``): decode over this rank's rows,
-        then one kernel that merges the rank's records, exchanges the result over NVLink and merges across ranks.
-        Do not mix with :meth:`combine` on the same combiner (the exchange buffer is laid out differently)."""
-        self.epoch += 1
+        """The whole sharded step in one cooperative launch (``shady_attn_decode_shard_p2p``): decode over this
+        rank's rows, grid barrier, merge of the rank's records, exchange over NVLink, merge across ranks (a shard
+        of a single span keeps two launches).  Do not mix with :meth:`combine` on the same combiner (the exchange
+        buffer is laid out differently)."""
         g = self.gpu
         key = (id(cache), _addr(q), _addr(seq_lens), seq_len_host, _addr(records), _addr(out), _addr(gate), _addr(workspace))
         call = self._calls.get(key)
@@ -77,16 +84,24 @@ class ShardCombiner:
             if len(self._calls) >= 64:
                 self._calls.clear()
             call = self._calls[key] = (args, (p, c, hl, cache))
-        call[0][8] = self.epoch
+        call[0][8] = self.epoch + 1
         st = g._L.shady_attn_decode_shard_p2p(*call[0])
         if st:
             g._check(st)
+        self.epoch += 1      # only a call that was launched counts
 
     def close(self, group=None) -> None:
-        if self.world > 1:
+        if self._dist:
             import torch.distributed as dist
             self.gpu.synchronize()
             dist.barrier(group=group)                              # nobody still writes into a peer's buffer
         for p in self._opened:
             self.gpu._L.shady_ipc_close(self.gpu.handle, C.c_void_p(p))
         self._opened.clear()
+        if self._dist:
+            import torch.distributed as dist
+            dist.barrier(group=group)                              # every mapping of this buffer is closed
+        for b in (self.table, self.buf):
+            if b is not None:
+                self.gpu.destroy_buffer(b)
+        self.table = self.buf = None

@@ -62,3 +62,71 @@ def test_model_config_rotary_dim():
     assert ModelConfig(16, 2).rotary_dim == 32          # 128 * 0.25 (weights.rs defaults)
     assert ModelConfig(16, 2, head_dim=256).rotary_dim == 64
     assert ModelConfig(16, 2, partial_rotary_factor=1.0).rotary_dim == 128
+
+
+# ---- the Rust binding as files: `rust/shady-attn-sys` must say what the header says -------------------------
+
+def _rust_lib():
+    return open(os.path.join(ROOT, "rust", "shady-attn-sys", "src", "lib.rs")).read()
+
+
+def _header_prototypes():
+    """name -> number of parameters, from include/shady_attn.h."""
+    src = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "shady_attn.h")).read(), flags=re.S)
+    out = {}
+    for name, args in re.findall(r"\b(shady_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", src, flags=re.S):
+        out[name] = len([a for a in args.split(",") if a.strip() and a.strip() != "void"])
+    return out
+
+
+def _header_structs():
+    src = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "shady_attn.h")).read(), flags=re.S)
+    out = {}
+    for body, name in re.findall(r"typedef struct\s*\{(.*?)\}\s*(shady_\w+)\s*;", src, flags=re.S):
+        out[name] = [re.search(r"(\w+)\s*(?:\[\d+\])?$", f.strip()).group(1) for f in body.split(";") if f.strip()]
+    return out
+
+
+def test_rust_extern_block_declares_every_export_with_the_same_arity():
+    block = re.search(r'extern "C" \{(.*?)\n\}', _rust_lib(), flags=re.S).group(1)
+    rust = {}
+    for name, args in re.findall(r"pub fn (shady_\w+)\((.*?)\) ->", block):
+        rust[name] = len([a for a in args.split(",") if a.strip()])
+    assert rust == _header_prototypes()
+    from shady_thinker_b200 import _lib
+    assert sorted(rust) == sorted(_lib.EXPORTS)
+
+
+def test_rust_repr_c_structs_keep_the_header_field_order():
+    from shady_thinker_b200 import _lib
+    lib_rs = _rust_lib()
+    ctypes_of = {"shady_kv_cache": _lib.KvCache, "shady_append_params": _lib.AppendParams,
+                 "shady_decode_params": _lib.DecodeParams, "shady_prefill_params": _lib.PrefillParams}
+    structs = _header_structs()
+    assert set(ctypes_of) <= set(structs)
+    for cname, fields in structs.items():
+        rname = "".join(w.capitalize() for w in cname.split("_"))
+        body = re.search(r"#\[repr\(C\)\]\s*#\[derive\(Clone, Copy\)\]\s*pub struct %s \{(.*?)\}" % rname, lib_rs, flags=re.S)
+        assert body, f"{rname} missing or not #[repr(C)]"
+        assert re.findall(r"pub (\w+):", body.group(1)) == fields, cname
+        if cname in ctypes_of:
+            assert [f[0] for f in ctypes_of[cname]._fields_] == fields, cname
+
+
+def test_rust_bindings_are_what_the_generator_writes():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("gen_bindings", os.path.join(ROOT, "rust", "shady-attn-sys", "gen_bindings.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    assert _rust_lib() == gen.generate(), "run python rust/shady-attn-sys/gen_bindings.py after changing the header"
+
+
+def test_rust_crate_files_exist_and_build_script_targets_sm_100a():
+    crate = os.path.join(ROOT, "rust", "shady-attn-sys")
+    for f in ("Cargo.toml", "build.rs", os.path.join("src", "lib.rs")):
+        assert os.path.exists(os.path.join(crate, f)), f
+    b = open(os.path.join(crate, "build.rs")).read()
+    assert "arch=compute_100a,code=sm_100a" in b
+    from shady_thinker_b200 import build
+    for src in build.SOURCES:
+        assert f'"{src}"' in b, f"build.rs does not compile {src}"

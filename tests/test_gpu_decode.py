@@ -340,32 +340,51 @@ def test_fused_append_decode_equals_the_two_calls(gpu_ctx, oracle, dt, in_dt, no
 
 
 @pytest.mark.parametrize("dt,nh,nkv,hd,lens", [(BF16, 16, 2, 256, [40000]), (F16, 32, 8, 128, [30000, 100, 5000, 1])])
-def test_merge_by_the_decode_grid_equals_the_second_launch(gpu_ctx, oracle, monkeypatch, dt, nh, nkv, hd, lens):
+def test_merge_by_the_decode_grid_equals_the_second_launch(oracle, monkeypatch, dt, nh, nkv, hd, lens):
     """Sequences cut into more spans than their last CTA merges alone: by default the decode grid meets at a barrier
-    and merges the records itself (one cooperative launch); SHADY_DECODE_GRID_MERGE=0 keeps the second launch.  Both
-    must give the reference's merge (gqa_reduce.wgsl:33-64) of the same records, gate included, launch after launch
-    (the barrier words zero themselves)."""
+    and merges the records itself (one cooperative launch; the blocks of a single long sequence are also interleaved
+    over all warps, SHADY_DECODE_INTERLEAVE=0 keeps fixed spans); SHADY_DECODE_GRID_MERGE=0 keeps the second launch.
+    All must give the reference's merge (gqa_reduce.wgsl:33-64) of the same rows, gate included, launch after launch
+    (the barrier words zero themselves).  The knobs are read when a context is created, hence one context each."""
+    from shady_thinker_b200.gpu import GpuContext
     S = len(lens)
     q = rounded(oracle, oracle.randn((S, nh, hd), 71, 1), dt)
     gate = torch.from_numpy(oracle.randn((S, nh, hd), 71, 2)).cuda()
     ks = [rounded(oracle, oracle.randn((L, nkv, hd), 71, 10 + i), dt) for i, L in enumerate(lens)]
     vs = [rounded(oracle, oracle.randn((L, nkv, hd), 71, 50 + i), dt) for i, L in enumerate(lens)]
     cache = RaggedCache(ks, vs, dt)
-    n0 = gpu_ctx.launch_count
-    outs = [run_decode(gpu_ctx, q, cache.view, lens, nh=nh, nkv=nkv, hd=hd, num_splits=0, q_dt=dt, out_dt=F32,
-                       want_lse=True, gate=gate) for _ in range(3)]
-    assert gpu_ctx.launch_count - n0 == 3            # one launch per decode
-    for o, l in outs[1:]:
-        np.testing.assert_array_equal(o, outs[0][0])
-        np.testing.assert_array_equal(l, outs[0][1])
+
+    def runs(ctx, n):
+        n0 = ctx.launch_count
+        outs = [run_decode(ctx, q, cache.view, lens, nh=nh, nkv=nkv, hd=hd, num_splits=0, q_dt=dt, out_dt=F32,
+                           want_lse=True, gate=gate) for _ in range(n)]
+        return outs, ctx.launch_count - n0
+
+    def same_bits(outs):
+        for o, l in outs[1:]:
+            np.testing.assert_array_equal(o, outs[0][0])
+            np.testing.assert_array_equal(l, outs[0][1])
+
+    with GpuContext(0, stream=0x1) as ctx:                       # defaults: a single long sequence is interleaved
+        ilv, launches = runs(ctx, 3)
+        assert launches == 3                                     # one launch per decode
+    same_bits(ilv)
+    monkeypatch.setenv("SHADY_DECODE_INTERLEAVE", "0")
+    with GpuContext(0, stream=0x1) as ctx:                       # fixed spans
+        outs, launches = runs(ctx, 3)
+        assert launches == 3
+    same_bits(outs)
     monkeypatch.setenv("SHADY_DECODE_GRID_MERGE", "0")
-    n0 = gpu_ctx.launch_count
-    two, two_lse = run_decode(gpu_ctx, q, cache.view, lens, nh=nh, nkv=nkv, hd=hd, num_splits=0, q_dt=dt, out_dt=F32,
-                              want_lse=True, gate=gate)
-    assert gpu_ctx.launch_count - n0 == 2
+    with GpuContext(0, stream=0x1) as ctx:
+        (two_pair,), launches = runs(ctx, 1)
+        assert launches == 2
+    two, two_lse = two_pair
     one, one_lse = outs[0]
     assert np.abs(one - two).max() <= 2e-6 * max(1.0, np.abs(two).max())
     assert np.abs(one_lse - two_lse).max() <= 1e-5
+    # interleaved, a warp sees other rows than in its span: its running maximum, and with it the 16-bit rounding of P, differs
+    assert np.abs(ilv[0][0] - two).max() <= 5e-3 * np.abs(two).max()
+    assert np.abs(ilv[0][1] - two_lse).max() <= 1e-3
     sig = 1.0 / (1.0 + np.exp(-to_host(gate).astype(np.float64)))
     for i, L in enumerate(lens):
         want = oracle.attention_f64(q[i], ks[i], vs[i], L, threads=8) * sig[i]

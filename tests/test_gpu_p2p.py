@@ -32,13 +32,30 @@ def test_world_of_one_is_a_copy_with_gate(gpu_ctx, oracle):
     comb.close()
 
 
-@pytest.mark.parametrize("grid_merge", ["1", "0"])
+@pytest.fixture()
+def knob_ctx(monkeypatch):
+    """A context of its own per test: the SHADY_DECODE_* knobs are read once, when a context is created."""
+    made = []
+
+    def make(**env):
+        from shady_thinker_b200.gpu import GpuContext
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        made.append(GpuContext(0, stream=0x1))
+        return made[-1]
+    yield make
+    for c in made:
+        c.close()
+
+
+@pytest.mark.parametrize("grid_merge,interleave", [("1", "1"), ("1", "0"), ("0", "1")])
 @pytest.mark.parametrize("L", [100, 20000])
-def test_world_of_one_fused_step_equals_plain_decode(gpu_ctx, oracle, monkeypatch, L, grid_merge):
+def test_world_of_one_fused_step_equals_plain_decode(knob_ctx, oracle, L, grid_merge, interleave):
     """decode + (merge, exchange, merge) with a world of one gives what shady_attn_decode gives: a single span (record
-    written directly) and many spans (records merged before the exchange), both as one cooperative launch (merge and
-    exchange in the decode kernel's tail, the default) and as two launches (SHADY_DECODE_GRID_MERGE=0)."""
-    monkeypatch.setenv("SHADY_DECODE_GRID_MERGE", grid_merge)
+    written directly) and many spans (records merged before the exchange), as one cooperative launch (merge and
+    exchange in the decode kernel's tail; blocks interleaved over the warps, the default, or in fixed spans) and as two
+    launches (SHADY_DECODE_GRID_MERGE=0)."""
+    gpu_ctx = knob_ctx(SHADY_DECODE_GRID_MERGE=grid_merge, SHADY_DECODE_INTERLEAVE=interleave)
     from _util import rounded, run_decode
     from shady_thinker_b200 import ops
     from shady_thinker_b200.p2p import ShardCombiner

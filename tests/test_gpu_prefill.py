@@ -114,3 +114,97 @@ def test_cfg3_full_size_sampled_rows_and_linearity_in_v(gpu_ctx, oracle):
                 got = out[b, r, h].float().cpu().numpy()
                 worst = max(worst, float(np.abs(got - ref).max() / np.abs(ref).max()))
     assert worst <= RTOL_16, worst
+
+
+# ---- the prefill step from the projections: K/V append + Q norm/RoPE inside the attention kernel + gate ----------
+
+def _fused_case(gpu, oracle, B, T, nh, nkv, dt, seed, rd, norm, gate, cap=None):
+    hd = 128
+    cap = cap or T
+    qrow = 2 * hd if gate else hd
+    qf = rounded(oracle, oracle.randn((B, T, nh, qrow), seed, 1), dt)
+    kp = rounded(oracle, oracle.randn((B, T, nkv, hd), seed, 2), dt)
+    vp = rounded(oracle, oracle.randn((B, T, nkv, hd), seed, 3), dt)
+    w = oracle.bf16_bits(oracle.randn((2 * hd,), seed, 4) * np.float32(0.02)) if norm else None
+    d_kc = torch.full((B, cap, nkv, hd), float("nan"), dtype=TORCH_DT[dt], device="cuda")
+    d_vc = torch.full((B, cap, nkv, hd), float("nan"), dtype=TORCH_DT[dt], device="cuda")
+    d_out = torch.full((B, T, nh, hd), float("nan"), dtype=TORCH_DT[dt], device="cuda")
+    ws_n = ops.prefill_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_seqs=B, seq_len=T, dtype=dt)
+    ws = torch.empty(ws_n, dtype=torch.uint8, device="cuda")
+    ops.attn_prefill_append(gpu, q_proj_full=to_dev(qf, dt), k_proj=to_dev(kp, dt), v_proj=to_dev(vp, dt),
+                            cache=ops.KvCacheView(dt, d_kc, d_vc, cap * nkv * hd), out=d_out, workspace=ws,
+                            workspace_bytes=ws_n, num_heads=nh, num_kv_heads=nkv, head_dim=hd, num_seqs=B, seq_len=T,
+                            rope_theta=1e6, rotary_dim=rd, dtype=dt,
+                            qk_norm_bf16=torch.from_numpy(w.view(np.int16)).cuda() if norm else None, has_gate=gate)
+    gpu.synchronize()
+    out = to_host(d_out)
+    assert np.isfinite(out).all()
+    for b in range(B):
+        # the oracle's token loop: append token t (norm, RoPE, cache rows), rows rounded to the cache dtype
+        okc, ovc = np.zeros((T, nkv, hd), np.float32), np.zeros((T, nkv, hd), np.float32)
+        oq = np.zeros((T, nh, hd), np.float32)
+        og = np.zeros((T, nh, hd), np.float32)
+        for t in range(T):
+            full = qf[b, t].reshape(nh, 2, hd) if gate else np.stack([qf[b, t], np.zeros_like(qf[b, t])], 1)
+            oq[t], og[t], _ = oracle.fused_split_qknorm_kvstore(full, kp[b, t], vp[b, t], okc, ovc, t, rope_theta=1e6,
+                                                              rotary_dim=rd, qk_norm_bf16=w)
+        okc, oq = rounded(oracle, okc, dt), rounded(oracle, oq, dt)
+        got_k = to_host(d_kc[b, :T])
+        assert np.abs(got_k - okc).max() <= 2.0 ** (-7 if dt == BF16 else -10) * np.abs(okc).max()
+        np.testing.assert_array_equal(to_host(d_vc[b, :T]), vp[b])
+        ref = oracle.causal_prefill(oq, okc, ovc, f64=True)
+        if gate:
+            ref = ref / (1.0 + np.exp(-og.astype(np.float64)))
+        err = np.abs(out[b] - ref).max(axis=(1, 2)) / np.abs(ref).max(axis=(1, 2))
+        assert err.max() <= RTOL_16, (b, int(err.argmax()), float(err.max()))
+    if cap > T:      # rows past T were not touched
+        assert torch.isnan(d_kc[:, T:].float()).all()
+
+
+@pytest.mark.parametrize("rd,norm,gate", [(128, False, False), (32, True, True), (128, True, False), (64, False, True)])
+def test_prefill_from_the_projections_matches_the_token_loop(gpu_ctx, oracle, rd, norm, gate):
+    _fused_case(gpu_ctx, oracle, 2, 384, 8, 2, BF16, 51, rd, norm, gate)
+
+
+def test_prefill_from_the_projections_f16_ragged_and_many_items(gpu_ctx, oracle):
+    _fused_case(gpu_ctx, oracle, 1, 333, 4, 2, F16, 52, 32, True, True, cap=400)
+    # more items than SMs, so every CTA walks several and the three Q buffers rotate through their phases
+    _fused_case(gpu_ctx, oracle, 3, 1100, 16, 4, BF16, 53, 32, True, True)
+
+
+def test_prefill_from_the_projections_equals_the_two_calls(gpu_ctx, oracle):
+    """Same step as shady_kv_append_rope followed by shady_attn_prefill (no gate): the cache rows are identical and
+    the outputs agree to the rounding of the rotated Q."""
+    B, T, nh, nkv, hd, dt = 2, 640, 8, 2, 128, BF16
+    qf = to_dev(rounded(oracle, oracle.randn((B, T, nh, hd), 54, 1), dt), dt)
+    kp = to_dev(rounded(oracle, oracle.randn((B, T, nkv, hd), 54, 2), dt), dt)
+    vp = to_dev(rounded(oracle, oracle.randn((B, T, nkv, hd), 54, 3), dt), dt)
+    outs, caches = [], []
+    for fused in (False, True):
+        d_kc = torch.zeros((B, T, nkv, hd), dtype=torch.bfloat16, device="cuda")
+        d_vc = torch.zeros_like(d_kc)
+        d_out = torch.zeros((B, T, nh, hd), dtype=torch.bfloat16, device="cuda")
+        view = ops.KvCacheView(dt, d_kc, d_vc, T * nkv * hd)
+        if fused:
+            ws_n = ops.prefill_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_seqs=B, seq_len=T)
+            ws = torch.empty(ws_n, dtype=torch.uint8, device="cuda")
+            ops.attn_prefill_append(gpu_ctx, q_proj_full=qf, k_proj=kp, v_proj=vp, cache=view, out=d_out, workspace=ws,
+                                    workspace_bytes=ws_n, num_heads=nh, num_kv_heads=nkv, head_dim=hd, num_seqs=B,
+                                    seq_len=T, rope_theta=1e6, rotary_dim=hd)
+        else:
+            d_q = torch.zeros((B, T, nh, hd), dtype=torch.bfloat16, device="cuda")
+            ops.kv_append_rope(gpu_ctx, q_proj_full=qf, k_proj=kp.clone(), v_proj=vp, q_out=d_q, q_gate=None, cache=view,
+                               pos_start=torch.zeros(B, dtype=torch.int32).cuda(), num_heads=nh, num_kv_heads=nkv,
+                               head_dim=hd, rope_theta=1e6, rotary_dim=hd, num_seqs=B, tokens_per_seq=T, in_dtype=dt,
+                               q_dtype=dt, has_gate=False, write_k_back=False)
+            ops.attn_prefill(gpu_ctx, q=d_q, cache=view, out=d_out, head_dim=hd, num_kv_heads=nkv, num_q_heads=nh,
+                             num_seqs=B, seq_len=T, dtype=dt)
+        gpu_ctx.synchronize()
+        outs.append(to_host(d_out))
+        caches.append((to_host(d_kc), to_host(d_vc)))
+    np.testing.assert_array_equal(caches[0][0], caches[1][0])
+    np.testing.assert_array_equal(caches[0][1], caches[1][1])
+    # the two kernels may contract the rotation's multiply-adds differently: a Q element can land on the neighbouring
+    # bf16 value, which moves an output by a fraction of its own rounding step
+    assert rel_err(outs[1], outs[0]) <= 1e-2
+    assert (outs[0] == outs[1]).mean() > 0.9

@@ -11,7 +11,7 @@ import torch
 
 from _util import RTOL_16, RaggedCache, rel_err, rounded, run_decode, to_dev, to_host
 from shady_thinker_b200 import ops
-from shady_thinker_b200._lib import F16, F32, ShadyError
+from shady_thinker_b200._lib import BF16, F16, F32, ShadyError
 
 pytestmark = pytest.mark.gpu
 
@@ -47,6 +47,28 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point(gpu_ctx, oracle):
         # and both agree with the oracle
         for i, L in enumerate(lens):
             assert rel_err(got[i], oracle.attention_f64(q[i], ks[i], vs[i], L)) <= RTOL_16, (call, i)
+
+
+@pytest.mark.parametrize("dt,hd,nh,nkv,lens", [(BF16, 256, 16, 2, [40000]), (F16, 128, 8, 2, [30000, 100, 5000, 1])])
+def test_long_sequences_are_merged_by_the_grid_as_in_the_workspace_entry_point(gpu_ctx, oracle, dt, hd, nh, nkv, lens):
+    """A sequence cut into dozens of spans: both entry points plan the same launch (records merged by the whole
+    grid after its barrier, one long sequence interleaved over all warps), here with the scratch in the built-in
+    array; twice in a row, against the workspace form and the f64 oracle."""
+    S = len(lens)
+    q = rounded(oracle, oracle.randn((S, nh, hd), 303, 1), dt)
+    ks = [rounded(oracle, oracle.randn((L, nkv, hd), 303, 10 + i), dt) for i, L in enumerate(lens)]
+    vs = [rounded(oracle, oracle.randn((L, nkv, hd), 303, 50 + i), dt) for i, L in enumerate(lens)]
+    cache = RaggedCache(ks, vs, dt)
+    want, want_lse = run_decode(gpu_ctx, q, cache.view, lens, nh=nh, nkv=nkv, hd=hd, num_splits=0, q_dt=dt, out_dt=F32,
+                                want_lse=True)
+    for call in range(2):
+        n0 = gpu_ctx.launch_count
+        got, got_lse = _static_decode(gpu_ctx, q, cache.view, lens, nh=nh, nkv=nkv, hd=hd, dt=dt)
+        assert gpu_ctx.launch_count - n0 == 1, "one cooperative launch, no second merge kernel"
+        for i, L in enumerate(lens):
+            assert rel_err(got[i], want[i]) <= 1e-5, (call, i)
+            assert rel_err(got[i], oracle.attention_f64(q[i], ks[i], vs[i], L)) <= RTOL_16, (call, i)
+        assert np.abs(got_lse - want_lse).max() <= 1e-5, call
 
 
 def test_f32_cache_and_explicit_splits(gpu_ctx, oracle):
