@@ -209,12 +209,13 @@ def run_reference(args, rank: int) -> None:
     }))
 
 
-def workload_config(n_gpus: int, shape: str = "plain") -> dict:
+def workload_config(n_gpus: int, shape: str = "plain", kv: str = "fp16") -> dict:
     rope = ("full rotary (rotary_dim = head_dim), no QK-norm, no gate" if shape == "plain" else
             "reference-shaped: rotary_dim = head_dim/4 interleaved, QK RMSNorm with bf16 weights, sigmoid gate")
     return {"workload": "cfg2: batched ragged decode attention, one layer, append+attend per step", "rope": rope,
             "seqs_per_gpu": SEQS_PER_GPU, "context": f"uniform[{LMIN},{LMAX}] (seeded)", "num_q_heads": NH,
-            "num_kv_heads": NKV, "head_dim": HD, "kv_dtype": "fp16", "q_dtype": "fp16", "accumulate": "fp32",
+            "num_kv_heads": NKV, "head_dim": HD, "kv_dtype": kv if kv == "fp16" else "fp8 e4m3 (algorithmic bytes count one byte per element)",
+            "q_dtype": "fp16", "accumulate": "fp32",
             "rope_theta": 1e6, "sharding": (f"{SEQS_PER_GPU * n_gpus} sequences dealt to {n_gpus} GPU(s) longest first to the rank with the fewest rows, "
                          "no collective"),
             "l2": f"KV per step > L2 and {N_SETS} cache sets rotate between steps"}
@@ -246,7 +247,7 @@ def cpu_baseline(rank: int, row_off, lens: np.ndarray) -> dict:
 def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     import torch
 
-    from shady_thinker_b200._lib import F16
+    from shady_thinker_b200._lib import F8E4M3, F16
     from shady_thinker_b200.batch import BatchedDecoder
     from shady_thinker_b200.gpu import GpuContext
     from shady_thinker_b200 import ops
@@ -268,6 +269,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     S = len(lens)
     sets = []
     ref_shape = args.shape == "reference"
+    kv_dt = F8E4M3 if args.kv == "fp8" else F16      # fp8: e4m3 cache rows (half the bytes per row), f16 activations
     qrow = NH * HD * (2 if ref_shape else 1)
     d_norm = None
     if ref_shape:       # bf16 q_norm[hd] then k_norm[hd], N(0, 0.02) (the uniform of model.rs:140-168)
@@ -276,13 +278,13 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         d_norm = gpu.upload_buffer("qknorm_weights", wbits.tobytes())
     for i in range(N_SETS):
         d = BatchedDecoder(gpu, num_seqs=S, capacities=lens, num_heads=NH, num_kv_heads=NKV, head_dim=HD,
-                           kv_dtype=F16, rope_theta=1e6, rotary_dim=HD // 4 if ref_shape else HD, has_gate=ref_shape,
+                           kv_dtype=kv_dt, rope_theta=1e6, rotary_dim=HD // 4 if ref_shape else HD, has_gate=ref_shape,
                            num_splits=0, qk_norm_bf16=d_norm)
         d.set_lengths(lens - 1)
         base = 1000 * rank + 10 * i
-        n = d.layer_bytes // 2
-        ops.fill_randn(gpu, d.k_cache[0], n, F16, SEED, base + 1)
-        ops.fill_randn(gpu, d.v_cache[0], n, F16, SEED, base + 2)
+        n = d.layer_bytes // (1 if kv_dt == F8E4M3 else 2)
+        ops.fill_randn(gpu, d.k_cache[0], n, kv_dt, SEED, base + 1)
+        ops.fill_randn(gpu, d.v_cache[0], n, kv_dt, SEED, base + 2)
         ops.fill_randn(gpu, d.q_in, S * qrow, F16, SEED, base + 3)
         ops.fill_randn(gpu, d.k_in, S * NKV * HD, F16, SEED, base + 4)
         ops.fill_randn(gpu, d.v_in, S * NKV * HD, F16, SEED, base + 5)
@@ -391,11 +393,13 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "metric": "decode_attn_kv_bandwidth", "value": all_bytes * args.steps / (total_ms * 1e-3) / 1e9, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": workload_config(world, args.shape),
+            "config": workload_config(world, args.shape, args.kv),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": (TRAFFIC_PER_ALGO_BYTE * step_bytes) if TRAFFIC_PER_ALGO_BYTE else None,
                          "peak_source": f"{peak_src} (copy bandwidth)",
-                         "kernel": "decode16_kernel<half,128> with the fused append and split merge (the whole step is this one launch)",
+                         "kernel": ("decode16_kernel<half,128> with the fused append and split merge (the whole step is this one launch)"
+                                    if args.kv == "fp16" else
+                                    "decode16_kernel<half,128,e4m3 cache> (attend launch of the step; the append is a launch of its own)"),
                          "traffic_source": f"algorithmic bytes x {TRAFFIC_PER_ALGO_BYTE}, the DRAM-byte ratio ncu measured at {TRAFFIC_MEASURED_AT}",
                          "algorithmic_bytes_per_launch": step_bytes, "avg_launch_ms": attend_ms,
                          "avg_launch_ms_single_bracketed": bracketed_ms,
@@ -414,7 +418,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         }
         if extra:
             line["extra"] = extra
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and args.kv == "fp16":
             line["cpu_baseline"] = cpu_baseline(rank, row_off0, lens)
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -880,6 +884,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    ap.add_argument("--kv", default="fp16", choices=["fp16", "fp8"],
+                    help="cfg2 only: storage of the KV cache (fp8 = e4m3 rows written by the quantising append)")
     ap.add_argument("--no-extra", action="store_true",
                     help="cfg2 only: skip the short cfg3 (prefill) and cfg4 (long context) legs added to the line as `extra`")
     ap.add_argument("--shape", default="plain", choices=["plain", "reference"],

@@ -44,6 +44,7 @@ extern "C" {
 #define SHADY_F32 0
 #define SHADY_F16 1
 #define SHADY_BF16 2
+#define SHADY_F8E4M3 3   /* KV cache only: 8-bit e4m3 (4 exponent bits, 3 mantissa bits, no infinities) */
 
 typedef struct shady_ctx shady_ctx;
 
@@ -111,6 +112,12 @@ int shady_synchronize(shady_ctx *ctx);
  * Sequences then grow a page at a time and share one pool.  Paged 16-bit caches are taken by
  * shady_kv_append_rope, shady_attn_decode / _static / _shard (num_splits 0 or 1) and
  * shady_attn_decode_append; the other entry points return SHADY_ERR_UNSUPPORTED for them.
+ *
+ * 8-bit cache (no reference counterpart; the reference's cache is f32, model.rs:241-256): with dtype ==
+ * SHADY_F8E4M3 a stored element is round-to-nearest-even e4m3 of value / k_scale (K rows) or value / v_scale
+ * (V rows), saturated at +-448; the scales are per cache (0 means 1).  shady_kv_append_rope quantises, and
+ * shady_attn_decode / _static / _shard read such caches (head_dim 128 or 256, Q and output f16 or f32); the
+ * other entry points return SHADY_ERR_UNSUPPORTED for them.
  * Zero the struct before filling it: fields added later default to "off". */
 typedef struct {
     void *d_k_base;
@@ -118,10 +125,12 @@ typedef struct {
     uint64_t seq_stride;     /* elements between consecutive sequences (ignored with ptr arrays) */
     void *const *d_k_ptrs;   /* device array [num_seqs] of device pointers, or NULL */
     void *const *d_v_ptrs;
-    uint32_t dtype;          /* SHADY_F32 / SHADY_F16 / SHADY_BF16 */
+    uint32_t dtype;          /* SHADY_F32 / SHADY_F16 / SHADY_BF16 / SHADY_F8E4M3 */
     uint32_t page_rows;      /* paged: rows per page (multiple of 16); else 0 */
     const uint32_t *d_page_table;   /* paged: device array [num_seqs][max_pages_per_seq]; else NULL */
     uint32_t max_pages_per_seq;
+    float k_scale;           /* SHADY_F8E4M3: value = stored * scale; 0 = 1 */
+    float v_scale;
     uint32_t _pad;
 } shady_kv_cache;
 
@@ -344,6 +353,40 @@ int shady_attn_prefill_append(shady_ctx *ctx, const shady_append_params *ap, con
 /* ===================================================================================== */
 /* x[i] *= 1/(1+exp(-gate[i])) in place (the reference needs a temp + copy: model.rs:584-592). */
 int shady_sigmoid_mul(shady_ctx *ctx, float *d_x, const float *d_gate, uint32_t n);
+
+/* ===================================================================================== */
+/* q/k/v projections (INT4 GPTQ matvec) with the KV append as their epilogue               */
+/* replaces Model::gptq_matvec (model.rs:357-381) at its q/k/v call sites (model.rs:698-714) */
+/* and the dispatch that follows them (model.rs:723); gptq_matvec.wgsl, gptq_matvec_4t.wgsl */
+/* ===================================================================================== */
+/* One symmetric INT4 weight matrix in the reference's layout: d_qweight [K/8][N] u32, eight nibbles along K per
+ * word, lowest row in the low nibble (gptq_matvec.wgsl:47-57); d_scales [K/group_size][N] f16, two per u32
+ * (unpack2x16float, wgsl:44-45); weight(k, n) = (nibble - 8) * scale(k / group_size, n).  K and group_size are
+ * multiples of 8 and group_size divides K. */
+typedef struct {
+    const uint32_t *d_qweight;
+    const uint32_t *d_scales;
+    uint32_t K;
+    uint32_t N;
+    uint32_t group_size;
+    uint32_t _pad;
+} shady_gptq_weight;
+
+/* Model::gptq_matvec (model.rs:357-381): d_y[v][n] = sum_k weight(k, n) * d_x[v][k] for num_vecs input vectors
+ * (the reference has one).  f32 in, f32 out. */
+int shady_gptq_matvec(shady_ctx *ctx, const shady_gptq_weight *w, const float *d_x, float *d_y, uint32_t num_vecs);
+
+/* The three projections of a self-attention layer and the append in ONE launch: what model.rs:698-714 followed by
+ * model.rs:723 compute with four dispatches and three f32 buffers in between (q_out, k_out, v_out, which are not
+ * written here).  d_x [num_seqs][K] f32 is the normed hidden state of one token per sequence.  wq has
+ * num_heads * (1 + has_gate) * head_dim columns (per head: Q columns, then gate columns — the layout
+ * fused_split_qknorm_kvstore.wgsl:122-135 reads), wk and wv num_kv_heads * head_dim each.  Outputs and the remaining
+ * arguments are those of shady_kv_append_rope (`p->tokens_per_seq` must be 1, `p->in_dtype` and `p->write_k_back`
+ * are ignored): d_q_out, d_q_gate, the cache row of every sequence at its position. */
+int shady_qkv_proj_append(shady_ctx *ctx, const shady_append_params *p, const shady_gptq_weight *wq,
+                          const shady_gptq_weight *wk, const shady_gptq_weight *wv, const float *d_x, void *d_q_out,
+                          float *d_q_gate, const shady_kv_cache *cache, const uint16_t *d_qk_norm_bf16,
+                          const uint32_t *d_pos_start, const uint32_t *d_pos_h, const uint32_t *d_pos_w);
 
 /* ===================================================================================== */
 /* Synthetic data — counter-based N(0,1) fill used by the benchmark and the tests         */

@@ -70,6 +70,7 @@ def lib() -> C.CDLL:
         L.oracle_fused_split_qknorm_kvstore_f32.argtypes = [C.POINTER(QkNormParams), f32p, f32p, f32p, f32p,
                                                             f32p, f32p, f32p, u16p]
         L.oracle_sigmoid_mul_f32.argtypes = [f32p, f32p, f32p, C.c_uint32]
+        L.oracle_gptq_matvec_f32.argtypes = [f32p, u32p, u32p, f32p, C.c_uint32, C.c_uint32, C.c_uint32]
         L.oracle_attention_f64.argtypes = [f32p, f32p, f32p, f64p] + [C.c_uint32] * 5 + [C.c_int]
         L.oracle_causal_prefill_f32.argtypes = [f32p, f32p, f32p, f32p] + [C.c_uint32] * 5 + [C.c_int]
         L.oracle_causal_prefill_f64.argtypes = [f32p, f32p, f32p, f64p] + [C.c_uint32] * 5 + [C.c_int]
@@ -155,6 +156,19 @@ def sigmoid_mul(x, gate) -> np.ndarray:
     return out
 
 
+def gptq_matvec(x, qweight, scales_f16, group_size: int) -> np.ndarray:
+    """x [K] f32; qweight [K/8, N] uint32; scales_f16 [K/group_size, N] float16 (packed two per u32 for the C side, as
+    the shader reads them).  Returns [N] f32 (gptq_matvec.wgsl)."""
+    x = _f32(x)
+    qw = np.ascontiguousarray(qweight, dtype=np.uint32)
+    sc = np.ascontiguousarray(scales_f16, dtype=np.float16)
+    K, N = x.size, qw.shape[1]
+    assert qw.shape[0] * 8 == K and sc.shape == (K // group_size, N) and (sc.size % 2) == 0
+    out = np.empty(N, np.float32)
+    lib().oracle_gptq_matvec_f32(_p(x), _p(qw, C.c_uint32), _p(sc.view(np.uint32), C.c_uint32), _p(out), K, N, group_size)
+    return out
+
+
 def attention_f64(q, k_cache, v_cache, seq_len: int, threads: int = 1) -> np.ndarray:
     q, k_cache, v_cache = _f32(q), _f32(k_cache), _f32(v_cache)
     nh, hd = q.shape
@@ -219,3 +233,21 @@ def bf16_bits(a) -> np.ndarray:
 
 def round_f16(a) -> np.ndarray:
     return _f32(a).astype(np.float16).astype(np.float32)
+
+
+def e4m3_stored(a, scale: float = 1.0) -> np.ndarray:
+    """The e4m3 values (as f32, on the e4m3 grid) an 8-bit cache stores for ``a``: ``a * (1/scale)`` in f32, rounded
+    to nearest even at 3 mantissa bits (subnormal step 2^-9), saturated at +-448.  The f32 multiply by the reciprocal
+    is what the append kernels do, so the bytes agree with the device."""
+    x = _f32(a) * (np.float32(1.0) / np.float32(scale)) if scale != 1.0 else _f32(a)
+    ax = np.minimum(np.abs(x.astype(np.float64)), 448.0)
+    e = np.floor(np.log2(np.maximum(ax, 2.0 ** -20)))
+    e = np.maximum(e, -6.0)                       # below 2^-6 the grid is the subnormal one
+    step = 2.0 ** (e - 3)
+    q = np.minimum(np.rint(ax / step) * step, 448.0)   # numpy rounds halves to even
+    return (np.sign(x) * q).astype(np.float32).reshape(np.shape(a))
+
+
+def round_e4m3(a, scale: float = 1.0) -> np.ndarray:
+    """What an 8-bit e4m3 cache with this scale holds for ``a``, dequantised: stored value times scale, as f32."""
+    return (e4m3_stored(a, scale).astype(np.float64) * np.float64(np.float32(scale))).astype(np.float32)

@@ -1,5 +1,6 @@
 /*
- * CPU restatement of the shady-thinker attention hot path.  TEST INFRASTRUCTURE ONLY:
+ * CPU restatement of the shady-thinker attention hot path (and of the INT4 projection that
+ * feeds it).  TEST INFRASTRUCTURE ONLY:
  * this file is the parity checker and the timed CPU baseline; no product code path may
  * call it.
  *
@@ -237,6 +238,48 @@ void oracle_sigmoid_mul_f32(const float *x, const float *gate, float *out, uint3
     for (uint32_t i = 0; i < n; ++i) {
         const float sig = 1.0f / (1.0f + expf(-gate[i]));
         out[i] = x[i] * sig;
+    }
+}
+
+/* f-4 (next row): gptq_matvec.wgsl:20-82 — symmetric INT4 GPTQ matrix-vector product, one output column
+ * at a time, terms added in row order in f32:  sum += ((f32(nibble) - 8) * scale) * input[row]   (wgsl:50-57).
+ * qweight [K/8][N] u32 (eight nibbles along K per word, lowest row in the low nibble), scales [K/group][N] f16,
+ * two per u32 (unpack2x16float, wgsl:44-45).  The 4-thread variant (gptq_matvec_4t.wgsl) adds the same terms in
+ * four interleaved chains; both are the same product to f32 rounding. */
+static float f16_bits_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+    uint32_t u;
+    if (exp == 0) {
+        if (man == 0) u = sign;
+        else {   /* subnormal: normalise */
+            int e = -1;
+            uint32_t m = man;
+            do { m <<= 1; ++e; } while (!(m & 0x400u));
+            u = sign | ((uint32_t)(127 - 15 - e) << 23) | ((m & 0x3ffu) << 13);
+        }
+    } else if (exp == 31) u = sign | 0x7f800000u | (man << 13);
+    else u = sign | ((exp + 112u) << 23) | (man << 13);
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+void oracle_gptq_matvec_f32(const float *input, const uint32_t *qweight, const uint32_t *scales, float *output,
+                            uint32_t K, uint32_t N, uint32_t group_size) {
+    const uint32_t packed_rows = K / 8u;
+    for (uint32_t col = 0; col < N; ++col) {
+        float sum = 0.0f;
+        for (uint32_t pr = 0; pr < packed_rows; ++pr) {
+            const uint32_t group = (pr * 8u) / group_size;
+            const uint32_t sf = group * N + col;
+            const uint32_t s2 = scales[sf / 2u];
+            const float scale = f16_bits_to_f32((uint16_t)((sf & 1u) ? (s2 >> 16) : (s2 & 0xffffu)));
+            const uint32_t packed = qweight[pr * N + col];
+            for (uint32_t nib = 0; nib < 8u; ++nib) {
+                const float w = ((float)((packed >> (4u * nib)) & 0xFu) - 8.0f) * scale;
+                sum += w * input[pr * 8u + nib];
+            }
+        }
+        output[col] = sum;
     }
 }
 

@@ -1,6 +1,6 @@
 //! Compiles the CUDA sources of the attention hot path for sm_100a and links them into the crate.
 //!
-//! SHADY_ATTN_CSRC points at the directory that holds api.cu, append.cu, decode.cu, prefill.cu and p2p.cu
+//! SHADY_ATTN_CSRC points at the directory that holds api.cu, append.cu, decode.cu, prefill.cu, p2p.cu and gptq.cu
 //! (default: `../../shady_thinker_b200/csrc`, their place in the repository this crate ships in); NVCC
 //! overrides the compiler.  There is one target architecture and no other backend.
 //!
@@ -8,7 +8,7 @@
 use std::path::PathBuf;
 use std::process::Command;
 
-const SOURCES: [&str; 5] = ["api.cu", "append.cu", "decode.cu", "prefill.cu", "p2p.cu"];
+const SOURCES: [&str; 6] = ["api.cu", "append.cu", "decode.cu", "prefill.cu", "p2p.cu", "gptq.cu"];
 
 fn main() {
     let out = PathBuf::from(std::env::var("OUT_DIR").expect("OUT_DIR"));

@@ -12,7 +12,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("SHADY_ATTN_LIB") or os.path.join(_PKG, "libshady_attn.so")
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT = range(6)
-F32, F16, BF16 = 0, 1, 2
+F32, F16, BF16, F8E4M3 = 0, 1, 2, 3
 
 # every symbol include/shady_attn.h declares
 EXPORTS = [
@@ -23,6 +23,7 @@ EXPORTS = [
     "shady_flush", "shady_synchronize", "shady_kv_append_rope", "shady_decode_workspace_size", "shady_decode_workspace_init",
     "shady_attn_decode", "shady_attn_decode_static", "shady_attn_decode_shard", "shady_attn_decode_append", "shady_attn_decode_partials", "shady_attn_reduce", "shady_attn_prefill",
     "shady_prefill_workspace_size", "shady_attn_prefill_append",
+    "shady_gptq_matvec", "shady_qkv_proj_append",
     "shady_sigmoid_mul", "shady_fill_randn", "shady_ipc_export", "shady_ipc_open", "shady_ipc_close",
     "shady_combine_p2p_buffer_size", "shady_attn_combine_p2p", "shady_attn_decode_shard_p2p",
 ]
@@ -38,7 +39,7 @@ class KvCache(C.Structure):
     _fields_ = [("d_k_base", C.c_void_p), ("d_v_base", C.c_void_p), ("seq_stride", C.c_uint64),
                 ("d_k_ptrs", C.c_void_p), ("d_v_ptrs", C.c_void_p), ("dtype", C.c_uint32),
                 ("page_rows", C.c_uint32), ("d_page_table", C.c_void_p), ("max_pages_per_seq", C.c_uint32),
-                ("_pad", C.c_uint32)]
+                ("k_scale", C.c_float), ("v_scale", C.c_float), ("_pad", C.c_uint32)]
 
 
 class AppendParams(C.Structure):
@@ -54,6 +55,11 @@ class DecodeParams(C.Structure):
     _fields_ = [("head_dim", C.c_uint32), ("num_kv_heads", C.c_uint32), ("num_q_heads", C.c_uint32),
                 ("heads_per_kv", C.c_uint32), ("num_splits", C.c_uint32), ("num_seqs", C.c_uint32),
                 ("q_dtype", C.c_uint32), ("out_dtype", C.c_uint32)]
+
+
+class GptqWeight(C.Structure):
+    _fields_ = [("d_qweight", C.c_void_p), ("d_scales", C.c_void_p), ("K", C.c_uint32), ("N", C.c_uint32),
+                ("group_size", C.c_uint32), ("_pad", C.c_uint32)]
 
 
 class PrefillParams(C.Structure):
@@ -119,6 +125,9 @@ def load() -> C.CDLL:
     L.shady_attn_decode_shard_p2p.argtypes = [vp, C.POINTER(DecodeParams), vp, C.POINTER(KvCache), u32p,
                                               C.POINTER(C.c_uint32), C.c_uint32, C.c_uint32, C.c_uint32, vp, f32p, vp,
                                               C.c_uint32, f32p, vp, sz]
+    L.shady_gptq_matvec.argtypes = [vp, C.POINTER(GptqWeight), f32p, f32p, C.c_uint32]
+    L.shady_qkv_proj_append.argtypes = [vp, C.POINTER(AppendParams), C.POINTER(GptqWeight), C.POINTER(GptqWeight),
+                                        C.POINTER(GptqWeight), f32p, vp, f32p, C.POINTER(KvCache), vp, u32p, u32p, u32p]
     L.shady_sigmoid_mul.argtypes = [vp, f32p, f32p, C.c_uint32]
     L.shady_fill_randn.argtypes = [vp, vp, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint64]
     for name in EXPORTS:

@@ -15,25 +15,31 @@ import os
 import numpy as np
 
 from . import ops
-from ._lib import BF16, F16, F32, AppendParams, DecodeParams
+from ._lib import BF16, F8E4M3, F16, F32, AppendParams, DecodeParams
 from .gpu import GpuContext, _addr
 
-_ESZ = {F32: 4, F16: 2, BF16: 2}
+_ESZ = {F32: 4, F16: 2, BF16: 2, F8E4M3: 1}
 
 
 class BatchedDecoder:
     def __init__(self, gpu: GpuContext, *, num_seqs: int, capacities, num_heads: int, num_kv_heads: int,
                  head_dim: int, kv_dtype: int = F16, act_dtype: int | None = None, rope_theta: float = 1e6,
                  rotary_dim: int | None = None, interleaved: bool = True, eps: float = 1e-6, has_gate: bool = False,
-                 num_layers: int = 1, num_splits: int = 0, qk_norm_bf16=None):
+                 num_layers: int = 1, num_splits: int = 0, qk_norm_bf16=None, k_scale: float = 0.0,
+                 v_scale: float = 0.0):
+        """``kv_dtype=F8E4M3`` keeps the caches as 8-bit e4m3 (``k_scale`` / ``v_scale``: value = stored * scale, 0
+        means 1); activations are then f16 and a step is the append launch followed by the attend launch."""
         self.gpu, self.S, self.nh, self.nkv, self.hd = gpu, num_seqs, num_heads, num_kv_heads, head_dim
         self.kv_dtype = kv_dtype
-        self.act_dtype = kv_dtype if act_dtype is None else act_dtype
+        if act_dtype is None:
+            act_dtype = F16 if kv_dtype == F8E4M3 else kv_dtype
+        self.act_dtype = act_dtype
         self.theta, self.rd = rope_theta, head_dim if rotary_dim is None else rotary_dim
         self.interleaved, self.eps, self.has_gate = interleaved, eps, has_gate
         self.num_layers, self.num_splits = num_layers, num_splits
         self.qk_norm = qk_norm_bf16   # device buffer: bf16 q_norm[hd] then k_norm[hd] (model.rs:140-168), or None
-        self.fused = not os.environ.get("SHADY_NO_FUSED_APPEND") and kv_dtype != F32 and interleaved and (kv_dtype if act_dtype is None else act_dtype) in (F32, kv_dtype)
+        self.fused = (not os.environ.get("SHADY_NO_FUSED_APPEND") and kv_dtype in (F16, BF16) and interleaved
+                      and act_dtype in (F32, kv_dtype))
         caps = np.asarray(capacities, dtype=np.int64)
         assert caps.shape == (num_seqs,)
         row = num_kv_heads * head_dim
@@ -52,7 +58,7 @@ class BatchedDecoder:
             vp = (self.v_cache[l].ptr + self.row_off[:-1] * row * esz).astype(np.uint64)
             dk, dv = gpu.upload_buffer(f"k_ptrs_{l}", kp.tobytes()), gpu.upload_buffer(f"v_ptrs_{l}", vp.tobytes())
             self._ptr_bufs += [dk, dv]
-            self.views.append(ops.KvCacheView(kv_dtype, k_ptrs=dk, v_ptrs=dv))
+            self.views.append(ops.KvCacheView(kv_dtype, k_ptrs=dk, v_ptrs=dv, k_scale=k_scale, v_scale=v_scale))
         qrow = num_heads * head_dim * (2 if has_gate else 1)
         self.q_in = mk("q_proj_full", num_seqs * qrow * asz)
         self.k_in = mk("k_proj", num_seqs * row * asz)

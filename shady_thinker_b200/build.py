@@ -8,7 +8,7 @@ import sys
 _PKG = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_PKG, "csrc")
 LIB_PATH = os.path.join(_PKG, "libshady_attn.so")
-SOURCES = ["api.cu", "append.cu", "decode.cu", "prefill.cu", "p2p.cu"]
+SOURCES = ["api.cu", "append.cu", "decode.cu", "prefill.cu", "p2p.cu", "gptq.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

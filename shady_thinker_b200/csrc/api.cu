@@ -40,8 +40,15 @@ static uint32_t env_u32(const char *name, uint32_t dflt) {
 
 int fill_kv_addr(shady_ctx *ctx, const shady_kv_cache *cache, uint32_t nkv, uint32_t hd, const char *who, KvAddr *out) {
     const std::string w(who);
-    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, w + ": bad cache dtype");
+    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_F8E4M3, SHADY_ERR_BAD_ARG, w + ": bad cache dtype");
     KvAddr kv{};
+    kv.k_scale = kv.v_scale = 1.0f;
+    if (cache->dtype == SHADY_F8E4M3) {
+        SHADY_REQUIRE(ctx, cache->k_scale >= 0.f && cache->v_scale >= 0.f && isfinite(cache->k_scale) && isfinite(cache->v_scale),
+                      SHADY_ERR_BAD_ARG, w + ": cache scales must be finite and not negative");
+        if (cache->k_scale > 0.f) kv.k_scale = cache->k_scale;
+        if (cache->v_scale > 0.f) kv.v_scale = cache->v_scale;
+    }
     kv.k_base = (const char *)cache->d_k_base; kv.v_base = (const char *)cache->d_v_base;
     kv.seq_stride_bytes = cache->seq_stride * dtype_size(cache->dtype);
     kv.k_ptrs = cache->d_k_ptrs; kv.v_ptrs = cache->d_v_ptrs;
@@ -50,7 +57,7 @@ int fill_kv_addr(shady_ctx *ctx, const shady_kv_cache *cache, uint32_t nkv, uint
                       w + ": a paged cache takes the two pool bases and no pointer arrays");
         SHADY_REQUIRE(ctx, cache->page_rows && cache->page_rows % 16 == 0 && cache->max_pages_per_seq, SHADY_ERR_BAD_ARG,
                       w + ": page_rows must be a positive multiple of 16 and max_pages_per_seq positive");
-        SHADY_REQUIRE(ctx, cache->dtype != SHADY_F32, SHADY_ERR_UNSUPPORTED, w + ": paged caches are 16-bit");
+        SHADY_REQUIRE(ctx, cache->dtype != SHADY_F32, SHADY_ERR_UNSUPPORTED, w + ": paged caches are 16-bit or 8-bit");
         kv.page_table = cache->d_page_table;
         kv.page_rows = cache->page_rows; kv.max_pages = cache->max_pages_per_seq;
         kv.page_bytes = (unsigned long long)cache->page_rows * nkv * hd * dtype_size(cache->dtype);
@@ -88,6 +95,10 @@ int launch_append(shady_ctx *, const shady_append_params *, const void *, void *
                   const shady_kv_cache *, const uint16_t *, const uint32_t *, const uint32_t *, const uint32_t *);
 int launch_prefill(shady_ctx *, const shady_prefill_params *, const void *, const shady_kv_cache *, void *);
 size_t prefill_workspace_bytes(const shady_prefill_params *p);
+int launch_gptq_matvec(shady_ctx *, const shady_gptq_weight *, const float *, float *, uint32_t);
+int launch_qkv_proj_append(shady_ctx *, const shady_append_params *, const shady_gptq_weight *, const shady_gptq_weight *,
+                           const shady_gptq_weight *, const float *, void *, float *, const shady_kv_cache *, const uint16_t *,
+                           const uint32_t *, const uint32_t *, const uint32_t *);
 int launch_prefill_append(shady_ctx *, const shady_append_params *, const shady_prefill_params *, const void *, const void *,
                           const void *, const uint16_t *, const shady_kv_cache *, void *, void *, size_t);
 unsigned long long p2p_buffer_bytes(uint32_t world, uint32_t nh, uint32_t hd);
@@ -404,6 +415,20 @@ int shady_attn_combine_p2p(shady_ctx *ctx, uint32_t world, uint32_t rank, uint32
     return launch_combine_p2p(ctx, world, rank, num_heads, head_dim, epoch, d_peer_table, d_records, d_out, out_dtype, d_gate);
 }
 
+int shady_gptq_matvec(shady_ctx *ctx, const shady_gptq_weight *w, const float *d_x, float *d_y, uint32_t num_vecs) {
+    CTX_ENTER(ctx);
+    return launch_gptq_matvec(ctx, w, d_x, d_y, num_vecs);
+}
+
+int shady_qkv_proj_append(shady_ctx *ctx, const shady_append_params *p, const shady_gptq_weight *wq, const shady_gptq_weight *wk,
+                          const shady_gptq_weight *wv, const float *d_x, void *d_q_out, float *d_q_gate,
+                          const shady_kv_cache *cache, const uint16_t *d_qk_norm_bf16, const uint32_t *d_pos_start,
+                          const uint32_t *d_pos_h, const uint32_t *d_pos_w) {
+    CTX_ENTER(ctx);
+    return launch_qkv_proj_append(ctx, p, wq, wk, wv, d_x, d_q_out, d_q_gate, cache, d_qk_norm_bf16, d_pos_start, d_pos_h,
+                                  d_pos_w);
+}
+
 int shady_sigmoid_mul(shady_ctx *ctx, float *d_x, const float *d_gate, uint32_t n) {
     CTX_ENTER(ctx);
     return launch_sigmoid_mul(ctx, d_x, d_gate, n);
@@ -413,7 +438,7 @@ int shady_fill_randn(shady_ctx *ctx, void *d_dst, uint64_t n, uint32_t dtype, ui
                      uint64_t first_idx) {
     CTX_ENTER(ctx);
     SHADY_REQUIRE(ctx, d_dst || !n, SHADY_ERR_BAD_ARG, "fill_randn: null destination");
-    SHADY_REQUIRE(ctx, dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "fill_randn: bad dtype");
+    SHADY_REQUIRE(ctx, dtype <= SHADY_F8E4M3, SHADY_ERR_BAD_ARG, "fill_randn: bad dtype");
     if (!n) return SHADY_OK;
     const unsigned long long key = mix64(seed ^ (tensor_id * 0xD1B54A32D192ED03ull));
     const unsigned long long want = (n + 255) / 256;

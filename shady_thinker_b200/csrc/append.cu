@@ -11,7 +11,7 @@
 // intrinsics: the shader takes cos/sin of up to 131071 radians in f32 (wgsl:66-68).
 #include <math.h>
 
-#include "common.cuh"
+#include "append_core.cuh"
 
 namespace shady {
 
@@ -32,6 +32,7 @@ struct AppendArgs {
     uint32_t head_slices;     // vectorised path: warps that share one token's heads (small batches need the parallelism)
     uint32_t skip_q;          // vectorised path: K/V only (Q is normed and rotated by the prefill attention kernel itself)
     float2 *cs_table;         // vectorised path, optional: (cos, sin) of [token j][pair i < hd/2] of sequence 0, (1, 0) past rd/2
+    float k_inv, v_inv;       // 8-bit caches: rows are stored as value * (1 / scale); 1 otherwise
     float inv_freq[128];      // [rd/2]
 };
 
@@ -53,60 +54,30 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(const AppendA
     const uint32_t kh = h - a.nh;
 
     // ---- load the head vector (and pass the gate through) ----
-    float ssq = 0.f;
     if (is_q) {
         const size_t row = (tok * a.nh + h) * (size_t)(a.has_gate ? 2 * hd : hd);
         for (uint32_t d = lane; d < hd; d += 32) {
-            const float v = load_as_f32(a.q_in, row + d, a.in_dtype);
-            vals[d] = v;
-            ssq += v * v;
+            vals[d] = load_as_f32(a.q_in, row + d, a.in_dtype);
             if (a.has_gate && a.q_gate)
                 a.q_gate[(tok * a.nh + h) * (size_t)hd + d] = load_as_f32(a.q_in, row + hd + d, a.in_dtype);
         }
     } else {
         const size_t row = (tok * a.nkv + kh) * (size_t)hd;
-        for (uint32_t d = lane; d < hd; d += 32) {
-            const float v = load_as_f32(a.k_io, row + d, a.in_dtype);
-            vals[d] = v;
-            ssq += v * v;
-        }
-    }
-    // ---- RMSNorm (wgsl:150-160 / :205-212) ----
-    if (a.norm_w) {
-        ssq = warp_sum(ssq);
-        const float rms = 1.0f / sqrtf(ssq / (float)hd + a.eps);
-        const uint16_t *w = a.norm_w + (is_q ? 0 : hd);
-        for (uint32_t d = lane; d < hd; d += 32) {
-            const float wf = __uint_as_float(((uint32_t)w[d]) << 16);
-            vals[d] = vals[d] * rms * (1.0f + wf);
-        }
+        for (uint32_t d = lane; d < hd; d += 32) vals[d] = load_as_f32(a.k_io, row + d, a.in_dtype);
     }
     __syncwarp();
-    // ---- (m)RoPE on the first rd dims (wgsl:56-104) ----
+    // ---- RMSNorm (wgsl:150-160 / :205-212) and (m)RoPE on the first rd dims (wgsl:56-104) ----
     const uint32_t p_t = (a.pos_start ? a.pos_start[s] : 0u) + j;
     const uint32_t p_h = a.pos_h ? a.pos_h[s] + j : p_t;
     const uint32_t p_w = a.pos_w ? a.pos_w[s] + j : p_t;
-    const uint32_t half = a.rd / 2;
-    for (uint32_t i = lane; i < half; i += 32) {
-        uint32_t pos = p_t;
-        if ((i % 3u) == 1u && i < a.s1) pos = p_h;
-        else if ((i % 3u) == 2u && i < a.s2) pos = p_w;
-        const float angle = (float)pos * a.inv_freq[i];
-        float sn, cs;
-        sincosf(angle, &sn, &cs);
-        const uint32_t ia = a.interleaved ? 2 * i : i;
-        const uint32_t ib = a.interleaved ? 2 * i + 1 : i + half;
-        const float x = vals[ia], y = vals[ib];
-        vals[ia] = x * cs - y * sn;
-        vals[ib] = y * cs + x * sn;
-    }
-    __syncwarp();
+    const RopeSpec spec{a.rd, a.s1, a.s2, a.interleaved, a.eps};
+    warp_norm_rope(vals, lane, hd, a.norm_w ? a.norm_w + (is_q ? 0 : hd) : nullptr, spec, a.inv_freq, p_t, p_h, p_w);
     // ---- stores ----
     if (is_q) {
         const size_t row = (tok * a.nh + h) * (size_t)hd;
         for (uint32_t d = lane; d < hd; d += 32) store_from_f32(a.q_out, row + d, a.q_dtype, vals[d]);
     } else {
-        const size_t esz = a.kv_dtype == SHADY_F32 ? 4 : 2;
+        const size_t esz = a.kv_dtype == SHADY_F32 ? 4 : (a.kv_dtype == SHADY_F8E4M3 ? 1 : 2);
         // cache_position == position (model.rs:493-496)
         char *kc = const_cast<char *>(kv_row_ptr(a.kv, false, s, p_t, (size_t)a.nkv * hd * esz));
         char *vc = const_cast<char *>(kv_row_ptr(a.kv, true, s, p_t, (size_t)a.nkv * hd * esz));
@@ -115,8 +86,8 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(const AppendA
         for (uint32_t d = lane; d < hd; d += 32) {
             const float kv = vals[d];
             if (a.write_k_back) store_from_f32(a.k_io, row + d, a.in_dtype, kv);
-            store_from_f32(kc, crow + d, a.kv_dtype, kv);
-            store_from_f32(vc, crow + d, a.kv_dtype, load_as_f32(a.v_in, row + d, a.in_dtype));
+            store_from_f32(kc, crow + d, a.kv_dtype, kv * a.k_inv);
+            store_from_f32(vc, crow + d, a.kv_dtype, load_as_f32(a.v_in, row + d, a.in_dtype) * a.v_inv);
         }
     }
 }
@@ -151,6 +122,22 @@ template <> struct Vec8<float> {
     static __device__ __forceinline__ void store(float *p, const float (&v)[8]) {
         *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+
+template <> struct Vec8<__nv_fp8_e4m3> {   // eight 1-byte elements: an 8-byte access
+    static __device__ __forceinline__ void load(const __nv_fp8_e4m3 *p, float (&v)[8]) {
+        const uint2 u = *reinterpret_cast<const uint2 *>(p);
+        const __nv_fp8_e4m3 *e = reinterpret_cast<const __nv_fp8_e4m3 *>(&u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = float(e[i]);
+    }
+    static __device__ __forceinline__ void store(__nv_fp8_e4m3 *p, const float (&v)[8]) {
+        uint2 u;
+        __nv_fp8_e4m3 *e = reinterpret_cast<__nv_fp8_e4m3 *>(&u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = __nv_fp8_e4m3(v[i]);
+        *reinterpret_cast<uint2 *>(p) = u;
     }
 };
 
@@ -246,6 +233,10 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
         norm_rope(v, wk);
         if (valid) {
             if (a.write_k_back) Vec8<TIn>::store(k_io + (size_t)kh * HD + d0, v);
+            if constexpr (sizeof(TKV) == 1) {   // 8-bit cache: stored = value / scale
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { v[e] *= a.k_inv; vv[e] *= a.v_inv; }
+            }
             Vec8<TKV>::store(k_row + (size_t)kh * HD + d0, v);
             Vec8<TKV>::store(v_row + (size_t)kh * HD + d0, vv);
         }
@@ -279,6 +270,8 @@ static bool try_append_fast(shady_ctx *ctx, AppendArgs &a, const void *q_in, con
     else if (i == SHADY_F32 && q == SHADY_F32 && k == SHADY_BF16) launch_append_fast<float, float, __nv_bfloat16>(ctx, a);
     else if (i == SHADY_F16 && q == SHADY_F16 && k == SHADY_F16) launch_append_fast<__half, __half, __half>(ctx, a);
     else if (i == SHADY_BF16 && q == SHADY_BF16 && k == SHADY_BF16) launch_append_fast<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(ctx, a);
+    else if (i == SHADY_F32 && q == SHADY_F32 && k == SHADY_F8E4M3) launch_append_fast<float, float, __nv_fp8_e4m3>(ctx, a);
+    else if (i == SHADY_F16 && q == SHADY_F16 && k == SHADY_F8E4M3) launch_append_fast<__half, __half, __nv_fp8_e4m3>(ctx, a);
     else return false;
     return true;
 }
@@ -296,6 +289,7 @@ int launch_append_kv_table(shady_ctx *ctx, const shady_append_params *p, const v
     a.num_seqs = p->num_seqs; a.T = p->tokens_per_seq;
     a.in_dtype = a.q_dtype = a.kv_dtype = p->in_dtype;
     a.skip_q = 1; a.cs_table = d_cs_table;
+    a.k_inv = a.v_inv = 1.0f;
     for (uint32_t i = 0; i < p->rotary_dim / 2; ++i)   // wgsl:57, same libm call as everywhere else
         a.inv_freq[i] = 1.0f / powf(p->rope_theta, 2.0f * (float)i / (float)p->rotary_dim);
     SHADY_REQUIRE(ctx, (unsigned long long)a.num_seqs * a.T <= 0x3fffffffull, SHADY_ERR_UNSUPPORTED, "attn_prefill_append: too many tokens for one launch");
@@ -320,7 +314,7 @@ int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_
     SHADY_REQUIRE(ctx, p->head_dim <= 256, SHADY_ERR_UNSUPPORTED, "kv_append_rope: head_dim > 256 (the reference shader's limit)");
     SHADY_REQUIRE(ctx, p->rotary_dim <= p->head_dim && (p->rotary_dim % 2) == 0, SHADY_ERR_BAD_ARG,
                   "kv_append_rope: rotary_dim must be even and <= head_dim");
-    SHADY_REQUIRE(ctx, p->in_dtype <= SHADY_BF16 && p->q_dtype <= SHADY_BF16 && cache->dtype <= SHADY_BF16,
+    SHADY_REQUIRE(ctx, p->in_dtype <= SHADY_BF16 && p->q_dtype <= SHADY_BF16 && cache->dtype <= SHADY_F8E4M3,
                   SHADY_ERR_BAD_ARG, "kv_append_rope: bad dtype");
     SHADY_REQUIRE(ctx, !p->has_gate || d_q_gate, SHADY_ERR_BAD_ARG, "kv_append_rope: has_gate needs d_q_gate");
     SHADY_REQUIRE(ctx, (cache->d_k_ptrs && cache->d_v_ptrs) || (cache->d_k_base && cache->d_v_base),
@@ -335,6 +329,7 @@ int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_
     a.num_seqs = p->num_seqs; a.T = p->tokens_per_seq;
     a.in_dtype = p->in_dtype; a.q_dtype = p->q_dtype; a.kv_dtype = cache->dtype;
     a.has_gate = p->has_gate; a.write_k_back = p->write_k_back;
+    a.k_inv = 1.0f / a.kv.k_scale; a.v_inv = 1.0f / a.kv.v_scale;
     // apply_mrope: freq = 1.0 / pow(ROPE_THETA, 2.0 * f32(freq_idx) / f32(PARTIAL_DIM))  (wgsl:57)
     for (uint32_t i = 0; i < p->rotary_dim / 2; ++i)
         a.inv_freq[i] = 1.0f / powf(p->rope_theta, 2.0f * (float)i / (float)p->rotary_dim);

@@ -509,6 +509,12 @@ __device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// D += A (16 x 32 e4m3, row) * B (32 x 8 e4m3, col), f32 accumulate: a thread holds four consecutive k per register
+__device__ __forceinline__ void mma16832_e4m3(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 template <>
 __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -525,13 +531,30 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
+// Two e4m3 bytes -> f16x2 holding value / 256, exact.  `SEL` picks the bytes of x: the low half of the result comes
+// from byte (SEL & 0xf), the high half from byte (SEL >> 4).  An e4m3 byte s.eeee.mmm, moved to the top of a 16-bit
+// half and its magnitude shifted right by one, reads as the f16 s.0eeee.mmm0000000: 2^(e-15) (1 + m/8) for e > 0 and
+// the f16 subnormal m 2^-17 for e = 0 — in both cases the e4m3 value times 2^-8, so one factor 256 on the score
+// scale (K) and on the output (V) puts it right.  Three integer-pipe instructions and a byte permute per pair; the
+// conversion instruction (cvt.rn.f16x2.e4m3x2) measured four times slower than the memory stream it has to keep up
+// with (the 8-bit batch took as long as the 16-bit one).
+constexpr float kE4M3Unscale = 256.0f;
+template <uint32_t SEL> __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t x) {
+    // bytes: result byte 1 <- x byte (SEL & 0xf), result byte 3 <- x byte (SEL >> 4), bytes 0 and 2 <- 0
+    const uint32_t y = __byte_perm(x, 0u, 0x0404u | ((SEL & 0xfu) << 4) | ((SEL >> 4) << 12));
+    return ((y & 0x7f007f00u) >> 1) | (y & 0x80008000u);
+}
+
 constexpr int kBlk = (int)kBlkPos;  // positions per warp block (one MMA k-step of P·V)
 
-template <int HD, int NW, int STAGES, int KPC> struct Decode16Smem {
-    static constexpr int kRowBytes = HD * 2;
+template <int HD, int NW, int STAGES, int KPC, bool F8 = false> struct Decode16Smem {
+    static constexpr int kRowBytes = HD * (F8 ? 1 : 2);          // one kv head's part of a cache row
     static constexpr int kTileBytes = kBlk * kRowBytes;          // one K or V block
     static constexpr int kWarpBytes = STAGES * kTileBytes;       // ring of STAGES tile slots; K and V tiles alternate in it
-    static constexpr int kQTile = 16 * kRowBytes;                // Q rows of one kv head
+    // Q rows of one kv head: 16-bit rows, or (8-bit cache) three planes of e4m3 bytes whose sum is Q (see the kernel)
+    static constexpr int kQRowBytes = HD * (F8 ? 1 : 2);
+    static constexpr int kQPlane = 16 * kQRowBytes;
+    static constexpr int kQTile = (F8 ? 3 : 1) * kQPlane;
     static constexpr int kQBytes = KPC * kQTile;
     static constexpr int kStatBytes = (2 * NW * 16 * 4 > HD * 4) ? 2 * NW * 16 * 4 : HD * 4;   // merge m and l; cos/sin table of the fused append
     static constexpr int kTotal = kQBytes + NW * kWarpBytes + kStatBytes + 32;
@@ -872,17 +895,29 @@ constexpr int decode16_min_blocks(int HD, int NW, int STAGES) {
 // measured slower (59.9 us: the counter's answer is one more dependent memory round trip per block, and under load
 // a round trip is a whole iteration).  Which rows a warp saw does not matter to the result: its (m, l, O) state is
 // merged by log-sum-exp like any other.
-template <typename T, int HD, int NW, int STAGES, int KPC, bool ILV = false>
-__global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) decode16_kernel(const __grid_constant__ DecodeArgs a) {
-    using S = Decode16Smem<HD, NW, STAGES, KPC>;
+// F8: the cache holds e4m3 bytes (T is __half).  Tiles are half as large; a 16-byte chunk is 16 head dims.
+//   S = Q K^T runs on the 8-bit tensor path (mma m16n8k32 e4m3 x e4m3 -> f32): ldmatrix hands a thread four
+//   consecutive dims of a K row, which is that MMA's B fragment as it stands, so K is never converted.  Q (f16 or
+//   f32 from the caller) is staged as THREE e4m3 planes whose sum is 16 Q — p0 = e4m3(16 q), p1 = e4m3(16 q - p0),
+//   p2 = e4m3(16 q - p0 - p1) — about twelve significant bits, more than f16 carries, and the three products add
+//   up in the same f32 accumulator; the 1/16 rides on the score scale.
+//   O += P V stays f16 (P would lose its precision in 8 bits): ldmatrix.trans hands a thread the bytes (pos 2t, dims
+//   2g, 2g+1) and (pos 2t+1, dims 2g, 2g+1); a byte permute and three integer instructions turn them into the f16 B
+//   fragments of the even and of the odd dim, so the accumulator tiles of a 16-dim group hold its even and its odd
+//   dims and the epilogue interleaves them.
+template <typename T, int HD, int NW, int STAGES, int KPC, bool ILV = false, bool F8 = false>
+__global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, F8 ? STAGES / 2 : STAGES)) decode16_kernel(const __grid_constant__ DecodeArgs a) {
+    using S = Decode16Smem<HD, NW, STAGES, KPC, F8>;
     constexpr int WPK = NW / KPC;
+    static_assert(!F8 || (KPC == 1 && sizeof(T) == 2), "8-bit caches: one kv head per CTA, f16 arithmetic");
     static_assert(!ILV || KPC == 1, "the interleaved mode serves one kv head per CTA");
     // a tile is requested STAGES-1 tiles ahead of its use: the K-phase of iteration i requests a tile of block
     // i + kOffK, the V-phase one of block i + kOffV
     constexpr int kOffK = (STAGES - 1) / 2, kOffV = STAGES / 2;
     static_assert(NW % KPC == 0, "warps must divide evenly over the kv heads of a CTA");
-    constexpr int CH = HD / 8;            // 16-byte chunks per row
-    constexpr bool QREG = HD <= 128;      // keep the Q fragments in registers (else re-read them from shared memory)
+    constexpr int CH = HD / 8;            // 16-byte chunks per 16-bit row (Q, and the projections of the fused append)
+    constexpr int CHK = S::kRowBytes / 16;   // 16-byte chunks per K/V tile row
+    constexpr bool QREG = HD <= 128 && !F8;   // keep the f16 Q fragments in registers (else re-read them from shared memory)
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char *sm_q = smem;
     unsigned char *sm_pipe = smem + S::kQBytes;
@@ -915,7 +950,7 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
     // per-lane load geometry: a warp instruction copies 512 bytes = 512/kRowBytes rows
     constexpr int RPI = 512 / S::kRowBytes;          // rows per instruction (2 for hd128, 1 for hd256)
     constexpr int NI = kBlk / RPI;                   // instructions per tile
-    const uint32_t l_row = lane / CH * (RPI > 1), l_chunk = lane % CH;
+    const uint32_t l_row = lane / CHK * (RPI > 1), l_chunk = lane % CHK;
 
     Piece p;
     bool ilv_todo = ILV;
@@ -934,9 +969,8 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
         const uint32_t my_n = nblk > sub ? (nblk - sub + WPK - 1) / WPK : 0;
         // The pipeline moves single tiles: item 2i is the K tile of the warp's i-th block, item 2i+1 its V tile,
         // item t lives in slot t % STAGES, and STAGES-1 items are in flight while one is being consumed.
-        const uint32_t n_items = 2 * my_n;
         constexpr int NIT = (2 * CH + 31) / 32;   // K and V chunks per lane
-        const bool tail = !ILV && a.fuse_append && p.L > 0 && p.end == p.L;
+        const bool tail = !ILV && !F8 && a.fuse_append && p.L > 0 && p.end == p.L;
         const bool owner = tail && ((nblk - 1) % WPK == sub) && KPC == 1;
         // interleaved mode: the warp's i-th block is block ilv_g + i * ilv_w of the sequence
         const uint32_t ilv_w = a.spans * NW, ilv_g = work * NW + warp;
@@ -1007,10 +1041,10 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             }
         }
         // ---- start the K/V stream, the rest of the prologue runs underneath it ----
-#pragma unroll
         // block number (within the piece) of the warp's i-th block, and how many it has
         auto block_of = [&](uint32_t i) { return ILV ? ilv_g + i * ilv_w : sub + i * WPK; };
         const uint32_t w_n = ILV ? ilv_n : my_n, w_items = 2 * w_n;
+#pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
             if ((uint32_t)s < w_items) issue(s, block_of(s >> 1));
             cp_async_commit();
@@ -1069,7 +1103,7 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
                 }
                 uint4 v;
                 v.x = pack2<T>(v8[0], v8[1]); v.y = pack2<T>(v8[2], v8[3]); v.z = pack2<T>(v8[4], v8[5]); v.w = pack2<T>(v8[6], v8[7]);
-                *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kRowBytes + ((c ^ (r & 7)) << 4)) = v;
+                *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kQRowBytes + ((c ^ (r & 7)) << 4)) = v;
             }
         } else
         for (uint32_t idx = tid; idx < KPC * 16 * CH; idx += NW * 32) {
@@ -1086,7 +1120,26 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
                     v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.q) + e0);
                 }
             }
-            *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kRowBytes + ((c ^ (r & 7)) << 4)) = v;
+            if constexpr (F8) {
+                // eight dims -> eight bytes in each of the three planes (8-byte half (c & 1) of 16-byte chunk c / 2)
+                const __half2 *hv = reinterpret_cast<const __half2 *>(&v);
+                unsigned long long plane[3] = {0ull, 0ull, 0ull};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float x = 16.0f * ((e & 1) ? __high2float(hv[e >> 1]) : __low2float(hv[e >> 1]));
+#pragma unroll
+                    for (int pl = 0; pl < 3; ++pl) {
+                        const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+                        plane[pl] |= (unsigned long long)b << (8 * e);
+                        x -= __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));   // exact: both are f32 here
+                    }
+                }
+                unsigned char *rowp = sm_q + k * S::kQTile + r * S::kQRowBytes + (((c >> 1) ^ (r & 7)) << 4) + (c & 1) * 8;
+#pragma unroll
+                for (int pl = 0; pl < 3; ++pl) *reinterpret_cast<unsigned long long *>(rowp + pl * S::kQPlane) = plane[pl];
+            } else {
+                *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kQRowBytes + ((c ^ (r & 7)) << 4)) = v;
+            }
         }
         __syncthreads();
         if (owner) {   // (fused append, second half) norm + RoPE of the new K row, V as it is; cache stores; kept for the patch
@@ -1134,7 +1187,7 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
                 const uint32_t row = (mat & 1) * 8 + rin, chunk = 2 * ks + (mat >> 1);
-                ldsm_x4(qa[ks], sm_q_addr + row * S::kRowBytes + ((chunk ^ rin) << 4));
+                ldsm_x4(qa[ks], sm_q_addr + row * S::kQRowBytes + ((chunk ^ rin) << 4));
             }
         }
 
@@ -1154,6 +1207,24 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             if (owner && i == w_n - 1) patch_tile(st, pos0, 0u);
             // ---- S = Q K^T : heads x 16 positions ----
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            if constexpr (F8) {
+                // a k-step of the 8-bit MMA is 32 dims = two 16-byte chunks; the K registers ldmatrix delivers (row g,
+                // bytes 4t..4t+3 of each chunk) are its B fragments, the Q planes' registers its A fragments
+#pragma unroll
+                for (int ks = 0; ks < HD / 32; ++ks) {
+                    uint32_t kb[4];   // (pos 0-7, chunk 2ks), (pos 0-7, chunk 2ks+1), (pos 8-15, chunk 2ks), (pos 8-15, chunk 2ks+1)
+                    const uint32_t row = (mat >> 1) * 8 + rin, chunk = 2 * ks + (mat & 1);
+                    ldsm_x4(kb, st + row * S::kRowBytes + ((chunk ^ rin) << 4));
+                    const uint32_t qrow = (mat & 1) * 8 + rin, qchunk = 2 * ks + (mat >> 1);
+#pragma unroll
+                    for (int pl = 0; pl < 3; ++pl) {
+                        uint32_t qf[4];   // (rows 0-7, chunk 2ks), (rows 8-15, chunk 2ks), (rows 0-7, chunk 2ks+1), (rows 8-15, chunk 2ks+1)
+                        ldsm_x4(qf, sm_q_addr + pl * S::kQPlane + qrow * S::kQRowBytes + ((qchunk ^ rin) << 4));
+                        mma16832_e4m3(s[0], qf, kb[0], kb[1]);
+                        mma16832_e4m3(s[1], qf, kb[2], kb[3]);
+                    }
+                }
+            } else {
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
                 uint32_t kb[4];
@@ -1164,10 +1235,11 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
                     mma16816<T>(s[1], qa[ks], kb[2], kb[3]);
                 } else {
                     const uint32_t qrow = (mat & 1) * 8 + rin, qchunk = 2 * ks + (mat >> 1);
-                    ldsm_x4(qa[0], sm_q_addr + qrow * S::kRowBytes + ((qchunk ^ rin) << 4));
+                    ldsm_x4(qa[0], sm_q_addr + qrow * S::kQRowBytes + ((qchunk ^ rin) << 4));
                     mma16816<T>(s[0], qa[0], kb[0], kb[1]);
                     mma16816<T>(s[1], qa[0], kb[2], kb[3]);
                 }
+            }
             }
             // ---- online softmax (log2 domain), rows g and g+8 ----
             float mx[2] = {-INFINITY, -INFINITY};
@@ -1198,6 +1270,9 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
                 }
             l_run[0] = l_run[0] * corr[0] + psum[0];
             l_run[1] = l_run[1] * corr[1] + psum[1];
+            // O is rescaled only when some row's maximum grew in this block (after the first few blocks of a piece that
+            // is rare): HD/2 multiplies per lane saved in the common case
+            const bool rescale = __any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f);
             uint32_t pa[4];
             pa[0] = pack2<T>(s[0][0], s[0][1]);
             pa[1] = pack2<T>(s[0][2], s[0][3]);
@@ -1210,18 +1285,43 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             cp_async_commit();
             const uint32_t stv = warp_smem + ((2 * i + 1) % STAGES) * S::kTileBytes;
             if (owner && i == w_n - 1) patch_tile(stv, pos0, 1u);
+            if constexpr (F8) {
+                // chunk c = dims 16c .. 16c+15; accumulator tile 2c holds its even dims, tile 2c+1 its odd dims
+#pragma unroll
+                for (int c2 = 0; c2 < HD / 16; c2 += 2) {
+                    uint32_t vb[4];   // (pos 0-7, chunk c2), (pos 8-15, chunk c2), (pos 0-7, chunk c2+1), (pos 8-15, chunk c2+1)
+                    const uint32_t row = (mat & 1) * 8 + rin, chunk = c2 + (mat >> 1);
+                    ldsm_x4_t(vb, stv + row * S::kRowBytes + ((chunk ^ rin) << 4));
+                    if (rescale) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            o[2 * c2 + u][0] *= corr[0]; o[2 * c2 + u][1] *= corr[0];
+                            o[2 * c2 + u][2] *= corr[1]; o[2 * c2 + u][3] *= corr[1];
+                        }
+                    }
+                    // a register holds (pos 2t, dim 2g), (pos 2t, dim 2g+1), (pos 2t+1, dim 2g), (pos 2t+1, dim 2g+1)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        mma16816<T>(o[2 * (c2 + h)], pa, e4m3x2_to_f16x2<0x20>(vb[2 * h]), e4m3x2_to_f16x2<0x20>(vb[2 * h + 1]));
+                        mma16816<T>(o[2 * (c2 + h) + 1], pa, e4m3x2_to_f16x2<0x31>(vb[2 * h]), e4m3x2_to_f16x2<0x31>(vb[2 * h + 1]));
+                    }
+                }
+            } else {
 #pragma unroll
             for (int jn = 0; jn < HD / 8; jn += 2) {
                 uint32_t vb[4];
                 const uint32_t row = (mat & 1) * 8 + rin, chunk = jn + (mat >> 1);
                 ldsm_x4_t(vb, stv + row * S::kRowBytes + ((chunk ^ rin) << 4));
+                if (rescale) {
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    o[jn + u][0] *= corr[0]; o[jn + u][1] *= corr[0];
-                    o[jn + u][2] *= corr[1]; o[jn + u][3] *= corr[1];
+                    for (int u = 0; u < 2; ++u) {
+                        o[jn + u][0] *= corr[0]; o[jn + u][1] *= corr[0];
+                        o[jn + u][2] *= corr[1]; o[jn + u][3] *= corr[1];
+                    }
                 }
                 mma16816<T>(o[jn], pa, vb[0], vb[1]);
                 mma16816<T>(o[jn + 1], pa, vb[2], vb[3]);
+            }
             }
         }
         cp_async_wait<0>();
@@ -1241,6 +1341,23 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
             sm_l[warp * 16 + g] = l_run[0];
             sm_l[warp * 16 + g + 8] = l_run[1];
         }
+        if constexpr (F8) {
+            // tiles 2c / 2c+1 hold the even / odd dims of group c: columns (2t, 2t+1) are dims 16c + 4t + {0, 2} / {1, 3};
+            // the cache scale of V is applied here, once per element of O
+            const float vs = a.kv.v_scale * kE4M3Unscale;
+            if (g < rows_valid) {
+#pragma unroll
+                for (int c = 0; c < HD / 16; ++c)
+                    *reinterpret_cast<float4 *>(my_o + g * S::kORow + c * 16 + 4 * t) =
+                        make_float4(o[2 * c][0] * vs, o[2 * c + 1][0] * vs, o[2 * c][1] * vs, o[2 * c + 1][1] * vs);
+            }
+            if (g + 8 < rows_valid) {
+#pragma unroll
+                for (int c = 0; c < HD / 16; ++c)
+                    *reinterpret_cast<float4 *>(my_o + (g + 8) * S::kORow + c * 16 + 4 * t) =
+                        make_float4(o[2 * c][2] * vs, o[2 * c + 1][2] * vs, o[2 * c][3] * vs, o[2 * c + 1][3] * vs);
+            }
+        } else {
         if (g < rows_valid) {          // only the head rows that exist go to shared memory
 #pragma unroll
             for (int jn = 0; jn < HD / 8; ++jn)
@@ -1250,6 +1367,7 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, STAGES)) 
 #pragma unroll
             for (int jn = 0; jn < HD / 8; ++jn)
                 *reinterpret_cast<float2 *>(my_o + (g + 8) * S::kORow + jn * 8 + 2 * t) = make_float2(o[jn][2], o[jn][3]);
+        }
         }
         __syncthreads();
         // after its first loop finish_piece no longer reads the O tiles: the pipeline memory doubles as merge scratch
@@ -1574,11 +1692,11 @@ __global__ void sigmoid_mul_kernel(float *x, const float *gate, uint32_t n) {
 // ---------------------------------------------------------------------------------------
 // Host launchers
 // ---------------------------------------------------------------------------------------
-template <typename T, int HD, int NW, int STAGES, int KPC, bool ILV = false>
+template <typename T, int HD, int NW, int STAGES, int KPC, bool ILV = false, bool F8 = false>
 static int launch16(shady_ctx *ctx, const DecodeArgs &a, uint32_t blocks) {
-    using S = Decode16Smem<HD, NW, STAGES, KPC>;
+    using S = Decode16Smem<HD, NW, STAGES, KPC, F8>;
     static_assert(S::kTotal <= 232448, "shared memory of this configuration exceeds 227 KB");
-    auto kern = decode16_kernel<T, HD, NW, STAGES, KPC, ILV>;
+    auto kern = decode16_kernel<T, HD, NW, STAGES, KPC, ILV, F8>;
     static thread_local int configured_dev = -1;
     if (configured_dev != ctx->device) {
         SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
@@ -1699,7 +1817,7 @@ struct DecodePlan {
     DecodeArgs a;
     Variant16 var;
     uint32_t kpc, blocks;
-    bool f32, half, need_ws, second_launch;
+    bool f32, half, f8, need_ws, second_launch;
     size_t counters_bytes;   // arrival counters + barrier words at the head of the scratch
     size_t scratch_bytes;    // counters + the records this launch writes (<= decode_workspace_bytes)
     dim3 merge_grid;         // second launch (no grid merge): balanced_merge_kernel / shard_merge_p2p_kernel
@@ -1716,13 +1834,17 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
                   "decode: zero-sized problem");
     SHADY_REQUIRE(ctx, p->num_q_heads == p->num_kv_heads * p->heads_per_kv, SHADY_ERR_BAD_ARG,
                   "decode: num_q_heads != num_kv_heads * heads_per_kv");
-    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_BF16, SHADY_ERR_BAD_ARG, "decode: bad cache dtype");
+    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_F8E4M3, SHADY_ERR_BAD_ARG, "decode: bad cache dtype");
     SHADY_REQUIRE(ctx, (cache->d_k_ptrs && cache->d_v_ptrs) || (cache->d_k_base && cache->d_v_base),
                   SHADY_ERR_BAD_ARG, "decode: cache has neither base pointers nor pointer arrays");
-    SHADY_REQUIRE(ctx, p->q_dtype == SHADY_F32 || p->q_dtype == cache->dtype, SHADY_ERR_UNSUPPORTED,
-                  "decode: q_dtype must be f32 or the cache dtype");
-    SHADY_REQUIRE(ctx, p->out_dtype == SHADY_F32 || p->out_dtype == cache->dtype, SHADY_ERR_UNSUPPORTED,
-                  "decode: out_dtype must be f32 or the cache dtype");
+    const bool f8 = cache->dtype == SHADY_F8E4M3;
+    const uint32_t act_dtype = f8 ? (uint32_t)SHADY_F16 : cache->dtype;   // what Q and the output may be besides f32
+    SHADY_REQUIRE(ctx, p->q_dtype == SHADY_F32 || p->q_dtype == act_dtype, SHADY_ERR_UNSUPPORTED,
+                  "decode: q_dtype must be f32 or the cache dtype (f16 for an 8-bit cache)");
+    SHADY_REQUIRE(ctx, p->out_dtype == SHADY_F32 || p->out_dtype == act_dtype, SHADY_ERR_UNSUPPORTED,
+                  "decode: out_dtype must be f32 or the cache dtype (f16 for an 8-bit cache)");
+    SHADY_REQUIRE(ctx, !f8 || (!fa && !d_force_partials), SHADY_ERR_UNSUPPORTED,
+                  "decode: an 8-bit cache is read by shady_attn_decode / _static / _shard (append with shady_kv_append_rope)");
     if (const int st = pending_timeout(ctx, "decode")) return st;
     const uint32_t hd = p->head_dim;
     SHADY_REQUIRE(ctx, hd <= 256, SHADY_ERR_UNSUPPORTED, "decode: head_dim > 256 (the reference shader's limit)");
@@ -1743,7 +1865,8 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
     }
     a.num_seqs = p->num_seqs; a.nkv = p->num_kv_heads; a.nh = p->num_q_heads; a.G = p->heads_per_kv; a.hd = hd;
     a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;
-    a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e;
+    // 8-bit cache: K's scale, and the 1/16 that undoes the scaling of the Q planes, ride on the score scale
+    a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e * a.kv.k_scale * (f8 ? 1.0f / 16.0f : 1.0f);
     a.num_splits = p->num_splits;
     a.out_row_stride = hd; a.lse_stride = 1;
     a.status = status_ref(ctx); a.wait_grid = ctx->wait_grid; a.wait_peer = ctx->wait_peer;
@@ -1785,11 +1908,12 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
         a.gate = nullptr;
     }
     const DecodeKnobs &kn = ctx->knobs;
-    const Variant16 var = variant16(hd, kn.variant);
+    // 8-bit tiles are half as large: twice the slots keep the same bytes in flight per warp
+    const Variant16 var = f8 ? (hd > 128 ? Variant16{8, 6, 1} : Variant16{4, 12, 2}) : variant16(hd, kn.variant);
     // One kv head per CTA measured fastest (sibling CTAs of the other kv heads run next to each other in
     // the grid and fetch the rest of each cache row); the kpc knob packs more kv heads into a CTA.
     uint32_t kpc = 1u;
-    if (!f32 && !fa && kn.kpc && kn.kpc <= kv_heads_per_cta(p->num_kv_heads, hd > 128 ? 4u : var.nw) && (kn.kpc & (kn.kpc - 1)) == 0)
+    if (!f32 && !f8 && !fa && kn.kpc && kn.kpc <= kv_heads_per_cta(p->num_kv_heads, hd > 128 ? 4u : var.nw) && (kn.kpc & (kn.kpc - 1)) == 0)
         kpc = kn.kpc;
     const uint32_t kv_groups = p->num_kv_heads / kpc;
     uint32_t ctas_per_sm = kn.ctas_per_sm ? kn.ctas_per_sm : (f32 ? 4u : var.ctas_per_sm);
@@ -1845,9 +1969,9 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
     if (a.defer_merge && plan->need_ws && !f32 && kn.grid_merge && !kn.ctas_per_sm) {   // (a single span has no workspace)
         a.grid_merge = 1;
         // one sequence of many spans in the default configuration: its blocks are interleaved over all warps
-        if (kn.interleave && p->num_seqs == 1 && !fa && !a.kv.page_table && kpc == 1 && kn.variant == 0) a.interleave = 1;
+        if (kn.interleave && p->num_seqs == 1 && !fa && !f8 && !a.kv.page_table && kpc == 1 && kn.variant == 0) a.interleave = 1;
     }
-    plan->var = var; plan->kpc = kpc; plan->f32 = f32; plan->half = cache->dtype == SHADY_F16;
+    plan->var = var; plan->kpc = kpc; plan->f32 = f32; plan->half = cache->dtype == SHADY_F16; plan->f8 = f8;
     plan->second_launch = a.defer_merge && !a.grid_merge;
     plan->merge_grid = px ? dim3(1, p->num_q_heads, p2p_chunks(hd)) : dim3(p->num_seqs, p->num_q_heads, (hd + 63) / 64);
     return SHADY_OK;
@@ -1871,7 +1995,9 @@ static int run_decode(shady_ctx *ctx, const shady_decode_params *p, DecodePlan &
     } else {
         const bool h = plan.half;
         const Variant16 &var = plan.var;
-        if (a.interleave) rc = hd == 128 ? launch16_ilv<128, 4, 6>(ctx, a, h, blocks) : launch16_ilv<256, 8, 3>(ctx, a, h, blocks);
+        if (plan.f8) rc = hd == 128 ? launch16<__half, 128, 4, 12, 1, false, true>(ctx, a, blocks)
+                                    : launch16<__half, 256, 8, 6, 1, false, true>(ctx, a, blocks);
+        else if (a.interleave) rc = hd == 128 ? launch16_ilv<128, 4, 6>(ctx, a, h, blocks) : launch16_ilv<256, 8, 3>(ctx, a, h, blocks);
         else if (hd == 128) {
             if (var.nw == 8 && var.stages == 6) rc = launch16_kpc<128, 8, 6>(ctx, a, plan.kpc, h, blocks);
             else if (var.nw == 8) rc = launch16_kpc<128, 8, 4>(ctx, a, plan.kpc, h, blocks);

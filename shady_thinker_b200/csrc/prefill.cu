@@ -26,7 +26,7 @@
 //
 // FUSED variant (shady_attn_prefill_append): Q comes straight from the projection (q_proj_full, Q and gate halves
 // per head) instead of from a buffer a separate append pass has normed and rotated.  The raw Q tile lands by TMA in
-// one of three rotating shared-memory buffers; two extra warps apply RMSNorm(1+w) and RoPE to it in place
+// one of three rotating shared-memory buffers; four extra warps apply RMSNorm(1+w) and RoPE to it in place
 // (fused_split_qknorm_kvstore.wgsl:126-166; cos/sin of (position, pair) from a table the K/V pass of the same step
 // wrote), make it visible to the tensor core's proxy and only then signal the MMA issuer; the epilogue multiplies
 // by sigmoid(gate) (sigmoid_mul.wgsl).  The 2 x 134 MB round trip of the rotated Q of a 16k-token step never
@@ -58,7 +58,13 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 enum { BAR_QFULL = 0, BAR_QEMPTY = 3, BAR_QRAW = 6, BAR_KVFULL = 9, BAR_KVEMPTY = 11, BAR_SFULL = 13, BAR_PFULL = 15,
        BAR_OFULL = 17, BAR_COUNT = 19 };
-constexpr uint32_t kQWarps = 2;   // fused: warps that norm and rotate the raw Q tiles
+// fused: four more warps (a warpgroup of their own) norm and rotate the raw Q tiles.  16 warps leave 128 registers
+// per thread at launch, too few for the softmax warps, so the warpgroups trade registers once the roles are taken:
+// the two softmax warpgroups grow to kRegsSoftmax, the producer/issuer warpgroup and the Q warpgroup shrink to
+// kRegsOther (2 x 128 x 176 + 2 x 128 x 80 = 65,536).
+constexpr uint32_t kQWarps = 4;
+constexpr uint32_t kFusedThreads = 512;
+constexpr uint32_t kRegsSoftmax = 176, kRegsOther = 80;
 
 struct PrefillArgs {
     void *out;
@@ -241,7 +247,7 @@ template <> __device__ __forceinline__ uint32_t pack16<__nv_bfloat16>(float lo, 
 }
 
 template <typename T, bool FUSED>
-__global__ void __launch_bounds__(FUSED ? 320 + 32 * kQWarps : 320, 1)
+__global__ void __launch_bounds__(FUSED ? kFusedThreads : 320, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
     constexpr uint32_t NQB = FUSED ? 3u : 2u;   // Q buffers; tile number tq of this CTA lives in buffer tq % NQB
@@ -307,6 +313,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
     // columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i = first 64 columns of S_i
 
+    if (warp >= 8) {
+    // the producer/issuer warpgroup and the Q warpgroup give registers up, the softmax warpgroups (below) take them
+    if constexpr (FUSED) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
     if (warp == 8) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
@@ -428,11 +437,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 gk += nkv; tc[0] += it.n[0]; tc[1] += it.n[1];
             }
         }
-    } else if (FUSED && warp >= 10) {
+    } else if (FUSED && warp >= 10 && warp < 12) {
+        // (the producer/issuer warpgroup's two spare warps: nothing to do until the teardown barrier)
+    } else if (FUSED && warp >= 12) {
         // =============================== Q warps (fused): RMSNorm(1+w) + RoPE of the raw tile, in place ===============================
-        // 16 lanes share a row (8 elements = 16 bytes each), two rows per warp instruction, four per pass of the two
+        // 16 lanes share a row (8 elements = 16 bytes each), two rows per warp instruction, eight per pass of the four
         // warps.  A lane always owns the same 8 head dims, hence the same four rotary pairs and norm weights.
-        const uint32_t qt = tid - 320;                      // 0..63
+        constexpr uint32_t kRowsPerPass = 2 * kQWarps, kPasses = kPM / kRowsPerPass;
+        const uint32_t qt = tid - 384;                      // 0..127
         const uint32_t c = qt & 15, rsub = qt >> 4;         // 16-byte chunk of the row, row within a pass
         float wq[8];
         if (a.norm_w) {
@@ -441,7 +453,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         bool ok = true;
         uint32_t tq = 0;
-        constexpr int kBatch = 4;                           // rows a thread has in flight
+        constexpr int kBatch = 2;                           // rows a thread has in flight (the register budget is 80)
         for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
             const uint32_t w = item_of_round(rnd);
             if (w >= total_items) continue;
@@ -456,7 +468,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 auto load_tab = [&](uint32_t pass0) {
 #pragma unroll
                     for (int u = 0; u < kBatch; ++u) {
-                        const uint32_t pos = min(row_base + (pass0 + u) * 4 + rsub, a.T - 1);
+                        const uint32_t pos = min(row_base + (pass0 + u) * kRowsPerPass + rsub, a.T - 1);
                         const float4 *tp = reinterpret_cast<const float4 *>(a.cs_table + (size_t)pos * 64 + c * 4);
                         tab[u][0] = __ldg(tp);
                         tab[u][1] = __ldg(tp + 1);
@@ -466,19 +478,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 ok = mbar_wait(bar(BAR_QRAW + buf), par, wc, 7);
                 if (!ok) break;
                 unsigned char *tile = smem + kSmemQ + buf * kTileBytes;
-                for (uint32_t pass0 = 0; pass0 < 32; pass0 += kBatch) {
+                for (uint32_t pass0 = 0; pass0 < kPasses; pass0 += kBatch) {
                     uint4 raw[kBatch];
                     uint32_t off[kBatch];
 #pragma unroll
                     for (int u = 0; u < kBatch; ++u) {
-                        const uint32_t r = (pass0 + u) * 4 + rsub;
+                        const uint32_t r = (pass0 + u) * kRowsPerPass + rsub;
                         off[u] = (c >> 3) * kSlabBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
                         raw[u] = *reinterpret_cast<const uint4 *>(tile + off[u]);
                     }
                     float4 cur[kBatch][2];
 #pragma unroll
                     for (int u = 0; u < kBatch; ++u) { cur[u][0] = tab[u][0]; cur[u][1] = tab[u][1]; }
-                    if (pass0 + kBatch < 32) load_tab(pass0 + kBatch);   // next batch's table rows travel under this batch's math
+                    if (pass0 + kBatch < kPasses) load_tab(pass0 + kBatch);   // next batch's table rows travel under this batch's math
 #pragma unroll
                     for (int u = 0; u < kBatch; ++u) {
                         float v[8];
@@ -512,7 +524,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 mbar_arrive(bar(BAR_QFULL + buf));
             }
         }
+    }
     } else {
+        if constexpr (FUSED) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));   // the two softmax warpgroups
         // =============================== softmax (one thread per query row) ===============================
         const uint32_t q = warp >> 2;                   // which 128-row tile
         const uint32_t r = tid & 127;                   // row in the tile == TMEM lane
@@ -787,7 +801,7 @@ static int launch_prefill_impl(shady_ctx *ctx, const char *who, const shady_pref
     }
     const bool bf = p->dtype == SHADY_BF16;
     if (fq) {
-        constexpr unsigned threads = 320 + 32 * kQWarps;
+        constexpr unsigned threads = kFusedThreads;
         if (bf) prefill_kernel<__nv_bfloat16, true><<<blocks, threads, prefill_smem(3), ctx->stream>>>(mq, mk, mv, a);
         else prefill_kernel<__half, true><<<blocks, threads, prefill_smem(3), ctx->stream>>>(mq, mk, mv, a);
     } else {

@@ -8,7 +8,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from . import _lib
-from ._lib import BF16, F16, F32, AppendParams, DecodeParams, KvCache, PrefillParams
+from ._lib import BF16, F8E4M3, F16, F32, AppendParams, DecodeParams, GptqWeight, KvCache, PrefillParams
 from .gpu import GpuContext, _addr
 
 _TORCH_DTYPES = None
@@ -41,11 +41,13 @@ class KvCacheView:
     page_table: object = None    # paged cache: device u32 [num_seqs][max_pages_per_seq]; k_base / v_base are the pools
     page_rows: int = 0
     max_pages_per_seq: int = 0
+    k_scale: float = 0.0         # 8-bit (e4m3) cache: value = stored * scale; 0 means 1
+    v_scale: float = 0.0
 
     def c_struct(self) -> KvCache:
         return KvCache(_addr(self.k_base) or None, _addr(self.v_base) or None, self.seq_stride,
                        _addr(self.k_ptrs) or None, _addr(self.v_ptrs) or None, self.dtype, self.page_rows,
-                       _addr(self.page_table) or None, self.max_pages_per_seq, 0)
+                       _addr(self.page_table) or None, self.max_pages_per_seq, self.k_scale, self.v_scale, 0)
 
 
 def kv_append_rope(gpu: GpuContext, *, q_proj_full, k_proj, v_proj, q_out, q_gate, cache: KvCacheView, pos_start,
@@ -196,6 +198,40 @@ def attn_prefill_append(gpu: GpuContext, *, q_proj_full, k_proj, v_proj, cache: 
     gpu._check(gpu._L.shady_attn_prefill_append(gpu.handle, C.byref(ap), C.byref(p), _addr(q_proj_full), _addr(k_proj),
                                                 _addr(v_proj), _addr(qk_norm_bf16) or None, C.byref(c), _addr(out),
                                                 _addr(workspace), workspace_bytes))
+
+
+@dataclass
+class GptqMatrix:
+    """One symmetric INT4 weight in the reference's layout (src/weights.rs:252-257): ``qweight`` device u32
+    [K/8][N], ``scales`` device f16 [K/group_size][N]."""
+
+    qweight: object
+    scales: object
+    K: int
+    N: int
+    group_size: int
+
+    def c_struct(self) -> GptqWeight:
+        return GptqWeight(_addr(self.qweight), _addr(self.scales), self.K, self.N, self.group_size, 0)
+
+
+def gptq_matvec(gpu: GpuContext, w: GptqMatrix, x, y, num_vecs: int = 1) -> None:
+    """``Model::gptq_matvec`` (model.rs:357-381): y[v] = W^T x[v], f32."""
+    c = w.c_struct()
+    gpu._check(gpu._L.shady_gptq_matvec(gpu.handle, C.byref(c), _addr(x), _addr(y), num_vecs))
+
+
+def qkv_proj_append(gpu: GpuContext, *, wq: GptqMatrix, wk: GptqMatrix, wv: GptqMatrix, x, q_out, q_gate,
+                    cache: KvCacheView, pos_start, num_heads: int, num_kv_heads: int, head_dim: int, rope_theta: float,
+                    rotary_dim: int, interleaved: bool = True, eps: float = 1e-6, qk_norm_bf16=None, num_seqs: int = 1,
+                    q_dtype: int = F32, has_gate: bool = True, pos_h=None, pos_w=None) -> None:
+    """The q/k/v projections of one token per sequence and the append (model.rs:698-714 + 723) in one launch."""
+    p = AppendParams(num_heads, num_kv_heads, head_dim, eps, rope_theta, rotary_dim, rotary_dim // 2, rotary_dim // 2,
+                     int(interleaved), num_seqs, 1, F32, q_dtype, int(has_gate), 0, 0)
+    cq, ck, cv, c = wq.c_struct(), wk.c_struct(), wv.c_struct(), cache.c_struct()
+    gpu._check(gpu._L.shady_qkv_proj_append(gpu.handle, C.byref(p), C.byref(cq), C.byref(ck), C.byref(cv), _addr(x),
+                                            _addr(q_out), _addr(q_gate) or None, C.byref(c), _addr(qk_norm_bf16) or None,
+                                            _addr(pos_start), _addr(pos_h) or None, _addr(pos_w) or None))
 
 
 def sigmoid_mul(gpu: GpuContext, x, gate, n: int) -> None:

@@ -36,7 +36,7 @@ def test_struct_sizes_match_header():
     assert C.sizeof(_lib.DecodeParams) == 32      # same size as the reference's 8 x u32 Params
     assert C.sizeof(_lib.AppendParams) == 64
     assert C.sizeof(_lib.PrefillParams) == 24
-    assert C.sizeof(_lib.KvCache) == 64
+    assert C.sizeof(_lib.KvCache) == 72
 
 
 def test_ctx_create_fails_cleanly_without_a_gpu(lib):

@@ -1,0 +1,177 @@
+"""8-bit (e4m3) KV caches: the append quantises, the decode kernel reads the bytes and converts them exactly.
+
+The oracle's input is what the cache holds (``oracle.round_e4m3``: round to nearest even at 3 mantissa bits,
+saturate at 448, per-cache scale), upcast to f32 — so the 2e-2 relative tolerance measures accumulation, softmax
+and P-rounding error only, as for the 16-bit caches.
+"""
+import numpy as np
+import pytest
+import torch
+
+from _util import RTOL_16, rel_err, to_dev, to_host
+from shady_thinker_b200 import ops
+from shady_thinker_b200._lib import F8E4M3, F16, F32, ShadyError
+from shady_thinker_b200.batch import BatchedDecoder
+
+pytestmark = pytest.mark.gpu
+
+
+def _to_e4m3_dev(stored):
+    """f32 values that already lie on the e4m3 grid -> device tensor of e4m3 bytes."""
+    t = torch.from_numpy(np.ascontiguousarray(stored, np.float32)).cuda().to(torch.float8_e4m3fn).contiguous()
+    assert torch.equal(t.float().cpu(), torch.from_numpy(np.ascontiguousarray(stored, np.float32)))
+    return t
+
+
+def _decode(gpu, q, views_k, views_v, lens, *, nh, nkv, hd, ks, vs, num_splits=0, q_dt=F16, out_dt=F32):
+    S = len(lens)
+    k_ptrs = torch.tensor([t.data_ptr() for t in views_k], dtype=torch.int64).cuda()
+    v_ptrs = torch.tensor([t.data_ptr() for t in views_v], dtype=torch.int64).cuda()
+    view = ops.KvCacheView(F8E4M3, k_ptrs=k_ptrs, v_ptrs=v_ptrs, k_scale=ks, v_scale=vs)
+    d_out = torch.full((S, nh, hd), float("nan"), dtype=torch.float32 if out_dt == F32 else torch.float16, device="cuda")
+    d_lse = torch.full((S, nh), float("nan"), device="cuda")
+    ws_n = ops.decode_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_splits=num_splits, num_seqs=S)
+    ws = torch.zeros(max(ws_n, 4), dtype=torch.uint8, device="cuda")
+    ops.attn_decode(gpu, q=to_dev(q, q_dt), cache=view, seq_lens=torch.tensor(lens, dtype=torch.int32).cuda(), out=d_out,
+                    head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_seqs=S, num_splits=num_splits, seq_lens_host=lens,
+                    q_dtype=q_dt, out_dtype=out_dt, lse=d_lse, workspace=ws, workspace_bytes=ws_n)
+    gpu.synchronize()
+    return to_host(d_out), to_host(d_lse)
+
+
+@pytest.mark.parametrize("hd,nh,nkv,lens,ks,vs", [
+    (128, 32, 8, [700, 33, 1500, 16, 2049, 1, 0, 5000], 0.0, 0.0),           # ragged batch, scale 1
+    (128, 8, 2, [3000], 0.05, 0.125),                                       # scales that are not 1
+    (256, 16, 2, [40000], 0.02, 0.03),                                      # long context: records merged by the grid
+    (256, 8, 1, [17, 300], 1.0, 0.5),
+])
+def test_decode_over_an_e4m3_cache_matches_f64_on_the_dequantised_rows(gpu_ctx, oracle, hd, nh, nkv, lens, ks, vs):
+    S = len(lens)
+    sk, sv = (ks or 1.0), (vs or 1.0)
+    q = oracle.round_f16(oracle.randn((S, nh, hd), 81, 1))
+    kraw = [oracle.randn((max(L, 1), nkv, hd), 81, 10 + i) for i, L in enumerate(lens)]
+    vraw = [oracle.randn((max(L, 1), nkv, hd), 81, 50 + i) for i, L in enumerate(lens)]
+    kq = [oracle.round_e4m3(k, sk) for k in kraw]          # what the cache means (dequantised) ...
+    vq = [oracle.round_e4m3(v, sv) for v in vraw]
+    dk = [_to_e4m3_dev(oracle.e4m3_stored(k, sk)) for k in kraw]   # ... and what it holds
+    dv = [_to_e4m3_dev(oracle.e4m3_stored(v, sv)) for v in vraw]
+    for q_dt, out_dt in ((F16, F32), (F32, F16)):
+        out, lse = _decode(gpu_ctx, q, dk, dv, lens, nh=nh, nkv=nkv, hd=hd, ks=ks, vs=vs, q_dt=q_dt, out_dt=out_dt)
+        for i, L in enumerate(lens):
+            if L == 0:
+                assert np.all(out[i] == 0) and np.all(np.isneginf(lse[i]))
+                continue
+            ref = oracle.attention_f64(q[i], kq[i], vq[i], L)
+            assert rel_err(out[i], ref) <= RTOL_16, (i, L, q_dt)
+
+
+def test_explicit_splits_and_static_entry_point(gpu_ctx, oracle):
+    nh, nkv, hd, L = 16, 2, 128, 777
+    q = oracle.round_f16(oracle.randn((1, nh, hd), 82, 1))
+    k = oracle.round_e4m3(oracle.randn((L, nkv, hd), 82, 2))
+    v = oracle.round_e4m3(oracle.randn((L, nkv, hd), 82, 3))
+    dk, dv = _to_e4m3_dev(k), _to_e4m3_dev(v)
+    ref = oracle.attention_f64(q[0], k, v, L)
+    for ns in (1, 3, 8):
+        out, _ = _decode(gpu_ctx, q, [dk], [dv], [L], nh=nh, nkv=nkv, hd=hd, ks=0.0, vs=0.0, num_splits=ns)
+        assert rel_err(out[0], ref) <= RTOL_16, ns
+    d_out = torch.full((1, nh, hd), float("nan"), device="cuda")
+    ops.attn_decode_static(gpu_ctx, q=to_dev(q, F16), cache=ops.KvCacheView(F8E4M3, dk, dv, 0),
+                           seq_lens=torch.tensor([L], dtype=torch.int32).cuda(), out=d_out, head_dim=hd, num_kv_heads=nkv,
+                           num_q_heads=nh, num_seqs=1, num_splits=0, seq_lens_host=[L], q_dtype=F16)
+    gpu_ctx.synchronize()
+    assert rel_err(to_host(d_out)[0], ref) <= RTOL_16
+
+
+@pytest.mark.parametrize("in_dt,rd,norm", [(F32, 32, True), (F16, 128, False), (F16, 32, True)])
+def test_append_quantises_like_the_oracle(gpu_ctx, oracle, in_dt, rd, norm):
+    """K: norm + RoPE in f32, times 1/k_scale, e4m3; V: times 1/v_scale, e4m3 — both the one-warp-per-head kernel
+    (f32 projections, three tokens per sequence) and the vectorised one (f16)."""
+    S, T, nh, nkv, hd, ks, vs = 2, 3, 4, 2, 128, 0.25, 0.5
+    rnd = (lambda a: a) if in_dt == F32 else oracle.round_f16
+    qf = rnd(oracle.randn((S, T, nh, 2, hd), 83, 1))
+    kp = rnd(oracle.randn((S, T, nkv, hd), 83, 2))
+    vp = rnd(oracle.randn((S, T, nkv, hd), 83, 3))
+    w = oracle.bf16_bits(oracle.randn((2 * hd,), 83, 4) * np.float32(0.02)) if norm else None
+    start = np.array([5, 100_000], np.uint32)
+    cap = 100_016
+    d_kc = torch.zeros((S, cap, nkv, hd), dtype=torch.float8_e4m3fn, device="cuda")
+    d_vc = torch.zeros_like(d_kc)
+    d_q = torch.empty((S, T, nh, hd), dtype=torch.float32 if in_dt == F32 else torch.float16, device="cuda")
+    d_g = torch.empty((S, T, nh, hd), device="cuda")
+    ops.kv_append_rope(gpu_ctx, q_proj_full=to_dev(qf, in_dt), k_proj=to_dev(kp, in_dt), v_proj=to_dev(vp, in_dt), q_out=d_q,
+                       q_gate=d_g, cache=ops.KvCacheView(F8E4M3, d_kc, d_vc, cap * nkv * hd, k_scale=ks, v_scale=vs),
+                       pos_start=torch.from_numpy(start.astype(np.int32)).cuda(), num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                       rope_theta=1e6, rotary_dim=rd, num_seqs=S, tokens_per_seq=T, in_dtype=in_dt, q_dtype=in_dt,
+                       has_gate=True, write_k_back=False, qk_norm_bf16=torch.from_numpy(w.view(np.int16)).cuda() if norm else None)
+    gpu_ctx.synchronize()
+    flips = total = 0
+    for s in range(S):
+        for t in range(T):
+            pos = int(start[s]) + t
+            okc, ovc = np.zeros((1, nkv, hd), np.float32), np.zeros((1, nkv, hd), np.float32)
+            oracle.fused_split_qknorm_kvstore(qf[s, t], kp[s, t], vp[s, t], okc, ovc, pos, rope_theta=1e6, rotary_dim=rd,
+                                              qk_norm_bf16=w, cache_position=0)
+            want_k, want_v = oracle.round_e4m3(okc[0], ks), oracle.round_e4m3(ovc[0], vs)
+            got_k = d_kc[s, pos].float().cpu().numpy() * np.float32(ks)
+            got_v = d_vc[s, pos].float().cpu().numpy() * np.float32(vs)
+            np.testing.assert_array_equal(got_v, want_v)           # V is quantised from the input itself
+            # K went through f32 norm/RoPE arithmetic on both sides: a last-bit difference there can move a value that
+            # sits on a rounding boundary to the neighbouring e4m3 value, never further
+            diff = np.abs(got_k - want_k)
+            assert np.all(diff <= np.maximum(np.abs(want_k), ks * 2.0 ** -6) * 0.126), (s, t)
+            flips += int((diff > 0).sum())
+            total += diff.size
+    assert flips <= 0.01 * total
+
+
+def test_batched_decoder_with_an_e4m3_cache(gpu_ctx, oracle):
+    """Three steps of a ragged batch through BatchedDecoder(kv_dtype=F8E4M3): append launch + attend launch per step,
+    against f64 attention over a host mirror of the quantised cache."""
+    S, nh, nkv, hd, steps, ks, vs = 4, 8, 2, 128, 3, 0.05, 0.05
+    start = np.array([0, 40, 1000, 3000], np.uint32)
+    d = BatchedDecoder(gpu_ctx, num_seqs=S, capacities=start + steps, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                       kv_dtype=F8E4M3, rope_theta=1e6, rotary_dim=hd, has_gate=False, num_splits=0, k_scale=ks, v_scale=vs)
+    assert not d.fused and d.act_dtype == F16
+    rows = int(d.row_off[-1])
+    rk, rv = oracle.randn((rows, nkv, hd), 84, 1), oracle.randn((rows, nkv, hd), 84, 2)
+    hk, hv = oracle.round_e4m3(rk, ks), oracle.round_e4m3(rv, vs)
+    gpu_ctx.copy_buffer(_to_e4m3_dev(oracle.e4m3_stored(rk, ks)), d.k_cache[0], d.layer_bytes)
+    gpu_ctx.copy_buffer(_to_e4m3_dev(oracle.e4m3_stored(rv, vs)), d.v_cache[0], d.layer_bytes)
+    worst = 0.0
+    for t in range(steps):
+        d.set_lengths(start + t)
+        q = oracle.round_f16(oracle.randn((S, nh, hd), 84, 100 + t))
+        k = oracle.round_f16(oracle.randn((S, nkv, hd), 84, 200 + t))
+        v = oracle.round_f16(oracle.randn((S, nkv, hd), 84, 300 + t))
+        gpu_ctx.write_buffer(d.q_in, 0, q.astype(np.float16).tobytes())
+        gpu_ctx.write_buffer(d.k_in, 0, k.astype(np.float16).tobytes())
+        gpu_ctx.write_buffer(d.v_in, 0, v.astype(np.float16).tobytes())
+        d.step()
+        gpu_ctx.synchronize()
+        out = np.frombuffer(gpu_ctx.read_buffer(d.out, d.out_bytes), np.float16).astype(np.float32).reshape(S, nh, hd)
+        for s in range(S):
+            pos, r0 = int(start[s]) + t, int(d.row_off[s])
+            okc, ovc = np.zeros((1, nkv, hd), np.float32), np.zeros((1, nkv, hd), np.float32)
+            oq, _, _ = oracle.fused_split_qknorm_kvstore(np.stack([q[s], q[s]], 1), k[s], v[s], okc, ovc, pos, rope_theta=1e6,
+                                                         rotary_dim=hd, cache_position=0)
+            hk[r0 + pos], hv[r0 + pos] = oracle.round_e4m3(okc[0], ks), oracle.round_e4m3(ovc[0], vs)
+            ref = oracle.attention_f64(oracle.round_f16(oq.reshape(nh, hd)), hk[r0:r0 + pos + 1], hv[r0:r0 + pos + 1], pos + 1)
+            worst = max(worst, rel_err(out[s], ref))
+    assert worst <= RTOL_16, worst
+    d.close()
+
+
+def test_entry_points_that_do_not_take_an_e4m3_cache_say_so(gpu_ctx):
+    d = torch.zeros(4096, dtype=torch.float16, device="cuda")
+    c8 = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    lens = torch.ones(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(ShadyError) as e:
+        ops.attn_decode_append(gpu_ctx, q_proj_full=d, k_proj=d, v_proj=d, cache=ops.KvCacheView(F8E4M3, c8, c8, 0), seq_lens=lens,
+                               out=d, num_heads=4, num_kv_heads=1, head_dim=128, rope_theta=1e6, rotary_dim=128, in_dtype=F16,
+                               out_dtype=F16, has_gate=False, seq_lens_host=[1], num_splits=1)
+    assert e.value.code == 2
+    with pytest.raises(ShadyError) as e:
+        ops.attn_prefill(gpu_ctx, q=d, cache=ops.KvCacheView(F8E4M3, c8, c8, 0), out=d, head_dim=128, num_kv_heads=1,
+                         num_q_heads=1, num_seqs=1, seq_len=8, dtype=F16)
+    assert e.value.code == 2
