@@ -214,7 +214,7 @@ def workload_config(n_gpus: int, shape: str = "plain", kv: str = "fp16") -> dict
             "reference-shaped: rotary_dim = head_dim/4 interleaved, QK RMSNorm with bf16 weights, sigmoid gate")
     return {"workload": "cfg2: batched ragged decode attention, one layer, append+attend per step", "rope": rope,
             "seqs_per_gpu": SEQS_PER_GPU, "context": f"uniform[{LMIN},{LMAX}] (seeded)", "num_q_heads": NH,
-            "num_kv_heads": NKV, "head_dim": HD, "kv_dtype": kv if kv == "fp16" else "fp8 e4m3 (algorithmic bytes count one byte per element)",
+            "num_kv_heads": NKV, "head_dim": HD, "kv_dtype": kv if kv == "fp16" else ("fp8 e4m3" if kv == "fp8" else "fp8 e5m2") + " (algorithmic bytes count one byte per element)",
             "q_dtype": "fp16", "accumulate": "fp32",
             "rope_theta": 1e6, "sharding": (f"{SEQS_PER_GPU * n_gpus} sequences dealt to {n_gpus} GPU(s) longest first to the rank with the fewest rows, "
                          "no collective"),
@@ -247,7 +247,7 @@ def cpu_baseline(rank: int, row_off, lens: np.ndarray) -> dict:
 def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     import torch
 
-    from shady_thinker_b200._lib import F8E4M3, F16
+    from shady_thinker_b200._lib import F8E4M3, F8E5M2, F16
     from shady_thinker_b200.batch import BatchedDecoder
     from shady_thinker_b200.gpu import GpuContext
     from shady_thinker_b200 import ops
@@ -269,7 +269,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     S = len(lens)
     sets = []
     ref_shape = args.shape == "reference"
-    kv_dt = F8E4M3 if args.kv == "fp8" else F16      # fp8: e4m3 cache rows (half the bytes per row), f16 activations
+    kv_dt = {"fp8": F8E4M3, "fp8e5m2": F8E5M2}.get(args.kv, F16)      # 8-bit cache rows (half the bytes per row), f16 activations
     qrow = NH * HD * (2 if ref_shape else 1)
     d_norm = None
     if ref_shape:       # bf16 q_norm[hd] then k_norm[hd], N(0, 0.02) (the uniform of model.rs:140-168)
@@ -282,7 +282,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                            num_splits=0, qk_norm_bf16=d_norm)
         d.set_lengths(lens - 1)
         base = 1000 * rank + 10 * i
-        n = d.layer_bytes // (1 if kv_dt == F8E4M3 else 2)
+        n = d.layer_bytes // (2 if kv_dt == F16 else 1)
         ops.fill_randn(gpu, d.k_cache[0], n, kv_dt, SEED, base + 1)
         ops.fill_randn(gpu, d.v_cache[0], n, kv_dt, SEED, base + 2)
         ops.fill_randn(gpu, d.q_in, S * qrow, F16, SEED, base + 3)
@@ -399,7 +399,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                          "peak_source": f"{peak_src} (copy bandwidth)",
                          "kernel": ("decode16_kernel<half,128> with the fused append and split merge (the whole step is this one launch)"
                                     if args.kv == "fp16" else
-                                    "decode16_kernel<half,128,e4m3 cache> (attend launch of the step; the append is a launch of its own)"),
+                                    "decode16_kernel<half,128,8-bit cache> (the step is the append launch plus this attend launch)"),
                          "traffic_source": f"algorithmic bytes x {TRAFFIC_PER_ALGO_BYTE}, the DRAM-byte ratio ncu measured at {TRAFFIC_MEASURED_AT}",
                          "algorithmic_bytes_per_launch": step_bytes, "avg_launch_ms": attend_ms,
                          "avg_launch_ms_single_bracketed": bracketed_ms,
@@ -884,8 +884,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
-    ap.add_argument("--kv", default="fp16", choices=["fp16", "fp8"],
-                    help="cfg2 only: storage of the KV cache (fp8 = e4m3 rows written by the quantising append)")
+    ap.add_argument("--kv", default="fp16", choices=["fp16", "fp8", "fp8e5m2"],
+                    help="cfg2 only: storage of the KV cache (fp8 = e4m3, fp8e5m2 = e5m2 rows written by the quantising append)")
     ap.add_argument("--no-extra", action="store_true",
                     help="cfg2 only: skip the short cfg3 (prefill) and cfg4 (long context) legs added to the line as `extra`")
     ap.add_argument("--shape", default="plain", choices=["plain", "reference"],

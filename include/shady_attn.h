@@ -45,6 +45,7 @@ extern "C" {
 #define SHADY_F16 1
 #define SHADY_BF16 2
 #define SHADY_F8E4M3 3   /* KV cache only: 8-bit e4m3 (4 exponent bits, 3 mantissa bits, no infinities) */
+#define SHADY_F8E5M2 4   /* KV cache only: 8-bit e5m2 (5 exponent bits, 2 mantissa bits: the top byte of an f16) */
 
 typedef struct shady_ctx shady_ctx;
 
@@ -114,10 +115,12 @@ int shady_synchronize(shady_ctx *ctx);
  * shady_attn_decode_append; the other entry points return SHADY_ERR_UNSUPPORTED for them.
  *
  * 8-bit cache (no reference counterpart; the reference's cache is f32, model.rs:241-256): with dtype ==
- * SHADY_F8E4M3 a stored element is round-to-nearest-even e4m3 of value / k_scale (K rows) or value / v_scale
- * (V rows), saturated at +-448; the scales are per cache (0 means 1).  shady_kv_append_rope quantises, and
- * shady_attn_decode / _static / _shard read such caches (head_dim 128 or 256, Q and output f16 or f32); the
- * other entry points return SHADY_ERR_UNSUPPORTED for them.
+ * SHADY_F8E4M3 or SHADY_F8E5M2 a stored element is the round-to-nearest-even 8-bit float of value / k_scale (K
+ * rows) or value / v_scale (V rows), saturated at the format's largest finite value (448 / 57344); the scales are
+ * per cache (0 means 1).  e4m3 keeps one more mantissa bit; e5m2 is cheaper to read (it is the top byte of the f16
+ * the tensor core takes, whereas e4m3 needs integer work per byte that bounds the decode kernel).
+ * shady_kv_append_rope and shady_qkv_proj_append quantise, and shady_attn_decode / _static / _shard read such
+ * caches (head_dim 128 or 256, Q and output f16 or f32); the other entry points return SHADY_ERR_UNSUPPORTED.
  * Zero the struct before filling it: fields added later default to "off". */
 typedef struct {
     void *d_k_base;
@@ -125,11 +128,11 @@ typedef struct {
     uint64_t seq_stride;     /* elements between consecutive sequences (ignored with ptr arrays) */
     void *const *d_k_ptrs;   /* device array [num_seqs] of device pointers, or NULL */
     void *const *d_v_ptrs;
-    uint32_t dtype;          /* SHADY_F32 / SHADY_F16 / SHADY_BF16 / SHADY_F8E4M3 */
+    uint32_t dtype;          /* SHADY_F32 / SHADY_F16 / SHADY_BF16 / SHADY_F8E4M3 / SHADY_F8E5M2 */
     uint32_t page_rows;      /* paged: rows per page (multiple of 16); else 0 */
     const uint32_t *d_page_table;   /* paged: device array [num_seqs][max_pages_per_seq]; else NULL */
     uint32_t max_pages_per_seq;
-    float k_scale;           /* SHADY_F8E4M3: value = stored * scale; 0 = 1 */
+    float k_scale;           /* 8-bit caches: value = stored * scale; 0 = 1 */
     float v_scale;
     uint32_t _pad;
 } shady_kv_cache;

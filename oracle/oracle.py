@@ -235,19 +235,33 @@ def round_f16(a) -> np.ndarray:
     return _f32(a).astype(np.float16).astype(np.float32)
 
 
-def e4m3_stored(a, scale: float = 1.0) -> np.ndarray:
-    """The e4m3 values (as f32, on the e4m3 grid) an 8-bit cache stores for ``a``: ``a * (1/scale)`` in f32, rounded
-    to nearest even at 3 mantissa bits (subnormal step 2^-9), saturated at +-448.  The f32 multiply by the reciprocal
-    is what the append kernels do, so the bytes agree with the device."""
+def _f8_stored(a, scale: float, man_bits: int, min_exp: int, max_val: float) -> np.ndarray:
+    """``a * (1/scale)`` in f32 (what the append kernels compute), rounded to nearest even onto the grid of an 8-bit
+    float with ``man_bits`` mantissa bits whose smallest normal number is 2^min_exp (subnormals below it), saturated
+    at +-max_val.  Returned as f32 values on that grid."""
     x = _f32(a) * (np.float32(1.0) / np.float32(scale)) if scale != 1.0 else _f32(a)
-    ax = np.minimum(np.abs(x.astype(np.float64)), 448.0)
-    e = np.floor(np.log2(np.maximum(ax, 2.0 ** -20)))
-    e = np.maximum(e, -6.0)                       # below 2^-6 the grid is the subnormal one
-    step = 2.0 ** (e - 3)
-    q = np.minimum(np.rint(ax / step) * step, 448.0)   # numpy rounds halves to even
+    ax = np.minimum(np.abs(x.astype(np.float64)), max_val)
+    e = np.floor(np.log2(np.maximum(ax, 2.0 ** -40)))
+    e = np.maximum(e, float(min_exp))             # below the smallest normal the grid is the subnormal one
+    step = 2.0 ** (e - man_bits)
+    q = np.minimum(np.rint(ax / step) * step, max_val)   # numpy rounds halves to even
     return (np.sign(x) * q).astype(np.float32).reshape(np.shape(a))
+
+
+def e4m3_stored(a, scale: float = 1.0) -> np.ndarray:
+    """The e4m3 values (as f32) an 8-bit cache stores for ``a``: 3 mantissa bits, subnormal step 2^-9, +-448."""
+    return _f8_stored(a, scale, 3, -6, 448.0)
+
+
+def e5m2_stored(a, scale: float = 1.0) -> np.ndarray:
+    """The e5m2 values (as f32) an 8-bit cache stores for ``a``: 2 mantissa bits, subnormal step 2^-16, +-57344."""
+    return _f8_stored(a, scale, 2, -14, 57344.0)
 
 
 def round_e4m3(a, scale: float = 1.0) -> np.ndarray:
     """What an 8-bit e4m3 cache with this scale holds for ``a``, dequantised: stored value times scale, as f32."""
     return (e4m3_stored(a, scale).astype(np.float64) * np.float64(np.float32(scale))).astype(np.float32)
+
+
+def round_e5m2(a, scale: float = 1.0) -> np.ndarray:
+    return (e5m2_stored(a, scale).astype(np.float64) * np.float64(np.float32(scale))).astype(np.float32)

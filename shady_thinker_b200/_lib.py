@@ -12,7 +12,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("SHADY_ATTN_LIB") or os.path.join(_PKG, "libshady_attn.so")
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT = range(6)
-F32, F16, BF16, F8E4M3 = 0, 1, 2, 3
+F32, F16, BF16, F8E4M3, F8E5M2 = 0, 1, 2, 3, 4
 
 # every symbol include/shady_attn.h declares
 EXPORTS = [

@@ -15,10 +15,10 @@ import os
 import numpy as np
 
 from . import ops
-from ._lib import BF16, F8E4M3, F16, F32, AppendParams, DecodeParams
+from ._lib import BF16, F8E4M3, F8E5M2, F16, F32, AppendParams, DecodeParams
 from .gpu import GpuContext, _addr
 
-_ESZ = {F32: 4, F16: 2, BF16: 2, F8E4M3: 1}
+_ESZ = {F32: 4, F16: 2, BF16: 2, F8E4M3: 1, F8E5M2: 1}
 
 
 class BatchedDecoder:
@@ -27,12 +27,12 @@ class BatchedDecoder:
                  rotary_dim: int | None = None, interleaved: bool = True, eps: float = 1e-6, has_gate: bool = False,
                  num_layers: int = 1, num_splits: int = 0, qk_norm_bf16=None, k_scale: float = 0.0,
                  v_scale: float = 0.0):
-        """``kv_dtype=F8E4M3`` keeps the caches as 8-bit e4m3 (``k_scale`` / ``v_scale``: value = stored * scale, 0
-        means 1); activations are then f16 and a step is the append launch followed by the attend launch."""
+        """``kv_dtype=F8E4M3`` / ``F8E5M2`` keeps the caches as 8-bit floats (``k_scale`` / ``v_scale``: value = stored *
+        scale, 0 means 1); activations are then f16 and a step is the append launch followed by the attend launch."""
         self.gpu, self.S, self.nh, self.nkv, self.hd = gpu, num_seqs, num_heads, num_kv_heads, head_dim
         self.kv_dtype = kv_dtype
         if act_dtype is None:
-            act_dtype = F16 if kv_dtype == F8E4M3 else kv_dtype
+            act_dtype = F16 if kv_dtype in (F8E4M3, F8E5M2) else kv_dtype
         self.act_dtype = act_dtype
         self.theta, self.rd = rope_theta, head_dim if rotary_dim is None else rotary_dim
         self.interleaved, self.eps, self.has_gate = interleaved, eps, has_gate

@@ -40,10 +40,10 @@ static uint32_t env_u32(const char *name, uint32_t dflt) {
 
 int fill_kv_addr(shady_ctx *ctx, const shady_kv_cache *cache, uint32_t nkv, uint32_t hd, const char *who, KvAddr *out) {
     const std::string w(who);
-    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_F8E4M3, SHADY_ERR_BAD_ARG, w + ": bad cache dtype");
+    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_F8E5M2, SHADY_ERR_BAD_ARG, w + ": bad cache dtype");
     KvAddr kv{};
     kv.k_scale = kv.v_scale = 1.0f;
-    if (cache->dtype == SHADY_F8E4M3) {
+    if (is_f8(cache->dtype)) {
         SHADY_REQUIRE(ctx, cache->k_scale >= 0.f && cache->v_scale >= 0.f && isfinite(cache->k_scale) && isfinite(cache->v_scale),
                       SHADY_ERR_BAD_ARG, w + ": cache scales must be finite and not negative");
         if (cache->k_scale > 0.f) kv.k_scale = cache->k_scale;
@@ -438,7 +438,7 @@ int shady_fill_randn(shady_ctx *ctx, void *d_dst, uint64_t n, uint32_t dtype, ui
                      uint64_t first_idx) {
     CTX_ENTER(ctx);
     SHADY_REQUIRE(ctx, d_dst || !n, SHADY_ERR_BAD_ARG, "fill_randn: null destination");
-    SHADY_REQUIRE(ctx, dtype <= SHADY_F8E4M3, SHADY_ERR_BAD_ARG, "fill_randn: bad dtype");
+    SHADY_REQUIRE(ctx, dtype <= SHADY_F8E5M2, SHADY_ERR_BAD_ARG, "fill_randn: bad dtype");
     if (!n) return SHADY_OK;
     const unsigned long long key = mix64(seed ^ (tensor_id * 0xD1B54A32D192ED03ull));
     const unsigned long long want = (n + 255) / 256;

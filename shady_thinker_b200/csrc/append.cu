@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(const AppendA
         const size_t row = (tok * a.nh + h) * (size_t)hd;
         for (uint32_t d = lane; d < hd; d += 32) store_from_f32(a.q_out, row + d, a.q_dtype, vals[d]);
     } else {
-        const size_t esz = a.kv_dtype == SHADY_F32 ? 4 : (a.kv_dtype == SHADY_F8E4M3 ? 1 : 2);
+        const size_t esz = dtype_size(a.kv_dtype);
         // cache_position == position (model.rs:493-496)
         char *kc = const_cast<char *>(kv_row_ptr(a.kv, false, s, p_t, (size_t)a.nkv * hd * esz));
         char *vc = const_cast<char *>(kv_row_ptr(a.kv, true, s, p_t, (size_t)a.nkv * hd * esz));
@@ -125,21 +125,23 @@ template <> struct Vec8<float> {
     }
 };
 
-template <> struct Vec8<__nv_fp8_e4m3> {   // eight 1-byte elements: an 8-byte access
-    static __device__ __forceinline__ void load(const __nv_fp8_e4m3 *p, float (&v)[8]) {
+template <typename F8T> struct Vec8F8 {   // eight 1-byte elements: an 8-byte access
+    static __device__ __forceinline__ void load(const F8T *p, float (&v)[8]) {
         const uint2 u = *reinterpret_cast<const uint2 *>(p);
-        const __nv_fp8_e4m3 *e = reinterpret_cast<const __nv_fp8_e4m3 *>(&u);
+        const F8T *e = reinterpret_cast<const F8T *>(&u);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = float(e[i]);
     }
-    static __device__ __forceinline__ void store(__nv_fp8_e4m3 *p, const float (&v)[8]) {
+    static __device__ __forceinline__ void store(F8T *p, const float (&v)[8]) {
         uint2 u;
-        __nv_fp8_e4m3 *e = reinterpret_cast<__nv_fp8_e4m3 *>(&u);
+        F8T *e = reinterpret_cast<F8T *>(&u);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) e[i] = __nv_fp8_e4m3(v[i]);
+        for (int i = 0; i < 8; ++i) e[i] = F8T(v[i]);
         *reinterpret_cast<uint2 *>(p) = u;
     }
 };
+template <> struct Vec8<__nv_fp8_e4m3> : Vec8F8<__nv_fp8_e4m3> {};
+template <> struct Vec8<__nv_fp8_e5m2> : Vec8F8<__nv_fp8_e5m2> {};
 
 template <typename TIn, typename TQ, typename TKV, int HD>
 __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const AppendArgs a) {
@@ -272,6 +274,8 @@ static bool try_append_fast(shady_ctx *ctx, AppendArgs &a, const void *q_in, con
     else if (i == SHADY_BF16 && q == SHADY_BF16 && k == SHADY_BF16) launch_append_fast<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(ctx, a);
     else if (i == SHADY_F32 && q == SHADY_F32 && k == SHADY_F8E4M3) launch_append_fast<float, float, __nv_fp8_e4m3>(ctx, a);
     else if (i == SHADY_F16 && q == SHADY_F16 && k == SHADY_F8E4M3) launch_append_fast<__half, __half, __nv_fp8_e4m3>(ctx, a);
+    else if (i == SHADY_F32 && q == SHADY_F32 && k == SHADY_F8E5M2) launch_append_fast<float, float, __nv_fp8_e5m2>(ctx, a);
+    else if (i == SHADY_F16 && q == SHADY_F16 && k == SHADY_F8E5M2) launch_append_fast<__half, __half, __nv_fp8_e5m2>(ctx, a);
     else return false;
     return true;
 }
@@ -314,7 +318,7 @@ int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_
     SHADY_REQUIRE(ctx, p->head_dim <= 256, SHADY_ERR_UNSUPPORTED, "kv_append_rope: head_dim > 256 (the reference shader's limit)");
     SHADY_REQUIRE(ctx, p->rotary_dim <= p->head_dim && (p->rotary_dim % 2) == 0, SHADY_ERR_BAD_ARG,
                   "kv_append_rope: rotary_dim must be even and <= head_dim");
-    SHADY_REQUIRE(ctx, p->in_dtype <= SHADY_BF16 && p->q_dtype <= SHADY_BF16 && cache->dtype <= SHADY_F8E4M3,
+    SHADY_REQUIRE(ctx, p->in_dtype <= SHADY_BF16 && p->q_dtype <= SHADY_BF16 && cache->dtype <= SHADY_F8E5M2,
                   SHADY_ERR_BAD_ARG, "kv_append_rope: bad dtype");
     SHADY_REQUIRE(ctx, !p->has_gate || d_q_gate, SHADY_ERR_BAD_ARG, "kv_append_rope: has_gate needs d_q_gate");
     SHADY_REQUIRE(ctx, (cache->d_k_ptrs && cache->d_v_ptrs) || (cache->d_k_base && cache->d_v_base),

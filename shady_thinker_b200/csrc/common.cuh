@@ -75,7 +75,8 @@ inline StatusRef status_ref(const shady_ctx *ctx) { return StatusRef{ctx->status
         if (!(cond)) return ::shady::fail(ctx, code, msg);        \
     } while (0)
 
-inline size_t dtype_size(uint32_t dt) { return dt == SHADY_F32 ? 4 : (dt == SHADY_F8E4M3 ? 1 : 2); }
+__host__ __device__ inline bool is_f8(uint32_t dt) { return dt == SHADY_F8E4M3 || dt == SHADY_F8E5M2; }
+__host__ __device__ inline size_t dtype_size(uint32_t dt) { return dt == SHADY_F32 ? 4 : (is_f8(dt) ? 1 : 2); }
 
 // ---- dtype conversion -------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f32(T v);
@@ -83,6 +84,7 @@ template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; 
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float to_f32<__nv_fp8_e4m3>(__nv_fp8_e4m3 v) { return float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_fp8_e5m2>(__nv_fp8_e5m2 v) { return float(v); }
 
 template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
@@ -90,18 +92,21 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 // round to nearest even, saturating at the largest finite e4m3 value (448); callers divide by the cache scale first
 template <> __device__ __forceinline__ __nv_fp8_e4m3 from_f32<__nv_fp8_e4m3>(float v) { return __nv_fp8_e4m3(v); }
+template <> __device__ __forceinline__ __nv_fp8_e5m2 from_f32<__nv_fp8_e5m2>(float v) { return __nv_fp8_e5m2(v); }
 
 // Load / store one element of a buffer whose dtype is only known at run time.
 __device__ __forceinline__ float load_as_f32(const void *p, size_t i, uint32_t dt) {
     if (dt == SHADY_F32) return reinterpret_cast<const float *>(p)[i];
     if (dt == SHADY_F16) return __half2float(reinterpret_cast<const __half *>(p)[i]);
     if (dt == SHADY_F8E4M3) return float(reinterpret_cast<const __nv_fp8_e4m3 *>(p)[i]);
+    if (dt == SHADY_F8E5M2) return float(reinterpret_cast<const __nv_fp8_e5m2 *>(p)[i]);
     return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
 }
 __device__ __forceinline__ void store_from_f32(void *p, size_t i, uint32_t dt, float v) {
     if (dt == SHADY_F32) reinterpret_cast<float *>(p)[i] = v;
     else if (dt == SHADY_F16) reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
     else if (dt == SHADY_F8E4M3) reinterpret_cast<__nv_fp8_e4m3 *>(p)[i] = __nv_fp8_e4m3(v);
+    else if (dt == SHADY_F8E5M2) reinterpret_cast<__nv_fp8_e5m2 *>(p)[i] = __nv_fp8_e5m2(v);
     else reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
 }
 

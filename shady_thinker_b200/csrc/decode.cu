@@ -509,11 +509,11 @@ __device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// D += A (16 x 32 e4m3, row) * B (32 x 8 e4m3, col), f32 accumulate: a thread holds four consecutive k per register
-__device__ __forceinline__ void mma16832_e4m3(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// transposes an 8x8 matrix of 16-bit elements held one row per eight threads (the mma C layout -> its B layout)
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
 }
 template <>
 __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -531,30 +531,38 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
-// Two e4m3 bytes -> f16x2 holding value / 256, exact.  `SEL` picks the bytes of x: the low half of the result comes
-// from byte (SEL & 0xf), the high half from byte (SEL >> 4).  An e4m3 byte s.eeee.mmm, moved to the top of a 16-bit
-// half and its magnitude shifted right by one, reads as the f16 s.0eeee.mmm0000000: 2^(e-15) (1 + m/8) for e > 0 and
-// the f16 subnormal m 2^-17 for e = 0 — in both cases the e4m3 value times 2^-8, so one factor 256 on the score
-// scale (K) and on the output (V) puts it right.  Three integer-pipe instructions and a byte permute per pair; the
-// conversion instruction (cvt.rn.f16x2.e4m3x2) measured four times slower than the memory stream it has to keep up
-// with (the 8-bit batch took as long as the 16-bit one).
-constexpr float kE4M3Unscale = 256.0f;
-template <uint32_t SEL> __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t x) {
-    // bytes: result byte 1 <- x byte (SEL & 0xf), result byte 3 <- x byte (SEL >> 4), bytes 0 and 2 <- 0
-    const uint32_t y = __byte_perm(x, 0u, 0x0404u | ((SEL & 0xfu) << 4) | ((SEL >> 4) << 12));
-    return ((y & 0x7f007f00u) >> 1) | (y & 0x80008000u);
+// Two 8-bit floats -> f16x2.  `SEL` picks the bytes of x: the low half of the result comes from byte (SEL & 0xf),
+// the high half from byte (SEL >> 4).  FMT 1 = e4m3, 2 = e5m2.
+//  * e5m2 is the top byte of the f16 with the same value: one byte permute.
+//  * An e4m3 byte s.eeee.mmm, shifted left by 7 inside its 16-bit half, has its magnitude where the f16
+//    0eeee.mmm0000000 wants it — 2^(e-15) (1 + m/8) for e > 0, the f16 subnormal m 2^-17 for e = 0: in both cases the
+//    e4m3 value times 2^-8, so one factor 256 on the score scale (K) and on the output (V) puts it right — and its
+//    sign one bit too low; adding the sign bit to itself moves it up (the carry never leaves the half).  The shift
+//    and the add are written as multiply-adds so that they can go to the FMA pipe: widening the bytes is integer
+//    work, and it is the integer pipe, not memory, that bounds this kernel (cvt.rn.f16x2.e4m3x2 measured no faster).
+__host__ __device__ constexpr float f8_unscale(int fmt) { return fmt == 1 ? 256.0f : 1.0f; }
+template <int FMT, uint32_t SEL> __device__ __forceinline__ uint32_t f8x2_to_f16x2(uint32_t x) {
+    if constexpr (FMT == 2) {
+        // result byte 1 <- x byte (SEL & 0xf), result byte 3 <- x byte (SEL >> 4), bytes 0 and 2 <- 0
+        return __byte_perm(x, 0u, 0x0404u | ((SEL & 0xfu) << 4) | ((SEL >> 4) << 12));
+    } else {
+        // result byte 0 <- x byte (SEL & 0xf), result byte 2 <- x byte (SEL >> 4), bytes 1 and 3 <- 0
+        const uint32_t z = __byte_perm(x, 0u, 0x4040u | (SEL & 0xfu) | ((SEL >> 4) << 8));
+        uint32_t t, out;
+        asm("mad.lo.u32 %0, %1, 128, 0;" : "=r"(t) : "r"(z));                  // bytes at bits 14..7 and 30..23
+        asm("mad.lo.u32 %0, %1, 1, %2;" : "=r"(out) : "r"(t & 0x40004000u), "r"(t));   // sign: bit 14 -> bit 15
+        return out;
+    }
 }
 
 constexpr int kBlk = (int)kBlkPos;  // positions per warp block (one MMA k-step of P·V)
 
-template <int HD, int NW, int STAGES, int KPC, bool F8 = false> struct Decode16Smem {
+template <int HD, int NW, int STAGES, int KPC, int F8 = 0> struct Decode16Smem {
     static constexpr int kRowBytes = HD * (F8 ? 1 : 2);          // one kv head's part of a cache row
     static constexpr int kTileBytes = kBlk * kRowBytes;          // one K or V block
     static constexpr int kWarpBytes = STAGES * kTileBytes;       // ring of STAGES tile slots; K and V tiles alternate in it
-    // Q rows of one kv head: 16-bit rows, or (8-bit cache) three planes of e4m3 bytes whose sum is Q (see the kernel)
-    static constexpr int kQRowBytes = HD * (F8 ? 1 : 2);
-    static constexpr int kQPlane = 16 * kQRowBytes;
-    static constexpr int kQTile = (F8 ? 3 : 1) * kQPlane;
+    static constexpr int kQRowBytes = HD * 2;                    // Q is staged as 16-bit whatever the cache holds
+    static constexpr int kQTile = 16 * kQRowBytes;               // Q rows of one kv head
     static constexpr int kQBytes = KPC * kQTile;
     static constexpr int kStatBytes = (2 * NW * 16 * 4 > HD * 4) ? 2 * NW * 16 * 4 : HD * 4;   // merge m and l; cos/sin table of the fused append
     static constexpr int kTotal = kQBytes + NW * kWarpBytes + kStatBytes + 32;
@@ -895,18 +903,21 @@ constexpr int decode16_min_blocks(int HD, int NW, int STAGES) {
 // measured slower (59.9 us: the counter's answer is one more dependent memory round trip per block, and under load
 // a round trip is a whole iteration).  Which rows a warp saw does not matter to the result: its (m, l, O) state is
 // merged by log-sum-exp like any other.
-// F8: the cache holds e4m3 bytes (T is __half).  Tiles are half as large; a 16-byte chunk is 16 head dims.
-//   S = Q K^T runs on the 8-bit tensor path (mma m16n8k32 e4m3 x e4m3 -> f32): ldmatrix hands a thread four
-//   consecutive dims of a K row, which is that MMA's B fragment as it stands, so K is never converted.  Q (f16 or
-//   f32 from the caller) is staged as THREE e4m3 planes whose sum is 16 Q — p0 = e4m3(16 q), p1 = e4m3(16 q - p0),
-//   p2 = e4m3(16 q - p0 - p1) — about twelve significant bits, more than f16 carries, and the three products add
-//   up in the same f32 accumulator; the 1/16 rides on the score scale.
-//   O += P V stays f16 (P would lose its precision in 8 bits): ldmatrix.trans hands a thread the bytes (pos 2t, dims
-//   2g, 2g+1) and (pos 2t+1, dims 2g, 2g+1); a byte permute and three integer instructions turn them into the f16 B
-//   fragments of the even and of the odd dim, so the accumulator tiles of a 16-dim group hold its even and its odd
-//   dims and the epilogue interleaves them.
-template <typename T, int HD, int NW, int STAGES, int KPC, bool ILV = false, bool F8 = false>
-__global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, F8 ? STAGES / 2 : STAGES)) decode16_kernel(const __grid_constant__ DecodeArgs a) {
+// F8: the cache holds e4m3 bytes (T is __half: Q, P and the MMAs are f16).  Tiles are half as large, a 16-byte
+// chunk is 16 head dims, and every byte has to be widened on its way to the tensor core — integer work that, not
+// memory, bounds this path.  So the MMAs are turned round to waste as little as possible: the 16 positions of a
+// block are the M rows and (up to) 8 query heads the N columns, S^T = K Q^T and O^T = V^T P^T; half the MMAs, half
+// the accumulator registers and half the exponentials of the heads-on-M form when a KV group has 8 heads or fewer.
+//   * ldmatrix moves 16-bit units, so a thread receives four consecutive dims of a K row where the f16 A fragment
+//     has two: the Q columns are staged in the matching order (a dot product does not care in which order its
+//     terms are added);
+//   * P^T comes out of the softmax in the accumulator layout (position g, heads 2t, 2t+1) and goes into the next
+//     MMA as a B fragment (positions 2t, 2t+1, head g): one movmatrix per eight positions;
+//   * for V^T, ldmatrix.trans hands a thread the bytes (pos 2t, dims 2g, 2g+1) and (pos 2t+1, dims 2g, 2g+1): its
+//     even bytes are the A fragment of dim 2g, its odd bytes that of dim 2g+1, so the M rows of an accumulator tile
+//     are the even dims of a 16-dim chunk followed by its odd dims.
+template <typename T, int HD, int NW, int STAGES, int KPC, bool ILV = false, int F8 = 0>
+__global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_blocks(HD, NW, STAGES)) decode16_kernel(const __grid_constant__ DecodeArgs a) {
     using S = Decode16Smem<HD, NW, STAGES, KPC, F8>;
     constexpr int WPK = NW / KPC;
     static_assert(!F8 || (KPC == 1 && sizeof(T) == 2), "8-bit caches: one kv head per CTA, f16 arithmetic");
@@ -917,7 +928,7 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, F8 ? STAG
     static_assert(NW % KPC == 0, "warps must divide evenly over the kv heads of a CTA");
     constexpr int CH = HD / 8;            // 16-byte chunks per 16-bit row (Q, and the projections of the fused append)
     constexpr int CHK = S::kRowBytes / 16;   // 16-byte chunks per K/V tile row
-    constexpr bool QREG = HD <= 128 && !F8;   // keep the f16 Q fragments in registers (else re-read them from shared memory)
+    constexpr bool QREG = HD <= 128;      // keep the Q fragments in registers (else re-read them from shared memory)
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char *sm_q = smem;
     unsigned char *sm_pipe = smem + S::kQBytes;
@@ -939,8 +950,9 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, F8 ? STAG
     }
     const uint32_t kvl = warp % KPC, sub = warp / KPC;             // kv head within the CTA, block phase
     const uint32_t kvh = kg * KPC + kvl;
-    const uint32_t row0 = zi * 16;                                 // first head of the group handled here
-    const uint32_t rows_valid = min(16u, a.G - row0);
+    constexpr uint32_t kRows = F8 ? 8u : 16u;                      // query heads a CTA serves (8-bit cache: the MMA's N columns)
+    const uint32_t row0 = zi * kRows;                              // first head of the group handled here
+    const uint32_t rows_valid = min(kRows, a.G - row0);
 
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t mat = lane >> 3, rin = lane & 7;
@@ -1121,22 +1133,12 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, F8 ? STAG
                 }
             }
             if constexpr (F8) {
-                // eight dims -> eight bytes in each of the three planes (8-byte half (c & 1) of 16-byte chunk c / 2)
-                const __half2 *hv = reinterpret_cast<const __half2 *>(&v);
-                unsigned long long plane[3] = {0ull, 0ull, 0ull};
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    float x = 16.0f * ((e & 1) ? __high2float(hv[e >> 1]) : __low2float(hv[e >> 1]));
-#pragma unroll
-                    for (int pl = 0; pl < 3; ++pl) {
-                        const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
-                        plane[pl] |= (unsigned long long)b << (8 * e);
-                        x -= __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));   // exact: both are f32 here
-                    }
-                }
-                unsigned char *rowp = sm_q + k * S::kQTile + r * S::kQRowBytes + (((c >> 1) ^ (r & 7)) << 4) + (c & 1) * 8;
-#pragma unroll
-                for (int pl = 0; pl < 3; ++pl) *reinterpret_cast<unsigned long long *>(rowp + pl * S::kQPlane) = plane[pl];
+                // dims 8c .. 8c+7 of the 16-dim group c/2: the pair (4u, 4u+1) goes to column 2u, the pair (4u+2, 4u+3)
+                // to column 8 + 2u of the group (u = 2*(c&1), 2*(c&1)+1): two 8-byte halves in the group's two chunks
+                const uint32_t u2 = (c & 1) * 2, grp = c >> 1;
+                unsigned char *rowp = sm_q + k * S::kQTile + r * S::kQRowBytes;
+                *reinterpret_cast<uint2 *>(rowp + (((2 * grp) ^ (r & 7)) << 4) + u2 * 4) = make_uint2(v.x, v.z);
+                *reinterpret_cast<uint2 *>(rowp + (((2 * grp + 1) ^ (r & 7)) << 4) + u2 * 4) = make_uint2(v.y, v.w);
             } else {
                 *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kQRowBytes + ((c ^ (r & 7)) << 4)) = v;
             }
@@ -1181,193 +1183,249 @@ __global__ void __launch_bounds__(NW * 32, decode16_min_blocks(HD, NW, F8 ? STAG
                 }
             }
         }
-        // Q fragments (A operand), one ldmatrix.x4 per k-step: mats = (rows0-7,c), (rows8-15,c), (rows0-7,c+1), (rows8-15,c+1)
-        uint32_t qa[QREG ? HD / 16 : 1][4];
-        if constexpr (QREG) {
+        float *sm_o = reinterpret_cast<float *>(sm_pipe);  // warp w's [16][HD] tile at w*kWarpBytes
+        if constexpr (F8) {
+            // ---- 8-bit cache: positions on the M rows, heads on the N columns (S^T = K Q^T, O^T = V^T P^T) ----
+            // Q^T fragments (B operand): per 16-dim k-step the (permuted) columns 0-7 and 8-15 of heads 0-7
+            uint32_t qb[HD / 16][2];
 #pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks) {
-                const uint32_t row = (mat & 1) * 8 + rin, chunk = 2 * ks + (mat >> 1);
-                ldsm_x4(qa[ks], sm_q_addr + row * S::kQRowBytes + ((chunk ^ rin) << 4));
+            for (int c = 0; c < HD / 16; c += 2) {
+                uint32_t r4[4];   // (heads 0-7, chunk 2c), (.., 2c+1), (.., 2c+2), (.., 2c+3) of the 16-bit Q rows
+                ldsm_x4(r4, sm_q_addr + rin * S::kQRowBytes + (((2 * c + mat) ^ rin) << 4));
+                qb[c][0] = r4[0]; qb[c][1] = r4[1]; qb[c + 1][0] = r4[2]; qb[c + 1][1] = r4[3];
             }
-        }
-
-        float o[HD / 8][4];
+            float oT[HD / 16][4];   // tile c: (dim 16c+2g, heads 2t, 2t+1), (dim 16c+2g+1, heads 2t, 2t+1)
 #pragma unroll
-        for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+            for (int c = 0; c < HD / 16; ++c) oT[c][0] = oT[c][1] = oT[c][2] = oT[c][3] = 0.f;
+            float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // heads 2t, 2t+1 (l: this lane's positions only)
 
-        for (uint32_t i = 0; i < w_n; ++i) {
-            cp_async_wait<STAGES - 2>();   // this block's K tile has landed
-            __syncwarp();
-            if (2 * i + STAGES - 1 < w_items) issue(2 * i + STAGES - 1, block_of(i + kOffK));
-            cp_async_commit();
-
-            const uint32_t st = warp_smem + ((2 * i) % STAGES) * S::kTileBytes;
-            const uint32_t pos0 = start + block_of(i) * kBlk;
-            if (owner && i == w_n - 1) patch_tile(st, pos0, 0u);
-            // ---- S = Q K^T : heads x 16 positions ----
-            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            if constexpr (F8) {
-                // a k-step of the 8-bit MMA is 32 dims = two 16-byte chunks; the K registers ldmatrix delivers (row g,
-                // bytes 4t..4t+3 of each chunk) are its B fragments, the Q planes' registers its A fragments
+            for (uint32_t i = 0; i < w_n; ++i) {
+                cp_async_wait<STAGES - 2>();   // this block's K tile has landed
+                __syncwarp();
+                if (2 * i + STAGES - 1 < w_items) issue(2 * i + STAGES - 1, block_of(i + kOffK));
+                cp_async_commit();
+                const uint32_t st = warp_smem + ((2 * i) % STAGES) * S::kTileBytes;
+                const uint32_t pos0 = start + block_of(i) * kBlk;
+                // ---- S^T = K Q^T : 16 positions x 8 heads ----
+                float sT[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int ks = 0; ks < HD / 32; ++ks) {
-                    uint32_t kb[4];   // (pos 0-7, chunk 2ks), (pos 0-7, chunk 2ks+1), (pos 8-15, chunk 2ks), (pos 8-15, chunk 2ks+1)
-                    const uint32_t row = (mat >> 1) * 8 + rin, chunk = 2 * ks + (mat & 1);
-                    ldsm_x4(kb, st + row * S::kRowBytes + ((chunk ^ rin) << 4));
-                    const uint32_t qrow = (mat & 1) * 8 + rin, qchunk = 2 * ks + (mat >> 1);
+                for (int c = 0; c < HD / 16; c += 2) {
+                    uint32_t kb[4];   // (pos 0-7, chunk c), (pos 8-15, chunk c), (pos 0-7, chunk c+1), (pos 8-15, chunk c+1)
+                    ldsm_x4(kb, st + ((mat & 1) * 8 + rin) * S::kRowBytes + (((c + (mat >> 1)) ^ rin) << 4));
 #pragma unroll
-                    for (int pl = 0; pl < 3; ++pl) {
-                        uint32_t qf[4];   // (rows 0-7, chunk 2ks), (rows 8-15, chunk 2ks), (rows 0-7, chunk 2ks+1), (rows 8-15, chunk 2ks+1)
-                        ldsm_x4(qf, sm_q_addr + pl * S::kQPlane + qrow * S::kQRowBytes + ((qchunk ^ rin) << 4));
-                        mma16832_e4m3(s[0], qf, kb[0], kb[1]);
-                        mma16832_e4m3(s[1], qf, kb[2], kb[3]);
+                    for (int h = 0; h < 2; ++h) {
+                        // a register holds dims 4t..4t+3 of its row: the low pair is k = 2t, 2t+1, the high pair k = 2t+8, 2t+9
+                        const uint32_t ka[4] = {f8x2_to_f16x2<F8, 0x10>(kb[2 * h]), f8x2_to_f16x2<F8, 0x10>(kb[2 * h + 1]),
+                                                f8x2_to_f16x2<F8, 0x32>(kb[2 * h]), f8x2_to_f16x2<F8, 0x32>(kb[2 * h + 1])};
+                        mma16816<T>(sT, ka, qb[c + h][0], qb[c + h][1]);
                     }
                 }
-            } else {
+                // ---- online softmax (log2 domain): this lane holds positions g, g+8 of heads 2t, 2t+1 ----
+                const bool v0 = pos0 + g < end, v1 = pos0 + g + 8 < end;
+                float x[4];
+                x[0] = v0 ? sT[0] * a.scale_log2 : -INFINITY; x[1] = v0 ? sT[1] * a.scale_log2 : -INFINITY;
+                x[2] = v1 ? sT[2] * a.scale_log2 : -INFINITY; x[3] = v1 ? sT[3] * a.scale_log2 : -INFINITY;
+                float mx[2] = {fmaxf(x[0], x[2]), fmaxf(x[1], x[3])}, corr[2];
 #pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks) {
-                uint32_t kb[4];
-                const uint32_t row = (mat >> 1) * 8 + rin, chunk = 2 * ks + (mat & 1);
-                ldsm_x4(kb, st + row * S::kRowBytes + ((chunk ^ rin) << 4));
-                if constexpr (QREG) {
-                    mma16816<T>(s[0], qa[ks], kb[0], kb[1]);
-                    mma16816<T>(s[1], qa[ks], kb[2], kb[3]);
-                } else {
-                    const uint32_t qrow = (mat & 1) * 8 + rin, qchunk = 2 * ks + (mat >> 1);
-                    ldsm_x4(qa[0], sm_q_addr + qrow * S::kQRowBytes + ((qchunk ^ rin) << 4));
-                    mma16816<T>(s[0], qa[0], kb[0], kb[1]);
-                    mma16816<T>(s[1], qa[0], kb[2], kb[3]);
+                for (int r = 0; r < 2; ++r) {
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 4));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 8));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
+                    const float m_new = fmaxf(m_run[r], mx[r]);   // finite: every block holds >= 1 valid position
+                    corr[r] = exp2f(m_run[r] - m_new);
+                    m_run[r] = m_new;
+                }
+                const float p0 = exp2f(x[0] - m_run[0]), p1 = exp2f(x[1] - m_run[1]);
+                const float p2 = exp2f(x[2] - m_run[0]), p3 = exp2f(x[3] - m_run[1]);
+                l_run[0] = l_run[0] * corr[0] + (p0 + p2);
+                l_run[1] = l_run[1] * corr[1] + (p1 + p3);
+                // P^T as the B operand: (pos g; heads 2t, 2t+1) -> (pos 2t, 2t+1; head g), positions 0-7 and 8-15
+                const uint32_t pb0 = movmatrix_trans(pack2<T>(p0, p1)), pb1 = movmatrix_trans(pack2<T>(p2, p3));
+                const bool rescale = __any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f);
+                // ---- O^T = O^T * corr + V^T P^T ----
+                cp_async_wait<STAGES - 2>();   // this block's V tile has landed
+                __syncwarp();
+                if (2 * i + STAGES < w_items) issue(2 * i + STAGES, block_of(i + kOffV));   // into the slot of the K tile just consumed
+                cp_async_commit();
+                const uint32_t stv = warp_smem + ((2 * i + 1) % STAGES) * S::kTileBytes;
+#pragma unroll
+                for (int c = 0; c < HD / 16; c += 2) {
+                    uint32_t vb[4];   // (pos 0-7, chunk c), (pos 8-15, chunk c), (pos 0-7, chunk c+1), (pos 8-15, chunk c+1)
+                    ldsm_x4_t(vb, stv + ((mat & 1) * 8 + rin) * S::kRowBytes + (((c + (mat >> 1)) ^ rin) << 4));
+                    if (rescale) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            oT[c + h][0] *= corr[0]; oT[c + h][1] *= corr[1];
+                            oT[c + h][2] *= corr[0]; oT[c + h][3] *= corr[1];
+                        }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        // a register holds (pos 2t, dim 2g), (pos 2t, dim 2g+1), (pos 2t+1, dim 2g), (pos 2t+1, dim 2g+1):
+                        // rows 0-7 of the tile are the even dims, rows 8-15 the odd dims
+                        const uint32_t va[4] = {f8x2_to_f16x2<F8, 0x20>(vb[2 * h]), f8x2_to_f16x2<F8, 0x31>(vb[2 * h]),
+                                                f8x2_to_f16x2<F8, 0x20>(vb[2 * h + 1]), f8x2_to_f16x2<F8, 0x31>(vb[2 * h + 1])};
+                        mma16816<T>(oT[c + h], va, pb0, pb1);
+                    }
                 }
             }
-            }
-            // ---- online softmax (log2 domain), rows g and g+8 ----
-            float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint32_t pos = pos0 + 8 * j + 2 * t + (c & 1);
-                    s[j][c] = pos < end ? s[j][c] * a.scale_log2 : -INFINITY;
-                    mx[c >> 1] = fmaxf(mx[c >> 1], s[j][c]);
-                }
-            float corr[2];
+            cp_async_wait<0>();
+            __syncthreads();  // every warp is done with its pipeline memory: reuse it for the merge
+
+            // ---- per-warp state -> shared: rows are heads, as the 16-bit path writes them ----
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-                const float m_new = fmaxf(m_run[r], mx[r]);   // finite: every block holds >= 1 valid position
-                corr[r] = exp2f(m_run[r] - m_new);
-                m_run[r] = m_new;
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 4);
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 8);
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 16);
             }
-            float psum[2] = {0.f, 0.f};
+            float *my_o = reinterpret_cast<float *>(sm_pipe + warp * S::kWarpBytes);
+            if (g == 0) {
+                sm_m[warp * 16 + 2 * t] = m_run[0]; sm_m[warp * 16 + 2 * t + 1] = m_run[1];
+                sm_l[warp * 16 + 2 * t] = l_run[0]; sm_l[warp * 16 + 2 * t + 1] = l_run[1];
+            }
+            // the cache scale of V and the 2^8 the byte-to-f16 conversion leaves out are applied here, once per element of O
+            const float vs = a.kv.v_scale * f8_unscale(F8);
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
+            for (int hh = 0; hh < 2; ++hh) {
+                const uint32_t head = 2 * t + hh;
+                if (head < rows_valid) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    s[j][c] = exp2f(s[j][c] - m_run[c >> 1]);
-                    psum[c >> 1] += s[j][c];
+                    for (int c = 0; c < HD / 16; ++c)
+                        *reinterpret_cast<float2 *>(my_o + head * S::kORow + c * 16 + 2 * g) = make_float2(oT[c][hh] * vs, oT[c][2 + hh] * vs);
                 }
-            l_run[0] = l_run[0] * corr[0] + psum[0];
-            l_run[1] = l_run[1] * corr[1] + psum[1];
-            // O is rescaled only when some row's maximum grew in this block (after the first few blocks of a piece that
-            // is rare): HD/2 multiplies per lane saved in the common case
-            const bool rescale = __any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f);
-            uint32_t pa[4];
-            pa[0] = pack2<T>(s[0][0], s[0][1]);
-            pa[1] = pack2<T>(s[0][2], s[0][3]);
-            pa[2] = pack2<T>(s[1][0], s[1][1]);
-            pa[3] = pack2<T>(s[1][2], s[1][3]);
-            // ---- O = O*corr + P V ----
-            cp_async_wait<STAGES - 2>();   // this block's V tile has landed
-            __syncwarp();
-            if (2 * i + STAGES < w_items) issue(2 * i + STAGES, block_of(i + kOffV));   // into the slot of the K tile just consumed
-            cp_async_commit();
-            const uint32_t stv = warp_smem + ((2 * i + 1) % STAGES) * S::kTileBytes;
-            if (owner && i == w_n - 1) patch_tile(stv, pos0, 1u);
-            if constexpr (F8) {
-                // chunk c = dims 16c .. 16c+15; accumulator tile 2c holds its even dims, tile 2c+1 its odd dims
+            }
+        } else {
+            // Q fragments (A operand), one ldmatrix.x4 per k-step: mats = (rows0-7,c), (rows8-15,c), (rows0-7,c+1), (rows8-15,c+1)
+            uint32_t qa[QREG ? HD / 16 : 1][4];
+            if constexpr (QREG) {
 #pragma unroll
-                for (int c2 = 0; c2 < HD / 16; c2 += 2) {
-                    uint32_t vb[4];   // (pos 0-7, chunk c2), (pos 8-15, chunk c2), (pos 0-7, chunk c2+1), (pos 8-15, chunk c2+1)
-                    const uint32_t row = (mat & 1) * 8 + rin, chunk = c2 + (mat >> 1);
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t row = (mat & 1) * 8 + rin, chunk = 2 * ks + (mat >> 1);
+                    ldsm_x4(qa[ks], sm_q_addr + row * S::kQRowBytes + ((chunk ^ rin) << 4));
+                }
+            }
+
+            float o[HD / 8][4];
+#pragma unroll
+            for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+            float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+            for (uint32_t i = 0; i < w_n; ++i) {
+                cp_async_wait<STAGES - 2>();   // this block's K tile has landed
+                __syncwarp();
+                if (2 * i + STAGES - 1 < w_items) issue(2 * i + STAGES - 1, block_of(i + kOffK));
+                cp_async_commit();
+
+                const uint32_t st = warp_smem + ((2 * i) % STAGES) * S::kTileBytes;
+                const uint32_t pos0 = start + block_of(i) * kBlk;
+                if (owner && i == w_n - 1) patch_tile(st, pos0, 0u);
+                // ---- S = Q K^T : heads x 16 positions ----
+                float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                #pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    uint32_t kb[4];
+                    const uint32_t row = (mat >> 1) * 8 + rin, chunk = 2 * ks + (mat & 1);
+                    ldsm_x4(kb, st + row * S::kRowBytes + ((chunk ^ rin) << 4));
+                    if constexpr (QREG) {
+                        mma16816<T>(s[0], qa[ks], kb[0], kb[1]);
+                        mma16816<T>(s[1], qa[ks], kb[2], kb[3]);
+                    } else {
+                        const uint32_t qrow = (mat & 1) * 8 + rin, qchunk = 2 * ks + (mat >> 1);
+                        ldsm_x4(qa[0], sm_q_addr + qrow * S::kQRowBytes + ((qchunk ^ rin) << 4));
+                        mma16816<T>(s[0], qa[0], kb[0], kb[1]);
+                        mma16816<T>(s[1], qa[0], kb[2], kb[3]);
+                    }
+                }
+            
+                // ---- online softmax (log2 domain), rows g and g+8 ----
+                float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint32_t pos = pos0 + 8 * j + 2 * t + (c & 1);
+                        s[j][c] = pos < end ? s[j][c] * a.scale_log2 : -INFINITY;
+                        mx[c >> 1] = fmaxf(mx[c >> 1], s[j][c]);
+                    }
+                float corr[2];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                    const float m_new = fmaxf(m_run[r], mx[r]);   // finite: every block holds >= 1 valid position
+                    corr[r] = exp2f(m_run[r] - m_new);
+                    m_run[r] = m_new;
+                }
+                float psum[2] = {0.f, 0.f};
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        s[j][c] = exp2f(s[j][c] - m_run[c >> 1]);
+                        psum[c >> 1] += s[j][c];
+                    }
+                l_run[0] = l_run[0] * corr[0] + psum[0];
+                l_run[1] = l_run[1] * corr[1] + psum[1];
+                // O is rescaled only when some row's maximum grew in this block (after the first few blocks of a piece that
+                // is rare): HD/2 multiplies per lane saved in the common case
+                const bool rescale = __any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f);
+                uint32_t pa[4];
+                pa[0] = pack2<T>(s[0][0], s[0][1]);
+                pa[1] = pack2<T>(s[0][2], s[0][3]);
+                pa[2] = pack2<T>(s[1][0], s[1][1]);
+                pa[3] = pack2<T>(s[1][2], s[1][3]);
+                // ---- O = O*corr + P V ----
+                cp_async_wait<STAGES - 2>();   // this block's V tile has landed
+                __syncwarp();
+                if (2 * i + STAGES < w_items) issue(2 * i + STAGES, block_of(i + kOffV));   // into the slot of the K tile just consumed
+                cp_async_commit();
+                const uint32_t stv = warp_smem + ((2 * i + 1) % STAGES) * S::kTileBytes;
+                if (owner && i == w_n - 1) patch_tile(stv, pos0, 1u);
+                #pragma unroll
+                for (int jn = 0; jn < HD / 8; jn += 2) {
+                    uint32_t vb[4];
+                    const uint32_t row = (mat & 1) * 8 + rin, chunk = jn + (mat >> 1);
                     ldsm_x4_t(vb, stv + row * S::kRowBytes + ((chunk ^ rin) << 4));
                     if (rescale) {
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            o[2 * c2 + u][0] *= corr[0]; o[2 * c2 + u][1] *= corr[0];
-                            o[2 * c2 + u][2] *= corr[1]; o[2 * c2 + u][3] *= corr[1];
+                        for (int u = 0; u < 2; ++u) {
+                            o[jn + u][0] *= corr[0]; o[jn + u][1] *= corr[0];
+                            o[jn + u][2] *= corr[1]; o[jn + u][3] *= corr[1];
                         }
                     }
-                    // a register holds (pos 2t, dim 2g), (pos 2t, dim 2g+1), (pos 2t+1, dim 2g), (pos 2t+1, dim 2g+1)
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        mma16816<T>(o[2 * (c2 + h)], pa, e4m3x2_to_f16x2<0x20>(vb[2 * h]), e4m3x2_to_f16x2<0x20>(vb[2 * h + 1]));
-                        mma16816<T>(o[2 * (c2 + h) + 1], pa, e4m3x2_to_f16x2<0x31>(vb[2 * h]), e4m3x2_to_f16x2<0x31>(vb[2 * h + 1]));
-                    }
+                    mma16816<T>(o[jn], pa, vb[0], vb[1]);
+                    mma16816<T>(o[jn + 1], pa, vb[2], vb[3]);
                 }
-            } else {
-#pragma unroll
-            for (int jn = 0; jn < HD / 8; jn += 2) {
-                uint32_t vb[4];
-                const uint32_t row = (mat & 1) * 8 + rin, chunk = jn + (mat >> 1);
-                ldsm_x4_t(vb, stv + row * S::kRowBytes + ((chunk ^ rin) << 4));
-                if (rescale) {
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        o[jn + u][0] *= corr[0]; o[jn + u][1] *= corr[0];
-                        o[jn + u][2] *= corr[1]; o[jn + u][3] *= corr[1];
-                    }
-                }
-                mma16816<T>(o[jn], pa, vb[0], vb[1]);
-                mma16816<T>(o[jn + 1], pa, vb[2], vb[3]);
+            
             }
-            }
-        }
-        cp_async_wait<0>();
-        __syncthreads();  // every warp is done with its pipeline memory: reuse it for the merge
+            cp_async_wait<0>();
+            __syncthreads();  // every warp is done with its pipeline memory: reuse it for the merge
 
-        // ---- per-warp state -> shared ----
+            // ---- per-warp state -> shared ----
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-        }
-        float *sm_o = reinterpret_cast<float *>(sm_pipe);  // warp w's [16][HD] tile at w*kWarpBytes
-        float *my_o = reinterpret_cast<float *>(sm_pipe + warp * S::kWarpBytes);
-        if (t == 0) {
-            sm_m[warp * 16 + g] = m_run[0];
-            sm_m[warp * 16 + g + 8] = m_run[1];
-            sm_l[warp * 16 + g] = l_run[0];
-            sm_l[warp * 16 + g + 8] = l_run[1];
-        }
-        if constexpr (F8) {
-            // tiles 2c / 2c+1 hold the even / odd dims of group c: columns (2t, 2t+1) are dims 16c + 4t + {0, 2} / {1, 3};
-            // the cache scale of V is applied here, once per element of O
-            const float vs = a.kv.v_scale * kE4M3Unscale;
-            if (g < rows_valid) {
+            for (int r = 0; r < 2; ++r) {
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+            }
+            float *my_o = reinterpret_cast<float *>(sm_pipe + warp * S::kWarpBytes);
+            if (t == 0) {
+                sm_m[warp * 16 + g] = m_run[0];
+                sm_m[warp * 16 + g + 8] = m_run[1];
+                sm_l[warp * 16 + g] = l_run[0];
+                sm_l[warp * 16 + g + 8] = l_run[1];
+            }
+                    if (g < rows_valid) {          // only the head rows that exist go to shared memory
 #pragma unroll
-                for (int c = 0; c < HD / 16; ++c)
-                    *reinterpret_cast<float4 *>(my_o + g * S::kORow + c * 16 + 4 * t) =
-                        make_float4(o[2 * c][0] * vs, o[2 * c + 1][0] * vs, o[2 * c][1] * vs, o[2 * c + 1][1] * vs);
+                for (int jn = 0; jn < HD / 8; ++jn)
+                    *reinterpret_cast<float2 *>(my_o + g * S::kORow + jn * 8 + 2 * t) = make_float2(o[jn][0], o[jn][1]);
             }
             if (g + 8 < rows_valid) {
 #pragma unroll
-                for (int c = 0; c < HD / 16; ++c)
-                    *reinterpret_cast<float4 *>(my_o + (g + 8) * S::kORow + c * 16 + 4 * t) =
-                        make_float4(o[2 * c][2] * vs, o[2 * c + 1][2] * vs, o[2 * c][3] * vs, o[2 * c + 1][3] * vs);
+                for (int jn = 0; jn < HD / 8; ++jn)
+                    *reinterpret_cast<float2 *>(my_o + (g + 8) * S::kORow + jn * 8 + 2 * t) = make_float2(o[jn][2], o[jn][3]);
             }
-        } else {
-        if (g < rows_valid) {          // only the head rows that exist go to shared memory
-#pragma unroll
-            for (int jn = 0; jn < HD / 8; ++jn)
-                *reinterpret_cast<float2 *>(my_o + g * S::kORow + jn * 8 + 2 * t) = make_float2(o[jn][0], o[jn][1]);
-        }
-        if (g + 8 < rows_valid) {
-#pragma unroll
-            for (int jn = 0; jn < HD / 8; ++jn)
-                *reinterpret_cast<float2 *>(my_o + (g + 8) * S::kORow + jn * 8 + 2 * t) = make_float2(o[jn][2], o[jn][3]);
-        }
+        
         }
         __syncthreads();
         // after its first loop finish_piece no longer reads the O tiles: the pipeline memory doubles as merge scratch
@@ -1692,7 +1750,7 @@ __global__ void sigmoid_mul_kernel(float *x, const float *gate, uint32_t n) {
 // ---------------------------------------------------------------------------------------
 // Host launchers
 // ---------------------------------------------------------------------------------------
-template <typename T, int HD, int NW, int STAGES, int KPC, bool ILV = false, bool F8 = false>
+template <typename T, int HD, int NW, int STAGES, int KPC, bool ILV = false, int F8 = 0>
 static int launch16(shady_ctx *ctx, const DecodeArgs &a, uint32_t blocks) {
     using S = Decode16Smem<HD, NW, STAGES, KPC, F8>;
     static_assert(S::kTotal <= 232448, "shared memory of this configuration exceeds 227 KB");
@@ -1773,6 +1831,7 @@ static uint32_t head_groups(uint32_t kv_dtype, uint32_t G) {
         const uint32_t gt = group_rows_f32(G);
         return (G + gt - 1) / gt;
     }
+    if (kv_dtype == SHADY_F8E4M3 || kv_dtype == SHADY_F8E5M2) return (G + 7) / 8;   // heads sit on the MMA's eight N columns
     return (G + 15) / 16;
 }
 
@@ -1817,7 +1876,8 @@ struct DecodePlan {
     DecodeArgs a;
     Variant16 var;
     uint32_t kpc, blocks;
-    bool f32, half, f8, need_ws, second_launch;
+    bool f32, half, need_ws, second_launch;
+    int f8;                  // 0: not an 8-bit cache, 1: e4m3, 2: e5m2
     size_t counters_bytes;   // arrival counters + barrier words at the head of the scratch
     size_t scratch_bytes;    // counters + the records this launch writes (<= decode_workspace_bytes)
     dim3 merge_grid;         // second launch (no grid merge): balanced_merge_kernel / shard_merge_p2p_kernel
@@ -1834,10 +1894,10 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
                   "decode: zero-sized problem");
     SHADY_REQUIRE(ctx, p->num_q_heads == p->num_kv_heads * p->heads_per_kv, SHADY_ERR_BAD_ARG,
                   "decode: num_q_heads != num_kv_heads * heads_per_kv");
-    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_F8E4M3, SHADY_ERR_BAD_ARG, "decode: bad cache dtype");
+    SHADY_REQUIRE(ctx, cache->dtype <= SHADY_F8E5M2, SHADY_ERR_BAD_ARG, "decode: bad cache dtype");
     SHADY_REQUIRE(ctx, (cache->d_k_ptrs && cache->d_v_ptrs) || (cache->d_k_base && cache->d_v_base),
                   SHADY_ERR_BAD_ARG, "decode: cache has neither base pointers nor pointer arrays");
-    const bool f8 = cache->dtype == SHADY_F8E4M3;
+    const int f8 = cache->dtype == SHADY_F8E4M3 ? 1 : (cache->dtype == SHADY_F8E5M2 ? 2 : 0);   // 8-bit format of the cache
     const uint32_t act_dtype = f8 ? (uint32_t)SHADY_F16 : cache->dtype;   // what Q and the output may be besides f32
     SHADY_REQUIRE(ctx, p->q_dtype == SHADY_F32 || p->q_dtype == act_dtype, SHADY_ERR_UNSUPPORTED,
                   "decode: q_dtype must be f32 or the cache dtype (f16 for an 8-bit cache)");
@@ -1865,8 +1925,8 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
     }
     a.num_seqs = p->num_seqs; a.nkv = p->num_kv_heads; a.nh = p->num_q_heads; a.G = p->heads_per_kv; a.hd = hd;
     a.q_dtype = p->q_dtype; a.out_dtype = p->out_dtype;
-    // 8-bit cache: K's scale, and the 1/16 that undoes the scaling of the Q planes, ride on the score scale
-    a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e * a.kv.k_scale * (f8 ? 1.0f / 16.0f : 1.0f);
+    // 8-bit cache: K's scale, and the 2^8 the byte-to-f16 conversion leaves out, ride on the score scale
+    a.scale_log2 = (1.0f / sqrtf((float)hd)) * kLog2e * a.kv.k_scale * f8_unscale(f8);
     a.num_splits = p->num_splits;
     a.out_row_stride = hd; a.lse_stride = 1;
     a.status = status_ref(ctx); a.wait_grid = ctx->wait_grid; a.wait_peer = ctx->wait_peer;
@@ -1909,7 +1969,7 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
     }
     const DecodeKnobs &kn = ctx->knobs;
     // 8-bit tiles are half as large: twice the slots keep the same bytes in flight per warp
-    const Variant16 var = f8 ? (hd > 128 ? Variant16{8, 6, 1} : Variant16{4, 12, 2}) : variant16(hd, kn.variant);
+    const Variant16 var = f8 ? (hd > 128 ? Variant16{8, 6, 1} : Variant16{4, 8, 3}) : variant16(hd, kn.variant);
     // One kv head per CTA measured fastest (sibling CTAs of the other kv heads run next to each other in
     // the grid and fetch the rest of each cache row); the kpc knob packs more kv heads into a CTA.
     uint32_t kpc = 1u;
@@ -1995,8 +2055,10 @@ static int run_decode(shady_ctx *ctx, const shady_decode_params *p, DecodePlan &
     } else {
         const bool h = plan.half;
         const Variant16 &var = plan.var;
-        if (plan.f8) rc = hd == 128 ? launch16<__half, 128, 4, 12, 1, false, true>(ctx, a, blocks)
-                                    : launch16<__half, 256, 8, 6, 1, false, true>(ctx, a, blocks);
+        if (plan.f8 == 1) rc = hd == 128 ? launch16<__half, 128, 4, 8, 1, false, 1>(ctx, a, blocks)
+                                         : launch16<__half, 256, 8, 6, 1, false, 1>(ctx, a, blocks);
+        else if (plan.f8 == 2) rc = hd == 128 ? launch16<__half, 128, 4, 8, 1, false, 2>(ctx, a, blocks)
+                                              : launch16<__half, 256, 8, 6, 1, false, 2>(ctx, a, blocks);
         else if (a.interleave) rc = hd == 128 ? launch16_ilv<128, 4, 6>(ctx, a, h, blocks) : launch16_ilv<256, 8, 3>(ctx, a, h, blocks);
         else if (hd == 128) {
             if (var.nw == 8 && var.stages == 6) rc = launch16_kpc<128, 8, 6>(ctx, a, plan.kpc, h, blocks);

@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(kGptqThreads) qkv_proj_kernel(const QkvArgs a,
         } else {
             const uint32_t kh = unit - a.nh;
             warp_norm_rope(vals, lane, hd, a.norm_w ? a.norm_w + hd : nullptr, a.rope, a.inv_freq, p_t, p_h, p_w);
-            const size_t esz = a.kv_dtype == SHADY_F32 ? 4 : (a.kv_dtype == SHADY_F8E4M3 ? 1 : 2);
+            const size_t esz = dtype_size(a.kv_dtype);
             // cache_position == position (model.rs:493-496)
             char *kc = const_cast<char *>(kv_row_ptr(a.kv, false, seq, p_t, (size_t)a.nkv * hd * esz));
             char *vc = const_cast<char *>(kv_row_ptr(a.kv, true, seq, p_t, (size_t)a.nkv * hd * esz));

@@ -10,24 +10,35 @@ import torch
 
 from _util import RTOL_16, rel_err, to_dev, to_host
 from shady_thinker_b200 import ops
-from shady_thinker_b200._lib import F8E4M3, F16, F32, ShadyError
+from shady_thinker_b200._lib import F8E4M3, F8E5M2, F16, F32, ShadyError
 from shady_thinker_b200.batch import BatchedDecoder
 
 pytestmark = pytest.mark.gpu
 
 
-def _to_e4m3_dev(stored):
-    """f32 values that already lie on the e4m3 grid -> device tensor of e4m3 bytes."""
-    t = torch.from_numpy(np.ascontiguousarray(stored, np.float32)).cuda().to(torch.float8_e4m3fn).contiguous()
+TORCH_F8 = {F8E4M3: torch.float8_e4m3fn, F8E5M2: torch.float8_e5m2}
+
+
+def _stored(oracle, fmt, a, scale=1.0):
+    return (oracle.e4m3_stored if fmt == F8E4M3 else oracle.e5m2_stored)(a, scale)
+
+
+def _deq(oracle, fmt, a, scale=1.0):
+    return (oracle.round_e4m3 if fmt == F8E4M3 else oracle.round_e5m2)(a, scale)
+
+
+def _to_e4m3_dev(stored, fmt=F8E4M3):
+    """f32 values that already lie on the 8-bit format's grid -> device tensor of its bytes."""
+    t = torch.from_numpy(np.ascontiguousarray(stored, np.float32)).cuda().to(TORCH_F8[fmt]).contiguous()
     assert torch.equal(t.float().cpu(), torch.from_numpy(np.ascontiguousarray(stored, np.float32)))
     return t
 
 
-def _decode(gpu, q, views_k, views_v, lens, *, nh, nkv, hd, ks, vs, num_splits=0, q_dt=F16, out_dt=F32):
+def _decode(gpu, q, views_k, views_v, lens, *, nh, nkv, hd, ks, vs, num_splits=0, q_dt=F16, out_dt=F32, fmt=F8E4M3):
     S = len(lens)
     k_ptrs = torch.tensor([t.data_ptr() for t in views_k], dtype=torch.int64).cuda()
     v_ptrs = torch.tensor([t.data_ptr() for t in views_v], dtype=torch.int64).cuda()
-    view = ops.KvCacheView(F8E4M3, k_ptrs=k_ptrs, v_ptrs=v_ptrs, k_scale=ks, v_scale=vs)
+    view = ops.KvCacheView(fmt, k_ptrs=k_ptrs, v_ptrs=v_ptrs, k_scale=ks, v_scale=vs)
     d_out = torch.full((S, nh, hd), float("nan"), dtype=torch.float32 if out_dt == F32 else torch.float16, device="cuda")
     d_lse = torch.full((S, nh), float("nan"), device="cuda")
     ws_n = ops.decode_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_splits=num_splits, num_seqs=S)
@@ -44,19 +55,21 @@ def _decode(gpu, q, views_k, views_v, lens, *, nh, nkv, hd, ks, vs, num_splits=0
     (128, 8, 2, [3000], 0.05, 0.125),                                       # scales that are not 1
     (256, 16, 2, [40000], 0.02, 0.03),                                      # long context: records merged by the grid
     (256, 8, 1, [17, 300], 1.0, 0.5),
+    (128, 16, 1, [100, 900], 0.0, 0.0),                                     # 16 heads per kv head: two groups of eight
 ])
-def test_decode_over_an_e4m3_cache_matches_f64_on_the_dequantised_rows(gpu_ctx, oracle, hd, nh, nkv, lens, ks, vs):
+@pytest.mark.parametrize("fmt", [F8E4M3, F8E5M2])
+def test_decode_over_an_e4m3_cache_matches_f64_on_the_dequantised_rows(gpu_ctx, oracle, hd, nh, nkv, lens, ks, vs, fmt):
     S = len(lens)
     sk, sv = (ks or 1.0), (vs or 1.0)
     q = oracle.round_f16(oracle.randn((S, nh, hd), 81, 1))
     kraw = [oracle.randn((max(L, 1), nkv, hd), 81, 10 + i) for i, L in enumerate(lens)]
     vraw = [oracle.randn((max(L, 1), nkv, hd), 81, 50 + i) for i, L in enumerate(lens)]
-    kq = [oracle.round_e4m3(k, sk) for k in kraw]          # what the cache means (dequantised) ...
-    vq = [oracle.round_e4m3(v, sv) for v in vraw]
-    dk = [_to_e4m3_dev(oracle.e4m3_stored(k, sk)) for k in kraw]   # ... and what it holds
-    dv = [_to_e4m3_dev(oracle.e4m3_stored(v, sv)) for v in vraw]
+    kq = [_deq(oracle, fmt, k, sk) for k in kraw]          # what the cache means (dequantised) ...
+    vq = [_deq(oracle, fmt, v, sv) for v in vraw]
+    dk = [_to_e4m3_dev(_stored(oracle, fmt, k, sk), fmt) for k in kraw]   # ... and what it holds
+    dv = [_to_e4m3_dev(_stored(oracle, fmt, v, sv), fmt) for v in vraw]
     for q_dt, out_dt in ((F16, F32), (F32, F16)):
-        out, lse = _decode(gpu_ctx, q, dk, dv, lens, nh=nh, nkv=nkv, hd=hd, ks=ks, vs=vs, q_dt=q_dt, out_dt=out_dt)
+        out, lse = _decode(gpu_ctx, q, dk, dv, lens, nh=nh, nkv=nkv, hd=hd, ks=ks, vs=vs, q_dt=q_dt, out_dt=out_dt, fmt=fmt)
         for i, L in enumerate(lens):
             if L == 0:
                 assert np.all(out[i] == 0) and np.all(np.isneginf(lse[i]))
@@ -83,8 +96,9 @@ def test_explicit_splits_and_static_entry_point(gpu_ctx, oracle):
     assert rel_err(to_host(d_out)[0], ref) <= RTOL_16
 
 
+@pytest.mark.parametrize("fmt", [F8E4M3, F8E5M2])
 @pytest.mark.parametrize("in_dt,rd,norm", [(F32, 32, True), (F16, 128, False), (F16, 32, True)])
-def test_append_quantises_like_the_oracle(gpu_ctx, oracle, in_dt, rd, norm):
+def test_append_quantises_like_the_oracle(gpu_ctx, oracle, in_dt, rd, norm, fmt):
     """K: norm + RoPE in f32, times 1/k_scale, e4m3; V: times 1/v_scale, e4m3 — both the one-warp-per-head kernel
     (f32 projections, three tokens per sequence) and the vectorised one (f16)."""
     S, T, nh, nkv, hd, ks, vs = 2, 3, 4, 2, 128, 0.25, 0.5
@@ -95,12 +109,12 @@ def test_append_quantises_like_the_oracle(gpu_ctx, oracle, in_dt, rd, norm):
     w = oracle.bf16_bits(oracle.randn((2 * hd,), 83, 4) * np.float32(0.02)) if norm else None
     start = np.array([5, 100_000], np.uint32)
     cap = 100_016
-    d_kc = torch.zeros((S, cap, nkv, hd), dtype=torch.float8_e4m3fn, device="cuda")
+    d_kc = torch.zeros((S, cap, nkv, hd), dtype=TORCH_F8[fmt], device="cuda")
     d_vc = torch.zeros_like(d_kc)
     d_q = torch.empty((S, T, nh, hd), dtype=torch.float32 if in_dt == F32 else torch.float16, device="cuda")
     d_g = torch.empty((S, T, nh, hd), device="cuda")
     ops.kv_append_rope(gpu_ctx, q_proj_full=to_dev(qf, in_dt), k_proj=to_dev(kp, in_dt), v_proj=to_dev(vp, in_dt), q_out=d_q,
-                       q_gate=d_g, cache=ops.KvCacheView(F8E4M3, d_kc, d_vc, cap * nkv * hd, k_scale=ks, v_scale=vs),
+                       q_gate=d_g, cache=ops.KvCacheView(fmt, d_kc, d_vc, cap * nkv * hd, k_scale=ks, v_scale=vs),
                        pos_start=torch.from_numpy(start.astype(np.int32)).cuda(), num_heads=nh, num_kv_heads=nkv, head_dim=hd,
                        rope_theta=1e6, rotary_dim=rd, num_seqs=S, tokens_per_seq=T, in_dtype=in_dt, q_dtype=in_dt,
                        has_gate=True, write_k_back=False, qk_norm_bf16=torch.from_numpy(w.view(np.int16)).cuda() if norm else None)
@@ -112,14 +126,14 @@ def test_append_quantises_like_the_oracle(gpu_ctx, oracle, in_dt, rd, norm):
             okc, ovc = np.zeros((1, nkv, hd), np.float32), np.zeros((1, nkv, hd), np.float32)
             oracle.fused_split_qknorm_kvstore(qf[s, t], kp[s, t], vp[s, t], okc, ovc, pos, rope_theta=1e6, rotary_dim=rd,
                                               qk_norm_bf16=w, cache_position=0)
-            want_k, want_v = oracle.round_e4m3(okc[0], ks), oracle.round_e4m3(ovc[0], vs)
+            want_k, want_v = _deq(oracle, fmt, okc[0], ks), _deq(oracle, fmt, ovc[0], vs)
             got_k = d_kc[s, pos].float().cpu().numpy() * np.float32(ks)
             got_v = d_vc[s, pos].float().cpu().numpy() * np.float32(vs)
             np.testing.assert_array_equal(got_v, want_v)           # V is quantised from the input itself
             # K went through f32 norm/RoPE arithmetic on both sides: a last-bit difference there can move a value that
             # sits on a rounding boundary to the neighbouring e4m3 value, never further
             diff = np.abs(got_k - want_k)
-            assert np.all(diff <= np.maximum(np.abs(want_k), ks * 2.0 ** -6) * 0.126), (s, t)
+            assert np.all(diff <= np.maximum(np.abs(want_k), ks * 2.0 ** -6) * (0.126 if fmt == F8E4M3 else 0.251)), (s, t)
             flips += int((diff > 0).sum())
             total += diff.size
     assert flips <= 0.01 * total
