@@ -320,7 +320,7 @@ int shady_attn_reduce(shady_ctx *ctx, uint32_t head_dim, uint32_t num_splits, ui
 /* ===================================================================================== */
 
 typedef struct {
-    uint32_t head_dim;        /* 128 */
+    uint32_t head_dim;        /* 128 or 256 */
     uint32_t num_kv_heads;
     uint32_t num_q_heads;
     uint32_t num_seqs;        /* batch */
@@ -343,8 +343,10 @@ int shady_attn_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void
  * in_dtype == p->dtype (bf16 or f16), interleaved RoPE with one position per token; q_out, q_gate and k_proj are not
  * written.  d_q_proj_full [num_seqs][T][nh][(1+has_gate)*hd]; d_k_proj / d_v_proj [num_seqs][T][nkv][hd];
  * d_out [num_seqs][T][nh][hd].  Cache addressing as in shady_attn_prefill.  d_workspace: at least
- * shady_prefill_workspace_size bytes, 16-byte aligned (a cos/sin table of the T positions; no initialisation
- * needed).  Replaces the prompt loop of src/inference.rs:93-95 for 16-bit caches. */
+ * shady_prefill_workspace_size bytes, 16-byte aligned, no initialisation needed (head_dim 128: a cos/sin table of
+ * the T positions; head_dim 256: the rotated Q of the batch, which that kernel takes from memory — there the step is
+ * one append pass over Q, K and V plus the attention kernel, whose epilogue still applies the gate).  Replaces the
+ * prompt loop of src/inference.rs:93-95 for 16-bit caches. */
 int shady_prefill_workspace_size(const shady_prefill_params *p, size_t *bytes);
 int shady_attn_prefill_append(shady_ctx *ctx, const shady_append_params *ap, const shady_prefill_params *p,
                               const void *d_q_proj_full, const void *d_k_proj, const void *d_v_proj,

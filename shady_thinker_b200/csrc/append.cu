@@ -307,11 +307,13 @@ int launch_append_kv_table(shady_ctx *ctx, const shady_append_params *p, const v
     return SHADY_OK;
 }
 
-int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,
-                  const void *d_v_proj, void *d_q_out, float *d_q_gate, const shady_kv_cache *cache,
-                  const uint16_t *d_qk_norm_bf16, const uint32_t *d_pos_start, const uint32_t *d_pos_h,
-                  const uint32_t *d_pos_w) {
-    SHADY_REQUIRE(ctx, p && d_q_proj_full && d_k_proj && d_v_proj && d_q_out && cache && d_pos_start,
+// `internal`: called by another launcher of this library, which may leave out the gate output and the positions
+// (all sequences then start at position 0)
+int launch_append_ex(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,
+                     const void *d_v_proj, void *d_q_out, float *d_q_gate, const shady_kv_cache *cache,
+                     const uint16_t *d_qk_norm_bf16, const uint32_t *d_pos_start, const uint32_t *d_pos_h,
+                     const uint32_t *d_pos_w, bool internal) {
+    SHADY_REQUIRE(ctx, p && d_q_proj_full && d_k_proj && d_v_proj && d_q_out && cache && (d_pos_start || internal),
                   SHADY_ERR_BAD_ARG, "kv_append_rope: null argument");
     SHADY_REQUIRE(ctx, p->num_heads && p->num_kv_heads && p->head_dim && p->num_seqs && p->tokens_per_seq,
                   SHADY_ERR_BAD_ARG, "kv_append_rope: zero-sized problem");
@@ -320,7 +322,7 @@ int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_
                   "kv_append_rope: rotary_dim must be even and <= head_dim");
     SHADY_REQUIRE(ctx, p->in_dtype <= SHADY_BF16 && p->q_dtype <= SHADY_BF16 && cache->dtype <= SHADY_F8E5M2,
                   SHADY_ERR_BAD_ARG, "kv_append_rope: bad dtype");
-    SHADY_REQUIRE(ctx, !p->has_gate || d_q_gate, SHADY_ERR_BAD_ARG, "kv_append_rope: has_gate needs d_q_gate");
+    SHADY_REQUIRE(ctx, !p->has_gate || d_q_gate || internal, SHADY_ERR_BAD_ARG, "kv_append_rope: has_gate needs d_q_gate");
     SHADY_REQUIRE(ctx, (cache->d_k_ptrs && cache->d_v_ptrs) || (cache->d_k_base && cache->d_v_base),
                   SHADY_ERR_BAD_ARG, "kv_append_rope: cache has neither base pointers nor pointer arrays");
     AppendArgs a{};
@@ -345,6 +347,14 @@ int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
+}
+
+int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,
+                  const void *d_v_proj, void *d_q_out, float *d_q_gate, const shady_kv_cache *cache,
+                  const uint16_t *d_qk_norm_bf16, const uint32_t *d_pos_start, const uint32_t *d_pos_h,
+                  const uint32_t *d_pos_w) {
+    return launch_append_ex(ctx, p, d_q_proj_full, d_k_proj, d_v_proj, d_q_out, d_q_gate, cache, d_qk_norm_bf16, d_pos_start,
+                            d_pos_h, d_pos_w, false);
 }
 
 }  // namespace shady

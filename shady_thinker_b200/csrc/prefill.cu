@@ -177,13 +177,13 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
 }
 // MN-major operand (V: each kv row holds 64 contiguous head dims = 128 B; 8-row groups 1024 B apart along K;
 // the second 64-dim slab kSlabBytes further): LBO = slab stride, SBO = 1024 B.
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
-    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(kSlabBytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t slab_bytes = kSlabBytes) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(slab_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
            (1ull << 46) | (2ull << 61);
 }
-// Instruction descriptor: fp32 accumulate, 16-bit A/B of format fmt (0 = f16, 1 = bf16), M = N = 128.
-__device__ __forceinline__ uint32_t make_idesc(uint32_t fmt, bool b_mn_major) {
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor: fp32 accumulate, 16-bit A/B of format fmt (0 = f16, 1 = bf16), M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(uint32_t fmt, bool b_mn_major, uint32_t n = 128) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -716,6 +716,314 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
 }
 
+
+// =====================================================================================================
+// head_dim 256 (the gated-attention layer shape): one 128-row Q tile per item, K/V tiles of 64 rows.
+//
+// S + O of two 128-row tiles would need 768 TMEM columns, so an item is ONE row tile: O takes 256 columns, and the
+// scores of consecutive K/V tiles alternate between two 64-column S buffers, so that the softmax of tile j runs while
+// the tensor core computes S(j+1).  M = 128, N = 64, K = 256 for S = Q K^T (16 MMAs), M = 128, N = 256, K = 64 for
+// O += P V (4 MMAs, P from TMEM, V as an MN-major shared-memory operand whose four 64-dim slabs the MMA walks).
+// Shared memory: Q 64 KB (four [128][64] slabs), K and V 32 KB per tile (four [64][64] slabs each), two stages.
+// Warps 0-3 softmax (one thread per row), warp 4 TMA producer, warp 5 MMA issuer and TMEM owner.
+// Because S(j+1) is issued ahead of PV(j), "S(j+1) complete" no longer says that O is free: PV(j) commits to a
+// barrier of its own, which the softmax threads pass before they touch O.
+// =====================================================================================================
+namespace p256 {
+constexpr int kM = 128, kN = 64, kD = 256, kStages = 2;
+constexpr uint32_t kQSlab = 128 * 128;          // [128 rows][64 elements] 16-bit
+constexpr uint32_t kQBytes = 4 * kQSlab;        // 64 KB
+constexpr uint32_t kKvSlab = 64 * 128;          // [64 rows][64 elements]
+constexpr uint32_t kKvTile = 4 * kKvSlab;       // 32 KB
+constexpr uint32_t kSmemK = kQBytes, kSmemV = kSmemK + kStages * kKvTile, kSmemBar = kSmemV + kStages * kKvTile;
+constexpr uint32_t kSmem = kSmemBar + 256 + 1024;
+enum { B_QFULL = 0, B_QEMPTY = 1, B_KVFULL = 2, B_KVEMPTY = 4, B_SFULL = 6, B_PFULL = 8, B_PVDONE = 10, B_OFULL = 11, B_COUNT = 12 };
+constexpr uint32_t kColS = 0, kColO = 128;      // TMEM columns: S0 [0,64) S1 [64,128) O [128,384); P_b = first 32 columns of S_b
+}  // namespace p256
+
+struct Prefill256Args {
+    void *out;
+    StatusRef status;
+    uint32_t wait_mbar;
+    uint32_t B, T, nh, nkv, G, m_tiles;   // m_tiles = ceil(T / 128)
+    float scale_log2;
+    const void *gate_src;   // optional: projection rows [B][T][nh][gate_row] whose elements [256, 512) are the gate
+    uint32_t gate_row;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(192, 1)
+prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v, const Prefill256Args a) {
+    using namespace p256;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char *smem = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar0 = smem_base + kSmemBar;
+    auto bar = [&](int i) { return bar0 + 8u * i; };
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemBar + 8 * B_COUNT);
+    volatile uint32_t *abort_word = tmem_slot + 1;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (gave_up(a.status)) return;
+    const WaitCtx wc{abort_word, a.status, a.wait_mbar};
+
+    struct Item { uint32_t b, h, kvh, q0, nkv; };
+    const uint32_t bh_count = a.B * a.nh, total_items = a.m_tiles * bh_count;
+    auto get_item = [&](uint32_t w) {   // heaviest (latest rows) first
+        Item it;
+        const uint32_t m = a.m_tiles - 1 - w / bh_count, bh = w % bh_count;
+        it.b = bh / a.nh; it.h = bh % a.nh; it.kvh = it.h / a.G; it.q0 = m * kM;
+        it.nkv = 2 * m + 2;             // kv tiles 0 .. (q0 + 127) / 64; rows past T read as zeros and are masked
+        return it;
+    };
+    auto item_of_round = [&](uint32_t rnd) {   // serpentine deal, as in the head_dim-128 kernel
+        return rnd * gridDim.x + ((rnd & 1u) ? gridDim.x - 1u - blockIdx.x : blockIdx.x);
+    };
+    constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+
+    if (warp == 4 && lane == 0) {
+        mbar_init(bar(B_QFULL), 1); mbar_init(bar(B_QEMPTY), 1); mbar_init(bar(B_PVDONE), 1); mbar_init(bar(B_OFULL), 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar(B_KVFULL + s), 1); mbar_init(bar(B_KVEMPTY + s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar(B_SFULL + b), 1); mbar_init(bar(B_PFULL + b), 128); }
+        *abort_word = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 4) {
+        // =============================== TMA producer ===============================
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t gk = 0, qi = 0;
+            for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
+                const uint32_t w = item_of_round(rnd);
+                if (w >= total_items) continue;
+                const Item it = get_item(w);
+                if (qi > 0) ok = mbar_wait(bar(B_QEMPTY), (qi - 1) & 1, wc, 12);
+                if (!ok) break;
+                ++qi;
+                mbar_expect_tx(bar(B_QFULL), kQBytes);
+                for (int c = 0; c < 4; ++c)
+                    tma_load_4d(smem_base + c * kQSlab, &map_q, bar(B_QFULL), 64 * c, (int)it.h, (int)it.q0, (int)it.b);
+                for (uint32_t j = 0; j < it.nkv && ok; ++j) {
+                    const uint32_t gi = gk + j, s = gi % kStages, ph = (gi / kStages) & 1;
+                    if (gi >= (uint32_t)kStages) ok = mbar_wait(bar(B_KVEMPTY + s), ph ^ 1, wc, 1);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(B_KVFULL + s), 2 * kKvTile);
+                    const uint32_t kd = smem_base + kSmemK + s * kKvTile, vd = smem_base + kSmemV + s * kKvTile;
+                    for (int c = 0; c < 4; ++c) {
+                        tma_load_4d(kd + c * kKvSlab, &map_k, bar(B_KVFULL + s), 64 * c, (int)it.kvh, (int)(j * kN), (int)it.b);
+                        tma_load_4d(vd + c * kKvSlab, &map_v, bar(B_KVFULL + s), 64 * c, (int)it.kvh, (int)(j * kN), (int)it.b);
+                    }
+                }
+                gk += it.nkv;
+            }
+        }
+    } else if (warp == 5) {
+        // =============================== MMA issuer ===============================
+        if (lane == 0) {
+            const uint32_t idesc_qk = make_idesc(kFmt, false, kN), idesc_pv = make_idesc(kFmt, true, kD);
+            bool ok = true;
+            auto issue_qk = [&](uint32_t sb, uint32_t s) {         // S_sb = Q * K(stage s)^T
+                const uint32_t kb = smem_base + kSmemK + s * kKvTile;
+#pragma unroll
+                for (uint32_t ks = 0; ks < kD / 16; ++ks)
+                    mma_ss(tmem + kColS + sb * kN, desc_kmajor(smem_base + (ks >> 2) * kQSlab + (ks & 3) * 32),
+                           desc_kmajor(kb + (ks >> 2) * kKvSlab + (ks & 3) * 32), idesc_qk, ks > 0);
+                tc_commit(bar(B_SFULL + sb));
+            };
+            auto issue_pv = [&](uint32_t sb, uint32_t s, bool first) {   // O (+)= P_sb * V(stage s)
+                const uint32_t vb = smem_base + kSmemV + s * kKvTile;
+#pragma unroll
+                for (uint32_t ks = 0; ks < kN / 16; ++ks)
+                    mma_ts(tmem + kColO, tmem + kColS + sb * kN + ks * 8, desc_mnmajor(vb + ks * 2048, kKvSlab), idesc_pv, !first || (ks > 0));
+            };
+            uint32_t gk = 0, qi = 0, sc = 0;   // running counts: K/V tiles, items, score tiles
+            for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
+                const uint32_t w = item_of_round(rnd);
+                if (w >= total_items) continue;
+                const Item it = get_item(w);
+                ok = mbar_wait(bar(B_QFULL), qi & 1, wc, 3);
+                ++qi;
+                if (!ok) break;
+                // S(0) first; then per tile: S(j+1) ahead of PV(j), so the tensor core has work while tile j is in its softmax
+                ok = mbar_wait(bar(B_KVFULL + gk % kStages), (gk / kStages) & 1, wc, 4);
+                if (!ok) break;
+                tc_fence_after();
+                issue_qk(sc & 1, gk % kStages);
+                if (it.nkv == 1) tc_commit(bar(B_QEMPTY));
+                for (uint32_t j = 0; j < it.nkv && ok; ++j) {
+                    if (j + 1 < it.nkv) {
+                        const uint32_t gi = gk + j + 1;
+                        ok = mbar_wait(bar(B_KVFULL + gi % kStages), (gi / kStages) & 1, wc, 4);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_qk((sc + j + 1) & 1, gi % kStages);
+                        if (j + 2 == it.nkv) tc_commit(bar(B_QEMPTY));   // the item's last S: Q is no longer needed
+                    }
+                    const uint32_t t = sc + j;
+                    ok = mbar_wait(bar(B_PFULL + (t & 1)), (t >> 1) & 1, wc, 8);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(t & 1, (gk + j) % kStages, j == 0);
+                    tc_commit(bar(B_KVEMPTY + (gk + j) % kStages));
+                    tc_commit(bar(B_PVDONE));
+                    if (j + 1 == it.nkv) tc_commit(bar(B_OFULL));
+                }
+                gk += it.nkv; sc += it.nkv;
+            }
+        }
+    } else {
+        // =============================== softmax (one thread per query row) ===============================
+        const uint32_t r = tid;                         // row in the tile == TMEM lane
+        const uint32_t lane_base = (warp * 32) << 16;
+        const uint32_t t_o = tmem + lane_base + kColO;
+        bool ok = true;
+        uint32_t sc = 0, oc = 0;                        // score tiles / items finished before the current item
+        for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
+            const uint32_t w = item_of_round(rnd);
+            if (w >= total_items) continue;
+            const Item item = get_item(w);
+            const uint32_t row = item.q0 + r;           // global query row == its causal limit
+            float m_ref = -INFINITY, l_sum = 0.f;
+            for (uint32_t j = 0; j < item.nkv && ok; ++j) {
+                const uint32_t t = sc + j, sb = t & 1;
+                const uint32_t t_s = tmem + lane_base + kColS + sb * kN;
+                ok = mbar_wait(bar(B_SFULL + sb), (t >> 1) & 1, wc, 9);
+                if (!ok) break;
+                tc_fence_after();
+                const int lim = (int)row - (int)(j * kN);   // columns 0..lim of this tile are visible (all 64 when lim >= 63)
+                uint32_t va[32], vb[32];
+                tmem_ld32(t_s, va);
+                tmem_ld32(t_s + 32, vb);
+                tmem_wait_ld();
+                float mx = -INFINITY;
+                if (lim >= kN - 1) {
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        m4[0] = max3(m4[0], __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
+                        m4[1] = max3(m4[1], __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
+                        m4[2] = max3(m4[2], __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
+                        m4[3] = max3(m4[3], __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
+                    }
+                    mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (i <= lim) mx = fmaxf(mx, __uint_as_float(va[i]));
+                        if (32 + i <= lim) mx = fmaxf(mx, __uint_as_float(vb[i]));
+                    }
+                }
+                mx *= a.scale_log2;                      // scale > 0; -inf stays -inf (a row that sees nothing of this tile)
+                float corr = 1.f;
+                if (j == 0) m_ref = mx;                  // key 0 is visible to every row: finite
+                else if (mx > m_ref + kRescaleThreshold) { corr = exp2f(m_ref - mx); m_ref = mx; }
+                // O belongs to PV(j-1) until that MMA has completed
+                if (j > 0) {
+                    ok = mbar_wait(bar(B_PVDONE), (t - 1) & 1, wc, 10);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+                    l_sum *= corr;
+#pragma unroll
+                    for (int c = 0; c < kD / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(t_o + c * 32, v);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                        tmem_st32(t_o + c * 32, v);
+                    }
+                }
+                // P = exp2(s * scale - m_ref), masked past the diagonal; packed over the first 32 columns of S
+                const float neg_m = -m_ref;
+                float ls[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = fast_exp2(fmaf(__uint_as_float(va[i]), a.scale_log2, neg_m));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(va[i + 1]), a.scale_log2, neg_m));
+                    float p2 = fast_exp2(fmaf(__uint_as_float(vb[i]), a.scale_log2, neg_m));
+                    float p3 = fast_exp2(fmaf(__uint_as_float(vb[i + 1]), a.scale_log2, neg_m));
+                    if (lim < kN - 1) {
+                        if (i > lim) p0 = 0.f;
+                        if (i + 1 > lim) p1 = 0.f;
+                        if (32 + i > lim) p2 = 0.f;
+                        if (33 + i > lim) p3 = 0.f;
+                    }
+                    ls[(i >> 1) & 1] += p0 + p1;
+                    ls[2 + ((i >> 1) & 1)] += p2 + p3;
+                    pk[i >> 1] = pack16<T>(p0, p1);
+                    pk[16 + (i >> 1)] = pack16<T>(p2, p3);
+                }
+                l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                tmem_st32(t_s, pk);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar(B_PFULL + sb));
+            }
+            // ---- epilogue: O / l (x sigmoid(gate)) -> global ----
+            if (ok) ok = mbar_wait(bar(B_OFULL), oc & 1, wc, 11);
+            if (ok) {
+                tc_fence_after();
+                const float inv = 1.0f / l_sum;
+                T *dst = reinterpret_cast<T *>(a.out) + (((size_t)item.b * a.T + row) * a.nh + item.h) * kD;
+                const T *gate = (a.gate_src && row < a.T)
+                                    ? reinterpret_cast<const T *>(a.gate_src) + (((size_t)item.b * a.T + row) * a.nh + item.h) * a.gate_row + kD : nullptr;
+#pragma unroll
+                for (int c = 0; c < kD / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(t_o + c * 32, v);
+                    tmem_wait_ld();
+                    if (row < a.T) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            float f[8];
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[i + k]) * inv;
+                            if (gate) {
+                                const uint4 g4 = *reinterpret_cast<const uint4 *>(gate + c * 32 + i);
+                                const T *ge = reinterpret_cast<const T *>(&g4);
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) f[k] *= sigmoidf_ref(to_f32<T>(ge[k]));
+                            }
+                            uint4 o4;
+                            o4.x = pack16<T>(f[0], f[1]); o4.y = pack16<T>(f[2], f[3]);
+                            o4.z = pack16<T>(f[4], f[5]); o4.w = pack16<T>(f[6], f[7]);
+                            *reinterpret_cast<uint4 *>(dst + c * 32 + i) = o4;
+                        }
+                    }
+                }
+                // the next item's first PV overwrites O: every row must have read it (the P barrier of that tile orders it)
+            }
+            sc += item.nkv;
+            ++oc;
+        }
+    }
+    // ---- teardown ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4 && lane == 0 && *abort_word) {
+        for (int s = 0; s < p256::kStages; ++s)
+            for (uint32_t i = 0; i < (1u << 16); ++i)
+                if (mbar_try(bar(p256::B_KVFULL + s), 0)) break;
+    }
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
 // ---- host side -----------------------------------------------------------------------------
 // cuTensorMapEncodeTiled is a driver API; it is looked up through the runtime so that the library does not link
 // against libcuda (and still loads on a machine without a driver, where only the host-side entry points work).
@@ -735,10 +1043,10 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 static bool make_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
-                        uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3) {
+                        uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t box_rows = 128) {
     cuuint64_t dims[4] = {d0, d1, d2, d3};
     cuuint64_t strides[3] = {s1, s2, s3};  // bytes, dims 1..3
-    cuuint32_t box[4] = {64, 1, 128, 1};   // 64 elements (128 B, the swizzle span) x 128 rows
+    cuuint32_t box[4] = {64, 1, box_rows, 1};   // 64 elements (128 B, the swizzle span) x box_rows rows
     cuuint32_t estr[4] = {1, 1, 1, 1};
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return false;
@@ -759,7 +1067,7 @@ static int launch_prefill_impl(shady_ctx *ctx, const char *who, const shady_pref
                                const shady_kv_cache *cache, void *d_out, const FusedQ *fq) {
     const std::string w(who);
     SHADY_REQUIRE(ctx, p && d_q && cache && d_out, SHADY_ERR_BAD_ARG, w + ": null argument");
-    SHADY_REQUIRE(ctx, p->head_dim == 128, SHADY_ERR_UNSUPPORTED, w + ": head_dim must be 128");
+    SHADY_REQUIRE(ctx, p->head_dim == 128, SHADY_ERR_UNSUPPORTED, w + ": head_dim must be 128 or 256");
     SHADY_REQUIRE(ctx, p->dtype == SHADY_BF16 || p->dtype == SHADY_F16, SHADY_ERR_UNSUPPORTED, w + ": dtype must be bf16 or f16");
     SHADY_REQUIRE(ctx, cache->dtype == p->dtype, SHADY_ERR_UNSUPPORTED, w + ": cache dtype must equal the Q dtype");
     SHADY_REQUIRE(ctx, p->num_seqs && p->seq_len && p->num_kv_heads && p->num_q_heads % p->num_kv_heads == 0, SHADY_ERR_BAD_ARG,
@@ -813,16 +1121,72 @@ static int launch_prefill_impl(shady_ctx *ctx, const char *who, const shady_pref
     return SHADY_OK;
 }
 
+// head_dim 256: Q [B][T][nh][256] already normed and rotated; gate_src (optional) the projection rows whose second
+// half is the gate
+static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefill_params *p, const void *d_q,
+                             const shady_kv_cache *cache, void *d_out, const void *gate_src, uint32_t gate_row) {
+    const std::string w(who);
+    SHADY_REQUIRE(ctx, p && d_q && cache && d_out, SHADY_ERR_BAD_ARG, w + ": null argument");
+    SHADY_REQUIRE(ctx, p->dtype == SHADY_BF16 || p->dtype == SHADY_F16, SHADY_ERR_UNSUPPORTED, w + ": dtype must be bf16 or f16");
+    SHADY_REQUIRE(ctx, cache->dtype == p->dtype, SHADY_ERR_UNSUPPORTED, w + ": cache dtype must equal the Q dtype");
+    SHADY_REQUIRE(ctx, p->num_seqs && p->seq_len && p->num_kv_heads && p->num_q_heads % p->num_kv_heads == 0, SHADY_ERR_BAD_ARG,
+                  w + ": bad shape");
+    SHADY_REQUIRE(ctx, cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs && !cache->d_page_table, SHADY_ERR_UNSUPPORTED,
+                  w + ": needs base + seq_stride cache addressing (TMA tensor maps), not pointer arrays or pages");
+    SHADY_REQUIRE(ctx, p->num_seqs == 1 || cache->seq_stride >= (uint64_t)p->seq_len * p->num_kv_heads * 256, SHADY_ERR_BAD_ARG,
+                  w + ": seq_stride smaller than one sequence");
+    SHADY_REQUIRE(ctx, ((uintptr_t)d_q | (uintptr_t)cache->d_k_base | (uintptr_t)cache->d_v_base | (uintptr_t)d_out | (uintptr_t)gate_src) % 16 == 0 &&
+                           (cache->seq_stride * 2) % 16 == 0,
+                  SHADY_ERR_BAD_ARG, w + ": buffers must be 16-byte aligned");
+    if (const int st = pending_timeout(ctx, who)) return st;
+    const uint32_t B = p->num_seqs, T = p->seq_len, nh = p->num_q_heads, nkv = p->num_kv_heads;
+    const CUtensorMapDataType dt = p->dtype == SHADY_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap mq, mk, mv;
+    const uint64_t seq_stride_b = (B == 1 ? (uint64_t)T * nkv * 256 : cache->seq_stride) * 2;
+    const bool maps_ok = make_map_4d(&mq, dt, d_q, 256, nh, T, B, 256 * 2, (uint64_t)nh * 256 * 2, (uint64_t)T * nh * 256 * 2, 128) &&
+                         make_map_4d(&mk, dt, cache->d_k_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64) &&
+                         make_map_4d(&mv, dt, cache->d_v_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64);
+    SHADY_REQUIRE(ctx, maps_ok, SHADY_ERR_CUDA, w + ": cuTensorMapEncodeTiled failed");
+    Prefill256Args a{};
+    a.out = d_out; a.status = status_ref(ctx); a.wait_mbar = ctx->wait_mbar;
+    a.B = B; a.T = T; a.nh = nh; a.nkv = nkv; a.G = nh / nkv;
+    a.m_tiles = (T + 127) / 128;
+    a.scale_log2 = (1.0f / sqrtf(256.0f)) * 1.4426950408889634f;
+    a.gate_src = gate_src; a.gate_row = gate_row;
+    const unsigned long long total_items = (unsigned long long)a.m_tiles * B * nh;
+    SHADY_REQUIRE(ctx, total_items <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, w + ": too many tiles for one launch");
+    const unsigned blocks = (unsigned)(total_items < (unsigned long long)ctx->num_sms ? total_items : (unsigned long long)ctx->num_sms);
+    static thread_local int configured_dev = -1;
+    if (configured_dev != ctx->device) {
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill256_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, p256::kSmem));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill256_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, p256::kSmem));
+        configured_dev = ctx->device;
+    }
+    if (p->dtype == SHADY_BF16) prefill256_kernel<__nv_bfloat16><<<blocks, 192, p256::kSmem, ctx->stream>>>(mq, mk, mv, a);
+    else prefill256_kernel<__half><<<blocks, 192, p256::kSmem, ctx->stream>>>(mq, mk, mv, a);
+    ctx->launches++;
+    SHADY_CUDA_OK(ctx, cudaGetLastError());
+    return SHADY_OK;
+}
+
 int launch_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_q, const shady_kv_cache *cache, void *d_out) {
+    if (p && p->head_dim == 256) return launch_prefill256(ctx, "attn_prefill", p, d_q, cache, d_out, nullptr, 0);
     return launch_prefill_impl(ctx, "attn_prefill", p, d_q, 128, cache, d_out, nullptr);
 }
+
+int launch_append_ex(shady_ctx *, const shady_append_params *, const void *, void *, const void *, void *, float *,
+                     const shady_kv_cache *, const uint16_t *, const uint32_t *, const uint32_t *, const uint32_t *, bool);
 
 // K/V half of the append (norm + RoPE of K, cache rows of K and V) plus the cos/sin table of positions [0, T)
 // (append.cu); Q is left to the attention kernel.
 int launch_append_kv_table(shady_ctx *ctx, const shady_append_params *ap, const void *d_k_proj, const void *d_v_proj,
                            const shady_kv_cache *cache, const uint16_t *d_qk_norm_bf16, float2 *d_cs_table);
 
-size_t prefill_workspace_bytes(const shady_prefill_params *p) { return (size_t)p->seq_len * 64 * sizeof(float2); }
+// head_dim 128: the cos/sin table of the T positions; head_dim 256: the normed and rotated Q of the whole batch
+size_t prefill_workspace_bytes(const shady_prefill_params *p) {
+    if (p->head_dim == 256) return (size_t)p->num_seqs * p->seq_len * p->num_q_heads * 256 * 2;
+    return (size_t)p->seq_len * 64 * sizeof(float2);
+}
 
 // The whole prefill step from the projections: one pass writes K (normed, rotated) and V into rows [0, T) of every
 // sequence's cache and the cos/sin table; the attention kernel then takes Q raw, norms and rotates it tile by tile in
@@ -840,6 +1204,16 @@ int launch_prefill_append(shady_ctx *ctx, const shady_append_params *ap, const s
                   SHADY_ERR_UNSUPPORTED, "attn_prefill_append: interleaved RoPE with one position per token only");
     SHADY_REQUIRE(ctx, d_ws && ws_bytes >= prefill_workspace_bytes(p) && ((uintptr_t)d_ws % 16) == 0, SHADY_ERR_WORKSPACE,
                   "attn_prefill_append: workspace missing, too small or not 16-byte aligned");
+    if (p->head_dim == 256) {
+        // the wide-head kernel takes Q rotated: one append pass writes it into the workspace (and K/V into the cache);
+        // the gate is read from the projection rows by the attention epilogue
+        shady_append_params ap2 = *ap;
+        ap2.q_dtype = p->dtype; ap2.write_k_back = 0;
+        if (const int st = launch_append_ex(ctx, &ap2, d_q_proj_full, const_cast<void *>(d_k_proj), d_v_proj, d_ws, nullptr, cache,
+                                            d_qk_norm_bf16, nullptr, nullptr, nullptr, true))
+            return st;
+        return launch_prefill256(ctx, "attn_prefill_append", p, d_ws, cache, d_out, ap->has_gate ? d_q_proj_full : nullptr, 512);
+    }
     float2 *table = reinterpret_cast<float2 *>(d_ws);
     if (const int st = launch_append_kv_table(ctx, ap, d_k_proj, d_v_proj, cache, d_qk_norm_bf16, table)) return st;
     const FusedQ fq{table, d_qk_norm_bf16, ap->has_gate, ap->eps};

@@ -11,8 +11,7 @@ from shady_thinker_b200._lib import BF16, F16, ShadyError
 pytestmark = pytest.mark.gpu
 
 
-def _run(gpu, oracle, B, T, nh, nkv, dt, seed, cap=None):
-    hd = 128
+def _run(gpu, oracle, B, T, nh, nkv, dt, seed, cap=None, hd=128):
     cap = cap or T
     q = rounded(oracle, oracle.randn((B, T, nh, hd), seed, 1), dt)
     k = rounded(oracle, oracle.randn((B, cap, nkv, hd), seed, 2), dt)
@@ -46,6 +45,18 @@ def test_ragged_length_and_padded_cache(gpu_ctx, oracle):
     # T not a multiple of the tile; cache capacity larger than T (rows >= T belong to the future)
     _run(gpu_ctx, oracle, 2, 333, 4, 2, BF16, 13, cap=400)
     _run(gpu_ctx, oracle, 1, 130, 4, 4, BF16, 14)
+
+
+@pytest.mark.parametrize("T", [128, 192, 256, 333, 640])
+def test_head_dim_256_small(gpu_ctx, oracle, T):
+    """The wide-head kernel (one 128-row tile per item, 64-row K/V tiles, S double-buffered in TMEM)."""
+    _run(gpu_ctx, oracle, 1, T, 2, 1, BF16, 21, hd=256)
+
+
+@pytest.mark.parametrize("dt", [BF16, F16])
+def test_head_dim_256_gqa_batch_more_items_than_sms(gpu_ctx, oracle, dt):
+    # 3 x 16 heads x 5 row tiles = 240 items: every CTA walks more than one, the barrier phases run on through them
+    _run(gpu_ctx, oracle, 3, 600, 16, 2, dt, 22, cap=640, hd=256)
 
 
 def test_equals_decode_of_the_last_token(gpu_ctx, oracle):
@@ -118,8 +129,7 @@ def test_cfg3_full_size_sampled_rows_and_linearity_in_v(gpu_ctx, oracle):
 
 # ---- the prefill step from the projections: K/V append + Q norm/RoPE inside the attention kernel + gate ----------
 
-def _fused_case(gpu, oracle, B, T, nh, nkv, dt, seed, rd, norm, gate, cap=None):
-    hd = 128
+def _fused_case(gpu, oracle, B, T, nh, nkv, dt, seed, rd, norm, gate, cap=None, hd=128):
     cap = cap or T
     qrow = 2 * hd if gate else hd
     qf = rounded(oracle, oracle.randn((B, T, nh, qrow), seed, 1), dt)
@@ -164,6 +174,13 @@ def _fused_case(gpu, oracle, B, T, nh, nkv, dt, seed, rd, norm, gate, cap=None):
 @pytest.mark.parametrize("rd,norm,gate", [(128, False, False), (32, True, True), (128, True, False), (64, False, True)])
 def test_prefill_from_the_projections_matches_the_token_loop(gpu_ctx, oracle, rd, norm, gate):
     _fused_case(gpu_ctx, oracle, 2, 384, 8, 2, BF16, 51, rd, norm, gate)
+
+
+@pytest.mark.parametrize("rd,norm,gate", [(64, True, True), (256, False, False)])
+def test_prefill_from_the_projections_head_dim_256(gpu_ctx, oracle, rd, norm, gate):
+    """The gated-attention layer shape: the step is one append pass (rotated Q into the workspace, K/V into the cache)
+    and the wide-head attention kernel, whose epilogue applies the gate."""
+    _fused_case(gpu_ctx, oracle, 2, 300, 4, 2, BF16, 55, rd, norm, gate, hd=256)
 
 
 def test_prefill_from_the_projections_f16_ragged_and_many_items(gpu_ctx, oracle):
