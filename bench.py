@@ -435,8 +435,17 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
 P_B, P_T, P_NH, P_NKV, P_HD = 4, 4096, 32, 8, 128
 
 
-def prefill_flops(B=P_B, T=P_T, nh=P_NH, hd=P_HD) -> float:
+def prefill_flops(B=None, T=None, nh=None, hd=None) -> float:
+    B, T, nh, hd = B or P_B, T or P_T, nh or P_NH, hd or P_HD
     return 4.0 * B * nh * hd * T * (T + 1) / 2
+
+
+def set_prefill_shape(hd: int) -> None:
+    """cfg3 as BASELINE.json states it has head_dim 128; `--prefill-hd 256` runs the same batch and length with the
+    head layout of config 4 (16 query heads, 2 KV heads, head_dim 256: the gated-attention layer shape)."""
+    global P_NH, P_NKV, P_HD
+    if hd == 256:
+        P_NH, P_NKV, P_HD = 16, 2, 256
 
 
 def prefill_config(n_gpus: int) -> dict:
@@ -666,7 +675,7 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
                          "traffic": None,
                          "peak_source": f"{src} cuBLAS bf16, {'sustained' if long_loop else 'burst'} figure "
                                         f"(burst {burst}, sustained {sustained})",
-                         "kernel": "prefill_kernel<bf16> alone (Q rotated beforehand); `value` is the whole step through shady_attn_prefill_append",
+                         "kernel": "prefill kernel alone (head_dim 128: prefill_kernel, 256: prefill256_kernel) on Q rotated beforehand; `value` is the whole step through shady_attn_prefill_append",
                          "algorithmic_flops_per_launch": flops,
                          "avg_launch_ms": attend_ms},
             "e2e": {"value": flops * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -886,6 +895,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--kv", default="fp16", choices=["fp16", "fp8", "fp8e5m2"],
                     help="cfg2 only: storage of the KV cache (fp8 = e4m3, fp8e5m2 = e5m2 rows written by the quantising append)")
+    ap.add_argument("--prefill-hd", type=int, default=128, choices=[128, 256],
+                    help="cfg3 only: 256 = the wide-head kernel on nh16/nkv2/hd256 (same batch and length)")
     ap.add_argument("--no-extra", action="store_true",
                     help="cfg2 only: skip the short cfg3 (prefill) and cfg4 (long context) legs added to the line as `extra`")
     ap.add_argument("--shape", default="plain", choices=["plain", "reference"],
@@ -901,6 +912,7 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.steps == 2000:   # the default suits cfg2 (0.1 ms steps); scale it for the others
         args.steps = {"cfg1": 300, "cfg3": 200, "cfg5": 5}.get(args.workload, 2000)
+    set_prefill_shape(args.prefill_hd)
     if args.impl == "reference":
         (run_reference_prefill if args.workload == "cfg3" else run_reference)(args, rank)   # decode configs share the cfg2 sample
         return
