@@ -330,7 +330,8 @@ typedef struct {
 
 /* d_q [num_seqs][T][nh][hd] (already normed/rotated by shady_kv_append_rope, which also
  * wrote rows [0,T) of the cache); d_out same shape.  Requires cache.d_k_base addressing with
- * seq_stride (one allocation) because the tiles are fetched through TMA tensor maps. */
+ * seq_stride (one allocation): one tensor map covers the batch.  Other caches and prompts of
+ * different lengths: shady_attn_prefill_ragged below. */
 int shady_attn_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_q,
                        const shady_kv_cache *cache, void *d_out);
 
@@ -352,6 +353,37 @@ int shady_attn_prefill_append(shady_ctx *ctx, const shady_append_params *ap, con
                               const void *d_q_proj_full, const void *d_k_proj, const void *d_v_proj,
                               const uint16_t *d_qk_norm_bf16, const shady_kv_cache *cache, void *d_out,
                               void *d_workspace, size_t workspace_bytes);
+
+/* Prompts of different lengths in one launch, and caches of any addressing (one allocation with seq_stride,
+ * per-sequence pointer arrays, page pools + page table) — what a batch built from the reference's cache slots
+ * (model.rs:973-1029), each prefilled by its own token loop (inference.rs:93-95), needs.  Sequence i has
+ * h_seq_lens[i] > 0 tokens; Q, the output and (for the _append form) the projections are packed token-major,
+ * sequence after sequence: [sum T_i][heads][...].  p->seq_len is not read.  The K/V tiles of a sequence come through
+ * a tensor map of its own, encoded on the HOST, which therefore needs the per-sequence base addresses: for a
+ * pointer-array cache pass host copies of the two arrays in h_k_ptrs / h_v_ptrs (NULL otherwise).  Rows past a
+ * sequence's end are never read from memory with those caches.  Paged caches: page_rows a multiple of the K/V tile
+ * (128 rows for head_dim 128, 64 for 256) or 8, 16, 32 or 64 below it; the rows between a sequence's end and the
+ * end of its last tile lie in the sequence's last page and must hold finite values — the _append form clears them,
+ * shady_attn_prefill_ragged expects the caller's pool to be initialised.  d_workspace: at least
+ * shady_prefill_ragged_workspace_size bytes (with_append = 1 for the _append form), 128-byte aligned, written by
+ * every call (row-block list, tensor maps, and for the _append form the cos/sin table or the rotated Q); the small
+ * tables are copied from a page-locked staging buffer of the context, so these two calls are not capturable into a
+ * CUDA graph.  No reference counterpart beyond the loop they replace. */
+typedef struct {
+    const uint32_t *h_seq_lens;      /* HOST [num_seqs] */
+    const void *const *h_k_ptrs;     /* HOST [num_seqs] copy of cache.d_k_ptrs, or NULL */
+    const void *const *h_v_ptrs;     /* HOST [num_seqs] copy of cache.d_v_ptrs, or NULL */
+} shady_prefill_batch;
+int shady_prefill_ragged_workspace_size(const shady_prefill_params *p, const uint32_t *h_seq_lens, int with_append,
+                                        size_t *bytes);
+int shady_attn_prefill_ragged(shady_ctx *ctx, const shady_prefill_params *p, const shady_prefill_batch *batch,
+                              const void *d_q, const shady_kv_cache *cache, void *d_out, void *d_workspace,
+                              size_t workspace_bytes);
+int shady_attn_prefill_append_ragged(shady_ctx *ctx, const shady_append_params *ap, const shady_prefill_params *p,
+                                     const shady_prefill_batch *batch, const void *d_q_proj_full,
+                                     const void *d_k_proj, const void *d_v_proj, const uint16_t *d_qk_norm_bf16,
+                                     const shady_kv_cache *cache, void *d_out, void *d_workspace,
+                                     size_t workspace_bytes);
 
 /* ===================================================================================== */
 /* Output gate — replaces Model::sigmoid_mul_gate (model.rs:576-593), sigmoid_mul.wgsl    */

@@ -23,6 +23,7 @@ EXPORTS = [
     "shady_flush", "shady_synchronize", "shady_kv_append_rope", "shady_decode_workspace_size", "shady_decode_workspace_init",
     "shady_attn_decode", "shady_attn_decode_static", "shady_attn_decode_shard", "shady_attn_decode_append", "shady_attn_decode_partials", "shady_attn_reduce", "shady_attn_prefill",
     "shady_prefill_workspace_size", "shady_attn_prefill_append",
+    "shady_prefill_ragged_workspace_size", "shady_attn_prefill_ragged", "shady_attn_prefill_append_ragged",
     "shady_gptq_matvec", "shady_qkv_proj_append",
     "shady_sigmoid_mul", "shady_fill_randn", "shady_ipc_export", "shady_ipc_open", "shady_ipc_close",
     "shady_combine_p2p_buffer_size", "shady_attn_combine_p2p", "shady_attn_decode_shard_p2p",
@@ -65,6 +66,10 @@ class GptqWeight(C.Structure):
 class PrefillParams(C.Structure):
     _fields_ = [("head_dim", C.c_uint32), ("num_kv_heads", C.c_uint32), ("num_q_heads", C.c_uint32),
                 ("num_seqs", C.c_uint32), ("seq_len", C.c_uint32), ("dtype", C.c_uint32)]
+
+
+class PrefillBatch(C.Structure):
+    _fields_ = [("h_seq_lens", C.c_void_p), ("h_k_ptrs", C.c_void_p), ("h_v_ptrs", C.c_void_p)]
 
 
 _lib = None
@@ -116,6 +121,11 @@ def load() -> C.CDLL:
     L.shady_prefill_workspace_size.argtypes = [C.POINTER(PrefillParams), C.POINTER(sz)]
     L.shady_attn_prefill_append.argtypes = [vp, C.POINTER(AppendParams), C.POINTER(PrefillParams), vp, vp, vp, vp,
                                             C.POINTER(KvCache), vp, vp, sz]
+    L.shady_prefill_ragged_workspace_size.argtypes = [C.POINTER(PrefillParams), vp, C.c_int, C.POINTER(sz)]
+    L.shady_attn_prefill_ragged.argtypes = [vp, C.POINTER(PrefillParams), C.POINTER(PrefillBatch), vp, C.POINTER(KvCache),
+                                            vp, vp, sz]
+    L.shady_attn_prefill_append_ragged.argtypes = [vp, C.POINTER(AppendParams), C.POINTER(PrefillParams),
+                                                   C.POINTER(PrefillBatch), vp, vp, vp, vp, C.POINTER(KvCache), vp, vp, sz]
     L.shady_ipc_export.argtypes = [vp, vp, C.c_char_p]
     L.shady_ipc_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
     L.shady_ipc_close.argtypes = [vp, vp]

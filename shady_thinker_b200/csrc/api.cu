@@ -95,6 +95,12 @@ int launch_append(shady_ctx *, const shady_append_params *, const void *, void *
                   const shady_kv_cache *, const uint16_t *, const uint32_t *, const uint32_t *, const uint32_t *);
 int launch_prefill(shady_ctx *, const shady_prefill_params *, const void *, const shady_kv_cache *, void *);
 size_t prefill_workspace_bytes(const shady_prefill_params *p);
+size_t prefill_ragged_workspace_bytes(const shady_prefill_params *p, const uint32_t *h_seq_lens, bool with_append);
+int launch_prefill_ragged(shady_ctx *, const shady_prefill_params *, const shady_prefill_batch *, const void *, const shady_kv_cache *,
+                          void *, void *, size_t);
+int launch_prefill_append_ragged(shady_ctx *, const shady_append_params *, const shady_prefill_params *, const shady_prefill_batch *,
+                                 const void *, const void *, const void *, const uint16_t *, const shady_kv_cache *, void *, void *,
+                                 size_t);
 int launch_gptq_matvec(shady_ctx *, const shady_gptq_weight *, const float *, float *, uint32_t);
 int launch_qkv_proj_append(shady_ctx *, const shady_append_params *, const shady_gptq_weight *, const shady_gptq_weight *,
                            const shady_gptq_weight *, const float *, void *, float *, const shady_kv_cache *, const uint16_t *,
@@ -193,6 +199,8 @@ int shady_ctx_destroy(shady_ctx *ctx) {
     }
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    if (ctx->stage_done) cudaEventDestroy(ctx->stage_done);
+    if (ctx->stage) cudaFreeHost(ctx->stage);
     delete ctx;
     return SHADY_OK;
 }
@@ -378,6 +386,28 @@ int shady_attn_prefill_append(shady_ctx *ctx, const shady_append_params *ap, con
     CTX_ENTER(ctx);
     return launch_prefill_append(ctx, ap, p, d_q_proj_full, d_k_proj, d_v_proj, d_qk_norm_bf16, cache, d_out, d_workspace,
                                  workspace_bytes);
+}
+
+int shady_prefill_ragged_workspace_size(const shady_prefill_params *p, const uint32_t *h_seq_lens, int with_append, size_t *bytes) {
+    if (!p || !h_seq_lens || !bytes || !p->num_seqs) return SHADY_ERR_BAD_ARG;
+    *bytes = prefill_ragged_workspace_bytes(p, h_seq_lens, with_append != 0);
+    return SHADY_OK;
+}
+
+int shady_attn_prefill_ragged(shady_ctx *ctx, const shady_prefill_params *p, const shady_prefill_batch *batch, const void *d_q,
+                              const shady_kv_cache *cache, void *d_out, void *d_workspace, size_t workspace_bytes) {
+    CTX_ENTER(ctx);
+    SHADY_REQUIRE(ctx, d_q && d_out, SHADY_ERR_BAD_ARG, "attn_prefill_ragged: null argument");
+    return launch_prefill_ragged(ctx, p, batch, d_q, cache, d_out, d_workspace, workspace_bytes);
+}
+
+int shady_attn_prefill_append_ragged(shady_ctx *ctx, const shady_append_params *ap, const shady_prefill_params *p,
+                                     const shady_prefill_batch *batch, const void *d_q_proj_full, const void *d_k_proj,
+                                     const void *d_v_proj, const uint16_t *d_qk_norm_bf16, const shady_kv_cache *cache, void *d_out,
+                                     void *d_workspace, size_t workspace_bytes) {
+    CTX_ENTER(ctx);
+    return launch_prefill_append_ragged(ctx, ap, p, batch, d_q_proj_full, d_k_proj, d_v_proj, d_qk_norm_bf16, cache, d_out,
+                                        d_workspace, workspace_bytes);
 }
 
 int shady_ipc_export(shady_ctx *ctx, void *d_buf, unsigned char handle[64]) {

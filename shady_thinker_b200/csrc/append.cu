@@ -33,6 +33,10 @@ struct AppendArgs {
     uint32_t skip_q;          // vectorised path: K/V only (Q is normed and rotated by the prefill attention kernel itself)
     float2 *cs_table;         // vectorised path, optional: (cos, sin) of [token j][pair i < hd/2] of sequence 0, (1, 0) past rd/2
     float k_inv, v_inv;       // 8-bit caches: rows are stored as value * (1 / scale); 1 otherwise
+    // vectorised path, listed batch: tokens are packed sequence after sequence, sequence s owns tokens
+    // [tok_start[s], tok_start[s+1]); T is not used
+    const uint32_t *tok_start;
+    uint32_t total_tokens, table_seq;
     float inv_freq[128];      // [rd/2]
 };
 
@@ -151,8 +155,19 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
     const unsigned long long wid = (unsigned long long)blockIdx.x * kAppendWarps + warp;
     const unsigned long long tok = wid / a.head_slices;
     const uint32_t slice = (uint32_t)(wid % a.head_slices);
-    if (tok >= (unsigned long long)a.num_seqs * a.T) return;
-    const uint32_t s = (uint32_t)(tok / a.T), j = (uint32_t)(tok % a.T);
+    uint32_t s, j;
+    if (a.tok_start) {
+        if (tok >= a.total_tokens) return;
+        uint32_t lo = 0, hi = a.num_seqs;   // the sequence with tok_start[s] <= tok < tok_start[s + 1]
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (__ldg(a.tok_start + mid) <= (uint32_t)tok) lo = mid; else hi = mid;
+        }
+        s = lo; j = (uint32_t)tok - __ldg(a.tok_start + lo);
+    } else {
+        if (tok >= (unsigned long long)a.num_seqs * a.T) return;
+        s = (uint32_t)(tok / a.T); j = (uint32_t)(tok % a.T);
+    }
     const uint32_t sub = lane / LPH, dl = lane % LPH, d0 = dl * 8;
     // ---- cos/sin of this lane's four pairs (wgsl:56-68) ----
     const uint32_t p_t = (a.pos_start ? a.pos_start[s] : 0u) + j;
@@ -170,7 +185,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
             sincosf((float)pos * a.inv_freq[i], &sn[k], &cs[k]);
         }
     }
-    if (a.cs_table && s == 0 && slice == 0 && sub == 0) {   // one 16-lane group per token writes the token's table row
+    if (a.cs_table && s == a.table_seq && slice == 0 && sub == 0) {   // one 16-lane group per token writes the token's table row
         float4 *row = reinterpret_cast<float4 *>(a.cs_table + (size_t)j * (HD / 2) + dl * 4);
         row[0] = make_float4(cs[0], sn[0], cs[1], sn[1]);
         row[1] = make_float4(cs[2], sn[2], cs[3], sn[3]);
@@ -247,7 +262,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
 
 template <typename TIn, typename TQ, typename TKV>
 static void launch_append_fast(shady_ctx *ctx, AppendArgs &a) {
-    const unsigned long long toks = (unsigned long long)a.num_seqs * a.T;
+    const unsigned long long toks = a.tok_start ? a.total_tokens : (unsigned long long)a.num_seqs * a.T;
     // enough warps to fill the GPU: split a token's heads over several warps when there are few tokens
     const uint32_t hpi = 32 / (a.hd / 8);
     const uint32_t max_slices = ((a.skip_q ? a.nkv : a.nh) + hpi - 1) / hpi;
@@ -281,7 +296,7 @@ static bool try_append_fast(shady_ctx *ctx, AppendArgs &a, const void *q_in, con
 }
 
 int launch_append_kv_table(shady_ctx *ctx, const shady_append_params *p, const void *d_k_proj, const void *d_v_proj,
-                           const shady_kv_cache *cache, const uint16_t *d_qk_norm_bf16, float2 *d_cs_table) {
+                           const shady_kv_cache *cache, const uint16_t *d_qk_norm_bf16, float2 *d_cs_table, const AppendRagged *rg) {
     SHADY_REQUIRE(ctx, p->head_dim == 128 && p->in_dtype == cache->dtype && p->in_dtype != SHADY_F32, SHADY_ERR_UNSUPPORTED,
                   "attn_prefill_append: head_dim 128 and 16-bit projections in the cache dtype");
     AppendArgs a{};
@@ -293,10 +308,12 @@ int launch_append_kv_table(shady_ctx *ctx, const shady_append_params *p, const v
     a.num_seqs = p->num_seqs; a.T = p->tokens_per_seq;
     a.in_dtype = a.q_dtype = a.kv_dtype = p->in_dtype;
     a.skip_q = 1; a.cs_table = d_cs_table;
+    if (rg) { a.tok_start = rg->d_tok_start; a.total_tokens = rg->total_tokens; a.table_seq = rg->table_seq; }
     a.k_inv = a.v_inv = 1.0f;
     for (uint32_t i = 0; i < p->rotary_dim / 2; ++i)   // wgsl:57, same libm call as everywhere else
         a.inv_freq[i] = 1.0f / powf(p->rope_theta, 2.0f * (float)i / (float)p->rotary_dim);
-    SHADY_REQUIRE(ctx, (unsigned long long)a.num_seqs * a.T <= 0x3fffffffull, SHADY_ERR_UNSUPPORTED, "attn_prefill_append: too many tokens for one launch");
+    SHADY_REQUIRE(ctx, (rg ? (unsigned long long)rg->total_tokens : (unsigned long long)a.num_seqs * a.T) <= 0x3fffffffull, SHADY_ERR_UNSUPPORTED,
+                  "attn_prefill_append: too many tokens for one launch");
     SHADY_REQUIRE(ctx, !((((uintptr_t)d_k_proj | (uintptr_t)d_v_proj | (uintptr_t)a.kv.k_base | (uintptr_t)a.kv.v_base) & 15) ||
                          (a.kv.seq_stride_bytes & 15)),
                   SHADY_ERR_BAD_ARG, "attn_prefill_append: buffers must be 16-byte aligned");
@@ -312,10 +329,10 @@ int launch_append_kv_table(shady_ctx *ctx, const shady_append_params *p, const v
 int launch_append_ex(shady_ctx *ctx, const shady_append_params *p, const void *d_q_proj_full, void *d_k_proj,
                      const void *d_v_proj, void *d_q_out, float *d_q_gate, const shady_kv_cache *cache,
                      const uint16_t *d_qk_norm_bf16, const uint32_t *d_pos_start, const uint32_t *d_pos_h,
-                     const uint32_t *d_pos_w, bool internal) {
+                     const uint32_t *d_pos_w, bool internal, const AppendRagged *rg) {
     SHADY_REQUIRE(ctx, p && d_q_proj_full && d_k_proj && d_v_proj && d_q_out && cache && (d_pos_start || internal),
                   SHADY_ERR_BAD_ARG, "kv_append_rope: null argument");
-    SHADY_REQUIRE(ctx, p->num_heads && p->num_kv_heads && p->head_dim && p->num_seqs && p->tokens_per_seq,
+    SHADY_REQUIRE(ctx, p->num_heads && p->num_kv_heads && p->head_dim && p->num_seqs && (p->tokens_per_seq || rg),
                   SHADY_ERR_BAD_ARG, "kv_append_rope: zero-sized problem");
     SHADY_REQUIRE(ctx, p->head_dim <= 256, SHADY_ERR_UNSUPPORTED, "kv_append_rope: head_dim > 256 (the reference shader's limit)");
     SHADY_REQUIRE(ctx, p->rotary_dim <= p->head_dim && (p->rotary_dim % 2) == 0, SHADY_ERR_BAD_ARG,
@@ -336,14 +353,18 @@ int launch_append_ex(shady_ctx *ctx, const shady_append_params *p, const void *d
     a.in_dtype = p->in_dtype; a.q_dtype = p->q_dtype; a.kv_dtype = cache->dtype;
     a.has_gate = p->has_gate; a.write_k_back = p->write_k_back;
     a.k_inv = 1.0f / a.kv.k_scale; a.v_inv = 1.0f / a.kv.v_scale;
+    if (rg) { a.tok_start = rg->d_tok_start; a.total_tokens = rg->total_tokens; a.table_seq = rg->table_seq; }
     // apply_mrope: freq = 1.0 / pow(ROPE_THETA, 2.0 * f32(freq_idx) / f32(PARTIAL_DIM))  (wgsl:57)
     for (uint32_t i = 0; i < p->rotary_dim / 2; ++i)
         a.inv_freq[i] = 1.0f / powf(p->rope_theta, 2.0f * (float)i / (float)p->rotary_dim);
     const unsigned long long warps = (unsigned long long)p->num_seqs * p->tokens_per_seq * (p->num_heads + p->num_kv_heads);
     const unsigned long long blocks = (warps + kAppendWarps - 1) / kAppendWarps;
     SHADY_REQUIRE(ctx, blocks <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, "kv_append_rope: too many tokens for one launch");
-    if (!try_append_fast(ctx, a, d_q_proj_full, d_k_proj, d_v_proj, d_q_out))
+    if (!try_append_fast(ctx, a, d_q_proj_full, d_k_proj, d_v_proj, d_q_out)) {
+        SHADY_REQUIRE(ctx, !rg, SHADY_ERR_UNSUPPORTED,
+                      "kv_append_rope: a listed batch needs interleaved RoPE, head_dim 128 or 256 and 16-byte aligned buffers");
         append_kernel<<<(unsigned)blocks, kAppendWarps * 32, 0, ctx->stream>>>(a);
+    }
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
@@ -354,7 +375,7 @@ int launch_append(shady_ctx *ctx, const shady_append_params *p, const void *d_q_
                   const uint16_t *d_qk_norm_bf16, const uint32_t *d_pos_start, const uint32_t *d_pos_h,
                   const uint32_t *d_pos_w) {
     return launch_append_ex(ctx, p, d_q_proj_full, d_k_proj, d_v_proj, d_q_out, d_q_gate, cache, d_qk_norm_bf16, d_pos_start,
-                            d_pos_h, d_pos_w, false);
+                            d_pos_h, d_pos_w, false, nullptr);
 }
 
 }  // namespace shady

@@ -40,6 +40,11 @@ struct shady_ctx {
     uint32_t wait_peer = 1u << 22;   // polls of a peer's NVLink flag
     uint32_t wait_mbar = 1u << 20;   // polls of an mbarrier in the prefill kernel
     bool rezero_workspace = false;   // a wait ran out: the next decode launch clears its workspace's counters first
+    // small host tables (row-block lists, tensor maps of a listed prefill batch) go to the device through this
+    // page-locked buffer; stage_done = the last copy out of it
+    void *stage = nullptr;
+    size_t stage_bytes = 0;
+    cudaEvent_t stage_done = nullptr;
 };
 
 // What a kernel needs to report (and notice) an expired wait.
@@ -149,6 +154,13 @@ __device__ __forceinline__ const char *kv_row_ptr(const KvAddr &kv, bool want_v,
     return kv_seq_ptr(want_v ? kv.v_base : kv.k_base, want_v ? kv.v_ptrs : kv.k_ptrs, kv.seq_stride_bytes, s) +
            (size_t)pos * row_bytes;
 }
+// How the append pass finds a token's sequence when the batch is a list of prompts of different lengths, packed
+// token-major (prefill of a listed batch).
+struct AppendRagged {
+    const uint32_t *d_tok_start;   // [num_seqs + 1] first packed token of every sequence
+    uint32_t total_tokens;
+    uint32_t table_seq;            // the sequence whose tokens write the cos/sin table (the longest one)
+};
 // Checks a caller's cache description and turns it into the device-side form (defined in api.cu).
 int fill_kv_addr(shady_ctx *ctx, const shady_kv_cache *cache, uint32_t nkv, uint32_t hd, const char *who, KvAddr *out);
 

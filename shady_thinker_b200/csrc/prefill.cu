@@ -33,7 +33,10 @@
 // happens, and with three buffers a tile of the next item is transformed while the current item still computes.
 #include <cuda.h>
 
+#include <string.h>
+
 #include <type_traits>
+#include <vector>
 
 #include "common.cuh"
 
@@ -66,8 +69,20 @@ constexpr uint32_t kQWarps = 4;
 constexpr uint32_t kFusedThreads = 512;
 constexpr uint32_t kRegsSoftmax = 176, kRegsOther = 80;
 
+// Batches that are not B equal sequences in one base + stride allocation.  The host lists the row blocks of all
+// sequences heaviest first; Q and the output are then packed token-major (sequence after sequence), and K/V rows
+// come through one tensor map per sequence (extent T_i, so rows past the sequence read as zero) or, for paged
+// caches, through the pool's map and the page table.
+struct RaggedRef {
+    const uint4 *items;           // [entries] {sequence, row block, T of the sequence, first packed token}; NULL = uniform batch
+    const CUtensorMap *kv_maps;   // [2 * num_seqs] K and V map of every sequence, in global memory; NULL = map_k / map_v cover the batch (or the pool)
+    const uint32_t *page_table;   // paged caches: [num_seqs][max_pages] page of every page_rows rows
+    uint32_t entries, max_pages, page_rows, box_rows, oob_page;
+};
+
 struct PrefillArgs {
     void *out;
+    RaggedRef rg;
     StatusRef status;    // where a wait that ran out is reported (code 1..12 = which barrier)
     uint32_t wait_mbar;  // poll limit of every mbarrier wait
     uint32_t B, T, nh, nkv, G;
@@ -122,6 +137,32 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+// a tensor map that lives in global memory (written by a copy that the stream ordered before this kernel): the
+// CTA's first use of it goes through this fence
+__device__ __forceinline__ void tensormap_acquire(const CUtensorMap *map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(map) : "memory");
+}
+// One K/V tile (ROWS rows x SLABS slabs of 64 elements) of sequence b, kv head kvh, first row row0, into dst (slab
+// stride slab_bytes), completing on bar.  Uniform batches: coordinate 3 = sequence.  Per-sequence maps: coordinate 3 = 0.
+// Paged caches: the tile is fetched in boxes of rg.box_rows rows (a page, or the whole tile when a page holds
+// several), each at (row in page, page); a box that starts past the sequence takes an out-of-range page and so
+// reads as zero, which also keeps the lookup inside the table entries the sequence owns.
+template <int ROWS, int SLABS>
+__device__ __forceinline__ void tma_load_kv_tile(uint32_t dst, uint32_t slab_bytes, const CUtensorMap *map, uint32_t bar, const RaggedRef &rg,
+                                                 uint32_t b, uint32_t kvh, uint32_t row0, uint32_t T, bool per_seq) {
+    if (rg.page_table) {
+        for (uint32_t r = 0; r < (uint32_t)ROWS; r += rg.box_rows) {
+            const uint32_t row = row0 + r;
+            const uint32_t page = row < T ? __ldg(rg.page_table + (size_t)b * rg.max_pages + row / rg.page_rows) : rg.oob_page;
+#pragma unroll
+            for (int c = 0; c < SLABS; ++c)
+                tma_load_4d(dst + c * slab_bytes + r * 128u, map, bar, 64 * c, (int)kvh, (int)(row % rg.page_rows), (int)page);
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < SLABS; ++c) tma_load_4d(dst + c * slab_bytes, map, bar, 64 * c, (int)kvh, (int)row0, per_seq ? 0 : (int)b);
+    }
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -271,15 +312,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     // the next item while the softmax warps finish the current one (pipeline fill/drain overlap instead of adding up).
     struct Item {
         uint32_t b, h, kvh, q0, n[2], nkv;
+        uint32_t len, tok0;     // rows of the sequence; packed row of its first token (Q, output, gate)
+        uint32_t qrow, qseq;    // TMA coordinates 2 and 3 of the item's first Q row
     };
     const uint32_t bh_count = a.B * a.nh;
-    const uint32_t total_items = a.m_tiles * bh_count;
+    const uint32_t total_items = a.rg.items ? a.rg.entries * a.nh : a.m_tiles * bh_count;
     auto get_item = [&](uint32_t w) {
         Item it;
-        const uint32_t m = a.m_tiles - 1 - w / bh_count, bh = w % bh_count;
-        it.b = bh / a.nh; it.h = bh % a.nh; it.kvh = it.h / a.G; it.q0 = m * 256;
+        uint32_t m;
+        if (a.rg.items) {   // listed row blocks (heaviest first), the heads of a block side by side
+            const uint4 e = __ldg(a.rg.items + w / a.nh);
+            it.b = e.x; m = e.y; it.len = e.z; it.tok0 = e.w; it.h = w % a.nh;
+            it.q0 = m * 256; it.qrow = it.tok0 + it.q0; it.qseq = 0;
+        } else {
+            const uint32_t bh = w % bh_count;
+            m = a.m_tiles - 1 - w / bh_count;
+            it.b = bh / a.nh; it.h = bh % a.nh; it.len = a.T; it.tok0 = it.b * a.T;
+            it.q0 = m * 256; it.qrow = it.q0; it.qseq = it.b;
+        }
+        it.kvh = it.h / a.G;
         it.n[0] = 2 * m + 1;                                   // kv tiles of the two 128-row query tiles
-        it.n[1] = (it.q0 + kPM < a.T) ? 2 * m + 2 : 0u;
+        it.n[1] = (it.q0 + kPM < it.len) ? 2 * m + 2 : 0u;
         it.nkv = it.n[1] ? it.n[1] : it.n[0];
         return it;
     };
@@ -335,8 +388,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     const uint32_t landed = bar((FUSED ? BAR_QRAW : BAR_QFULL) + buf);
                     mbar_expect_tx(landed, kTileBytes);
                     const uint32_t dst = smem_base + kSmemQ + buf * kTileBytes;
-                    tma_load_4d(dst, &map_q, landed, 0, (int)it.h, (int)(it.q0 + q * kPM), (int)it.b);
-                    tma_load_4d(dst + kSlabBytes, &map_q, landed, 64, (int)it.h, (int)(it.q0 + q * kPM), (int)it.b);
+                    tma_load_4d(dst, &map_q, landed, 0, (int)it.h, (int)(it.qrow + q * kPM), (int)it.qseq);
+                    tma_load_4d(dst + kSlabBytes, &map_q, landed, 64, (int)it.h, (int)(it.qrow + q * kPM), (int)it.qseq);
+                }
+                const CUtensorMap *mk = &map_k, *mv = &map_v;
+                if (a.rg.kv_maps) {
+                    mk = a.rg.kv_maps + 2 * it.b; mv = mk + 1;
+                    tensormap_acquire(mk); tensormap_acquire(mv);
                 }
                 for (uint32_t j = 0; j < it.nkv && ok; ++j) {   // K and V tile j travel together: one stage, one barrier
                     const uint32_t gi = gk + j;
@@ -345,10 +403,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (!ok) break;
                     mbar_expect_tx(bar(BAR_KVFULL + s), 2 * kTileBytes);
                     const uint32_t kd = smem_base + kSmemK + s * kTileBytes, vd = smem_base + kSmemV + s * kTileBytes;
-                    tma_load_4d(kd, &map_k, bar(BAR_KVFULL + s), 0, (int)it.kvh, (int)(j * kPN), (int)it.b);
-                    tma_load_4d(kd + kSlabBytes, &map_k, bar(BAR_KVFULL + s), 64, (int)it.kvh, (int)(j * kPN), (int)it.b);
-                    tma_load_4d(vd, &map_v, bar(BAR_KVFULL + s), 0, (int)it.kvh, (int)(j * kPN), (int)it.b);
-                    tma_load_4d(vd + kSlabBytes, &map_v, bar(BAR_KVFULL + s), 64, (int)it.kvh, (int)(j * kPN), (int)it.b);
+                    tma_load_kv_tile<kPN, 2>(kd, kSlabBytes, mk, bar(BAR_KVFULL + s), a.rg, it.b, it.kvh, j * kPN, it.len, a.rg.kv_maps != nullptr);
+                    tma_load_kv_tile<kPN, 2>(vd, kSlabBytes, mv, bar(BAR_KVFULL + s), a.rg, it.b, it.kvh, j * kPN, it.len, a.rg.kv_maps != nullptr);
                 }
                 gk += it.nkv;
             }
@@ -468,7 +524,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 auto load_tab = [&](uint32_t pass0) {
 #pragma unroll
                     for (int u = 0; u < kBatch; ++u) {
-                        const uint32_t pos = min(row_base + (pass0 + u) * kRowsPerPass + rsub, a.T - 1);
+                        const uint32_t pos = min(row_base + (pass0 + u) * kRowsPerPass + rsub, it.len - 1);
                         const float4 *tp = reinterpret_cast<const float4 *>(a.cs_table + (size_t)pos * 64 + c * 4);
                         tab[u][0] = __ldg(tp);
                         tab[u][1] = __ldg(tp + 1);
@@ -538,8 +594,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint32_t w = item_of_round(rnd);
         if (w >= total_items) continue;
         const Item item = get_item(w);
-        const uint32_t nq = item.n[q], h = item.h, b = item.b;
-        const uint32_t row = item.q0 + q * kPM + r;     // global query row == its causal limit
+        const uint32_t nq = item.n[q], h = item.h;
+        const uint32_t row = item.q0 + q * kPM + r;     // query row within its sequence == its causal limit
         if (!nq) continue;
         float m_ref = -INFINITY, l_sum = 0.f;
         for (uint32_t j = 0; j < nq && ok; ++j) {
@@ -663,10 +719,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (nq && ok) {
             tc_fence_after();
             const float inv = 1.0f / l_sum;
-            T *dst = reinterpret_cast<T *>(a.out) + (((size_t)b * a.T + row) * a.nh + h) * kPD;
+            T *dst = reinterpret_cast<T *>(a.out) + (((size_t)item.tok0 + row) * a.nh + h) * kPD;
             // fused: the gate half of the row's projection (fused_split_qknorm_kvstore.wgsl:122-135) scales the output
-            const T *gate = (FUSED && a.has_gate && row < a.T)
-                                ? reinterpret_cast<const T *>(a.q_src) + (((size_t)b * a.T + row) * a.nh + h) * a.qrow + kPD : nullptr;
+            const T *gate = (FUSED && a.has_gate && row < item.len)
+                                ? reinterpret_cast<const T *>(a.q_src) + (((size_t)item.tok0 + row) * a.nh + h) * a.qrow + kPD : nullptr;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t v[32];
@@ -682,7 +738,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                             v[i + k] = __float_as_uint(__uint_as_float(v[i + k]) * sigmoidf_ref(to_f32<T>(ge[k])));
                     }
                 }
-                if (row < a.T) {
+                if (row < item.len) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 w;
@@ -743,6 +799,7 @@ constexpr uint32_t kColS = 0, kColO = 128;      // TMEM columns: S0 [0,64) S1 [6
 
 struct Prefill256Args {
     void *out;
+    RaggedRef rg;
     StatusRef status;
     uint32_t wait_mbar;
     uint32_t B, T, nh, nkv, G, m_tiles;   // m_tiles = ceil(T / 128)
@@ -767,12 +824,22 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (gave_up(a.status)) return;
     const WaitCtx wc{abort_word, a.status, a.wait_mbar};
 
-    struct Item { uint32_t b, h, kvh, q0, nkv; };
-    const uint32_t bh_count = a.B * a.nh, total_items = a.m_tiles * bh_count;
+    struct Item { uint32_t b, h, kvh, q0, nkv, len, tok0, qrow, qseq; };   // fields as in the head_dim-128 kernel
+    const uint32_t bh_count = a.B * a.nh, total_items = a.rg.items ? a.rg.entries * a.nh : a.m_tiles * bh_count;
     auto get_item = [&](uint32_t w) {   // heaviest (latest rows) first
         Item it;
-        const uint32_t m = a.m_tiles - 1 - w / bh_count, bh = w % bh_count;
-        it.b = bh / a.nh; it.h = bh % a.nh; it.kvh = it.h / a.G; it.q0 = m * kM;
+        uint32_t m;
+        if (a.rg.items) {
+            const uint4 e = __ldg(a.rg.items + w / a.nh);
+            it.b = e.x; m = e.y; it.len = e.z; it.tok0 = e.w; it.h = w % a.nh;
+            it.q0 = m * kM; it.qrow = it.tok0 + it.q0; it.qseq = 0;
+        } else {
+            const uint32_t bh = w % bh_count;
+            m = a.m_tiles - 1 - w / bh_count;
+            it.b = bh / a.nh; it.h = bh % a.nh; it.len = a.T; it.tok0 = it.b * a.T;
+            it.q0 = m * kM; it.qrow = it.q0; it.qseq = it.b;
+        }
+        it.kvh = it.h / a.G;
         it.nkv = 2 * m + 2;             // kv tiles 0 .. (q0 + 127) / 64; rows past T read as zeros and are masked
         return it;
     };
@@ -811,17 +878,20 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 ++qi;
                 mbar_expect_tx(bar(B_QFULL), kQBytes);
                 for (int c = 0; c < 4; ++c)
-                    tma_load_4d(smem_base + c * kQSlab, &map_q, bar(B_QFULL), 64 * c, (int)it.h, (int)it.q0, (int)it.b);
+                    tma_load_4d(smem_base + c * kQSlab, &map_q, bar(B_QFULL), 64 * c, (int)it.h, (int)it.qrow, (int)it.qseq);
+                const CUtensorMap *mk = &map_k, *mv = &map_v;
+                if (a.rg.kv_maps) {
+                    mk = a.rg.kv_maps + 2 * it.b; mv = mk + 1;
+                    tensormap_acquire(mk); tensormap_acquire(mv);
+                }
                 for (uint32_t j = 0; j < it.nkv && ok; ++j) {
                     const uint32_t gi = gk + j, s = gi % kStages, ph = (gi / kStages) & 1;
                     if (gi >= (uint32_t)kStages) ok = mbar_wait(bar(B_KVEMPTY + s), ph ^ 1, wc, 1);
                     if (!ok) break;
                     mbar_expect_tx(bar(B_KVFULL + s), 2 * kKvTile);
                     const uint32_t kd = smem_base + kSmemK + s * kKvTile, vd = smem_base + kSmemV + s * kKvTile;
-                    for (int c = 0; c < 4; ++c) {
-                        tma_load_4d(kd + c * kKvSlab, &map_k, bar(B_KVFULL + s), 64 * c, (int)it.kvh, (int)(j * kN), (int)it.b);
-                        tma_load_4d(vd + c * kKvSlab, &map_v, bar(B_KVFULL + s), 64 * c, (int)it.kvh, (int)(j * kN), (int)it.b);
-                    }
+                    tma_load_kv_tile<kN, 4>(kd, kKvSlab, mk, bar(B_KVFULL + s), a.rg, it.b, it.kvh, j * kN, it.len, a.rg.kv_maps != nullptr);
+                    tma_load_kv_tile<kN, 4>(vd, kKvSlab, mv, bar(B_KVFULL + s), a.rg, it.b, it.kvh, j * kN, it.len, a.rg.kv_maps != nullptr);
                 }
                 gk += it.nkv;
             }
@@ -976,15 +1046,15 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             if (ok) {
                 tc_fence_after();
                 const float inv = 1.0f / l_sum;
-                T *dst = reinterpret_cast<T *>(a.out) + (((size_t)item.b * a.T + row) * a.nh + item.h) * kD;
-                const T *gate = (a.gate_src && row < a.T)
-                                    ? reinterpret_cast<const T *>(a.gate_src) + (((size_t)item.b * a.T + row) * a.nh + item.h) * a.gate_row + kD : nullptr;
+                T *dst = reinterpret_cast<T *>(a.out) + (((size_t)item.tok0 + row) * a.nh + item.h) * kD;
+                const T *gate = (a.gate_src && row < item.len)
+                                    ? reinterpret_cast<const T *>(a.gate_src) + (((size_t)item.tok0 + row) * a.nh + item.h) * a.gate_row + kD : nullptr;
 #pragma unroll
                 for (int c = 0; c < kD / 32; ++c) {
                     uint32_t v[32];
                     tmem_ld32(t_o + c * 32, v);
                     tmem_wait_ld();
-                    if (row < a.T) {
+                    if (row < item.len) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
                             float f[8];
@@ -1044,6 +1114,7 @@ static EncodeTiledFn encode_tiled_fn() {
 
 static bool make_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
                         uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t box_rows = 128) {
+    if (d3 == 1 && s3 >= (1ull << 40)) s3 = 1ull << 39;   // the stride of a dimension of extent 1 is never used, but must encode
     cuuint64_t dims[4] = {d0, d1, d2, d3};
     cuuint64_t strides[3] = {s1, s2, s3};  // bytes, dims 1..3
     cuuint32_t box[4] = {64, 1, box_rows, 1};   // 64 elements (128 B, the swizzle span) x box_rows rows
@@ -1055,8 +1126,158 @@ static bool make_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *ba
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// ---- listed (ragged) batches: host tables --------------------------------------------------
+// Workspace of a listed batch: [row-block list][first packed token of every sequence][K and V map of every sequence]
+// [what the step from the projections needs].  Every part starts on a 128-byte boundary (tensor maps need 64).
+struct RaggedLayout {
+    size_t items_off, tok_off, maps_off, extra_off, total;
+    uint32_t entries, total_tokens, max_len;
+};
+static size_t up128(size_t v) { return (v + 127) & ~(size_t)127; }
+static RaggedLayout ragged_layout(const shady_prefill_params *p, const uint32_t *lens, bool with_append) {
+    RaggedLayout L{};
+    const uint32_t block_rows = p->head_dim == 256 ? 128u : 256u;
+    unsigned long long toks = 0, entries = 0;
+    for (uint32_t s = 0; s < p->num_seqs; ++s) {
+        toks += lens[s];
+        entries += (lens[s] + block_rows - 1) / block_rows;
+        if (lens[s] > L.max_len) L.max_len = lens[s];
+    }
+    L.entries = (uint32_t)(entries > 0xffffffffull ? 0xffffffffull : entries);
+    L.total_tokens = (uint32_t)(toks > 0xffffffffull ? 0xffffffffull : toks);
+    L.items_off = 0;
+    L.tok_off = up128(L.items_off + (size_t)L.entries * sizeof(uint4));
+    L.maps_off = up128(L.tok_off + ((size_t)p->num_seqs + 1) * sizeof(uint32_t));
+    L.extra_off = up128(L.maps_off + (size_t)p->num_seqs * 2 * sizeof(CUtensorMap));
+    size_t extra = 0;
+    if (with_append)
+        extra = p->head_dim == 256 ? (size_t)L.total_tokens * p->num_q_heads * 256 * 2 : (size_t)L.max_len * 64 * sizeof(float2);
+    L.total = up128(L.extra_off + extra);
+    return L;
+}
+size_t prefill_ragged_workspace_bytes(const shady_prefill_params *p, const uint32_t *h_seq_lens, bool with_append) {
+    return ragged_layout(p, h_seq_lens, with_append).total;
+}
+
+// Small host tables travel through one page-locked staging buffer of the context; the event says when the last
+// copy out of it is done.
+static int stage_upload(shady_ctx *ctx, const void *src, size_t bytes, void *d_dst) {
+    if (ctx->stage_done) SHADY_CUDA_OK(ctx, cudaEventSynchronize(ctx->stage_done));
+    else SHADY_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->stage_done, cudaEventDisableTiming));
+    if (bytes > ctx->stage_bytes) {
+        if (ctx->stage) cudaFreeHost(ctx->stage);
+        ctx->stage = nullptr; ctx->stage_bytes = 0;
+        const size_t want = bytes * 2 > (64u << 10) ? bytes * 2 : (64u << 10);
+        SHADY_CUDA_OK(ctx, cudaHostAlloc(&ctx->stage, want, cudaHostAllocDefault));
+        ctx->stage_bytes = want;
+    }
+    memcpy(ctx->stage, src, bytes);
+    SHADY_CUDA_OK(ctx, cudaMemcpyAsync(d_dst, ctx->stage, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    SHADY_CUDA_OK(ctx, cudaEventRecord(ctx->stage_done, ctx->stream));
+    return SHADY_OK;
+}
+
+// What a launcher needs to know about a listed batch once its tables are on their way to the device.
+struct RaggedSetup {
+    RaggedRef rg;
+    RaggedLayout lay;
+    bool pool_maps;         // paged cache: map_k / map_v cover the page pools
+    CUtensorMap mk, mv;     // ... and are these
+    const uint32_t *d_tok_start;
+};
+
+// Checks the batch, lists its row blocks heaviest first, encodes the K/V maps and sends everything to the workspace.
+static int setup_ragged(shady_ctx *ctx, const std::string &w, const shady_prefill_params *p, const shady_prefill_batch *batch,
+                        const shady_kv_cache *cache, void *d_ws, size_t ws_bytes, bool with_append, RaggedSetup *out) {
+    SHADY_REQUIRE(ctx, p && batch && batch->h_seq_lens && cache, SHADY_ERR_BAD_ARG, w + ": null argument");
+    SHADY_REQUIRE(ctx, p->head_dim == 128 || p->head_dim == 256, SHADY_ERR_UNSUPPORTED, w + ": head_dim must be 128 or 256");
+    SHADY_REQUIRE(ctx, p->dtype == SHADY_BF16 || p->dtype == SHADY_F16, SHADY_ERR_UNSUPPORTED, w + ": dtype must be bf16 or f16");
+    SHADY_REQUIRE(ctx, cache->dtype == p->dtype, SHADY_ERR_UNSUPPORTED, w + ": cache dtype must equal the Q dtype");
+    SHADY_REQUIRE(ctx, p->num_seqs && p->num_kv_heads && p->num_q_heads && p->num_q_heads % p->num_kv_heads == 0, SHADY_ERR_BAD_ARG,
+                  w + ": bad shape");
+    const uint32_t S = p->num_seqs, hd = p->head_dim, nkv = p->num_kv_heads;
+    const uint32_t block_rows = hd == 256 ? 128u : 256u, kv_rows = hd == 256 ? 64u : 128u;
+    const uint32_t *lens = batch->h_seq_lens;
+    for (uint32_t s = 0; s < S; ++s)
+        SHADY_REQUIRE(ctx, lens[s] > 0, SHADY_ERR_BAD_ARG, w + ": sequence " + std::to_string(s) + " is empty");
+    const RaggedLayout L = ragged_layout(p, lens, with_append);
+    SHADY_REQUIRE(ctx, L.entries != 0xffffffffu && L.total_tokens < 0x7fffffffu && (unsigned long long)L.entries * p->num_q_heads <= 0x7fffffffull,
+                  SHADY_ERR_UNSUPPORTED, w + ": too many tokens for one launch");
+    SHADY_REQUIRE(ctx, d_ws && ((uintptr_t)d_ws % 128) == 0 && ws_bytes >= L.total, SHADY_ERR_WORKSPACE,
+                  w + ": workspace missing, not 128-byte aligned or smaller than shady_prefill_ragged_workspace_size says (" +
+                      std::to_string(L.total) + " bytes)");
+    const bool paged = cache->d_page_table != nullptr, ptrs = cache->d_k_ptrs != nullptr;
+    SHADY_REQUIRE(ctx, paged ? (cache->d_k_base && cache->d_v_base && cache->page_rows && cache->max_pages_per_seq)
+                             : ptrs ? (cache->d_v_ptrs && batch->h_k_ptrs && batch->h_v_ptrs) : (cache->d_k_base && cache->d_v_base),
+                  SHADY_ERR_BAD_ARG,
+                  w + ": the cache needs page pools + table, or pointer arrays with their host copies in the batch, or base pointers");
+    if (const int st = pending_timeout(ctx, w.c_str())) return st;
+
+    std::vector<unsigned char> host(L.extra_off, 0);
+    uint4 *items = reinterpret_cast<uint4 *>(host.data() + L.items_off);
+    uint32_t *tok = reinterpret_cast<uint32_t *>(host.data() + L.tok_off);
+    CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(host.data() + L.maps_off);
+    // row blocks, heaviest (latest rows: most K/V tiles) first; blocks of equal weight keep the sequences' order
+    uint32_t t0 = 0, max_blocks = 0;
+    for (uint32_t s = 0; s < S; ++s) {
+        tok[s] = t0; t0 += lens[s];
+        const uint32_t nb = (lens[s] + block_rows - 1) / block_rows;
+        if (nb > max_blocks) max_blocks = nb;
+    }
+    tok[S] = t0;
+    uint32_t e = 0;
+    for (uint32_t m = max_blocks; m-- > 0;)
+        for (uint32_t s = 0; s < S; ++s)
+            if ((uint64_t)m * block_rows < lens[s]) items[e++] = make_uint4(s, m, lens[s], tok[s]);
+
+    RaggedSetup rs{};
+    rs.lay = L;
+    rs.rg.items = reinterpret_cast<const uint4 *>((char *)d_ws + L.items_off);
+    rs.rg.entries = L.entries;
+    rs.d_tok_start = reinterpret_cast<const uint32_t *>((char *)d_ws + L.tok_off);
+    const CUtensorMapDataType dt = p->dtype == SHADY_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const uint64_t head_b = (uint64_t)hd * 2, row_b = (uint64_t)nkv * hd * 2;
+    if (paged) {
+        const uint32_t pr = cache->page_rows;
+        SHADY_REQUIRE(ctx, (pr % kv_rows) == 0 || (pr < kv_rows && (kv_rows % pr) == 0 && (pr % 8) == 0), SHADY_ERR_UNSUPPORTED,
+                      w + ": page_rows must be a multiple of " + std::to_string(kv_rows) + " or one of 8, 16, 32, 64 below it");
+        SHADY_REQUIRE(ctx, (((uintptr_t)cache->d_k_base | (uintptr_t)cache->d_v_base) % 16) == 0, SHADY_ERR_BAD_ARG,
+                      w + ": page pools must be 16-byte aligned");
+        for (uint32_t s = 0; s < S; ++s)
+            SHADY_REQUIRE(ctx, (lens[s] + pr - 1) / pr <= cache->max_pages_per_seq, SHADY_ERR_BAD_ARG,
+                          w + ": sequence " + std::to_string(s) + " needs more pages than max_pages_per_seq");
+        // the pool's size is not part of the cache description: the map's page extent is a bound the table's entries
+        // stay below, and the first page number past it is what a box that starts beyond the sequence asks for
+        const uint32_t pages_extent = 1u << 24;
+        rs.rg.page_table = cache->d_page_table; rs.rg.max_pages = cache->max_pages_per_seq; rs.rg.page_rows = pr;
+        rs.rg.box_rows = pr < kv_rows ? pr : kv_rows; rs.rg.oob_page = pages_extent;
+        rs.pool_maps = true;
+        const bool ok = make_map_4d(&rs.mk, dt, cache->d_k_base, hd, nkv, pr, pages_extent, head_b, row_b, row_b * pr, rs.rg.box_rows) &&
+                        make_map_4d(&rs.mv, dt, cache->d_v_base, hd, nkv, pr, pages_extent, head_b, row_b, row_b * pr, rs.rg.box_rows);
+        SHADY_REQUIRE(ctx, ok, SHADY_ERR_CUDA, w + ": cuTensorMapEncodeTiled failed (page pools)");
+    } else {
+        SHADY_REQUIRE(ctx, ptrs || ((cache->seq_stride * 2) % 16 == 0 && (S == 1 || cache->seq_stride >= (uint64_t)L.max_len * nkv * hd)),
+                      SHADY_ERR_BAD_ARG, w + ": seq_stride smaller than the longest sequence or not a multiple of 16 bytes");
+        for (uint32_t s = 0; s < S; ++s) {
+            const char *kb = ptrs ? (const char *)batch->h_k_ptrs[s] : (const char *)cache->d_k_base + (size_t)s * cache->seq_stride * 2;
+            const char *vb = ptrs ? (const char *)batch->h_v_ptrs[s] : (const char *)cache->d_v_base + (size_t)s * cache->seq_stride * 2;
+            SHADY_REQUIRE(ctx, kb && vb && (((uintptr_t)kb | (uintptr_t)vb) % 16) == 0, SHADY_ERR_BAD_ARG,
+                          w + ": cache of sequence " + std::to_string(s) + " is null or not 16-byte aligned");
+            // extent = the sequence's own rows: what lies past them reads as zero whatever the memory holds
+            const bool ok = make_map_4d(&maps[2 * s], dt, kb, hd, nkv, lens[s], 1, head_b, row_b, row_b * lens[s], kv_rows) &&
+                            make_map_4d(&maps[2 * s + 1], dt, vb, hd, nkv, lens[s], 1, head_b, row_b, row_b * lens[s], kv_rows);
+            SHADY_REQUIRE(ctx, ok, SHADY_ERR_CUDA, w + ": cuTensorMapEncodeTiled failed (sequence " + std::to_string(s) + ")");
+        }
+        rs.rg.kv_maps = reinterpret_cast<const CUtensorMap *>((char *)d_ws + L.maps_off);
+    }
+    if (const int st = stage_upload(ctx, host.data(), host.size(), d_ws)) return st;
+    *out = rs;
+    return SHADY_OK;
+}
+
 // What the two entry points share: argument checks, tensor maps, the launch.  q_base/qrow describe where Q tiles
 // are fetched from: [B][T][nh][qrow] elements with the Q half in the first 128 of every head's qrow elements.
+// `rs`: a listed batch (set up by setup_ragged): Q and the output are packed token-major.
 struct FusedQ {
     const float2 *cs_table;
     const uint16_t *norm_w;
@@ -1064,39 +1285,48 @@ struct FusedQ {
     float eps;
 };
 static int launch_prefill_impl(shady_ctx *ctx, const char *who, const shady_prefill_params *p, const void *d_q, uint32_t qrow,
-                               const shady_kv_cache *cache, void *d_out, const FusedQ *fq) {
+                               const shady_kv_cache *cache, void *d_out, const FusedQ *fq, const RaggedSetup *rs = nullptr) {
     const std::string w(who);
     SHADY_REQUIRE(ctx, p && d_q && cache && d_out, SHADY_ERR_BAD_ARG, w + ": null argument");
     SHADY_REQUIRE(ctx, p->head_dim == 128, SHADY_ERR_UNSUPPORTED, w + ": head_dim must be 128 or 256");
     SHADY_REQUIRE(ctx, p->dtype == SHADY_BF16 || p->dtype == SHADY_F16, SHADY_ERR_UNSUPPORTED, w + ": dtype must be bf16 or f16");
     SHADY_REQUIRE(ctx, cache->dtype == p->dtype, SHADY_ERR_UNSUPPORTED, w + ": cache dtype must equal the Q dtype");
-    SHADY_REQUIRE(ctx, p->num_seqs && p->seq_len && p->num_kv_heads && p->num_q_heads % p->num_kv_heads == 0, SHADY_ERR_BAD_ARG,
+    SHADY_REQUIRE(ctx, p->num_seqs && (rs || p->seq_len) && p->num_kv_heads && p->num_q_heads % p->num_kv_heads == 0, SHADY_ERR_BAD_ARG,
                   w + ": bad shape");
-    SHADY_REQUIRE(ctx, cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs && !cache->d_page_table, SHADY_ERR_UNSUPPORTED,
-                  w + ": needs base + seq_stride cache addressing (TMA tensor maps), not pointer arrays or pages");
-    SHADY_REQUIRE(ctx, p->num_seqs == 1 || cache->seq_stride >= (uint64_t)p->seq_len * p->num_kv_heads * 128, SHADY_ERR_BAD_ARG,
+    SHADY_REQUIRE(ctx, rs || (cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs && !cache->d_page_table), SHADY_ERR_UNSUPPORTED,
+                  w + ": needs base + seq_stride cache addressing; pointer arrays and pages go through shady_attn_prefill_ragged");
+    SHADY_REQUIRE(ctx, rs || p->num_seqs == 1 || cache->seq_stride >= (uint64_t)p->seq_len * p->num_kv_heads * 128, SHADY_ERR_BAD_ARG,
                   w + ": seq_stride smaller than one sequence");
-    SHADY_REQUIRE(ctx, ((uintptr_t)d_q | (uintptr_t)cache->d_k_base | (uintptr_t)cache->d_v_base | (uintptr_t)d_out) % 16 == 0 &&
-                           (cache->seq_stride * 2) % 16 == 0,
+    SHADY_REQUIRE(ctx, ((uintptr_t)d_q | (uintptr_t)d_out) % 16 == 0 &&
+                           (rs || (((uintptr_t)cache->d_k_base | (uintptr_t)cache->d_v_base) % 16 == 0 && (cache->seq_stride * 2) % 16 == 0)),
                   SHADY_ERR_BAD_ARG, w + ": buffers must be 16-byte aligned");
     if (const int st = pending_timeout(ctx, who)) return st;
     const uint32_t B = p->num_seqs, T = p->seq_len, nh = p->num_q_heads, nkv = p->num_kv_heads;
     const CUtensorMapDataType dt = p->dtype == SHADY_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap mq, mk, mv;
-    const uint64_t seq_stride_b = (B == 1 ? (uint64_t)T * nkv * 128 : cache->seq_stride) * 2;
+    bool maps_ok;
     // the Q map sees 128 of the qrow elements of every head: the gate half (if any) is skipped by the head stride
-    const bool maps_ok = make_map_4d(&mq, dt, d_q, 128, nh, T, B, (uint64_t)qrow * 2, (uint64_t)nh * qrow * 2, (uint64_t)T * nh * qrow * 2) &&
-                         make_map_4d(&mk, dt, cache->d_k_base, 128, nkv, T, B, 128 * 2, (uint64_t)nkv * 128 * 2, seq_stride_b) &&
-                         make_map_4d(&mv, dt, cache->d_v_base, 128, nkv, T, B, 128 * 2, (uint64_t)nkv * 128 * 2, seq_stride_b);
+    if (rs) {
+        const uint64_t toks = rs->lay.total_tokens;
+        maps_ok = make_map_4d(&mq, dt, d_q, 128, nh, toks, 1, (uint64_t)qrow * 2, (uint64_t)nh * qrow * 2, toks * nh * qrow * 2);
+        if (rs->pool_maps) { mk = rs->mk; mv = rs->mv; }
+        else { mk = mq; mv = mq; }   // unused: every sequence brings its own pair
+    } else {
+        const uint64_t seq_stride_b = (B == 1 ? (uint64_t)T * nkv * 128 : cache->seq_stride) * 2;
+        maps_ok = make_map_4d(&mq, dt, d_q, 128, nh, T, B, (uint64_t)qrow * 2, (uint64_t)nh * qrow * 2, (uint64_t)T * nh * qrow * 2) &&
+                  make_map_4d(&mk, dt, cache->d_k_base, 128, nkv, T, B, 128 * 2, (uint64_t)nkv * 128 * 2, seq_stride_b) &&
+                  make_map_4d(&mv, dt, cache->d_v_base, 128, nkv, T, B, 128 * 2, (uint64_t)nkv * 128 * 2, seq_stride_b);
+    }
     SHADY_REQUIRE(ctx, maps_ok, SHADY_ERR_CUDA, w + ": cuTensorMapEncodeTiled failed");
     PrefillArgs a{};
     a.out = d_out; a.status = status_ref(ctx); a.wait_mbar = ctx->wait_mbar;
     a.B = B; a.T = T; a.nh = nh; a.nkv = nkv; a.G = nh / nkv;
     a.m_tiles = (T + 255) / 256;
+    if (rs) a.rg = rs->rg;
     a.scale_log2 = (1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
     a.q_src = d_q; a.qrow = qrow;
     if (fq) { a.cs_table = fq->cs_table; a.norm_w = fq->norm_w; a.has_gate = fq->has_gate; a.eps = fq->eps; }
-    const unsigned long long total_items = (unsigned long long)a.m_tiles * B * nh;
+    const unsigned long long total_items = rs ? (unsigned long long)rs->rg.entries * nh : (unsigned long long)a.m_tiles * B * nh;
     SHADY_REQUIRE(ctx, total_items <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, w + ": too many tiles for one launch");
     const unsigned blocks = (unsigned)(total_items < (unsigned long long)ctx->num_sms ? total_items : (unsigned long long)ctx->num_sms);   // persistent: one CTA per SM
     static thread_local int configured_dev = -1;
@@ -1124,36 +1354,46 @@ static int launch_prefill_impl(shady_ctx *ctx, const char *who, const shady_pref
 // head_dim 256: Q [B][T][nh][256] already normed and rotated; gate_src (optional) the projection rows whose second
 // half is the gate
 static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefill_params *p, const void *d_q,
-                             const shady_kv_cache *cache, void *d_out, const void *gate_src, uint32_t gate_row) {
+                             const shady_kv_cache *cache, void *d_out, const void *gate_src, uint32_t gate_row,
+                             const RaggedSetup *rs = nullptr) {
     const std::string w(who);
     SHADY_REQUIRE(ctx, p && d_q && cache && d_out, SHADY_ERR_BAD_ARG, w + ": null argument");
     SHADY_REQUIRE(ctx, p->dtype == SHADY_BF16 || p->dtype == SHADY_F16, SHADY_ERR_UNSUPPORTED, w + ": dtype must be bf16 or f16");
     SHADY_REQUIRE(ctx, cache->dtype == p->dtype, SHADY_ERR_UNSUPPORTED, w + ": cache dtype must equal the Q dtype");
-    SHADY_REQUIRE(ctx, p->num_seqs && p->seq_len && p->num_kv_heads && p->num_q_heads % p->num_kv_heads == 0, SHADY_ERR_BAD_ARG,
+    SHADY_REQUIRE(ctx, p->num_seqs && (rs || p->seq_len) && p->num_kv_heads && p->num_q_heads % p->num_kv_heads == 0, SHADY_ERR_BAD_ARG,
                   w + ": bad shape");
-    SHADY_REQUIRE(ctx, cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs && !cache->d_page_table, SHADY_ERR_UNSUPPORTED,
-                  w + ": needs base + seq_stride cache addressing (TMA tensor maps), not pointer arrays or pages");
-    SHADY_REQUIRE(ctx, p->num_seqs == 1 || cache->seq_stride >= (uint64_t)p->seq_len * p->num_kv_heads * 256, SHADY_ERR_BAD_ARG,
+    SHADY_REQUIRE(ctx, rs || (cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs && !cache->d_page_table), SHADY_ERR_UNSUPPORTED,
+                  w + ": needs base + seq_stride cache addressing; pointer arrays and pages go through shady_attn_prefill_ragged");
+    SHADY_REQUIRE(ctx, rs || p->num_seqs == 1 || cache->seq_stride >= (uint64_t)p->seq_len * p->num_kv_heads * 256, SHADY_ERR_BAD_ARG,
                   w + ": seq_stride smaller than one sequence");
-    SHADY_REQUIRE(ctx, ((uintptr_t)d_q | (uintptr_t)cache->d_k_base | (uintptr_t)cache->d_v_base | (uintptr_t)d_out | (uintptr_t)gate_src) % 16 == 0 &&
-                           (cache->seq_stride * 2) % 16 == 0,
+    SHADY_REQUIRE(ctx, ((uintptr_t)d_q | (uintptr_t)d_out | (uintptr_t)gate_src) % 16 == 0 &&
+                           (rs || (((uintptr_t)cache->d_k_base | (uintptr_t)cache->d_v_base) % 16 == 0 && (cache->seq_stride * 2) % 16 == 0)),
                   SHADY_ERR_BAD_ARG, w + ": buffers must be 16-byte aligned");
     if (const int st = pending_timeout(ctx, who)) return st;
     const uint32_t B = p->num_seqs, T = p->seq_len, nh = p->num_q_heads, nkv = p->num_kv_heads;
     const CUtensorMapDataType dt = p->dtype == SHADY_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap mq, mk, mv;
-    const uint64_t seq_stride_b = (B == 1 ? (uint64_t)T * nkv * 256 : cache->seq_stride) * 2;
-    const bool maps_ok = make_map_4d(&mq, dt, d_q, 256, nh, T, B, 256 * 2, (uint64_t)nh * 256 * 2, (uint64_t)T * nh * 256 * 2, 128) &&
-                         make_map_4d(&mk, dt, cache->d_k_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64) &&
-                         make_map_4d(&mv, dt, cache->d_v_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64);
+    bool maps_ok;
+    if (rs) {
+        const uint64_t toks = rs->lay.total_tokens;
+        maps_ok = make_map_4d(&mq, dt, d_q, 256, nh, toks, 1, 256 * 2, (uint64_t)nh * 256 * 2, toks * nh * 256 * 2, 128);
+        if (rs->pool_maps) { mk = rs->mk; mv = rs->mv; }
+        else { mk = mq; mv = mq; }
+    } else {
+        const uint64_t seq_stride_b = (B == 1 ? (uint64_t)T * nkv * 256 : cache->seq_stride) * 2;
+        maps_ok = make_map_4d(&mq, dt, d_q, 256, nh, T, B, 256 * 2, (uint64_t)nh * 256 * 2, (uint64_t)T * nh * 256 * 2, 128) &&
+                  make_map_4d(&mk, dt, cache->d_k_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64) &&
+                  make_map_4d(&mv, dt, cache->d_v_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64);
+    }
     SHADY_REQUIRE(ctx, maps_ok, SHADY_ERR_CUDA, w + ": cuTensorMapEncodeTiled failed");
     Prefill256Args a{};
     a.out = d_out; a.status = status_ref(ctx); a.wait_mbar = ctx->wait_mbar;
     a.B = B; a.T = T; a.nh = nh; a.nkv = nkv; a.G = nh / nkv;
     a.m_tiles = (T + 127) / 128;
+    if (rs) a.rg = rs->rg;
     a.scale_log2 = (1.0f / sqrtf(256.0f)) * 1.4426950408889634f;
     a.gate_src = gate_src; a.gate_row = gate_row;
-    const unsigned long long total_items = (unsigned long long)a.m_tiles * B * nh;
+    const unsigned long long total_items = rs ? (unsigned long long)rs->rg.entries * nh : (unsigned long long)a.m_tiles * B * nh;
     SHADY_REQUIRE(ctx, total_items <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, w + ": too many tiles for one launch");
     const unsigned blocks = (unsigned)(total_items < (unsigned long long)ctx->num_sms ? total_items : (unsigned long long)ctx->num_sms);
     static thread_local int configured_dev = -1;
@@ -1175,17 +1415,29 @@ int launch_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_
 }
 
 int launch_append_ex(shady_ctx *, const shady_append_params *, const void *, void *, const void *, void *, float *,
-                     const shady_kv_cache *, const uint16_t *, const uint32_t *, const uint32_t *, const uint32_t *, bool);
+                     const shady_kv_cache *, const uint16_t *, const uint32_t *, const uint32_t *, const uint32_t *, bool,
+                     const AppendRagged *);
 
 // K/V half of the append (norm + RoPE of K, cache rows of K and V) plus the cos/sin table of positions [0, T)
 // (append.cu); Q is left to the attention kernel.
 int launch_append_kv_table(shady_ctx *ctx, const shady_append_params *ap, const void *d_k_proj, const void *d_v_proj,
-                           const shady_kv_cache *cache, const uint16_t *d_qk_norm_bf16, float2 *d_cs_table);
+                           const shady_kv_cache *cache, const uint16_t *d_qk_norm_bf16, float2 *d_cs_table, const AppendRagged *rg);
 
 // head_dim 128: the cos/sin table of the T positions; head_dim 256: the normed and rotated Q of the whole batch
 size_t prefill_workspace_bytes(const shady_prefill_params *p) {
     if (p->head_dim == 256) return (size_t)p->num_seqs * p->seq_len * p->num_q_heads * 256 * 2;
     return (size_t)p->seq_len * 64 * sizeof(float2);
+}
+
+static int check_prefill_append(shady_ctx *ctx, const shady_append_params *ap, const shady_prefill_params *p, bool listed) {
+    SHADY_REQUIRE(ctx, ap->num_heads == p->num_q_heads && ap->num_kv_heads == p->num_kv_heads && ap->head_dim == p->head_dim &&
+                           ap->num_seqs == p->num_seqs && (listed || ap->tokens_per_seq == p->seq_len),
+                  SHADY_ERR_BAD_ARG, "attn_prefill_append: append and prefill parameters disagree");
+    SHADY_REQUIRE(ctx, ap->in_dtype == p->dtype, SHADY_ERR_UNSUPPORTED, "attn_prefill_append: the projections must have the cache dtype (bf16 or f16)");
+    SHADY_REQUIRE(ctx, ap->interleaved && ap->rotary_dim <= p->head_dim && (ap->rotary_dim % 2) == 0 &&
+                           ap->s1_limit == ap->rotary_dim / 2 && ap->s2_limit == ap->rotary_dim / 2,
+                  SHADY_ERR_UNSUPPORTED, "attn_prefill_append: interleaved RoPE with one position per token only");
+    return SHADY_OK;
 }
 
 // The whole prefill step from the projections: one pass writes K (normed, rotated) and V into rows [0, T) of every
@@ -1195,13 +1447,7 @@ int launch_prefill_append(shady_ctx *ctx, const shady_append_params *ap, const s
                           const void *d_k_proj, const void *d_v_proj, const uint16_t *d_qk_norm_bf16, const shady_kv_cache *cache,
                           void *d_out, void *d_ws, size_t ws_bytes) {
     SHADY_REQUIRE(ctx, ap && p && d_q_proj_full && d_k_proj && d_v_proj && cache && d_out, SHADY_ERR_BAD_ARG, "attn_prefill_append: null argument");
-    SHADY_REQUIRE(ctx, ap->num_heads == p->num_q_heads && ap->num_kv_heads == p->num_kv_heads && ap->head_dim == p->head_dim &&
-                           ap->num_seqs == p->num_seqs && ap->tokens_per_seq == p->seq_len,
-                  SHADY_ERR_BAD_ARG, "attn_prefill_append: append and prefill parameters disagree");
-    SHADY_REQUIRE(ctx, ap->in_dtype == p->dtype, SHADY_ERR_UNSUPPORTED, "attn_prefill_append: the projections must have the cache dtype (bf16 or f16)");
-    SHADY_REQUIRE(ctx, ap->interleaved && ap->rotary_dim <= p->head_dim && (ap->rotary_dim % 2) == 0 &&
-                           ap->s1_limit == ap->rotary_dim / 2 && ap->s2_limit == ap->rotary_dim / 2,
-                  SHADY_ERR_UNSUPPORTED, "attn_prefill_append: interleaved RoPE with one position per token only");
+    if (const int st = check_prefill_append(ctx, ap, p, false)) return st;
     SHADY_REQUIRE(ctx, d_ws && ws_bytes >= prefill_workspace_bytes(p) && ((uintptr_t)d_ws % 16) == 0, SHADY_ERR_WORKSPACE,
                   "attn_prefill_append: workspace missing, too small or not 16-byte aligned");
     if (p->head_dim == 256) {
@@ -1210,14 +1456,72 @@ int launch_prefill_append(shady_ctx *ctx, const shady_append_params *ap, const s
         shady_append_params ap2 = *ap;
         ap2.q_dtype = p->dtype; ap2.write_k_back = 0;
         if (const int st = launch_append_ex(ctx, &ap2, d_q_proj_full, const_cast<void *>(d_k_proj), d_v_proj, d_ws, nullptr, cache,
-                                            d_qk_norm_bf16, nullptr, nullptr, nullptr, true))
+                                            d_qk_norm_bf16, nullptr, nullptr, nullptr, true, nullptr))
             return st;
         return launch_prefill256(ctx, "attn_prefill_append", p, d_ws, cache, d_out, ap->has_gate ? d_q_proj_full : nullptr, 512);
     }
     float2 *table = reinterpret_cast<float2 *>(d_ws);
-    if (const int st = launch_append_kv_table(ctx, ap, d_k_proj, d_v_proj, cache, d_qk_norm_bf16, table)) return st;
+    if (const int st = launch_append_kv_table(ctx, ap, d_k_proj, d_v_proj, cache, d_qk_norm_bf16, table, nullptr)) return st;
     const FusedQ fq{table, d_qk_norm_bf16, ap->has_gate, ap->eps};
     return launch_prefill_impl(ctx, "attn_prefill_append", p, d_q_proj_full, ap->has_gate ? 256u : 128u, cache, d_out, &fq);
+}
+
+// ---- listed batches: prompts of different lengths, caches of any addressing ------------------------------------
+int launch_prefill_ragged(shady_ctx *ctx, const shady_prefill_params *p, const shady_prefill_batch *batch, const void *d_q,
+                          const shady_kv_cache *cache, void *d_out, void *d_ws, size_t ws_bytes) {
+    RaggedSetup rs;
+    if (const int st = setup_ragged(ctx, "attn_prefill_ragged", p, batch, cache, d_ws, ws_bytes, false, &rs)) return st;
+    if (p->head_dim == 256) return launch_prefill256(ctx, "attn_prefill_ragged", p, d_q, cache, d_out, nullptr, 0, &rs);
+    return launch_prefill_impl(ctx, "attn_prefill_ragged", p, d_q, 128, cache, d_out, nullptr, &rs);
+}
+
+// Paged caches: the rows between the end of a sequence and the end of the K/V box that holds its last row belong to
+// the sequence's last page and travel with the box; the step that has just written the rows before them clears them,
+// so that whatever an earlier owner of the page left there cannot reach the output (0 x NaN).
+__global__ void zero_page_tail_kernel(KvAddr kv, const uint32_t *tok_start, uint32_t box_rows, uint32_t row_bytes) {
+    const uint32_t s = blockIdx.x;
+    const uint32_t len = tok_start[s + 1] - tok_start[s];
+    const uint32_t end = (len + box_rows - 1) / box_rows * box_rows;
+    for (uint32_t row = len; row < end; ++row) {
+        uint4 *k = reinterpret_cast<uint4 *>(const_cast<char *>(kv_row_ptr(kv, false, s, row, row_bytes)));
+        uint4 *v = reinterpret_cast<uint4 *>(const_cast<char *>(kv_row_ptr(kv, true, s, row, row_bytes)));
+        for (uint32_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) k[i] = v[i] = make_uint4(0, 0, 0, 0);
+    }
+}
+
+int launch_prefill_append_ragged(shady_ctx *ctx, const shady_append_params *ap, const shady_prefill_params *p,
+                                 const shady_prefill_batch *batch, const void *d_q_proj_full, const void *d_k_proj, const void *d_v_proj,
+                                 const uint16_t *d_qk_norm_bf16, const shady_kv_cache *cache, void *d_out, void *d_ws, size_t ws_bytes) {
+    SHADY_REQUIRE(ctx, ap && p && d_q_proj_full && d_k_proj && d_v_proj && cache && d_out, SHADY_ERR_BAD_ARG, "attn_prefill_append_ragged: null argument");
+    if (const int st = check_prefill_append(ctx, ap, p, true)) return st;
+    RaggedSetup rs;
+    if (const int st = setup_ragged(ctx, "attn_prefill_append_ragged", p, batch, cache, d_ws, ws_bytes, true, &rs)) return st;
+    uint32_t longest = 0;
+    for (uint32_t s = 1; s < p->num_seqs; ++s)
+        if (batch->h_seq_lens[s] > batch->h_seq_lens[longest]) longest = s;
+    const AppendRagged ar{rs.d_tok_start, rs.lay.total_tokens, longest};
+    void *extra = (char *)d_ws + rs.lay.extra_off;
+    int st;
+    if (p->head_dim == 256) {
+        shady_append_params ap2 = *ap;
+        ap2.q_dtype = p->dtype; ap2.write_k_back = 0;
+        st = launch_append_ex(ctx, &ap2, d_q_proj_full, const_cast<void *>(d_k_proj), d_v_proj, extra, nullptr, cache, d_qk_norm_bf16,
+                              nullptr, nullptr, nullptr, true, &ar);
+    } else {
+        st = launch_append_kv_table(ctx, ap, d_k_proj, d_v_proj, cache, d_qk_norm_bf16, reinterpret_cast<float2 *>(extra), &ar);
+    }
+    if (st) return st;
+    if (rs.rg.page_table) {
+        KvAddr kv;
+        if (const int st2 = fill_kv_addr(ctx, cache, p->num_kv_heads, p->head_dim, "attn_prefill_append_ragged", &kv)) return st2;
+        zero_page_tail_kernel<<<p->num_seqs, 128, 0, ctx->stream>>>(kv, rs.d_tok_start, rs.rg.box_rows, p->num_kv_heads * p->head_dim * 2);
+        ctx->launches++;
+        SHADY_CUDA_OK(ctx, cudaGetLastError());
+    }
+    if (p->head_dim == 256)
+        return launch_prefill256(ctx, "attn_prefill_append_ragged", p, extra, cache, d_out, ap->has_gate ? d_q_proj_full : nullptr, 512, &rs);
+    const FusedQ fq{reinterpret_cast<const float2 *>(extra), d_qk_norm_bf16, ap->has_gate, ap->eps};
+    return launch_prefill_impl(ctx, "attn_prefill_append_ragged", p, d_q_proj_full, ap->has_gate ? 256u : 128u, cache, d_out, &fq, &rs);
 }
 
 }  // namespace shady

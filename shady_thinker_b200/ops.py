@@ -200,6 +200,58 @@ def attn_prefill_append(gpu: GpuContext, *, q_proj_full, k_proj, v_proj, cache: 
                                                 _addr(workspace), workspace_bytes))
 
 
+class _ListedBatch:
+    """Host arrays of a listed prefill batch, kept alive for the duration of the call."""
+
+    def __init__(self, seq_lens, k_ptrs=None, v_ptrs=None):
+        n = len(seq_lens)
+        self.lens = (C.c_uint32 * n)(*[int(v) for v in seq_lens])
+        self.k = (C.c_void_p * n)(*[int(v) for v in k_ptrs]) if k_ptrs is not None else None
+        self.v = (C.c_void_p * n)(*[int(v) for v in v_ptrs]) if v_ptrs is not None else None
+        self.c = _lib.PrefillBatch(C.cast(self.lens, C.c_void_p), C.cast(self.k, C.c_void_p) if self.k is not None else None,
+                                   C.cast(self.v, C.c_void_p) if self.v is not None else None)
+
+
+def prefill_ragged_workspace_size(*, seq_lens, head_dim: int, num_kv_heads: int, num_q_heads: int, dtype: int = BF16,
+                                  with_append: bool = False) -> int:
+    p = PrefillParams(head_dim, num_kv_heads, num_q_heads, len(seq_lens), 0, dtype)
+    lens = (C.c_uint32 * len(seq_lens))(*[int(v) for v in seq_lens])
+    n = C.c_size_t()
+    st = _lib.load().shady_prefill_ragged_workspace_size(C.byref(p), C.cast(lens, C.c_void_p), int(with_append), C.byref(n))
+    if st != _lib.OK:
+        raise _lib.ShadyError(st, "prefill_ragged_workspace_size")
+    return n.value
+
+
+def attn_prefill_ragged(gpu: GpuContext, *, q, cache: KvCacheView, out, seq_lens, workspace, workspace_bytes: int,
+                        head_dim: int, num_kv_heads: int, num_q_heads: int, dtype: int = BF16, k_ptrs=None,
+                        v_ptrs=None) -> None:
+    """Causal attention of prompts of different lengths; ``q`` and ``out`` packed ``[sum T_i][nh][hd]``.  ``k_ptrs`` /
+    ``v_ptrs``: the per-sequence cache addresses as host integers when ``cache`` is a pointer-array cache."""
+    p = PrefillParams(head_dim, num_kv_heads, num_q_heads, len(seq_lens), 0, dtype)
+    b = _ListedBatch(seq_lens, k_ptrs, v_ptrs)
+    c = cache.c_struct()
+    gpu._check(gpu._L.shady_attn_prefill_ragged(gpu.handle, C.byref(p), C.byref(b.c), _addr(q), C.byref(c), _addr(out),
+                                                _addr(workspace), workspace_bytes))
+
+
+def attn_prefill_append_ragged(gpu: GpuContext, *, q_proj_full, k_proj, v_proj, cache: KvCacheView, out, seq_lens,
+                               workspace, workspace_bytes: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                               rope_theta: float, rotary_dim: int, dtype: int = BF16, eps: float = 1e-6,
+                               qk_norm_bf16=None, has_gate: bool = False, k_ptrs=None, v_ptrs=None) -> None:
+    """The prefill step from the projections for prompts of different lengths (everything packed token-major)."""
+    S = len(seq_lens)
+    ap = AppendParams(num_heads, num_kv_heads, head_dim, eps, rope_theta, rotary_dim, rotary_dim // 2, rotary_dim // 2,
+                      1, S, 0, dtype, dtype, int(has_gate), 0, 0)
+    p = PrefillParams(head_dim, num_kv_heads, num_heads, S, 0, dtype)
+    b = _ListedBatch(seq_lens, k_ptrs, v_ptrs)
+    c = cache.c_struct()
+    gpu._check(gpu._L.shady_attn_prefill_append_ragged(gpu.handle, C.byref(ap), C.byref(p), C.byref(b.c),
+                                                       _addr(q_proj_full), _addr(k_proj), _addr(v_proj),
+                                                       _addr(qk_norm_bf16) or None, C.byref(c), _addr(out),
+                                                       _addr(workspace), workspace_bytes))
+
+
 @dataclass
 class GptqMatrix:
     """One symmetric INT4 weight in the reference's layout (src/weights.rs:252-257): ``qweight`` device u32
