@@ -34,8 +34,9 @@ N_SETS = 3            # rotating cache sets so no step finds its KV rows in L2
 # DRAM bytes (read + write, one launch) per algorithmic byte of the headline decode kernel, as ncu counted them on
 # this workload, and the commit whose kernel was captured; the ratio is a property of the kernel's access pattern,
 # so a launch timed here is credited with its own algorithmic bytes times this figure.
-TRAFFIC_PER_ALGO_BYTE = 1.011
-TRAFFIC_MEASURED_AT = "5c1021b (ncu --set full, decode16_kernel<half,128,4,6,1>, 528.8 MB DRAM for 523.3 MB algorithmic)"
+TRAFFIC_PER_ALGO_BYTE = {"fp16": 1.011, "fp8": 1.019, "fp8e5m2": 1.022}   # by cache format, from the captures under profiles/
+TRAFFIC_MEASURED_AT = ("38616fd (ncu --set full, one launch of decode16_kernel<half,128>: fp16 524.4 MB read + 4.4 MB written for 523.3 MB "
+                       "algorithmic; e4m3 262.5 + 4.2 and e5m2 262.6 + 4.7 for 261.6)")
 
 
 def draw_lengths(rank: int) -> np.ndarray:
@@ -395,12 +396,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": workload_config(world, args.shape, args.kv),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": (TRAFFIC_PER_ALGO_BYTE * step_bytes) if TRAFFIC_PER_ALGO_BYTE else None,
+                         "traffic": TRAFFIC_PER_ALGO_BYTE[args.kv] * step_bytes,
                          "peak_source": f"{peak_src} (copy bandwidth)",
                          "kernel": ("decode16_kernel<half,128> with the fused append and split merge (the whole step is this one launch)"
                                     if args.kv == "fp16" else
                                     "decode16_kernel<half,128,8-bit cache> (the step is the append launch plus this attend launch)"),
-                         "traffic_source": f"algorithmic bytes x {TRAFFIC_PER_ALGO_BYTE}, the DRAM-byte ratio ncu measured at {TRAFFIC_MEASURED_AT}",
+                         "traffic_source": f"algorithmic bytes x {TRAFFIC_PER_ALGO_BYTE[args.kv]}, the DRAM-byte ratio ncu measured at {TRAFFIC_MEASURED_AT}",
                          "algorithmic_bytes_per_launch": step_bytes, "avg_launch_ms": attend_ms,
                          "avg_launch_ms_single_bracketed": bracketed_ms,
                          "avg_launch_ms_long": {"launches": int(long_blocks * long_per), "median": float(np.median(long_ms)),

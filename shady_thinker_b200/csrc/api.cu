@@ -23,7 +23,7 @@ int pending_timeout(shady_ctx *ctx, const char *who) {
     return SHADY_OK;
 }
 
-// Text of a wait code: 1..12 = mbarriers of the prefill kernel, 90 = the decode grid barrier, 100 + r = the NVLink
+// Text of a wait code: 1..13 = mbarriers of the prefill kernels, 90 = the decode grid barrier, 100 + r = the NVLink
 // flag of rank r.
 std::string timeout_message(int code) {
     if (code >= 100)

@@ -786,14 +786,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // barrier of its own, which the softmax threads pass before they touch O.
 // =====================================================================================================
 namespace p256 {
-constexpr int kM = 128, kN = 64, kD = 256, kStages = 2;
+constexpr int kM = 128, kN = 64, kD = 256, kKStages = 3, kVStages = 2;
 constexpr uint32_t kQSlab = 128 * 128;          // [128 rows][64 elements] 16-bit
 constexpr uint32_t kQBytes = 4 * kQSlab;        // 64 KB
 constexpr uint32_t kKvSlab = 64 * 128;          // [64 rows][64 elements]
 constexpr uint32_t kKvTile = 4 * kKvSlab;       // 32 KB
-constexpr uint32_t kSmemK = kQBytes, kSmemV = kSmemK + kStages * kKvTile, kSmemBar = kSmemV + kStages * kKvTile;
+constexpr uint32_t kSmemK = kQBytes, kSmemV = kSmemK + kKStages * kKvTile, kSmemBar = kSmemV + kVStages * kKvTile;
 constexpr uint32_t kSmem = kSmemBar + 256 + 1024;
-enum { B_QFULL = 0, B_QEMPTY = 1, B_KVFULL = 2, B_KVEMPTY = 4, B_SFULL = 6, B_PFULL = 8, B_PVDONE = 10, B_OFULL = 11, B_COUNT = 12 };
+static_assert(kSmem <= 232448, "Q + three K tiles + two V tiles must fit in 227 KB");
+enum { B_QFULL = 0, B_QEMPTY = 1, B_KFULL = 2, B_KEMPTY = 5, B_VFULL = 8, B_VEMPTY = 10, B_SFULL = 12, B_PFULL = 14, B_PVDONE = 16,
+       B_OFULL = 17, B_COUNT = 18 };
 constexpr uint32_t kColS = 0, kColO = 128;      // TMEM columns: S0 [0,64) S1 [64,128) O [128,384); P_b = first 32 columns of S_b
 }  // namespace p256
 
@@ -850,7 +852,8 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
     if (warp == 4 && lane == 0) {
         mbar_init(bar(B_QFULL), 1); mbar_init(bar(B_QEMPTY), 1); mbar_init(bar(B_PVDONE), 1); mbar_init(bar(B_OFULL), 1);
-        for (int s = 0; s < kStages; ++s) { mbar_init(bar(B_KVFULL + s), 1); mbar_init(bar(B_KVEMPTY + s), 1); }
+        for (int s = 0; s < kKStages; ++s) { mbar_init(bar(B_KFULL + s), 1); mbar_init(bar(B_KEMPTY + s), 1); }
+        for (int s = 0; s < kVStages; ++s) { mbar_init(bar(B_VFULL + s), 1); mbar_init(bar(B_VEMPTY + s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar(B_SFULL + b), 1); mbar_init(bar(B_PFULL + b), 128); }
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -866,34 +869,60 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
     if (warp == 4) {
         // =============================== TMA producer ===============================
+        // K and V travel separately: a K tile's slot is free again as soon as its S is computed, a V tile's only
+        // after its PV, so K (three slots) runs one tile ahead of V (two slots) and the next S never waits for a PV.
+        // Two cursors walk the item list, one requesting K tiles (and each item's Q ahead of its first K), one V tiles.
         if (lane == 0) {
             bool ok = true;
-            uint32_t gk = 0, qi = 0;
-            for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
-                const uint32_t w = item_of_round(rnd);
-                if (w >= total_items) continue;
-                const Item it = get_item(w);
-                if (qi > 0) ok = mbar_wait(bar(B_QEMPTY), (qi - 1) & 1, wc, 12);
-                if (!ok) break;
-                ++qi;
-                mbar_expect_tx(bar(B_QFULL), kQBytes);
-                for (int c = 0; c < 4; ++c)
-                    tma_load_4d(smem_base + c * kQSlab, &map_q, bar(B_QFULL), 64 * c, (int)it.h, (int)it.qrow, (int)it.qseq);
-                const CUtensorMap *mk = &map_k, *mv = &map_v;
-                if (a.rg.kv_maps) {
-                    mk = a.rg.kv_maps + 2 * it.b; mv = mk + 1;
-                    tensormap_acquire(mk); tensormap_acquire(mv);
+            struct Cursor { uint32_t rnd, j, g; bool have, done; Item it; const CUtensorMap *map; };
+            auto advance = [&](Cursor &c) {   // to the next tile of the CTA's list
+                if (c.have && ++c.j < c.it.nkv) return;
+                c.have = false;
+                for (; c.rnd * gridDim.x < total_items; ++c.rnd) {
+                    const uint32_t w = item_of_round(c.rnd);
+                    if (w >= total_items) continue;
+                    c.it = get_item(w); c.j = 0; c.have = true; ++c.rnd;
+                    return;
                 }
-                for (uint32_t j = 0; j < it.nkv && ok; ++j) {
-                    const uint32_t gi = gk + j, s = gi % kStages, ph = (gi / kStages) & 1;
-                    if (gi >= (uint32_t)kStages) ok = mbar_wait(bar(B_KVEMPTY + s), ph ^ 1, wc, 1);
-                    if (!ok) break;
-                    mbar_expect_tx(bar(B_KVFULL + s), 2 * kKvTile);
-                    const uint32_t kd = smem_base + kSmemK + s * kKvTile, vd = smem_base + kSmemV + s * kKvTile;
-                    tma_load_kv_tile<kN, 4>(kd, kKvSlab, mk, bar(B_KVFULL + s), a.rg, it.b, it.kvh, j * kN, it.len, a.rg.kv_maps != nullptr);
-                    tma_load_kv_tile<kN, 4>(vd, kKvSlab, mv, bar(B_KVFULL + s), a.rg, it.b, it.kvh, j * kN, it.len, a.rg.kv_maps != nullptr);
+                c.done = true;
+            };
+            Cursor kc{0, 0, 0, false, false, {}, &map_k}, vc{0, 0, 0, false, false, {}, &map_v};
+            advance(kc); advance(vc);
+            uint32_t qi = 0;
+            auto request_k = [&]() {
+                if (kc.j == 0) {   // the item's Q, once the previous item's last S is done with the buffer
+                    if (qi > 0) ok = mbar_wait(bar(B_QEMPTY), (qi - 1) & 1, wc, 12);
+                    if (!ok) return;
+                    ++qi;
+                    mbar_expect_tx(bar(B_QFULL), kQBytes);
+                    for (int c = 0; c < 4; ++c)
+                        tma_load_4d(smem_base + c * kQSlab, &map_q, bar(B_QFULL), 64 * c, (int)kc.it.h, (int)kc.it.qrow, (int)kc.it.qseq);
+                    if (a.rg.kv_maps) { kc.map = a.rg.kv_maps + 2 * kc.it.b; tensormap_acquire(kc.map); }
                 }
-                gk += it.nkv;
+                const uint32_t s = kc.g % kKStages, ph = (kc.g / kKStages) & 1;
+                if (kc.g >= (uint32_t)kKStages) ok = mbar_wait(bar(B_KEMPTY + s), ph ^ 1, wc, 1);
+                if (!ok) return;
+                mbar_expect_tx(bar(B_KFULL + s), kKvTile);
+                tma_load_kv_tile<kN, 4>(smem_base + kSmemK + s * kKvTile, kKvSlab, kc.map, bar(B_KFULL + s), a.rg, kc.it.b, kc.it.kvh,
+                                        kc.j * kN, kc.it.len, a.rg.kv_maps != nullptr);
+                ++kc.g;
+                advance(kc);
+            };
+            auto request_v = [&]() {
+                if (vc.j == 0 && a.rg.kv_maps) { vc.map = a.rg.kv_maps + 2 * vc.it.b + 1; tensormap_acquire(vc.map); }
+                const uint32_t s = vc.g % kVStages, ph = (vc.g / kVStages) & 1;
+                if (vc.g >= (uint32_t)kVStages) ok = mbar_wait(bar(B_VEMPTY + s), ph ^ 1, wc, 13);
+                if (!ok) return;
+                mbar_expect_tx(bar(B_VFULL + s), kKvTile);
+                tma_load_kv_tile<kN, 4>(smem_base + kSmemV + s * kKvTile, kKvSlab, vc.map, bar(B_VFULL + s), a.rg, vc.it.b, vc.it.kvh,
+                                        vc.j * kN, vc.it.len, a.rg.kv_maps != nullptr);
+                ++vc.g;
+                advance(vc);
+            };
+            if (!kc.done) request_k();
+            while (!vc.done && ok) {
+                if (!kc.done) request_k();   // K of the tile after the one whose V follows
+                if (ok) request_v();
             }
         }
     } else if (warp == 5) {
@@ -908,6 +937,7 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     mma_ss(tmem + kColS + sb * kN, desc_kmajor(smem_base + (ks >> 2) * kQSlab + (ks & 3) * 32),
                            desc_kmajor(kb + (ks >> 2) * kKvSlab + (ks & 3) * 32), idesc_qk, ks > 0);
                 tc_commit(bar(B_SFULL + sb));
+                tc_commit(bar(B_KEMPTY + s));   // the K slot is free as soon as this S is computed
             };
             auto issue_pv = [&](uint32_t sb, uint32_t s, bool first) {   // O (+)= P_sb * V(stage s)
                 const uint32_t vb = smem_base + kSmemV + s * kKvTile;
@@ -924,26 +954,28 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 ++qi;
                 if (!ok) break;
                 // S(0) first; then per tile: S(j+1) ahead of PV(j), so the tensor core has work while tile j is in its softmax
-                ok = mbar_wait(bar(B_KVFULL + gk % kStages), (gk / kStages) & 1, wc, 4);
+                ok = mbar_wait(bar(B_KFULL + gk % kKStages), (gk / kKStages) & 1, wc, 4);
                 if (!ok) break;
                 tc_fence_after();
-                issue_qk(sc & 1, gk % kStages);
+                issue_qk(sc & 1, gk % kKStages);
                 if (it.nkv == 1) tc_commit(bar(B_QEMPTY));
                 for (uint32_t j = 0; j < it.nkv && ok; ++j) {
                     if (j + 1 < it.nkv) {
                         const uint32_t gi = gk + j + 1;
-                        ok = mbar_wait(bar(B_KVFULL + gi % kStages), (gi / kStages) & 1, wc, 4);
+                        ok = mbar_wait(bar(B_KFULL + gi % kKStages), (gi / kKStages) & 1, wc, 4);
                         if (!ok) break;
                         tc_fence_after();
-                        issue_qk((sc + j + 1) & 1, gi % kStages);
+                        issue_qk((sc + j + 1) & 1, gi % kKStages);
                         if (j + 2 == it.nkv) tc_commit(bar(B_QEMPTY));   // the item's last S: Q is no longer needed
                     }
                     const uint32_t t = sc + j;
-                    ok = mbar_wait(bar(B_PFULL + (t & 1)), (t >> 1) & 1, wc, 8);
+                    const uint32_t gv = gk + j;
+                    ok = mbar_wait(bar(B_VFULL + gv % kVStages), (gv / kVStages) & 1, wc, 5);
+                    if (ok) ok = mbar_wait(bar(B_PFULL + (t & 1)), (t >> 1) & 1, wc, 8);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_pv(t & 1, (gk + j) % kStages, j == 0);
-                    tc_commit(bar(B_KVEMPTY + (gk + j) % kStages));
+                    issue_pv(t & 1, gv % kVStages, j == 0);
+                    tc_commit(bar(B_VEMPTY + gv % kVStages));
                     tc_commit(bar(B_PVDONE));
                     if (j + 1 == it.nkv) tc_commit(bar(B_OFULL));
                 }
@@ -969,77 +1001,89 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 ok = mbar_wait(bar(B_SFULL + sb), (t >> 1) & 1, wc, 9);
                 if (!ok) break;
                 tc_fence_after();
-                const int lim = (int)row - (int)(j * kN);   // columns 0..lim of this tile are visible (all 64 when lim >= 63)
-                uint32_t va[32], vb[32];
-                tmem_ld32(t_s, va);
-                tmem_ld32(t_s + 32, vb);
-                tmem_wait_ld();
-                float mx = -INFINITY;
-                if (lim >= kN - 1) {
-                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                // one tile of the online softmax; tiles that touch the diagonal (the item's last two) are a second
+                // instantiation, so the common path carries no mask code
+                auto tile_body = [&](auto diag_c) {
+                    constexpr bool diag = decltype(diag_c)::value;
+                    const int lim = diag ? (int)row - (int)(j * kN) : kN - 1;   // columns 0..lim of this tile are visible
+                    uint32_t va[32], vb[32];
+                    tmem_ld32(t_s, va);
+                    tmem_ld32(t_s + 32, vb);
+                    tmem_wait_ld();
+                    float mx = -INFINITY;
+                    if (!diag || lim >= kN - 1) {
+                        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        m4[0] = max3(m4[0], __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
-                        m4[1] = max3(m4[1], __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
-                        m4[2] = max3(m4[2], __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
-                        m4[3] = max3(m4[3], __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
+                        for (int i = 0; i < 32; i += 4) {
+                            m4[0] = max3(m4[0], __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
+                            m4[1] = max3(m4[1], __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
+                            m4[2] = max3(m4[2], __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
+                            m4[3] = max3(m4[3], __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
+                        }
+                        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (i <= lim) mx = fmaxf(mx, __uint_as_float(va[i]));
+                            if (32 + i <= lim) mx = fmaxf(mx, __uint_as_float(vb[i]));
+                        }
                     }
-                    mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-                } else {
+                    mx *= a.scale_log2;                      // scale > 0; -inf stays -inf (a row that sees nothing of this tile)
+                    float corr = 1.f;
+                    if (j == 0) m_ref = mx;                  // key 0 is visible to every row: finite
+                    else if (mx > m_ref + kRescaleThreshold) { corr = exp2f(m_ref - mx); m_ref = mx; }
+                    if (__any_sync(0xffffffffu, corr != 1.f)) {
+                        // O belongs to PV(j-1) until that MMA has completed; only a rescale has to wait for it (S(j)
+                        // complete already says that PV(j-2) is, so the barrier is at most one phase behind)
+                        ok = mbar_wait(bar(B_PVDONE), (t - 1) & 1, wc, 10);
+                        if (!ok) return;
+                        tc_fence_after();
+                        l_sum *= corr;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (i <= lim) mx = fmaxf(mx, __uint_as_float(va[i]));
-                        if (32 + i <= lim) mx = fmaxf(mx, __uint_as_float(vb[i]));
+                        for (int c = 0; c < kD / 32; ++c) {
+                            uint32_t v[32];
+                            tmem_ld32(t_o + c * 32, v);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                            tmem_st32(t_o + c * 32, v);
+                        }
                     }
-                }
-                mx *= a.scale_log2;                      // scale > 0; -inf stays -inf (a row that sees nothing of this tile)
-                float corr = 1.f;
-                if (j == 0) m_ref = mx;                  // key 0 is visible to every row: finite
-                else if (mx > m_ref + kRescaleThreshold) { corr = exp2f(m_ref - mx); m_ref = mx; }
-                // O belongs to PV(j-1) until that MMA has completed
-                if (j > 0) {
-                    ok = mbar_wait(bar(B_PVDONE), (t - 1) & 1, wc, 10);
-                    if (!ok) break;
-                    tc_fence_after();
-                }
-                if (__any_sync(0xffffffffu, corr != 1.f)) {
-                    l_sum *= corr;
+                    // P = exp2(s * scale - m_ref), masked past the diagonal; packed over the first 32 columns of S
+                    const float neg_m = -m_ref;
+                    const unsigned long long scale2 = pack_f32x2(a.scale_log2, a.scale_log2), negm2 = pack_f32x2(neg_m, neg_m);
+                    unsigned long long ls2[2] = {0ull, 0ull};
+                    uint32_t pk[32];
 #pragma unroll
-                    for (int c = 0; c < kD / 32; ++c) {
-                        uint32_t v[32];
-                        tmem_ld32(t_o + c * 32, v);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                        tmem_st32(t_o + c * 32, v);
+                    for (int i = 0; i < 32; i += 2) {
+                        float x0, x1, x2, x3;
+                        fma_f32x2(x0, x1, __uint_as_float(va[i]), __uint_as_float(va[i + 1]), scale2, negm2);
+                        fma_f32x2(x2, x3, __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]), scale2, negm2);
+                        float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+                        if (diag) {
+                            if (i > lim) p0 = 0.f;
+                            if (i + 1 > lim) p1 = 0.f;
+                            if (32 + i > lim) p2 = 0.f;
+                            if (33 + i > lim) p3 = 0.f;
+                        }
+                        ls2[0] = add_f32x2(ls2[0], pack_f32x2(p0, p1));
+                        ls2[1] = add_f32x2(ls2[1], pack_f32x2(p2, p3));
+                        pk[i >> 1] = pack16<T>(p0, p1);
+                        pk[16 + (i >> 1)] = pack16<T>(p2, p3);
                     }
-                }
-                // P = exp2(s * scale - m_ref), masked past the diagonal; packed over the first 32 columns of S
-                const float neg_m = -m_ref;
-                float ls[4] = {0.f, 0.f, 0.f, 0.f};
-                uint32_t pk[32];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(va[i]), a.scale_log2, neg_m));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(va[i + 1]), a.scale_log2, neg_m));
-                    float p2 = fast_exp2(fmaf(__uint_as_float(vb[i]), a.scale_log2, neg_m));
-                    float p3 = fast_exp2(fmaf(__uint_as_float(vb[i + 1]), a.scale_log2, neg_m));
-                    if (lim < kN - 1) {
-                        if (i > lim) p0 = 0.f;
-                        if (i + 1 > lim) p1 = 0.f;
-                        if (32 + i > lim) p2 = 0.f;
-                        if (33 + i > lim) p3 = 0.f;
+                    {
+                        float s0, s1, s2, s3;
+                        asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(ls2[0]));
+                        asm("mov.b64 {%0, %1}, %2;" : "=f"(s2), "=f"(s3) : "l"(ls2[1]));
+                        l_sum += (s0 + s1) + (s2 + s3);
                     }
-                    ls[(i >> 1) & 1] += p0 + p1;
-                    ls[2 + ((i >> 1) & 1)] += p2 + p3;
-                    pk[i >> 1] = pack16<T>(p0, p1);
-                    pk[16 + (i >> 1)] = pack16<T>(p2, p3);
-                }
-                l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-                tmem_st32(t_s, pk);
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(bar(B_PFULL + sb));
+                    tmem_st32(t_s, pk);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(bar(B_PFULL + sb));
+                };
+                if ((j + 1) * kN - 1 > item.q0) tile_body(std::true_type{});
+                else tile_body(std::false_type{});
             }
             // ---- epilogue: O / l (x sigmoid(gate)) -> global ----
             if (ok) ok = mbar_wait(bar(B_OFULL), oc & 1, wc, 11);
@@ -1083,9 +1127,9 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     tc_fence_before();
     __syncthreads();
     if (warp == 4 && lane == 0 && *abort_word) {
-        for (int s = 0; s < p256::kStages; ++s)
+        for (int s = 0; s < p256::kKStages + p256::kVStages; ++s)
             for (uint32_t i = 0; i < (1u << 16); ++i)
-                if (mbar_try(bar(p256::B_KVFULL + s), 0)) break;
+                if (mbar_try(bar(s < p256::kKStages ? p256::B_KFULL + s : p256::B_VFULL + (s - p256::kKStages)), 0)) break;
     }
     __syncthreads();
     if (warp == 5) {
