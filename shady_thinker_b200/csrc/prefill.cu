@@ -780,23 +780,30 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // scores of consecutive K/V tiles alternate between two 64-column S buffers, so that the softmax of tile j runs while
 // the tensor core computes S(j+1).  M = 128, N = 64, K = 256 for S = Q K^T (16 MMAs), M = 128, N = 256, K = 64 for
 // O += P V (4 MMAs, P from TMEM, V as an MN-major shared-memory operand whose four 64-dim slabs the MMA walks).
-// Shared memory: Q 64 KB (four [128][64] slabs), K and V 32 KB per tile (four [64][64] slabs each), two stages.
-// Warps 0-3 softmax (one thread per row), warp 4 TMA producer, warp 5 MMA issuer and TMEM owner.
-// Because S(j+1) is issued ahead of PV(j), "S(j+1) complete" no longer says that O is free: PV(j) commits to a
-// barrier of its own, which the softmax threads pass before they touch O.
+// Q lives in TMEM (128 columns), not in shared memory: with N = 64 a score MMA that fetched both operands from shared
+// memory would read 4 KB of Q and 2 KB of K per 32 clocks, more than the 128 bytes per clock shared memory gives, on
+// top of the TMA writes of the next tiles.  Four loader warps read the item's Q rows from global memory into
+// registers (one row per thread, while the previous item still computes) and store them to TMEM once that item's
+// last score MMA is done.  Shared memory then holds only K/V: four K tiles and three V tiles of 32 KB, in rings of
+// their own (a K slot is free once its S is computed, a V slot once its PV is).
+// Warps 0-3 softmax (one thread per row), warp 4 TMA producer, warps 5 (TMEM owner) and 11 score-MMA issuers, warps 6-9
+// Q loaders, warp 10 PV-MMA issuer.  The score MMAs run up to two tiles ahead of the PV MMAs, so "S(t) complete" does not
+// say that O is free: PV(t) commits to a barrier (one per S buffer), which a softmax thread passes before it rescales O
+// and the score issuer before it overwrites the buffer P(t) lived in.
 // =====================================================================================================
 namespace p256 {
-constexpr int kM = 128, kN = 64, kD = 256, kKStages = 3, kVStages = 2;
-constexpr uint32_t kQSlab = 128 * 128;          // [128 rows][64 elements] 16-bit
-constexpr uint32_t kQBytes = 4 * kQSlab;        // 64 KB
-constexpr uint32_t kKvSlab = 64 * 128;          // [64 rows][64 elements]
+constexpr int kM = 128, kN = 64, kD = 256, kKStages = 4, kVStages = 3;
+constexpr uint32_t kKvSlab = 64 * 128;          // [64 rows][64 elements] 16-bit
 constexpr uint32_t kKvTile = 4 * kKvSlab;       // 32 KB
-constexpr uint32_t kSmemK = kQBytes, kSmemV = kSmemK + kKStages * kKvTile, kSmemBar = kSmemV + kVStages * kKvTile;
+constexpr uint32_t kSmemK = 0, kSmemV = kSmemK + kKStages * kKvTile, kSmemBar = kSmemV + kVStages * kKvTile;
 constexpr uint32_t kSmem = kSmemBar + 256 + 1024;
-static_assert(kSmem <= 232448, "Q + three K tiles + two V tiles must fit in 227 KB");
-enum { B_QFULL = 0, B_QEMPTY = 1, B_KFULL = 2, B_KEMPTY = 5, B_VFULL = 8, B_VEMPTY = 10, B_SFULL = 12, B_PFULL = 14, B_PVDONE = 16,
-       B_OFULL = 17, B_COUNT = 18 };
-constexpr uint32_t kColS = 0, kColO = 128;      // TMEM columns: S0 [0,64) S1 [64,128) O [128,384); P_b = first 32 columns of S_b
+static_assert(kSmem <= 232448, "four K tiles + three V tiles must fit in 227 KB");
+enum { B_QFULL = 0, B_QEMPTY = 1, B_KFULL = 2, B_KEMPTY = 6, B_VFULL = 10, B_VEMPTY = 13, B_SFULL = 16, B_PFULL = 18, B_PVDONE = 20,
+       B_OFULL = 22, B_COUNT = 23 };
+// TMEM columns: S0 [0,64) S1 [64,128) O [128,384) Q [384,512); P_b = first 32 columns of S_b.  Q (128 rows x 256
+// 16-bit elements, two per column) is the A operand of the score MMAs straight from TMEM.
+constexpr uint32_t kColS = 0, kColO = 128, kColQ = 384;
+constexpr uint32_t kThreads = 384;              // warps 0-3 softmax, 4 TMA producer, 5 and 11 score-MMA issuers, 6-9 Q loaders, 10 PV-MMA issuer
 }  // namespace p256
 
 struct Prefill256Args {
@@ -808,12 +815,12 @@ struct Prefill256Args {
     float scale_log2;
     const void *gate_src;   // optional: projection rows [B][T][nh][gate_row] whose elements [256, 512) are the gate
     uint32_t gate_row;
+    const void *q;          // [tokens][nh][256], normed and rotated
 };
 
 template <typename T>
-__global__ void __launch_bounds__(192, 1)
-prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                  const __grid_constant__ CUtensorMap map_v, const Prefill256Args a) {
+__global__ void __launch_bounds__(p256::kThreads, 1)
+prefill256_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Prefill256Args a) {
     using namespace p256;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -851,7 +858,8 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
     if (warp == 4 && lane == 0) {
-        mbar_init(bar(B_QFULL), 1); mbar_init(bar(B_QEMPTY), 1); mbar_init(bar(B_PVDONE), 1); mbar_init(bar(B_OFULL), 1);
+        mbar_init(bar(B_QFULL), 128); mbar_init(bar(B_QEMPTY), 2); mbar_init(bar(B_OFULL), 1);
+        mbar_init(bar(B_PVDONE), 1); mbar_init(bar(B_PVDONE + 1), 1);
         for (int s = 0; s < kKStages; ++s) { mbar_init(bar(B_KFULL + s), 1); mbar_init(bar(B_KEMPTY + s), 1); }
         for (int s = 0; s < kVStages; ++s) { mbar_init(bar(B_VFULL + s), 1); mbar_init(bar(B_VEMPTY + s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar(B_SFULL + b), 1); mbar_init(bar(B_PFULL + b), 128); }
@@ -870,8 +878,8 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (warp == 4) {
         // =============================== TMA producer ===============================
         // K and V travel separately: a K tile's slot is free again as soon as its S is computed, a V tile's only
-        // after its PV, so K (three slots) runs one tile ahead of V (two slots) and the next S never waits for a PV.
-        // Two cursors walk the item list, one requesting K tiles (and each item's Q ahead of its first K), one V tiles.
+        // after its PV, so K runs ahead of V and the next S never waits for a PV.  Two cursors walk the item list,
+        // one requesting K tiles, one V tiles.
         if (lane == 0) {
             bool ok = true;
             struct Cursor { uint32_t rnd, j, g; bool have, done; Item it; const CUtensorMap *map; };
@@ -888,17 +896,8 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             };
             Cursor kc{0, 0, 0, false, false, {}, &map_k}, vc{0, 0, 0, false, false, {}, &map_v};
             advance(kc); advance(vc);
-            uint32_t qi = 0;
             auto request_k = [&]() {
-                if (kc.j == 0) {   // the item's Q, once the previous item's last S is done with the buffer
-                    if (qi > 0) ok = mbar_wait(bar(B_QEMPTY), (qi - 1) & 1, wc, 12);
-                    if (!ok) return;
-                    ++qi;
-                    mbar_expect_tx(bar(B_QFULL), kQBytes);
-                    for (int c = 0; c < 4; ++c)
-                        tma_load_4d(smem_base + c * kQSlab, &map_q, bar(B_QFULL), 64 * c, (int)kc.it.h, (int)kc.it.qrow, (int)kc.it.qseq);
-                    if (a.rg.kv_maps) { kc.map = a.rg.kv_maps + 2 * kc.it.b; tensormap_acquire(kc.map); }
-                }
+                if (kc.j == 0 && a.rg.kv_maps) { kc.map = a.rg.kv_maps + 2 * kc.it.b; tensormap_acquire(kc.map); }
                 const uint32_t s = kc.g % kKStages, ph = (kc.g / kKStages) & 1;
                 if (kc.g >= (uint32_t)kKStages) ok = mbar_wait(bar(B_KEMPTY + s), ph ^ 1, wc, 1);
                 if (!ok) return;
@@ -925,26 +924,55 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 if (ok) request_v();
             }
         }
-    } else if (warp == 5) {
-        // =============================== MMA issuer ===============================
+    } else if (warp >= 6 && warp < 10) {
+        // =============================== Q loaders: global -> registers -> TMEM ===============================
+        // One thread per query row (TMEM lane; a warp reaches the lane quarter warp % 4).  A row is 512 bytes: 32
+        // 16-byte loads, whose words are already what a TMEM column of a 16-bit A operand holds (two consecutive
+        // elements).  Rows past the end of the sequence are zeros.
+        const uint32_t quarter = warp & 3, r = quarter * 32 + lane;
+        const uint32_t t_q = tmem + ((quarter * 32) << 16) + kColQ;
+        bool ok = true;
+        uint32_t qi = 0;
+        for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
+            const uint32_t w = item_of_round(rnd);
+            if (w >= total_items) continue;
+            const Item it = get_item(w);
+            const bool live = it.q0 + r < it.len;
+            const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.q) +
+                                                               (((size_t)it.tok0 + it.q0 + r) * a.nh + it.h) * kD);
+            uint32_t v[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 u = live ? __ldg(src + c * 8 + i) : make_uint4(0, 0, 0, 0);
+                    v[c][4 * i] = u.x; v[c][4 * i + 1] = u.y; v[c][4 * i + 2] = u.z; v[c][4 * i + 3] = u.w;
+                }
+            // the previous item's last score MMA has read Q: the columns may be overwritten
+            if (qi > 0) ok = mbar_wait(bar(B_QEMPTY), (qi - 1) & 1, wc, 12);
+            if (!ok) break;
+            ++qi;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_st32(t_q + c * 32, v[c]);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(B_QFULL));
+        }
+    } else if (warp == 5 || warp == 11) {
+        // =============================== score-MMA issuers ===============================
+        // Three issuing threads, because one is not enough at this tile shape: the 16 small score MMAs, the 4 PV MMAs,
+        // four commits and three barrier waits of a 64-row K/V tile cost a single thread about twice the time the
+        // tensor pipe needs to execute them (a satisfied wait ~250 clocks, a commit ~80, an MMA issue that the pipe
+        // back-pressures 64).  This thread issues the score MMAs of the even tiles (S buffer 0), warp 11 those of the
+        // odd tiles (S buffer 1), warp 10 the PV MMAs; each commits its own.  An item has an even number of K/V tiles,
+        // so a tile's parity in the item is its parity in the CTA's running count.
+        // S(t) overwrites the buffer that held P(t-2): it waits for PV(t-2), which also keeps "S(t) complete" meaning
+        // "PV(t-2) complete" for the softmax threads.
         if (lane == 0) {
-            const uint32_t idesc_qk = make_idesc(kFmt, false, kN), idesc_pv = make_idesc(kFmt, true, kD);
+            const uint32_t sb = warp == 5 ? 0u : 1u;
+            const uint32_t idesc_qk = make_idesc(kFmt, false, kN);
             bool ok = true;
-            auto issue_qk = [&](uint32_t sb, uint32_t s) {         // S_sb = Q * K(stage s)^T
-                const uint32_t kb = smem_base + kSmemK + s * kKvTile;
-#pragma unroll
-                for (uint32_t ks = 0; ks < kD / 16; ++ks)
-                    mma_ss(tmem + kColS + sb * kN, desc_kmajor(smem_base + (ks >> 2) * kQSlab + (ks & 3) * 32),
-                           desc_kmajor(kb + (ks >> 2) * kKvSlab + (ks & 3) * 32), idesc_qk, ks > 0);
-                tc_commit(bar(B_SFULL + sb));
-                tc_commit(bar(B_KEMPTY + s));   // the K slot is free as soon as this S is computed
-            };
-            auto issue_pv = [&](uint32_t sb, uint32_t s, bool first) {   // O (+)= P_sb * V(stage s)
-                const uint32_t vb = smem_base + kSmemV + s * kKvTile;
-#pragma unroll
-                for (uint32_t ks = 0; ks < kN / 16; ++ks)
-                    mma_ts(tmem + kColO, tmem + kColS + sb * kN + ks * 8, desc_mnmajor(vb + ks * 2048, kKvSlab), idesc_pv, !first || (ks > 0));
-            };
             uint32_t gk = 0, qi = 0, sc = 0;   // running counts: K/V tiles, items, score tiles
             for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
                 const uint32_t w = item_of_round(rnd);
@@ -952,37 +980,53 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const Item it = get_item(w);
                 ok = mbar_wait(bar(B_QFULL), qi & 1, wc, 3);
                 ++qi;
-                if (!ok) break;
-                // S(0) first; then per tile: S(j+1) ahead of PV(j), so the tensor core has work while tile j is in its softmax
-                ok = mbar_wait(bar(B_KFULL + gk % kKStages), (gk / kKStages) & 1, wc, 4);
-                if (!ok) break;
-                tc_fence_after();
-                issue_qk(sc & 1, gk % kKStages);
-                if (it.nkv == 1) tc_commit(bar(B_QEMPTY));
-                for (uint32_t j = 0; j < it.nkv && ok; ++j) {
-                    if (j + 1 < it.nkv) {
-                        const uint32_t gi = gk + j + 1;
-                        ok = mbar_wait(bar(B_KFULL + gi % kKStages), (gi / kKStages) & 1, wc, 4);
-                        if (!ok) break;
-                        tc_fence_after();
-                        issue_qk((sc + j + 1) & 1, gi % kKStages);
-                        if (j + 2 == it.nkv) tc_commit(bar(B_QEMPTY));   // the item's last S: Q is no longer needed
-                    }
-                    const uint32_t t = sc + j;
-                    const uint32_t gv = gk + j;
-                    ok = mbar_wait(bar(B_VFULL + gv % kVStages), (gv / kVStages) & 1, wc, 5);
-                    if (ok) ok = mbar_wait(bar(B_PFULL + (t & 1)), (t >> 1) & 1, wc, 8);
+                for (uint32_t j = sb; j < it.nkv && ok; j += 2) {
+                    const uint32_t g = gk + j, t = sc + j, s = g % kKStages;
+                    ok = mbar_wait(bar(B_KFULL + s), (g / kKStages) & 1, wc, 4);
+                    if (ok && t >= 2) ok = mbar_wait(bar(B_PVDONE + sb), ((t >> 1) - 1) & 1, wc, 6);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_pv(t & 1, gv % kVStages, j == 0);
-                    tc_commit(bar(B_VEMPTY + gv % kVStages));
-                    tc_commit(bar(B_PVDONE));
+                    const uint32_t kb = smem_base + kSmemK + s * kKvTile;
+#pragma unroll
+                    for (uint32_t ks = 0; ks < kD / 16; ++ks)      // S_sb = Q (TMEM) * K(slot s)^T
+                        mma_ts(tmem + kColS + sb * kN, tmem + kColQ + ks * 8, desc_kmajor(kb + (ks >> 2) * kKvSlab + (ks & 3) * 32),
+                               idesc_qk, ks > 0);
+                    tc_commit(bar(B_SFULL + sb));
+                    tc_commit(bar(B_KEMPTY + s));                  // the K slot is free as soon as this S is computed
+                    if (j + 2 >= it.nkv) tc_commit(bar(B_QEMPTY)); // this thread's last S of the item (Q is free when both have said so)
+                }
+                gk += it.nkv; sc += it.nkv;
+            }
+        }
+    } else if (warp == 10) {
+        // =============================== PV issuer ===============================
+        if (lane == 0) {
+            const uint32_t idesc_pv = make_idesc(kFmt, true, kD);
+            bool ok = true;
+            uint32_t gk = 0, sc = 0;
+            for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
+                const uint32_t w = item_of_round(rnd);
+                if (w >= total_items) continue;
+                const Item it = get_item(w);
+                for (uint32_t j = 0; j < it.nkv && ok; ++j) {
+                    const uint32_t g = gk + j, t = sc + j, s = g % kVStages, sb = t & 1;
+                    ok = mbar_wait(bar(B_VFULL + s), (g / kVStages) & 1, wc, 5);
+                    if (ok) ok = mbar_wait(bar(B_PFULL + sb), (t >> 1) & 1, wc, 8);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t vb = smem_base + kSmemV + s * kKvTile;
+#pragma unroll
+                    for (uint32_t ks = 0; ks < kN / 16; ++ks)      // O (+)= P_sb * V(slot s)
+                        mma_ts(tmem + kColO, tmem + kColS + sb * kN + ks * 8, desc_mnmajor(vb + ks * 2048, kKvSlab), idesc_pv,
+                               j > 0 || ks > 0);
+                    tc_commit(bar(B_VEMPTY + s));
+                    tc_commit(bar(B_PVDONE + sb));
                     if (j + 1 == it.nkv) tc_commit(bar(B_OFULL));
                 }
                 gk += it.nkv; sc += it.nkv;
             }
         }
-    } else {
+    } else if (warp < 4) {
         // =============================== softmax (one thread per query row) ===============================
         const uint32_t r = tid;                         // row in the tile == TMEM lane
         const uint32_t lane_base = (warp * 32) << 16;
@@ -1033,9 +1077,9 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     if (j == 0) m_ref = mx;                  // key 0 is visible to every row: finite
                     else if (mx > m_ref + kRescaleThreshold) { corr = exp2f(m_ref - mx); m_ref = mx; }
                     if (__any_sync(0xffffffffu, corr != 1.f)) {
-                        // O belongs to PV(j-1) until that MMA has completed; only a rescale has to wait for it (S(j)
-                        // complete already says that PV(j-2) is, so the barrier is at most one phase behind)
-                        ok = mbar_wait(bar(B_PVDONE), (t - 1) & 1, wc, 10);
+                        // O belongs to PV(t-1) until that MMA has completed; only a rescale has to wait for it (the
+                        // barrier of that parity completes next for PV(t+1), which needs this thread's P(t+1) first)
+                        ok = mbar_wait(bar(B_PVDONE + ((t - 1) & 1)), ((t - 1) >> 1) & 1, wc, 10);
                         if (!ok) return;
                         tc_fence_after();
                         l_sum *= corr;
@@ -1416,17 +1460,14 @@ static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefil
     if (const int st = pending_timeout(ctx, who)) return st;
     const uint32_t B = p->num_seqs, T = p->seq_len, nh = p->num_q_heads, nkv = p->num_kv_heads;
     const CUtensorMapDataType dt = p->dtype == SHADY_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap mq, mk, mv;
-    bool maps_ok;
+    CUtensorMap mk, mv;
+    bool maps_ok = true;
     if (rs) {
-        const uint64_t toks = rs->lay.total_tokens;
-        maps_ok = make_map_4d(&mq, dt, d_q, 256, nh, toks, 1, 256 * 2, (uint64_t)nh * 256 * 2, toks * nh * 256 * 2, 128);
         if (rs->pool_maps) { mk = rs->mk; mv = rs->mv; }
-        else { mk = mq; mv = mq; }
+        else { memset(&mk, 0, sizeof(mk)); memset(&mv, 0, sizeof(mv)); }   // unused: every sequence brings its own pair
     } else {
         const uint64_t seq_stride_b = (B == 1 ? (uint64_t)T * nkv * 256 : cache->seq_stride) * 2;
-        maps_ok = make_map_4d(&mq, dt, d_q, 256, nh, T, B, 256 * 2, (uint64_t)nh * 256 * 2, (uint64_t)T * nh * 256 * 2, 128) &&
-                  make_map_4d(&mk, dt, cache->d_k_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64) &&
+        maps_ok = make_map_4d(&mk, dt, cache->d_k_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64) &&
                   make_map_4d(&mv, dt, cache->d_v_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64);
     }
     SHADY_REQUIRE(ctx, maps_ok, SHADY_ERR_CUDA, w + ": cuTensorMapEncodeTiled failed");
@@ -1436,7 +1477,7 @@ static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefil
     a.m_tiles = (T + 127) / 128;
     if (rs) a.rg = rs->rg;
     a.scale_log2 = (1.0f / sqrtf(256.0f)) * 1.4426950408889634f;
-    a.gate_src = gate_src; a.gate_row = gate_row;
+    a.gate_src = gate_src; a.gate_row = gate_row; a.q = d_q;
     const unsigned long long total_items = rs ? (unsigned long long)rs->rg.entries * nh : (unsigned long long)a.m_tiles * B * nh;
     SHADY_REQUIRE(ctx, total_items <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, w + ": too many tiles for one launch");
     const unsigned blocks = (unsigned)(total_items < (unsigned long long)ctx->num_sms ? total_items : (unsigned long long)ctx->num_sms);
@@ -1446,8 +1487,8 @@ static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefil
         SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill256_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, p256::kSmem));
         configured_dev = ctx->device;
     }
-    if (p->dtype == SHADY_BF16) prefill256_kernel<__nv_bfloat16><<<blocks, 192, p256::kSmem, ctx->stream>>>(mq, mk, mv, a);
-    else prefill256_kernel<__half><<<blocks, 192, p256::kSmem, ctx->stream>>>(mq, mk, mv, a);
+    if (p->dtype == SHADY_BF16) prefill256_kernel<__nv_bfloat16><<<blocks, p256::kThreads, p256::kSmem, ctx->stream>>>(mk, mv, a);
+    else prefill256_kernel<__half><<<blocks, p256::kThreads, p256::kSmem, ctx->stream>>>(mk, mv, a);
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
