@@ -23,7 +23,7 @@ int pending_timeout(shady_ctx *ctx, const char *who) {
     return SHADY_OK;
 }
 
-// Text of a wait code: 1..13 = mbarriers of the prefill kernels, 90 = the decode grid barrier, 100 + r = the NVLink
+// Text of a wait code: 1..16 = waits of the prefill kernels (mbarriers, shared-memory handshakes), 90 = the decode grid barrier, 100 + r = the NVLink
 // flag of rank r.
 std::string timeout_message(int code) {
     if (code >= 100)
@@ -184,6 +184,7 @@ int shady_ctx_create(int device, void *stream, shady_ctx **out) {
     c->knobs.min_span = env_u32("SHADY_DECODE_MIN_SPAN", 0);
     c->knobs.grid_merge = env_u32("SHADY_DECODE_GRID_MERGE", 1);
     c->knobs.interleave = env_u32("SHADY_DECODE_INTERLEAVE", 1);
+    c->knobs.prefill_variant = env_u32("SHADY_PREFILL_VARIANT", 0);
     *out = c;
     return SHADY_OK;
 }

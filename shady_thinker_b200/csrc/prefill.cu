@@ -164,6 +164,15 @@ __device__ __forceinline__ void tma_load_kv_tile(uint32_t dst, uint32_t slab_byt
         for (int c = 0; c < SLABS; ++c) tma_load_4d(dst + c * slab_bytes, map, bar, 64 * c, (int)kvh, (int)row0, per_seq ? 0 : (int)b);
     }
 }
+// one 8-byte shared-memory word read / written as a unit (the {maximum, tile number} pair two warpgroups hand over)
+__device__ __forceinline__ uint2 lds_pair(uint32_t saddr) {
+    uint2 v;
+    asm volatile("ld.volatile.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(saddr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts_pair(uint32_t saddr, uint32_t x, uint32_t y) {
+    asm volatile("st.volatile.shared.v2.u32 [%0], {%1, %2};" ::"r"(saddr), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -191,6 +200,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -774,66 +790,92 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
 
 // =====================================================================================================
-// head_dim 256 (the gated-attention layer shape): one 128-row Q tile per item, K/V tiles of 64 rows.
+// Row-tile kernel: one 128-row Q tile per item, K/V tiles of 32 KB (64 rows at head_dim 256, 128 rows at 128).
 //
-// S + O of two 128-row tiles would need 768 TMEM columns, so an item is ONE row tile: O takes 256 columns, and the
-// scores of consecutive K/V tiles alternate between two 64-column S buffers, so that the softmax of tile j runs while
-// the tensor core computes S(j+1).  M = 128, N = 64, K = 256 for S = Q K^T (16 MMAs), M = 128, N = 256, K = 64 for
-// O += P V (4 MMAs, P from TMEM, V as an MN-major shared-memory operand whose four 64-dim slabs the MMA walks).
-// Q lives in TMEM (128 columns), not in shared memory: with N = 64 a score MMA that fetched both operands from shared
-// memory would read 4 KB of Q and 2 KB of K per 32 clocks, more than the 128 bytes per clock shared memory gives, on
-// top of the TMA writes of the next tiles.  Four loader warps read the item's Q rows from global memory into
-// registers (one row per thread, while the previous item still computes) and store them to TMEM once that item's
-// last score MMA is done.  Shared memory then holds only K/V: four K tiles and three V tiles of 32 KB, in rings of
-// their own (a K slot is free once its S is computed, a V slot once its PV is).
-// Warps 0-3 softmax (one thread per row), warp 4 TMA producer, warps 5 (TMEM owner) and 11 score-MMA issuers, warps 6-9
-// Q loaders, warp 10 PV-MMA issuer.  The score MMAs run up to two tiles ahead of the PV MMAs, so "S(t) complete" does not
-// say that O is free: PV(t) commits to a barrier (one per S buffer), which a softmax thread passes before it rescales O
-// and the score issuer before it overwrites the buffer P(t) lived in.
+// head_dim 256 is the gated-attention layer shape.  S + O of two 128-row tiles would need 768 TMEM columns there, so
+// an item is ONE row tile and the depth of the pipeline comes from the score buffers instead: O takes head_dim TMEM
+// columns, the other 256 (head_dim 256: four buffers of 64 columns) or 384 (head_dim 128: three of 128) hold the
+// scores of consecutive K/V tiles.  P overwrites the first half of its own S buffer and is the A operand of the PV MMA
+// straight from TMEM, so a buffer goes through S -> softmax -> PV before the next S may land in it; with three or
+// four buffers that chain (about 4,000 clocks) is no longer what the tile rate waits for.
+//   * Shared memory: Q (one buffer, TMA), three K tiles and two V tiles in rings of their own — a K slot is free as
+//     soon as its S is computed, a V slot only after its PV, so K runs ahead of V.
+//   * Three MMA-issuing threads, because one is not enough at these tile shapes: a satisfied barrier wait costs a
+//     thread ~250 clocks, a commit ~80, an MMA issue that the pipe back-pressures 64, and the waits, commits and
+//     issues of one K/V tile add up to about twice the time the tensor pipe needs to execute its MMAs.  Two threads
+//     issue the score MMAs (tiles of even / odd running number), one the PV MMAs; each commits its own.  MMAs of
+//     different threads are not ordered among themselves, so what must be ordered goes through barriers: S(t) waits
+//     for PV(t - NB) (its buffer), the first PV of an item for the epilogue's reads of O.
+//   * Softmax: one thread per row.  head_dim 256: one warpgroup, 64 scores per tile in registers.  head_dim 128: two
+//     warpgroups take alternate tiles (two passes over 128 scores each), so that one tile's exponentials run under the
+//     other's loads and maxima.  What stays sequential is each row's running maximum: the thread that takes tile t
+//     reads {maximum, t} as the other warpgroup's thread left it after tile t - 1, decides (keep the reference, or
+//     move it and rescale O) and publishes {maximum, t + 1} before its long pass.  Each warpgroup sums its own
+//     tiles' row sums relative to the reference it last used; the epilogue brings the two together.
+//   * Four epilogue warps drain O (x 1/l, x sigmoid(gate)) while the softmax warps are already in the next item.
+// Warps: 4 per softmax warpgroup, then TMA producer, score issuer (even tiles; TMEM owner), PV issuer, score issuer
+// (odd tiles), four epilogue warps.
 // =====================================================================================================
-namespace p256 {
-constexpr int kM = 128, kN = 64, kD = 256, kKStages = 4, kVStages = 3;
-constexpr uint32_t kKvSlab = 64 * 128;          // [64 rows][64 elements] 16-bit
-constexpr uint32_t kKvTile = 4 * kKvSlab;       // 32 KB
-constexpr uint32_t kSmemK = 0, kSmemV = kSmemK + kKStages * kKvTile, kSmemBar = kSmemV + kVStages * kKvTile;
-constexpr uint32_t kSmem = kSmemBar + 256 + 1024;
-static_assert(kSmem <= 232448, "four K tiles + three V tiles must fit in 227 KB");
-enum { B_QFULL = 0, B_QEMPTY = 1, B_KFULL = 2, B_KEMPTY = 6, B_VFULL = 10, B_VEMPTY = 13, B_SFULL = 16, B_PFULL = 18, B_PVDONE = 20,
-       B_OFULL = 22, B_COUNT = 23 };
-// TMEM columns: S0 [0,64) S1 [64,128) O [128,384) Q [384,512); P_b = first 32 columns of S_b.  Q (128 rows x 256
-// 16-bit elements, two per column) is the A operand of the score MMAs straight from TMEM.
-constexpr uint32_t kColS = 0, kColO = 128, kColQ = 384;
-constexpr uint32_t kThreads = 384;              // warps 0-3 softmax, 4 TMA producer, 5 and 11 score-MMA issuers, 6-9 Q loaders, 10 PV-MMA issuer
-}  // namespace p256
+namespace rt {
+constexpr int kM = 128, kKStages = 3, kVStages = 2;
+constexpr uint32_t kKvTile = 32768;             // a K or V tile: 64 rows of 256 elements or 128 rows of 128, as [rows][64]-element slabs
+constexpr uint32_t kRegsSoftmax2 = 160, kRegsOther2 = 96;   // two softmax warpgroups: 256 x 160 + 256 x 96 = 65,536 registers
+enum { B_QFULL = 0, B_QEMPTY = 1, B_KFULL = 2, B_KEMPTY = 5, B_VFULL = 8, B_VEMPTY = 10, B_SFULL = 12, B_PFULL = 16, B_PVDONE = 20,
+       B_OFULL = 24, B_OFREE = 25, B_COUNT = 26 };
+template <int D> struct Shape {
+    static constexpr int kN = 16384 / D;                  // K/V rows per tile
+    static constexpr int kNB = D == 128 ? 3 : 4;          // score buffers in TMEM
+    static constexpr int kNSW = D == 128 ? 2 : 1;         // softmax warpgroups
+    static constexpr uint32_t kQSlab = 128 * 128;         // [128 rows][64 elements] 16-bit
+    static constexpr uint32_t kQBytes = (D / 64) * kQSlab;
+    static constexpr uint32_t kKvSlab = kN * 128;         // [kN rows][64 elements]
+    static constexpr uint32_t kSmemQ = 0, kSmemK = kQBytes, kSmemV = kSmemK + kKStages * kKvTile, kSmemBar = kSmemV + kVStages * kKvTile;
+    // Words the softmax and epilogue threads of a row hand each other (8-byte pairs written and read as units, each
+    // with a running number so that the reader knows what it has): {running maximum, tile number} of the row's last
+    // decision (two warpgroups only); per warpgroup {row sum of the item, item number + 1} and the maximum that sum is
+    // relative to (two warpgroups only); the number of items whose sums the epilogue thread has taken.
+    static constexpr uint32_t kSmemMSeq = kSmemBar + 256, kSmemLPair = kSmemMSeq + (kNSW == 2 ? 128 * 8 : 0);
+    static constexpr uint32_t kSmemLRef = kSmemLPair + kNSW * 128 * 8, kSmemAck = kSmemLRef + (kNSW == 2 ? 2 * 128 * 4 : 0);
+    static constexpr uint32_t kSmem = kSmemAck + 128 * 4 + 1024;
+    static constexpr uint32_t kColO = kNB * kN;           // TMEM: S buffers [0, kNB * kN), then O; P_b = first kN / 2 columns of S_b
+    static constexpr uint32_t kThreads = 128 * kNSW + 256;
+    static_assert(kColO + D <= kTmemCols, "the score buffers and O must fit in TMEM");
+    static_assert(kSmem <= 232448, "Q and the K and V rings must fit in 227 KB");
+};
+}  // namespace rt
 
-struct Prefill256Args {
+struct RowTileArgs {
     void *out;
     RaggedRef rg;
     StatusRef status;
     uint32_t wait_mbar;
     uint32_t B, T, nh, nkv, G, m_tiles;   // m_tiles = ceil(T / 128)
     float scale_log2;
-    const void *gate_src;   // optional: projection rows [B][T][nh][gate_row] whose elements [256, 512) are the gate
+    const void *gate_src;   // optional: projection rows [tokens][nh][gate_row] whose elements [head_dim, 2 head_dim) are the gate
     uint32_t gate_row;
-    const void *q;          // [tokens][nh][256], normed and rotated
 };
 
-template <typename T>
-__global__ void __launch_bounds__(p256::kThreads, 1)
-prefill256_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Prefill256Args a) {
-    using namespace p256;
+template <typename T, int kD>
+__global__ void __launch_bounds__(rt::Shape<kD>::kThreads, 1)
+rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const RowTileArgs a) {
+    using namespace rt;
+    using Sh = Shape<kD>;
+    constexpr int kN = Sh::kN, kNB = Sh::kNB, NSW = Sh::kNSW, kSlabs = kD / 64;
+    constexpr uint32_t kKvSlab = Sh::kKvSlab, kQSlab = Sh::kQSlab, kColO = Sh::kColO;
+    constexpr uint32_t kWProd = 4 * NSW, kWSEven = kWProd + 1, kWPv = kWProd + 2, kWSOdd = kWProd + 3, kWEpi = kWProd + 4;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *smem = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t bar0 = smem_base + kSmemBar;
+    const uint32_t bar0 = smem_base + Sh::kSmemBar;
     auto bar = [&](int i) { return bar0 + 8u * i; };
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemBar + 8 * B_COUNT);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + Sh::kSmemBar + 8 * B_COUNT);
     volatile uint32_t *abort_word = tmem_slot + 1;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (gave_up(a.status)) return;
     const WaitCtx wc{abort_word, a.status, a.wait_mbar};
 
-    struct Item { uint32_t b, h, kvh, q0, nkv, len, tok0, qrow, qseq; };   // fields as in the head_dim-128 kernel
+    struct Item { uint32_t b, h, kvh, q0, nkv, len, tok0, qrow, qseq; };   // fields as in the two-tile kernel
     const uint32_t bh_count = a.B * a.nh, total_items = a.rg.items ? a.rg.entries * a.nh : a.m_tiles * bh_count;
     auto get_item = [&](uint32_t w) {   // heaviest (latest rows) first
         Item it;
@@ -849,24 +891,29 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             it.q0 = m * kM; it.qrow = it.q0; it.qseq = it.b;
         }
         it.kvh = it.h / a.G;
-        it.nkv = 2 * m + 2;             // kv tiles 0 .. (q0 + 127) / 64; rows past T read as zeros and are masked
+        it.nkv = (m + 1) * (kM / kN);   // kv tiles 0 .. (q0 + 127) / kN; rows past T read as zeros and are masked
         return it;
     };
-    auto item_of_round = [&](uint32_t rnd) {   // serpentine deal, as in the head_dim-128 kernel
+    auto item_of_round = [&](uint32_t rnd) {   // serpentine deal, as in the two-tile kernel
         return rnd * gridDim.x + ((rnd & 1u) ? gridDim.x - 1u - blockIdx.x : blockIdx.x);
     };
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
-    if (warp == 4 && lane == 0) {
-        mbar_init(bar(B_QFULL), 128); mbar_init(bar(B_QEMPTY), 2); mbar_init(bar(B_OFULL), 1);
-        mbar_init(bar(B_PVDONE), 1); mbar_init(bar(B_PVDONE + 1), 1);
+    if (warp == kWProd && lane == 0) {
+        mbar_init(bar(B_QFULL), 1); mbar_init(bar(B_QEMPTY), 2); mbar_init(bar(B_OFULL), 1);
+        mbar_init(bar(B_OFREE), 128);
         for (int s = 0; s < kKStages; ++s) { mbar_init(bar(B_KFULL + s), 1); mbar_init(bar(B_KEMPTY + s), 1); }
         for (int s = 0; s < kVStages; ++s) { mbar_init(bar(B_VFULL + s), 1); mbar_init(bar(B_VEMPTY + s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar(B_SFULL + b), 1); mbar_init(bar(B_PFULL + b), 128); }
+        for (int b = 0; b < kNB; ++b) { mbar_init(bar(B_SFULL + b), 1); mbar_init(bar(B_PFULL + b), 128); mbar_init(bar(B_PVDONE + b), 1); }
         *abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (tid < 128) {   // nothing decided, posted or taken yet
+        if (NSW == 2) sts_pair(smem_base + Sh::kSmemMSeq + 8 * tid, 0u, 0u);
+        for (int xx = 0; xx < NSW; ++xx) sts_pair(smem_base + Sh::kSmemLPair + 8 * (xx * 128 + tid), 0u, 0u);
+        reinterpret_cast<volatile uint32_t *>(smem + Sh::kSmemAck)[tid] = 0u;
+    }
+    if (warp == kWSEven) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -875,11 +922,16 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 4) {
+    // two softmax warpgroups leave 128 registers per thread at launch: they take registers from the other warps
+    // (the instruction sits inside the branch it applies to, which is what lets the compiler use the larger budget there)
+    if (warp >= kWProd) {
+    if constexpr (NSW == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther2));
+    if (warp == kWProd) {
         // =============================== TMA producer ===============================
-        // K and V travel separately: a K tile's slot is free again as soon as its S is computed, a V tile's only
-        // after its PV, so K runs ahead of V and the next S never waits for a PV.  Two cursors walk the item list,
-        // one requesting K tiles, one V tiles.
+        // Two cursors walk the item list, one requesting K tiles (and each item's Q ahead of its first K), one V tiles.
+        // Neither waits for the other: the thread polls what each needs next (a free slot; for Q, both score issuers
+        // done with the previous item) and requests whatever can go, so K runs as far ahead of V as its ring allows —
+        // the score MMAs run up to NB tiles ahead of the PV MMAs, which free the V slots.
         if (lane == 0) {
             bool ok = true;
             struct Cursor { uint32_t rnd, j, g; bool have, done; Item it; const CUtensorMap *map; };
@@ -896,82 +948,58 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             };
             Cursor kc{0, 0, 0, false, false, {}, &map_k}, vc{0, 0, 0, false, false, {}, &map_v};
             advance(kc); advance(vc);
+            uint32_t qi = 0;
+            auto k_ready = [&]() {
+                if (kc.j == 0 && qi > 0 && !mbar_try(bar(B_QEMPTY), (qi - 1) & 1)) return false;
+                return kc.g < (uint32_t)kKStages || mbar_try(bar(B_KEMPTY + kc.g % kKStages), ((kc.g / kKStages) & 1) ^ 1);
+            };
+            auto v_ready = [&]() {
+                return vc.g < (uint32_t)kVStages || mbar_try(bar(B_VEMPTY + vc.g % kVStages), ((vc.g / kVStages) & 1) ^ 1);
+            };
             auto request_k = [&]() {
-                if (kc.j == 0 && a.rg.kv_maps) { kc.map = a.rg.kv_maps + 2 * kc.it.b; tensormap_acquire(kc.map); }
-                const uint32_t s = kc.g % kKStages, ph = (kc.g / kKStages) & 1;
-                if (kc.g >= (uint32_t)kKStages) ok = mbar_wait(bar(B_KEMPTY + s), ph ^ 1, wc, 1);
-                if (!ok) return;
+                if (kc.j == 0) {   // the item's Q, once both score issuers are done with the previous item's
+                    ++qi;
+                    mbar_expect_tx(bar(B_QFULL), Sh::kQBytes);
+                    for (int c = 0; c < kSlabs; ++c)
+                        tma_load_4d(smem_base + Sh::kSmemQ + c * kQSlab, &map_q, bar(B_QFULL), 64 * c, (int)kc.it.h, (int)kc.it.qrow, (int)kc.it.qseq);
+                    if (a.rg.kv_maps) { kc.map = a.rg.kv_maps + 2 * kc.it.b; tensormap_acquire(kc.map); }
+                }
+                const uint32_t s = kc.g % kKStages;
                 mbar_expect_tx(bar(B_KFULL + s), kKvTile);
-                tma_load_kv_tile<kN, 4>(smem_base + kSmemK + s * kKvTile, kKvSlab, kc.map, bar(B_KFULL + s), a.rg, kc.it.b, kc.it.kvh,
-                                        kc.j * kN, kc.it.len, a.rg.kv_maps != nullptr);
+                tma_load_kv_tile<kN, kSlabs>(smem_base + Sh::kSmemK + s * kKvTile, kKvSlab, kc.map, bar(B_KFULL + s), a.rg, kc.it.b, kc.it.kvh,
+                                             kc.j * kN, kc.it.len, a.rg.kv_maps != nullptr);
                 ++kc.g;
                 advance(kc);
             };
             auto request_v = [&]() {
                 if (vc.j == 0 && a.rg.kv_maps) { vc.map = a.rg.kv_maps + 2 * vc.it.b + 1; tensormap_acquire(vc.map); }
-                const uint32_t s = vc.g % kVStages, ph = (vc.g / kVStages) & 1;
-                if (vc.g >= (uint32_t)kVStages) ok = mbar_wait(bar(B_VEMPTY + s), ph ^ 1, wc, 13);
-                if (!ok) return;
+                const uint32_t s = vc.g % kVStages;
                 mbar_expect_tx(bar(B_VFULL + s), kKvTile);
-                tma_load_kv_tile<kN, 4>(smem_base + kSmemV + s * kKvTile, kKvSlab, vc.map, bar(B_VFULL + s), a.rg, vc.it.b, vc.it.kvh,
-                                        vc.j * kN, vc.it.len, a.rg.kv_maps != nullptr);
+                tma_load_kv_tile<kN, kSlabs>(smem_base + Sh::kSmemV + s * kKvTile, kKvSlab, vc.map, bar(B_VFULL + s), a.rg, vc.it.b, vc.it.kvh,
+                                             vc.j * kN, vc.it.len, a.rg.kv_maps != nullptr);
                 ++vc.g;
                 advance(vc);
             };
-            if (!kc.done) request_k();
-            while (!vc.done && ok) {
-                if (!kc.done) request_k();   // K of the tile after the one whose V follows
-                if (ok) request_v();
+            uint32_t idle = 0;
+            while ((!kc.done || !vc.done) && ok) {
+                bool did = false;
+                if (!kc.done && k_ready()) { request_k(); did = true; }
+                if (!vc.done && v_ready()) { request_v(); did = true; }
+                if (did) { idle = 0; continue; }
+                if ((++idle & 1023u) == 0 && (*wc.abort_word || gave_up(wc.status))) ok = false;
+                if (idle >= wc.limit) {   // nothing could be requested for the whole wait limit
+                    *wc.abort_word = 1;
+                    report_timeout(wc.status, 1);
+                    ok = false;
+                }
             }
         }
-    } else if (warp >= 6 && warp < 10) {
-        // =============================== Q loaders: global -> registers -> TMEM ===============================
-        // One thread per query row (TMEM lane; a warp reaches the lane quarter warp % 4).  A row is 512 bytes: 32
-        // 16-byte loads, whose words are already what a TMEM column of a 16-bit A operand holds (two consecutive
-        // elements).  Rows past the end of the sequence are zeros.
-        const uint32_t quarter = warp & 3, r = quarter * 32 + lane;
-        const uint32_t t_q = tmem + ((quarter * 32) << 16) + kColQ;
-        bool ok = true;
-        uint32_t qi = 0;
-        for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
-            const uint32_t w = item_of_round(rnd);
-            if (w >= total_items) continue;
-            const Item it = get_item(w);
-            const bool live = it.q0 + r < it.len;
-            const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.q) +
-                                                               (((size_t)it.tok0 + it.q0 + r) * a.nh + it.h) * kD);
-            uint32_t v[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint4 u = live ? __ldg(src + c * 8 + i) : make_uint4(0, 0, 0, 0);
-                    v[c][4 * i] = u.x; v[c][4 * i + 1] = u.y; v[c][4 * i + 2] = u.z; v[c][4 * i + 3] = u.w;
-                }
-            // the previous item's last score MMA has read Q: the columns may be overwritten
-            if (qi > 0) ok = mbar_wait(bar(B_QEMPTY), (qi - 1) & 1, wc, 12);
-            if (!ok) break;
-            ++qi;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_st32(t_q + c * 32, v[c]);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(B_QFULL));
-        }
-    } else if (warp == 5 || warp == 11) {
+    } else if (warp == kWSEven || warp == kWSOdd) {
         // =============================== score-MMA issuers ===============================
-        // Three issuing threads, because one is not enough at this tile shape: the 16 small score MMAs, the 4 PV MMAs,
-        // four commits and three barrier waits of a 64-row K/V tile cost a single thread about twice the time the
-        // tensor pipe needs to execute them (a satisfied wait ~250 clocks, a commit ~80, an MMA issue that the pipe
-        // back-pressures 64).  This thread issues the score MMAs of the even tiles (S buffer 0), warp 11 those of the
-        // odd tiles (S buffer 1), warp 10 the PV MMAs; each commits its own.  An item has an even number of K/V tiles,
-        // so a tile's parity in the item is its parity in the CTA's running count.
-        // S(t) overwrites the buffer that held P(t-2): it waits for PV(t-2), which also keeps "S(t) complete" meaning
-        // "PV(t-2) complete" for the softmax threads.
         if (lane == 0) {
-            const uint32_t sb = warp == 5 ? 0u : 1u;
+            const uint32_t par = warp == kWSEven ? 0u : 1u;      // this thread's tiles: those whose running number has this parity
             const uint32_t idesc_qk = make_idesc(kFmt, false, kN);
+            const uint32_t qa = smem_base + Sh::kSmemQ;
             bool ok = true;
             uint32_t gk = 0, qi = 0, sc = 0;   // running counts: K/V tiles, items, score tiles
             for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
@@ -980,57 +1008,149 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 const Item it = get_item(w);
                 ok = mbar_wait(bar(B_QFULL), qi & 1, wc, 3);
                 ++qi;
-                for (uint32_t j = sb; j < it.nkv && ok; j += 2) {
-                    const uint32_t g = gk + j, t = sc + j, s = g % kKStages;
+                const uint32_t j0 = (par ^ sc) & 1u;
+                if (ok && j0 >= it.nkv) mbar_arrive(bar(B_QEMPTY));   // none in this item (one tile, the other thread's)
+                for (uint32_t j = j0; j < it.nkv && ok; j += 2) {
+                    const uint32_t g = gk + j, t = sc + j, s = g % kKStages, b = t % kNB;
                     ok = mbar_wait(bar(B_KFULL + s), (g / kKStages) & 1, wc, 4);
-                    if (ok && t >= 2) ok = mbar_wait(bar(B_PVDONE + sb), ((t >> 1) - 1) & 1, wc, 6);
+                    // S(t) lands where P(t - NB) lived: that PV must be complete
+                    if (ok && t >= (uint32_t)kNB) ok = mbar_wait(bar(B_PVDONE + b), ((t / kNB) - 1) & 1, wc, 6);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t kb = smem_base + kSmemK + s * kKvTile;
+                    const uint32_t kb = smem_base + Sh::kSmemK + s * kKvTile;
 #pragma unroll
-                    for (uint32_t ks = 0; ks < kD / 16; ++ks)      // S_sb = Q (TMEM) * K(slot s)^T
-                        mma_ts(tmem + kColS + sb * kN, tmem + kColQ + ks * 8, desc_kmajor(kb + (ks >> 2) * kKvSlab + (ks & 3) * 32),
-                               idesc_qk, ks > 0);
-                    tc_commit(bar(B_SFULL + sb));
-                    tc_commit(bar(B_KEMPTY + s));                  // the K slot is free as soon as this S is computed
-                    if (j + 2 >= it.nkv) tc_commit(bar(B_QEMPTY)); // this thread's last S of the item (Q is free when both have said so)
+                    for (uint32_t ks = 0; ks < kD / 16; ++ks) {      // S_b = Q * K(slot s)^T
+                        const uint32_t so = (ks >> 2), ko = (ks & 3) * 32;
+                        mma_ss(tmem + b * kN, desc_kmajor(qa + so * kQSlab + ko), desc_kmajor(kb + so * kKvSlab + ko), idesc_qk, ks > 0);
+                    }
+                    tc_commit(bar(B_SFULL + b));
+                    tc_commit(bar(B_KEMPTY + s));                    // the K slot is free as soon as this S is computed
+                    if (j + 2 >= it.nkv) tc_commit(bar(B_QEMPTY));   // this thread's last S of the item (Q is free when both have said so)
                 }
                 gk += it.nkv; sc += it.nkv;
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == kWPv) {
         // =============================== PV issuer ===============================
         if (lane == 0) {
             const uint32_t idesc_pv = make_idesc(kFmt, true, kD);
             bool ok = true;
-            uint32_t gk = 0, sc = 0;
+            uint32_t gk = 0, sc = 0, n_item = 0;
             for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
                 const uint32_t w = item_of_round(rnd);
                 if (w >= total_items) continue;
                 const Item it = get_item(w);
                 for (uint32_t j = 0; j < it.nkv && ok; ++j) {
-                    const uint32_t g = gk + j, t = sc + j, s = g % kVStages, sb = t & 1;
+                    const uint32_t g = gk + j, t = sc + j, s = g % kVStages, b = t % kNB;
                     ok = mbar_wait(bar(B_VFULL + s), (g / kVStages) & 1, wc, 5);
-                    if (ok) ok = mbar_wait(bar(B_PFULL + sb), (t >> 1) & 1, wc, 8);
+                    if (ok) ok = mbar_wait(bar(B_PFULL + b), (t / kNB) & 1, wc, 8);
+                    // the item's first PV overwrites O: the epilogue must have read the previous item's
+                    if (ok && j == 0 && n_item > 0) ok = mbar_wait(bar(B_OFREE), (n_item - 1) & 1, wc, 7);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t vb = smem_base + kSmemV + s * kKvTile;
+                    const uint32_t vb = smem_base + Sh::kSmemV + s * kKvTile;
 #pragma unroll
-                    for (uint32_t ks = 0; ks < kN / 16; ++ks)      // O (+)= P_sb * V(slot s)
-                        mma_ts(tmem + kColO, tmem + kColS + sb * kN + ks * 8, desc_mnmajor(vb + ks * 2048, kKvSlab), idesc_pv,
-                               j > 0 || ks > 0);
+                    for (uint32_t ks = 0; ks < kN / 16; ++ks)      // O (+)= P_b * V(slot s)
+                        mma_ts(tmem + kColO, tmem + b * kN + ks * 8, desc_mnmajor(vb + ks * 2048, kKvSlab), idesc_pv, j > 0 || ks > 0);
                     tc_commit(bar(B_VEMPTY + s));
-                    tc_commit(bar(B_PVDONE + sb));
+                    tc_commit(bar(B_PVDONE + b));
                     if (j + 1 == it.nkv) tc_commit(bar(B_OFULL));
                 }
-                gk += it.nkv; sc += it.nkv;
+                gk += it.nkv; sc += it.nkv; ++n_item;
             }
         }
-    } else if (warp < 4) {
+    } else if (warp >= kWEpi) {
+        // =============================== epilogue: O / l (x sigmoid(gate)) -> global ===============================
+        const uint32_t quarter = warp & 3, r = quarter * 32 + lane;    // row in the tile == TMEM lane
+        const uint32_t t_o = tmem + ((quarter * 32) << 16) + kColO;
+        bool ok = true;
+        uint32_t oc = 0;
+        for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
+            const uint32_t w = item_of_round(rnd);
+            if (w >= total_items) continue;
+            const Item item = get_item(w);
+            const uint32_t row = item.q0 + r;
+            // the row's sum(s), as the softmax thread(s) of this row posted them for item number oc (bounded spin)
+            float lw[NSW], lr[NSW];
+#pragma unroll
+            for (int xx = 0; xx < NSW; ++xx) {
+                const uint32_t slot = smem_base + Sh::kSmemLPair + 8 * (xx * 128 + r);
+                uint2 pr = lds_pair(slot);
+                for (uint32_t i = 0; pr.y != oc + 1 && i < wc.limit; ++i) {
+                    pr = lds_pair(slot);
+                    if ((i & 1023u) == 1023u && (*wc.abort_word || gave_up(wc.status))) break;
+                }
+                if (pr.y != oc + 1) {
+                    *wc.abort_word = 1;
+                    report_timeout(wc.status, 15);
+                    ok = false;
+                }
+                lw[xx] = __uint_as_float(pr.x);
+                lr[xx] = NSW == 2 ? reinterpret_cast<volatile float *>(smem + Sh::kSmemLRef)[xx * 128 + r] : 0.f;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            reinterpret_cast<volatile uint32_t *>(smem + Sh::kSmemAck)[r] = oc + 1;   // taken: the slots may be written again
+            float l_total;
+            if constexpr (NSW == 2) {   // each warpgroup's sum is relative to the reference it last used; the later (larger) one is O's
+                const float mfin = fmaxf(lr[0], lr[1]);
+                l_total = (lw[0] == 0.f ? 0.f : lw[0] * exp2f(lr[0] - mfin)) + (lw[1] == 0.f ? 0.f : lw[1] * exp2f(lr[1] - mfin));
+            } else {
+                l_total = lw[0];
+            }
+            const float inv = 1.0f / l_total;
+            ok = mbar_wait(bar(B_OFULL), oc & 1, wc, 11);
+            if (!ok) break;
+            tc_fence_after();
+            T *dst = reinterpret_cast<T *>(a.out) + (((size_t)item.tok0 + row) * a.nh + item.h) * kD;
+            const T *gate = (a.gate_src && row < item.len)
+                                ? reinterpret_cast<const T *>(a.gate_src) + (((size_t)item.tok0 + row) * a.nh + item.h) * a.gate_row + kD : nullptr;
+            // The row leaves TMEM first, scaled and packed to 16 bits (head_dim / 2 registers), so that O is free for the
+            // next item's first PV after a few hundred clocks; the stores (one row per thread: 32 separate lines per
+            // warp instruction, slow) follow, under the next item's MMAs.  With a gate, the row is held as fp32 x
+            // sigmoid(gate) rounded once, the gate words loaded while this thread waited for the item's last PV.
+            uint32_t pk[kD / 2];
+#pragma unroll
+            for (int c = 0; c < kD / 16; ++c) {   // 16 columns at a time: the packed row and one chunk are what is live
+                uint32_t v[16];
+                tmem_ld16(t_o + c * 16, v);
+                tmem_wait_ld();
+                if (c == kD / 16 - 1) {   // O is read: the next item's first PV may overwrite it
+                    tc_fence_before();
+                    mbar_arrive(bar(B_OFREE));
+                }
+                if (gate) {
+#pragma unroll
+                    for (int i = 0; i < 16; i += 8) {
+                        const uint4 g4 = __ldg(reinterpret_cast<const uint4 *>(gate + c * 16 + i));
+                        const T *ge = reinterpret_cast<const T *>(&g4);
+#pragma unroll
+                        for (int k = 0; k < 8; k += 2)
+                            pk[c * 8 + (i + k) / 2] = pack16<T>(__uint_as_float(v[i + k]) * inv * sigmoidf_ref(to_f32<T>(ge[k])),
+                                                                __uint_as_float(v[i + k + 1]) * inv * sigmoidf_ref(to_f32<T>(ge[k + 1])));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2)
+                        pk[c * 8 + i / 2] = pack16<T>(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                }
+            }
+            if (row < item.len) {
+#pragma unroll
+                for (int i = 0; i < kD / 8; ++i)
+                    reinterpret_cast<uint4 *>(dst)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+            }
+            ++oc;
+        }
+    }
+    } else {
+        if constexpr (NSW == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax2));
         // =============================== softmax (one thread per query row) ===============================
-        const uint32_t r = tid;                         // row in the tile == TMEM lane
-        const uint32_t lane_base = (warp * 32) << 16;
+        const uint32_t x = warp >> 2;                   // warpgroup (always 0 with one)
+        const uint32_t r = tid & 127;                   // row in the tile == TMEM lane
+        const uint32_t lane_base = ((warp & 3) * 32) << 16;
         const uint32_t t_o = tmem + lane_base + kColO;
+        const uint32_t mseq = smem_base + Sh::kSmemMSeq + 8 * r;
         bool ok = true;
         uint32_t sc = 0, oc = 0;                        // score tiles / items finished before the current item
         for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
@@ -1038,51 +1158,78 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             if (w >= total_items) continue;
             const Item item = get_item(w);
             const uint32_t row = item.q0 + r;           // global query row == its causal limit
-            float m_ref = -INFINITY, l_sum = 0.f;
-            for (uint32_t j = 0; j < item.nkv && ok; ++j) {
-                const uint32_t t = sc + j, sb = t & 1;
-                const uint32_t t_s = tmem + lane_base + kColS + sb * kN;
-                ok = mbar_wait(bar(B_SFULL + sb), (t >> 1) & 1, wc, 9);
+            float m_ref = -INFINITY, l_sum = 0.f, l_ref = -INFINITY;
+            for (uint32_t j = (NSW == 2 ? ((x ^ sc) & 1u) : 0u); j < item.nkv && ok; j += NSW) {
+                const uint32_t t = sc + j, b = t % kNB;
+                const uint32_t t_s = tmem + lane_base + b * kN;
+                ok = mbar_wait(bar(B_SFULL + b), (t / kNB) & 1, wc, 9);
                 if (!ok) break;
                 tc_fence_after();
-                // one tile of the online softmax; tiles that touch the diagonal (the item's last two) are a second
-                // instantiation, so the common path carries no mask code
+                // one tile of the online softmax; tiles that touch the diagonal are a second instantiation, so the
+                // common path carries no mask code
                 auto tile_body = [&](auto diag_c) {
                     constexpr bool diag = decltype(diag_c)::value;
                     const int lim = diag ? (int)row - (int)(j * kN) : kN - 1;   // columns 0..lim of this tile are visible
+                    // ---- row maximum.  64 columns stay in registers for the second pass; 128 are read again ----
                     uint32_t va[32], vb[32];
-                    tmem_ld32(t_s, va);
-                    tmem_ld32(t_s + 32, vb);
-                    tmem_wait_ld();
-                    float mx = -INFINITY;
-                    if (!diag || lim >= kN - 1) {
-                        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            m4[0] = max3(m4[0], __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
-                            m4[1] = max3(m4[1], __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
-                            m4[2] = max3(m4[2], __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
-                            m4[3] = max3(m4[3], __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
-                        }
-                        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-                    } else {
+                    for (int hb = 0; hb < kN / 64; ++hb) {
+                        tmem_ld32(t_s + hb * 64, va);
+                        tmem_ld32(t_s + hb * 64 + 32, vb);
+                        tmem_wait_ld();
+                        if (!diag || lim >= kN - 1) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            if (i <= lim) mx = fmaxf(mx, __uint_as_float(va[i]));
-                            if (32 + i <= lim) mx = fmaxf(mx, __uint_as_float(vb[i]));
+                            for (int i = 0; i < 32; i += 4) {
+                                m4[0] = max3(m4[0], __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
+                                m4[1] = max3(m4[1], __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
+                                m4[2] = max3(m4[2], __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
+                                m4[3] = max3(m4[3], __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                if (hb * 64 + i <= lim) m4[i & 1] = fmaxf(m4[i & 1], __uint_as_float(va[i]));
+                                if (hb * 64 + 32 + i <= lim) m4[2 + (i & 1)] = fmaxf(m4[2 + (i & 1)], __uint_as_float(vb[i]));
+                            }
                         }
                     }
-                    mx *= a.scale_log2;                      // scale > 0; -inf stays -inf (a row that sees nothing of this tile)
+                    // scale > 0; -inf stays -inf (a row that sees nothing of this tile)
+                    const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * a.scale_log2;
+                    if constexpr (NSW == 2) {   // the row's reference as tile t - 1 left it (bounded spin on shared memory)
+                        if (t > 0) {
+                            uint2 ms = lds_pair(mseq);
+                            for (uint32_t i = 0; ms.y != t && i < wc.limit; ++i) {
+                                ms = lds_pair(mseq);
+                                if ((i & 1023u) == 1023u && (*wc.abort_word || gave_up(wc.status))) break;
+                            }
+                            if (ms.y != t) {
+                                *wc.abort_word = 1;
+                                report_timeout(wc.status, 14);
+                                ok = false;
+                            }
+                            m_ref = __uint_as_float(ms.x);
+                        }
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) return;
+                    }
                     float corr = 1.f;
                     if (j == 0) m_ref = mx;                  // key 0 is visible to every row: finite
                     else if (mx > m_ref + kRescaleThreshold) { corr = exp2f(m_ref - mx); m_ref = mx; }
+                    if constexpr (NSW == 2) {
+                        sts_pair(mseq, __float_as_uint(m_ref), t + 1);
+                        // this warpgroup's row sum follows the reference (the other one's catches up at its next tile)
+                        if (l_ref != m_ref) { l_sum = l_sum == 0.f ? 0.f : l_sum * exp2f(l_ref - m_ref); l_ref = m_ref; }
+                    } else {
+                        l_sum *= corr;
+                        l_ref = m_ref;
+                    }
                     if (__any_sync(0xffffffffu, corr != 1.f)) {
-                        // O belongs to PV(t-1) until that MMA has completed; only a rescale has to wait for it (the
-                        // barrier of that parity completes next for PV(t+1), which needs this thread's P(t+1) first)
-                        ok = mbar_wait(bar(B_PVDONE + ((t - 1) & 1)), ((t - 1) >> 1) & 1, wc, 10);
+                        // O belongs to PV(t-1) until that MMA has completed; only a rescale has to wait for it (that
+                        // barrier completes next for PV(t-1+NB), which needs the P of a tile after this one first)
+                        ok = mbar_wait(bar(B_PVDONE + ((t - 1) % kNB)), ((t - 1) / kNB) & 1, wc, 10);
                         if (!ok) return;
                         tc_fence_after();
-                        l_sum *= corr;
 #pragma unroll
                         for (int c = 0; c < kD / 32; ++c) {
                             uint32_t v[32];
@@ -1093,27 +1240,42 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                             tmem_st32(t_o + c * 32, v);
                         }
                     }
-                    // P = exp2(s * scale - m_ref), masked past the diagonal; packed over the first 32 columns of S
+                    // ---- P = exp2(s * scale - m_ref), masked past the diagonal; packed over the first kN/2 columns of S ----
                     const float neg_m = -m_ref;
                     const unsigned long long scale2 = pack_f32x2(a.scale_log2, a.scale_log2), negm2 = pack_f32x2(neg_m, neg_m);
                     unsigned long long ls2[2] = {0ull, 0ull};
-                    uint32_t pk[32];
+                    // 32 columns -> 16 packed words; base = first column of the chunk
+                    auto exp_chunk = [&](const uint32_t (&v)[32], uint32_t (&pk)[16], int base) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float x0, x1, x2, x3;
-                        fma_f32x2(x0, x1, __uint_as_float(va[i]), __uint_as_float(va[i + 1]), scale2, negm2);
-                        fma_f32x2(x2, x3, __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]), scale2, negm2);
-                        float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
-                        if (diag) {
-                            if (i > lim) p0 = 0.f;
-                            if (i + 1 > lim) p1 = 0.f;
-                            if (32 + i > lim) p2 = 0.f;
-                            if (33 + i > lim) p3 = 0.f;
+                        for (int i = 0; i < 32; i += 2) {
+                            float x0, x1;
+                            fma_f32x2(x0, x1, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), scale2, negm2);
+                            float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                            if (diag) {
+                                if (base + i > lim) p0 = 0.f;
+                                if (base + i + 1 > lim) p1 = 0.f;
+                            }
+                            ls2[(i >> 1) & 1] = add_f32x2(ls2[(i >> 1) & 1], pack_f32x2(p0, p1));
+                            pk[i >> 1] = pack16<T>(p0, p1);
                         }
-                        ls2[0] = add_f32x2(ls2[0], pack_f32x2(p0, p1));
-                        ls2[1] = add_f32x2(ls2[1], pack_f32x2(p2, p3));
-                        pk[i >> 1] = pack16<T>(p0, p1);
-                        pk[16 + (i >> 1)] = pack16<T>(p2, p3);
+                    };
+                    if constexpr (kN == 64) {
+                        uint32_t pa[16], pb[16];
+                        exp_chunk(va, pa, 0);
+                        exp_chunk(vb, pb, 32);
+                        tmem_st16(t_s, pa);
+                        tmem_st16(t_s + 16, pb);
+                    } else {   // four chunks of 32 columns, the next one's load in flight under the current one's math
+                        uint32_t vbuf[2][32];
+                        tmem_ld32(t_s, vbuf[0]);
+#pragma unroll
+                        for (int c = 0; c < kN / 32; ++c) {
+                            tmem_wait_ld();
+                            if (c + 1 < kN / 32) tmem_ld32(t_s + (c + 1) * 32, vbuf[(c + 1) & 1]);
+                            uint32_t pk[16];
+                            exp_chunk(vbuf[c & 1], pk, c * 32);
+                            tmem_st16(t_s + c * 16, pk);
+                        }
                     }
                     {
                         float s0, s1, s2, s3;
@@ -1121,47 +1283,32 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         asm("mov.b64 {%0, %1}, %2;" : "=f"(s2), "=f"(s3) : "l"(ls2[1]));
                         l_sum += (s0 + s1) + (s2 + s3);
                     }
-                    tmem_st32(t_s, pk);
                     tmem_wait_st();
                     tc_fence_before();
-                    mbar_arrive(bar(B_PFULL + sb));
+                    mbar_arrive(bar(B_PFULL + b));
                 };
                 if ((j + 1) * kN - 1 > item.q0) tile_body(std::true_type{});
                 else tile_body(std::false_type{});
             }
-            // ---- epilogue: O / l (x sigmoid(gate)) -> global ----
-            if (ok) ok = mbar_wait(bar(B_OFULL), oc & 1, wc, 11);
+            // the item's row sum goes to the epilogue warps; this thread is free for the next item
             if (ok) {
-                tc_fence_after();
-                const float inv = 1.0f / l_sum;
-                T *dst = reinterpret_cast<T *>(a.out) + (((size_t)item.tok0 + row) * a.nh + item.h) * kD;
-                const T *gate = (a.gate_src && row < item.len)
-                                    ? reinterpret_cast<const T *>(a.gate_src) + (((size_t)item.tok0 + row) * a.nh + item.h) * a.gate_row + kD : nullptr;
-#pragma unroll
-                for (int c = 0; c < kD / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(t_o + c * 32, v);
-                    tmem_wait_ld();
-                    if (row < item.len) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            float f[8];
-#pragma unroll
-                            for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[i + k]) * inv;
-                            if (gate) {
-                                const uint4 g4 = *reinterpret_cast<const uint4 *>(gate + c * 32 + i);
-                                const T *ge = reinterpret_cast<const T *>(&g4);
-#pragma unroll
-                                for (int k = 0; k < 8; ++k) f[k] *= sigmoidf_ref(to_f32<T>(ge[k]));
-                            }
-                            uint4 o4;
-                            o4.x = pack16<T>(f[0], f[1]); o4.y = pack16<T>(f[2], f[3]);
-                            o4.z = pack16<T>(f[4], f[5]); o4.w = pack16<T>(f[6], f[7]);
-                            *reinterpret_cast<uint4 *>(dst + c * 32 + i) = o4;
-                        }
-                    }
+                // (the epilogue thread of this row must have taken the previous item's: bounded spin)
+                volatile uint32_t *ack = reinterpret_cast<volatile uint32_t *>(smem + Sh::kSmemAck) + r;
+                uint32_t got = *ack;
+                for (uint32_t i = 0; got < oc && i < wc.limit; ++i) {
+                    got = *ack;
+                    if ((i & 1023u) == 1023u && (*wc.abort_word || gave_up(wc.status))) break;
                 }
-                // the next item's first PV overwrites O: every row must have read it (the P barrier of that tile orders it)
+                if (got < oc) {
+                    *wc.abort_word = 1;
+                    report_timeout(wc.status, 16);
+                    ok = false;
+                }
+                if constexpr (NSW == 2) {
+                    reinterpret_cast<volatile float *>(smem + Sh::kSmemLRef)[x * 128 + r] = l_ref;
+                    __threadfence_block();
+                }
+                sts_pair(smem_base + Sh::kSmemLPair + 8 * (x * 128 + r), __float_as_uint(l_sum), oc + 1);
             }
             sc += item.nkv;
             ++oc;
@@ -1170,13 +1317,14 @@ prefill256_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     // ---- teardown ----
     tc_fence_before();
     __syncthreads();
-    if (warp == 4 && lane == 0 && *abort_word) {
-        for (int s = 0; s < p256::kKStages + p256::kVStages; ++s)
+    if (warp == kWProd && lane == 0 && *abort_word) {
+        // an aborted CTA may still have copies in flight: give them a bounded time to land before shared memory is handed back
+        for (int s = 0; s < kKStages + kVStages; ++s)
             for (uint32_t i = 0; i < (1u << 16); ++i)
-                if (mbar_try(bar(s < p256::kKStages ? p256::B_KFULL + s : p256::B_VFULL + (s - p256::kKStages)), 0)) break;
+                if (mbar_try(bar(s < kKStages ? B_KFULL + s : B_VFULL + (s - kKStages)), 0)) break;
     }
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kWSEven) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
@@ -1439,8 +1587,8 @@ static int launch_prefill_impl(shady_ctx *ctx, const char *who, const shady_pref
     return SHADY_OK;
 }
 
-// head_dim 256: Q [B][T][nh][256] already normed and rotated; gate_src (optional) the projection rows whose second
-// half is the gate
+// The row-tile kernel: Q [tokens][nh][hd] already normed and rotated; gate_src (optional) the projection rows whose
+// second half is the gate
 static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefill_params *p, const void *d_q,
                              const shady_kv_cache *cache, void *d_out, const void *gate_src, uint32_t gate_row,
                              const RaggedSetup *rs = nullptr) {
@@ -1452,7 +1600,9 @@ static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefil
                   w + ": bad shape");
     SHADY_REQUIRE(ctx, rs || (cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs && !cache->d_page_table), SHADY_ERR_UNSUPPORTED,
                   w + ": needs base + seq_stride cache addressing; pointer arrays and pages go through shady_attn_prefill_ragged");
-    SHADY_REQUIRE(ctx, rs || p->num_seqs == 1 || cache->seq_stride >= (uint64_t)p->seq_len * p->num_kv_heads * 256, SHADY_ERR_BAD_ARG,
+    const uint32_t hd = p->head_dim, kv_rows = 16384 / hd;
+    SHADY_REQUIRE(ctx, hd == 128 || hd == 256, SHADY_ERR_UNSUPPORTED, w + ": head_dim must be 128 or 256");
+    SHADY_REQUIRE(ctx, rs || p->num_seqs == 1 || cache->seq_stride >= (uint64_t)p->seq_len * p->num_kv_heads * hd, SHADY_ERR_BAD_ARG,
                   w + ": seq_stride smaller than one sequence");
     SHADY_REQUIRE(ctx, ((uintptr_t)d_q | (uintptr_t)d_out | (uintptr_t)gate_src) % 16 == 0 &&
                            (rs || (((uintptr_t)cache->d_k_base | (uintptr_t)cache->d_v_base) % 16 == 0 && (cache->seq_stride * 2) % 16 == 0)),
@@ -1460,42 +1610,56 @@ static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefil
     if (const int st = pending_timeout(ctx, who)) return st;
     const uint32_t B = p->num_seqs, T = p->seq_len, nh = p->num_q_heads, nkv = p->num_kv_heads;
     const CUtensorMapDataType dt = p->dtype == SHADY_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap mk, mv;
-    bool maps_ok = true;
+    CUtensorMap mq, mk, mv;
+    bool maps_ok;
     if (rs) {
+        const uint64_t toks = rs->lay.total_tokens;
+        maps_ok = make_map_4d(&mq, dt, d_q, hd, nh, toks, 1, hd * 2, (uint64_t)nh * hd * 2, toks * nh * hd * 2, 128);
         if (rs->pool_maps) { mk = rs->mk; mv = rs->mv; }
-        else { memset(&mk, 0, sizeof(mk)); memset(&mv, 0, sizeof(mv)); }   // unused: every sequence brings its own pair
+        else { mk = mq; mv = mq; }   // unused: every sequence brings its own pair
     } else {
-        const uint64_t seq_stride_b = (B == 1 ? (uint64_t)T * nkv * 256 : cache->seq_stride) * 2;
-        maps_ok = make_map_4d(&mk, dt, cache->d_k_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64) &&
-                  make_map_4d(&mv, dt, cache->d_v_base, 256, nkv, T, B, 256 * 2, (uint64_t)nkv * 256 * 2, seq_stride_b, 64);
+        const uint64_t seq_stride_b = (B == 1 ? (uint64_t)T * nkv * hd : cache->seq_stride) * 2;
+        maps_ok = make_map_4d(&mq, dt, d_q, hd, nh, T, B, hd * 2, (uint64_t)nh * hd * 2, (uint64_t)T * nh * hd * 2, 128) &&
+                  make_map_4d(&mk, dt, cache->d_k_base, hd, nkv, T, B, hd * 2, (uint64_t)nkv * hd * 2, seq_stride_b, kv_rows) &&
+                  make_map_4d(&mv, dt, cache->d_v_base, hd, nkv, T, B, hd * 2, (uint64_t)nkv * hd * 2, seq_stride_b, kv_rows);
     }
     SHADY_REQUIRE(ctx, maps_ok, SHADY_ERR_CUDA, w + ": cuTensorMapEncodeTiled failed");
-    Prefill256Args a{};
+    RowTileArgs a{};
     a.out = d_out; a.status = status_ref(ctx); a.wait_mbar = ctx->wait_mbar;
     a.B = B; a.T = T; a.nh = nh; a.nkv = nkv; a.G = nh / nkv;
     a.m_tiles = (T + 127) / 128;
     if (rs) a.rg = rs->rg;
-    a.scale_log2 = (1.0f / sqrtf(256.0f)) * 1.4426950408889634f;
-    a.gate_src = gate_src; a.gate_row = gate_row; a.q = d_q;
+    a.scale_log2 = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f;
+    a.gate_src = gate_src; a.gate_row = gate_row;
     const unsigned long long total_items = rs ? (unsigned long long)rs->rg.entries * nh : (unsigned long long)a.m_tiles * B * nh;
     SHADY_REQUIRE(ctx, total_items <= 0x7fffffffull, SHADY_ERR_UNSUPPORTED, w + ": too many tiles for one launch");
     const unsigned blocks = (unsigned)(total_items < (unsigned long long)ctx->num_sms ? total_items : (unsigned long long)ctx->num_sms);
     static thread_local int configured_dev = -1;
     if (configured_dev != ctx->device) {
-        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill256_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, p256::kSmem));
-        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(prefill256_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, p256::kSmem));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(rowtile_kernel<__nv_bfloat16, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, rt::Shape<256>::kSmem));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(rowtile_kernel<__half, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, rt::Shape<256>::kSmem));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(rowtile_kernel<__nv_bfloat16, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, rt::Shape<128>::kSmem));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(rowtile_kernel<__half, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, rt::Shape<128>::kSmem));
         configured_dev = ctx->device;
     }
-    if (p->dtype == SHADY_BF16) prefill256_kernel<__nv_bfloat16><<<blocks, p256::kThreads, p256::kSmem, ctx->stream>>>(mk, mv, a);
-    else prefill256_kernel<__half><<<blocks, p256::kThreads, p256::kSmem, ctx->stream>>>(mk, mv, a);
+    const bool bf = p->dtype == SHADY_BF16;
+    if (hd == 256) {
+        using Sh = rt::Shape<256>;
+        if (bf) rowtile_kernel<__nv_bfloat16, 256><<<blocks, Sh::kThreads, Sh::kSmem, ctx->stream>>>(mq, mk, mv, a);
+        else rowtile_kernel<__half, 256><<<blocks, Sh::kThreads, Sh::kSmem, ctx->stream>>>(mq, mk, mv, a);
+    } else {
+        using Sh = rt::Shape<128>;
+        if (bf) rowtile_kernel<__nv_bfloat16, 128><<<blocks, Sh::kThreads, Sh::kSmem, ctx->stream>>>(mq, mk, mv, a);
+        else rowtile_kernel<__half, 128><<<blocks, Sh::kThreads, Sh::kSmem, ctx->stream>>>(mq, mk, mv, a);
+    }
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
 }
 
 int launch_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_q, const shady_kv_cache *cache, void *d_out) {
-    if (p && p->head_dim == 256) return launch_prefill256(ctx, "attn_prefill", p, d_q, cache, d_out, nullptr, 0);
+    if (p && (p->head_dim == 256 || (ctx->knobs.prefill_variant == 1 && p->head_dim == 128)))
+        return launch_prefill256(ctx, "attn_prefill", p, d_q, cache, d_out, nullptr, 0);
     return launch_prefill_impl(ctx, "attn_prefill", p, d_q, 128, cache, d_out, nullptr);
 }
 
