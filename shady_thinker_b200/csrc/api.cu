@@ -184,7 +184,6 @@ int shady_ctx_create(int device, void *stream, shady_ctx **out) {
     c->knobs.min_span = env_u32("SHADY_DECODE_MIN_SPAN", 0);
     c->knobs.grid_merge = env_u32("SHADY_DECODE_GRID_MERGE", 1);
     c->knobs.interleave = env_u32("SHADY_DECODE_INTERLEAVE", 1);
-    c->knobs.prefill_variant = env_u32("SHADY_PREFILL_VARIANT", 0);
     *out = c;
     return SHADY_OK;
 }

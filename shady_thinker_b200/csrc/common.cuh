@@ -19,7 +19,6 @@ struct DecodeKnobs {
     uint32_t min_span = 0;      // SHADY_DECODE_MIN_SPAN: smallest span in 16-row blocks
     uint32_t grid_merge = 1;    // SHADY_DECODE_GRID_MERGE=0: merge many-span sequences in a second launch
     uint32_t interleave = 1;    // SHADY_DECODE_INTERLEAVE=0: fixed spans for a single long sequence
-    uint32_t prefill_variant = 0;   // SHADY_PREFILL_VARIANT
 };
 
 struct shady_ctx {

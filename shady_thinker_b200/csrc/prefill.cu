@@ -790,58 +790,48 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
 
 // =====================================================================================================
-// Row-tile kernel: one 128-row Q tile per item, K/V tiles of 32 KB (64 rows at head_dim 256, 128 rows at 128).
+// Row-tile kernel (head_dim 256, the gated-attention layer shape): one 128-row Q tile per item, K/V tiles of 64 rows.
 //
-// head_dim 256 is the gated-attention layer shape.  S + O of two 128-row tiles would need 768 TMEM columns there, so
-// an item is ONE row tile and the depth of the pipeline comes from the score buffers instead: O takes head_dim TMEM
-// columns, the other 256 (head_dim 256: four buffers of 64 columns) or 384 (head_dim 128: three of 128) hold the
-// scores of consecutive K/V tiles.  P overwrites the first half of its own S buffer and is the A operand of the PV MMA
-// straight from TMEM, so a buffer goes through S -> softmax -> PV before the next S may land in it; with three or
+// S + O of two 128-row tiles would need 768 TMEM columns at this head_dim, so an item is ONE row tile and the depth of
+// the pipeline comes from the score buffers instead: O takes 256 TMEM columns, the other 256 hold the scores of four
+// consecutive K/V tiles (64 columns each).  P overwrites the first half of its own S buffer and is the A operand of
+// the PV MMA straight from TMEM, so a buffer goes through S -> softmax -> PV before the next S may land in it; with
 // four buffers that chain (about 4,000 clocks) is no longer what the tile rate waits for.
-//   * Shared memory: Q (one buffer, TMA), three K tiles and two V tiles in rings of their own — a K slot is free as
-//     soon as its S is computed, a V slot only after its PV, so K runs ahead of V.
-//   * Three MMA-issuing threads, because one is not enough at these tile shapes: a satisfied barrier wait costs a
-//     thread ~250 clocks, a commit ~80, an MMA issue that the pipe back-pressures 64, and the waits, commits and
-//     issues of one K/V tile add up to about twice the time the tensor pipe needs to execute its MMAs.  Two threads
-//     issue the score MMAs (tiles of even / odd running number), one the PV MMAs; each commits its own.  MMAs of
-//     different threads are not ordered among themselves, so what must be ordered goes through barriers: S(t) waits
-//     for PV(t - NB) (its buffer), the first PV of an item for the epilogue's reads of O.
-//   * Softmax: one thread per row.  head_dim 256: one warpgroup, 64 scores per tile in registers.  head_dim 128: two
-//     warpgroups take alternate tiles (two passes over 128 scores each), so that one tile's exponentials run under the
-//     other's loads and maxima.  What stays sequential is each row's running maximum: the thread that takes tile t
-//     reads {maximum, t} as the other warpgroup's thread left it after tile t - 1, decides (keep the reference, or
-//     move it and rescale O) and publishes {maximum, t + 1} before its long pass.  Each warpgroup sums its own
-//     tiles' row sums relative to the reference it last used; the epilogue brings the two together.
-//   * Four epilogue warps drain O (x 1/l, x sigmoid(gate)) while the softmax warps are already in the next item.
-// Warps: 4 per softmax warpgroup, then TMA producer, score issuer (even tiles; TMEM owner), PV issuer, score issuer
-// (odd tiles), four epilogue warps.
+//   * Shared memory: Q (one buffer of 64 KB, TMA), three K tiles and two V tiles of 32 KB in rings of their own — a K
+//     slot is free as soon as its S is computed, a V slot only after its PV, so K runs ahead of V.
+//   * Three MMA-issuing threads, because one is not enough at this tile shape: a satisfied barrier wait costs a thread
+//     ~250 clocks, a commit ~80, an MMA issue that the pipe back-pressures 64 (the N = 64 score MMAs run at half
+//     rate), and the waits, commits and issues of one K/V tile add up to about twice the time the tensor pipe needs to
+//     execute its MMAs.  Two threads issue the score MMAs (tiles of even / odd running number), one the PV MMAs; each
+//     commits its own.  MMAs of different threads are not ordered among themselves, so what must be ordered goes
+//     through barriers: S(t) waits for PV(t - 4) (its buffer), the first PV of an item for the epilogue's reads of O.
+//   * Softmax: one warpgroup, one thread per row, the 64 scores of a tile in registers (one pass over TMEM).
+//   * Four epilogue warps drain O (x 1/l, x sigmoid(gate)) while the softmax warps are already in the next item; the
+//     row sum travels through a shared-memory word with the item's number in it.
+// Warps 0-3 softmax, 4 TMA producer, 5 score issuer (even tiles; TMEM owner), 6 PV issuer, 7 score issuer (odd tiles),
+// 8-11 epilogue.
+// The same kernel was also built for head_dim 128 (128-row K/V tiles, three score buffers, two softmax warpgroups on
+// alternate tiles with the rows' running maxima handed over through shared memory, two Q buffers); it reached 953
+// TFLOP/s at T = 4096 where the two-tile kernel above gives 1,000, so head_dim 128 stays there.
 // =====================================================================================================
 namespace rt {
-constexpr int kM = 128, kKStages = 3, kVStages = 2;
-constexpr uint32_t kKvTile = 32768;             // a K or V tile: 64 rows of 256 elements or 128 rows of 128, as [rows][64]-element slabs
-constexpr uint32_t kRegsSoftmax2 = 160, kRegsOther2 = 96;   // two softmax warpgroups: 256 x 160 + 256 x 96 = 65,536 registers
+constexpr int kM = 128, kD = 256, kN = 64, kNB = 4, kKStages = 3, kVStages = 2, kSlabs = kD / 64;
+constexpr uint32_t kKvSlab = kN * 128;          // [64 rows][64 elements] 16-bit
+constexpr uint32_t kKvTile = kSlabs * kKvSlab;  // a K or V tile: 32 KB
+constexpr uint32_t kQSlab = 128 * 128;          // [128 rows][64 elements]
+constexpr uint32_t kQBytes = kSlabs * kQSlab;   // 64 KB
 enum { B_QFULL = 0, B_QEMPTY = 1, B_KFULL = 2, B_KEMPTY = 5, B_VFULL = 8, B_VEMPTY = 10, B_SFULL = 12, B_PFULL = 16, B_PVDONE = 20,
        B_OFULL = 24, B_OFREE = 25, B_COUNT = 26 };
-template <int D> struct Shape {
-    static constexpr int kN = 16384 / D;                  // K/V rows per tile
-    static constexpr int kNB = D == 128 ? 3 : 4;          // score buffers in TMEM
-    static constexpr int kNSW = D == 128 ? 2 : 1;         // softmax warpgroups
-    static constexpr uint32_t kQSlab = 128 * 128;         // [128 rows][64 elements] 16-bit
-    static constexpr uint32_t kQBytes = (D / 64) * kQSlab;
-    static constexpr uint32_t kKvSlab = kN * 128;         // [kN rows][64 elements]
-    static constexpr uint32_t kSmemQ = 0, kSmemK = kQBytes, kSmemV = kSmemK + kKStages * kKvTile, kSmemBar = kSmemV + kVStages * kKvTile;
-    // Words the softmax and epilogue threads of a row hand each other (8-byte pairs written and read as units, each
-    // with a running number so that the reader knows what it has): {running maximum, tile number} of the row's last
-    // decision (two warpgroups only); per warpgroup {row sum of the item, item number + 1} and the maximum that sum is
-    // relative to (two warpgroups only); the number of items whose sums the epilogue thread has taken.
-    static constexpr uint32_t kSmemMSeq = kSmemBar + 256, kSmemLPair = kSmemMSeq + (kNSW == 2 ? 128 * 8 : 0);
-    static constexpr uint32_t kSmemLRef = kSmemLPair + kNSW * 128 * 8, kSmemAck = kSmemLRef + (kNSW == 2 ? 2 * 128 * 4 : 0);
-    static constexpr uint32_t kSmem = kSmemAck + 128 * 4 + 1024;
-    static constexpr uint32_t kColO = kNB * kN;           // TMEM: S buffers [0, kNB * kN), then O; P_b = first kN / 2 columns of S_b
-    static constexpr uint32_t kThreads = 128 * kNSW + 256;
-    static_assert(kColO + D <= kTmemCols, "the score buffers and O must fit in TMEM");
-    static_assert(kSmem <= 232448, "Q and the K and V rings must fit in 227 KB");
-};
+constexpr uint32_t kSmemQ0 = 0, kSmemK = kQBytes, kSmemV = kSmemK + kKStages * kKvTile, kSmemBar = kSmemV + kVStages * kKvTile;
+// Words the softmax and the epilogue thread of a row hand each other: {row sum of the item, item number + 1} (an
+// 8-byte pair written and read as a unit, the number telling the reader what it has) and the number of items whose
+// sum the epilogue thread has taken.
+constexpr uint32_t kSmemLPair = kSmemBar + 256, kSmemAck = kSmemLPair + 128 * 8;
+constexpr uint32_t kSmem = kSmemAck + 128 * 4 + 1024;
+constexpr uint32_t kColO = kNB * kN;            // TMEM: S buffers [0, 256), then O [256, 512); P_b = first 32 columns of S_b
+constexpr uint32_t kThreads = 384;
+static_assert(kColO + kD <= kTmemCols, "the score buffers and O must fit in TMEM");
+static_assert(kSmem <= 232448, "Q and the K and V rings must fit in 227 KB");
 }  // namespace rt
 
 struct RowTileArgs {
@@ -855,21 +845,18 @@ struct RowTileArgs {
     uint32_t gate_row;
 };
 
-template <typename T, int kD>
-__global__ void __launch_bounds__(rt::Shape<kD>::kThreads, 1)
+template <typename T>
+__global__ void __launch_bounds__(rt::kThreads, 1)
 rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const RowTileArgs a) {
     using namespace rt;
-    using Sh = Shape<kD>;
-    constexpr int kN = Sh::kN, kNB = Sh::kNB, NSW = Sh::kNSW, kSlabs = kD / 64;
-    constexpr uint32_t kKvSlab = Sh::kKvSlab, kQSlab = Sh::kQSlab, kColO = Sh::kColO;
-    constexpr uint32_t kWProd = 4 * NSW, kWSEven = kWProd + 1, kWPv = kWProd + 2, kWSOdd = kWProd + 3, kWEpi = kWProd + 4;
+    constexpr uint32_t kWProd = 4, kWSEven = 5, kWPv = 6, kWSOdd = 7, kWEpi = 8;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *smem = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t bar0 = smem_base + Sh::kSmemBar;
+    const uint32_t bar0 = smem_base + kSmemBar;
     auto bar = [&](int i) { return bar0 + 8u * i; };
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + Sh::kSmemBar + 8 * B_COUNT);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + kSmemBar + 8 * B_COUNT);
     volatile uint32_t *abort_word = tmem_slot + 1;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (gave_up(a.status)) return;
@@ -909,9 +896,8 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < 128) {   // nothing decided, posted or taken yet
-        if (NSW == 2) sts_pair(smem_base + Sh::kSmemMSeq + 8 * tid, 0u, 0u);
-        for (int xx = 0; xx < NSW; ++xx) sts_pair(smem_base + Sh::kSmemLPair + 8 * (xx * 128 + tid), 0u, 0u);
-        reinterpret_cast<volatile uint32_t *>(smem + Sh::kSmemAck)[tid] = 0u;
+        sts_pair(smem_base + kSmemLPair + 8 * tid, 0u, 0u);
+        reinterpret_cast<volatile uint32_t *>(smem + kSmemAck)[tid] = 0u;
     }
     if (warp == kWSEven) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_slot)), "r"(kTmemCols) : "memory");
@@ -922,10 +908,6 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    // two softmax warpgroups leave 128 registers per thread at launch: they take registers from the other warps
-    // (the instruction sits inside the branch it applies to, which is what lets the compiler use the larger budget there)
-    if (warp >= kWProd) {
-    if constexpr (NSW == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther2));
     if (warp == kWProd) {
         // =============================== TMA producer ===============================
         // Two cursors walk the item list, one requesting K tiles (and each item's Q ahead of its first K), one V tiles.
@@ -957,16 +939,16 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 return vc.g < (uint32_t)kVStages || mbar_try(bar(B_VEMPTY + vc.g % kVStages), ((vc.g / kVStages) & 1) ^ 1);
             };
             auto request_k = [&]() {
-                if (kc.j == 0) {   // the item's Q, once both score issuers are done with the previous item's
+                if (kc.j == 0) {   // the item's Q (both score issuers are done with the previous item's)
                     ++qi;
-                    mbar_expect_tx(bar(B_QFULL), Sh::kQBytes);
+                    mbar_expect_tx(bar(B_QFULL), kQBytes);
                     for (int c = 0; c < kSlabs; ++c)
-                        tma_load_4d(smem_base + Sh::kSmemQ + c * kQSlab, &map_q, bar(B_QFULL), 64 * c, (int)kc.it.h, (int)kc.it.qrow, (int)kc.it.qseq);
+                        tma_load_4d(smem_base + kSmemQ0 + c * kQSlab, &map_q, bar(B_QFULL), 64 * c, (int)kc.it.h, (int)kc.it.qrow, (int)kc.it.qseq);
                     if (a.rg.kv_maps) { kc.map = a.rg.kv_maps + 2 * kc.it.b; tensormap_acquire(kc.map); }
                 }
                 const uint32_t s = kc.g % kKStages;
                 mbar_expect_tx(bar(B_KFULL + s), kKvTile);
-                tma_load_kv_tile<kN, kSlabs>(smem_base + Sh::kSmemK + s * kKvTile, kKvSlab, kc.map, bar(B_KFULL + s), a.rg, kc.it.b, kc.it.kvh,
+                tma_load_kv_tile<kN, kSlabs>(smem_base + kSmemK + s * kKvTile, kKvSlab, kc.map, bar(B_KFULL + s), a.rg, kc.it.b, kc.it.kvh,
                                              kc.j * kN, kc.it.len, a.rg.kv_maps != nullptr);
                 ++kc.g;
                 advance(kc);
@@ -975,7 +957,7 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (vc.j == 0 && a.rg.kv_maps) { vc.map = a.rg.kv_maps + 2 * vc.it.b + 1; tensormap_acquire(vc.map); }
                 const uint32_t s = vc.g % kVStages;
                 mbar_expect_tx(bar(B_VFULL + s), kKvTile);
-                tma_load_kv_tile<kN, kSlabs>(smem_base + Sh::kSmemV + s * kKvTile, kKvSlab, vc.map, bar(B_VFULL + s), a.rg, vc.it.b, vc.it.kvh,
+                tma_load_kv_tile<kN, kSlabs>(smem_base + kSmemV + s * kKvTile, kKvSlab, vc.map, bar(B_VFULL + s), a.rg, vc.it.b, vc.it.kvh,
                                              vc.j * kN, vc.it.len, a.rg.kv_maps != nullptr);
                 ++vc.g;
                 advance(vc);
@@ -999,17 +981,16 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (lane == 0) {
             const uint32_t par = warp == kWSEven ? 0u : 1u;      // this thread's tiles: those whose running number has this parity
             const uint32_t idesc_qk = make_idesc(kFmt, false, kN);
-            const uint32_t qa = smem_base + Sh::kSmemQ;
             bool ok = true;
             uint32_t gk = 0, qi = 0, sc = 0;   // running counts: K/V tiles, items, score tiles
             for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
                 const uint32_t w = item_of_round(rnd);
                 if (w >= total_items) continue;
                 const Item it = get_item(w);
+                const uint32_t qa = smem_base + kSmemQ0;
                 ok = mbar_wait(bar(B_QFULL), qi & 1, wc, 3);
                 ++qi;
-                const uint32_t j0 = (par ^ sc) & 1u;
-                if (ok && j0 >= it.nkv) mbar_arrive(bar(B_QEMPTY));   // none in this item (one tile, the other thread's)
+                const uint32_t j0 = (par ^ sc) & 1u;   // (an item has an even number of tiles, so both threads have some)
                 for (uint32_t j = j0; j < it.nkv && ok; j += 2) {
                     const uint32_t g = gk + j, t = sc + j, s = g % kKStages, b = t % kNB;
                     ok = mbar_wait(bar(B_KFULL + s), (g / kKStages) & 1, wc, 4);
@@ -1017,7 +998,7 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (ok && t >= (uint32_t)kNB) ok = mbar_wait(bar(B_PVDONE + b), ((t / kNB) - 1) & 1, wc, 6);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t kb = smem_base + Sh::kSmemK + s * kKvTile;
+                    const uint32_t kb = smem_base + kSmemK + s * kKvTile;
 #pragma unroll
                     for (uint32_t ks = 0; ks < kD / 16; ++ks) {      // S_b = Q * K(slot s)^T
                         const uint32_t so = (ks >> 2), ko = (ks & 3) * 32;
@@ -1048,7 +1029,7 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (ok && j == 0 && n_item > 0) ok = mbar_wait(bar(B_OFREE), (n_item - 1) & 1, wc, 7);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t vb = smem_base + Sh::kSmemV + s * kKvTile;
+                    const uint32_t vb = smem_base + kSmemV + s * kKvTile;
 #pragma unroll
                     for (uint32_t ks = 0; ks < kN / 16; ++ks)      // O (+)= P_b * V(slot s)
                         mma_ts(tmem + kColO, tmem + b * kN + ks * 8, desc_mnmajor(vb + ks * 2048, kKvSlab), idesc_pv, j > 0 || ks > 0);
@@ -1070,11 +1051,10 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (w >= total_items) continue;
             const Item item = get_item(w);
             const uint32_t row = item.q0 + r;
-            // the row's sum(s), as the softmax thread(s) of this row posted them for item number oc (bounded spin)
-            float lw[NSW], lr[NSW];
-#pragma unroll
-            for (int xx = 0; xx < NSW; ++xx) {
-                const uint32_t slot = smem_base + Sh::kSmemLPair + 8 * (xx * 128 + r);
+            // the row's sum, as the softmax thread of this row posted it for item number oc (bounded spin)
+            float l_total;
+            {
+                const uint32_t slot = smem_base + kSmemLPair + 8 * r;
                 uint2 pr = lds_pair(slot);
                 for (uint32_t i = 0; pr.y != oc + 1 && i < wc.limit; ++i) {
                     pr = lds_pair(slot);
@@ -1085,19 +1065,11 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     report_timeout(wc.status, 15);
                     ok = false;
                 }
-                lw[xx] = __uint_as_float(pr.x);
-                lr[xx] = NSW == 2 ? reinterpret_cast<volatile float *>(smem + Sh::kSmemLRef)[xx * 128 + r] : 0.f;
+                l_total = __uint_as_float(pr.x);
             }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            reinterpret_cast<volatile uint32_t *>(smem + Sh::kSmemAck)[r] = oc + 1;   // taken: the slots may be written again
-            float l_total;
-            if constexpr (NSW == 2) {   // each warpgroup's sum is relative to the reference it last used; the later (larger) one is O's
-                const float mfin = fmaxf(lr[0], lr[1]);
-                l_total = (lw[0] == 0.f ? 0.f : lw[0] * exp2f(lr[0] - mfin)) + (lw[1] == 0.f ? 0.f : lw[1] * exp2f(lr[1] - mfin));
-            } else {
-                l_total = lw[0];
-            }
+            reinterpret_cast<volatile uint32_t *>(smem + kSmemAck)[r] = oc + 1;   // taken: the slot may be written again
             const float inv = 1.0f / l_total;
             ok = mbar_wait(bar(B_OFULL), oc & 1, wc, 11);
             if (!ok) break;
@@ -1142,15 +1114,11 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             }
             ++oc;
         }
-    }
     } else {
-        if constexpr (NSW == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax2));
         // =============================== softmax (one thread per query row) ===============================
-        const uint32_t x = warp >> 2;                   // warpgroup (always 0 with one)
-        const uint32_t r = tid & 127;                   // row in the tile == TMEM lane
-        const uint32_t lane_base = ((warp & 3) * 32) << 16;
+        const uint32_t r = tid;                         // row in the tile == TMEM lane
+        const uint32_t lane_base = (warp * 32) << 16;
         const uint32_t t_o = tmem + lane_base + kColO;
-        const uint32_t mseq = smem_base + Sh::kSmemMSeq + 8 * r;
         bool ok = true;
         uint32_t sc = 0, oc = 0;                        // score tiles / items finished before the current item
         for (uint32_t rnd = 0; rnd * gridDim.x < total_items && ok; ++rnd) {
@@ -1158,8 +1126,8 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (w >= total_items) continue;
             const Item item = get_item(w);
             const uint32_t row = item.q0 + r;           // global query row == its causal limit
-            float m_ref = -INFINITY, l_sum = 0.f, l_ref = -INFINITY;
-            for (uint32_t j = (NSW == 2 ? ((x ^ sc) & 1u) : 0u); j < item.nkv && ok; j += NSW) {
+            float m_ref = -INFINITY, l_sum = 0.f;
+            for (uint32_t j = 0; j < item.nkv && ok; ++j) {
                 const uint32_t t = sc + j, b = t % kNB;
                 const uint32_t t_s = tmem + lane_base + b * kN;
                 ok = mbar_wait(bar(B_SFULL + b), (t / kNB) & 1, wc, 9);
@@ -1170,60 +1138,33 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 auto tile_body = [&](auto diag_c) {
                     constexpr bool diag = decltype(diag_c)::value;
                     const int lim = diag ? (int)row - (int)(j * kN) : kN - 1;   // columns 0..lim of this tile are visible
-                    // ---- row maximum.  64 columns stay in registers for the second pass; 128 are read again ----
+                    // ---- row maximum; the 64 scores stay in registers for the second pass ----
                     uint32_t va[32], vb[32];
+                    tmem_ld32(t_s, va);
+                    tmem_ld32(t_s + 32, vb);
+                    tmem_wait_ld();
                     float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    if (!diag || lim >= kN - 1) {
 #pragma unroll
-                    for (int hb = 0; hb < kN / 64; ++hb) {
-                        tmem_ld32(t_s + hb * 64, va);
-                        tmem_ld32(t_s + hb * 64 + 32, vb);
-                        tmem_wait_ld();
-                        if (!diag || lim >= kN - 1) {
+                        for (int i = 0; i < 32; i += 4) {
+                            m4[0] = max3(m4[0], __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
+                            m4[1] = max3(m4[1], __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
+                            m4[2] = max3(m4[2], __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
+                            m4[3] = max3(m4[3], __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
+                        }
+                    } else {
 #pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                m4[0] = max3(m4[0], __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
-                                m4[1] = max3(m4[1], __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
-                                m4[2] = max3(m4[2], __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
-                                m4[3] = max3(m4[3], __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                if (hb * 64 + i <= lim) m4[i & 1] = fmaxf(m4[i & 1], __uint_as_float(va[i]));
-                                if (hb * 64 + 32 + i <= lim) m4[2 + (i & 1)] = fmaxf(m4[2 + (i & 1)], __uint_as_float(vb[i]));
-                            }
+                        for (int i = 0; i < 32; ++i) {
+                            if (i <= lim) m4[i & 1] = fmaxf(m4[i & 1], __uint_as_float(va[i]));
+                            if (32 + i <= lim) m4[2 + (i & 1)] = fmaxf(m4[2 + (i & 1)], __uint_as_float(vb[i]));
                         }
                     }
                     // scale > 0; -inf stays -inf (a row that sees nothing of this tile)
                     const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * a.scale_log2;
-                    if constexpr (NSW == 2) {   // the row's reference as tile t - 1 left it (bounded spin on shared memory)
-                        if (t > 0) {
-                            uint2 ms = lds_pair(mseq);
-                            for (uint32_t i = 0; ms.y != t && i < wc.limit; ++i) {
-                                ms = lds_pair(mseq);
-                                if ((i & 1023u) == 1023u && (*wc.abort_word || gave_up(wc.status))) break;
-                            }
-                            if (ms.y != t) {
-                                *wc.abort_word = 1;
-                                report_timeout(wc.status, 14);
-                                ok = false;
-                            }
-                            m_ref = __uint_as_float(ms.x);
-                        }
-                        ok = __all_sync(0xffffffffu, ok);
-                        if (!ok) return;
-                    }
                     float corr = 1.f;
                     if (j == 0) m_ref = mx;                  // key 0 is visible to every row: finite
                     else if (mx > m_ref + kRescaleThreshold) { corr = exp2f(m_ref - mx); m_ref = mx; }
-                    if constexpr (NSW == 2) {
-                        sts_pair(mseq, __float_as_uint(m_ref), t + 1);
-                        // this warpgroup's row sum follows the reference (the other one's catches up at its next tile)
-                        if (l_ref != m_ref) { l_sum = l_sum == 0.f ? 0.f : l_sum * exp2f(l_ref - m_ref); l_ref = m_ref; }
-                    } else {
-                        l_sum *= corr;
-                        l_ref = m_ref;
-                    }
+                    l_sum *= corr;
                     if (__any_sync(0xffffffffu, corr != 1.f)) {
                         // O belongs to PV(t-1) until that MMA has completed; only a rescale has to wait for it (that
                         // barrier completes next for PV(t-1+NB), which needs the P of a tile after this one first)
@@ -1259,24 +1200,11 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                             pk[i >> 1] = pack16<T>(p0, p1);
                         }
                     };
-                    if constexpr (kN == 64) {
-                        uint32_t pa[16], pb[16];
-                        exp_chunk(va, pa, 0);
-                        exp_chunk(vb, pb, 32);
-                        tmem_st16(t_s, pa);
-                        tmem_st16(t_s + 16, pb);
-                    } else {   // four chunks of 32 columns, the next one's load in flight under the current one's math
-                        uint32_t vbuf[2][32];
-                        tmem_ld32(t_s, vbuf[0]);
-#pragma unroll
-                        for (int c = 0; c < kN / 32; ++c) {
-                            tmem_wait_ld();
-                            if (c + 1 < kN / 32) tmem_ld32(t_s + (c + 1) * 32, vbuf[(c + 1) & 1]);
-                            uint32_t pk[16];
-                            exp_chunk(vbuf[c & 1], pk, c * 32);
-                            tmem_st16(t_s + c * 16, pk);
-                        }
-                    }
+                    uint32_t pa[16], pb[16];
+                    exp_chunk(va, pa, 0);
+                    exp_chunk(vb, pb, 32);
+                    tmem_st16(t_s, pa);
+                    tmem_st16(t_s + 16, pb);
                     {
                         float s0, s1, s2, s3;
                         asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(ls2[0]));
@@ -1293,7 +1221,7 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // the item's row sum goes to the epilogue warps; this thread is free for the next item
             if (ok) {
                 // (the epilogue thread of this row must have taken the previous item's: bounded spin)
-                volatile uint32_t *ack = reinterpret_cast<volatile uint32_t *>(smem + Sh::kSmemAck) + r;
+                volatile uint32_t *ack = reinterpret_cast<volatile uint32_t *>(smem + kSmemAck) + r;
                 uint32_t got = *ack;
                 for (uint32_t i = 0; got < oc && i < wc.limit; ++i) {
                     got = *ack;
@@ -1304,11 +1232,7 @@ rowtile_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     report_timeout(wc.status, 16);
                     ok = false;
                 }
-                if constexpr (NSW == 2) {
-                    reinterpret_cast<volatile float *>(smem + Sh::kSmemLRef)[x * 128 + r] = l_ref;
-                    __threadfence_block();
-                }
-                sts_pair(smem_base + Sh::kSmemLPair + 8 * (x * 128 + r), __float_as_uint(l_sum), oc + 1);
+                sts_pair(smem_base + kSmemLPair + 8 * r, __float_as_uint(l_sum), oc + 1);
             }
             sc += item.nkv;
             ++oc;
@@ -1587,8 +1511,8 @@ static int launch_prefill_impl(shady_ctx *ctx, const char *who, const shady_pref
     return SHADY_OK;
 }
 
-// The row-tile kernel: Q [tokens][nh][hd] already normed and rotated; gate_src (optional) the projection rows whose
-// second half is the gate
+// head_dim 256 (the row-tile kernel): Q [tokens][nh][256] already normed and rotated; gate_src (optional) the
+// projection rows whose second half is the gate
 static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefill_params *p, const void *d_q,
                              const shady_kv_cache *cache, void *d_out, const void *gate_src, uint32_t gate_row,
                              const RaggedSetup *rs = nullptr) {
@@ -1600,8 +1524,7 @@ static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefil
                   w + ": bad shape");
     SHADY_REQUIRE(ctx, rs || (cache->d_k_base && cache->d_v_base && !cache->d_k_ptrs && !cache->d_page_table), SHADY_ERR_UNSUPPORTED,
                   w + ": needs base + seq_stride cache addressing; pointer arrays and pages go through shady_attn_prefill_ragged");
-    const uint32_t hd = p->head_dim, kv_rows = 16384 / hd;
-    SHADY_REQUIRE(ctx, hd == 128 || hd == 256, SHADY_ERR_UNSUPPORTED, w + ": head_dim must be 128 or 256");
+    const uint32_t hd = 256, kv_rows = rt::kN;
     SHADY_REQUIRE(ctx, rs || p->num_seqs == 1 || cache->seq_stride >= (uint64_t)p->seq_len * p->num_kv_heads * hd, SHADY_ERR_BAD_ARG,
                   w + ": seq_stride smaller than one sequence");
     SHADY_REQUIRE(ctx, ((uintptr_t)d_q | (uintptr_t)d_out | (uintptr_t)gate_src) % 16 == 0 &&
@@ -1636,30 +1559,19 @@ static int launch_prefill256(shady_ctx *ctx, const char *who, const shady_prefil
     const unsigned blocks = (unsigned)(total_items < (unsigned long long)ctx->num_sms ? total_items : (unsigned long long)ctx->num_sms);
     static thread_local int configured_dev = -1;
     if (configured_dev != ctx->device) {
-        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(rowtile_kernel<__nv_bfloat16, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, rt::Shape<256>::kSmem));
-        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(rowtile_kernel<__half, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, rt::Shape<256>::kSmem));
-        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(rowtile_kernel<__nv_bfloat16, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, rt::Shape<128>::kSmem));
-        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(rowtile_kernel<__half, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, rt::Shape<128>::kSmem));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(rowtile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, rt::kSmem));
+        SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(rowtile_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, rt::kSmem));
         configured_dev = ctx->device;
     }
-    const bool bf = p->dtype == SHADY_BF16;
-    if (hd == 256) {
-        using Sh = rt::Shape<256>;
-        if (bf) rowtile_kernel<__nv_bfloat16, 256><<<blocks, Sh::kThreads, Sh::kSmem, ctx->stream>>>(mq, mk, mv, a);
-        else rowtile_kernel<__half, 256><<<blocks, Sh::kThreads, Sh::kSmem, ctx->stream>>>(mq, mk, mv, a);
-    } else {
-        using Sh = rt::Shape<128>;
-        if (bf) rowtile_kernel<__nv_bfloat16, 128><<<blocks, Sh::kThreads, Sh::kSmem, ctx->stream>>>(mq, mk, mv, a);
-        else rowtile_kernel<__half, 128><<<blocks, Sh::kThreads, Sh::kSmem, ctx->stream>>>(mq, mk, mv, a);
-    }
+    if (p->dtype == SHADY_BF16) rowtile_kernel<__nv_bfloat16><<<blocks, rt::kThreads, rt::kSmem, ctx->stream>>>(mq, mk, mv, a);
+    else rowtile_kernel<__half><<<blocks, rt::kThreads, rt::kSmem, ctx->stream>>>(mq, mk, mv, a);
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
 }
 
 int launch_prefill(shady_ctx *ctx, const shady_prefill_params *p, const void *d_q, const shady_kv_cache *cache, void *d_out) {
-    if (p && (p->head_dim == 256 || (ctx->knobs.prefill_variant == 1 && p->head_dim == 128)))
-        return launch_prefill256(ctx, "attn_prefill", p, d_q, cache, d_out, nullptr, 0);
+    if (p && p->head_dim == 256) return launch_prefill256(ctx, "attn_prefill", p, d_q, cache, d_out, nullptr, 0);
     return launch_prefill_impl(ctx, "attn_prefill", p, d_q, 128, cache, d_out, nullptr);
 }
 
