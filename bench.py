@@ -371,6 +371,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         for d in sets:
             d.close()
         extra["cfg3"] = measure_cfg3(gpu, stream, rank, world, local_rank, dist, barrier, steps=30, warmup=3)
+        set_prefill_shape(256)      # the same batch and length in the gated-attention head shape (16 / 2 heads of 256)
+        extra["cfg3_head_dim_256"] = measure_cfg3(gpu, stream, rank, world, local_rank, dist, barrier, steps=20, warmup=3)
+        set_prefill_shape(args.prefill_hd)
         extra["cfg4"] = measure_cfg4(gpu, stream, rank, world, local_rank, dist, barrier, steps=200, warmup=10)
 
     # ---------------- reduce over ranks: max time, sum bytes ----------------
@@ -445,8 +448,7 @@ def set_prefill_shape(hd: int) -> None:
     """cfg3 as BASELINE.json states it has head_dim 128; `--prefill-hd 256` runs the same batch and length with the
     head layout of config 4 (16 query heads, 2 KV heads, head_dim 256: the gated-attention layer shape)."""
     global P_NH, P_NKV, P_HD
-    if hd == 256:
-        P_NH, P_NKV, P_HD = 16, 2, 256
+    P_NH, P_NKV, P_HD = (16, 2, 256) if hd == 256 else (32, 8, 128)
 
 
 def prefill_config(n_gpus: int) -> dict:
@@ -606,9 +608,13 @@ def measure_cfg3(gpu, stream, rank, world, local_rank, dist, barrier, steps: int
     step = flops / (total_ms / steps * 1e-3) / 1e12
     return {"workload": prefill_config(world)["workload"], "metric": "prefill_attn_tflops", "unit": "TFLOP/s",
             "steps": steps, "warmup": warmup, "n_gpus": world, "per_gpu": True,
-            "attention_launch": {"tflops": attn, "ms": attend_ms, "what": "prefill_kernel alone, on Q rotated beforehand"},
+            "attention_launch": {"tflops": attn, "ms": attend_ms,
+                                 "what": ("prefill_kernel" if P_HD == 128 else "rowtile_kernel") + " alone, on Q rotated beforehand"},
+            "head_dim": P_HD, "num_q_heads": P_NH, "num_kv_heads": P_NKV,
             "whole_step": {"tflops": step, "ms": total_ms / steps,
-                           "includes": "shady_attn_prefill_append: K/V pass (norm, RoPE, cache rows) + attention kernel that norms/rotates Q itself"},
+                           "includes": ("shady_attn_prefill_append: K/V pass (norm, RoPE, cache rows) + attention kernel that norms/rotates Q itself"
+                                        if P_HD == 128 else
+                                        "shady_attn_prefill_append: one append pass (Q, K normed and rotated, cache rows) + attention kernel with the gate in its epilogue")},
             "whole_step_two_calls": {"tflops": flops / (two_call_ms * 1e-3) / 1e12, "ms": two_call_ms,
                                      "includes": "shady_kv_append_rope (Q, K, V) + shady_attn_prefill"},
             "roofline": {"bound": "tensor", "achieved": attn, "peak": burst, "unit": "TFLOP/s", "frac": attn / burst,
@@ -676,7 +682,7 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
                          "traffic": None,
                          "peak_source": f"{src} cuBLAS bf16, {'sustained' if long_loop else 'burst'} figure "
                                         f"(burst {burst}, sustained {sustained})",
-                         "kernel": "prefill kernel alone (head_dim 128: prefill_kernel, 256: prefill256_kernel) on Q rotated beforehand; `value` is the whole step through shady_attn_prefill_append",
+                         "kernel": "prefill kernel alone (head_dim 128: prefill_kernel, 256: rowtile_kernel) on Q rotated beforehand; `value` is the whole step through shady_attn_prefill_append",
                          "algorithmic_flops_per_launch": flops,
                          "avg_launch_ms": attend_ms},
             "e2e": {"value": flops * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",

@@ -588,7 +588,7 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
     return v;
 }
 
-constexpr int kTailBatch = 12;   // records whose value and log-sum-exp one thread requests together
+constexpr int kTailBatch = 20;   // records whose value and log-sum-exp one thread requests together (148 records over 8 warps: one round trip; over the 4 warps of a half in the exchange tail: two)
 
 // What the tail reads in its dependent chains, by value: the function is not inlined (inlined, it cost the
 // streaming loop registers), and through the reference every field of the kernel's parameter block is a
