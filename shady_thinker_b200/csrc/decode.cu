@@ -861,6 +861,12 @@ __device__ __noinline__ void grid_exchange_tail(const DecodeArgs &a, const TailA
             if (!sm_misc[1]) {
                 const float *mine = reinterpret_cast<const float *>(my_base + flags_bytes);
                 auto slot_of = [&](uint32_t r) { return mine + ((((size_t)par * world + r) * ta.nh + head) * chunks + chunk) * kP2PSlotFloats; };
+                // every rank's value is requested before any is used, and before the log-sum-exps are staged: the slots
+                // were written by the peers over NVLink, so each first read goes out to memory, and one after the other
+                // they took 3 us for 8 ranks
+                float pv[kP2PMaxWorld];
+#pragma unroll
+                for (uint32_t r = 0; r < kP2PMaxWorld; ++r) pv[r] = (r < world && d < ta.hd) ? __ldcg(slot_of(r) + xt) : 0.f;
                 if (xt < world) sm_lse[xt] = __ldcg(slot_of(xt) + kP2PChunk);
                 bar64();
                 if (d < ta.hd) {
@@ -868,11 +874,12 @@ __device__ __noinline__ void grid_exchange_tail(const DecodeArgs &a, const TailA
                     for (uint32_t r = 0; r < world; ++r)
                         if (sm_lse[r] > -INFINITY) gmax = fmaxf(gmax, sm_lse[r]);
                     float acc = 0.f, wsum = 0.f;
-                    for (uint32_t r = 0; r < world; ++r) {
-                        const float l = sm_lse[r];
+#pragma unroll
+                    for (uint32_t r = 0; r < kP2PMaxWorld; ++r) {
+                        const float l = r < world ? sm_lse[r] : -INFINITY;
                         if (!(l > -INFINITY)) continue;
                         const float w = expf(l - gmax);
-                        acc += w * __ldcg(slot_of(r) + xt);
+                        acc += w * pv[r];
                         wsum += w;
                     }
                     float out = wsum > 0.f ? acc / wsum : 0.f;
@@ -1979,6 +1986,9 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
     uint32_t ctas_per_sm = kn.ctas_per_sm ? kn.ctas_per_sm : (f32 ? 4u : var.ctas_per_sm);
     if (ctas_per_sm > 8) ctas_per_sm = 8;
     uint32_t min_span = kn.min_span ? kn.min_span : (f32 ? 2u : 4u * (var.nw / kpc));
+    // one sequence: nothing else fills the SMs, so spans go down to one 16-row block per warp (a 16384-row shard of a
+    // row-sharded context then streams on all SMs instead of 64: 22.6 -> 21.3 us per step)
+    if (!kn.min_span && !f32 && p->num_seqs == 1) min_span = var.nw / kpc;
 
     const size_t rec_bytes = (size_t)p->num_q_heads * (hd + 2) * sizeof(float);
     unsigned long long items, recs = 0;
