@@ -184,6 +184,7 @@ int shady_ctx_create(int device, void *stream, shady_ctx **out) {
     c->knobs.min_span = env_u32("SHADY_DECODE_MIN_SPAN", 0);
     c->knobs.grid_merge = env_u32("SHADY_DECODE_GRID_MERGE", 1);
     c->knobs.interleave = env_u32("SHADY_DECODE_INTERLEAVE", 1);
+    c->knobs.pad = env_u32("SHADY_DECODE_PAD", ~0u);
     *out = c;
     return SHADY_OK;
 }

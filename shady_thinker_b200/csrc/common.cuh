@@ -19,6 +19,7 @@ struct DecodeKnobs {
     uint32_t min_span = 0;      // SHADY_DECODE_MIN_SPAN: smallest span in 16-row blocks
     uint32_t grid_merge = 1;    // SHADY_DECODE_GRID_MERGE=0: merge many-span sequences in a second launch
     uint32_t interleave = 1;    // SHADY_DECODE_INTERLEAVE=0: fixed spans for a single long sequence
+    uint32_t pad = ~0u;         // SHADY_DECODE_PAD: line units that a sequence boundary costs a span (unset: from the block size)
 };
 
 struct shady_ctx {

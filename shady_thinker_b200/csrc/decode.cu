@@ -41,7 +41,8 @@ struct DecodeArgs {
     uint32_t gz;         // head groups per kv head (folded into blockIdx.x)
     uint32_t num_seqs, nkv, nh, G, hd;
     uint32_t num_splits; // >0: every sequence is cut into ceil(L/ns) ranges (wgsl:46-48); 0: balanced spans
-    uint32_t line_blocks; // balanced mode: total row-blocks of the batch, sum_i max(1, ceil(L_i/16))
+    uint32_t line_blocks; // balanced mode: length of the work line, sum_i (max(1, ceil(L_i/16)) + pad)
+    uint32_t pad;         // balanced mode: line units appended to every sequence (see the comment on span_begin)
     uint32_t spans;       // balanced mode: number of equal spans the line is cut into
     uint32_t span_math32; // (spans + 1) * line_blocks + spans < 2^32: span arithmetic in 32 bits
     uint32_t q_dtype, out_dtype;
@@ -137,10 +138,16 @@ __device__ __forceinline__ float gate_value(const DecodeArgs &a, uint32_t seq, u
 __device__ __forceinline__ bool has_gate(const DecodeArgs &a) { return a.fuse_append ? a.ap_has_gate != 0 : a.gate != nullptr; }
 
 // ---- balanced ("stream-K") partition of the batch -------------------------------------------
-// All sequences are laid end to end on a line of 16-position row-blocks; span c owns blocks
-// [ceil(c*T/C), ceil((c+1)*T/C)).  A span may end one sequence, hold several whole ones and start
-// another; each intersection is a "piece".  Every CTA streams the same number of rows, so there is
-// one full wave and no tail.
+// All sequences are laid end to end on a line of 16-position row-blocks; span c owns units
+// [ceil(c*T/C), ceil((c+1)*T/C)) of it.  A span may end one sequence, hold several whole ones and start
+// another; each intersection is a "piece".  There is one full wave and no tail.
+// Every sequence is followed by a.pad units that stand for no rows: starting a second piece costs a CTA about
+// 8 us (its pipeline drains 0.8, the warps' states are merged, a record written, fenced and counted 3.6, the next
+// sequence's pointers, Q rows and first tiles are requested 2.7, and data has to arrive) — in the cfg2 batch the CTAs
+// whose span held a sequence boundary ended at 78-89 us and the others at 69-73 us.  A span that contains a boundary
+// also contains the pad and so gets that many fewer row-blocks: spans are equal in time, not in rows (after: both
+// kinds end at 77-79 us on average; what is left of the spread, 64-90 us, is between CTAs of equal work).  A span that
+// begins inside a pad starts at the next sequence's first block.
 // (products that fit 32 bits — every batch short of some 50 million rows — take the 32-bit divider: the 64-bit one
 //  is a long dependent instruction sequence, and these sit at the head of every piece)
 __device__ __forceinline__ uint32_t span_begin(const DecodeArgs &a, uint32_t c) {
@@ -185,7 +192,7 @@ __device__ __forceinline__ void cursor_init(const DecodeArgs &a, uint32_t work, 
     bool found = false;
     for (uint32_t base = 0; base < a.num_seqs && !found; base += 32) {
         const uint32_t j = base + lane;
-        const uint32_t nb = j < a.num_seqs ? blocks_of(seq_len_at(a, j)) : 0u;
+        const uint32_t nb = j < a.num_seqs ? blocks_of(seq_len_at(a, j)) + a.pad : 0u;   // the sequence's extent on the line
         uint32_t incl = nb;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -196,8 +203,13 @@ __device__ __forceinline__ void cursor_init(const DecodeArgs &a, uint32_t work, 
         if (u0 < pref + total) {
             const uint32_t mask = __ballot_sync(0xffffffffu, pref + incl > u0);
             const uint32_t f = __ffs(mask) - 1;
-            const uint32_t excl = __shfl_sync(0xffffffffu, incl, f) - __shfl_sync(0xffffffffu, nb, f);
-            if (lane == 0) { res[0] = base + f; res[1] = pref + excl; res[2] = u0; res[3] = u1; res[4] = 0; }
+            const uint32_t ext = __shfl_sync(0xffffffffu, nb, f);
+            const uint32_t excl = __shfl_sync(0xffffffffu, incl, f) - ext;
+            if (lane == 0) {
+                uint32_t seq = base + f, B = pref + excl, u = u0;
+                if (u0 >= B + ext - a.pad) { ++seq; B += ext; u = B; }   // the span begins in the pad: on to the next sequence
+                res[0] = seq; res[1] = B; res[2] = u; res[3] = u1; res[4] = 0;
+            }
             found = true;
         }
         pref += total;
@@ -226,7 +238,7 @@ __device__ __forceinline__ bool next_piece(const DecodeArgs &a, Cursor &cur, Pie
     p.nrec = span_of(a, cur.B + nb - 1) - p.c0 + 1;
     p.my_rec = cur.span - p.c0;
     cur.u = ub1;
-    if (ub1 == cur.B + nb) { cur.B += nb; cur.seq++; }
+    if (ub1 == cur.B + nb) { cur.B += nb + a.pad; cur.seq++; cur.u = cur.B; }   // over the pad (possibly past the span's end)
     return true;
 }
 
@@ -602,11 +614,12 @@ struct TailArgs {
     uint32_t wait_grid, wait_peer;
     uint32_t nh, hd, num_seqs, out_row_stride, lse_stride, out_dtype, spans, line_blocks, span_math32, gated;
     uint32_t len0;   // length of sequence 0 (the others are read through the reference)
+    uint32_t pad;
 };
 __device__ __forceinline__ TailArgs tail_args(const DecodeArgs &a) {
     return TailArgs{a.partials, a.out, a.lse, a.grid_sync, a.status, a.wait_grid, a.wait_peer, a.nh, a.hd, a.num_seqs, a.out_row_stride,
                     a.lse_stride, a.out_dtype, a.spans, a.line_blocks, a.span_math32, has_gate(a) ? 1u : 0u,
-                    seq_len_at(a, 0)};
+                    seq_len_at(a, 0), a.pad};
 }
 
 // The two halves of the grid barrier, both called by thread 0 of every CTA after its arrival (atomicAdd on
@@ -656,7 +669,7 @@ __device__ __noinline__ void grid_merge_tail(const DecodeArgs &a, const TailArgs
             __syncthreads();
             if (tid < 32) {
                 uint32_t acc = 0;
-                for (uint32_t j = tid; j < x.seq; j += 32) acc += blocks_of(seq_len_at(a, j));
+                for (uint32_t j = tid; j < x.seq; j += 32) acc += blocks_of(seq_len_at(a, j)) + ta.pad;
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
                 if (tid == 0) sm_misc[1] = acc;
@@ -972,6 +985,8 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
     const uint32_t l_row = lane / CHK * (RPI > 1), l_chunk = lane % CHK;
 
     Piece p;
+    uint32_t pf_seq = 0xffffffffu;            // sequence whose cache pointers were requested ahead (pointer-array caches)
+    const char *pf_k = nullptr, *pf_v = nullptr;
     bool ilv_todo = ILV;
     if constexpr (ILV) {   // the whole sequence is this CTA's piece; its record is number `work` of a.spans
         p.seq = 0; p.L = seq_len_at(a, 0); p.start = 0; p.end = p.L; p.nrec = a.spans; p.my_rec = work; p.c0 = 0; p.B = 0;
@@ -982,8 +997,21 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
         // paged cache: kbase/vbase are the pools and every 16-row block takes its page number from the table; the
         // number of the warp's next block is fetched one block ahead so that its latency never meets a cp.async
         const uint32_t *ptab = a.kv.page_table ? a.kv.page_table + (size_t)p.seq * a.kv.max_pages : nullptr;
-        const char *kbase = (ptab ? a.kv.k_base : kv_seq_ptr(a.kv.k_base, a.kv.k_ptrs, a.kv.seq_stride_bytes, p.seq)) + (size_t)kvh * S::kRowBytes;
-        const char *vbase = (ptab ? a.kv.v_base : kv_seq_ptr(a.kv.v_base, a.kv.v_ptrs, a.kv.seq_stride_bytes, p.seq)) + (size_t)kvh * S::kRowBytes;
+        // pointer-array caches: the sequence's two base pointers are a dependent load at the head of the piece; the next
+        // sequence's are requested now, a whole piece ahead of their use
+        const char *kseq, *vseq;
+        if (!ptab && a.kv.k_ptrs && p.seq == pf_seq) { kseq = pf_k; vseq = pf_v; }
+        else {
+            kseq = ptab ? a.kv.k_base : kv_seq_ptr(a.kv.k_base, a.kv.k_ptrs, a.kv.seq_stride_bytes, p.seq);
+            vseq = ptab ? a.kv.v_base : kv_seq_ptr(a.kv.v_base, a.kv.v_ptrs, a.kv.seq_stride_bytes, p.seq);
+        }
+        if (!ILV && !ptab && a.kv.k_ptrs && p.seq + 1 < a.num_seqs) {
+            pf_seq = p.seq + 1;
+            pf_k = reinterpret_cast<const char *>(__ldg(reinterpret_cast<const unsigned long long *>(a.kv.k_ptrs) + pf_seq));
+            pf_v = reinterpret_cast<const char *>(__ldg(reinterpret_cast<const unsigned long long *>(a.kv.v_ptrs) + pf_seq));
+        }
+        const char *kbase = kseq + (size_t)kvh * S::kRowBytes;
+        const char *vbase = vseq + (size_t)kvh * S::kRowBytes;
         const uint32_t nblk = (end - start + kBlk - 1) / kBlk;
         const uint32_t my_n = nblk > sub ? (nblk - sub + WPK - 1) / WPK : 0;
         // The pipeline moves single tiles: item 2i is the K tile of the warp's i-th block, item 2i+1 its V tile,
@@ -1582,7 +1610,7 @@ __device__ __forceinline__ void merge_balanced_records(const DecodeArgs &a, uint
     const uint32_t tid = threadIdx.x, g = tid >> 6, t = tid & 63u;
     if (tid < 32) {   // first row-block of this sequence on the line
         uint32_t acc = 0;
-        for (uint32_t j = tid; j < seq; j += 32) acc += blocks_of(seq_len_at(a, j));
+        for (uint32_t j = tid; j < seq; j += 32) acc += blocks_of(seq_len_at(a, j)) + a.pad;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (tid == 0) sm_b = acc;
@@ -2004,8 +2032,17 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
         recs = items;
     } else {
         SHADY_REQUIRE(ctx, seq_lens_host, SHADY_ERR_BAD_ARG, "decode: num_splits == 0 needs seq_lens_host");
+        // what a second piece costs a CTA, in row-blocks: 7.6 us from the first piece's drain to the second piece's
+        // first tile request, a bit more until data flows — at a CTA's share of the memory bandwidth about 320 KB of K
+        // and V (8 KB per block at head_dim 128 and 16 bits: 40 blocks, the best of 0/12/20/25/32/40/56 on the cfg2
+        // batch); the SHADY_DECODE_PAD knob overrides (0 = none)
+        if (p->num_seqs > 1 && !f32) {
+            const unsigned long long block_bytes = 2ull * kBlkPos * hd * dtype_size(cache->dtype) * kpc;
+            unsigned long long pad = kn.pad != ~0u ? kn.pad : (320ull << 10) / block_bytes;
+            a.pad = (uint32_t)(pad > 64 ? 64 : pad);
+        }
         unsigned long long line = 0;
-        for (uint32_t i = 0; i < p->num_seqs; ++i) line += seq_lens_host[i] == 0 ? 1 : (seq_lens_host[i] + kBlkPos - 1) / kBlkPos;
+        for (uint32_t i = 0; i < p->num_seqs; ++i) line += (seq_lens_host[i] == 0 ? 1 : (seq_lens_host[i] + kBlkPos - 1) / kBlkPos) + a.pad;
         SHADY_REQUIRE(ctx, line <= 0xffffffffull, SHADY_ERR_UNSUPPORTED, "decode: batch too long for one launch");
         unsigned long long slots = (unsigned long long)ctx->num_sms * ctas_per_sm;
         if (slots > kMaxSlots) slots = kMaxSlots;
@@ -2025,7 +2062,7 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
             const unsigned long long nb = seq_lens_host[i] == 0 ? 1 : (seq_lens_host[i] + kBlkPos - 1) / kBlkPos;
             const unsigned long long nrec = ((u + nb - 1) * spans) / line - (u * spans) / line + 1;
             if (nrec > kDeferMergeRecords) a.defer_merge = 1;
-            u += nb;
+            u += nb + a.pad;
         }
     }
     plan->counters_bytes = counters_bytes(p);
