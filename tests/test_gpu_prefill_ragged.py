@@ -231,3 +231,12 @@ def test_bad_batches_return_a_status(gpu_ctx):
         ops.attn_prefill_ragged(gpu_ctx, cache=ops.KvCacheView(BF16, d, d, 0, None, None, ptrs, 48, 4), seq_lens=[16], **base)
     assert e.value.code == 2
     gpu_ctx.synchronize()
+
+
+@pytest.mark.parametrize("hd", [128, 256])
+def test_many_short_prompts(gpu_ctx, oracle, hd):
+    """Hundreds of items of one or two K/V tiles each: the roles of a CTA run several items apart (the softmax is
+    done with an item long before its epilogue starts), which is what the per-row hand-over words are numbered for."""
+    rng = np.random.default_rng(77)
+    lens = [int(v) for v in rng.integers(1, 200, 90)] + [130, 257, 64, 1, 128]
+    _plain_case(gpu_ctx, oracle, lens, 8, 2, hd, BF16, 65, "ptrs")
