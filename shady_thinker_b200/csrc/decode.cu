@@ -2032,13 +2032,13 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
         recs = items;
     } else {
         SHADY_REQUIRE(ctx, seq_lens_host, SHADY_ERR_BAD_ARG, "decode: num_splits == 0 needs seq_lens_host");
-        // what a second piece costs a CTA, in row-blocks: 7.6 us from the first piece's drain to the second piece's
-        // first tile request, a bit more until data flows — at a CTA's share of the memory bandwidth about 320 KB of K
-        // and V (8 KB per block at head_dim 128 and 16 bits: 40 blocks, the best of 0/12/20/25/32/40/56 on the cfg2
-        // batch); the SHADY_DECODE_PAD knob overrides (0 = none)
+        // what a second piece costs a CTA, in row-blocks: a least-squares fit of the spans' end times on the cfg2 batch
+        // gives 0.265 us per block and 7.7 us per piece, i.e. 29 blocks of 8 KB (head_dim 128, 16 bits) — about 256 KB
+        // of K and V at a CTA's share of the memory bandwidth (steps measured with 0/12/20/25/32/40/56 blocks lie within
+        // 2 % of each other, the best between 32 and 40); the SHADY_DECODE_PAD knob overrides (0 = none)
         if (p->num_seqs > 1 && !f32) {
             const unsigned long long block_bytes = 2ull * kBlkPos * hd * dtype_size(cache->dtype) * kpc;
-            unsigned long long pad = kn.pad != ~0u ? kn.pad : (320ull << 10) / block_bytes;
+            unsigned long long pad = kn.pad != ~0u ? kn.pad : (256ull << 10) / block_bytes;
             a.pad = (uint32_t)(pad > 64 ? 64 : pad);
         }
         unsigned long long line = 0;
