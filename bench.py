@@ -374,7 +374,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         set_prefill_shape(256)      # the same batch and length in the gated-attention head shape (16 / 2 heads of 256)
         extra["cfg3_head_dim_256"] = measure_cfg3(gpu, stream, rank, world, local_rank, dist, barrier, steps=20, warmup=3)
         set_prefill_shape(args.prefill_hd)
-        extra["cfg4"] = measure_cfg4(gpu, stream, rank, world, local_rank, dist, barrier, steps=200, warmup=10)
+        extra["cfg4"] = measure_cfg4(gpu, stream, rank, world, local_rank, dist, barrier, steps=500, warmup=20)
 
     # ---------------- reduce over ranks: max time, sum bytes ----------------
     t = torch.tensor([total_ms, e2e_ms, attend_ms], dtype=torch.float64, device="cuda")
