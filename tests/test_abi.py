@@ -130,3 +130,24 @@ def test_rust_crate_files_exist_and_build_script_targets_sm_100a():
     from shady_thinker_b200 import build
     for src in build.SOURCES:
         assert f'"{src}"' in b, f"build.rs does not compile {src}"
+
+
+def test_listed_prefill_workspace_is_host_arithmetic():
+    """`shady_prefill_ragged_workspace_size` touches no device: row-block list + packed token starts + two tensor maps
+    per sequence (+ the cos/sin table or the rotated Q for the step from the projections), every part 128-byte aligned."""
+    from shady_thinker_b200 import ops
+    from shady_thinker_b200._lib import BF16
+
+    def up(v):
+        return (v + 127) // 128 * 128
+
+    lens = [300, 1, 129, 515]
+    for hd, block in ((128, 256), (256, 128)):
+        entries = sum((L + block - 1) // block for L in lens)
+        base = up(up(up(entries * 16) + (len(lens) + 1) * 4) + len(lens) * 2 * 128)
+        plain = ops.prefill_ragged_workspace_size(seq_lens=lens, head_dim=hd, num_kv_heads=2, num_q_heads=4, dtype=BF16)
+        fused = ops.prefill_ragged_workspace_size(seq_lens=lens, head_dim=hd, num_kv_heads=2, num_q_heads=4, dtype=BF16,
+                                                  with_append=True)
+        assert plain == base
+        extra = sum(lens) * 4 * 256 * 2 if hd == 256 else max(lens) * 64 * 8
+        assert fused == up(base + extra)
