@@ -103,13 +103,16 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_kernel(const AppendA
 // reuses them for every Q and K head of the token; each lane moves 8 contiguous elements per
 // head with 16/32-byte accesses, and a warp covers 32*8/HD heads per iteration.
 // ---------------------------------------------------------------------------------------
+// ldraw() only requests the bytes, unpack() is their first use: a warp can hold several requests in flight.
 template <typename T> struct Vec8 {
-    static __device__ __forceinline__ void load(const T *p, float (&v)[8]) {
-        const uint4 u = *reinterpret_cast<const uint4 *>(p);
+    using raw_t = uint4;
+    static __device__ __forceinline__ raw_t ldraw(const T *p) { return *reinterpret_cast<const uint4 *>(p); }
+    static __device__ __forceinline__ void unpack(const raw_t &u, float (&v)[8]) {
         const T *e = reinterpret_cast<const T *>(&u);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = to_f32<T>(e[i]);
     }
+    static __device__ __forceinline__ void load(const T *p, float (&v)[8]) { unpack(ldraw(p), v); }
     static __device__ __forceinline__ void store(T *p, const float (&v)[8]) {
         uint4 u;
         T *e = reinterpret_cast<T *>(&u);
@@ -119,10 +122,14 @@ template <typename T> struct Vec8 {
     }
 };
 template <> struct Vec8<float> {
-    static __device__ __forceinline__ void load(const float *p, float (&v)[8]) {
-        const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    struct raw_t { float4 a, b; };
+    static __device__ __forceinline__ raw_t ldraw(const float *p) {
+        return raw_t{*reinterpret_cast<const float4 *>(p), *reinterpret_cast<const float4 *>(p + 4)};
     }
+    static __device__ __forceinline__ void unpack(const raw_t &r, float (&v)[8]) {
+        v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
+    }
+    static __device__ __forceinline__ void load(const float *p, float (&v)[8]) { unpack(ldraw(p), v); }
     static __device__ __forceinline__ void store(float *p, const float (&v)[8]) {
         *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -130,12 +137,14 @@ template <> struct Vec8<float> {
 };
 
 template <typename F8T> struct Vec8F8 {   // eight 1-byte elements: an 8-byte access
-    static __device__ __forceinline__ void load(const F8T *p, float (&v)[8]) {
-        const uint2 u = *reinterpret_cast<const uint2 *>(p);
+    using raw_t = uint2;
+    static __device__ __forceinline__ raw_t ldraw(const F8T *p) { return *reinterpret_cast<const uint2 *>(p); }
+    static __device__ __forceinline__ void unpack(const raw_t &u, float (&v)[8]) {
         const F8T *e = reinterpret_cast<const F8T *>(&u);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = float(e[i]);
     }
+    static __device__ __forceinline__ void load(const F8T *p, float (&v)[8]) { unpack(ldraw(p), v); }
     static __device__ __forceinline__ void store(F8T *p, const float (&v)[8]) {
         uint2 u;
         F8T *e = reinterpret_cast<F8T *>(&u);
@@ -148,7 +157,7 @@ template <> struct Vec8<__nv_fp8_e4m3> : Vec8F8<__nv_fp8_e4m3> {};
 template <> struct Vec8<__nv_fp8_e5m2> : Vec8F8<__nv_fp8_e5m2> {};
 
 template <typename TIn, typename TQ, typename TKV, int HD>
-__global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const AppendArgs a) {
+__global__ void __launch_bounds__(kAppendWarps * 32, 6) append_fast_kernel(const AppendArgs a) {
     constexpr int LPH = HD / 8;       // lanes per head
     constexpr int HPI = 32 / LPH;     // heads per warp iteration
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -169,6 +178,35 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
         s = (uint32_t)(tok / a.T); j = (uint32_t)(tok % a.T);
     }
     const uint32_t sub = lane / LPH, dl = lane % LPH, d0 = dl * 8;
+    // Every lane takes every trip (the norm shuffles are warp-wide).  A trip's rows are requested kPF trips before
+    // they are used: with the request and the use in one trip a warp waited a memory round trip per head, and a
+    // pass over 16k tokens ran at under half the memory bandwidth.
+    using Raw = typename Vec8<TIn>::raw_t;
+    constexpr int kPF = 3;
+    const uint32_t step = HPI * a.head_slices;
+    // ---- K heads (+ V copy): the first trip's rows are requested here, the second's while the first is worked on ----
+    TIn *k_io = reinterpret_cast<TIn *>(a.k_io) + tok * a.nkv * (size_t)HD;
+    const TIn *v_in = reinterpret_cast<const TIn *>(a.v_in) + tok * a.nkv * (size_t)HD;
+    Raw rk = Raw{}, rv = Raw{};
+    auto kv_request = [&](uint32_t kh0) {
+        const uint32_t kh = kh0 + sub;
+        if (kh < a.nkv) { rk = Vec8<TIn>::ldraw(k_io + (size_t)kh * HD + d0); rv = Vec8<TIn>::ldraw(v_in + (size_t)kh * HD + d0); }
+    };
+    kv_request(slice * HPI);
+    // ---- Q heads: the first kPF trips' rows ----
+    const uint32_t qrow = a.has_gate ? 2 * HD : HD;
+    const TIn *q_in = reinterpret_cast<const TIn *>(a.q_in) + tok * a.nh * (size_t)qrow;
+    TQ *q_out = reinterpret_cast<TQ *>(a.q_out) + tok * a.nh * (size_t)HD;
+    Raw rq[kPF];
+    uint32_t q_next = slice * HPI;   // the next trip to request
+    auto q_request = [&](Raw &r) {
+        const uint32_t h = q_next + sub;
+        r = Raw{};
+        if (h < a.nh && !a.skip_q) r = Vec8<TIn>::ldraw(q_in + (size_t)h * qrow + d0);
+        q_next += step;
+    };
+#pragma unroll
+    for (int u = 0; u < kPF; ++u) q_request(rq[u]);
     // ---- cos/sin of this lane's four pairs (wgsl:56-68) ----
     const uint32_t p_t = (a.pos_start ? a.pos_start[s] : 0u) + j;
     const uint32_t p_h = a.pos_h ? a.pos_h[s] + j : p_t;
@@ -216,37 +254,17 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
             v[2 * k + 1] = y * cs[k] + x * sn[k];
         }
     };
-    // ---- Q heads ----
-    const uint32_t qrow = a.has_gate ? 2 * HD : HD;
-    const TIn *q_in = reinterpret_cast<const TIn *>(a.q_in) + tok * a.nh * (size_t)qrow;
-    TQ *q_out = reinterpret_cast<TQ *>(a.q_out) + tok * a.nh * (size_t)HD;
-    for (uint32_t h0 = slice * HPI; h0 < a.nh && !a.skip_q; h0 += HPI * a.head_slices) {   // every lane takes every trip: the norm shuffles are warp-wide
-        const uint32_t h = h0 + sub;
-        const bool valid = h < a.nh;
-        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (valid) Vec8<TIn>::load(q_in + (size_t)h * qrow + d0, v);
-        if (valid && a.has_gate && a.q_gate) {
-            float gt[8];
-            Vec8<TIn>::load(q_in + (size_t)h * qrow + HD + d0, gt);
-            Vec8<float>::store(a.q_gate + (tok * a.nh + h) * (size_t)HD + d0, gt);
-        }
-        norm_rope(v, wq);
-        if (valid) Vec8<TQ>::store(q_out + (size_t)h * HD + d0, v);
-    }
-    // ---- K heads (+ V copy) ----
-    TIn *k_io = reinterpret_cast<TIn *>(a.k_io) + tok * a.nkv * (size_t)HD;
-    const TIn *v_in = reinterpret_cast<const TIn *>(a.v_in) + tok * a.nkv * (size_t)HD;
     // cache_position == position (model.rs:493-496)
     TKV *k_row = reinterpret_cast<TKV *>(const_cast<char *>(kv_row_ptr(a.kv, false, s, p_t, (size_t)a.nkv * HD * sizeof(TKV))));
     TKV *v_row = reinterpret_cast<TKV *>(const_cast<char *>(kv_row_ptr(a.kv, true, s, p_t, (size_t)a.nkv * HD * sizeof(TKV))));
-    for (uint32_t kh0 = slice * HPI; kh0 < a.nkv; kh0 += HPI * a.head_slices) {
+    for (uint32_t kh0 = slice * HPI; kh0 < a.nkv; kh0 += step) {
         const uint32_t kh = kh0 + sub;
         const bool valid = kh < a.nkv;
-        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, vv[8];
-        if (valid) {
-            Vec8<TIn>::load(k_io + (size_t)kh * HD + d0, v);
-            Vec8<TIn>::load(v_in + (size_t)kh * HD + d0, vv);
-        }
+        float v[8], vv[8];
+        Vec8<TIn>::unpack(rk, v);
+        Vec8<TIn>::unpack(rv, vv);
+        rk = Raw{}; rv = Raw{};
+        kv_request(kh0 + step);
         norm_rope(v, wk);
         if (valid) {
             if (a.write_k_back) Vec8<TIn>::store(k_io + (size_t)kh * HD + d0, v);
@@ -256,6 +274,27 @@ __global__ void __launch_bounds__(kAppendWarps * 32) append_fast_kernel(const Ap
             }
             Vec8<TKV>::store(k_row + (size_t)kh * HD + d0, v);
             Vec8<TKV>::store(v_row + (size_t)kh * HD + d0, vv);
+        }
+    }
+    // ---- Q heads ----
+    for (uint32_t h0 = slice * HPI; h0 < a.nh && !a.skip_q;) {
+#pragma unroll
+        for (int u = 0; u < kPF; ++u) {
+            if (h0 < a.nh) {   // (the same for every lane)
+                const uint32_t h = h0 + sub;
+                const bool valid = h < a.nh;
+                float v[8];
+                Vec8<TIn>::unpack(rq[u], v);
+                q_request(rq[u]);
+                if (valid && a.has_gate && a.q_gate) {
+                    float gt[8];
+                    Vec8<TIn>::load(q_in + (size_t)h * qrow + HD + d0, gt);
+                    Vec8<float>::store(a.q_gate + (tok * a.nh + h) * (size_t)HD + d0, gt);
+                }
+                norm_rope(v, wq);
+                if (valid) Vec8<TQ>::store(q_out + (size_t)h * HD + d0, v);
+                h0 += step;
+            }
         }
     }
 }
