@@ -23,13 +23,14 @@ int pending_timeout(shady_ctx *ctx, const char *who) {
     return SHADY_OK;
 }
 
-// Text of a wait code: 1..16 = waits of the prefill kernels (mbarriers, shared-memory handshakes), 90 = the decode grid barrier, 100 + r = the NVLink
-// flag of rank r.
+// Text of a wait code: 1..16 = waits of the prefill kernels (mbarriers, shared-memory handshakes), 17 = the bulk copies of the staged
+// append pass, 90 = the decode grid barrier, 100 + r = the NVLink flag of rank r.
 std::string timeout_message(int code) {
     if (code >= 100)
         return "combine_p2p: the flag of rank " + std::to_string(code - 100) + " did not arrive in time";
     if (code == 90)
         return "decode: the grid barrier before the record merge ran out; the workspace counters are cleared again before the next launch";
+    if (code == 17) return "kv_append: a token's bulk copies into shared memory did not land in time";
     return "attn_prefill: a device-side wait expired (code " + std::to_string(code) + ")";
 }
 

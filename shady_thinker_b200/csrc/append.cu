@@ -10,6 +10,7 @@
 // cos/sin use the accurate sincosf (full-range argument reduction), never the fast
 // intrinsics: the shader takes cos/sin of up to 131071 radians in f32 (wgsl:66-68).
 #include <math.h>
+#include <type_traits>
 
 #include "append_core.cuh"
 
@@ -37,6 +38,9 @@ struct AppendArgs {
     // [tok_start[s], tok_start[s+1]); T is not used
     const uint32_t *tok_start;
     uint32_t total_tokens, table_seq;
+    // staged path: shared-memory bytes of one warp's token, the status words and the poll limit of its bounded wait
+    uint32_t stage_bytes, wait_limit;
+    StatusRef status;
     float inv_freq[128];      // [rd/2]
 };
 
@@ -156,17 +160,10 @@ template <typename F8T> struct Vec8F8 {   // eight 1-byte elements: an 8-byte ac
 template <> struct Vec8<__nv_fp8_e4m3> : Vec8F8<__nv_fp8_e4m3> {};
 template <> struct Vec8<__nv_fp8_e5m2> : Vec8F8<__nv_fp8_e5m2> {};
 
-template <typename TIn, typename TQ, typename TKV, int HD>
-__global__ void __launch_bounds__(kAppendWarps * 32, 6) append_fast_kernel(const AppendArgs a) {
-    constexpr int LPH = HD / 8;       // lanes per head
-    constexpr int HPI = 32 / LPH;     // heads per warp iteration
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const unsigned long long wid = (unsigned long long)blockIdx.x * kAppendWarps + warp;
-    const unsigned long long tok = wid / a.head_slices;
-    const uint32_t slice = (uint32_t)(wid % a.head_slices);
-    uint32_t s, j;
+// Which sequence a packed token belongs to and its index there; false past the last token.
+__device__ __forceinline__ bool locate_token(const AppendArgs &a, unsigned long long tok, uint32_t &s, uint32_t &j) {
     if (a.tok_start) {
-        if (tok >= a.total_tokens) return;
+        if (tok >= a.total_tokens) return false;
         uint32_t lo = 0, hi = a.num_seqs;   // the sequence with tok_start[s] <= tok < tok_start[s + 1]
         while (hi - lo > 1) {
             const uint32_t mid = (lo + hi) >> 1;
@@ -174,9 +171,130 @@ __global__ void __launch_bounds__(kAppendWarps * 32, 6) append_fast_kernel(const
         }
         s = lo; j = (uint32_t)tok - __ldg(a.tok_start + lo);
     } else {
-        if (tok >= (unsigned long long)a.num_seqs * a.T) return;
+        if (tok >= (unsigned long long)a.num_seqs * a.T) return false;
         s = (uint32_t)(tok / a.T); j = (uint32_t)(tok % a.T);
     }
+    return true;
+}
+
+// What a lane keeps for one token: cos/sin of its four pairs (wgsl:56-68), the norm weights of its eight dims.
+template <int HD> struct LaneMath {
+    static constexpr int LPH = HD / 8;   // lanes per head
+    float cs[4], sn[4], wq[8], wk[8], eps;
+    bool has_norm;
+    uint32_t p_t;                        // the token's position == its cache row (model.rs:493-496)
+    __device__ __forceinline__ void init(const AppendArgs &a, uint32_t s, uint32_t j, uint32_t dl, bool writes_table) {
+        p_t = (a.pos_start ? a.pos_start[s] : 0u) + j;
+        const uint32_t p_h = a.pos_h ? a.pos_h[s] + j : p_t;
+        const uint32_t p_w = a.pos_w ? a.pos_w[s] + j : p_t;
+        const uint32_t lane = threadIdx.x & 31, pairs = a.rd / 2;
+        auto angle = [&](uint32_t i, float &c, float &sv) {
+            uint32_t pos = p_t;
+            if ((i % 3u) == 1u && i < a.s1) pos = p_h;
+            else if ((i % 3u) == 2u && i < a.s2) pos = p_w;
+            sincosf((float)pos * a.inv_freq[i], &sv, &c);
+        };
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { cs[k] = 1.f; sn[k] = 0.f; }
+        if (pairs <= 64) {
+            // Few rotated dims: the warp evaluates each pair once (lane l takes pairs l and l + 32) and hands the
+            // values to the lanes that rotate with them.  The accurate sincosf is the longest run of instructions a
+            // token costs, and with a quarter of the dims rotated only a quarter of the lanes would be inside it,
+            // four times over.
+            for (uint32_t base = 0; base < pairs; base += 32) {   // (the same trips for every lane)
+                float c = 1.f, sv = 0.f;
+                if (base + lane < pairs) angle(base + lane, c, sv);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t want = dl * 4 + k;
+                    const float ck = __shfl_sync(0xffffffffu, c, want & 31), sk = __shfl_sync(0xffffffffu, sv, want & 31);
+                    if (want >= base && want < base + 32 && want < pairs) { cs[k] = ck; sn[k] = sk; }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (dl * 4 + k < pairs) angle(dl * 4 + k, cs[k], sn[k]);
+        }
+        if (a.cs_table && s == a.table_seq && writes_table) {   // one group of HD/8 lanes per token writes the token's table row
+            float4 *row = reinterpret_cast<float4 *>(a.cs_table + (size_t)j * (HD / 2) + dl * 4);
+            row[0] = make_float4(cs[0], sn[0], cs[1], sn[1]);
+            row[1] = make_float4(cs[2], sn[2], cs[3], sn[3]);
+        }
+        has_norm = a.norm_w != nullptr;
+        eps = a.eps;
+        if (has_norm) {
+            uint16_t bq[8], bk[8];   // bf16 bits
+            if (((uintptr_t)a.norm_w & 15) == 0) {   // the lane's eight weights in one access each
+                *reinterpret_cast<uint4 *>(bq) = *reinterpret_cast<const uint4 *>(a.norm_w + dl * 8);
+                *reinterpret_cast<uint4 *>(bk) = *reinterpret_cast<const uint4 *>(a.norm_w + HD + dl * 8);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { bq[e] = a.norm_w[dl * 8 + e]; bk[e] = a.norm_w[HD + dl * 8 + e]; }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                wq[e] = 1.0f + __uint_as_float(((uint32_t)bq[e]) << 16);
+                wk[e] = 1.0f + __uint_as_float(((uint32_t)bk[e]) << 16);
+            }
+        }
+    }
+    // Two heads at once: the same arithmetic as norm_rope on each, written side by side so that one head's shuffles
+    // and square root wait under the other's
+    __device__ __forceinline__ void norm_rope2(float (&u)[8], float (&v)[8], const float (&w)[8]) const {
+        if (has_norm) {
+            float su = 0.f, sv = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { su += u[e] * u[e]; sv += v[e] * v[e]; }
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) {
+                su += __shfl_xor_sync(0xffffffffu, su, o);
+                sv += __shfl_xor_sync(0xffffffffu, sv, o);
+            }
+            const float ru = 1.0f / sqrtf(su / (float)HD + eps), rv = 1.0f / sqrtf(sv / (float)HD + eps);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { u[e] = u[e] * ru * w[e]; v[e] = v[e] * rv * w[e]; }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float xu = u[2 * k], yu = u[2 * k + 1], xv = v[2 * k], yv = v[2 * k + 1];
+            u[2 * k] = xu * cs[k] - yu * sn[k];
+            u[2 * k + 1] = yu * cs[k] + xu * sn[k];
+            v[2 * k] = xv * cs[k] - yv * sn[k];
+            v[2 * k + 1] = yv * cs[k] + xv * sn[k];
+        }
+    }
+    // RMSNorm over the head (wgsl:150-160 / :205-212; every lane of the warp calls it), then the rotation
+    __device__ __forceinline__ void norm_rope(float (&v)[8], const float (&w)[8]) const {
+        if (has_norm) {
+            float ssq = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ssq += v[e] * v[e];
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+            const float rms = 1.0f / sqrtf(ssq / (float)HD + eps);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = v[e] * rms * w[e];
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float x = v[2 * k], y = v[2 * k + 1];
+            v[2 * k] = x * cs[k] - y * sn[k];
+            v[2 * k + 1] = y * cs[k] + x * sn[k];
+        }
+    }
+};
+
+template <typename TIn, typename TQ, typename TKV, int HD>
+__global__ void __launch_bounds__(kAppendWarps * 32, sizeof(TIn) == 4 ? 4 : 6) append_fast_kernel(const AppendArgs a) {
+    constexpr int LPH = HD / 8;       // lanes per head
+    constexpr int HPI = 32 / LPH;     // heads per warp iteration
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const unsigned long long wid = (unsigned long long)blockIdx.x * kAppendWarps + warp;
+    const unsigned long long tok = wid / a.head_slices;
+    const uint32_t slice = (uint32_t)(wid % a.head_slices);
+    uint32_t s, j;
+    if (!locate_token(a, tok, s, j)) return;
     const uint32_t sub = lane / LPH, dl = lane % LPH, d0 = dl * 8;
     // Every lane takes every trip (the norm shuffles are warp-wide).  A trip's rows are requested kPF trips before
     // they are used: with the request and the use in one trip a warp waited a memory round trip per head, and a
@@ -207,56 +325,10 @@ __global__ void __launch_bounds__(kAppendWarps * 32, 6) append_fast_kernel(const
     };
 #pragma unroll
     for (int u = 0; u < kPF; ++u) q_request(rq[u]);
-    // ---- cos/sin of this lane's four pairs (wgsl:56-68) ----
-    const uint32_t p_t = (a.pos_start ? a.pos_start[s] : 0u) + j;
-    const uint32_t p_h = a.pos_h ? a.pos_h[s] + j : p_t;
-    const uint32_t p_w = a.pos_w ? a.pos_w[s] + j : p_t;
-    float cs[4], sn[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const uint32_t i = dl * 4 + k;
-        cs[k] = 1.f; sn[k] = 0.f;
-        if (i < a.rd / 2) {
-            uint32_t pos = p_t;
-            if ((i % 3u) == 1u && i < a.s1) pos = p_h;
-            else if ((i % 3u) == 2u && i < a.s2) pos = p_w;
-            sincosf((float)pos * a.inv_freq[i], &sn[k], &cs[k]);
-        }
-    }
-    if (a.cs_table && s == a.table_seq && slice == 0 && sub == 0) {   // one 16-lane group per token writes the token's table row
-        float4 *row = reinterpret_cast<float4 *>(a.cs_table + (size_t)j * (HD / 2) + dl * 4);
-        row[0] = make_float4(cs[0], sn[0], cs[1], sn[1]);
-        row[1] = make_float4(cs[2], sn[2], cs[3], sn[3]);
-    }
-    float wq[8], wk[8];
-    if (a.norm_w) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            wq[e] = 1.0f + __uint_as_float(((uint32_t)a.norm_w[d0 + e]) << 16);
-            wk[e] = 1.0f + __uint_as_float(((uint32_t)a.norm_w[HD + d0 + e]) << 16);
-        }
-    }
-    auto norm_rope = [&](float (&v)[8], const float (&w)[8]) {
-        if (a.norm_w) {
-            float ssq = 0.f;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) ssq += v[e] * v[e];
-#pragma unroll
-            for (int o = LPH / 2; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-            const float rms = 1.0f / sqrtf(ssq / (float)HD + a.eps);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = v[e] * rms * w[e];
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float x = v[2 * k], y = v[2 * k + 1];
-            v[2 * k] = x * cs[k] - y * sn[k];
-            v[2 * k + 1] = y * cs[k] + x * sn[k];
-        }
-    };
-    // cache_position == position (model.rs:493-496)
-    TKV *k_row = reinterpret_cast<TKV *>(const_cast<char *>(kv_row_ptr(a.kv, false, s, p_t, (size_t)a.nkv * HD * sizeof(TKV))));
-    TKV *v_row = reinterpret_cast<TKV *>(const_cast<char *>(kv_row_ptr(a.kv, true, s, p_t, (size_t)a.nkv * HD * sizeof(TKV))));
+    LaneMath<HD> m;
+    m.init(a, s, j, dl, slice == 0 && sub == 0);
+    TKV *k_row = reinterpret_cast<TKV *>(const_cast<char *>(kv_row_ptr(a.kv, false, s, m.p_t, (size_t)a.nkv * HD * sizeof(TKV))));
+    TKV *v_row = reinterpret_cast<TKV *>(const_cast<char *>(kv_row_ptr(a.kv, true, s, m.p_t, (size_t)a.nkv * HD * sizeof(TKV))));
     for (uint32_t kh0 = slice * HPI; kh0 < a.nkv; kh0 += step) {
         const uint32_t kh = kh0 + sub;
         const bool valid = kh < a.nkv;
@@ -265,7 +337,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32, 6) append_fast_kernel(const
         Vec8<TIn>::unpack(rv, vv);
         rk = Raw{}; rv = Raw{};
         kv_request(kh0 + step);
-        norm_rope(v, wk);
+        m.norm_rope(v, m.wk);
         if (valid) {
             if (a.write_k_back) Vec8<TIn>::store(k_io + (size_t)kh * HD + d0, v);
             if constexpr (sizeof(TKV) == 1) {   // 8-bit cache: stored = value / scale
@@ -291,7 +363,7 @@ __global__ void __launch_bounds__(kAppendWarps * 32, 6) append_fast_kernel(const
                     Vec8<TIn>::load(q_in + (size_t)h * qrow + HD + d0, gt);
                     Vec8<float>::store(a.q_gate + (tok * a.nh + h) * (size_t)HD + d0, gt);
                 }
-                norm_rope(v, wq);
+                m.norm_rope(v, m.wq);
                 if (valid) Vec8<TQ>::store(q_out + (size_t)h * HD + d0, v);
                 h0 += step;
             }
@@ -299,9 +371,136 @@ __global__ void __launch_bounds__(kAppendWarps * 32, 6) append_fast_kernel(const
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Staged path (many tokens, 16-bit projections in the cache's dtype): one warp per token.  The token's K, V and Q
+// rows come into shared memory as a few bulk copies (each a contiguous run of up to nh * HD elements, so memory sees
+// long bursts instead of one 256/512-byte row per trip and the warp waits once, not once per head); K and Q are
+// normed and rotated in place; the rows go out as bulk copies from the same bytes (V is never touched by a lane).
+// ---------------------------------------------------------------------------------------
+namespace stg {
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bulk_load(void *dst_smem, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void *dst, const void *src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(dst), "r"(smem_u32(src_smem)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+}   // namespace stg
+
+constexpr int kTimeoutAppendStage = 17;   // status code: a token's bulk copies did not land
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(kAppendWarps * 32) append_staged_kernel(const AppendArgs a) {
+    constexpr int LPH = HD / 8, HPI = 32 / LPH;
+    extern __shared__ __align__(128) unsigned char stage_smem[];
+    __shared__ __align__(8) unsigned long long bars[kAppendWarps];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const unsigned long long tok = (unsigned long long)blockIdx.x * kAppendWarps + warp;
+    uint32_t s, j;
+    if (!locate_token(a, tok, s, j)) return;   // (nothing below synchronises across warps)
+    const uint32_t sub = lane / LPH, dl = lane % LPH, d0 = dl * 8;
+    const uint32_t kv_elems = a.nkv * HD, q_elems = a.skip_q ? 0u : a.nh * HD;
+    T *sk = reinterpret_cast<T *>(stage_smem + (size_t)warp * a.stage_bytes), *sv = sk + kv_elems, *sq = sv + kv_elems;
+    T *k_io = reinterpret_cast<T *>(a.k_io) + tok * (size_t)kv_elems;
+    const T *v_in = reinterpret_cast<const T *>(a.v_in) + tok * (size_t)kv_elems;
+    const uint32_t qrow = a.has_gate ? 2 * HD : HD;
+    const T *q_in = reinterpret_cast<const T *>(a.q_in) + tok * a.nh * (size_t)qrow;
+    const uint32_t bar = stg::smem_u32(&bars[warp]);
+    if (lane == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((2 * kv_elems + q_elems) * (uint32_t)sizeof(T)) : "memory");
+        stg::bulk_load(sk, k_io, kv_elems * sizeof(T), bar);
+        stg::bulk_load(sv, v_in, kv_elems * sizeof(T), bar);
+        if (q_elems) {
+            if (!a.has_gate) stg::bulk_load(sq, q_in, q_elems * sizeof(T), bar);
+            else for (uint32_t h = 0; h < a.nh; ++h) stg::bulk_load(sq + h * HD, q_in + (size_t)h * qrow, HD * sizeof(T), bar);   // the gate halves stay where they are
+        }
+    }
+    __syncwarp();
+    LaneMath<HD> m;
+    m.init(a, s, j, dl, sub == 0);   // (under the copies)
+    // Bounded wait for the copies.  If it runs out the code is latched and the warp waits once more, as long again,
+    // before it leaves: the shared memory must not go to another block while a copy may still land in it.
+    bool landed = false;
+    for (uint32_t round = 0; round < 2 && !landed; ++round) {
+        for (uint32_t i = 0; i < a.wait_limit && !landed; ++i) landed = stg::mbar_try(bar, 0);
+        if (!landed && round == 0) report_timeout(a.status, kTimeoutAppendStage);
+    }
+    if (!landed) return;
+    // two trips' heads per turn (norm_rope2)
+    auto heads_in_place = [&](T *rows, uint32_t n, const float (&w)[8]) {
+        for (uint32_t h0 = 0; h0 < n; h0 += 2 * HPI) {
+            const uint32_t ha = h0 + sub, hb = h0 + HPI + sub;
+            float u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (ha < n) Vec8<T>::load(rows + ha * HD + d0, u);
+            if (hb < n) Vec8<T>::load(rows + hb * HD + d0, v);
+            m.norm_rope2(u, v, w);
+            if (ha < n) Vec8<T>::store(rows + ha * HD + d0, u);
+            if (hb < n) Vec8<T>::store(rows + hb * HD + d0, v);
+        }
+    };
+    heads_in_place(sk, a.nkv, m.wk);
+    if (q_elems) heads_in_place(sq, a.nh, m.wq);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the lanes' writes, before the bulk copies read them
+    __syncwarp();
+    if (lane == 0) {
+        const size_t row_bytes = (size_t)kv_elems * sizeof(T);
+        stg::bulk_store(const_cast<char *>(kv_row_ptr(a.kv, false, s, m.p_t, row_bytes)), sk, (uint32_t)row_bytes);
+        stg::bulk_store(const_cast<char *>(kv_row_ptr(a.kv, true, s, m.p_t, row_bytes)), sv, (uint32_t)row_bytes);
+        if (a.write_k_back) stg::bulk_store(k_io, sk, (uint32_t)row_bytes);
+        if (q_elems) stg::bulk_store(reinterpret_cast<T *>(a.q_out) + tok * (size_t)q_elems, sq, q_elems * sizeof(T));
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the block's shared memory stays until the copies have read it
+    }
+    __syncwarp();
+}
+
+// The staged kernel takes a pass when every token has a warp's worth of work anyway (no head slices), the three
+// tensors share one 16-bit type, nobody wants the gate copied out, and four tokens' rows fit a block's shared memory.
+template <typename T>
+static bool try_append_staged(shady_ctx *ctx, AppendArgs &a, unsigned long long toks) {
+    if (a.has_gate && a.q_gate) return false;
+    if (toks < (unsigned long long)ctx->num_sms * 8) return false;
+    const size_t stage = ((size_t)(2 * a.nkv + (a.skip_q ? 0 : a.nh)) * a.hd * sizeof(T) + 127) & ~(size_t)127;
+    const size_t smem = stage * kAppendWarps;
+    if (smem > 96 * 1024) return false;   // (two blocks of four warps per SM at least)
+    if (!a.skip_q && (((uintptr_t)a.q_in | (uintptr_t)a.q_out) & 15)) return false;
+    if ((((uintptr_t)a.k_io | (uintptr_t)a.v_in | (uintptr_t)a.kv.k_base | (uintptr_t)a.kv.v_base) & 15) || (a.kv.seq_stride_bytes & 15) ||
+        (a.kv.page_bytes & 15))
+        return false;   // bulk copies start on 16-byte boundaries
+    a.head_slices = 1;
+    a.stage_bytes = (uint32_t)stage; a.wait_limit = ctx->wait_mbar; a.status = status_ref(ctx);
+    const unsigned blocks = (unsigned)((toks + kAppendWarps - 1) / kAppendWarps);
+    auto launch = [&](auto kernel) {
+        if (smem > 40 * 1024 &&   // (the kernel's static words count against the 48 KB a launch gets unasked)
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        kernel<<<blocks, kAppendWarps * 32, smem, ctx->stream>>>(a);
+        return true;
+    };
+    return a.hd == 128 ? launch(append_staged_kernel<T, 128>) : launch(append_staged_kernel<T, 256>);
+}
+
 template <typename TIn, typename TQ, typename TKV>
 static void launch_append_fast(shady_ctx *ctx, AppendArgs &a) {
     const unsigned long long toks = a.tok_start ? a.total_tokens : (unsigned long long)a.num_seqs * a.T;
+    if constexpr (std::is_same<TIn, TQ>::value && std::is_same<TIn, TKV>::value && sizeof(TIn) == 2) {
+        if (try_append_staged<TIn>(ctx, a, toks)) return;
+    }
     // enough warps to fill the GPU: split a token's heads over several warps when there are few tokens
     const uint32_t hpi = 32 / (a.hd / 8);
     const uint32_t max_slices = ((a.skip_q ? a.nkv : a.nh) + hpi - 1) / hpi;

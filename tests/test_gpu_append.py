@@ -123,3 +123,54 @@ def test_plain_q_without_gate_bf16_in_bf16_out(gpu_ctx, oracle):
         assert np.abs(to_host(d_q)[j] - oq).max() <= 2.0 ** -7 * np.abs(oq).max()
     assert np.abs(to_host(d_kc) - okc).max() <= 2.0 ** -7 * np.abs(okc).max()
     np.testing.assert_array_equal(to_host(d_vc), ovc)
+
+
+@pytest.mark.parametrize("dt", [F16, BF16])
+@pytest.mark.parametrize("hd,nh,nkv", [(128, 8, 2), (256, 4, 1)])
+@pytest.mark.parametrize("write_k_back", [False, True])
+def test_many_token_pass_equals_per_sequence_passes(gpu_ctx, oracle, dt, hd, nh, nkv, write_k_back):
+    """A pass over enough tokens to give every warp one (rows staged through shared memory by bulk copies) against
+    the same tokens appended one sequence per call (few enough tokens for the register kernel): bit for bit; and a
+    few tokens against the oracle."""
+    S, T, rd = 3, 512, hd // 4
+    starts = [0, 37, 1000]
+    rows = 1600
+    q_in = rounded(oracle, oracle.randn((S, T, nh, hd), 23, 1), dt)
+    k_in = rounded(oracle, oracle.randn((S, T, nkv, hd), 23, 2), dt)
+    v_in = rounded(oracle, oracle.randn((S, T, nkv, hd), 23, 3), dt)
+    w = oracle.bf16_bits(oracle.randn((2 * hd,), 23, 4) * np.float32(0.02))
+    d_w = torch.from_numpy(w.view(np.int16)).cuda()
+
+    def run(seqs, batched):
+        d_kc = torch.zeros((S, rows, nkv, hd), dtype=TORCH_DT[dt], device="cuda")
+        d_vc = torch.zeros_like(d_kc)
+        d_q = torch.zeros((S, T, nh, hd), dtype=TORCH_DT[dt], device="cuda")
+        d_k = to_dev(k_in, dt)
+        d_qi, d_v = to_dev(q_in, dt), to_dev(v_in, dt)
+        calls = [list(seqs)] if batched else [[s] for s in seqs]
+        for group in calls:
+            s0, n = group[0], len(group)
+            ops.kv_append_rope(gpu_ctx, q_proj_full=d_qi[s0:s0 + n], k_proj=d_k[s0:s0 + n], v_proj=d_v[s0:s0 + n],
+                               q_out=d_q[s0:s0 + n], q_gate=None,
+                               cache=ops.KvCacheView(dt, d_kc[s0:s0 + n], d_vc[s0:s0 + n], rows * nkv * hd),
+                               pos_start=torch.tensor(starts[s0:s0 + n], dtype=torch.int32).cuda(), num_heads=nh,
+                               num_kv_heads=nkv, head_dim=hd, rope_theta=1e7, rotary_dim=rd, qk_norm_bf16=d_w,
+                               num_seqs=n, tokens_per_seq=T, in_dtype=dt, q_dtype=dt, has_gate=False,
+                               write_k_back=write_k_back)
+        gpu_ctx.synchronize()
+        return [t.view(torch.int16).cpu().numpy() for t in (d_q, d_k, d_kc, d_vc)], (d_q, d_kc)
+
+    many, (d_q, d_kc) = run(range(S), True)
+    each, _ = run(range(S), False)
+    for a, b in zip(many, each):
+        np.testing.assert_array_equal(a, b)
+    if write_k_back:   # the rotated K went back over the projection
+        np.testing.assert_array_equal(many[1].reshape(S, T, nkv, hd)[1], many[2][1, starts[1]:starts[1] + T])
+    q, kc = to_host(d_q), to_host(d_kc)
+    okc, ovc = np.zeros((rows, nkv, hd), np.float32), np.zeros((rows, nkv, hd), np.float32)
+    for s, j in [(0, 0), (1, 300), (2, T - 1)]:
+        qf = np.stack([q_in[s, j], np.zeros_like(q_in[s, j])], axis=1)
+        oq, _, _ = oracle.fused_split_qknorm_kvstore(qf, k_in[s, j], v_in[s, j], okc, ovc, starts[s] + j, rope_theta=1e7,
+                                                     rotary_dim=rd, qk_norm_bf16=w)
+        assert np.abs(q[s, j] - oq).max() <= 2.0 ** -7 * np.abs(oq).max()
+        assert np.abs(kc[s, starts[s] + j] - okc[starts[s] + j]).max() <= 2.0 ** -7 * np.abs(okc[starts[s] + j]).max()

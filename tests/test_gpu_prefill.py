@@ -183,6 +183,12 @@ def test_prefill_from_the_projections_head_dim_256(gpu_ctx, oracle, rd, norm, ga
     _fused_case(gpu_ctx, oracle, 2, 300, 4, 2, BF16, 55, rd, norm, gate, hd=256)
 
 
+def test_prefill_from_the_projections_head_dim_256_many_tokens(gpu_ctx, oracle):
+    """Enough tokens for the append pass to stage each token's rows through shared memory (Q heads fetched one by
+    one past their gate halves)."""
+    _fused_case(gpu_ctx, oracle, 2, 700, 4, 2, BF16, 56, 64, True, True, hd=256)
+
+
 def test_prefill_from_the_projections_f16_ragged_and_many_items(gpu_ctx, oracle):
     _fused_case(gpu_ctx, oracle, 1, 333, 4, 2, F16, 52, 32, True, True, cap=400)
     # more items than SMs, so every CTA walks several and the three Q buffers rotate through their phases
