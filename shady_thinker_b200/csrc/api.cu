@@ -186,6 +186,7 @@ int shady_ctx_create(int device, void *stream, shady_ctx **out) {
     c->knobs.grid_merge = env_u32("SHADY_DECODE_GRID_MERGE", 1);
     c->knobs.interleave = env_u32("SHADY_DECODE_INTERLEAVE", 1);
     c->knobs.pad = env_u32("SHADY_DECODE_PAD", ~0u);
+    c->knobs.early_launch = env_u32("SHADY_DECODE_EARLY_LAUNCH", 1);
     *out = c;
     return SHADY_OK;
 }

@@ -20,6 +20,7 @@ struct DecodeKnobs {
     uint32_t grid_merge = 1;    // SHADY_DECODE_GRID_MERGE=0: merge many-span sequences in a second launch
     uint32_t interleave = 1;    // SHADY_DECODE_INTERLEAVE=0: fixed spans for a single long sequence
     uint32_t pad = ~0u;         // SHADY_DECODE_PAD: line units that a sequence boundary costs a span (unset: from the block size)
+    uint32_t early_launch = 1;  // SHADY_DECODE_EARLY_LAUNCH=0: plain stream order between a decode launch and the kernel before it
 };
 
 struct shady_ctx {

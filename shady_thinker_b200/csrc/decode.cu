@@ -957,6 +957,11 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
     uint32_t *sm_item = reinterpret_cast<uint32_t *>(smem + S::kQBytes + NW * S::kWarpBytes + S::kStatBytes);  // 8 words
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // A launch in programmatic stream order (the host launcher) starts while the kernel before it drains: let the
+    // next launch do the same with this one, and read nothing that kernel may have written before it has completed.
+    // Both are no-ops in a plain launch.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // blockIdx.x = (work * KG + kg) * gz + z, KG = nkv / KPC groups of kv heads
     const uint32_t KG = a.nkv / KPC;
     const uint32_t zi = blockIdx.x % a.gz, kg = (blockIdx.x / a.gz) % KG;
@@ -1795,13 +1800,22 @@ static int launch16(shady_ctx *ctx, const DecodeArgs &a, uint32_t blocks) {
         SHADY_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
         configured_dev = ctx->device;
     }
-    if (a.grid_merge) {   // the grid barrier needs every CTA resident: a cooperative launch, refused if they would not fit
-        void *params[] = {const_cast<DecodeArgs *>(&a)};
-        SHADY_CUDA_OK(ctx, cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kern), dim3(blocks), dim3(NW * 32), params,
-                                                       S::kTotal, ctx->stream));
-    } else {
-        kern<<<blocks, NW * 32, S::kTotal, ctx->stream>>>(a);
+    // Programmatic stream order: the CTAs of this launch may become resident while the kernel before it in the
+    // stream drains (a decode launch ends with a few CTAs merging records while the other SMs idle) and wait at the
+    // kernel's first instructions until that kernel has completed and its writes are visible.
+    // The grid barrier needs every CTA resident: a cooperative launch, refused if they would not fit.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks); cfg.blockDim = dim3(NW * 32); cfg.dynamicSmemBytes = S::kTotal; cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2]{};
+    unsigned n = 0;
+    if (a.grid_merge) { attr[n].id = cudaLaunchAttributeCooperative; attr[n].val.cooperative = 1; ++n; }
+    if (ctx->knobs.early_launch && !a.grid_merge) {   // (measured on cooperative launches too: no gain)
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
     }
+    cfg.attrs = attr; cfg.numAttrs = n;
+    SHADY_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, kern, a));
     ctx->launches++;
     SHADY_CUDA_OK(ctx, cudaGetLastError());
     return SHADY_OK;
