@@ -403,6 +403,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                          "peak_source": f"{peak_src} (copy bandwidth)",
                          "kernel": ("decode16_kernel<half,128> with the fused append and split merge (the whole step is this one launch)"
                                     if args.kv == "fp16" else
+                                    "decode16_kernel<half,128,8-bit cache> with the fused (quantising) append and split merge "
+                                    "(the whole step is this one launch)" if d0.fused else
                                     "decode16_kernel<half,128,8-bit cache> (the step is the append launch plus this attend launch)"),
                          "traffic_source": f"algorithmic bytes x {TRAFFIC_PER_ALGO_BYTE[args.kv]}, the DRAM-byte ratio ncu measured at {TRAFFIC_MEASURED_AT}",
                          "algorithmic_bytes_per_launch": step_bytes, "avg_launch_ms": attend_ms,

@@ -226,7 +226,8 @@ int shady_attn_decode(shady_ctx *ctx, const shady_decode_params *p, const void *
                       void *d_workspace, size_t workspace_bytes);
 
 /* Append and attend in ONE launch — the three calls of a self-attention layer (model.rs:723-725:
- * fused_split_qknorm_kvstore, gqa_attention, sigmoid_mul_gate) for a batch of sequences with 16-bit caches.
+ * fused_split_qknorm_kvstore, gqa_attention, sigmoid_mul_gate) for a batch of sequences with 16-bit or 8-bit
+ * caches (8-bit: f16 or f32 projections; the new rows are quantised as shady_kv_append_rope quantises them).
  * Q is normed/rotated while it is staged; the CTA that owns the tail of a sequence norms/rotates the new K row,
  * stores it and the V row at row seq_len-1 of the cache, then streams them with the rest.  `ap` describes the
  * projections as in shady_kv_append_rope (tokens_per_seq must be 1, interleaved RoPE, one position per token:

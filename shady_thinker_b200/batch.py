@@ -28,7 +28,7 @@ class BatchedDecoder:
                  num_layers: int = 1, num_splits: int = 0, qk_norm_bf16=None, k_scale: float = 0.0,
                  v_scale: float = 0.0):
         """``kv_dtype=F8E4M3`` / ``F8E5M2`` keeps the caches as 8-bit floats (``k_scale`` / ``v_scale``: value = stored *
-        scale, 0 means 1); activations are then f16 and a step is the append launch followed by the attend launch."""
+        scale, 0 means 1); activations are then f16."""
         self.gpu, self.S, self.nh, self.nkv, self.hd = gpu, num_seqs, num_heads, num_kv_heads, head_dim
         self.kv_dtype = kv_dtype
         if act_dtype is None:
@@ -38,8 +38,8 @@ class BatchedDecoder:
         self.interleaved, self.eps, self.has_gate = interleaved, eps, has_gate
         self.num_layers, self.num_splits = num_layers, num_splits
         self.qk_norm = qk_norm_bf16   # device buffer: bf16 q_norm[hd] then k_norm[hd] (model.rs:140-168), or None
-        self.fused = (not os.environ.get("SHADY_NO_FUSED_APPEND") and kv_dtype in (F16, BF16) and interleaved
-                      and act_dtype in (F32, kv_dtype))
+        self.fused = (not os.environ.get("SHADY_NO_FUSED_APPEND") and interleaved and
+                      act_dtype in ((F32, F16) if kv_dtype in (F8E4M3, F8E5M2) else (F32, kv_dtype)) and kv_dtype != F32)
         caps = np.asarray(capacities, dtype=np.int64)
         assert caps.shape == (num_seqs,)
         row = num_kv_heads * head_dim
@@ -117,8 +117,8 @@ class BatchedDecoder:
                         out_dtype=self.act_dtype, gate=self.q_gate, workspace=self.ws, workspace_bytes=self.ws_bytes)
 
     def step(self, layer: int = 0) -> None:
-        """Device-resident step: activations already in q_in/k_in/v_in.  16-bit caches take the single fused
-        launch (append + attend + gate); fp32 caches the reference's sequence of calls."""
+        """Device-resident step: activations already in q_in/k_in/v_in.  16-bit and 8-bit caches take the
+        single fused launch (append + attend + gate); fp32 caches the reference's sequence of calls."""
         if self.fused:
             self.step_fused(layer)
         else:
@@ -153,9 +153,9 @@ class BatchedDecoder:
     def step_from_pinned(self, q_host: int, k_host: int, v_host: int, out_host: int, layer: int = 0) -> None:
         """Full step on page-locked host buffers without copies: the fused launch reads the activations from host
         memory and writes the output rows there itself (the bytes still cross the host link, inside the kernel);
-        returns when the output has arrived.  16-bit caches only (needs the fused launch)."""
+        returns when the output has arrived.  Not for fp32 caches (needs the fused launch)."""
         if not self.fused:
-            raise ValueError("step_from_pinned needs the fused append+attend launch (16-bit cache, interleaved RoPE)")
+            raise ValueError("step_from_pinned needs the fused append+attend launch (16-bit or 8-bit cache, interleaved RoPE)")
         key = (q_host, k_host, v_host, out_host)
         if getattr(self, "_pinned_key", None) != key:
             self._pinned = tuple(self.gpu.host_device_ptr(a) for a in key)

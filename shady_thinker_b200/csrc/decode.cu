@@ -553,6 +553,11 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
 //    and the add are written as multiply-adds so that they can go to the FMA pipe: widening the bytes is integer
 //    work, and it is the integer pipe, not memory, that bounds this kernel (cvt.rn.f16x2.e4m3x2 measured no faster).
 __host__ __device__ constexpr float f8_unscale(int fmt) { return fmt == 1 ? 256.0f : 1.0f; }
+// One value into the cache's 8-bit format (1: e4m3, 2: e5m2), rounded and saturated as the stand-alone append does it.
+template <int FMT> __device__ __forceinline__ unsigned char f32_to_f8(float v) {
+    if constexpr (FMT == 2) return __nv_fp8_e5m2(v).__x;
+    else return __nv_fp8_e4m3(v).__x;
+}
 template <int FMT, uint32_t SEL> __device__ __forceinline__ uint32_t f8x2_to_f16x2(uint32_t x) {
     if constexpr (FMT == 2) {
         // result byte 1 <- x byte (SEL & 0xf), result byte 3 <- x byte (SEL >> 4), bytes 0 and 2 <- 0
@@ -1022,7 +1027,7 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
         // The pipeline moves single tiles: item 2i is the K tile of the warp's i-th block, item 2i+1 its V tile,
         // item t lives in slot t % STAGES, and STAGES-1 items are in flight while one is being consumed.
         constexpr int NIT = (2 * CH + 31) / 32;   // K and V chunks per lane
-        const bool tail = !ILV && !F8 && a.fuse_append && p.L > 0 && p.end == p.L;
+        const bool tail = !ILV && a.fuse_append && p.L > 0 && p.end == p.L;
         const bool owner = tail && ((nblk - 1) % WPK == sub) && KPC == 1;
         // interleaved mode: the warp's i-th block is block ilv_g + i * ilv_w of the sequence
         const uint32_t ilv_w = a.spans * NW, ilv_g = work * NW + warp;
@@ -1036,8 +1041,12 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
                 const uint32_t tt = lane + 32 * it;
                 if (tt < 2 * CH && tt / CH == want_v) {
                     const uint32_t c = tt % CH;
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_addr + r * S::kRowBytes + ((c ^ (r & 7)) << 4)),
-                                 "r"(newrow[it].x), "r"(newrow[it].y), "r"(newrow[it].z), "r"(newrow[it].w) : "memory");
+                    if constexpr (F8)   // eight bytes: half (c & 1) of the row's 16-byte chunk c / 2
+                        asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(tile_addr + r * S::kRowBytes + (((c >> 1) ^ (r & 7)) << 4) + (c & 1) * 8),
+                                     "r"(newrow[it].x), "r"(newrow[it].y) : "memory");
+                    else
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_addr + r * S::kRowBytes + ((c ^ (r & 7)) << 4)),
+                                     "r"(newrow[it].x), "r"(newrow[it].y), "r"(newrow[it].z), "r"(newrow[it].w) : "memory");
                 }
             }
             __syncwarp();
@@ -1116,6 +1125,18 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
             }
         }
         // stage Q of the CTA's kv heads (rows >= rows_valid are zero) as T, swizzled
+        auto store_q_chunk = [&](uint32_t k, uint32_t r, uint32_t c, const uint4 &v) {
+            if constexpr (F8) {
+                // dims 8c .. 8c+7 of the 16-dim group c/2: the pair (4u, 4u+1) goes to column 2u, the pair (4u+2, 4u+3)
+                // to column 8 + 2u of the group (u = 2*(c&1), 2*(c&1)+1): two 8-byte halves in the group's two chunks
+                const uint32_t u2 = (c & 1) * 2, grp = c >> 1;
+                unsigned char *rowp = sm_q + k * S::kQTile + r * S::kQRowBytes;
+                *reinterpret_cast<uint2 *>(rowp + (((2 * grp) ^ (r & 7)) << 4) + u2 * 4) = make_uint2(v.x, v.z);
+                *reinterpret_cast<uint2 *>(rowp + (((2 * grp + 1) ^ (r & 7)) << 4) + u2 * 4) = make_uint2(v.y, v.w);
+            } else {
+                *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kQRowBytes + ((c ^ (r & 7)) << 4)) = v;
+            }
+        };
         if (a.fuse_append) {
             // raw Q row -> RMSNorm(1+w) -> RoPE at position L-1 (wgsl:126-166); CH consecutive threads share a row.
             // cos/sin of the rotary pairs are the same for all rows: one table per piece in the merge-statistics area
@@ -1155,7 +1176,7 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
                 }
                 uint4 v;
                 v.x = pack2<T>(v8[0], v8[1]); v.y = pack2<T>(v8[2], v8[3]); v.z = pack2<T>(v8[4], v8[5]); v.w = pack2<T>(v8[6], v8[7]);
-                *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kQRowBytes + ((c ^ (r & 7)) << 4)) = v;
+                store_q_chunk(k, r, c, v);
             }
         } else
         for (uint32_t idx = tid; idx < KPC * 16 * CH; idx += NW * 32) {
@@ -1172,16 +1193,7 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
                     v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.q) + e0);
                 }
             }
-            if constexpr (F8) {
-                // dims 8c .. 8c+7 of the 16-dim group c/2: the pair (4u, 4u+1) goes to column 2u, the pair (4u+2, 4u+3)
-                // to column 8 + 2u of the group (u = 2*(c&1), 2*(c&1)+1): two 8-byte halves in the group's two chunks
-                const uint32_t u2 = (c & 1) * 2, grp = c >> 1;
-                unsigned char *rowp = sm_q + k * S::kQTile + r * S::kQRowBytes;
-                *reinterpret_cast<uint2 *>(rowp + (((2 * grp) ^ (r & 7)) << 4) + u2 * 4) = make_uint2(v.x, v.z);
-                *reinterpret_cast<uint2 *>(rowp + (((2 * grp + 1) ^ (r & 7)) << 4) + u2 * 4) = make_uint2(v.y, v.w);
-            } else {
-                *reinterpret_cast<uint4 *>(sm_q + k * S::kQTile + r * S::kQRowBytes + ((c ^ (r & 7)) << 4)) = v;
-            }
+            store_q_chunk(k, r, c, v);
         }
         __syncthreads();
         if (owner) {   // (fused append, second half) norm + RoPE of the new K row, V as it is; cache stores; kept for the patch
@@ -1215,11 +1227,21 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
                         v8[2 * k2 + 1] = y * t2.x + x * t2.y;
                     }
                 }
-                newrow[it].x = pack2<T>(v8[0], v8[1]); newrow[it].y = pack2<T>(v8[2], v8[3]);
-                newrow[it].z = pack2<T>(v8[4], v8[5]); newrow[it].w = pack2<T>(v8[6], v8[7]);
-                if (act) {
-                    char *dst = const_cast<char *>(kv_row_ptr(a.kv, is_v != 0, p.seq, pos, pos_stride)) + (size_t)kvh * S::kRowBytes;
-                    *reinterpret_cast<uint4 *>(dst + c * 16) = newrow[it];
+                char *dst = act ? const_cast<char *>(kv_row_ptr(a.kv, is_v != 0, p.seq, pos, pos_stride)) + (size_t)kvh * S::kRowBytes : nullptr;
+                if constexpr (F8) {   // stored = value / scale, rounded as the stand-alone append rounds it
+                    const float inv = 1.0f / (is_v ? a.kv.v_scale : a.kv.k_scale);
+                    uint32_t lo = 0, hi = 0;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        lo |= (uint32_t)f32_to_f8<F8>(v8[e] * inv) << (8 * e);
+                        hi |= (uint32_t)f32_to_f8<F8>(v8[4 + e] * inv) << (8 * e);
+                    }
+                    newrow[it] = make_uint4(lo, hi, 0u, 0u);
+                    if (act) *reinterpret_cast<uint2 *>(dst + c * 8) = make_uint2(newrow[it].x, newrow[it].y);
+                } else {
+                    newrow[it].x = pack2<T>(v8[0], v8[1]); newrow[it].y = pack2<T>(v8[2], v8[3]);
+                    newrow[it].z = pack2<T>(v8[4], v8[5]); newrow[it].w = pack2<T>(v8[6], v8[7]);
+                    if (act) *reinterpret_cast<uint4 *>(dst + c * 16) = newrow[it];
                 }
             }
         }
@@ -1246,6 +1268,7 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
                 cp_async_commit();
                 const uint32_t st = warp_smem + ((2 * i) % STAGES) * S::kTileBytes;
                 const uint32_t pos0 = start + block_of(i) * kBlk;
+                if (owner && i == w_n - 1) patch_tile(st, pos0, 0u);
                 // ---- S^T = K Q^T : 16 positions x 8 heads ----
                 float sT[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -1288,6 +1311,7 @@ __global__ void __launch_bounds__(NW * 32, (F8 && HD <= 128) ? 3 : decode16_min_
                 if (2 * i + STAGES < w_items) issue(2 * i + STAGES, block_of(i + kOffV));   // into the slot of the K tile just consumed
                 cp_async_commit();
                 const uint32_t stv = warp_smem + ((2 * i + 1) % STAGES) * S::kTileBytes;
+                if (owner && i == w_n - 1) patch_tile(stv, pos0, 1u);
 #pragma unroll
                 for (int c = 0; c < HD / 16; c += 2) {
                     uint32_t vb[4];   // (pos 0-7, chunk c), (pos 8-15, chunk c), (pos 0-7, chunk c+1), (pos 8-15, chunk c+1)
@@ -1952,8 +1976,8 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
                   "decode: q_dtype must be f32 or the cache dtype (f16 for an 8-bit cache)");
     SHADY_REQUIRE(ctx, p->out_dtype == SHADY_F32 || p->out_dtype == act_dtype, SHADY_ERR_UNSUPPORTED,
                   "decode: out_dtype must be f32 or the cache dtype (f16 for an 8-bit cache)");
-    SHADY_REQUIRE(ctx, !f8 || (!fa && !d_force_partials), SHADY_ERR_UNSUPPORTED,
-                  "decode: an 8-bit cache is read by shady_attn_decode / _static / _shard (append with shady_kv_append_rope)");
+    SHADY_REQUIRE(ctx, !f8 || !d_force_partials, SHADY_ERR_UNSUPPORTED,
+                  "decode: an 8-bit cache is read by shady_attn_decode / _static / _shard / _append");
     if (const int st = pending_timeout(ctx, "decode")) return st;
     const uint32_t hd = p->head_dim;
     SHADY_REQUIRE(ctx, hd <= 256, SHADY_ERR_UNSUPPORTED, "decode: head_dim > 256 (the reference shader's limit)");

@@ -140,13 +140,13 @@ def test_append_quantises_like_the_oracle(gpu_ctx, oracle, in_dt, rd, norm, fmt)
 
 
 def test_batched_decoder_with_an_e4m3_cache(gpu_ctx, oracle):
-    """Three steps of a ragged batch through BatchedDecoder(kv_dtype=F8E4M3): append launch + attend launch per step,
+    """Three steps of a ragged batch through BatchedDecoder(kv_dtype=F8E4M3) — the fused append + attend launch —
     against f64 attention over a host mirror of the quantised cache."""
     S, nh, nkv, hd, steps, ks, vs = 4, 8, 2, 128, 3, 0.05, 0.05
     start = np.array([0, 40, 1000, 3000], np.uint32)
     d = BatchedDecoder(gpu_ctx, num_seqs=S, capacities=start + steps, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
                        kv_dtype=F8E4M3, rope_theta=1e6, rotary_dim=hd, has_gate=False, num_splits=0, k_scale=ks, v_scale=vs)
-    assert not d.fused and d.act_dtype == F16
+    assert d.fused and d.act_dtype == F16
     rows = int(d.row_off[-1])
     rk, rv = oracle.randn((rows, nkv, hd), 84, 1), oracle.randn((rows, nkv, hd), 84, 2)
     hk, hv = oracle.round_e4m3(rk, ks), oracle.round_e4m3(rv, vs)
@@ -179,13 +179,68 @@ def test_batched_decoder_with_an_e4m3_cache(gpu_ctx, oracle):
 def test_entry_points_that_do_not_take_an_e4m3_cache_say_so(gpu_ctx):
     d = torch.zeros(4096, dtype=torch.float16, device="cuda")
     c8 = torch.zeros(4096, dtype=torch.uint8, device="cuda")
-    lens = torch.ones(1, dtype=torch.int32, device="cuda")
-    with pytest.raises(ShadyError) as e:
-        ops.attn_decode_append(gpu_ctx, q_proj_full=d, k_proj=d, v_proj=d, cache=ops.KvCacheView(F8E4M3, c8, c8, 0), seq_lens=lens,
-                               out=d, num_heads=4, num_kv_heads=1, head_dim=128, rope_theta=1e6, rotary_dim=128, in_dtype=F16,
-                               out_dtype=F16, has_gate=False, seq_lens_host=[1], num_splits=1)
-    assert e.value.code == 2
     with pytest.raises(ShadyError) as e:
         ops.attn_prefill(gpu_ctx, q=d, cache=ops.KvCacheView(F8E4M3, c8, c8, 0), out=d, head_dim=128, num_kv_heads=1,
                          num_q_heads=1, num_seqs=1, seq_len=8, dtype=F16)
     assert e.value.code == 2
+
+
+@pytest.mark.parametrize("fmt", [F8E4M3, F8E5M2])
+@pytest.mark.parametrize("hd,nh,nkv,lens", [(128, 32, 8, [1, 16, 17, 700, 2500, 33]), (128, 16, 1, [20000, 50]),
+                                            (256, 8, 2, [300, 4097, 1])], ids=["short", "long-16-heads", "hd256"])
+@pytest.mark.parametrize("in_dt,norm,gate,rd_div", [(F16, False, False, 1), (F32, True, True, 4)])
+def test_fused_append_decode_on_an_8bit_cache_equals_the_two_calls(gpu_ctx, oracle, fmt, hd, nh, nkv, lens, in_dt, norm, gate, rd_div):
+    """shady_attn_decode_append over an 8-bit cache == shady_kv_append_rope followed by shady_attn_decode: the new
+    rows quantised into the cache (and patched into the tiles in flight), the older rows untouched."""
+    S, rd, ks, vs = len(lens), hd // rd_div, 0.05, 0.125     # lengths INCLUDE the appended token
+    qmul = 2 if gate else 1
+    rnd = (lambda a: oracle.round_f16(a)) if in_dt == F16 else (lambda a: a)
+    q_full = rnd(oracle.randn((S, nh, qmul * hd), 91, 1))
+    k_new, v_new = rnd(oracle.randn((S, nkv, hd), 91, 2)), rnd(oracle.randn((S, nkv, hd), 91, 3))
+    w = oracle.bf16_bits(oracle.randn((2 * hd,), 91, 4) * np.float32(0.02)) if norm else None
+    d_w = torch.from_numpy(w.view(np.int16)).cuda() if norm else None
+    kraw = [oracle.randn((L, nkv, hd), 91, 10 + i) for i, L in enumerate(lens)]
+    vraw = [oracle.randn((L, nkv, hd), 91, 50 + i) for i, L in enumerate(lens)]
+    d_lens = torch.tensor(lens, dtype=torch.int32).cuda()
+    d_pos = torch.tensor([L - 1 for L in lens], dtype=torch.int32).cuda()
+    ws_n = ops.decode_workspace_size(head_dim=hd, num_kv_heads=nkv, num_q_heads=nh, num_splits=0, num_seqs=S)
+    ws = torch.zeros(ws_n, dtype=torch.uint8, device="cuda")
+
+    def caches():
+        dk = [_to_e4m3_dev(_stored(oracle, fmt, k, ks), fmt) for k in kraw]
+        dv = [_to_e4m3_dev(_stored(oracle, fmt, v, vs), fmt) for v in vraw]
+        k_ptrs = torch.tensor([t.data_ptr() for t in dk], dtype=torch.int64).cuda()
+        v_ptrs = torch.tensor([t.data_ptr() for t in dv], dtype=torch.int64).cuda()
+        return dk, dv, (k_ptrs, v_ptrs), ops.KvCacheView(fmt, k_ptrs=k_ptrs, v_ptrs=v_ptrs, k_scale=ks, v_scale=vs)
+
+    # --- reference: two calls ---
+    k1, v1, _keep1, view1 = caches()
+    d_q = torch.empty((S, nh, hd), dtype=torch.float16 if in_dt == F16 else torch.float32, device="cuda")
+    d_g = torch.empty((S, nh, hd), device="cuda") if gate else None
+    ops.kv_append_rope(gpu_ctx, q_proj_full=to_dev(q_full, in_dt), k_proj=to_dev(k_new, in_dt), v_proj=to_dev(v_new, in_dt),
+                       q_out=d_q, q_gate=d_g, cache=view1, pos_start=d_pos, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                       rope_theta=1e6, rotary_dim=rd, qk_norm_bf16=d_w, num_seqs=S, in_dtype=in_dt, q_dtype=in_dt,
+                       has_gate=gate, write_k_back=False)
+    want = torch.empty((S, nh, hd), device="cuda")
+    ops.attn_decode(gpu_ctx, q=d_q, cache=view1, seq_lens=d_lens, out=want, head_dim=hd, num_kv_heads=nkv, num_q_heads=nh,
+                    num_seqs=S, num_splits=0, seq_lens_host=lens, q_dtype=in_dt, gate=d_g, workspace=ws, workspace_bytes=ws_n)
+    gpu_ctx.synchronize()
+    # --- fused: one call on a fresh copy of the caches ---
+    k2, v2, _keep2, view2 = caches()
+    got = torch.full((S, nh, hd), float("nan"), device="cuda")
+    ops.attn_decode_append(gpu_ctx, q_proj_full=to_dev(q_full, in_dt), k_proj=to_dev(k_new, in_dt), v_proj=to_dev(v_new, in_dt),
+                           cache=view2, seq_lens=d_lens, out=got, num_heads=nh, num_kv_heads=nkv, head_dim=hd, rope_theta=1e6,
+                           rotary_dim=rd, num_seqs=S, qk_norm_bf16=d_w, in_dtype=in_dt, has_gate=gate, seq_lens_host=lens,
+                           workspace=ws, workspace_bytes=ws_n)
+    gpu_ctx.synchronize()
+    for i, L in enumerate(lens):
+        a, b = k1[i].float().cpu().numpy(), k2[i].float().cpu().numpy()
+        # the two kernels may contract their FMAs differently: a value that sits on a rounding boundary may land on
+        # the neighbouring 8-bit code (one step = 2^-3 relative for e4m3, 2^-2 for e5m2), nothing more
+        step = 2.0 ** -3 if fmt == F8E4M3 else 2.0 ** -2
+        assert np.all(np.abs(b[L - 1] - a[L - 1]) <= step * np.abs(a[L - 1]) + 1e-6), (i, L)
+        assert np.mean(b[L - 1] != a[L - 1]) <= 0.01, (i, L)
+        np.testing.assert_array_equal(v2[i].view(torch.uint8).cpu().numpy()[L - 1], v1[i].view(torch.uint8).cpu().numpy()[L - 1])
+        np.testing.assert_array_equal(b[:L - 1], a[:L - 1])                               # older rows untouched
+        np.testing.assert_array_equal(v2[i].view(torch.uint8).cpu().numpy()[:L - 1], v1[i].view(torch.uint8).cpu().numpy()[:L - 1])
+        assert rel_err(to_host(got)[i], to_host(want)[i]) <= RTOL_16, (i, L)
