@@ -34,9 +34,9 @@ N_SETS = 3            # rotating cache sets so no step finds its KV rows in L2
 # DRAM bytes (read + write, one launch) per algorithmic byte of the headline decode kernel, as ncu counted them on
 # this workload, and the commit whose kernel was captured; the ratio is a property of the kernel's access pattern,
 # so a launch timed here is credited with its own algorithmic bytes times this figure.
-TRAFFIC_PER_ALGO_BYTE = {"fp16": 1.010, "fp8": 1.019, "fp8e5m2": 1.022}   # by cache format, from the captures under profiles/
+TRAFFIC_PER_ALGO_BYTE = {"fp16": 1.010, "fp8": 1.023, "fp8e5m2": 1.026}   # by cache format, from the captures under profiles/
 TRAFFIC_MEASURED_AT = ("8ae8e09 for fp16 (ncu --set full, one launch of decode16_kernel<half,128>: 524.2 MB read + 4.1 MB written for 523.3 MB "
-                       "algorithmic), 38616fd for the 8-bit caches (e4m3 262.5 + 4.2, e5m2 262.6 + 4.7 for 261.6)")
+                       "algorithmic), e207074 for the 8-bit caches (fused step; e4m3 262.7 + 5.0, e5m2 262.6 + 5.8 for 261.6)")
 
 
 def draw_lengths(rank: int) -> np.ndarray:
