@@ -2075,10 +2075,11 @@ static int plan_decode(shady_ctx *ctx, const shady_decode_params *p, const void 
         // of K and V at a CTA's share of the memory bandwidth (steps measured with 0/12/20/25/32/40/56 blocks lie within
         // 2 % of each other, the best between 32 and 40); the SHADY_DECODE_PAD knob overrides (0 = none)
         if (p->num_seqs > 1 && !f32) {
-            // (e5m2 caches count as 16-bit here: their blocks take about as long; with e4m3, where widening the bytes
-            //  bounds the launch and three CTAs share an SM, a pad measured no gain: 75.6 us without, 76.0-76.5 with)
+            // (8-bit caches: three CTAs share an SM and a boundary idles a third of its streams; half the 16-bit figure
+            //  measured best for both formats on the cfg2 batch: e4m3 70.9 / 70.7 / 70.1 / 72.3 / 78.8 us with
+            //  0 / 8 / 16 / 32 / 64 blocks, e5m2 56.6 / 55.4 / 54.9 / 55.3 / 59.7)
             const unsigned long long block_bytes = 2ull * kBlkPos * hd * 2 * kpc;
-            unsigned long long pad = kn.pad != ~0u ? kn.pad : (cache->dtype == SHADY_F8E4M3 ? 0ull : (256ull << 10) / block_bytes);
+            unsigned long long pad = kn.pad != ~0u ? kn.pad : (256ull << 10) / block_bytes / (f8 ? 2 : 1);
             a.pad = (uint32_t)(pad > 64 ? 64 : pad);
         }
         unsigned long long line = 0;
