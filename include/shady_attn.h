@@ -67,7 +67,8 @@ void *shady_ctx_stream(const shady_ctx *ctx);
 uint64_t shady_ctx_launch_count(const shady_ctx *ctx);
 /* Iteration limits of the bounded device-side waits of this context's later launches (0 keeps a limit as it is):
  * the grid barrier ahead of the in-launch record merge of shady_attn_decode* (default 2^21 polls), a peer's NVLink
- * flag in shady_attn_combine_p2p / shady_attn_decode_shard_p2p (2^22), an mbarrier of shady_attn_prefill (2^20).
+ * flag in shady_attn_combine_p2p / shady_attn_decode_shard_p2p (2^22), an mbarrier of shady_attn_prefill or of the
+ * many-token pass of shady_kv_append_rope / shady_attn_prefill_append (2^20).
  * A wait that runs out makes its kernel skip the rest of its work and return; the next shady_synchronize then
  * returns SHADY_ERR_TIMEOUT once (the message names the wait), outputs of launches since the previous successful
  * shady_synchronize are undefined, and until the status has been collected every launch on the context is refused
