@@ -50,7 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if failed:
         raise RuntimeError("nvcc failed")
     if force or procs or _stale(LIB_PATH, objs):
-        subprocess.check_call([_nvcc(), "-shared", "-o", LIB_PATH, *objs, "-lcudart"])
+        subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB_PATH, *objs, "-lcudart"])
     return LIB_PATH
 
 
