@@ -248,24 +248,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// Instruction-count knobs of the softmax loop (each measured on cfg3; see the profile summary).
-#ifndef SHADY_PF_MAX3
-#define SHADY_PF_MAX3 1      // three-input max for the row maximum
-#endif
-#ifndef SHADY_PF_FMA2
-#define SHADY_PF_FMA2 1      // packed two-lane fp32 FMA/ADD for s*scale-m and the row sum
-#endif
-#ifndef SHADY_PF_POLY
-#define SHADY_PF_POLY 0      // every n-th pair takes 2^x from an FMA-pipe polynomial instead of MUFU (0 = never)
-#endif
+// Instruction savers of the softmax loop: a three-input max for the row maximum, packed two-lane fp32 FMA/ADD for
+// s * scale - m and the row sum.  (2^x from an FMA-pipe polynomial for a share of the elements was measured too:
+// slower, the issue slots it takes cost more than the exponential unit it relieves.)
 __device__ __forceinline__ float max3(float a, float b, float c) {
-#if SHADY_PF_MAX3
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
-#else
-    return fmaxf(a, fmaxf(b, c));
-#endif
 }
 __device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
     unsigned long long r;
@@ -282,16 +271,6 @@ __device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, un
     unsigned long long d;
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
-}
-// 2^x on the FMA pipe (Cody-Waite split + cubic), relative error ~6e-4 — below the 16-bit rounding of P.
-__device__ __forceinline__ float poly_exp2(float x) {
-    x = fmaxf(x, -125.0f);
-    const float t = x + 12582912.0f;             // 1.5 * 2^23: the integer part lands in the low mantissa bits
-    const float f = x - (t - 12582912.0f);       // fraction in [-0.5, 0.5]
-    float p = fmaf(f, 0.0555041f, 0.2402265f);
-    p = fmaf(p, f, 0.6931472f);
-    p = fmaf(p, f, 1.0f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 template <typename T> __device__ __forceinline__ uint32_t pack16(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack16<__half>(float lo, float hi) {
@@ -670,11 +649,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
                 // ---- pass 2: P = exp2(s*scale - m_ref), row sum, pack, store over S; next chunk's load in flight ----
                 const float neg_m = -m_ref;
-                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-    #if SHADY_PF_FMA2
                 const unsigned long long scale2 = pack_f32x2(a.scale_log2, a.scale_log2), negm2 = pack_f32x2(neg_m, neg_m);
                 unsigned long long ls2[2] = {0ull, 0ull};
-    #endif
                 uint32_t vbuf[2][32];
                 tmem_ld32(t_s, vbuf[0]);
     #pragma unroll
@@ -686,43 +662,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         float x0, x1;
-    #if SHADY_PF_FMA2
                         fma_f32x2(x0, x1, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), scale2, negm2);
-    #else
-                        x0 = fmaf(__uint_as_float(v[i]), a.scale_log2, neg_m);
-                        x1 = fmaf(__uint_as_float(v[i + 1]), a.scale_log2, neg_m);
-    #endif
-                        float p0, p1;
-                        if (SHADY_PF_POLY > 0 && ((i >> 1) % (SHADY_PF_POLY > 0 ? SHADY_PF_POLY : 1)) == 0) {
-                            p0 = poly_exp2(x0);
-                            p1 = poly_exp2(x1);
-                        } else {
-                            p0 = fast_exp2(x0);
-                            p1 = fast_exp2(x1);
-                        }
+                        float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                         if (diag) {
                             if (c * 32 + i > lim) p0 = 0.f;
                             if (c * 32 + i + 1 > lim) p1 = 0.f;
                         }
-    #if SHADY_PF_FMA2
                         ls2[(i >> 1) & 1] = add_f32x2(ls2[(i >> 1) & 1], pack_f32x2(p0, p1));
-    #else
-                        ls4[(i >> 1) & 3] += p0 + p1;
-    #endif
                         pk[i >> 1] = pack16<T>(p0, p1);
                     }
                     tmem_st16(t_s + c * 16, pk);
                 }
-    #if SHADY_PF_FMA2
-                {
-                    float s0, s1, s2, s3;
-                    asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(ls2[0]));
-                    asm("mov.b64 {%0, %1}, %2;" : "=f"(s2), "=f"(s3) : "l"(ls2[1]));
-                    ls4[0] = s0 + s1;
-                    ls4[1] = s2 + s3;
-                }
-    #endif
-                l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+                float s0, s1, s2, s3;
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(ls2[0]));
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(s2), "=f"(s3) : "l"(ls2[1]));
+                l_sum += (s0 + s1) + (s2 + s3);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(bar(BAR_PFULL + q));
